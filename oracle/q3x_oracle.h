@@ -1,0 +1,165 @@
+/*
+ * q3x_oracle.h -- CPU restatement of the Qwen3x-Orin host reference ops for the
+ * fused per-layer elementwise / normalisation path.
+ *
+ * TEST INFRASTRUCTURE ONLY.  This library is the checker for the CUDA path: it is
+ * loaded by the tests, by the smoke check and by the bench's cpu_baseline leg, and by
+ * nothing else.  The product library never links or calls it.
+ *
+ * Every function restates, in plain C, the algorithm of one reference function and
+ * names that function (path inside the reference project : line).  Arithmetic is IEEE
+ * binary32 with no contraction (build with -ffp-contract=off): the sums are the same
+ * left-to-right FP32 sums the reference performs, so results are bit-identical to the
+ * reference compiled with an ISO-conforming compiler.
+ *
+ * Pinning: the restatement is compared bit-for-bit with the reference's own sources
+ * compiled from where they lie (oracle/_ref, see oracle/Makefile) and with the
+ * committed fixtures under tests/golden/.
+ *
+ * NVFP4 ACTIVATION ENCODER: PARITY UNPINNED.  The reference only decodes NVFP4
+ * (src/quantization/nvfp4.cpp:9-59) and only encodes E4M3 per tensor
+ * (src/kernels/reference/gemv_reference.cpp:35-62).  The encoder here is a new
+ * specification built from those primitives; it is pinned at the primitive level
+ * (E2M1/E4M3 value tables, E4M3 round-to-nearest-even with saturation, nibble order,
+ * the dequantisation formula) and not as a whole.
+ *
+ * All tensors are raw bfloat16 bits in uint16_t, row-major.
+ */
+#ifndef Q3X_ORACLE_H_
+#define Q3X_ORACLE_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Status values follow DecodeOpStatus (include/q3x/runtime/decode_ops.h:52-59). */
+enum {
+  Q3X_ORACLE_OK = 0,
+  Q3X_ORACLE_INVALID_ARGUMENT = 1,
+  Q3X_ORACLE_INVALID_DIMENSION = 2,
+  Q3X_ORACLE_SIZE_OVERFLOW = 3,
+  Q3X_ORACLE_TOKEN_OUT_OF_RANGE = 4,
+  Q3X_ORACLE_INVALID_ALIAS = 5,       /* GdnStatus::kInvalidAlias, LayoutOpStatus::kOverlappingStorage */
+  Q3X_ORACLE_INVALID_COLUMN_COUNT = 6 /* NvFp4Status::kInvalidColumnCount */
+};
+
+/* bf16 codec: src/runtime/reference/decode_ops.cpp:15-33 */
+float q3x_oracle_decode_bf16(uint16_t bits);
+uint16_t q3x_oracle_encode_bf16(float value);
+
+/* src/runtime/reference/decode_ops.cpp:287-300 */
+int q3x_oracle_fp32_to_bf16(const float* in, size_t count, uint16_t* out);
+
+/* Prompt form of src/runtime/reference/decode_ops.cpp:191-212: one call per token id;
+ * a token id outside the vocabulary leaves its output row untouched (device kernel rule,
+ * src/kernels/reference/decode_ops.cu:374-391) and the call returns TOKEN_OUT_OF_RANGE
+ * after finishing the other rows. */
+int q3x_oracle_embedding_gather(const uint16_t* table, size_t vocab, size_t hidden,
+                                const uint32_t* token_ids, size_t token_count, uint16_t* out);
+
+/* src/runtime/reference/decode_ops.cpp:52-84 (centered: gamma = 1 + w) and :86-133 */
+int q3x_oracle_rms_norm(const uint16_t* in, const uint16_t* weight, size_t width, float eps,
+                        int centered, uint16_t* out);
+int q3x_oracle_headwise_rms_norm(const uint16_t* in, const uint16_t* weight,
+                                 const uint16_t* gate /* NULL = no SiLU gate */, size_t heads,
+                                 size_t dim, float eps, int centered, uint16_t* out);
+
+/* src/runtime/reference/decode_ops.cpp:268-284 */
+int q3x_oracle_residual_add(const uint16_t* left, const uint16_t* right, size_t count,
+                            uint16_t* out);
+
+/* The two-op chain that the fused launchers must equal bit for bit
+ * (include/q3x/runtime/decode_ops.h:230-246): residual = bf16(left+right) per token row,
+ * then centered RMSNorm of the ROUNDED residual.  normalized may be NULL. */
+int q3x_oracle_residual_add_rms_norm(const uint16_t* left, const uint16_t* right,
+                                     const uint16_t* weight, size_t tokens, size_t hidden,
+                                     float eps, uint16_t* residual, uint16_t* normalized);
+
+/* src/runtime/reference/decode_ops.cpp:302-319; merged form = gate in columns [0,I),
+ * up in [I,2I) of each row (src/kernels/sm87/nvfp4_marlin_w4a16.cu:211-227). */
+int q3x_oracle_silu_mul(const uint16_t* gate, const uint16_t* up, size_t count, uint16_t* out);
+int q3x_oracle_silu_mul_merged(const uint16_t* merged, size_t tokens, size_t intermediate,
+                               uint16_t* out);
+
+/* src/runtime/reference/decode_ops.cpp:321-342 */
+int q3x_oracle_sigmoid_gate(const uint16_t* value, const uint16_t* gate, size_t count,
+                            uint16_t* out);
+
+/* src/runtime/reference/decode_ops.cpp:344-376.  scale multiplies the normalised value
+ * before the bf16 rounding; 1.0f reproduces the reference function exactly, 1/sqrt(128)
+ * gives the prefill compact-q form (src/kernels/reference/
+ * gdn_prefill_whole_span_conv_sm87.cu:344-371). */
+int q3x_oracle_l2_normalize_heads(const uint16_t* in, size_t heads, size_t dim, float eps,
+                                  float scale, uint16_t* out);
+
+/* src/runtime/reference/decode_ops.cpp:378-411: cos/sin hold 32 floats for ONE position. */
+int q3x_oracle_partial_neox_rope_256_64(const uint16_t* in, const float* cosines,
+                                        const float* sines, size_t heads, uint16_t* out);
+
+/* src/runtime/request_state.cpp:2092-2108 (+ :326-334): [positions,32] tables, values
+ * passed through bf16 and stored as FP32. */
+void q3x_oracle_rope_tables(size_t first_position, size_t positions, float* cosines,
+                            float* sines);
+
+/* src/runtime/reference/layout_ops.cpp:93-113 */
+int q3x_oracle_split_interleaved_q_gate(const uint16_t* in, size_t heads, size_t dim,
+                                        uint16_t* q_out, uint16_t* gate_out);
+
+/* The chain behind launch_full_attention_preprocess_24_4_256_64_cuda
+ * (include/q3x/runtime/decode_ops.h:318-377): split, centered head norm of q (24 heads)
+ * and k (4 heads, in place), partial RoPE of both with table row first_position + t.
+ * cos/sin are the bases of [position,32] tables. */
+int q3x_oracle_full_attention_preprocess(const uint16_t* interleaved_q_gate, uint16_t* key,
+                                         const uint16_t* q_weight, const uint16_t* k_weight,
+                                         float eps, uint16_t* q_out, uint16_t* gate_out,
+                                         const float* cosines, const float* sines,
+                                         size_t first_position, size_t tokens);
+
+/* src/runtime/reference/gdn_decode.cpp:141-184 applied to `tokens` rows in order.
+ * raw/out are [tokens,channels]; weight [channels,4]; history [channels,3] oldest->newest,
+ * updated in place with the RAW inputs.  channels = 10240 reproduces the reference. */
+int q3x_oracle_causal_conv1d_silu(const uint16_t* raw, size_t tokens, size_t channels,
+                                  const uint16_t* weight, uint16_t* history, uint16_t* out);
+
+/* ---- NVFP4 primitives (src/quantization/nvfp4.cpp:9-59) ---- */
+float q3x_oracle_decode_e2m1(uint8_t nibble);
+float q3x_oracle_decode_e4m3fn(uint8_t bits);
+/* Round-to-nearest-even over the finite codes 0x00..0x7e with saturation at 448, the
+ * rule of src/kernels/reference/gemv_reference.cpp:35-62.  NaN -> 0x7f. */
+uint8_t q3x_oracle_encode_e4m3fn(float value);
+/* Nearest-even onto {0,.5,1,1.5,2,3,4,6} with saturation; NaN -> 0x7. */
+uint8_t q3x_oracle_encode_e2m1(float value);
+
+/* src/quantization/nvfp4.cpp:75-113 */
+int q3x_oracle_nvfp4_dequantize(const uint8_t* codes, const uint8_t* scales,
+                                float global_scale, size_t rows, size_t cols, float* out);
+
+/* NEW (parity unpinned).  Rows are grouped `rows_per_scale` at a time (0 = all rows in one
+ * group); each group g has one FP32 global scale:
+ *   A      = max |x| over the FINITE elements of the group (x = decode_bf16(in))
+ *   global = A == 0 ? 1.0f : A / 2688.0f
+ *   k      = 1.0f / (global * 6.0f)
+ * and per 16-element block b of a row:
+ *   s   = encode_e4m3fn(amax_b * k)                     (amax_b over finite elements)
+ *   d   = decode_e4m3fn(s) * global
+ *   inv = d == 0 ? 0 : min(1.0f / d, FLT_MAX)
+ *   code_i = encode_e2m1(x_i * inv), even column in the low nibble.
+ * Outputs: codes [rows, cols/2], scales [rows, cols/16], global_scales [groups]. */
+int q3x_oracle_nvfp4_quantize(const uint16_t* in, size_t rows, size_t cols,
+                              size_t rows_per_scale, uint8_t* codes, uint8_t* scales,
+                              float* global_scales);
+/* Same, with the global scales supplied by the caller instead of derived. */
+int q3x_oracle_nvfp4_quantize_with_scales(const uint16_t* in, size_t rows, size_t cols,
+                                          size_t rows_per_scale, const float* global_scales,
+                                          uint8_t* codes, uint8_t* scales);
+/* The group amax itself, as bf16 magnitude bits widened to float. */
+int q3x_oracle_group_amax(const uint16_t* in, size_t rows, size_t cols, size_t rows_per_scale,
+                          float* amax_out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* Q3X_ORACLE_H_ */
