@@ -1,0 +1,231 @@
+/*
+ * q3x_b200.h -- C ABI of libq3x_b200.so: the B200 (sm_100a) implementation of the fused
+ * per-layer elementwise / normalisation operators of the Qwen3.6-27B hybrid model
+ * (gated-delta-net + full-attention layers).
+ *
+ * Each entry point is what a binding of the reference project's operator API for this path
+ * would call; the comment above it names the reference declaration it stands in for (path
+ * inside the reference project : line).
+ *
+ * Conventions (those of the reference launchers, include/q3x/runtime/decode_ops.h:172-176):
+ *   - every tensor pointer is device-accessible memory; bf16 tensors are raw bfloat16 bits in
+ *     uint16_t, row-major; arithmetic is FP32, outputs are rounded to nearest-even;
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream);
+ *   - the return value is a cudaError_t as int; 0 = the work was enqueued;
+ *   - a call allocates nothing, copies nothing to the host and never synchronises;
+ *   - invalid host-visible arguments return cudaErrorInvalidValue (1) BEFORE anything is
+ *     enqueued; a valid shape this build has no kernel for returns cudaErrorNotSupported (801);
+ *   - an empty shape is a successful no-op, even with NULL pointers;
+ *   - a stale CUDA last-error of the calling thread is cleared before the first launch, and the
+ *     value returned is the status of this call's own launches.
+ * Aliasing: an output may be EXACTLY an input where stated; every partial overlap is rejected.
+ * Any alignment is accepted; 16-byte aligned pointers with widths that are multiples of 8
+ * elements take the 128-bit fast paths, everything else a scalar path with identical results.
+ */
+#ifndef Q3X_B200_H_
+#define Q3X_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define Q3X_B200_ABI_VERSION 1
+
+/* Model constants of the path (include/q3x/runtime/decode_ops.h:8-9,39;
+ * include/q3x/runtime/gdn_decode.h:8-22). */
+#define Q3X_B200_HIDDEN 5120
+#define Q3X_B200_Q_HEADS 24
+#define Q3X_B200_KV_HEADS 4
+#define Q3X_B200_ATTN_HEAD_DIM 256
+#define Q3X_B200_ROTARY_DIM 64
+#define Q3X_B200_GDN_QK_HEADS 16
+#define Q3X_B200_GDN_V_HEADS 48
+#define Q3X_B200_GDN_HEAD_DIM 128
+#define Q3X_B200_GDN_CHANNELS 10240
+#define Q3X_B200_NVFP4_BLOCK 16
+
+int q3x_b200_abi_version(void);
+/* cudaGetErrorString of a value returned by any entry point (diagnostics only). */
+const char* q3x_b200_error_string(int status);
+
+/* ---------------------------------------------------------------- embedding */
+
+/* launch_embedding_gather_prompt_reference_cuda (include/q3x/runtime/decode_ops.h:192-196);
+ * with token_count == 1 also launch_embedding_gather_reference_cuda (:178-181) once the id is
+ * on the device.  out[t,:] = table[ids[t],:], a bitwise copy.  An id >= vocab leaves its
+ * output row untouched.  table, ids and out must be pairwise disjoint. */
+int q3x_b200_embedding_gather(const uint16_t* table, size_t vocab, size_t hidden,
+                              const uint32_t* token_ids, size_t token_count, uint16_t* out,
+                              void* stream);
+
+/* ---------------------------------------------------------------- RMS norms */
+
+/* launch_centered_rms_norm_reference_cuda / launch_plain_rms_norm_reference_cuda (rows = 1)
+ * and launch_headwise_centered_/plain_rms_norm_reference_cuda (decode_ops.h:198-216):
+ * y = bf16(x * 1/sqrt(mean(x^2)+eps) * (w [+1 if centered])) for each of `rows` rows of
+ * `width` elements sharing one weight vector.  out may be exactly in. */
+int q3x_b200_rms_norm(const uint16_t* in, const uint16_t* weight, size_t rows, size_t width,
+                      float eps, int centered, uint16_t* out, void* stream);
+
+/* launch_headwise_plain_rms_norm_silu_gate_reference_cuda (decode_ops.h:218-222): plain norm
+ * times silu(gate) in FP32, one rounding.  out may be exactly in or exactly gate. */
+int q3x_b200_rms_norm_silu_gate(const uint16_t* in, const uint16_t* weight, const uint16_t* gate,
+                                size_t rows, size_t width, float eps, uint16_t* out,
+                                void* stream);
+
+/* launch_l2_normalize_heads_reference_cuda (decode_ops.h:300-303): y = bf16(x * s) with
+ * s = scale / sqrt(sum(x^2)+eps) (scale folded into the factor first).  scale = 1 is the
+ * reference op; 1/sqrt(128) is the q form of the prefill compact layout
+ * (src/kernels/reference/gdn_prefill_whole_span_conv_sm87.cu:344-371). */
+int q3x_b200_l2_normalize_heads(const uint16_t* in, size_t heads, size_t dim, float eps,
+                                float scale, uint16_t* out, void* stream);
+
+/* ---------------------------------------------------------------- residual stream */
+
+/* launch_residual_add_reference_cuda (decode_ops.h:228-231): out = bf16(left+right).
+ * left/right disjoint; out may be exactly left or exactly right. */
+int q3x_b200_residual_add(const uint16_t* left, const uint16_t* right, size_t count,
+                          uint16_t* out, void* stream);
+
+/* launch_residual_add_centered_rms_norm_5120_cuda (decode_ops.h:238-243, tokens = 1),
+ * launch_residual_add_headwise_centered_rms_norm_m32_5120_cuda (:252-259) and
+ * ..._prefill_5120_cuda (:265-272), for any token count and any hidden size:
+ * residual = bf16(left+right); normalized = centred RMSNorm of the ROUNDED residual, bit-equal
+ * to the two-op chain.  residual_out must be disjoint from everything; normalized_out may be
+ * exactly `right`, NULL skips it. */
+int q3x_b200_residual_add_rms_norm(const uint16_t* left, const uint16_t* right,
+                                   const uint16_t* weight, size_t tokens, size_t hidden,
+                                   float eps, uint16_t* residual_out, uint16_t* normalized_out,
+                                   void* stream);
+
+/* ---------------------------------------------------------------- NVFP4 activations
+ * No counterpart in the reference, which only decodes NVFP4 weights
+ * (include/q3x/quantization/nvfp4.h:28-34 gives the scale convention this follows:
+ * real = E2M1(code) * E4M3(block scale) * global scale, global = amax / 2688; 16-element blocks;
+ * even column in the low nibble).  Rows are grouped `rows_per_scale` at a time (0 = one group);
+ * group g owns global_scales[g].  codes [rows, cols/2], scales [rows, cols/16] row-major. */
+
+/* Scratch words one amax reduction needs: one uint32 per scale group. */
+size_t q3x_b200_nvfp4_group_count(size_t rows, size_t rows_per_scale);
+
+/* amax_bits[g] = largest finite |x| of group g as bf16 magnitude bits (uint32).  The call
+ * zeroes amax_bits itself. */
+int q3x_b200_group_amax(const uint16_t* in, size_t rows, size_t cols, size_t rows_per_scale,
+                        uint32_t* amax_bits, void* stream);
+/* global_scales[g] = amax == 0 ? 1 : amax / 2688. */
+int q3x_b200_amax_to_global_scale(const uint32_t* amax_bits, size_t groups, float* global_scales,
+                                  void* stream);
+/* Quantise with the given global scales. */
+int q3x_b200_nvfp4_quantize(const uint16_t* in, size_t rows, size_t cols, size_t rows_per_scale,
+                            const float* global_scales, uint8_t* codes, uint8_t* scales,
+                            void* stream);
+/* The three steps above in one call (amax_scratch: q3x_b200_nvfp4_group_count words). */
+int q3x_b200_nvfp4_quantize_dynamic(const uint16_t* in, size_t rows, size_t cols,
+                                    size_t rows_per_scale, uint32_t* amax_scratch,
+                                    float* global_scales_out, uint8_t* codes, uint8_t* scales,
+                                    void* stream);
+
+/* Residual add + centred RMSNorm + NVFP4 of the normalised rows, global scale from the group
+ * amax.  normalized_out is required (it is the operand the codes are derived from, bit for
+ * bit); it may be exactly `right`.  amax_scratch: q3x_b200_nvfp4_group_count words. */
+int q3x_b200_residual_add_rms_norm_nvfp4(const uint16_t* left, const uint16_t* right,
+                                         const uint16_t* weight, size_t tokens, size_t hidden,
+                                         float eps, size_t rows_per_scale, uint16_t* residual_out,
+                                         uint16_t* normalized_out, uint32_t* amax_scratch,
+                                         float* global_scales_out, uint8_t* codes, uint8_t* scales,
+                                         void* stream);
+
+/* Gated RMSNorm * silu(z) + NVFP4 of its output rows.  `heads_per_row` heads of `dim` form one
+ * quantisation row (48 x 128 = 6144 for the GDN output). */
+int q3x_b200_rms_norm_silu_gate_nvfp4(const uint16_t* in, const uint16_t* weight,
+                                      const uint16_t* gate, size_t tokens, size_t heads_per_row,
+                                      size_t dim, float eps, size_t rows_per_scale, uint16_t* out,
+                                      uint32_t* amax_scratch, float* global_scales_out,
+                                      uint8_t* codes, uint8_t* scales, void* stream);
+
+/* Diagnostics (no counterpart in the reference): the two narrow conversions the quantiser uses,
+ * one value per output byte.  format 0 = E4M3 round-to-nearest-even with saturation at 448,
+ * format 1 = E2M1 (code in the low nibble). */
+int q3x_b200_debug_encode(const float* in, size_t count, int format, uint8_t* out, void* stream);
+/* Diagnostics: returns the CUDA last-error pending in this library's runtime without clearing it;
+ * with plant != 0 first leaves a stale host-side argument error there (nothing reaches the GPU),
+ * which the next entry point must clear before its own launch
+ * (the stale-error rule the reference tests with launch_after_stale,
+ * tests/decode_ops_cuda_test.cu:374-387). */
+int q3x_b200_debug_stale_error(int plant);
+
+/* ---------------------------------------------------------------- full attention */
+
+/* launch_split_interleaved_q_gate_reference_cuda (include/q3x/runtime/layout_ops.h:35-38) */
+int q3x_b200_split_interleaved_q_gate(const uint16_t* in, size_t heads, size_t dim,
+                                      uint16_t* q_out, uint16_t* gate_out, void* stream);
+
+/* launch_partial_neox_rope_256_64_reference_cuda (decode_ops.h:305-308): one position,
+ * cos/sin [32] FP32; out may be exactly in. */
+int q3x_b200_partial_neox_rope_256_64(const uint16_t* in, const float* cosines,
+                                      const float* sines, size_t heads, uint16_t* out,
+                                      void* stream);
+
+/* launch_qk_partial_neox_rope_tile_24_4_256_64_cuda (decode_ops.h:314-317): in-place rotation of
+ * query [tokens,24,256] and key [tokens,4,256] with [position,32] tables; any tokens >= 1. */
+int q3x_b200_qk_partial_neox_rope(uint16_t* query, uint16_t* key, const float* cosines,
+                                  const float* sines, size_t first_position, size_t tokens,
+                                  void* stream);
+
+/* launch_full_attention_preprocess_24_4_256_64_cuda and its _reference_256 / _prompt_wide_p8000
+ * forms (decode_ops.h:333-377): split q|gate, centred head norm of q and (in place) k, partial
+ * RoPE of both at positions first_position + t.  Any tokens >= 1 (the reference admits <= 512
+ * or exactly 8000).  Writable tensors must not overlap each other or any input. */
+int q3x_b200_full_attention_preprocess(const uint16_t* interleaved_q_gate, uint16_t* key,
+                                       const uint16_t* q_weight, const uint16_t* k_weight,
+                                       float eps, uint16_t* q_out, uint16_t* gate_out,
+                                       const float* cosines, const float* sines,
+                                       size_t first_position, size_t tokens, void* stream);
+
+/* launch_sigmoid_gate_reference_cuda (decode_ops.h:295-298): out = bf16(value * sigmoid(gate));
+ * out may be exactly value or exactly gate. */
+int q3x_b200_sigmoid_gate(const uint16_t* value, const uint16_t* gate, size_t count,
+                          uint16_t* out, void* stream);
+
+/* ---------------------------------------------------------------- MLP */
+
+/* launch_silu_mul_reference_cuda (decode_ops.h:290-293): out = bf16(silu(gate) * up);
+ * out may be exactly gate or exactly up. */
+int q3x_b200_silu_mul(const uint16_t* gate, const uint16_t* up, size_t count, uint16_t* out,
+                      void* stream);
+/* The merged-projection layout of src/kernels/sm87/nvfp4_marlin_w4a16.cu:211-227:
+ * merged [tokens, 2*intermediate], gate first; out [tokens, intermediate], disjoint. */
+int q3x_b200_silu_mul_merged(const uint16_t* merged, size_t tokens, size_t intermediate,
+                             uint16_t* out, void* stream);
+
+/* launch_fp32_to_bf16_reference_cuda (decode_ops.h:274-276) */
+int q3x_b200_fp32_to_bf16(const float* in, size_t count, uint16_t* out, void* stream);
+
+/* ---------------------------------------------------------------- gated delta net */
+
+/* launch_causal_conv1d_silu_update_reference_cuda (tokens = 1), ..._tile_reference_cuda
+ * (include/q3x/runtime/gdn_decode.h:75-93) and the prefill whole-span / token-parallel launchers
+ * (src/kernels/reference/gdn_prefill_whole_span_conv_sm87.h), for any token count:
+ * out[t,c] = bf16(silu(fma chain over raw[t-3..t,c] and w[c,0..3])), history [channels,3]
+ * (oldest first) supplies rows before t = 0 and receives the last three RAW rows.
+ * channels must be 10240 and every pointer 16-byte aligned (else cudaErrorNotSupported).
+ * raw may be exactly out (serial path: one token run per channel block). */
+int q3x_b200_causal_conv1d_silu(const uint16_t* raw, size_t tokens, size_t channels,
+                                const uint16_t* conv_weight, uint16_t* history_in_out,
+                                uint16_t* out, void* stream);
+
+/* The conv above with the q/k L2 norm applied to its rounded output in the same pass
+ * (channels [0,2048) = q heads, [2048,4096) = k heads of 128; q additionally times q_scale):
+ * the prefill fusion of gdn_prefill_whole_span_conv_sm87.cu:210-373, written token-major in
+ * place of the compact chunk layout.  raw and out must be disjoint. */
+int q3x_b200_causal_conv1d_silu_l2norm(const uint16_t* raw, size_t tokens,
+                                       const uint16_t* conv_weight, uint16_t* history_in_out,
+                                       float l2_eps, float q_scale, uint16_t* out, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* Q3X_B200_H_ */

@@ -467,7 +467,7 @@ int q3x_oracle_nvfp4_quantize_with_scales(const uint16_t* in, size_t rows, size_
         uint16_t m = finite_mag(x[i]);
         if (m > top) top = m;
       }
-      uint8_t s = q3x_oracle_encode_e4m3fn(DEC(top) * k);
+      uint8_t s = top == 0 ? 0 : q3x_oracle_encode_e4m3fn(DEC(top) * k);
       scales[r * (cols / 16) + b] = s;
       float d = q3x_oracle_decode_e4m3fn(s) * global;
       float inv = 0.0f;

@@ -143,7 +143,7 @@ int q3x_oracle_nvfp4_dequantize(const uint8_t* codes, const uint8_t* scales,
  *   global = A == 0 ? 1.0f : A / 2688.0f
  *   k      = 1.0f / (global * 6.0f)
  * and per 16-element block b of a row:
- *   s   = encode_e4m3fn(amax_b * k)                     (amax_b over finite elements)
+ *   s   = amax_b == 0 ? 0 : encode_e4m3fn(amax_b * k)   (amax_b over finite elements)
  *   d   = decode_e4m3fn(s) * global
  *   inv = d == 0 ? 0 : min(1.0f / d, FLT_MAX)
  *   code_i = encode_e2m1(x_i * inv), even column in the low nibble.

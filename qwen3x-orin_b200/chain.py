@@ -1,0 +1,190 @@
+"""The per-layer operator chains of the 64-layer hybrid stack, driven through the C ABI.
+
+A `LayerStack` owns the device buffers of one token shard and enqueues, layer by layer, exactly the
+fused operators the reference runner calls between its projections
+(src/runtime/reference_runner.cpp:9565-10584): the projections themselves are out of scope, so their
+outputs are synthetic tensors that stay fixed while the residual stream, the key rows and the conv
+histories evolve.  Layer l is a full-attention layer when (l + 1) % 4 == 0, else a gated-delta-net
+layer (reference_runner.cpp:1463-1471).
+
+Per layer:
+  GDN : residual+RMSNorm+NVFP4 -> conv1d+SiLU+q/k L2 norm -> gated RMSNorm*silu(z)+NVFP4
+        -> residual+RMSNorm+NVFP4 -> SwiGLU
+  FA  : residual+RMSNorm+NVFP4 -> split+q/k head norm+RoPE -> sigmoid gate
+        -> residual+RMSNorm+NVFP4 -> SwiGLU
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+
+from . import capi
+
+HIDDEN = 5120
+INTERMEDIATE = 17408
+VOCAB = 248320
+LAYERS = 64
+Q_HEADS, KV_HEADS, HEAD_DIM = 24, 4, 256
+GDN_CHANNELS, GDN_V = 10240, 48 * 128
+CHUNK = 512            # the reference's prefill chunk: the scope of one NVFP4 global scale
+EPS = 1e-6
+ROPE_THETA = 1e7
+
+# Algorithmic HBM bytes per token of each fused operator: every input read once, every output
+# written once, weights amortised.
+BYTES_PER_TOKEN = {
+    "embedding_gather": 2 * HIDDEN * 2 + 4,
+    "residual_rmsnorm_nvfp4": 4 * HIDDEN * 2 + HIDDEN // 2 + HIDDEN // 16,
+    "conv1d_silu_l2norm": 2 * GDN_CHANNELS * 2,
+    "gated_rmsnorm_nvfp4": 3 * GDN_V * 2 + GDN_V // 2 + GDN_V // 16,
+    "attention_preprocess": (2 * Q_HEADS + KV_HEADS) * HEAD_DIM * 2 + 256 + (2 * Q_HEADS + KV_HEADS) * HEAD_DIM * 2,
+    "sigmoid_gate": 3 * Q_HEADS * HEAD_DIM * 2,
+    "swiglu": 3 * INTERMEDIATE * 2,
+}
+# kernels each entry point launches (memset nodes not counted)
+KERNELS = {
+    "embedding_gather": 1, "residual_rmsnorm_nvfp4": 3, "conv1d_silu_l2norm": 1, "gated_rmsnorm_nvfp4": 3,
+    "attention_preprocess": 1, "sigmoid_gate": 1, "swiglu": 1,
+}
+GDN_OPS = ["residual_rmsnorm_nvfp4", "conv1d_silu_l2norm", "gated_rmsnorm_nvfp4", "residual_rmsnorm_nvfp4", "swiglu"]
+FA_OPS = ["residual_rmsnorm_nvfp4", "attention_preprocess", "sigmoid_gate", "residual_rmsnorm_nvfp4", "swiglu"]
+
+
+def is_full_attention(layer: int) -> bool:
+    return (layer + 1) % 4 == 0
+
+
+def layer_ops(layer: int):
+    return FA_OPS if is_full_attention(layer) else GDN_OPS
+
+
+def bytes_per_token_per_step(layers: int = LAYERS) -> int:
+    total = BYTES_PER_TOKEN["embedding_gather"]
+    for l in range(layers):
+        total += sum(BYTES_PER_TOKEN[o] for o in layer_ops(l))
+    return total
+
+
+def kernels_per_step(layers: int = LAYERS) -> int:
+    return KERNELS["embedding_gather"] + sum(KERNELS[o] for l in range(layers) for o in layer_ops(l))
+
+
+def rope_tables(first_position: int, positions: int, device):
+    """[positions, 32] cos / sin FP32 tables whose values went through bf16, the recipe of the
+    reference's request state (src/runtime/request_state.cpp:2092-2108)."""
+    pair = torch.arange(32, dtype=torch.float32)
+    inv = 1.0 / torch.pow(torch.tensor(ROPE_THETA, dtype=torch.float32), 2.0 * pair / 64.0)
+    pos = torch.arange(first_position, first_position + positions, dtype=torch.float32)[:, None]
+    ang = pos * inv[None, :]
+    cos = torch.cos(ang).to(torch.bfloat16).to(torch.float32)
+    sin = torch.sin(ang).to(torch.bfloat16).to(torch.float32)
+    return cos.to(device).contiguous(), sin.to(device).contiguous()
+
+
+@dataclass
+class ShardInputs:
+    """Names of the synthetic per-shard inputs, their per-token widths (bf16 elements) and std."""
+    names = ("proj_out", "conv_raw", "gdn_core", "gdn_z", "q_gate", "key", "attn_value", "mlp_gate", "mlp_up")
+    widths = (HIDDEN, GDN_CHANNELS, GDN_V, GDN_V, 2 * Q_HEADS * HEAD_DIM, KV_HEADS * HEAD_DIM, Q_HEADS * HEAD_DIM,
+              INTERMEDIATE, INTERMEDIATE)
+
+
+class LayerStack:
+    """Device state of one token shard: synthetic projection outputs, weights, evolving tensors."""
+
+    def __init__(self, tokens: int, first_position: int = 0, seed: int = 0, device="cuda", layers: int = LAYERS,
+                 table_rows: int = VOCAB):
+        self.tokens, self.layers, self.first_position = tokens, layers, first_position
+        dev = torch.device(device)
+        gen = torch.Generator(device=dev).manual_seed(seed)
+
+        def normal(shape, std=1.0):
+            return (torch.randn(shape, generator=gen, device=dev, dtype=torch.float32) * std).to(torch.bfloat16)
+
+        T = tokens
+        self.inputs = {n: normal((T, w)) for n, w in zip(ShardInputs.names, ShardInputs.widths)}
+        self.table = normal((table_rows, HIDDEN), 0.02)
+        self.token_ids = torch.randint(0, table_rows, (T,), generator=gen, device=dev, dtype=torch.int64).to(torch.int32)
+        # weights: distinct per layer, all tiny
+        self.norm_w = normal((layers, 2, HIDDEN), 0.02)
+        self.q_norm_w = normal((layers, HEAD_DIM), 0.02)
+        self.k_norm_w = normal((layers, HEAD_DIM), 0.02)
+        self.gdn_norm_w = (1.0 + normal((layers, 128), 0.1).float()).to(torch.bfloat16)
+        self.conv_w = normal((layers, GDN_CHANNELS, 4), 0.5)
+        self.conv_hist = torch.zeros((layers, GDN_CHANNELS, 3), device=dev, dtype=torch.bfloat16)
+        self.cos, self.sin = rope_tables(0, first_position + T, dev)
+        # evolving / output tensors
+        bf = dict(device=dev, dtype=torch.bfloat16)
+        self.residual = [torch.empty((T, HIDDEN), **bf) for _ in range(2)]
+        self.normalized = torch.empty((T, HIDDEN), **bf)
+        self.conv_out = torch.empty((T, GDN_CHANNELS), **bf)
+        self.gdn_out = torch.empty((T, GDN_V), **bf)
+        self.q_out = torch.empty((T, Q_HEADS * HEAD_DIM), **bf)
+        self.gate_out = torch.empty((T, Q_HEADS * HEAD_DIM), **bf)
+        self.attn_out = torch.empty((T, Q_HEADS * HEAD_DIM), **bf)
+        self.mlp_out = torch.empty((T, INTERMEDIATE), **bf)
+        groups = max(1, math.ceil(T / CHUNK))
+        self.groups = groups
+        self.amax = torch.zeros(groups, device=dev, dtype=torch.int32)
+        self.global_scales = torch.empty(groups, device=dev, dtype=torch.float32)
+        self.codes = torch.empty((T, HIDDEN // 2), device=dev, dtype=torch.uint8)
+        self.scales = torch.empty((T, HIDDEN // 16), device=dev, dtype=torch.uint8)
+        self.gdn_codes = torch.empty((T, GDN_V // 2), device=dev, dtype=torch.uint8)
+        self.gdn_scales = torch.empty((T, GDN_V // 16), device=dev, dtype=torch.uint8)
+        self.q_scale = 1.0 / math.sqrt(128.0)
+
+    # ---- individual operators (each is one C-ABI call) ------------------------------------
+    def op_embedding(self, stream):
+        capi.check("q3x_b200_embedding_gather", self.table, self.table.shape[0], HIDDEN, self.token_ids, self.tokens,
+                   self.residual[0], stream)
+
+    def op_residual_norm(self, layer, which, src, dst, stream):
+        capi.check("q3x_b200_residual_add_rms_norm_nvfp4", self.residual[src], self.inputs["proj_out"],
+                   self.norm_w[layer, which], self.tokens, HIDDEN, EPS, CHUNK, self.residual[dst], self.normalized,
+                   self.amax, self.global_scales, self.codes, self.scales, stream)
+
+    def op_conv(self, layer, stream):
+        capi.check("q3x_b200_causal_conv1d_silu_l2norm", self.inputs["conv_raw"], self.tokens, self.conv_w[layer],
+                   self.conv_hist[layer], EPS, self.q_scale, self.conv_out, stream)
+
+    def op_gated_norm(self, layer, stream):
+        capi.check("q3x_b200_rms_norm_silu_gate_nvfp4", self.inputs["gdn_core"], self.gdn_norm_w[layer],
+                   self.inputs["gdn_z"], self.tokens, 48, 128, EPS, CHUNK, self.gdn_out, self.amax,
+                   self.global_scales, self.gdn_codes, self.gdn_scales, stream)
+
+    def op_preprocess(self, layer, stream):
+        capi.check("q3x_b200_full_attention_preprocess", self.inputs["q_gate"], self.inputs["key"], self.q_norm_w[layer],
+                   self.k_norm_w[layer], EPS, self.q_out, self.gate_out, self.cos, self.sin, self.first_position,
+                   self.tokens, stream)
+
+    def op_sigmoid_gate(self, stream):
+        capi.check("q3x_b200_sigmoid_gate", self.inputs["attn_value"], self.gate_out, self.tokens * Q_HEADS * HEAD_DIM,
+                   self.attn_out, stream)
+
+    def op_swiglu(self, stream):
+        capi.check("q3x_b200_silu_mul", self.inputs["mlp_gate"], self.inputs["mlp_up"], self.tokens * INTERMEDIATE,
+                   self.mlp_out, stream)
+
+    # ---- the whole step ------------------------------------------------------------------------
+    def enqueue_step(self, stream) -> int:
+        """Embedding gather + every layer's chain on `stream` (a raw cudaStream_t).  Returns the
+        index of the residual buffer that holds the final residual stream."""
+        # (the key rows are normalised and rotated in place by every full-attention layer, as the
+        # reference does inside its KV cache; they stay bounded, so no reset is needed per step)
+        self.op_embedding(stream)
+        cur = 0
+        for layer in range(self.layers):
+            self.op_residual_norm(layer, 0, cur, 1 - cur, stream)
+            cur = 1 - cur
+            if is_full_attention(layer):
+                self.op_preprocess(layer, stream)
+                self.op_sigmoid_gate(stream)
+            else:
+                self.op_conv(layer, stream)
+                self.op_gated_norm(layer, stream)
+            self.op_residual_norm(layer, 1, cur, 1 - cur, stream)
+            cur = 1 - cur
+            self.op_swiglu(stream)
+        return cur

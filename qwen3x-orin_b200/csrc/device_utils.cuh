@@ -1,0 +1,139 @@
+// Device helpers shared by every kernel of the library: the bfloat16 codec, 128-bit global
+// accesses with cache hints, warp / block reductions and the SiLU / sigmoid forms.
+//
+// Numerical contract (the reference's host ops, src/runtime/reference/decode_ops.cpp:15-33):
+// bf16 -> FP32 is exact; FP32 -> bf16 rounds to nearest-even; no fast-math anywhere.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace q3x {
+
+constexpr int kWarp = 32;
+constexpr unsigned kFullMask = 0xffffffffu;
+
+// ---------------------------------------------------------------------------- bf16 codec
+
+__device__ __forceinline__ float bf16_lo(uint32_t packed) { return __uint_as_float(packed << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t packed) { return __uint_as_float(packed & 0xffff0000u); }
+__device__ __forceinline__ float bf16_to_float(uint16_t bits) {
+  return __uint_as_float(static_cast<uint32_t>(bits) << 16);
+}
+
+// Exact integer rule of the reference: RNE, a NaN keeps sign and upper payload and gets the quiet
+// bit.  Needed where an FP32 NaN arrives from memory with an arbitrary payload.
+__device__ __forceinline__ uint16_t float_to_bf16_exact(float value) {
+  uint32_t u = __float_as_uint(value);
+  if ((u & 0x7fffffffu) > 0x7f800000u) return static_cast<uint16_t>((u >> 16) | 0x0040u);
+  u += 0x7fffu + ((u >> 16) & 1u);
+  return static_cast<uint16_t>(u >> 16);
+}
+
+// Two FP32 results of arithmetic -> packed bf16 (first in the low half).  The hardware
+// conversion is RNE with overflow to infinity, identical to the integer rule for every
+// non-NaN value; a NaN produced by GPU arithmetic is always the canonical 0x7fffffff, which
+// both rules map to 0x7fff (sign aside), so the single instruction is exact here.
+__device__ __forceinline__ uint32_t pack_bf16x2(float first, float second) {
+  uint32_t out;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(out) : "f"(second), "f"(first));
+  return out;
+}
+__device__ __forceinline__ uint16_t float_to_bf16(float value) {
+  return static_cast<uint16_t>(pack_bf16x2(value, 0.0f) & 0xffffu);
+}
+
+// Eight bf16 (one 128-bit vector) <-> eight floats.
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+  f[0] = bf16_lo(v.x); f[1] = bf16_hi(v.x);
+  f[2] = bf16_lo(v.y); f[3] = bf16_hi(v.y);
+  f[4] = bf16_lo(v.z); f[5] = bf16_hi(v.z);
+  f[6] = bf16_lo(v.w); f[7] = bf16_hi(v.w);
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint4 v;
+  v.x = pack_bf16x2(f[0], f[1]);
+  v.y = pack_bf16x2(f[2], f[3]);
+  v.z = pack_bf16x2(f[4], f[5]);
+  v.w = pack_bf16x2(f[6], f[7]);
+  return v;
+}
+
+// ---------------------------------------------------------------------------- memory
+
+// Streaming 128-bit load: read-only path, no L1 allocation (every byte is used once).
+__device__ __forceinline__ uint4 ld_stream(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+// Plain coherent 128-bit load (for buffers the same launch may also write, e.g. in-place ops).
+__device__ __forceinline__ uint4 ld_vec(const void* p) { return *reinterpret_cast<const uint4*>(p); }
+__device__ __forceinline__ void st_vec(void* p, const uint4& v) { *reinterpret_cast<uint4*>(p) = v; }
+// Streaming store: the line is not expected to be re-read by this kernel.
+__device__ __forceinline__ void st_stream(void* p, const uint4& v) {
+  asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+// Small read-mostly operands (weights, tables): keep them cached.
+__device__ __forceinline__ uint4 ld_weight(const void* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
+
+// ---------------------------------------------------------------------------- reductions
+
+template <int LANES>
+__device__ __forceinline__ float group_sum(float v) {
+#pragma unroll
+  for (int o = LANES / 2; o > 0; o >>= 1) v += __shfl_xor_sync(kFullMask, v, o);
+  return v;
+}
+template <int LANES>
+__device__ __forceinline__ uint32_t group_max_u32(uint32_t v) {
+#pragma unroll
+  for (int o = LANES / 2; o > 0; o >>= 1) v = max(v, __shfl_xor_sync(kFullMask, v, o));
+  return v;
+}
+
+// Sum over a CTA of WARPS warps; every thread receives the total.  `scratch` holds WARPS floats.
+template <int WARPS>
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  v = group_sum<32>(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float total = 0.0f;
+#pragma unroll
+  for (int w = 0; w < WARPS; ++w) total += scratch[w];  // same order in every thread
+  return total;
+}
+
+// ---------------------------------------------------------------------------- activations
+
+// silu(g) = g / (1 + exp(-g)): the form of src/runtime/reference/decode_ops.cpp:315-316.
+// expf and the division are the IEEE-accurate CUDA versions (no fast-math).
+__device__ __forceinline__ float silu(float g) { return g / (1.0f + expf(-g)); }
+
+// Branch-stable sigmoid of decode_ops.cpp:334-337.
+__device__ __forceinline__ float stable_sigmoid(float g) {
+  if (g >= 0.0f) return 1.0f / (1.0f + expf(-g));
+  const float e = expf(g);
+  return e / (1.0f + e);
+}
+
+// ---------------------------------------------------------------------------- bf16 amax
+
+// Magnitude bits of the finite halves of a packed bf16 pair, non-finite halves give 0; bf16
+// magnitudes order like their bit patterns, so an unsigned max of these is the amax.
+__device__ __forceinline__ uint32_t finite_mag2(uint32_t packed) {
+  const uint32_t m = packed & 0x7fff7fffu;
+  const uint32_t keep = __vcmpltu2(m, 0x7f807f80u);  // 0xffff per half where finite
+  return m & keep;
+}
+__device__ __forceinline__ uint32_t amax8(const uint4& v) {
+  uint32_t m = __vmaxu2(__vmaxu2(finite_mag2(v.x), finite_mag2(v.y)),
+                        __vmaxu2(finite_mag2(v.z), finite_mag2(v.w)));
+  return max(m & 0xffffu, m >> 16);
+}
+
+}  // namespace q3x

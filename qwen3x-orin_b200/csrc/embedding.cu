@@ -1,0 +1,84 @@
+// Token-embedding gather: out[t,:] = table[ids[t],:], a bitwise copy of one table row per token.
+//
+// One 128-thread CTA per token; for the 5120-wide table each thread issues its five 128-bit loads
+// back to back (the whole 10 KB row is in flight at once) and then stores them.  Rows are random in
+// a 2.5 GB table, so the reads are 10 KB bursts at random HBM addresses; the writes are one
+// contiguous stream.  A token id outside the vocabulary leaves its row untouched, the rule of the
+// reference's prompt kernel (src/kernels/reference/decode_ops.cu:374-391).
+#include "device_utils.cuh"
+#include "host_checks.hpp"
+#include "q3x_b200.h"
+
+namespace q3x {
+namespace {
+
+constexpr int kThreads = 128;
+
+template <int VPT>
+__global__ void __launch_bounds__(kThreads) embedding_rows_kernel(const uint4* __restrict__ table, size_t vocab,
+                                                                  int row_vectors,
+                                                                  const uint32_t* __restrict__ token_ids,
+                                                                  uint4* __restrict__ out) {
+  const size_t token = blockIdx.x;
+  const size_t id = __ldg(token_ids + token);
+  if (id >= vocab) return;
+  const uint4* src = table + id * static_cast<size_t>(row_vectors);
+  uint4* dst = out + token * static_cast<size_t>(row_vectors);
+  for (int base = 0; base < row_vectors; base += kThreads * VPT) {
+    uint4 v[VPT];
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+      const int i = base + threadIdx.x + k * kThreads;
+      if (i < row_vectors) v[k] = ld_stream(src + i);
+    }
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+      const int i = base + threadIdx.x + k * kThreads;
+      if (i < row_vectors) st_vec(dst + i, v[k]);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kThreads) embedding_rows_scalar_kernel(const uint16_t* table, size_t vocab,
+                                                                         size_t hidden, const uint32_t* token_ids,
+                                                                         uint16_t* out) {
+  const size_t token = blockIdx.x;
+  const size_t id = token_ids[token];
+  if (id >= vocab) return;
+  for (size_t i = threadIdx.x; i < hidden; i += kThreads) out[token * hidden + i] = table[id * hidden + i];
+}
+
+}  // namespace
+}  // namespace q3x
+
+using namespace q3x;
+using namespace q3x::host;
+
+extern "C" int q3x_b200_embedding_gather(const uint16_t* table, size_t vocab, size_t hidden,
+                                         const uint32_t* token_ids, size_t token_count, uint16_t* out,
+                                         void* stream) {
+  if (mul3_overflows(vocab, hidden, sizeof(uint16_t)) || mul3_overflows(token_count, hidden, sizeof(uint16_t)) ||
+      mul_overflows(token_count, sizeof(uint32_t)))
+    return kInvalid;
+  if (token_count == 0 || hidden == 0) return kOk;
+  if (vocab == 0 || token_count > 0x7fffffffu) return kInvalid;
+  if (table == nullptr || token_ids == nullptr || out == nullptr) return kInvalid;
+  const Span st = span(table, vocab * hidden * 2), si = span(token_ids, token_count * 4),
+             so = span(out, token_count * hidden * 2);
+  if (wraps(st) || wraps(si) || wraps(so) || overlap(st, si) || overlap(st, so) || overlap(si, so)) return kInvalid;
+  cudaStream_t s = as_stream(stream);
+  const unsigned grid = static_cast<unsigned>(token_count);
+  clear_stale_error();
+  if (hidden % 8 == 0 && hidden / 8 <= 0x7fffffffu && aligned16(table) && aligned16(out)) {
+    const int row_vectors = static_cast<int>(hidden / 8);
+    auto T = reinterpret_cast<const uint4*>(table);
+    auto O = reinterpret_cast<uint4*>(out);
+    if (row_vectors > 3 * kThreads)
+      embedding_rows_kernel<5><<<grid, kThreads, 0, s>>>(T, vocab, row_vectors, token_ids, O);
+    else
+      embedding_rows_kernel<2><<<grid, kThreads, 0, s>>>(T, vocab, row_vectors, token_ids, O);
+  } else {
+    embedding_rows_scalar_kernel<<<grid, kThreads, 0, s>>>(table, vocab, hidden, token_ids, out);
+  }
+  return launch_status();
+}

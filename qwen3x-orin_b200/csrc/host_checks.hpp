@@ -1,0 +1,75 @@
+// Host-side argument checks run by every entry point before anything is enqueued, so that a bad
+// call fails with cudaErrorInvalidValue and no device work.  The rules are those of the
+// reference launchers (src/kernels/reference/decode_ops.cu:142-211): element counts must not
+// overflow size_t, byte ranges must not wrap the address space, an output may alias an input only
+// exactly, and epsilon must be finite and positive.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstddef>
+#include <cstdint>
+#include <limits>
+
+namespace q3x::host {
+
+inline bool mul_overflows(size_t a, size_t b) {
+  return b != 0 && a > std::numeric_limits<size_t>::max() / b;
+}
+inline bool mul3_overflows(size_t a, size_t b, size_t c) {
+  return mul_overflows(a, b) || mul_overflows(a * b, c);
+}
+inline bool valid_epsilon(float eps) { return std::isfinite(eps) && eps > 0.0f; }
+
+struct Span {
+  const void* p;
+  size_t bytes;
+};
+inline Span span(const void* p, size_t bytes) { return Span{p, bytes}; }
+
+inline bool wraps(const Span& s) {
+  return s.bytes > std::numeric_limits<uintptr_t>::max() - reinterpret_cast<uintptr_t>(s.p);
+}
+inline bool overlap(const Span& a, const Span& b) {
+  if (a.bytes == 0 || b.bytes == 0) return false;
+  if (wraps(a) || wraps(b)) return true;
+  const uintptr_t x = reinterpret_cast<uintptr_t>(a.p), y = reinterpret_cast<uintptr_t>(b.p);
+  return x < y + b.bytes && y < x + a.bytes;
+}
+// Overlapping without being the very same range.
+inline bool partial_overlap(const Span& a, const Span& b) {
+  return !(a.p == b.p && a.bytes == b.bytes) && overlap(a, b);
+}
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+inline cudaStream_t as_stream(void* s) { return static_cast<cudaStream_t>(s); }
+
+// Clears a stale last-error left by unrelated earlier work of this thread, so that the value
+// returned after the launches is this call's own.
+inline void clear_stale_error() { (void)cudaGetLastError(); }
+inline int launch_status() { return static_cast<int>(cudaGetLastError()); }
+
+constexpr int kInvalid = static_cast<int>(cudaErrorInvalidValue);
+constexpr int kNotSupported = static_cast<int>(cudaErrorNotSupported);
+constexpr int kOk = static_cast<int>(cudaSuccess);
+
+// Grid sizing: enough CTAs to fill the machine a few times over without exceeding what the work
+// needs.  148 SMs on B200; the multiplier is the number of resident CTAs per SM we aim for.
+inline unsigned grid_for(size_t work_items, unsigned items_per_cta, unsigned ctas_per_sm_target) {
+  static int sm_count = 0;
+  if (sm_count == 0) {
+    int dev = 0, n = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess &&
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0)
+      sm_count = n;
+    else
+      sm_count = 148;
+  }
+  const size_t needed = (work_items + items_per_cta - 1) / items_per_cta;
+  const size_t cap = static_cast<size_t>(sm_count) * ctas_per_sm_target;
+  const size_t g = needed < cap ? needed : cap;
+  return static_cast<unsigned>(g == 0 ? 1 : g);
+}
+
+}  // namespace q3x::host

@@ -1,0 +1,36 @@
+// Declarations shared between the translation units of libq3x_b200.so (not part of the ABI).
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstddef>
+#include <cstdint>
+
+namespace q3x {
+
+enum class NormMode : int {
+  kCentered = 0,       // y = x * inv_rms * (1 + w)
+  kPlain = 1,          // y = x * inv_rms * w
+  kPlainSiluGate = 2,  // y = x * inv_rms * w * silu(z)
+  kL2 = 3,             // y = x * scale / sqrt(sum x^2 + eps)
+};
+
+// Enqueues the row-norm kernel that fits the shape; arguments are already validated.
+//   a / b        input (or left / right when residual_out != nullptr)
+//   out          normalised rows (nullptr allowed only together with residual_out)
+//   coherent     an output aliases an input exactly: use coherent loads
+//   amax_bits    when non-null, atomically raised to the bf16 magnitude bits of the largest
+//                finite output of each group of rows_per_amax_group rows (vector paths only)
+void launch_norm_rows(NormMode mode, const uint16_t* a, const uint16_t* b, const uint16_t* weight,
+                      const uint16_t* gate, size_t rows, size_t width, float eps, float l2_scale,
+                      uint16_t* residual_out, uint16_t* out, bool coherent, uint32_t* amax_bits,
+                      size_t rows_per_amax_group, cudaStream_t stream);
+
+bool norm_rows_vector_path(const void* a, const void* b, const void* weight, const void* gate, size_t width,
+                           const void* residual_out, const void* out, NormMode mode);
+
+int check_residual_norm(const uint16_t* left, const uint16_t* right, const uint16_t* weight, size_t tokens,
+                        size_t hidden, float eps, const uint16_t* residual_out, const uint16_t* normalized_out,
+                        bool* done);
+
+}  // namespace q3x

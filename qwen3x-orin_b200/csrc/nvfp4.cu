@@ -1,0 +1,400 @@
+// NVFP4 activation quantisation: 16-element blocks, one E4M3 scale per block, one FP32 global
+// scale per group of rows.  real = E2M1(code) * E4M3(scale) * global; global = amax / (448 * 6).
+//
+// The arithmetic, step for step (all IEEE binary32, no contraction):
+//   A      = largest finite |x| of the group          (exact: unsigned max of bf16 magnitude bits)
+//   global = A == 0 ? 1 : A / 2688
+//   k      = 1 / (global * 6)
+//   per block: s   = amax_b == 0 ? 0 : e4m3_rn_satfinite(amax_b * k)
+//              d   = e4m3_decode(s) * global
+//              inv = d == 0 ? 0 : min(1 / d, FLT_MAX)
+//              code_i = e2m1_rn_satfinite(x_i * inv), even column in the low nibble.
+// The two narrow conversions are the hardware ones (cvt.rn.satfinite.e4m3x2.f32 /
+// cvt.rn.satfinite.e2m1x2.f32): round-to-nearest-even onto the format's grid with saturation to
+// its largest finite value.
+//
+// Work layout of the quantiser: a lane owns eight elements (one 128-bit load), lane pairs share a
+// block's amax through one shuffle, each lane stores its four code bytes as one 32-bit word (a
+// warp writes 128 contiguous bytes) and the even lane stores the block scale.
+#include <cfloat>
+
+#include "device_utils.cuh"
+#include "host_checks.hpp"
+#include "internal.hpp"
+#include "q3x_b200.h"
+
+namespace q3x {
+namespace {
+
+constexpr int kThreads = 256;
+
+__device__ __forceinline__ uint32_t encode_e4m3(float v) {
+  uint16_t pair;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(pair) : "f"(0.0f), "f"(v));
+  return pair & 0xffu;
+}
+
+// Non-negative E4M3 code -> float (exact).
+__device__ __forceinline__ float decode_e4m3_positive(uint32_t code) {
+  const uint32_t e = (code >> 3) & 0xfu, m = code & 7u;
+  if (e == 0) return static_cast<float>(m) * 0.001953125f;     // m * 2^-9
+  if (code == 0x7fu) return __uint_as_float(0x7fffffffu);        // NaN (never produced by encode)
+  return __uint_as_float(((e + 120u) << 23) | (m << 20));        // (1 + m/8) * 2^(e-7)
+}
+
+// Eight floats -> eight E2M1 codes in one word, element i in nibble i.
+__device__ __forceinline__ uint32_t encode_e2m1x8(const float (&r)[8]) {
+  uint32_t out;
+  asm("{\n"
+      ".reg .b8 b0, b1, b2, b3;\n"
+      "cvt.rn.satfinite.e2m1x2.f32 b0, %2, %1;\n"
+      "cvt.rn.satfinite.e2m1x2.f32 b1, %4, %3;\n"
+      "cvt.rn.satfinite.e2m1x2.f32 b2, %6, %5;\n"
+      "cvt.rn.satfinite.e2m1x2.f32 b3, %8, %7;\n"
+      "mov.b32 %0, {b0, b1, b2, b3};\n"
+      "}"
+      : "=r"(out)
+      : "f"(r[0]), "f"(r[1]), "f"(r[2]), "f"(r[3]), "f"(r[4]), "f"(r[5]), "f"(r[6]), "f"(r[7]));
+  return out;
+}
+
+__device__ __forceinline__ float block_inverse(uint32_t scale_code, float global) {
+  const float d = __fmul_rn(decode_e4m3_positive(scale_code), global);
+  return d == 0.0f ? 0.0f : fminf(__fdiv_rn(1.0f, d), FLT_MAX);
+}
+
+// ---- group amax -------------------------------------------------------------------------
+
+__global__ void __launch_bounds__(kThreads) group_amax_vec_kernel(const uint4* __restrict__ in, size_t nvec,
+                                                                  size_t chunk, size_t group_vectors,
+                                                                  uint32_t* amax_bits) {
+  const size_t begin = static_cast<size_t>(blockIdx.x) * chunk;
+  const size_t end = min(nvec, begin + chunk);
+  size_t v = begin + threadIdx.x;
+  size_t group = v / group_vectors;
+  size_t boundary = (group + 1) * group_vectors;
+  uint32_t top = 0;
+  for (; v < end; v += kThreads) {
+    while (v >= boundary) {
+      if (top != 0) atomicMax(amax_bits + group, top);
+      top = 0;
+      ++group;
+      boundary += group_vectors;
+    }
+    top = max(top, amax8(ld_stream(in + v)));
+  }
+  // one atomic per warp when the warp ends inside a single group
+  const size_t g0 = static_cast<size_t>(__shfl_sync(kFullMask, static_cast<unsigned long long>(group), 0));
+  if (__all_sync(kFullMask, group == g0)) {
+    top = group_max_u32<32>(top);
+    if ((threadIdx.x & 31) == 0 && top != 0) atomicMax(amax_bits + g0, top);
+  } else if (top != 0) {
+    atomicMax(amax_bits + group, top);
+  }
+}
+
+__global__ void __launch_bounds__(kThreads) group_amax_scalar_kernel(const uint16_t* in, size_t count,
+                                                                     size_t group_elements, uint32_t* amax_bits) {
+  const size_t stride = static_cast<size_t>(gridDim.x) * kThreads;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x; i < count; i += stride) {
+    const uint32_t m = in[i] & 0x7fffu;
+    if (m != 0 && m < 0x7f80u) atomicMax(amax_bits + i / group_elements, m);
+  }
+}
+
+__global__ void amax_to_scale_kernel(const uint32_t* amax_bits, size_t groups, float* global_scales) {
+  const size_t g = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (g >= groups) return;
+  const float amax = __uint_as_float(amax_bits[g] << 16);
+  global_scales[g] = amax == 0.0f ? 1.0f : __fdiv_rn(amax, 2688.0f);
+}
+
+// ---- quantiser --------------------------------------------------------------------------
+
+__global__ void __launch_bounds__(kThreads) nvfp4_quantize_vec_kernel(const uint4* __restrict__ in, size_t nvec,
+                                                                      unsigned row_vectors, size_t rows_per_scale,
+                                                                      const float* __restrict__ global_scales,
+                                                                      uint32_t* __restrict__ codes,
+                                                                      uint8_t* __restrict__ scales) {
+  const size_t stride = static_cast<size_t>(gridDim.x) * kThreads;
+  // nvec is even (cols % 16 == 0) and the stride is a multiple of 32, so lane pairs stay together
+  const unsigned lane = threadIdx.x & 31u;
+  // the loop bound is the same for all lanes of a warp, so the pair shuffle always has its partner
+  for (size_t v = static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x; v - lane < nvec; v += stride) {
+    const bool valid = v < nvec;  // lane pairs are valid together (nvec is even)
+    const uint4 x = valid ? ld_stream(in + v) : make_uint4(0, 0, 0, 0);
+    uint32_t m = amax8(x);
+    m = max(m, __shfl_xor_sync(kFullMask, m, 1));
+    if (!valid) continue;
+    const size_t row = v / row_vectors;
+    const float global = __ldg(global_scales + (rows_per_scale ? row / rows_per_scale : 0));
+    const float k = __fdiv_rn(1.0f, __fmul_rn(global, 6.0f));
+    const uint32_t s = m == 0 ? 0u : encode_e4m3(__fmul_rn(__uint_as_float(m << 16), k));
+    const float inv = block_inverse(s, global);
+    float f[8];
+    unpack8(x, f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = __fmul_rn(f[i], inv);
+    codes[v] = encode_e2m1x8(f);
+    if ((threadIdx.x & 1) == 0) scales[v >> 1] = static_cast<uint8_t>(s);
+  }
+}
+
+// Any alignment: one thread per 16-element block.
+__global__ void __launch_bounds__(kThreads) nvfp4_quantize_scalar_kernel(const uint16_t* in, size_t blocks,
+                                                                         size_t row_blocks, size_t rows_per_scale,
+                                                                         const float* global_scales, uint8_t* codes,
+                                                                         uint8_t* scales) {
+  const size_t stride = static_cast<size_t>(gridDim.x) * kThreads;
+  for (size_t b = static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x; b < blocks; b += stride) {
+    const uint16_t* x = in + b * 16;
+    uint32_t m = 0;
+    for (int i = 0; i < 16; ++i) {
+      const uint32_t mag = x[i] & 0x7fffu;
+      if (mag < 0x7f80u) m = max(m, mag);
+    }
+    const size_t row = b / row_blocks;
+    const float global = global_scales[rows_per_scale ? row / rows_per_scale : 0];
+    const float k = __fdiv_rn(1.0f, __fmul_rn(global, 6.0f));
+    const uint32_t s = m == 0 ? 0u : encode_e4m3(__fmul_rn(__uint_as_float(m << 16), k));
+    const float inv = block_inverse(s, global);
+    scales[b] = static_cast<uint8_t>(s);
+    for (int h = 0; h < 2; ++h) {
+      float f[8];
+      for (int i = 0; i < 8; ++i) f[i] = __fmul_rn(bf16_to_float(x[h * 8 + i]), inv);
+      const uint32_t word = encode_e2m1x8(f);
+      for (int i = 0; i < 4; ++i) codes[b * 8 + h * 4 + i] = static_cast<uint8_t>(word >> (8 * i));
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kThreads) debug_encode_kernel(const float* in, size_t count, uint8_t* out,
+                                                                int format) {
+  const size_t i = static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x;
+  if (i >= count) return;
+  if (format == 0) {
+    out[i] = static_cast<uint8_t>(encode_e4m3(in[i]));
+  } else {
+    const float f[8] = {in[i], 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+    out[i] = static_cast<uint8_t>(encode_e2m1x8(f) & 0xfu);
+  }
+}
+
+size_t group_count(size_t rows, size_t rows_per_scale) {
+  if (rows == 0) return 0;
+  return rows_per_scale == 0 ? 1 : (rows + rows_per_scale - 1) / rows_per_scale;
+}
+
+// shared shape checks of the NVFP4 entry points; *done marks a finished no-op
+int check_matrix(const void* in, size_t rows, size_t cols, bool* done) {
+  using namespace host;
+  *done = false;
+  if (cols % Q3X_B200_NVFP4_BLOCK != 0) return kInvalid;
+  if (mul3_overflows(rows, cols, sizeof(uint16_t))) return kInvalid;
+  if (rows == 0 || cols == 0) {
+    *done = true;
+    return kOk;
+  }
+  if (in == nullptr) return kInvalid;
+  return kOk;
+}
+
+void enqueue_amax(const uint16_t* in, size_t rows, size_t cols, size_t rows_per_scale, uint32_t* amax_bits,
+                  cudaStream_t s) {
+  using namespace host;
+  const size_t groups = group_count(rows, rows_per_scale);
+  const size_t group_rows = rows_per_scale ? rows_per_scale : rows;
+  cudaMemsetAsync(amax_bits, 0, groups * sizeof(uint32_t), s);
+  if (aligned16(in) && cols % 8 == 0) {
+    const size_t nvec = rows * cols / 8;
+    const unsigned grid = grid_for(nvec, kThreads * 8, 8);
+    size_t chunk = (nvec + grid - 1) / grid;
+    chunk = (chunk + kThreads - 1) / kThreads * kThreads;
+    const unsigned ctas = static_cast<unsigned>((nvec + chunk - 1) / chunk);
+    group_amax_vec_kernel<<<ctas, kThreads, 0, s>>>(reinterpret_cast<const uint4*>(in), nvec, chunk,
+                                                    group_rows * (cols / 8), amax_bits);
+  } else {
+    const size_t count = rows * cols;
+    group_amax_scalar_kernel<<<grid_for(count, kThreads, 8), kThreads, 0, s>>>(in, count, group_rows * cols,
+                                                                               amax_bits);
+  }
+}
+
+void enqueue_scales(const uint32_t* amax_bits, size_t groups, float* global_scales, cudaStream_t s) {
+  amax_to_scale_kernel<<<static_cast<unsigned>((groups + 127) / 128), 128, 0, s>>>(amax_bits, groups, global_scales);
+}
+
+void enqueue_quantize(const uint16_t* in, size_t rows, size_t cols, size_t rows_per_scale, const float* global_scales,
+                      uint8_t* codes, uint8_t* scales, cudaStream_t s) {
+  using namespace host;
+  if (aligned16(in) && (reinterpret_cast<uintptr_t>(codes) & 3u) == 0 && cols / 8 <= 0xffffffffu) {
+    const size_t nvec = rows * cols / 8;
+    nvfp4_quantize_vec_kernel<<<grid_for(nvec, kThreads * 2, 8), kThreads, 0, s>>>(
+        reinterpret_cast<const uint4*>(in), nvec, static_cast<unsigned>(cols / 8), rows_per_scale, global_scales,
+        reinterpret_cast<uint32_t*>(codes), scales);
+  } else {
+    const size_t blocks = rows * cols / 16;
+    nvfp4_quantize_scalar_kernel<<<grid_for(blocks, kThreads, 8), kThreads, 0, s>>>(in, blocks, cols / 16,
+                                                                                   rows_per_scale, global_scales,
+                                                                                   codes, scales);
+  }
+}
+
+int check_quant_outputs(const uint16_t* in, size_t rows, size_t cols, const void* codes, const void* scales) {
+  using namespace host;
+  if (codes == nullptr || scales == nullptr) return kInvalid;
+  const Span si = span(in, rows * cols * 2), sc = span(codes, rows * cols / 2), ss = span(scales, rows * cols / 16);
+  if (wraps(si) || wraps(sc) || wraps(ss) || overlap(si, sc) || overlap(si, ss) || overlap(sc, ss)) return kInvalid;
+  return kOk;
+}
+
+}  // namespace
+}  // namespace q3x
+
+using namespace q3x;
+using namespace q3x::host;
+
+extern "C" size_t q3x_b200_nvfp4_group_count(size_t rows, size_t rows_per_scale) {
+  return group_count(rows, rows_per_scale);
+}
+
+extern "C" int q3x_b200_group_amax(const uint16_t* in, size_t rows, size_t cols, size_t rows_per_scale,
+                                   uint32_t* amax_bits, void* stream) {
+  if (mul3_overflows(rows, cols, sizeof(uint16_t))) return kInvalid;
+  if (rows == 0 || cols == 0) return kOk;
+  if (in == nullptr || amax_bits == nullptr) return kInvalid;
+  const Span si = span(in, rows * cols * 2), sa = span(amax_bits, group_count(rows, rows_per_scale) * 4);
+  if (wraps(si) || overlap(si, sa)) return kInvalid;
+  clear_stale_error();
+  enqueue_amax(in, rows, cols, rows_per_scale, amax_bits, as_stream(stream));
+  return launch_status();
+}
+
+extern "C" int q3x_b200_amax_to_global_scale(const uint32_t* amax_bits, size_t groups, float* global_scales,
+                                             void* stream) {
+  if (groups == 0) return kOk;
+  if (amax_bits == nullptr || global_scales == nullptr || mul_overflows(groups, 4)) return kInvalid;
+  if (overlap(span(amax_bits, groups * 4), span(global_scales, groups * 4))) return kInvalid;
+  clear_stale_error();
+  enqueue_scales(amax_bits, groups, global_scales, as_stream(stream));
+  return launch_status();
+}
+
+extern "C" int q3x_b200_nvfp4_quantize(const uint16_t* in, size_t rows, size_t cols, size_t rows_per_scale,
+                                       const float* global_scales, uint8_t* codes, uint8_t* scales, void* stream) {
+  bool done;
+  int st = check_matrix(in, rows, cols, &done);
+  if (st != kOk || done) return st;
+  if (global_scales == nullptr) return kInvalid;
+  if ((st = check_quant_outputs(in, rows, cols, codes, scales)) != kOk) return st;
+  clear_stale_error();
+  enqueue_quantize(in, rows, cols, rows_per_scale, global_scales, codes, scales, as_stream(stream));
+  return launch_status();
+}
+
+extern "C" int q3x_b200_nvfp4_quantize_dynamic(const uint16_t* in, size_t rows, size_t cols, size_t rows_per_scale,
+                                               uint32_t* amax_scratch, float* global_scales_out, uint8_t* codes,
+                                               uint8_t* scales, void* stream) {
+  bool done;
+  int st = check_matrix(in, rows, cols, &done);
+  if (st != kOk || done) return st;
+  if (amax_scratch == nullptr || global_scales_out == nullptr) return kInvalid;
+  if ((st = check_quant_outputs(in, rows, cols, codes, scales)) != kOk) return st;
+  const size_t groups = group_count(rows, rows_per_scale);
+  cudaStream_t s = as_stream(stream);
+  clear_stale_error();
+  enqueue_amax(in, rows, cols, rows_per_scale, amax_scratch, s);
+  enqueue_scales(amax_scratch, groups, global_scales_out, s);
+  enqueue_quantize(in, rows, cols, rows_per_scale, global_scales_out, codes, scales, s);
+  return launch_status();
+}
+
+extern "C" int q3x_b200_residual_add_rms_norm_nvfp4(const uint16_t* left, const uint16_t* right,
+                                                    const uint16_t* weight, size_t tokens, size_t hidden, float eps,
+                                                    size_t rows_per_scale, uint16_t* residual_out,
+                                                    uint16_t* normalized_out, uint32_t* amax_scratch,
+                                                    float* global_scales_out, uint8_t* codes, uint8_t* scales,
+                                                    void* stream) {
+  bool done;
+  int st = check_residual_norm(left, right, weight, tokens, hidden, eps, residual_out, normalized_out, &done);
+  if (st != kOk) return st;
+  if (hidden % Q3X_B200_NVFP4_BLOCK != 0) return kInvalid;
+  if (done) return kOk;
+  if (normalized_out == nullptr || amax_scratch == nullptr || global_scales_out == nullptr) return kInvalid;
+  if ((st = check_quant_outputs(normalized_out, tokens, hidden, codes, scales)) != kOk) return st;
+  if (!norm_rows_vector_path(left, right, weight, nullptr, hidden, residual_out, normalized_out, NormMode::kCentered))
+    return kNotSupported;
+  const size_t groups = group_count(tokens, rows_per_scale);
+  cudaStream_t s = as_stream(stream);
+  clear_stale_error();
+  cudaMemsetAsync(amax_scratch, 0, groups * sizeof(uint32_t), s);
+  launch_norm_rows(NormMode::kCentered, left, right, weight, nullptr, tokens, hidden, eps, 1.0f, residual_out,
+                   normalized_out, /*coherent=*/normalized_out == right, amax_scratch,
+                   rows_per_scale ? rows_per_scale : tokens, s);
+  enqueue_scales(amax_scratch, groups, global_scales_out, s);
+  enqueue_quantize(normalized_out, tokens, hidden, rows_per_scale, global_scales_out, codes, scales, s);
+  return launch_status();
+}
+
+extern "C" int q3x_b200_rms_norm_silu_gate_nvfp4(const uint16_t* in, const uint16_t* weight, const uint16_t* gate,
+                                                 size_t tokens, size_t heads_per_row, size_t dim, float eps,
+                                                 size_t rows_per_scale, uint16_t* out, uint32_t* amax_scratch,
+                                                 float* global_scales_out, uint8_t* codes, uint8_t* scales,
+                                                 void* stream) {
+  if (!valid_epsilon(eps)) return kInvalid;
+  if (mul3_overflows(tokens, heads_per_row, dim) || mul_overflows(tokens * heads_per_row * dim, 2)) return kInvalid;
+  const size_t cols = heads_per_row * dim;
+  if (cols % Q3X_B200_NVFP4_BLOCK != 0) return kInvalid;
+  if (tokens == 0 || cols == 0) return kOk;
+  if (in == nullptr || weight == nullptr || gate == nullptr || out == nullptr || amax_scratch == nullptr ||
+      global_scales_out == nullptr)
+    return kInvalid;
+  const size_t bytes = tokens * cols * 2;
+  const Span si = span(in, bytes), sg = span(gate, bytes), so = span(out, bytes), sw = span(weight, dim * 2);
+  if (wraps(si) || wraps(sg) || wraps(so) || partial_overlap(so, si) || partial_overlap(so, sg) || overlap(so, sw))
+    return kInvalid;
+  int st = check_quant_outputs(out, tokens, cols, codes, scales);
+  if (st != kOk) return st;
+  if (!norm_rows_vector_path(in, nullptr, weight, gate, dim, nullptr, out, NormMode::kPlainSiluGate) ||
+      !(dim == 64 || dim == 128 || dim == 256))
+    return kNotSupported;
+  const size_t groups = group_count(tokens, rows_per_scale);
+  const size_t token_group = rows_per_scale ? rows_per_scale : tokens;
+  cudaStream_t s = as_stream(stream);
+  clear_stale_error();
+  cudaMemsetAsync(amax_scratch, 0, groups * sizeof(uint32_t), s);
+  launch_norm_rows(NormMode::kPlainSiluGate, in, nullptr, weight, gate, tokens * heads_per_row, dim, eps, 1.0f,
+                   nullptr, out, /*coherent=*/out == in || out == gate, amax_scratch, token_group * heads_per_row, s);
+  enqueue_scales(amax_scratch, groups, global_scales_out, s);
+  enqueue_quantize(out, tokens, cols, rows_per_scale, global_scales_out, codes, scales, s);
+  return launch_status();
+}
+
+// Diagnostics: the two narrow conversions on their own, so that tests can sweep them against the
+// CPU definition.  format 0 = E4M3 (one byte per value), 1 = E2M1 (one nibble per value, in a byte).
+extern "C" int q3x_b200_debug_encode(const float* in, size_t count, int format, uint8_t* out, void* stream) {
+  if (count == 0) return kOk;
+  if (in == nullptr || out == nullptr || (format != 0 && format != 1)) return kInvalid;
+  clear_stale_error();
+  debug_encode_kernel<<<static_cast<unsigned>((count + kThreads - 1) / kThreads), kThreads, 0, as_stream(stream)>>>(
+      in, count, out, format);
+  return launch_status();
+}
+
+// Diagnostics: with `plant` non-zero, leaves a stale error in this library's CUDA runtime through a
+// host-side argument error (an invalid copy direction; nothing reaches the GPU), the situation the
+// entry points must clear before their own launch.  Returns the pending last-error without
+// clearing it.
+extern "C" int q3x_b200_debug_stale_error(int plant) {
+  if (plant) {
+    int dummy = 0;
+    (void)cudaMemcpyAsync(&dummy, &dummy, sizeof(dummy), static_cast<cudaMemcpyKind>(99), nullptr);
+  }
+  return static_cast<int>(cudaPeekAtLastError());
+}
+
+extern "C" int q3x_b200_abi_version(void) { return Q3X_B200_ABI_VERSION; }
+
+extern "C" const char* q3x_b200_error_string(int status) {
+  return cudaGetErrorString(static_cast<cudaError_t>(status));
+}

@@ -1,0 +1,189 @@
+"""GPU parity tests of the NVFP4 activation quantiser.  The requirement is bit-exact codes, E4M3
+block scales and FP32 global scales given identical pre-quantisation values, so every comparison
+feeds the CPU encoder the very bf16 tensor the GPU quantised."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as orc
+from tests import fixtures as fx
+
+pytestmark = pytest.mark.gpu
+EPS = 1e-6
+
+
+@pytest.fixture(scope="module")
+def g():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from tests import gpu_util
+
+    orc.build()
+    gpu_util.capi.load()
+    return gpu_util
+
+
+def sweep_values():
+    rng = np.random.default_rng(31)
+    mids = np.array([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0], dtype=np.float32)
+    near = np.concatenate([np.nextafter(mids, np.float32(0)), mids, np.nextafter(mids, np.float32(9))])
+    e4 = np.array([orc.oracle_lib().decode_e4m3(c) for c in range(0x7F)], dtype=np.float32)
+    e4_mid = (e4[:-1] + e4[1:]) / np.float32(2)
+    e4_near = np.concatenate([e4, e4_mid, np.nextafter(e4_mid, np.float32(0)), np.nextafter(e4_mid, np.float32(1e9))])
+    vals = np.concatenate([
+        near, -near, e4_near, -e4_near,
+        np.array([0.0, -0.0, np.inf, -np.inf, np.nan, 1e-45, -1e-45, 6.0, 6.5, 447.0, 448.0, 449.0, 464.0, 480.0,
+                  1e30, -1e30, 2.0**-10, 2.0**-9, 1.5 * 2.0**-10, 0.0009765626], dtype=np.float32),
+        (rng.standard_normal(200_000) * 3).astype(np.float32),
+        (rng.standard_normal(100_000) * 200).astype(np.float32),
+        (rng.standard_normal(100_000) * 0.01).astype(np.float32),
+        rng.integers(0, 2**32, size=100_000, dtype=np.uint64).astype(np.uint32).view(np.float32),
+    ])
+    return vals.astype(np.float32)
+
+
+@pytest.mark.parametrize("fmt,name", [(0, "e4m3"), (1, "e2m1")])
+def test_narrow_conversions_match_the_cpu_definition(g, fmt, name):
+    """The hardware conversions the kernels use against the oracle's encoders on a sweep that holds
+    every grid point, every midpoint and its neighbours, specials and random bit patterns."""
+    vals = sweep_values()
+    d = g.Dev(vals)
+    out = g.empty_like_dev((vals.size,), dtype=np.uint8)
+    g.capi.check("q3x_b200_debug_encode", d, vals.size, fmt, out, None)
+    g.sync()
+    L = orc.oracle_lib()
+    enc = L.encode_e4m3 if fmt == 0 else L.encode_e2m1
+    want = np.array([enc(float(v)) for v in vals], dtype=np.uint8)
+    got = out.get()
+    bad = np.nonzero(got != want)[0]
+    assert bad.size == 0, [(float(vals[i]), hex(got[i]), hex(want[i])) for i in bad[:10]]
+
+
+CASES = [(7, 64, 0), (40, 5120, 16), (33, 6144, 512), (5, 17408, 2), (512, 5120, 512), (513, 5120, 512), (1, 16, 0)]
+
+
+def make_input(rows, cols, seed):
+    rng = np.random.default_rng([rows, cols, seed])
+    x = fx.normal_bf16(rng, (rows, cols))
+    x[0, :16] = 0
+    x[rows // 2, 16:32] = 0x0001
+    if rows > 4:
+        fx.sprinkle_specials(rng, x[-1:], 0.01)
+    return x
+
+
+@pytest.mark.parametrize("rows,cols,rps", CASES)
+@pytest.mark.parametrize("misalign", [0, 1])
+def test_quantize_dynamic(g, rows, cols, rps, misalign):
+    x = make_input(rows, cols, 1)
+    groups = 1 if rps == 0 else (rows + rps - 1) // rps
+    dx = g.Dev(x, misalign)
+    amax = g.empty_like_dev((groups,), dtype=np.uint32, fill=0x7FFFFFFF)  # stale contents must not matter
+    gs = g.empty_like_dev((groups,), dtype=np.float32)
+    codes = g.empty_like_dev((rows, cols // 2), dtype=np.uint8, misalign=misalign)
+    scales = g.empty_like_dev((rows, cols // 16), dtype=np.uint8)
+    g.capi.check("q3x_b200_nvfp4_quantize_dynamic", dx, rows, cols, rps, amax, gs, codes, scales, None)
+    g.sync()
+    want_c, want_s, want_g = orc.nvfp4_quantize(x, rps)
+    assert np.array_equal(gs.get().view(np.uint32), want_g.view(np.uint32)), "global scales"
+    assert np.array_equal(amax.get() << 16, orc.group_amax(x, rps).view(np.uint32)), "group amax bits"
+    g.assert_bits_equal(scales.get(), want_s, "E4M3 block scales")
+    g.assert_bits_equal(codes.get(), want_c, "E2M1 codes")
+    assert codes.guards_intact() and scales.guards_intact() and gs.guards_intact() and amax.guards_intact()
+    # the pieces, called one by one, give the same bytes
+    amax2 = g.empty_like_dev((groups,), dtype=np.uint32, fill=77)
+    gs2 = g.empty_like_dev((groups,), dtype=np.float32)
+    c2 = g.empty_like_dev((rows, cols // 2), dtype=np.uint8)
+    s2 = g.empty_like_dev((rows, cols // 16), dtype=np.uint8)
+    assert g.capi.lib().q3x_b200_nvfp4_group_count(rows, rps) == groups
+    g.capi.check("q3x_b200_group_amax", dx, rows, cols, rps, amax2, None)
+    g.capi.check("q3x_b200_amax_to_global_scale", amax2, groups, gs2, None)
+    g.capi.check("q3x_b200_nvfp4_quantize", dx, rows, cols, rps, gs2, c2, s2, None)
+    g.sync()
+    g.assert_bits_equal(c2.get(), want_c, "codes (stepwise)")
+    g.assert_bits_equal(s2.get(), want_s, "scales (stepwise)")
+
+
+def test_quantize_round_trip_and_static_scale(g):
+    """dequantise(GPU codes) reproduces E2M1 * E4M3 * global exactly, the formula of the reference's
+    decoder (src/quantization/nvfp4.cpp:52-59); a caller-supplied (static) scale is honoured."""
+    x = make_input(64, 5120, 2)
+    gs = np.array([0.004, 0.0015], dtype=np.float32)
+    dx, dg = g.Dev(x), g.Dev(gs)
+    codes = g.empty_like_dev((64, 2560), dtype=np.uint8)
+    scales = g.empty_like_dev((64, 320), dtype=np.uint8)
+    g.capi.check("q3x_b200_nvfp4_quantize", dx, 64, 5120, 32, dg, codes, scales, None)
+    g.sync()
+    want_c, want_s = orc.nvfp4_quantize_with_scales(x, gs, 32)
+    g.assert_bits_equal(codes.get(), want_c, "codes, static scale")
+    g.assert_bits_equal(scales.get(), want_s, "scales, static scale")
+    deq = orc.nvfp4_dequantize(codes.get()[:32], scales.get()[:32], gs[0])
+    L = orc.oracle_lib()
+    e2 = np.array([L.decode_e2m1(i) for i in range(16)], dtype=np.float32)
+    e4 = np.array([L.decode_e4m3(i) for i in range(256)], dtype=np.float32)
+    c = codes.get()[:32]
+    nib = np.stack([c & 0xF, c >> 4], axis=-1).reshape(32, 5120)
+    manual = e2[nib] * np.repeat(e4[scales.get()[:32]], 16, axis=1) * gs[0]
+    assert np.array_equal(deq.view(np.uint32), manual.astype(np.float32).view(np.uint32))
+
+
+@pytest.mark.parametrize("tokens,rps", [(1, 0), (7, 0), (33, 16), (512, 512), (513, 512), (1024, 512)])
+def test_residual_norm_nvfp4(g, tokens, rps):
+    hidden = 5120
+    rng = np.random.default_rng([tokens, rps, 3])
+    left, right = fx.normal_bf16(rng, (tokens, hidden)), fx.normal_bf16(rng, (tokens, hidden))
+    w = fx.normal_bf16(rng, (hidden,), 0.02)
+    groups = 1 if rps == 0 else (tokens + rps - 1) // rps
+    dl, dr, dw = g.Dev(left), g.Dev(right), g.Dev(w)
+    res, nrm = g.empty_like_dev((tokens, hidden)), g.empty_like_dev((tokens, hidden))
+    amax = g.empty_like_dev((groups,), dtype=np.uint32, fill=123456)
+    gs = g.empty_like_dev((groups,), dtype=np.float32)
+    codes = g.empty_like_dev((tokens, hidden // 2), dtype=np.uint8)
+    scales = g.empty_like_dev((tokens, hidden // 16), dtype=np.uint8)
+    g.capi.check("q3x_b200_residual_add_rms_norm_nvfp4", dl, dr, dw, tokens, hidden, EPS, rps, res, nrm, amax, gs,
+                 codes, scales, None)
+    g.sync()
+    want_r, want_n = orc.residual_add_rms_norm(left, right, w, EPS)
+    g.assert_bits_equal(res.get(), want_r, "residual")
+    g.assert_bf16_within(nrm.get(), want_n, 1, 0.98, "normalized")
+    # identical pre-quantisation values -> identical bytes
+    want_c, want_s, want_g = orc.nvfp4_quantize(nrm.get(), rps)
+    assert np.array_equal(gs.get().view(np.uint32), want_g.view(np.uint32)), "global scale"
+    g.assert_bits_equal(scales.get(), want_s, "block scales")
+    g.assert_bits_equal(codes.get(), want_c, "codes")
+    # and the un-fused sequence of entry points produces the same bytes
+    r2, n2 = g.empty_like_dev((tokens, hidden)), g.empty_like_dev((tokens, hidden))
+    c2 = g.empty_like_dev((tokens, hidden // 2), dtype=np.uint8)
+    s2 = g.empty_like_dev((tokens, hidden // 16), dtype=np.uint8)
+    g.capi.check("q3x_b200_residual_add_rms_norm", dl, dr, dw, tokens, hidden, EPS, r2, n2, None)
+    g.capi.check("q3x_b200_nvfp4_quantize_dynamic", n2, tokens, hidden, rps, amax, gs, c2, s2, None)
+    g.sync()
+    g.assert_bits_equal(n2.get(), nrm.get(), "normalized, fused vs unfused")
+    g.assert_bits_equal(c2.get(), codes.get(), "codes, fused vs unfused")
+    g.assert_bits_equal(s2.get(), scales.get(), "scales, fused vs unfused")
+    for d in (res, nrm, codes, scales, gs, amax):
+        assert d.guards_intact()
+
+
+@pytest.mark.parametrize("tokens,rps", [(1, 0), (9, 4), (512, 512), (600, 512)])
+def test_gated_norm_nvfp4(g, tokens, rps):
+    heads, dim = 48, 128
+    rng = np.random.default_rng([tokens, rps, 4])
+    x, z = fx.normal_bf16(rng, (tokens, heads, dim)), fx.normal_bf16(rng, (tokens, heads, dim))
+    w = orc.bf16_encode((0.75 + rng.random(dim) * 0.5).astype(np.float32))
+    groups = 1 if rps == 0 else (tokens + rps - 1) // rps
+    dx, dz, dw = g.Dev(x), g.Dev(z), g.Dev(w)
+    out = g.empty_like_dev((tokens, heads * dim))
+    amax = g.empty_like_dev((groups,), dtype=np.uint32, fill=99)
+    gs = g.empty_like_dev((groups,), dtype=np.float32)
+    codes = g.empty_like_dev((tokens, heads * dim // 2), dtype=np.uint8)
+    scales = g.empty_like_dev((tokens, heads * dim // 16), dtype=np.uint8)
+    g.capi.check("q3x_b200_rms_norm_silu_gate_nvfp4", dx, dw, dz, tokens, heads, dim, EPS, rps, out, amax, gs, codes,
+                 scales, None)
+    g.sync()
+    want = orc.rms_norm_rows(x, w, EPS, centered=False, gate=z).reshape(tokens, heads * dim)
+    g.assert_bf16_within(out.get(), want, 1, 0.98, "gated norm")
+    want_c, want_s, want_g = orc.nvfp4_quantize(out.get(), rps)
+    assert np.array_equal(gs.get().view(np.uint32), want_g.view(np.uint32))
+    g.assert_bits_equal(scales.get(), want_s, "block scales")
+    g.assert_bits_equal(codes.get(), want_c, "codes")
