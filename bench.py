@@ -46,6 +46,8 @@ def parse_args():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--probe-only", action="store_true",
+                    help="time each operator alone (few launches; the form profiled under ncu) and exit")
     return ap.parse_args()
 
 
@@ -288,6 +290,39 @@ def workload_config(tokens, gpus):
 
 # ------------------------------------------------------------------------------------ GPU arm
 
+def probe_ops(stack, chain, stream_obj, T, peak, warm, reps):
+    """Times every fused operator alone with CUDA events on its own stream: microseconds per call,
+    algorithmic GB/s and the fraction of the HBM peak."""
+    import torch
+
+    stream = stream_obj.cuda_stream
+    probes = {
+        "embedding_gather": lambda: stack.op_embedding(stream),
+        "residual_rmsnorm_nvfp4": lambda: stack.op_residual_norm(0, 0, 0, 1, stream),
+        "conv1d_silu_l2norm": lambda: stack.op_conv(0, stream),
+        "gated_rmsnorm_nvfp4": lambda: stack.op_gated_norm(0, stream),
+        "attention_preprocess": lambda: stack.op_preprocess(3, stream),
+        "sigmoid_gate": lambda: stack.op_sigmoid_gate(stream),
+        "swiglu": lambda: stack.op_swiglu(stream),
+    }
+    per_op = {}
+    with torch.cuda.stream(stream_obj):
+        for name, fn in probes.items():
+            for _ in range(warm):
+                fn()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream_obj)
+            for _ in range(reps):
+                fn()
+            e1.record(stream_obj)
+            stream_obj.synchronize()
+            us = e0.elapsed_time(e1) * 1e3 / reps
+            gbs = chain.BYTES_PER_TOKEN[name] * T / (us * 1e-6) / 1e9
+            per_op[name] = {"us": round(us, 2), "algorithmic_GBs": round(gbs, 1), "frac_of_peak": round(gbs / peak, 4),
+                            "bytes_per_token": chain.BYTES_PER_TOKEN[name], "kernels": chain.KERNELS[name]}
+    return per_op
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
@@ -321,6 +356,12 @@ def main():
         if distributed:
             dist.barrier()
         torch.cuda.synchronize()
+
+    if args.probe_only:
+        peak, _ = measured_peak()
+        print(json.dumps({"probe_only": True, "tokens": T, "per_op": probe_ops(stack, chain, stream_obj, T, peak, 1, 3)}),
+              flush=True)
+        return 0
 
     # ---- warm-up (eager), then capture one step into a CUDA graph ------------------------------
     with torch.cuda.stream(stream_obj):
@@ -368,32 +409,7 @@ def main():
 
     # ---- per-operator timing (each op alone, CUDA events on its stream) --------------------------
     peak, peak_kind = measured_peak()
-    per_op = {}
-    if rank == 0:
-        probes = {
-            "embedding_gather": lambda: stack.op_embedding(stream),
-            "residual_rmsnorm_nvfp4": lambda: stack.op_residual_norm(0, 0, 0, 1, stream),
-            "conv1d_silu_l2norm": lambda: stack.op_conv(0, stream),
-            "gated_rmsnorm_nvfp4": lambda: stack.op_gated_norm(0, stream),
-            "attention_preprocess": lambda: stack.op_preprocess(3, stream),
-            "sigmoid_gate": lambda: stack.op_sigmoid_gate(stream),
-            "swiglu": lambda: stack.op_swiglu(stream),
-        }
-        reps = 10
-        with torch.cuda.stream(stream_obj):
-            for name, fn in probes.items():
-                for _ in range(3):
-                    fn()
-                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                e0.record(stream_obj)
-                for _ in range(reps):
-                    fn()
-                e1.record(stream_obj)
-                stream_obj.synchronize()
-                us = e0.elapsed_time(e1) * 1e3 / reps
-                gbs = chain.BYTES_PER_TOKEN[name] * T / (us * 1e-6) / 1e9
-                per_op[name] = {"us": round(us, 2), "algorithmic_GBs": round(gbs, 1), "frac_of_peak": round(gbs / peak, 4),
-                                "bytes_per_token": chain.BYTES_PER_TOKEN[name], "kernels": chain.KERNELS[name]}
+    per_op = probe_ops(stack, chain, stream_obj, T, peak, 3, 10) if rank == 0 else {}
     # dominant kernel = the SwiGLU stream (the largest share of the step's bytes, one kernel per launch)
     roofline = None
     if rank == 0:

@@ -108,11 +108,16 @@ int q3x_b200_residual_add_rms_norm(const uint16_t* left, const uint16_t* right,
  * even column in the low nibble).  Rows are grouped `rows_per_scale` at a time (0 = one group);
  * group g owns global_scales[g].  codes [rows, cols/2], scales [rows, cols/16] row-major. */
 
-/* Scratch words one amax reduction needs: one uint32 per scale group. */
+/* Number of scale groups of a [rows, *] tensor. */
 size_t q3x_b200_nvfp4_group_count(size_t rows, size_t rows_per_scale);
+/* Size, in uint32 words, of the `scratch` argument of the entry points below: one amax word and
+ * one finished-row counter per scale group plus an error word.  The caller owns the memory; every
+ * call clears what it uses.  After a fused call, scratch[2 * groups] is non-zero only if a bounded
+ * wait inside the kernel gave up (the outputs are then not valid). */
+size_t q3x_b200_nvfp4_scratch_words(size_t rows, size_t rows_per_scale);
 
-/* amax_bits[g] = largest finite |x| of group g as bf16 magnitude bits (uint32).  The call
- * zeroes amax_bits itself. */
+/* amax_bits[g] = largest finite |x| of group g as bf16 magnitude bits (uint32), group_count words.
+ * The call zeroes amax_bits itself. */
 int q3x_b200_group_amax(const uint16_t* in, size_t rows, size_t cols, size_t rows_per_scale,
                         uint32_t* amax_bits, void* stream);
 /* global_scales[g] = amax == 0 ? 1 : amax / 2688. */
@@ -122,28 +127,31 @@ int q3x_b200_amax_to_global_scale(const uint32_t* amax_bits, size_t groups, floa
 int q3x_b200_nvfp4_quantize(const uint16_t* in, size_t rows, size_t cols, size_t rows_per_scale,
                             const float* global_scales, uint8_t* codes, uint8_t* scales,
                             void* stream);
-/* The three steps above in one call (amax_scratch: q3x_b200_nvfp4_group_count words). */
+/* The three steps above in one call. */
 int q3x_b200_nvfp4_quantize_dynamic(const uint16_t* in, size_t rows, size_t cols,
-                                    size_t rows_per_scale, uint32_t* amax_scratch,
+                                    size_t rows_per_scale, uint32_t* scratch,
                                     float* global_scales_out, uint8_t* codes, uint8_t* scales,
                                     void* stream);
 
 /* Residual add + centred RMSNorm + NVFP4 of the normalised rows, global scale from the group
  * amax.  normalized_out is required (it is the operand the codes are derived from, bit for
- * bit); it may be exactly `right`.  amax_scratch: q3x_b200_nvfp4_group_count words. */
+ * bit); it may be exactly `right`.  When a scale group is no longer than one sweep of the
+ * resident thread teams (592 rows on a B200) this is ONE pass over HBM: a cooperative kernel
+ * that defers each row's quantisation until its group's amax is complete; otherwise three
+ * kernels.  Both produce the same bytes. */
 int q3x_b200_residual_add_rms_norm_nvfp4(const uint16_t* left, const uint16_t* right,
                                          const uint16_t* weight, size_t tokens, size_t hidden,
                                          float eps, size_t rows_per_scale, uint16_t* residual_out,
-                                         uint16_t* normalized_out, uint32_t* amax_scratch,
+                                         uint16_t* normalized_out, uint32_t* scratch,
                                          float* global_scales_out, uint8_t* codes, uint8_t* scales,
                                          void* stream);
 
 /* Gated RMSNorm * silu(z) + NVFP4 of its output rows.  `heads_per_row` heads of `dim` form one
- * quantisation row (48 x 128 = 6144 for the GDN output). */
+ * quantisation row (48 x 128 = 6144 for the GDN output).  Same single-pass scheme. */
 int q3x_b200_rms_norm_silu_gate_nvfp4(const uint16_t* in, const uint16_t* weight,
                                       const uint16_t* gate, size_t tokens, size_t heads_per_row,
                                       size_t dim, float eps, size_t rows_per_scale, uint16_t* out,
-                                      uint32_t* amax_scratch, float* global_scales_out,
+                                      uint32_t* scratch, float* global_scales_out,
                                       uint8_t* codes, uint8_t* scales, void* stream);
 
 /* Diagnostics (no counterpart in the reference): the two narrow conversions the quantiser uses,

@@ -30,6 +30,7 @@ SIGNATURES = {
     "q3x_b200_residual_add": (_i, [_p, _p, _z, _p, _p]),
     "q3x_b200_residual_add_rms_norm": (_i, [_p, _p, _p, _z, _z, _f, _p, _p, _p]),
     "q3x_b200_nvfp4_group_count": (_z, [_z, _z]),
+    "q3x_b200_nvfp4_scratch_words": (_z, [_z, _z]),
     "q3x_b200_group_amax": (_i, [_p, _z, _z, _z, _p, _p]),
     "q3x_b200_amax_to_global_scale": (_i, [_p, _z, _p, _p]),
     "q3x_b200_nvfp4_quantize": (_i, [_p, _z, _z, _z, _p, _p, _p, _p]),

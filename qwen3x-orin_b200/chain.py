@@ -45,7 +45,7 @@ BYTES_PER_TOKEN = {
 }
 # kernels each entry point launches (memset nodes not counted)
 KERNELS = {
-    "embedding_gather": 1, "residual_rmsnorm_nvfp4": 3, "conv1d_silu_l2norm": 1, "gated_rmsnorm_nvfp4": 3,
+    "embedding_gather": 1, "residual_rmsnorm_nvfp4": 2, "conv1d_silu_l2norm": 1, "gated_rmsnorm_nvfp4": 2,
     "attention_preprocess": 1, "sigmoid_gate": 1, "swiglu": 1,
 }
 GDN_OPS = ["residual_rmsnorm_nvfp4", "conv1d_silu_l2norm", "gated_rmsnorm_nvfp4", "residual_rmsnorm_nvfp4", "swiglu"]
@@ -127,7 +127,7 @@ class LayerStack:
         self.mlp_out = torch.empty((T, INTERMEDIATE), **bf)
         groups = max(1, math.ceil(T / CHUNK))
         self.groups = groups
-        self.amax = torch.zeros(groups, device=dev, dtype=torch.int32)
+        self.amax = torch.zeros(2 * groups + 2, device=dev, dtype=torch.int32)  # NVFP4 scratch words
         self.global_scales = torch.empty(groups, device=dev, dtype=torch.float32)
         self.codes = torch.empty((T, HIDDEN // 2), device=dev, dtype=torch.uint8)
         self.scales = torch.empty((T, HIDDEN // 16), device=dev, dtype=torch.uint8)

@@ -70,55 +70,48 @@ __device__ __forceinline__ uint4 centered_norm_head(const uint4& x, const uint4&
   return pack8(y);
 }
 
-// items = tokens * 28; a warp takes two items per iteration so that four 128-bit loads are in flight.
-__global__ void __launch_bounds__(kThreads) attention_preprocess_kernel(
+// One CTA of seven warps owns one token per iteration: warps 0..5 take four q heads each (with their
+// gates), warp 6 the four k heads, so the q / k choice is warp-uniform and no index division is
+// needed.  A lane issues the eight (q, gate) or four (k) 128-bit loads of its heads back to back.
+constexpr int kPreWarps = 7;
+constexpr int kPreThreads = kPreWarps * 32;
+constexpr int kHeadsPerWarp = 4;
+static_assert(kPreWarps * kHeadsPerWarp == kHeadsPerToken, "28 heads = 7 warps x 4");
+
+__global__ void __launch_bounds__(kPreThreads) attention_preprocess_kernel(
     const uint4* __restrict__ q_gate, uint4* key, const uint4* __restrict__ q_weight,
     const uint4* __restrict__ k_weight, float eps, uint4* __restrict__ q_out, uint4* __restrict__ gate_out,
-    const float* __restrict__ cosines, const float* __restrict__ sines, size_t first_position, size_t items) {
+    const float* __restrict__ cosines, const float* __restrict__ sines, size_t first_position, size_t tokens) {
   const int lane = threadIdx.x & 31;
-  const size_t warp = static_cast<size_t>(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5);
-  const size_t stride = static_cast<size_t>(gridDim.x) * kWarpsPerCta;
-  const uint4 wq = ld_weight(q_weight + lane);
-  const uint4 wk = ld_weight(k_weight + lane);
+  const int warp = threadIdx.x >> 5;
+  const bool is_q = warp < kPreWarps - 1;
+  const uint4 w = ld_weight((is_q ? q_weight : k_weight) + lane);
 
-  for (size_t item0 = warp; item0 < items; item0 += 2 * stride) {
-    uint4 x[2], g[2];
-    size_t token[2];
-    int head[2];
-    bool valid[2];
+  for (size_t token = blockIdx.x; token < tokens; token += gridDim.x) {
+    uint4 x[kHeadsPerWarp], g[kHeadsPerWarp];
+    if (is_q) {
+      const uint4* src = q_gate + (token * (2 * kQHeads) + 2 * (warp * kHeadsPerWarp)) * kVecPerHead + lane;
 #pragma unroll
-    for (int u = 0; u < 2; ++u) {
-      const size_t item = item0 + u * stride;
-      valid[u] = item < items;
-      token[u] = item / kHeadsPerToken;
-      head[u] = static_cast<int>(item - token[u] * kHeadsPerToken);
-      x[u] = g[u] = make_uint4(0, 0, 0, 0);
-      if (valid[u]) {
-        if (head[u] < kQHeads) {
-          const uint4* src = q_gate + (token[u] * (2 * kQHeads) + 2 * head[u]) * kVecPerHead + lane;
-          x[u] = ld_stream(src);
-          g[u] = ld_stream(src + kVecPerHead);
-        } else {
-          x[u] = ld_vec(key + (token[u] * kKvHeads + (head[u] - kQHeads)) * kVecPerHead + lane);
-        }
+      for (int h = 0; h < kHeadsPerWarp; ++h) {
+        x[h] = ld_stream(src + (2 * h) * kVecPerHead);
+        g[h] = ld_stream(src + (2 * h + 1) * kVecPerHead);
       }
+    } else {
+#pragma unroll
+      for (int h = 0; h < kHeadsPerWarp; ++h) x[h] = ld_vec(key + (token * kKvHeads + h) * kVecPerHead + lane);
     }
+    const size_t table = (first_position + token) * kPairs;
 #pragma unroll
-    for (int u = 0; u < 2; ++u) {
-      if (!valid[u]) continue;  // warp-uniform
-      const bool is_q = head[u] < kQHeads;
-      uint4 y = centered_norm_head(x[u], is_q ? wq : wk, eps);
+    for (int h = 0; h < kHeadsPerWarp; ++h) {
+      uint4 y = centered_norm_head(x[h], w, eps);
       const uint4 partner = shfl_xor_vec(y, 4);
-      if (lane < 8) {
-        const size_t table = (first_position + token[u]) * kPairs;
-        y = rotate8(y, partner, cosines + table, sines + table, lane);
-      }
+      if (lane < 8) y = rotate8(y, partner, cosines + table, sines + table, lane);
       if (is_q) {
-        const size_t dst = (token[u] * kQHeads + head[u]) * kVecPerHead + lane;
+        const size_t dst = (token * kQHeads + warp * kHeadsPerWarp + h) * kVecPerHead + lane;
         st_vec(q_out + dst, y);
-        st_vec(gate_out + dst, g[u]);
+        st_vec(gate_out + dst, g[h]);
       } else {
-        st_vec(key + (token[u] * kKvHeads + (head[u] - kQHeads)) * kVecPerHead + lane, y);
+        st_vec(key + (token * kKvHeads + h) * kVecPerHead + lane, y);
       }
     }
   }
@@ -214,12 +207,11 @@ extern "C" int q3x_b200_full_attention_preprocess(const uint16_t* interleaved_q_
   if (!aligned16(interleaved_q_gate) || !aligned16(key) || !aligned16(q_weight) || !aligned16(k_weight) ||
       !aligned16(q_out) || !aligned16(gate_out) || !aligned16(cosines) || !aligned16(sines))
     return kNotSupported;
-  const size_t items = tokens * kHeadsPerToken;
   clear_stale_error();
-  attention_preprocess_kernel<<<grid_for(items, 2 * kWarpsPerCta, 8), kThreads, 0, as_stream(stream)>>>(
+  attention_preprocess_kernel<<<grid_for(tokens, 1, 32), kPreThreads, 0, as_stream(stream)>>>(
       reinterpret_cast<const uint4*>(interleaved_q_gate), reinterpret_cast<uint4*>(key),
       reinterpret_cast<const uint4*>(q_weight), reinterpret_cast<const uint4*>(k_weight), eps,
-      reinterpret_cast<uint4*>(q_out), reinterpret_cast<uint4*>(gate_out), cosines, sines, first_position, items);
+      reinterpret_cast<uint4*>(q_out), reinterpret_cast<uint4*>(gate_out), cosines, sines, first_position, tokens);
   return launch_status();
 }
 

@@ -110,15 +110,45 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 
 // ---------------------------------------------------------------------------- activations
 
-// silu(g) = g / (1 + exp(-g)): the form of src/runtime/reference/decode_ops.cpp:315-316.
-// expf and the division are the IEEE-accurate CUDA versions (no fast-math).
-__device__ __forceinline__ float silu(float g) { return g / (1.0f + expf(-g)); }
+// exp(-|g|) in (0, 1] from one MUFU.EX2.  ex2.approx has a relative error of 2^-22; the rounded
+// argument adds |g| * 2^-24, so the total stays below 2e-6 for |g| <= 20 and below 1e-5 wherever the
+// result is not yet a bf16 subnormal.
+// It is evaluated as the square of exp(-|g|/2): the single-instruction (flushing) form of ex2 then
+// only flushes beyond |g| = 174, where the result is below every bf16 subnormal anyway, while the
+// product keeps FP32 subnormals -- the tail of silu for g in (-92, -87) needs them.
+__device__ __forceinline__ float exp_neg_abs(float g) {
+  float h;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(h) : "f"(-fabsf(g) * 0.7213475204444817f));
+  return h * h;
+}
+// 1 / b for b in [1, 2]: one MUFU.RCP (relative error 2^-23; no subnormals in this range).
+__device__ __forceinline__ float rcp_approx(float b) {
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(b));
+  return r;
+}
 
-// Branch-stable sigmoid of decode_ops.cpp:334-337.
+// sigmoid(g) in the branch-stable form of src/runtime/reference/decode_ops.cpp:334-337, written
+// so that both branches share one exponential and one reciprocal: with e = exp(-|g|),
+//   g >= 0: 1 / (1 + e)        g < 0: e / (1 + e).
+// Nothing can overflow (e <= 1, 1 + e <= 2), so the whole bf16 range of g is handled, including
+// gates so negative that the result is a subnormal.  The FP32 error is a few 2^-22, far inside the
+// half-ulp of the bf16 rounding that follows, so a result differs from the host op by at most one
+// bf16 ulp, and only when the exact value sits within ~1e-6 (relative) of a rounding boundary.
 __device__ __forceinline__ float stable_sigmoid(float g) {
-  if (g >= 0.0f) return 1.0f / (1.0f + expf(-g));
-  const float e = expf(g);
-  return e / (1.0f + e);
+  const float e = exp_neg_abs(g);
+  const float r = rcp_approx(1.0f + e);
+  return (g >= 0.0f ? 1.0f : e) * r;
+}
+
+// silu(g) = g / (1 + exp(-g)) (decode_ops.cpp:315-316) = g * sigmoid(g), same stable evaluation.
+// The host op evaluates exp(-g) in FP32, which overflows to infinity for g < -88.7228317 and makes
+// its quotient -0 there; the same cut-off is applied so that the two agree on that tail too.
+__device__ __forceinline__ float silu(float g) {
+  const float e = exp_neg_abs(g);
+  const float r = rcp_approx(1.0f + e);
+  const float num = g >= 0.0f ? 1.0f : (g < -88.72283172607422f ? 0.0f : e);
+  return g * (num * r);
 }
 
 // ---------------------------------------------------------------------------- bf16 amax

@@ -22,71 +22,75 @@ namespace {
 
 constexpr int kThreads = 128;
 constexpr int kTokenUnroll = 4;
-constexpr int kRunTokens = 32;  // tokens per CTA on the parallel path (multiple of kTokenUnroll)
+constexpr int kRunTokens = 64;  // tokens per CTA on the parallel path (multiple of kTokenUnroll)
 constexpr int kHeadVectors = Q3X_B200_GDN_HEAD_DIM / 8;                               // 16 lanes per head
 constexpr int kQkVectors = 2 * Q3X_B200_GDN_QK_HEADS * Q3X_B200_GDN_HEAD_DIM / 8;     // 512: q then k
 
-__device__ __forceinline__ uint16_t half_of(const uint4& v, int i) {
+__device__ __forceinline__ uint32_t half_of(const uint4& v, int i) {
   const uint32_t w = i < 2 ? v.x : i < 4 ? v.y : i < 6 ? v.z : v.w;
-  return static_cast<uint16_t>((i & 1) ? (w >> 16) : (w & 0xffffu));
+  return (i & 1) ? (w >> 16) : (w & 0xffffu);
 }
 
-template <bool kL2>
-__global__ void __launch_bounds__(kThreads) causal_conv_kernel(const uint4* raw, size_t tokens, int channel_vectors,
-                                                               const uint4* __restrict__ weight, uint4* history,
-                                                               uint4* out, size_t run_tokens, float l2_eps,
-                                                               float q_scale) {
+// history vectors (channel-major: element 3j + r = channel j, slot r) -> row r as a packed vector
+__device__ __forceinline__ uint4 history_row(const uint4 (&h)[3], int r) {
+  uint32_t e[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int idx = 3 * j + r;
+    e[j] = half_of(h[idx / 8], idx % 8);
+  }
+  return make_uint4(e[0] | (e[1] << 16), e[2] | (e[3] << 16), e[4] | (e[5] << 16), e[6] | (e[7] << 16));
+}
+
+// kInPlace: raw == out with a single token run; the last three raw rows are then kept as bits in
+// registers because memory no longer holds them when the history is published.
+template <bool kL2, bool kInPlace>
+__global__ void __launch_bounds__(kThreads, kInPlace ? 1 : 4)
+    causal_conv_kernel(const uint4* raw, size_t tokens, int channel_vectors, const uint4* __restrict__ weight,
+                       uint4* history, uint4* out, size_t run_tokens, float l2_eps, float q_scale) {
   const int cv = blockIdx.x * kThreads + threadIdx.x;  // channel vector: channels 8cv .. 8cv+7
   const bool active = cv < channel_vectors;
   const size_t t0 = static_cast<size_t>(blockIdx.y) * run_tokens;
   const size_t t1 = min(tokens, t0 + run_tokens);
 
-  // taps: weight[(8cv + j) * 4 + tap]  ->  four vectors, vector k = channels 2k and 2k+1
-  float w[8][4];
-  // the three rows before t0, per channel, as floats (exact bf16 values): win[r][j], r = 0 oldest
-  float win[3][8];
-  uint4 win_bits[3];
+  float w[8][4];   // taps: weight[(8cv + j) * 4 + tap]: four vectors, vector k = channels 2k, 2k+1
+  float win[3][8]; // the three rows before the current token (exact bf16 values), win[0] oldest
+  uint4 keep[3];   // their bits (in-place path only)
 #pragma unroll
-  for (int r = 0; r < 3; ++r) win_bits[r] = make_uint4(0, 0, 0, 0);
-  if (active) {
+  for (int r = 0; r < 3; ++r) keep[r] = make_uint4(0, 0, 0, 0);
+  {
+    uint4 rows[3];
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      float f[8];
-      unpack8(ld_weight(weight + static_cast<size_t>(cv) * 4 + k), f);
+    for (int r = 0; r < 3; ++r) rows[r] = make_uint4(0, 0, 0, 0);
+    if (active) {
 #pragma unroll
-      for (int tap = 0; tap < 4; ++tap) {
-        w[2 * k][tap] = f[tap];
-        w[2 * k + 1][tap] = f[4 + tap];
+      for (int k = 0; k < 4; ++k) {
+        float f[8];
+        unpack8(ld_weight(weight + static_cast<size_t>(cv) * 4 + k), f);
+#pragma unroll
+        for (int tap = 0; tap < 4; ++tap) {
+          w[2 * k][tap] = f[tap];
+          w[2 * k + 1][tap] = f[4 + tap];
+        }
+      }
+      if (t0 == 0) {
+        uint4 h[3];
+#pragma unroll
+        for (int k = 0; k < 3; ++k) h[k] = ld_vec(history + static_cast<size_t>(cv) * 3 + k);
+#pragma unroll
+        for (int r = 0; r < 3; ++r) rows[r] = history_row(h, r);
+      } else {
+#pragma unroll
+        for (int r = 0; r < 3; ++r)  // t0 >= run_tokens >= 3
+          rows[r] = ld_vec(raw + (t0 - 3 + r) * channel_vectors + cv);
       }
     }
-    if (t0 == 0) {
-      // history[(8cv + j) * 3 + r]: 24 bf16 = three vectors, channel-major -> transpose to rows
-      uint4 h[3];
 #pragma unroll
-      for (int k = 0; k < 3; ++k) h[k] = ld_vec(history + static_cast<size_t>(cv) * 3 + k);
-      uint16_t rows[3][8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j)
-#pragma unroll
-        for (int r = 0; r < 3; ++r) {
-          const int e = j * 3 + r;
-          rows[r][j] = half_of(h[e / 8], e % 8);
-        }
-#pragma unroll
-      for (int r = 0; r < 3; ++r) {
-        win_bits[r].x = rows[r][0] | (static_cast<uint32_t>(rows[r][1]) << 16);
-        win_bits[r].y = rows[r][2] | (static_cast<uint32_t>(rows[r][3]) << 16);
-        win_bits[r].z = rows[r][4] | (static_cast<uint32_t>(rows[r][5]) << 16);
-        win_bits[r].w = rows[r][6] | (static_cast<uint32_t>(rows[r][7]) << 16);
-      }
-    } else {
-#pragma unroll
-      for (int r = 0; r < 3; ++r)  // t0 >= run_tokens >= 3
-        win_bits[r] = ld_vec(raw + (t0 - 3 + r) * channel_vectors + cv);
+    for (int r = 0; r < 3; ++r) {
+      unpack8(rows[r], win[r]);
+      if (kInPlace) keep[r] = rows[r];
     }
   }
-#pragma unroll
-  for (int r = 0; r < 3; ++r) unpack8(win_bits[r], win[r]);
 
   const bool is_q = kL2 && cv < kQkVectors / 2;
   const bool is_qk = kL2 && cv < kQkVectors;  // uniform per CTA: 128 vectors per CTA divide 256
@@ -96,7 +100,8 @@ __global__ void __launch_bounds__(kThreads) causal_conv_kernel(const uint4* raw,
 #pragma unroll
     for (int u = 0; u < kTokenUnroll; ++u) {
       x_bits[u] = make_uint4(0, 0, 0, 0);
-      if (active && t + u < t1) x_bits[u] = ld_vec(raw + (t + u) * channel_vectors + cv);
+      if (active && t + u < t1) x_bits[u] = kInPlace ? ld_vec(raw + (t + u) * channel_vectors + cv)
+                                                     : ld_stream(raw + (t + u) * channel_vectors + cv);
     }
 #pragma unroll
     for (int u = 0; u < kTokenUnroll; ++u) {
@@ -114,9 +119,11 @@ __global__ void __launch_bounds__(kThreads) causal_conv_kernel(const uint4* raw,
         win[1][j] = win[2][j];
         win[2][j] = x[j];
       }
-      win_bits[0] = win_bits[1];
-      win_bits[1] = win_bits[2];
-      win_bits[2] = x_bits[u];
+      if (kInPlace) {
+        keep[0] = keep[1];
+        keep[1] = keep[2];
+        keep[2] = x_bits[u];
+      }
       uint4 packed = pack8(y);
       if (is_qk) {
         // L2 norm of the ROUNDED conv output over the 128 channels of this head (16 lanes)
@@ -136,26 +143,39 @@ __global__ void __launch_bounds__(kThreads) causal_conv_kernel(const uint4* raw,
     }
   }
 
-  // new history = the last three raw rows of (old history ++ raw); published by the first run's CTA
+  // New history = the last three rows of (old history ++ raw), published by the first run's CTA.
   if (blockIdx.y == 0 && active) {
-    if (gridDim.y > 1) {  // tokens > run_tokens >= 3: the rows come straight from raw
+    uint4 rows[3];
+    if (kInPlace) {
 #pragma unroll
-      for (int r = 0; r < 3; ++r) win_bits[r] = ld_vec(raw + (tokens - 3 + r) * channel_vectors + cv);
-    }  // else the register window already is that sequence (also when tokens < 3)
-    uint16_t flat[24];
+      for (int r = 0; r < 3; ++r) rows[r] = keep[r];
+    } else {
+      uint4 h[3];
+      if (tokens < 3) {
+#pragma unroll
+        for (int k = 0; k < 3; ++k) h[k] = ld_vec(history + static_cast<size_t>(cv) * 3 + k);
+      }
+#pragma unroll
+      for (int r = 0; r < 3; ++r) {
+        // row index in the concatenation, counted from the first raw row (negative = old history)
+        const long long idx = static_cast<long long>(tokens) - 3 + r;
+        if (idx >= 0) {
+          rows[r] = ld_vec(raw + static_cast<size_t>(idx) * channel_vectors + cv);
+        } else {
+          rows[r] = idx == -1 ? history_row(h, 2) : idx == -2 ? history_row(h, 1) : history_row(h, 0);
+        }
+      }
+    }
+    uint32_t flat[24];
 #pragma unroll
     for (int j = 0; j < 8; ++j)
 #pragma unroll
-      for (int r = 0; r < 3; ++r) flat[j * 3 + r] = half_of(win_bits[r], j);
+      for (int r = 0; r < 3; ++r) flat[j * 3 + r] = half_of(rows[r], j);
 #pragma unroll
-    for (int k = 0; k < 3; ++k) {
-      uint4 v;
-      v.x = flat[k * 8 + 0] | (static_cast<uint32_t>(flat[k * 8 + 1]) << 16);
-      v.y = flat[k * 8 + 2] | (static_cast<uint32_t>(flat[k * 8 + 3]) << 16);
-      v.z = flat[k * 8 + 4] | (static_cast<uint32_t>(flat[k * 8 + 5]) << 16);
-      v.w = flat[k * 8 + 6] | (static_cast<uint32_t>(flat[k * 8 + 7]) << 16);
-      st_vec(history + static_cast<size_t>(cv) * 3 + k, v);
-    }
+    for (int k = 0; k < 3; ++k)
+      st_vec(history + static_cast<size_t>(cv) * 3 + k,
+             make_uint4(flat[k * 8 + 0] | (flat[k * 8 + 1] << 16), flat[k * 8 + 2] | (flat[k * 8 + 3] << 16),
+                        flat[k * 8 + 4] | (flat[k * 8 + 5] << 16), flat[k * 8 + 6] | (flat[k * 8 + 7] << 16)));
   }
 }
 
@@ -197,12 +217,13 @@ int launch_conv(const uint16_t* raw, size_t tokens, size_t channels, const uint1
   auto W = reinterpret_cast<const uint4*>(weight);
   auto H = reinterpret_cast<uint4*>(history);
   auto O = reinterpret_cast<uint4*>(out);
+  cudaStream_t s = as_stream(stream);
   if (l2)
-    causal_conv_kernel<true><<<grid, kThreads, 0, as_stream(stream)>>>(R, tokens, channel_vectors, W, H, O, run,
-                                                                      l2_eps, q_scale);
+    causal_conv_kernel<true, false><<<grid, kThreads, 0, s>>>(R, tokens, channel_vectors, W, H, O, run, l2_eps, q_scale);
+  else if (serial)
+    causal_conv_kernel<false, true><<<grid, kThreads, 0, s>>>(R, tokens, channel_vectors, W, H, O, run, 0.0f, 1.0f);
   else
-    causal_conv_kernel<false><<<grid, kThreads, 0, as_stream(stream)>>>(R, tokens, channel_vectors, W, H, O, run,
-                                                                       0.0f, 1.0f);
+    causal_conv_kernel<false, false><<<grid, kThreads, 0, s>>>(R, tokens, channel_vectors, W, H, O, run, 0.0f, 1.0f);
   return launch_status();
 }
 

@@ -34,3 +34,22 @@ int check_residual_norm(const uint16_t* left, const uint16_t* right, const uint1
                         bool* done);
 
 }  // namespace q3x
+
+namespace q3x {
+
+// Scratch words (uint32) of the NVFP4 entry points for `groups` scale groups:
+// [0,G) amax bits, [G,2G) finished-row counters, [2G] error flag, one spare.
+size_t fused_scratch_words(size_t groups);
+
+// Single-pass kernels (fused_nvfp4.cu).  Return false, with nothing enqueued, when the fused path does
+// not apply; the caller then takes the multi-kernel path, which produces the same bytes.
+bool launch_residual_norm_nvfp4_fused(const uint16_t* left, const uint16_t* right, const uint16_t* weight,
+                                      size_t tokens, size_t hidden, float eps, size_t rows_per_scale,
+                                      uint16_t* residual_out, uint16_t* normalized_out, uint32_t* scratch,
+                                      float* global_scales_out, uint8_t* codes, uint8_t* scales, cudaStream_t s);
+bool launch_gated_norm_nvfp4_fused(const uint16_t* in, const uint16_t* weight, const uint16_t* gate, size_t tokens,
+                                   size_t heads_per_row, size_t dim, float eps, size_t rows_per_scale, uint16_t* out,
+                                   uint32_t* scratch, float* global_scales_out, uint8_t* codes, uint8_t* scales,
+                                   cudaStream_t s);
+
+}  // namespace q3x

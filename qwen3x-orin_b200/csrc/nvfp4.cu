@@ -13,55 +13,23 @@
 // cvt.rn.satfinite.e2m1x2.f32): round-to-nearest-even onto the format's grid with saturation to
 // its largest finite value.
 //
-// Work layout of the quantiser: a lane owns eight elements (one 128-bit load), lane pairs share a
-// block's amax through one shuffle, each lane stores its four code bytes as one 32-bit word (a
-// warp writes 128 contiguous bytes) and the even lane stores the block scale.
-#include <cfloat>
-
+// Work layout of the stand-alone quantiser: one 128-thread CTA per row, so the row's group, its
+// global scale and k are computed once per CTA; a lane owns eight elements (one 128-bit load),
+// lane pairs share a block's amax through one shuffle, each lane stores its four code bytes as one
+// 32-bit word (a warp writes 512 contiguous bytes) and the row's block scales are collected in
+// shared memory and written as 128-bit stores.
 #include "device_utils.cuh"
 #include "host_checks.hpp"
 #include "internal.hpp"
+#include "nvfp4_math.cuh"
 #include "q3x_b200.h"
 
 namespace q3x {
 namespace {
 
 constexpr int kThreads = 256;
-
-__device__ __forceinline__ uint32_t encode_e4m3(float v) {
-  uint16_t pair;
-  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(pair) : "f"(0.0f), "f"(v));
-  return pair & 0xffu;
-}
-
-// Non-negative E4M3 code -> float (exact).
-__device__ __forceinline__ float decode_e4m3_positive(uint32_t code) {
-  const uint32_t e = (code >> 3) & 0xfu, m = code & 7u;
-  if (e == 0) return static_cast<float>(m) * 0.001953125f;     // m * 2^-9
-  if (code == 0x7fu) return __uint_as_float(0x7fffffffu);        // NaN (never produced by encode)
-  return __uint_as_float(((e + 120u) << 23) | (m << 20));        // (1 + m/8) * 2^(e-7)
-}
-
-// Eight floats -> eight E2M1 codes in one word, element i in nibble i.
-__device__ __forceinline__ uint32_t encode_e2m1x8(const float (&r)[8]) {
-  uint32_t out;
-  asm("{\n"
-      ".reg .b8 b0, b1, b2, b3;\n"
-      "cvt.rn.satfinite.e2m1x2.f32 b0, %2, %1;\n"
-      "cvt.rn.satfinite.e2m1x2.f32 b1, %4, %3;\n"
-      "cvt.rn.satfinite.e2m1x2.f32 b2, %6, %5;\n"
-      "cvt.rn.satfinite.e2m1x2.f32 b3, %8, %7;\n"
-      "mov.b32 %0, {b0, b1, b2, b3};\n"
-      "}"
-      : "=r"(out)
-      : "f"(r[0]), "f"(r[1]), "f"(r[2]), "f"(r[3]), "f"(r[4]), "f"(r[5]), "f"(r[6]), "f"(r[7]));
-  return out;
-}
-
-__device__ __forceinline__ float block_inverse(uint32_t scale_code, float global) {
-  const float d = __fmul_rn(decode_e4m3_positive(scale_code), global);
-  return d == 0.0f ? 0.0f : fminf(__fdiv_rn(1.0f, d), FLT_MAX);
-}
+constexpr int kRowThreads = 128;
+constexpr int kMaxRowScaleBytes = 8192;  // shared-memory staging of one row's block scales
 
 // ---- group amax -------------------------------------------------------------------------
 
@@ -104,39 +72,59 @@ __global__ void __launch_bounds__(kThreads) group_amax_scalar_kernel(const uint1
 
 __global__ void amax_to_scale_kernel(const uint32_t* amax_bits, size_t groups, float* global_scales) {
   const size_t g = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (g >= groups) return;
-  const float amax = __uint_as_float(amax_bits[g] << 16);
-  global_scales[g] = amax == 0.0f ? 1.0f : __fdiv_rn(amax, 2688.0f);
+  if (g < groups) global_scales[g] = global_scale_from_amax_bits(amax_bits[g]);
 }
 
 // ---- quantiser --------------------------------------------------------------------------
 
-__global__ void __launch_bounds__(kThreads) nvfp4_quantize_vec_kernel(const uint4* __restrict__ in, size_t nvec,
-                                                                      unsigned row_vectors, size_t rows_per_scale,
-                                                                      const float* __restrict__ global_scales,
-                                                                      uint32_t* __restrict__ codes,
-                                                                      uint8_t* __restrict__ scales) {
-  const size_t stride = static_cast<size_t>(gridDim.x) * kThreads;
-  // nvec is even (cols % 16 == 0) and the stride is a multiple of 32, so lane pairs stay together
-  const unsigned lane = threadIdx.x & 31u;
-  // the loop bound is the same for all lanes of a warp, so the pair shuffle always has its partner
-  for (size_t v = static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x; v - lane < nvec; v += stride) {
-    const bool valid = v < nvec;  // lane pairs are valid together (nvec is even)
-    const uint4 x = valid ? ld_stream(in + v) : make_uint4(0, 0, 0, 0);
-    uint32_t m = amax8(x);
-    m = max(m, __shfl_xor_sync(kFullMask, m, 1));
-    if (!valid) continue;
-    const size_t row = v / row_vectors;
+// One CTA per row (grid-stride over rows).  kWideScales: the row's scale bytes are a multiple of 16
+// and 16-byte aligned, so they go out as 128-bit stores from shared memory.
+template <bool kWideScales>
+__global__ void __launch_bounds__(kRowThreads) nvfp4_quantize_rows_kernel(const uint4* __restrict__ in, size_t rows,
+                                                                          int row_vectors, size_t rows_per_scale,
+                                                                          const float* __restrict__ global_scales,
+                                                                          uint32_t* __restrict__ codes,
+                                                                          uint8_t* __restrict__ scales) {
+  __shared__ __align__(16) uint8_t scale_bytes[kWideScales ? kMaxRowScaleBytes : 16];
+  const int tid = threadIdx.x;
+  for (size_t row = blockIdx.x; row < rows; row += gridDim.x) {
     const float global = __ldg(global_scales + (rows_per_scale ? row / rows_per_scale : 0));
-    const float k = __fdiv_rn(1.0f, __fmul_rn(global, 6.0f));
-    const uint32_t s = m == 0 ? 0u : encode_e4m3(__fmul_rn(__uint_as_float(m << 16), k));
-    const float inv = block_inverse(s, global);
-    float f[8];
-    unpack8(x, f);
+    const float k = block_scale_factor(global);
+    const uint4* src = in + row * static_cast<size_t>(row_vectors);
+    uint32_t* dst = codes + row * static_cast<size_t>(row_vectors);
+    uint8_t* srow = scales + row * static_cast<size_t>(row_vectors / 2);
+    // the bound is the same for all lanes of a warp, so the pair shuffle always has its partner
+    for (int base = 0; base < row_vectors; base += 2 * kRowThreads) {
+      uint4 x[2];
+      bool valid[2];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) f[i] = __fmul_rn(f[i], inv);
-    codes[v] = encode_e2m1x8(f);
-    if ((threadIdx.x & 1) == 0) scales[v >> 1] = static_cast<uint8_t>(s);
+      for (int u = 0; u < 2; ++u) {
+        const int v = base + u * kRowThreads + tid;
+        valid[u] = v < row_vectors;  // lane pairs are valid together (row_vectors is even)
+        x[u] = valid[u] ? ld_stream(src + v) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int v = base + u * kRowThreads + tid;
+        uint32_t m = amax8(x[u]);
+        m = max(m, __shfl_xor_sync(kFullMask, m, 1));
+        const uint32_t s = block_scale_code(m, k);
+        const float inv = block_inverse(s, global);
+        if (valid[u]) {
+          dst[v] = quantize8(x[u], inv);
+          if ((tid & 1) == 0) {
+            if (kWideScales) scale_bytes[v >> 1] = static_cast<uint8_t>(s);
+            else srow[v >> 1] = static_cast<uint8_t>(s);
+          }
+        }
+      }
+    }
+    if (kWideScales) {
+      __syncthreads();
+      for (int i = tid; i < row_vectors / 32; i += kRowThreads)
+        reinterpret_cast<uint4*>(srow)[i] = reinterpret_cast<const uint4*>(scale_bytes)[i];
+      __syncthreads();
+    }
   }
 }
 
@@ -155,8 +143,7 @@ __global__ void __launch_bounds__(kThreads) nvfp4_quantize_scalar_kernel(const u
     }
     const size_t row = b / row_blocks;
     const float global = global_scales[rows_per_scale ? row / rows_per_scale : 0];
-    const float k = __fdiv_rn(1.0f, __fmul_rn(global, 6.0f));
-    const uint32_t s = m == 0 ? 0u : encode_e4m3(__fmul_rn(__uint_as_float(m << 16), k));
+    const uint32_t s = block_scale_code(m, block_scale_factor(global));
     const float inv = block_inverse(s, global);
     scales[b] = static_cast<uint8_t>(s);
     for (int h = 0; h < 2; ++h) {
@@ -227,11 +214,18 @@ void enqueue_scales(const uint32_t* amax_bits, size_t groups, float* global_scal
 void enqueue_quantize(const uint16_t* in, size_t rows, size_t cols, size_t rows_per_scale, const float* global_scales,
                       uint8_t* codes, uint8_t* scales, cudaStream_t s) {
   using namespace host;
-  if (aligned16(in) && (reinterpret_cast<uintptr_t>(codes) & 3u) == 0 && cols / 8 <= 0xffffffffu) {
-    const size_t nvec = rows * cols / 8;
-    nvfp4_quantize_vec_kernel<<<grid_for(nvec, kThreads * 2, 8), kThreads, 0, s>>>(
-        reinterpret_cast<const uint4*>(in), nvec, static_cast<unsigned>(cols / 8), rows_per_scale, global_scales,
-        reinterpret_cast<uint32_t*>(codes), scales);
+  if (aligned16(in) && (reinterpret_cast<uintptr_t>(codes) & 3u) == 0 && cols / 8 <= 0x7fffffffu) {
+    const int row_vectors = static_cast<int>(cols / 8);
+    const unsigned grid = grid_for(rows, 1, 16);
+    const bool wide = aligned16(scales) && (cols / 16) % 16 == 0 && cols / 16 <= kMaxRowScaleBytes;
+    auto I = reinterpret_cast<const uint4*>(in);
+    auto C = reinterpret_cast<uint32_t*>(codes);
+    if (wide)
+      nvfp4_quantize_rows_kernel<true><<<grid, kRowThreads, 0, s>>>(I, rows, row_vectors, rows_per_scale,
+                                                                    global_scales, C, scales);
+    else
+      nvfp4_quantize_rows_kernel<false><<<grid, kRowThreads, 0, s>>>(I, rows, row_vectors, rows_per_scale,
+                                                                     global_scales, C, scales);
   } else {
     const size_t blocks = rows * cols / 16;
     nvfp4_quantize_scalar_kernel<<<grid_for(blocks, kThreads, 8), kThreads, 0, s>>>(in, blocks, cols / 16,
@@ -256,6 +250,10 @@ using namespace q3x::host;
 
 extern "C" size_t q3x_b200_nvfp4_group_count(size_t rows, size_t rows_per_scale) {
   return group_count(rows, rows_per_scale);
+}
+
+extern "C" size_t q3x_b200_nvfp4_scratch_words(size_t rows, size_t rows_per_scale) {
+  return fused_scratch_words(group_count(rows, rows_per_scale));
 }
 
 extern "C" int q3x_b200_group_amax(const uint16_t* in, size_t rows, size_t cols, size_t rows_per_scale,
@@ -293,18 +291,18 @@ extern "C" int q3x_b200_nvfp4_quantize(const uint16_t* in, size_t rows, size_t c
 }
 
 extern "C" int q3x_b200_nvfp4_quantize_dynamic(const uint16_t* in, size_t rows, size_t cols, size_t rows_per_scale,
-                                               uint32_t* amax_scratch, float* global_scales_out, uint8_t* codes,
+                                               uint32_t* scratch, float* global_scales_out, uint8_t* codes,
                                                uint8_t* scales, void* stream) {
   bool done;
   int st = check_matrix(in, rows, cols, &done);
   if (st != kOk || done) return st;
-  if (amax_scratch == nullptr || global_scales_out == nullptr) return kInvalid;
+  if (scratch == nullptr || global_scales_out == nullptr) return kInvalid;
   if ((st = check_quant_outputs(in, rows, cols, codes, scales)) != kOk) return st;
   const size_t groups = group_count(rows, rows_per_scale);
   cudaStream_t s = as_stream(stream);
   clear_stale_error();
-  enqueue_amax(in, rows, cols, rows_per_scale, amax_scratch, s);
-  enqueue_scales(amax_scratch, groups, global_scales_out, s);
+  enqueue_amax(in, rows, cols, rows_per_scale, scratch, s);
+  enqueue_scales(scratch, groups, global_scales_out, s);
   enqueue_quantize(in, rows, cols, rows_per_scale, global_scales_out, codes, scales, s);
   return launch_status();
 }
@@ -312,7 +310,7 @@ extern "C" int q3x_b200_nvfp4_quantize_dynamic(const uint16_t* in, size_t rows, 
 extern "C" int q3x_b200_residual_add_rms_norm_nvfp4(const uint16_t* left, const uint16_t* right,
                                                     const uint16_t* weight, size_t tokens, size_t hidden, float eps,
                                                     size_t rows_per_scale, uint16_t* residual_out,
-                                                    uint16_t* normalized_out, uint32_t* amax_scratch,
+                                                    uint16_t* normalized_out, uint32_t* scratch,
                                                     float* global_scales_out, uint8_t* codes, uint8_t* scales,
                                                     void* stream) {
   bool done;
@@ -320,25 +318,29 @@ extern "C" int q3x_b200_residual_add_rms_norm_nvfp4(const uint16_t* left, const 
   if (st != kOk) return st;
   if (hidden % Q3X_B200_NVFP4_BLOCK != 0) return kInvalid;
   if (done) return kOk;
-  if (normalized_out == nullptr || amax_scratch == nullptr || global_scales_out == nullptr) return kInvalid;
+  if (normalized_out == nullptr || scratch == nullptr || global_scales_out == nullptr) return kInvalid;
   if ((st = check_quant_outputs(normalized_out, tokens, hidden, codes, scales)) != kOk) return st;
   if (!norm_rows_vector_path(left, right, weight, nullptr, hidden, residual_out, normalized_out, NormMode::kCentered))
     return kNotSupported;
   const size_t groups = group_count(tokens, rows_per_scale);
   cudaStream_t s = as_stream(stream);
   clear_stale_error();
-  cudaMemsetAsync(amax_scratch, 0, groups * sizeof(uint32_t), s);
+  // single pass when a scale group fits one sweep of the resident teams, else three kernels
+  if (launch_residual_norm_nvfp4_fused(left, right, weight, tokens, hidden, eps, rows_per_scale, residual_out,
+                                       normalized_out, scratch, global_scales_out, codes, scales, s))
+    return launch_status();
+  cudaMemsetAsync(scratch, 0, fused_scratch_words(groups) * sizeof(uint32_t), s);
   launch_norm_rows(NormMode::kCentered, left, right, weight, nullptr, tokens, hidden, eps, 1.0f, residual_out,
-                   normalized_out, /*coherent=*/normalized_out == right, amax_scratch,
+                   normalized_out, /*coherent=*/normalized_out == right, scratch,
                    rows_per_scale ? rows_per_scale : tokens, s);
-  enqueue_scales(amax_scratch, groups, global_scales_out, s);
+  enqueue_scales(scratch, groups, global_scales_out, s);
   enqueue_quantize(normalized_out, tokens, hidden, rows_per_scale, global_scales_out, codes, scales, s);
   return launch_status();
 }
 
 extern "C" int q3x_b200_rms_norm_silu_gate_nvfp4(const uint16_t* in, const uint16_t* weight, const uint16_t* gate,
                                                  size_t tokens, size_t heads_per_row, size_t dim, float eps,
-                                                 size_t rows_per_scale, uint16_t* out, uint32_t* amax_scratch,
+                                                 size_t rows_per_scale, uint16_t* out, uint32_t* scratch,
                                                  float* global_scales_out, uint8_t* codes, uint8_t* scales,
                                                  void* stream) {
   if (!valid_epsilon(eps)) return kInvalid;
@@ -346,7 +348,7 @@ extern "C" int q3x_b200_rms_norm_silu_gate_nvfp4(const uint16_t* in, const uint1
   const size_t cols = heads_per_row * dim;
   if (cols % Q3X_B200_NVFP4_BLOCK != 0) return kInvalid;
   if (tokens == 0 || cols == 0) return kOk;
-  if (in == nullptr || weight == nullptr || gate == nullptr || out == nullptr || amax_scratch == nullptr ||
+  if (in == nullptr || weight == nullptr || gate == nullptr || out == nullptr || scratch == nullptr ||
       global_scales_out == nullptr)
     return kInvalid;
   const size_t bytes = tokens * cols * 2;
@@ -362,10 +364,13 @@ extern "C" int q3x_b200_rms_norm_silu_gate_nvfp4(const uint16_t* in, const uint1
   const size_t token_group = rows_per_scale ? rows_per_scale : tokens;
   cudaStream_t s = as_stream(stream);
   clear_stale_error();
-  cudaMemsetAsync(amax_scratch, 0, groups * sizeof(uint32_t), s);
+  if (launch_gated_norm_nvfp4_fused(in, weight, gate, tokens, heads_per_row, dim, eps, rows_per_scale, out, scratch,
+                                    global_scales_out, codes, scales, s))
+    return launch_status();
+  cudaMemsetAsync(scratch, 0, fused_scratch_words(groups) * sizeof(uint32_t), s);
   launch_norm_rows(NormMode::kPlainSiluGate, in, nullptr, weight, gate, tokens * heads_per_row, dim, eps, 1.0f,
-                   nullptr, out, /*coherent=*/out == in || out == gate, amax_scratch, token_group * heads_per_row, s);
-  enqueue_scales(amax_scratch, groups, global_scales_out, s);
+                   nullptr, out, /*coherent=*/out == in || out == gate, scratch, token_group * heads_per_row, s);
+  enqueue_scales(scratch, groups, global_scales_out, s);
   enqueue_quantize(out, tokens, cols, rows_per_scale, global_scales_out, codes, scales, s);
   return launch_status();
 }

@@ -78,7 +78,7 @@ def test_quantize_dynamic(g, rows, cols, rps, misalign):
     x = make_input(rows, cols, 1)
     groups = 1 if rps == 0 else (rows + rps - 1) // rps
     dx = g.Dev(x, misalign)
-    amax = g.empty_like_dev((groups,), dtype=np.uint32, fill=0x7FFFFFFF)  # stale contents must not matter
+    amax = g.empty_like_dev((2 * groups + 2,), dtype=np.uint32, fill=0x7FFFFFFF)  # stale contents must not matter
     gs = g.empty_like_dev((groups,), dtype=np.float32)
     codes = g.empty_like_dev((rows, cols // 2), dtype=np.uint8, misalign=misalign)
     scales = g.empty_like_dev((rows, cols // 16), dtype=np.uint8)
@@ -86,7 +86,7 @@ def test_quantize_dynamic(g, rows, cols, rps, misalign):
     g.sync()
     want_c, want_s, want_g = orc.nvfp4_quantize(x, rps)
     assert np.array_equal(gs.get().view(np.uint32), want_g.view(np.uint32)), "global scales"
-    assert np.array_equal(amax.get() << 16, orc.group_amax(x, rps).view(np.uint32)), "group amax bits"
+    assert np.array_equal(amax.get()[:groups] << 16, orc.group_amax(x, rps).view(np.uint32)), "group amax bits"
     g.assert_bits_equal(scales.get(), want_s, "E4M3 block scales")
     g.assert_bits_equal(codes.get(), want_c, "E2M1 codes")
     assert codes.guards_intact() and scales.guards_intact() and gs.guards_intact() and amax.guards_intact()
@@ -136,7 +136,7 @@ def test_residual_norm_nvfp4(g, tokens, rps):
     groups = 1 if rps == 0 else (tokens + rps - 1) // rps
     dl, dr, dw = g.Dev(left), g.Dev(right), g.Dev(w)
     res, nrm = g.empty_like_dev((tokens, hidden)), g.empty_like_dev((tokens, hidden))
-    amax = g.empty_like_dev((groups,), dtype=np.uint32, fill=123456)
+    amax = g.empty_like_dev((2 * groups + 2,), dtype=np.uint32, fill=123456)
     gs = g.empty_like_dev((groups,), dtype=np.float32)
     codes = g.empty_like_dev((tokens, hidden // 2), dtype=np.uint8)
     scales = g.empty_like_dev((tokens, hidden // 16), dtype=np.uint8)
@@ -174,7 +174,7 @@ def test_gated_norm_nvfp4(g, tokens, rps):
     groups = 1 if rps == 0 else (tokens + rps - 1) // rps
     dx, dz, dw = g.Dev(x), g.Dev(z), g.Dev(w)
     out = g.empty_like_dev((tokens, heads * dim))
-    amax = g.empty_like_dev((groups,), dtype=np.uint32, fill=99)
+    amax = g.empty_like_dev((2 * groups + 2,), dtype=np.uint32, fill=99)
     gs = g.empty_like_dev((groups,), dtype=np.float32)
     codes = g.empty_like_dev((tokens, heads * dim // 2), dtype=np.uint8)
     scales = g.empty_like_dev((tokens, heads * dim // 16), dtype=np.uint8)
