@@ -46,6 +46,7 @@ def parse_args():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--probe-reps", type=int, default=3)
     ap.add_argument("--probe-only", action="store_true",
                     help="time each operator alone (few launches; the form profiled under ncu) and exit")
     return ap.parse_args()
@@ -304,6 +305,9 @@ def probe_ops(stack, chain, stream_obj, T, peak, warm, reps):
         "attention_preprocess": lambda: stack.op_preprocess(3, stream),
         "sigmoid_gate": lambda: stack.op_sigmoid_gate(stream),
         "swiglu": lambda: stack.op_swiglu(stream),
+        # the one-pass cooperative forms of the two norm + NVFP4 operators (not used by the step)
+        "residual_rmsnorm_nvfp4/single_pass": lambda: stack.op_residual_norm_single_pass(0, 0, 0, 1, stream),
+        "gated_rmsnorm_nvfp4/single_pass": lambda: stack.op_gated_norm_single_pass(0, stream),
     }
     per_op = {}
     with torch.cuda.stream(stream_obj):
@@ -317,9 +321,10 @@ def probe_ops(stack, chain, stream_obj, T, peak, warm, reps):
             e1.record(stream_obj)
             stream_obj.synchronize()
             us = e0.elapsed_time(e1) * 1e3 / reps
-            gbs = chain.BYTES_PER_TOKEN[name] * T / (us * 1e-6) / 1e9
+            base = name.split("/")[0]
+            gbs = chain.BYTES_PER_TOKEN[base] * T / (us * 1e-6) / 1e9
             per_op[name] = {"us": round(us, 2), "algorithmic_GBs": round(gbs, 1), "frac_of_peak": round(gbs / peak, 4),
-                            "bytes_per_token": chain.BYTES_PER_TOKEN[name], "kernels": chain.KERNELS[name]}
+                            "bytes_per_token": chain.BYTES_PER_TOKEN[base], "kernels": chain.KERNELS[base]}
     return per_op
 
 
@@ -359,7 +364,7 @@ def main():
 
     if args.probe_only:
         peak, _ = measured_peak()
-        print(json.dumps({"probe_only": True, "tokens": T, "per_op": probe_ops(stack, chain, stream_obj, T, peak, 1, 3)}),
+        print(json.dumps({"probe_only": True, "tokens": T, "per_op": probe_ops(stack, chain, stream_obj, T, peak, 1, args.probe_reps)}),
               flush=True)
         return 0
 

@@ -127,7 +127,7 @@ class LayerStack:
         self.mlp_out = torch.empty((T, INTERMEDIATE), **bf)
         groups = max(1, math.ceil(T / CHUNK))
         self.groups = groups
-        self.amax = torch.zeros(2 * groups + 2, device=dev, dtype=torch.int32)  # NVFP4 scratch words
+        self.amax = torch.zeros(capi.lib().q3x_b200_nvfp4_scratch_words(T, CHUNK), device=dev, dtype=torch.int32)
         self.global_scales = torch.empty(groups, device=dev, dtype=torch.float32)
         self.codes = torch.empty((T, HIDDEN // 2), device=dev, dtype=torch.uint8)
         self.scales = torch.empty((T, HIDDEN // 16), device=dev, dtype=torch.uint8)
@@ -144,6 +144,16 @@ class LayerStack:
         capi.check("q3x_b200_residual_add_rms_norm_nvfp4", self.residual[src], self.inputs["proj_out"],
                    self.norm_w[layer, which], self.tokens, HIDDEN, EPS, CHUNK, self.residual[dst], self.normalized,
                    self.amax, self.global_scales, self.codes, self.scales, stream)
+
+    def op_residual_norm_single_pass(self, layer, which, src, dst, stream):
+        capi.check("q3x_b200_residual_add_rms_norm_nvfp4_single_pass", self.residual[src], self.inputs["proj_out"],
+                   self.norm_w[layer, which], self.tokens, HIDDEN, EPS, CHUNK, self.residual[dst], self.normalized,
+                   self.amax, self.global_scales, self.codes, self.scales, stream)
+
+    def op_gated_norm_single_pass(self, layer, stream):
+        capi.check("q3x_b200_rms_norm_silu_gate_nvfp4_single_pass", self.inputs["gdn_core"], self.gdn_norm_w[layer],
+                   self.inputs["gdn_z"], self.tokens, 48, 128, EPS, CHUNK, self.gdn_out, self.amax,
+                   self.global_scales, self.gdn_codes, self.gdn_scales, stream)
 
     def op_conv(self, layer, stream):
         capi.check("q3x_b200_causal_conv1d_silu_l2norm", self.inputs["conv_raw"], self.tokens, self.conv_w[layer],

@@ -4,22 +4,25 @@
 // The NVFP4 global scale of a group of rows is its amax, which is only known once every row of the
 // group has been normalised -- a grid-wide dependency.  It is resolved without a second pass over
 // memory by DEFERRING the quantisation of a row:
-//   * a team of 128 threads owns rows team, team + teams, team + 2 teams, ... (all CTAs co-resident,
-//     cooperative launch);
-//   * iteration i of a team normalises its row i ("phase A"): it writes the bf16 outputs, keeps the
-//     normalised row in a shared-memory ring (each thread keeps exactly the vectors it will later
-//     quantise, so the ring needs no synchronisation), raises the group's amax with one atomic and
-//     then counts the row as finished for its group;
-//   * the same iteration quantises the row of iteration i - 2 ("phase B") from the ring.  Because a
-//     group is no longer than one sweep of all teams, every row of that group belongs to iteration
-//     i - 2 or i - 1 of some team, so by then the group is normally complete; the team checks the
-//     group's finished-row counter (acquire load) and only spins if another team lags.
-// Progress: the team with the smallest iteration number never waits on anything unfinished, so the
-// wait cannot deadlock while all CTAs are resident.  Every spin is bounded; a team that gives up
-// sets the error word of the scratch area and carries on with the amax it can see, so the kernel
-// always terminates.
+//   * a team (one CTA of 128 threads) owns rows team, team + teams, team + 2 teams, ...; all CTAs
+//     are co-resident (cooperative launch);
+//   * the inputs of a team's NEXT row are copied global -> shared with cp.async while the current
+//     row is processed, so HBM latency is off the critical path; every thread stages, rings and
+//     later quantises the same vectors (tid + k * 128), so none of these buffers needs a barrier;
+//   * iteration i normalises row i ("phase A"): it writes the bf16 outputs, keeps the normalised
+//     row in a shared-memory ring and publishes the row's amax as ONE 32-bit word (magnitude bits
+//     plus a valid bit) -- no atomics and no fence, the word itself says that it is there;
+//   * the same iteration quantises the row of iteration i - (depth - 1) ("phase B") from the ring:
+//     the team reads the amax words of that row's whole group (<= a few KB, from L2), and only
+//     spins while a word is not valid yet.  depth is chosen so that every row of that group belongs
+//     to an iteration at least one behind the current one of its owner, so the words are normally
+//     all there.
+// Progress: the team with the smallest iteration number only ever needs words of iterations that
+// every team has already finished, so the waits cannot deadlock while all CTAs are resident.  Every
+// spin is bounded; a team that gives up sets the error word and carries on, so the kernel always
+// terminates.
 //
-// Scratch words (uint32): [0,G) group amax bits, [G,2G) finished rows per group, [2G] error flag.
+// Scratch words (uint32): [0, rows) per-row amax words, last word = error flag.
 #include <atomic>
 #include <mutex>
 
@@ -33,81 +36,86 @@
 namespace q3x {
 namespace {
 
-constexpr int kTeam = 128;           // threads that own one row
-constexpr int kTeamsPerCta = 2;
-constexpr int kCtaThreads = kTeam * kTeamsPerCta;
-constexpr int kDepth = 3;            // ring slots per team: rows of iterations i, i-1, i-2
-constexpr int kSpinLimit = 1 << 21;  // polls of a counter before giving up (~1 s)
+constexpr int kTeam = 128;           // threads of a CTA; they own one row at a time
+constexpr int kMaxDepth = 8;         // ring slots a team may be given
+constexpr int kSpinLimit = 1 << 20;  // polls of one word before giving up (~1 s with the sleep)
+constexpr uint32_t kValid = 0x80000000u;
 
-__device__ __forceinline__ void team_sync(int team) {
-  asm volatile("bar.sync %0, %1;" ::"r"(team + 1), "r"(kTeam) : "memory");
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* global_src) {
+  const unsigned dst = static_cast<unsigned>(__cvta_generic_to_shared(smem_dst));
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(global_src) : "memory");
 }
-__device__ __forceinline__ uint32_t ld_acquire(const uint32_t* p) {
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+__device__ __forceinline__ uint32_t ld_volatile(const uint32_t* p) {
   uint32_t v;
-  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
 
-struct GroupBoard {
-  uint32_t* amax;      // [groups]
-  uint32_t* finished;  // [groups]
+struct RowBoard {
+  uint32_t* row_amax;  // [rows]: kValid | bf16 magnitude bits of the row's largest finite output
   uint32_t* error;     // [1]
   size_t rows, rows_per_group;
-  __device__ __forceinline__ size_t group_of(size_t row) const { return row / rows_per_group; }
-  __device__ __forceinline__ uint32_t rows_in(size_t group) const {
-    const size_t first = group * rows_per_group;
-    return static_cast<uint32_t>(min(rows_per_group, rows - first));
-  }
 };
 
-// Per-team shared memory besides the ring.
 struct TeamShared {
   float sums[4];
-  uint32_t tops[4];
-  float global_scale;
-  uint32_t pad[3];
+  uint32_t tops_a[4];
+  uint32_t tops_b[4];
+  uint32_t pad[4];
   uint8_t scale_bytes[512];  // one row of block scales (row_vectors / 2 <= 512)
 };
 
-// Publishes a finished row: raises the group amax, then (after a fence) counts the row.
-__device__ __forceinline__ void publish_row(const GroupBoard& board, TeamShared& ts, int team, int tid, size_t row,
+// Phase A epilogue: the row's amax as one self-validating word.
+__device__ __forceinline__ void publish_row(const RowBoard& board, TeamShared& ts, int tid, size_t row,
                                             uint32_t thread_top) {
   const uint32_t warp_top = group_max_u32<32>(thread_top);
-  if ((tid & 31) == 0) ts.tops[tid >> 5] = warp_top;
-  team_sync(team);
+  if ((tid & 31) == 0) ts.tops_a[tid >> 5] = warp_top;
+  __syncthreads();
   if (tid == 0) {
-    const uint32_t m = max(max(ts.tops[0], ts.tops[1]), max(ts.tops[2], ts.tops[3]));
-    const size_t g = board.group_of(row);
-    if (m != 0) atomicMax(board.amax + g, m);
-    __threadfence();
-    atomicAdd(board.finished + g, 1u);
+    const uint32_t m = max(max(ts.tops_a[0], ts.tops_a[1]), max(ts.tops_a[2], ts.tops_a[3]));
+    __stcg(board.row_amax + row, m | kValid);
   }
 }
 
-// Waits (bounded) until the group of `row` is complete and returns its global scale to the team.
-__device__ __forceinline__ float await_group_scale(const GroupBoard& board, TeamShared& ts, int team, int tid,
-                                                   size_t row) {
-  if (tid == 0) {
-    const size_t g = board.group_of(row);
-    const uint32_t expected = board.rows_in(g);
+// Phase B prologue: the global scale of the group of `row`, once all of the group's words are valid.
+__device__ __forceinline__ float await_group_scale(const RowBoard& board, TeamShared& ts, int tid, size_t row) {
+  const size_t group = row / board.rows_per_group;
+  const size_t first = group * board.rows_per_group;
+  const size_t count = min(board.rows_per_group, board.rows - first);
+  uint32_t top = 0;
+  for (size_t j = tid; j < count; j += kTeam) {
+    uint32_t word = ld_volatile(board.row_amax + first + j);
     int polls = 0;
-    while (ld_acquire(board.finished + g) < expected) {
+    while ((word & kValid) == 0) {
       if (++polls >= kSpinLimit) {
         atomicExch(board.error, 1u);
         break;
       }
-      __nanosleep(64);
+      __nanosleep(100);
+      word = ld_volatile(board.row_amax + first + j);
     }
-    ts.global_scale = global_scale_from_amax_bits(ld_acquire(board.amax + g));
+    top = max(top, word & 0xffffu);
   }
-  team_sync(team);
-  return ts.global_scale;
+  top = group_max_u32<32>(top);
+  if ((tid & 31) == 0) ts.tops_b[tid >> 5] = top;
+  __syncthreads();
+  const uint32_t m = max(max(ts.tops_b[0], ts.tops_b[1]), max(ts.tops_b[2], ts.tops_b[3]));
+  return global_scale_from_amax_bits(m);
 }
+
+struct QuantOut {
+  uint32_t* codes;   // [rows, row_vectors] words
+  uint8_t* scales;   // [rows, row_vectors / 2] bytes
+  bool wide_scale_stores;
+};
 
 // Phase B: quantises one row from the team's ring slot.  Thread tid owns vectors tid + k * 128.
 template <int VPT>
 __device__ __forceinline__ void quantize_ring_row(const uint4* slot, int row_vectors, float global, TeamShared& ts,
-                                                  int team, int tid, uint32_t* codes_row, uint8_t* scales_row,
+                                                  int tid, uint32_t* codes_row, uint8_t* scales_row,
                                                   bool wide_scale_stores) {
   const float k = block_scale_factor(global);
 #pragma unroll
@@ -128,70 +136,91 @@ __device__ __forceinline__ void quantize_ring_row(const uint4* slot, int row_vec
     }
   }
   if (wide_scale_stores) {  // row_vectors / 2 bytes, a multiple of 16, written as 128-bit stores
-    team_sync(team);
+    __syncthreads();
     const int n = row_vectors / 32;
     if (tid < n) reinterpret_cast<uint4*>(scales_row)[tid] = reinterpret_cast<const uint4*>(ts.scale_bytes)[tid];
   }
 }
 
-struct QuantOut {
-  uint32_t* codes;   // [rows, row_vectors] words
-  uint8_t* scales;   // [rows, row_vectors / 2] bytes
-  bool wide_scale_stores;
+// Shared-memory carve-up: [2 staging rows][depth ring rows][TeamShared]
+template <int VPT>
+struct Carve {
+  static constexpr int kRowVectors = VPT * kTeam;
+  __device__ static uint4* stage(unsigned char* smem, int which) {
+    return reinterpret_cast<uint4*>(smem) + which * kRowVectors;
+  }
+  __device__ static uint4* ring(unsigned char* smem, int slot) {
+    return reinterpret_cast<uint4*>(smem) + (2 + slot) * kRowVectors;
+  }
+  __device__ static TeamShared& shared(unsigned char* smem, int depth) {
+    return *reinterpret_cast<TeamShared*>(smem + sizeof(uint4) * (2 + depth) * kRowVectors);
+  }
 };
+
+template <int VPT>
+__device__ __forceinline__ void stage_row(unsigned char* smem, const uint4* a, const uint4* b, size_t base,
+                                          int row_vectors, int tid) {
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = tid + i * kTeam;
+    if (v < row_vectors) {
+      cp_async16(Carve<VPT>::stage(smem, 0) + v, a + base + v);
+      cp_async16(Carve<VPT>::stage(smem, 1) + v, b + base + v);
+    }
+  }
+  cp_async_commit();
+}
 
 // ---- residual add + centred RMSNorm + NVFP4 ------------------------------------------------
 template <int VPT>
-__global__ void __launch_bounds__(kCtaThreads) residual_norm_nvfp4_kernel(
+__global__ void __launch_bounds__(kTeam) residual_norm_nvfp4_kernel(
     const uint4* left, const uint4* right, const uint4* __restrict__ weight, int row_vectors, float width, float eps,
-    uint4* residual_out, uint4* normalized_out, bool coherent, GroupBoard board, QuantOut q) {
+    uint4* residual_out, uint4* normalized_out, int depth, RowBoard board, QuantOut q) {
   extern __shared__ __align__(16) unsigned char smem[];
-  const int team = threadIdx.x / kTeam, tid = threadIdx.x % kTeam;
-  uint4* ring = reinterpret_cast<uint4*>(smem) + static_cast<size_t>(team) * kDepth * VPT * kTeam;
-  TeamShared& ts = reinterpret_cast<TeamShared*>(smem + sizeof(uint4) * kTeamsPerCta * kDepth * VPT * kTeam)[team];
-  const size_t teams = static_cast<size_t>(gridDim.x) * kTeamsPerCta;
-  const size_t first = static_cast<size_t>(blockIdx.x) * kTeamsPerCta + team;
+  const int tid = threadIdx.x;
+  TeamShared& ts = Carve<VPT>::shared(smem, depth);
+  const size_t teams = gridDim.x;
+  const size_t first = blockIdx.x;
+  const size_t lag = static_cast<size_t>(depth - 1);
+  if (first < board.rows) stage_row<VPT>(smem, left, right, first * static_cast<size_t>(row_vectors), row_vectors, tid);
 
   for (size_t it = 0;; ++it) {
     const size_t row = first + it * teams;
     const bool has_row = row < board.rows;
-    const bool has_old = it >= kDepth - 1 && first + (it - (kDepth - 1)) * teams < board.rows;
+    const bool has_old = it >= lag && first + (it - lag) * teams < board.rows;
     if (!has_row && !has_old) {
-      if (it >= kDepth - 1) break;  // nothing left in the ring either
-      continue;                     // rows are exhausted but the ring still drains
+      if (it >= lag) break;  // nothing left in the ring either
+      continue;              // rows are exhausted but the ring still drains
     }
-
     if (has_row) {
       const size_t base = row * static_cast<size_t>(row_vectors);
-      uint4 x[VPT], r[VPT];
-#pragma unroll
-      for (int i = 0; i < VPT; ++i) {
-        const int v = tid + i * kTeam;
-        x[i] = r[i] = make_uint4(0, 0, 0, 0);
-        if (v < row_vectors) {
-          x[i] = ld_stream(left + base + v);
-          r[i] = coherent ? ld_vec(right + base + v) : ld_stream(right + base + v);
-        }
-      }
+      uint4 x[VPT];
+      cp_async_wait_all();
       float partial = 0.0f;
 #pragma unroll
       for (int i = 0; i < VPT; ++i) {
-        float a[8], b[8];
-        unpack8(x[i], a);
-        unpack8(r[i], b);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) a[j] = a[j] + b[j];
-        x[i] = pack8(a);
         const int v = tid + i * kTeam;
-        if (v < row_vectors) st_vec(residual_out + base + v, x[i]);
+        x[i] = make_uint4(0, 0, 0, 0);
+        if (v < row_vectors) {
+          float a[8], b[8];
+          unpack8(Carve<VPT>::stage(smem, 0)[v], a);
+          unpack8(Carve<VPT>::stage(smem, 1)[v], b);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) a[j] = a[j] + b[j];
+          x[i] = pack8(a);
+          st_vec(residual_out + base + v, x[i]);
+        }
         partial += sum_squares8(x[i]);
       }
+      // this thread has consumed its staged vectors: refill them with the next row's
+      if (row + teams < board.rows)
+        stage_row<VPT>(smem, left, right, (row + teams) * static_cast<size_t>(row_vectors), row_vectors, tid);
       partial = group_sum<32>(partial);
       if ((tid & 31) == 0) ts.sums[tid >> 5] = partial;
-      team_sync(team);
+      __syncthreads();
       const float total = ts.sums[0] + ts.sums[1] + ts.sums[2] + ts.sums[3];
       const float inv = inverse_rms(total, width, eps);
-      uint4* slot = ring + (it % kDepth) * VPT * kTeam;
+      uint4* slot = Carve<VPT>::ring(smem, static_cast<int>(it % depth));
       uint32_t top = 0;
 #pragma unroll
       for (int i = 0; i < VPT; ++i) {
@@ -203,13 +232,13 @@ __global__ void __launch_bounds__(kCtaThreads) residual_norm_nvfp4_kernel(
           top = max(top, amax8(y));
         }
       }
-      publish_row(board, ts, team, tid, row, top);
+      publish_row(board, ts, tid, row, top);
     }
     if (has_old) {
-      const size_t old_it = it - (kDepth - 1);
+      const size_t old_it = it - lag;
       const size_t old_row = first + old_it * teams;
-      const float global = await_group_scale(board, ts, team, tid, old_row);
-      quantize_ring_row<VPT>(ring + (old_it % kDepth) * VPT * kTeam, row_vectors, global, ts, team, tid,
+      const float global = await_group_scale(board, ts, tid, old_row);
+      quantize_ring_row<VPT>(Carve<VPT>::ring(smem, static_cast<int>(old_it % depth)), row_vectors, global, ts, tid,
                              q.codes + old_row * static_cast<size_t>(row_vectors),
                              q.scales + old_row * static_cast<size_t>(row_vectors / 2), q.wide_scale_stores);
     }
@@ -218,40 +247,43 @@ __global__ void __launch_bounds__(kCtaThreads) residual_norm_nvfp4_kernel(
 
 // ---- gated RMSNorm * silu(z) + NVFP4: one row = one token = heads_per_row heads of 128 -------
 template <int VPT>
-__global__ void __launch_bounds__(kCtaThreads) gated_norm_nvfp4_kernel(
+__global__ void __launch_bounds__(kTeam) gated_norm_nvfp4_kernel(
     const uint4* in, const uint4* gate, const uint4* __restrict__ weight, int row_vectors, float eps, uint4* out,
-    bool coherent, GroupBoard board, QuantOut q) {
+    int depth, RowBoard board, QuantOut q) {
   constexpr int kLanes = Q3X_B200_GDN_HEAD_DIM / 8;  // 16 lanes own one head
   extern __shared__ __align__(16) unsigned char smem[];
-  const int team = threadIdx.x / kTeam, tid = threadIdx.x % kTeam;
-  uint4* ring = reinterpret_cast<uint4*>(smem) + static_cast<size_t>(team) * kDepth * VPT * kTeam;
-  TeamShared& ts = reinterpret_cast<TeamShared*>(smem + sizeof(uint4) * kTeamsPerCta * kDepth * VPT * kTeam)[team];
-  const size_t teams = static_cast<size_t>(gridDim.x) * kTeamsPerCta;
-  const size_t first = static_cast<size_t>(blockIdx.x) * kTeamsPerCta + team;
+  const int tid = threadIdx.x;
+  TeamShared& ts = Carve<VPT>::shared(smem, depth);
+  const size_t teams = gridDim.x;
+  const size_t first = blockIdx.x;
+  const size_t lag = static_cast<size_t>(depth - 1);
   const uint4 w = ld_weight(weight + (tid % kLanes));
+  if (first < board.rows) stage_row<VPT>(smem, in, gate, first * static_cast<size_t>(row_vectors), row_vectors, tid);
 
   for (size_t it = 0;; ++it) {
     const size_t row = first + it * teams;
     const bool has_row = row < board.rows;
-    const bool has_old = it >= kDepth - 1 && first + (it - (kDepth - 1)) * teams < board.rows;
+    const bool has_old = it >= lag && first + (it - lag) * teams < board.rows;
     if (!has_row && !has_old) {
-      if (it >= kDepth - 1) break;  // nothing left in the ring either
-      continue;                     // rows are exhausted but the ring still drains
+      if (it >= lag) break;
+      continue;
     }
-
     if (has_row) {
       const size_t base = row * static_cast<size_t>(row_vectors);
       uint4 x[VPT], z[VPT];
+      cp_async_wait_all();
 #pragma unroll
       for (int i = 0; i < VPT; ++i) {
         const int v = tid + i * kTeam;
         x[i] = z[i] = make_uint4(0, 0, 0, 0);
         if (v < row_vectors) {
-          x[i] = coherent ? ld_vec(in + base + v) : ld_stream(in + base + v);
-          z[i] = coherent ? ld_vec(gate + base + v) : ld_stream(gate + base + v);
+          x[i] = Carve<VPT>::stage(smem, 0)[v];
+          z[i] = Carve<VPT>::stage(smem, 1)[v];
         }
       }
-      uint4* slot = ring + (it % kDepth) * VPT * kTeam;
+      if (row + teams < board.rows)
+        stage_row<VPT>(smem, in, gate, (row + teams) * static_cast<size_t>(row_vectors), row_vectors, tid);
+      uint4* slot = Carve<VPT>::ring(smem, static_cast<int>(it % depth));
       uint32_t top = 0;
 #pragma unroll
       for (int i = 0; i < VPT; ++i) {
@@ -265,74 +297,107 @@ __global__ void __launch_bounds__(kCtaThreads) gated_norm_nvfp4_kernel(
           top = max(top, amax8(y));
         }
       }
-      publish_row(board, ts, team, tid, row, top);
+      publish_row(board, ts, tid, row, top);
     }
     if (has_old) {
-      const size_t old_it = it - (kDepth - 1);
+      const size_t old_it = it - lag;
       const size_t old_row = first + old_it * teams;
-      const float global = await_group_scale(board, ts, team, tid, old_row);
-      quantize_ring_row<VPT>(ring + (old_it % kDepth) * VPT * kTeam, row_vectors, global, ts, team, tid,
+      const float global = await_group_scale(board, ts, tid, old_row);
+      quantize_ring_row<VPT>(Carve<VPT>::ring(smem, static_cast<int>(old_it % depth)), row_vectors, global, ts, tid,
                              q.codes + old_row * static_cast<size_t>(row_vectors),
                              q.scales + old_row * static_cast<size_t>(row_vectors / 2), q.wide_scale_stores);
     }
   }
 }
 
-__global__ void finish_scales_kernel(const uint32_t* amax_bits, size_t groups, float* global_scales) {
-  const size_t g = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (g < groups) global_scales[g] = global_scale_from_amax_bits(amax_bits[g]);
+// One CTA per group: global scale = f(max of the group's row words).
+__global__ void __launch_bounds__(kTeam) finish_scales_kernel(const uint32_t* row_amax, size_t rows,
+                                                              size_t rows_per_group, float* global_scales) {
+  __shared__ uint32_t tops[4];
+  const size_t first = static_cast<size_t>(blockIdx.x) * rows_per_group;
+  const size_t count = min(rows_per_group, rows - first);
+  uint32_t top = 0;
+  for (size_t j = threadIdx.x; j < count; j += kTeam) top = max(top, row_amax[first + j] & 0xffffu);
+  top = group_max_u32<32>(top);
+  if ((threadIdx.x & 31) == 0) tops[threadIdx.x >> 5] = top;
+  __syncthreads();
+  if (threadIdx.x == 0)
+    global_scales[blockIdx.x] = global_scale_from_amax_bits(max(max(tops[0], tops[1]), max(tops[2], tops[3])));
 }
 
-size_t smem_bytes(int vpt) {
-  return sizeof(uint4) * kTeamsPerCta * kDepth * vpt * kTeam + sizeof(TeamShared) * kTeamsPerCta;
+size_t smem_bytes(int vpt, int depth) {
+  return sizeof(uint4) * static_cast<size_t>(2 + depth) * vpt * kTeam + sizeof(TeamShared);
 }
 
-// Resident CTAs of `kernel` on the current device (0 when the kernel cannot be configured).  The
-// answer is cached per (device, kernel family, vectors per thread): it is a pure function of them.
+// Resident CTAs of `kernel` with `smem` bytes on the current device (0 = cannot be configured).
+// Cached per (device, kernel family, vectors per thread, depth): a pure function of them.
 template <typename K>
-int resident_ctas(K kernel, size_t smem, int family, int vpt) {
+int resident_ctas(K kernel, size_t smem, int family, int vpt, int depth) {
   constexpr int kMaxDevices = 64;
-  static std::atomic<int> cache[kMaxDevices][2][9];
-  static std::atomic<bool> ready{false};
+  static std::atomic<int> cache[kMaxDevices][2][9][kMaxDepth + 1];
   static std::once_flag once;
   std::call_once(once, [] {
     for (auto& d : cache)
       for (auto& f : d)
-        for (auto& v : f) v.store(-1);
-    ready.store(true);
+        for (auto& v : f)
+          for (auto& e : v) e.store(-1);
   });
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return 0;
   const bool cacheable = dev >= 0 && dev < kMaxDevices;
   if (cacheable) {
-    const int hit = cache[dev][family][vpt].load();
+    const int hit = cache[dev][family][vpt][depth].load();
     if (hit >= 0) return hit;
   }
-  int sms = 0, per_sm = 0, total = 0;
-  if ((smem <= 48 * 1024 ||
-       cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) ==
-           cudaSuccess) &&
+  int sms = 0, per_sm = 0, total = 0, limit = 0;
+  if (cudaDeviceGetAttribute(&limit, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) == cudaSuccess &&
+      smem <= static_cast<size_t>(limit) &&
+      cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, limit) == cudaSuccess &&
       cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess &&
-      cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kCtaThreads, smem) == cudaSuccess)
+      cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kTeam, smem) == cudaSuccess)
     total = sms * per_sm;
-  if (cacheable) cache[dev][family][vpt].store(total);
+  if (cacheable) cache[dev][family][vpt][depth].store(total);
   return total;
+}
+
+// Picks the ring depth and grid: depth = 2 + ceil(group rows / teams) so that every row of the group
+// being quantised belongs to an iteration its owner has left behind; more ring slots cost shared
+// memory and so teams, hence the small search.  Returns false when no configuration fits.
+template <typename K>
+bool plan_launch(K kernel, int family, int vpt, size_t rows, size_t rows_per_group, int* depth_out,
+                 unsigned* grid_out, size_t* smem_out) {
+  for (int depth = 3; depth <= kMaxDepth; ++depth) {
+    const size_t smem = smem_bytes(vpt, depth);
+    const int cap = resident_ctas(kernel, smem, family, vpt, depth);
+    if (cap <= 0) return false;
+    const size_t grid = rows < static_cast<size_t>(cap) ? rows : static_cast<size_t>(cap);
+    const size_t group_rows = rows_per_group < rows ? rows_per_group : rows;
+    const size_t sweeps = (group_rows + grid - 1) / grid;  // iterations a group can reach past one of its rows
+    if (static_cast<size_t>(depth) >= 2 + sweeps) {
+      *depth_out = depth;
+      *grid_out = static_cast<unsigned>(grid);
+      *smem_out = smem;
+      return true;
+    }
+  }
+  return false;
 }
 
 template <typename K, typename... Args>
 bool launch_cooperative(K kernel, unsigned grid, size_t smem, cudaStream_t s, Args... args) {
   void* params[] = {static_cast<void*>(&args)...};
-  return cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(kernel), dim3(grid), dim3(kCtaThreads), params,
-                                     smem, s) == cudaSuccess;
+  return cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(kernel), dim3(grid), dim3(kTeam), params, smem,
+                                     s) == cudaSuccess;
 }
 
 }  // namespace
 
-size_t fused_scratch_words(size_t groups) { return 2 * groups + 2; }
+// [0, rows) row words or [0, groups) group amax words, whichever path runs, + error word + spare
+size_t fused_scratch_words(size_t rows, size_t groups) { return (rows > 2 * groups ? rows : 2 * groups) + 2; }
 
-// Both launchers return false when the fused path does not apply (shape, alignment, group longer
-// than one sweep of the teams, or the cooperative launch is refused); nothing has been enqueued
-// then and the caller takes the multi-kernel path.
+// Both launchers return false when the fused path does not apply (shape, alignment, a group too long
+// for the ring, or the cooperative launch is refused); nothing has been enqueued then and the
+// caller takes the multi-kernel path.
 bool launch_residual_norm_nvfp4_fused(const uint16_t* left, const uint16_t* right, const uint16_t* weight,
                                       size_t tokens, size_t hidden, float eps, size_t rows_per_scale,
                                       uint16_t* residual_out, uint16_t* normalized_out, uint32_t* scratch,
@@ -344,13 +409,12 @@ bool launch_residual_norm_nvfp4_fused(const uint16_t* left, const uint16_t* righ
     return false;
   const int row_vectors = static_cast<int>(hidden / 8);
   const int vpt = (row_vectors + kTeam - 1) / kTeam;
-  const size_t smem = smem_bytes(vpt);
   const size_t rps = rows_per_scale ? rows_per_scale : tokens;
   const size_t groups = (tokens + rps - 1) / rps;
-  GroupBoard board{scratch, scratch + groups, scratch + 2 * groups, tokens, rps};
+  const size_t words = fused_scratch_words(tokens, groups);
+  RowBoard board{scratch, scratch + words - 1, tokens, rps};
   QuantOut q{reinterpret_cast<uint32_t*>(codes), scales,
              row_vectors % 32 == 0 && aligned16(scales) && (row_vectors / 2) % 16 == 0};
-  const bool coherent = normalized_out == right;
   const float width = static_cast<float>(hidden);
   auto L = reinterpret_cast<const uint4*>(left);
   auto R = reinterpret_cast<const uint4*>(right);
@@ -358,24 +422,24 @@ bool launch_residual_norm_nvfp4_fused(const uint16_t* left, const uint16_t* righ
   auto RO = reinterpret_cast<uint4*>(residual_out);
   auto NO = reinterpret_cast<uint4*>(normalized_out);
   bool ok = false;
-#define Q3X_TRY(V)                                                                                        \
-  case V: {                                                                                               \
-    const int cap = resident_ctas(residual_norm_nvfp4_kernel<V>, smem, 0, V);                                   \
-    const size_t want = (tokens + kTeamsPerCta - 1) / kTeamsPerCta;                                       \
-    const unsigned grid = static_cast<unsigned>(want < static_cast<size_t>(cap) ? want : cap);            \
-    if (cap > 0 && rps <= static_cast<size_t>(grid) * kTeamsPerCta) {                                      \
-      cudaMemsetAsync(scratch, 0, fused_scratch_words(groups) * sizeof(uint32_t), s);                     \
-      ok = launch_cooperative(residual_norm_nvfp4_kernel<V>, grid, smem, s, L, R, W, row_vectors, width,  \
-                              eps, RO, NO, coherent, board, q);                                           \
-    }                                                                                                     \
-  } break;
+  int depth = 0;
+  unsigned grid = 0;
+  size_t smem = 0;
+#define Q3X_TRY(V)                                                                                             \
+  case V:                                                                                                      \
+    if (plan_launch(residual_norm_nvfp4_kernel<V>, 0, V, tokens, rps, &depth, &grid, &smem)) {                 \
+      cudaMemsetAsync(scratch, 0, words * sizeof(uint32_t), s);                                                \
+      ok = launch_cooperative(residual_norm_nvfp4_kernel<V>, grid, smem, s, L, R, W, row_vectors, width, eps,  \
+                              RO, NO, depth, board, q);                                                        \
+    }                                                                                                          \
+    break;
   switch (vpt) { Q3X_TRY(1) Q3X_TRY(2) Q3X_TRY(3) Q3X_TRY(4) Q3X_TRY(5) Q3X_TRY(6) Q3X_TRY(7) Q3X_TRY(8) }
 #undef Q3X_TRY
   if (!ok) {
     (void)cudaGetLastError();
     return false;
   }
-  finish_scales_kernel<<<static_cast<unsigned>((groups + 127) / 128), 128, 0, s>>>(scratch, groups, global_scales_out);
+  finish_scales_kernel<<<static_cast<unsigned>(groups), kTeam, 0, s>>>(scratch, tokens, rps, global_scales_out);
   return true;
 }
 
@@ -386,41 +450,42 @@ bool launch_gated_norm_nvfp4_fused(const uint16_t* in, const uint16_t* weight, c
   using namespace host;
   const size_t cols = heads_per_row * dim;
   if (dim != Q3X_B200_GDN_HEAD_DIM || cols > 8192 || tokens == 0) return false;
+  // in-place forms would let a staged copy of the next row race with this row's stores
+  if (out == in || out == gate) return false;
   if (!aligned16(in) || !aligned16(gate) || !aligned16(weight) || !aligned16(out) ||
       (reinterpret_cast<uintptr_t>(codes) & 3u) != 0)
     return false;
   const int row_vectors = static_cast<int>(cols / 8);
   const int vpt = (row_vectors + kTeam - 1) / kTeam;
-  const size_t smem = smem_bytes(vpt);
   const size_t rps = rows_per_scale ? rows_per_scale : tokens;
   const size_t groups = (tokens + rps - 1) / rps;
-  GroupBoard board{scratch, scratch + groups, scratch + 2 * groups, tokens, rps};
+  const size_t words = fused_scratch_words(tokens, groups);
+  RowBoard board{scratch, scratch + words - 1, tokens, rps};
   QuantOut q{reinterpret_cast<uint32_t*>(codes), scales,
              row_vectors % 32 == 0 && aligned16(scales) && (row_vectors / 2) % 16 == 0};
-  const bool coherent = out == in || out == gate;
   auto X = reinterpret_cast<const uint4*>(in);
   auto Z = reinterpret_cast<const uint4*>(gate);
   auto W = reinterpret_cast<const uint4*>(weight);
   auto O = reinterpret_cast<uint4*>(out);
   bool ok = false;
-#define Q3X_TRY(V)                                                                                        \
-  case V: {                                                                                               \
-    const int cap = resident_ctas(gated_norm_nvfp4_kernel<V>, smem, 1, V);                                      \
-    const size_t want = (tokens + kTeamsPerCta - 1) / kTeamsPerCta;                                       \
-    const unsigned grid = static_cast<unsigned>(want < static_cast<size_t>(cap) ? want : cap);            \
-    if (cap > 0 && rps <= static_cast<size_t>(grid) * kTeamsPerCta) {                                      \
-      cudaMemsetAsync(scratch, 0, fused_scratch_words(groups) * sizeof(uint32_t), s);                     \
-      ok = launch_cooperative(gated_norm_nvfp4_kernel<V>, grid, smem, s, X, Z, W, row_vectors, eps, O,    \
-                              coherent, board, q);                                                        \
-    }                                                                                                     \
-  } break;
+  int depth = 0;
+  unsigned grid = 0;
+  size_t smem = 0;
+#define Q3X_TRY(V)                                                                                          \
+  case V:                                                                                                   \
+    if (plan_launch(gated_norm_nvfp4_kernel<V>, 1, V, tokens, rps, &depth, &grid, &smem)) {                 \
+      cudaMemsetAsync(scratch, 0, words * sizeof(uint32_t), s);                                             \
+      ok = launch_cooperative(gated_norm_nvfp4_kernel<V>, grid, smem, s, X, Z, W, row_vectors, eps, O,      \
+                              depth, board, q);                                                             \
+    }                                                                                                       \
+    break;
   switch (vpt) { Q3X_TRY(1) Q3X_TRY(2) Q3X_TRY(3) Q3X_TRY(4) Q3X_TRY(5) Q3X_TRY(6) Q3X_TRY(7) Q3X_TRY(8) }
 #undef Q3X_TRY
   if (!ok) {
     (void)cudaGetLastError();
     return false;
   }
-  finish_scales_kernel<<<static_cast<unsigned>((groups + 127) / 128), 128, 0, s>>>(scratch, groups, global_scales_out);
+  finish_scales_kernel<<<static_cast<unsigned>(groups), kTeam, 0, s>>>(scratch, tokens, rps, global_scales_out);
   return true;
 }
 

@@ -38,8 +38,9 @@ int check_residual_norm(const uint16_t* left, const uint16_t* right, const uint1
 namespace q3x {
 
 // Scratch words (uint32) of the NVFP4 entry points for `groups` scale groups:
-// [0,G) amax bits, [G,2G) finished-row counters, [2G] error flag, one spare.
-size_t fused_scratch_words(size_t groups);
+// either [0,rows) per-row amax words (single-pass kernels) or [0,G) group amax words (multi-kernel
+// path); the last word is the error flag.
+size_t fused_scratch_words(size_t rows, size_t groups);
 
 // Single-pass kernels (fused_nvfp4.cu).  Return false, with nothing enqueued, when the fused path does
 // not apply; the caller then takes the multi-kernel path, which produces the same bytes.

@@ -83,12 +83,22 @@ template <bool kWideScales>
 __global__ void __launch_bounds__(kRowThreads) nvfp4_quantize_rows_kernel(const uint4* __restrict__ in, size_t rows,
                                                                           int row_vectors, size_t rows_per_scale,
                                                                           const float* __restrict__ global_scales,
+                                                                          const uint32_t* __restrict__ amax_bits,
+                                                                          float* global_scales_out,
                                                                           uint32_t* __restrict__ codes,
                                                                           uint8_t* __restrict__ scales) {
   __shared__ __align__(16) uint8_t scale_bytes[kWideScales ? kMaxRowScaleBytes : 16];
   const int tid = threadIdx.x;
   for (size_t row = blockIdx.x; row < rows; row += gridDim.x) {
-    const float global = __ldg(global_scales + (rows_per_scale ? row / rows_per_scale : 0));
+    const size_t group = rows_per_scale ? row / rows_per_scale : 0;
+    float global;
+    if (amax_bits != nullptr) {
+      // the scale is derived here from the group amax; the group's first row also publishes it
+      global = global_scale_from_amax_bits(__ldg(amax_bits + group));
+      if (tid == 0 && row == group * rows_per_scale) global_scales_out[group] = global;
+    } else {
+      global = __ldg(global_scales + group);
+    }
     const float k = block_scale_factor(global);
     const uint4* src = in + row * static_cast<size_t>(row_vectors);
     uint32_t* dst = codes + row * static_cast<size_t>(row_vectors);
@@ -211,9 +221,18 @@ void enqueue_scales(const uint32_t* amax_bits, size_t groups, float* global_scal
   amax_to_scale_kernel<<<static_cast<unsigned>((groups + 127) / 128), 128, 0, s>>>(amax_bits, groups, global_scales);
 }
 
+// global_scales given: quantise with them.  Else amax_bits given: derive each group's scale from its
+// amax word inside the quantiser and write it to global_scales_out.
 void enqueue_quantize(const uint16_t* in, size_t rows, size_t cols, size_t rows_per_scale, const float* global_scales,
-                      uint8_t* codes, uint8_t* scales, cudaStream_t s) {
+                      const uint32_t* amax_bits, float* global_scales_out, uint8_t* codes, uint8_t* scales,
+                      cudaStream_t s) {
   using namespace host;
+  if (global_scales == nullptr && !(aligned16(in) && (reinterpret_cast<uintptr_t>(codes) & 3u) == 0)) {
+    // the scalar quantiser takes ready-made scales
+    enqueue_scales(amax_bits, group_count(rows, rows_per_scale), global_scales_out, s);
+    global_scales = global_scales_out;
+    amax_bits = nullptr;
+  }
   if (aligned16(in) && (reinterpret_cast<uintptr_t>(codes) & 3u) == 0 && cols / 8 <= 0x7fffffffu) {
     const int row_vectors = static_cast<int>(cols / 8);
     const unsigned grid = grid_for(rows, 1, 16);
@@ -222,10 +241,12 @@ void enqueue_quantize(const uint16_t* in, size_t rows, size_t cols, size_t rows_
     auto C = reinterpret_cast<uint32_t*>(codes);
     if (wide)
       nvfp4_quantize_rows_kernel<true><<<grid, kRowThreads, 0, s>>>(I, rows, row_vectors, rows_per_scale,
-                                                                    global_scales, C, scales);
+                                                                    global_scales, amax_bits, global_scales_out, C,
+                                                                    scales);
     else
       nvfp4_quantize_rows_kernel<false><<<grid, kRowThreads, 0, s>>>(I, rows, row_vectors, rows_per_scale,
-                                                                     global_scales, C, scales);
+                                                                     global_scales, amax_bits, global_scales_out, C,
+                                                                     scales);
   } else {
     const size_t blocks = rows * cols / 16;
     nvfp4_quantize_scalar_kernel<<<grid_for(blocks, kThreads, 8), kThreads, 0, s>>>(in, blocks, cols / 16,
@@ -253,7 +274,7 @@ extern "C" size_t q3x_b200_nvfp4_group_count(size_t rows, size_t rows_per_scale)
 }
 
 extern "C" size_t q3x_b200_nvfp4_scratch_words(size_t rows, size_t rows_per_scale) {
-  return fused_scratch_words(group_count(rows, rows_per_scale));
+  return fused_scratch_words(rows, group_count(rows, rows_per_scale));
 }
 
 extern "C" int q3x_b200_group_amax(const uint16_t* in, size_t rows, size_t cols, size_t rows_per_scale,
@@ -286,7 +307,7 @@ extern "C" int q3x_b200_nvfp4_quantize(const uint16_t* in, size_t rows, size_t c
   if (global_scales == nullptr) return kInvalid;
   if ((st = check_quant_outputs(in, rows, cols, codes, scales)) != kOk) return st;
   clear_stale_error();
-  enqueue_quantize(in, rows, cols, rows_per_scale, global_scales, codes, scales, as_stream(stream));
+  enqueue_quantize(in, rows, cols, rows_per_scale, global_scales, nullptr, nullptr, codes, scales, as_stream(stream));
   return launch_status();
 }
 
@@ -301,18 +322,20 @@ extern "C" int q3x_b200_nvfp4_quantize_dynamic(const uint16_t* in, size_t rows, 
   const size_t groups = group_count(rows, rows_per_scale);
   cudaStream_t s = as_stream(stream);
   clear_stale_error();
+  (void)groups;
   enqueue_amax(in, rows, cols, rows_per_scale, scratch, s);
-  enqueue_scales(scratch, groups, global_scales_out, s);
-  enqueue_quantize(in, rows, cols, rows_per_scale, global_scales_out, codes, scales, s);
+  enqueue_quantize(in, rows, cols, rows_per_scale, nullptr, scratch, global_scales_out, codes, scales, s);
   return launch_status();
 }
 
-extern "C" int q3x_b200_residual_add_rms_norm_nvfp4(const uint16_t* left, const uint16_t* right,
-                                                    const uint16_t* weight, size_t tokens, size_t hidden, float eps,
-                                                    size_t rows_per_scale, uint16_t* residual_out,
-                                                    uint16_t* normalized_out, uint32_t* scratch,
-                                                    float* global_scales_out, uint8_t* codes, uint8_t* scales,
-                                                    void* stream) {
+namespace {
+
+// Shared body of the residual + norm + NVFP4 entry points.  single_pass: the cooperative kernel with
+// deferred quantisation; otherwise two kernels (norm with group amax, then the quantiser).
+int residual_norm_nvfp4(const uint16_t* left, const uint16_t* right, const uint16_t* weight, size_t tokens,
+                        size_t hidden, float eps, size_t rows_per_scale, uint16_t* residual_out,
+                        uint16_t* normalized_out, uint32_t* scratch, float* global_scales_out, uint8_t* codes,
+                        uint8_t* scales, void* stream, bool single_pass) {
   bool done;
   int st = check_residual_norm(left, right, weight, tokens, hidden, eps, residual_out, normalized_out, &done);
   if (st != kOk) return st;
@@ -325,24 +348,25 @@ extern "C" int q3x_b200_residual_add_rms_norm_nvfp4(const uint16_t* left, const 
   const size_t groups = group_count(tokens, rows_per_scale);
   cudaStream_t s = as_stream(stream);
   clear_stale_error();
-  // single pass when a scale group fits one sweep of the resident teams, else three kernels
-  if (launch_residual_norm_nvfp4_fused(left, right, weight, tokens, hidden, eps, rows_per_scale, residual_out,
-                                       normalized_out, scratch, global_scales_out, codes, scales, s))
+  if (single_pass) {
+    if (!launch_residual_norm_nvfp4_fused(left, right, weight, tokens, hidden, eps, rows_per_scale, residual_out,
+                                          normalized_out, scratch, global_scales_out, codes, scales, s))
+      return kNotSupported;
     return launch_status();
-  cudaMemsetAsync(scratch, 0, fused_scratch_words(groups) * sizeof(uint32_t), s);
+  }
+  cudaMemsetAsync(scratch, 0, fused_scratch_words(tokens, groups) * sizeof(uint32_t), s);
   launch_norm_rows(NormMode::kCentered, left, right, weight, nullptr, tokens, hidden, eps, 1.0f, residual_out,
                    normalized_out, /*coherent=*/normalized_out == right, scratch,
                    rows_per_scale ? rows_per_scale : tokens, s);
-  enqueue_scales(scratch, groups, global_scales_out, s);
-  enqueue_quantize(normalized_out, tokens, hidden, rows_per_scale, global_scales_out, codes, scales, s);
+  enqueue_quantize(normalized_out, tokens, hidden, rows_per_scale, nullptr, scratch, global_scales_out, codes, scales,
+                   s);
   return launch_status();
 }
 
-extern "C" int q3x_b200_rms_norm_silu_gate_nvfp4(const uint16_t* in, const uint16_t* weight, const uint16_t* gate,
-                                                 size_t tokens, size_t heads_per_row, size_t dim, float eps,
-                                                 size_t rows_per_scale, uint16_t* out, uint32_t* scratch,
-                                                 float* global_scales_out, uint8_t* codes, uint8_t* scales,
-                                                 void* stream) {
+int gated_norm_nvfp4(const uint16_t* in, const uint16_t* weight, const uint16_t* gate, size_t tokens,
+                     size_t heads_per_row, size_t dim, float eps, size_t rows_per_scale, uint16_t* out,
+                     uint32_t* scratch, float* global_scales_out, uint8_t* codes, uint8_t* scales, void* stream,
+                     bool single_pass) {
   if (!valid_epsilon(eps)) return kInvalid;
   if (mul3_overflows(tokens, heads_per_row, dim) || mul_overflows(tokens * heads_per_row * dim, 2)) return kInvalid;
   const size_t cols = heads_per_row * dim;
@@ -364,15 +388,58 @@ extern "C" int q3x_b200_rms_norm_silu_gate_nvfp4(const uint16_t* in, const uint1
   const size_t token_group = rows_per_scale ? rows_per_scale : tokens;
   cudaStream_t s = as_stream(stream);
   clear_stale_error();
-  if (launch_gated_norm_nvfp4_fused(in, weight, gate, tokens, heads_per_row, dim, eps, rows_per_scale, out, scratch,
-                                    global_scales_out, codes, scales, s))
+  if (single_pass) {
+    if (!launch_gated_norm_nvfp4_fused(in, weight, gate, tokens, heads_per_row, dim, eps, rows_per_scale, out,
+                                       scratch, global_scales_out, codes, scales, s))
+      return kNotSupported;
     return launch_status();
-  cudaMemsetAsync(scratch, 0, fused_scratch_words(groups) * sizeof(uint32_t), s);
+  }
+  cudaMemsetAsync(scratch, 0, fused_scratch_words(tokens, groups) * sizeof(uint32_t), s);
   launch_norm_rows(NormMode::kPlainSiluGate, in, nullptr, weight, gate, tokens * heads_per_row, dim, eps, 1.0f,
                    nullptr, out, /*coherent=*/out == in || out == gate, scratch, token_group * heads_per_row, s);
-  enqueue_scales(scratch, groups, global_scales_out, s);
-  enqueue_quantize(out, tokens, cols, rows_per_scale, global_scales_out, codes, scales, s);
+  enqueue_quantize(out, tokens, cols, rows_per_scale, nullptr, scratch, global_scales_out, codes, scales, s);
   return launch_status();
+}
+
+}  // namespace
+
+extern "C" int q3x_b200_residual_add_rms_norm_nvfp4(const uint16_t* left, const uint16_t* right,
+                                                    const uint16_t* weight, size_t tokens, size_t hidden, float eps,
+                                                    size_t rows_per_scale, uint16_t* residual_out,
+                                                    uint16_t* normalized_out, uint32_t* scratch,
+                                                    float* global_scales_out, uint8_t* codes, uint8_t* scales,
+                                                    void* stream) {
+  return residual_norm_nvfp4(left, right, weight, tokens, hidden, eps, rows_per_scale, residual_out, normalized_out,
+                             scratch, global_scales_out, codes, scales, stream, false);
+}
+
+extern "C" int q3x_b200_residual_add_rms_norm_nvfp4_single_pass(const uint16_t* left, const uint16_t* right,
+                                                                const uint16_t* weight, size_t tokens, size_t hidden,
+                                                                float eps, size_t rows_per_scale,
+                                                                uint16_t* residual_out, uint16_t* normalized_out,
+                                                                uint32_t* scratch, float* global_scales_out,
+                                                                uint8_t* codes, uint8_t* scales, void* stream) {
+  return residual_norm_nvfp4(left, right, weight, tokens, hidden, eps, rows_per_scale, residual_out, normalized_out,
+                             scratch, global_scales_out, codes, scales, stream, true);
+}
+
+extern "C" int q3x_b200_rms_norm_silu_gate_nvfp4(const uint16_t* in, const uint16_t* weight, const uint16_t* gate,
+                                                 size_t tokens, size_t heads_per_row, size_t dim, float eps,
+                                                 size_t rows_per_scale, uint16_t* out, uint32_t* scratch,
+                                                 float* global_scales_out, uint8_t* codes, uint8_t* scales,
+                                                 void* stream) {
+  return gated_norm_nvfp4(in, weight, gate, tokens, heads_per_row, dim, eps, rows_per_scale, out, scratch,
+                          global_scales_out, codes, scales, stream, false);
+}
+
+extern "C" int q3x_b200_rms_norm_silu_gate_nvfp4_single_pass(const uint16_t* in, const uint16_t* weight,
+                                                             const uint16_t* gate, size_t tokens,
+                                                             size_t heads_per_row, size_t dim, float eps,
+                                                             size_t rows_per_scale, uint16_t* out, uint32_t* scratch,
+                                                             float* global_scales_out, uint8_t* codes,
+                                                             uint8_t* scales, void* stream) {
+  return gated_norm_nvfp4(in, weight, gate, tokens, heads_per_row, dim, eps, rows_per_scale, out, scratch,
+                          global_scales_out, codes, scales, stream, true);
 }
 
 // Diagnostics: the two narrow conversions on their own, so that tests can sweep them against the

@@ -26,14 +26,16 @@ namespace {
 struct AmaxTracker {
   uint32_t value = 0;
   size_t group = 0;
+  size_t boundary = 0;  // first row of the next group; rows arrive in increasing order
   bool live = false;
-  __device__ __forceinline__ void add(uint32_t* amax_bits, size_t g, uint32_t m) {
-    if (live && g != group) {
-      atomicMax(amax_bits + group, value);
+  __device__ __forceinline__ void add(uint32_t* amax_bits, size_t row, size_t rows_per_group, uint32_t m) {
+    if (!live || row >= boundary) {  // the division runs once per group a thread visits, not per row
+      if (live && value != 0) atomicMax(amax_bits + group, value);
       value = 0;
+      group = row / rows_per_group;
+      boundary = (group + 1) * rows_per_group;
+      live = true;
     }
-    group = g;
-    live = true;
     value = max(value, m);
   }
   __device__ __forceinline__ void flush(uint32_t* amax_bits) {
@@ -94,7 +96,7 @@ __global__ void __launch_bounds__(256) head_rows_kernel(const uint4* in, const u
         const size_t row = base + p * kRowsPerPass + slot;
         const uint4 y = scale8<MODE>(x[p], w, z[p], inv);
         st_vec(out + row * LANES + lane, y);
-        if (kAmax) tracker.add(amax_bits, row / rows_per_amax_group, amax8(y));
+        if (kAmax) tracker.add(amax_bits, row, rows_per_amax_group, amax8(y));
       }
     }
   }

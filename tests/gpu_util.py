@@ -67,6 +67,13 @@ def empty_like_dev(shape, dtype=np.uint16, misalign=0, fill=None):
     return Dev(a, misalign)
 
 
+def scratch_for(rows, rows_per_scale, fill=0x7FFFFFFF):
+    """The caller-owned scratch of the NVFP4 entry points, pre-filled with garbage: stale contents
+    must not matter."""
+    words = capi.lib().q3x_b200_nvfp4_scratch_words(rows, rows_per_scale)
+    return empty_like_dev((words,), dtype=np.uint32, fill=fill)
+
+
 def sync():
     torch.cuda.synchronize()
 

@@ -71,7 +71,7 @@ def test_graph_capture_and_replay(g):
     w = fx.normal_bf16(rng, (hidden,), 0.02)
     dl, dr, dw = g.Dev(left), g.Dev(right), g.Dev(w)
     res, nrm = g.empty_like_dev((tokens, hidden)), g.empty_like_dev((tokens, hidden))
-    amax = g.empty_like_dev((4,), dtype=np.uint32)
+    amax = g.scratch_for(tokens, 0)
     gs = g.empty_like_dev((1,), dtype=np.float32)
     codes = g.empty_like_dev((tokens, hidden // 2), dtype=np.uint8)
     scales = g.empty_like_dev((tokens, hidden // 16), dtype=np.uint8)
@@ -135,7 +135,7 @@ def test_full_size_properties(g):
     # NVFP4 at full width: the reconstruction error is bounded by the block scale, and the largest
     # element of every scale group lands on +-6 under the largest scale (448)
     x = o1[:1024]
-    amax = torch.zeros(6, device="cuda", dtype=torch.int32)
+    amax = torch.zeros(g.capi.lib().q3x_b200_nvfp4_scratch_words(1024, 512), device="cuda", dtype=torch.int32)
     gs = torch.empty(2, device="cuda", dtype=torch.float32)
     codes = torch.empty(1024, I // 2, device="cuda", dtype=torch.uint8)
     scales = torch.empty(1024, I // 16, device="cuda", dtype=torch.uint8)
