@@ -9,6 +9,7 @@
 // the arithmetic of the host reference (src/runtime/reference/decode_ops.cpp:392-404).
 #include "device_utils.cuh"
 #include "host_checks.hpp"
+#include "norm_math.cuh"
 #include "q3x_b200.h"
 
 namespace q3x {
@@ -63,7 +64,7 @@ __device__ __forceinline__ uint4 centered_norm_head(const uint4& x, const uint4&
 #pragma unroll
   for (int i = 0; i < 8; ++i) partial = fmaf(f[i], f[i], partial);
   const float sum = group_sum<32>(partial);
-  const float inv = 1.0f / sqrtf(__fadd_rn(__fdiv_rn(sum, 256.0f), eps));
+  const float inv = inverse_rms(sum, 1.0f / 256.0f, eps);
   unpack8(w, g);
 #pragma unroll
   for (int i = 0; i < 8; ++i) y[i] = f[i] * inv * (g[i] + 1.0f);
@@ -208,7 +209,8 @@ extern "C" int q3x_b200_full_attention_preprocess(const uint16_t* interleaved_q_
       !aligned16(q_out) || !aligned16(gate_out) || !aligned16(cosines) || !aligned16(sines))
     return kNotSupported;
   clear_stale_error();
-  attention_preprocess_kernel<<<grid_for(tokens, 1, 32), kPreThreads, 0, as_stream(stream)>>>(
+  attention_preprocess_kernel<<<wave_grid(attention_preprocess_kernel, kPreThreads, tokens, 1), kPreThreads, 0,
+                                as_stream(stream)>>>(
       reinterpret_cast<const uint4*>(interleaved_q_gate), reinterpret_cast<uint4*>(key),
       reinterpret_cast<const uint4*>(q_weight), reinterpret_cast<const uint4*>(k_weight), eps,
       reinterpret_cast<uint4*>(q_out), reinterpret_cast<uint4*>(gate_out), cosines, sines, first_position, tokens);

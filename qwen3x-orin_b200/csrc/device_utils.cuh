@@ -141,14 +141,16 @@ __device__ __forceinline__ float stable_sigmoid(float g) {
   return (g >= 0.0f ? 1.0f : e) * r;
 }
 
-// silu(g) = g / (1 + exp(-g)) (decode_ops.cpp:315-316) = g * sigmoid(g), same stable evaluation.
-// The host op evaluates exp(-g) in FP32, which overflows to infinity for g < -88.7228317 and makes
-// its quotient -0 there; the same cut-off is applied so that the two agree on that tail too.
+// silu(g) = g / (1 + exp(-g)) (decode_ops.cpp:315-316).
+// It is evaluated in exactly that shape, g * (1 / (1 + exp(-g))), with the two fast units: for
+// g < -88.72 exp(-g) overflows to +inf, the reciprocal is 0 and the product is -0, just as in the
+// host op; for large positive g the exponential vanishes and the result is g.  The reciprocal keeps
+// subnormal results (g in (-88.7, -87.3) needs them), the exponential may flush (1 + tiny == 1).
 __device__ __forceinline__ float silu(float g) {
-  const float e = exp_neg_abs(g);
-  const float r = rcp_approx(1.0f + e);
-  const float num = g >= 0.0f ? 1.0f : (g < -88.72283172607422f ? 0.0f : e);
-  return g * (num * r);
+  float e, r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(g * -1.4426950408889634f));
+  asm("rcp.approx.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+  return g * r;
 }
 
 // ---------------------------------------------------------------------------- bf16 amax

@@ -182,6 +182,7 @@ __global__ void __launch_bounds__(kTeam) residual_norm_nvfp4_kernel(
   const size_t teams = gridDim.x;
   const size_t first = blockIdx.x;
   const size_t lag = static_cast<size_t>(depth - 1);
+  const float inv_width = 1.0f / width;
   if (first < board.rows) stage_row<VPT>(smem, left, right, first * static_cast<size_t>(row_vectors), row_vectors, tid);
 
   for (size_t it = 0;; ++it) {
@@ -219,7 +220,7 @@ __global__ void __launch_bounds__(kTeam) residual_norm_nvfp4_kernel(
       if ((tid & 31) == 0) ts.sums[tid >> 5] = partial;
       __syncthreads();
       const float total = ts.sums[0] + ts.sums[1] + ts.sums[2] + ts.sums[3];
-      const float inv = inverse_rms(total, width, eps);
+      const float inv = inverse_rms(total, inv_width, eps);
       uint4* slot = Carve<VPT>::ring(smem, static_cast<int>(it % depth));
       uint32_t top = 0;
 #pragma unroll
@@ -289,7 +290,7 @@ __global__ void __launch_bounds__(kTeam) gated_norm_nvfp4_kernel(
       for (int i = 0; i < VPT; ++i) {
         const int v = tid + i * kTeam;  // head = v / 16: the 16 lanes of a head sit in one warp
         const float sum = group_sum<kLanes>(sum_squares8(x[i]));
-        const float inv = inverse_rms(sum, static_cast<float>(Q3X_B200_GDN_HEAD_DIM), eps);
+        const float inv = inverse_rms(sum, 1.0f / static_cast<float>(Q3X_B200_GDN_HEAD_DIM), eps);
         if (v < row_vectors) {
           const uint4 y = scale8<NormMode::kPlainSiluGate>(x[i], w, z[i], inv);
           st_vec(out + base + v, y);

@@ -15,14 +15,27 @@
 // write and is also the one that publishes the new history, so the update is race-free in place.
 #include "device_utils.cuh"
 #include "host_checks.hpp"
+#include "norm_math.cuh"
 #include "q3x_b200.h"
 
 namespace q3x {
 namespace {
 
 constexpr int kThreads = 128;
-constexpr int kTokenUnroll = 4;
-constexpr int kRunTokens = 64;  // tokens per CTA on the parallel path (multiple of kTokenUnroll)
+constexpr int kBatch = 8;        // token rows staged per cp.async group
+constexpr int kMinRunTokens = 64;  // shortest token run per CTA on the parallel path (halo overhead 3/64)
+
+// Input rows reach the SM through cp.async into shared memory, two batches of kBatch rows deep: the
+// next batch is in flight while the current one is computed, so a warp keeps 8 x 512 bytes of loads
+// outstanding at all times.  A thread copies, reads and later overwrites only its own 16-byte slots,
+// so the staging needs no barrier, only the per-thread cp.async wait.
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* global_src) {
+  const unsigned dst = static_cast<unsigned>(__cvta_generic_to_shared(smem_dst));
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(global_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 constexpr int kHeadVectors = Q3X_B200_GDN_HEAD_DIM / 8;                               // 16 lanes per head
 constexpr int kQkVectors = 2 * Q3X_B200_GDN_QK_HEADS * Q3X_B200_GDN_HEAD_DIM / 8;     // 512: q then k
 
@@ -81,7 +94,7 @@ __global__ void __launch_bounds__(kThreads, kInPlace ? 1 : 4)
         for (int r = 0; r < 3; ++r) rows[r] = history_row(h, r);
       } else {
 #pragma unroll
-        for (int r = 0; r < 3; ++r)  // t0 >= run_tokens >= 3
+        for (int r = 0; r < 3; ++r)  // t0 >= run_tokens >= kBatch > 3
           rows[r] = ld_vec(raw + (t0 - 3 + r) * channel_vectors + cv);
       }
     }
@@ -95,19 +108,29 @@ __global__ void __launch_bounds__(kThreads, kInPlace ? 1 : 4)
   const bool is_q = kL2 && cv < kQkVectors / 2;
   const bool is_qk = kL2 && cv < kQkVectors;  // uniform per CTA: 128 vectors per CTA divide 256
 
-  for (size_t t = t0; t < t1; t += kTokenUnroll) {
-    uint4 x_bits[kTokenUnroll];
+  __shared__ __align__(16) uint4 stage[2][kBatch][kThreads];
+  auto issue_batch = [&](size_t first_token, int buffer) {
 #pragma unroll
-    for (int u = 0; u < kTokenUnroll; ++u) {
-      x_bits[u] = make_uint4(0, 0, 0, 0);
-      if (active && t + u < t1) x_bits[u] = kInPlace ? ld_vec(raw + (t + u) * channel_vectors + cv)
-                                                     : ld_stream(raw + (t + u) * channel_vectors + cv);
+    for (int u = 0; u < kBatch; ++u)
+      if (active && first_token + u < t1)
+        cp_async16(&stage[buffer][u][threadIdx.x], raw + (first_token + u) * channel_vectors + cv);
+    cp_async_commit();
+  };
+  issue_batch(t0, 0);
+  int buffer = 0;
+  for (size_t t = t0; t < t1; t += kBatch, buffer ^= 1) {
+    if (t + kBatch < t1) {
+      issue_batch(t + kBatch, buffer ^ 1);
+      cp_async_wait<1>();  // everything but the batch just issued has landed
+    } else {
+      cp_async_wait<0>();
     }
 #pragma unroll
-    for (int u = 0; u < kTokenUnroll; ++u) {
+    for (int u = 0; u < kBatch; ++u) {
       if (t + u >= t1) break;  // uniform across the CTA
+      const uint4 x_bits = active ? stage[buffer][u][threadIdx.x] : make_uint4(0, 0, 0, 0);
       float x[8], y[8];
-      unpack8(x_bits[u], x);
+      unpack8(x_bits, x);
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         float acc = fmaf(win[0][j], w[j][0], 0.0f);
@@ -122,7 +145,7 @@ __global__ void __launch_bounds__(kThreads, kInPlace ? 1 : 4)
       if (kInPlace) {
         keep[0] = keep[1];
         keep[1] = keep[2];
-        keep[2] = x_bits[u];
+        keep[2] = x_bits;
       }
       uint4 packed = pack8(y);
       if (is_qk) {
@@ -133,7 +156,7 @@ __global__ void __launch_bounds__(kThreads, kInPlace ? 1 : 4)
 #pragma unroll
         for (int j = 0; j < 8; ++j) partial = fmaf(r[j], r[j], partial);
         const float sum = group_sum<kHeadVectors>(partial);
-        float inv = 1.0f / sqrtf(__fadd_rn(sum, l2_eps));
+        float inv = inverse_l2(sum, l2_eps);
         if (is_q && q_scale != 1.0f) inv = inv * q_scale;
 #pragma unroll
         for (int j = 0; j < 8; ++j) r[j] = r[j] * inv;
@@ -198,7 +221,20 @@ int launch_conv(const uint16_t* raw, size_t tokens, size_t channels, const uint1
   if (!aligned16(raw) || !aligned16(out) || !aligned16(weight) || !aligned16(history)) return kNotSupported;
   const int channel_vectors = static_cast<int>(channels / 8);
   const bool serial = raw == out;  // in place: one run, each thread reads a row before overwriting it
-  const size_t run = serial ? tokens : static_cast<size_t>(kRunTokens);
+  const unsigned channel_blocks = static_cast<unsigned>((channel_vectors + kThreads - 1) / kThreads);
+  size_t run = tokens;
+  if (!serial) {
+    // token runs sized so that the grid is a whole number of resident waves (no idle tail wave),
+    // with runs no shorter than kMinRunTokens, in multiples of the staging batch
+    const unsigned resident = l2 ? resident_grid(causal_conv_kernel<true, false>, kThreads)
+                                 : resident_grid(causal_conv_kernel<false, false>, kThreads);
+    const size_t runs_per_wave = resident / channel_blocks > 0 ? resident / channel_blocks : 1;
+    const size_t waves = (tokens + runs_per_wave * kMinRunTokens - 1) / (runs_per_wave * kMinRunTokens);
+    const size_t want_runs = runs_per_wave * (waves > 0 ? waves : 1);
+    run = (tokens + want_runs - 1) / want_runs;
+    run = (run + kBatch - 1) / kBatch * kBatch;
+    if (run < static_cast<size_t>(kBatch)) run = kBatch;
+  }
   const size_t runs = (tokens + run - 1) / run;
   if (runs > 65535u) {
     // grid.y limit: longer spans are cut into launches that hand the history over in order
@@ -211,7 +247,7 @@ int launch_conv(const uint16_t* raw, size_t tokens, size_t channels, const uint1
     }
     return kOk;
   }
-  const dim3 grid((channel_vectors + kThreads - 1) / kThreads, static_cast<unsigned>(runs));
+  const dim3 grid(channel_blocks, static_cast<unsigned>(runs));
   clear_stale_error();
   auto R = reinterpret_cast<const uint4*>(raw);
   auto W = reinterpret_cast<const uint4*>(weight);

@@ -7,10 +7,12 @@
 
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <cmath>
 #include <cstddef>
 #include <cstdint>
 #include <limits>
+#include <mutex>
 
 namespace q3x::host {
 
@@ -68,6 +70,51 @@ inline unsigned grid_for(size_t work_items, unsigned items_per_cta, unsigned cta
   }
   const size_t needed = (work_items + items_per_cta - 1) / items_per_cta;
   const size_t cap = static_cast<size_t>(sm_count) * ctas_per_sm_target;
+  const size_t g = needed < cap ? needed : cap;
+  return static_cast<unsigned>(g == 0 ? 1 : g);
+}
+
+// CTAs of `kernel` (with `threads` threads and `smem` dynamic bytes) that are resident at once on the
+// current device: occupancy per SM x SM count.  A grid-stride kernel launched with exactly this many
+// CTAs runs as one full wave; a larger grid would leave a partial last wave that idles most SMs.
+// The answer is cached per kernel (a few dozen entries; lock-free reads).
+template <typename Kernel>
+inline unsigned resident_grid(Kernel kernel, int threads, size_t smem = 0) {
+  struct Entry {
+    const void* key;
+    unsigned value;
+  };
+  constexpr int kSlots = 128;
+  static Entry table[kSlots] = {};
+  static std::atomic<int> used{0};
+  const void* key = reinterpret_cast<const void*>(kernel);
+  const int n = used.load(std::memory_order_acquire);
+  for (int i = 0; i < n; ++i)
+    if (table[i].key == key) return table[i].value;
+  int dev = 0, sms = 0, per_sm = 0;
+  unsigned value = 148u * 4u;
+  if (cudaGetDevice(&dev) == cudaSuccess &&
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess &&
+      cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, smem) == cudaSuccess && sms > 0 &&
+      per_sm > 0)
+    value = static_cast<unsigned>(sms) * static_cast<unsigned>(per_sm);
+  static std::mutex mu;
+  std::lock_guard<std::mutex> lock(mu);
+  const int m = used.load(std::memory_order_relaxed);
+  for (int i = 0; i < m; ++i)
+    if (table[i].key == key) return table[i].value;
+  if (m < kSlots) {
+    table[m] = Entry{key, value};
+    used.store(m + 1, std::memory_order_release);
+  }
+  return value;
+}
+
+// Grid of a grid-stride kernel: one full wave, or fewer CTAs when the work is smaller than that.
+template <typename Kernel>
+inline unsigned wave_grid(Kernel kernel, int threads, size_t work_items, size_t items_per_cta, size_t smem = 0) {
+  const size_t needed = (work_items + items_per_cta - 1) / items_per_cta;
+  const size_t cap = resident_grid(kernel, threads, smem);
   const size_t g = needed < cap ? needed : cap;
   return static_cast<unsigned>(g == 0 ? 1 : g);
 }

@@ -16,10 +16,25 @@ __device__ __forceinline__ float sum_squares8(const uint4& v) {
   return s;
 }
 
-// 1 / sqrt(sum / n + eps)  (src/runtime/reference/decode_ops.cpp:74-76)
-__device__ __forceinline__ float inverse_rms(float sum, float n, float eps) {
-  return 1.0f / sqrtf(__fadd_rn(__fdiv_rn(sum, n), eps));
+// 1 / sqrt(t) from MUFU.RSQ plus one Newton step: relative error about 2^-23, the accuracy class of
+// the IEEE divide / sqrt / divide chain it stands in for, at a fifth of the instructions (every
+// lane of a row evaluates it).
+__device__ __forceinline__ float refined_rsqrt(float t) {
+  float r;
+  asm("rsqrt.approx.f32 %0, %1;" : "=f"(r) : "f"(t));
+  const float half_t = 0.5f * t;
+  const float refined = r * fmaf(-half_t * r, r, 1.5f);
+  // an overflowed sum (t = inf) gives r = 0 like the IEEE chain; the Newton step would turn it into NaN
+  return t < 3.0e38f ? refined : r;
 }
+
+// inverse RMS: 1 / sqrt(sum / n + eps)  (src/runtime/reference/decode_ops.cpp:74-76); inv_n = 1 / n.
+// eps > 0 keeps the argument positive and normal; an infinite or NaN sum propagates as 0 / NaN.
+__device__ __forceinline__ float inverse_rms(float sum, float inv_n, float eps) {
+  return refined_rsqrt(fmaf(sum, inv_n, eps));
+}
+// inverse L2 norm: 1 / sqrt(sum + eps)  (decode_ops.cpp:369)
+__device__ __forceinline__ float inverse_l2(float sum, float eps) { return refined_rsqrt(sum + eps); }
 
 template <NormMode MODE>
 __device__ __forceinline__ uint4 scale8(const uint4& x, const uint4& w, const uint4& z, float inv) {

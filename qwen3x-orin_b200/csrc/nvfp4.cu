@@ -88,6 +88,8 @@ __global__ void __launch_bounds__(kRowThreads) nvfp4_quantize_rows_kernel(const 
                                                                           uint32_t* __restrict__ codes,
                                                                           uint8_t* __restrict__ scales) {
   __shared__ __align__(16) uint8_t scale_bytes[kWideScales ? kMaxRowScaleBytes : 16];
+  __shared__ float inv_table[kRowThreads];  // indexed by E4M3 code 0..127
+  static_assert(kRowThreads == 128, "one thread per non-negative E4M3 code");
   const int tid = threadIdx.x;
   for (size_t row = blockIdx.x; row < rows; row += gridDim.x) {
     const size_t group = rows_per_scale ? row / rows_per_scale : 0;
@@ -100,6 +102,10 @@ __global__ void __launch_bounds__(kRowThreads) nvfp4_quantize_rows_kernel(const 
       global = __ldg(global_scales + group);
     }
     const float k = block_scale_factor(global);
+    // 1 / (decode(s) * global) for every scale code, once per row instead of once per lane and block
+    __syncthreads();  // the previous row's readers of inv_table / scale_bytes are done
+    inv_table[tid] = block_inverse(static_cast<uint32_t>(tid), global);
+    __syncthreads();
     const uint4* src = in + row * static_cast<size_t>(row_vectors);
     uint32_t* dst = codes + row * static_cast<size_t>(row_vectors);
     uint8_t* srow = scales + row * static_cast<size_t>(row_vectors / 2);
@@ -119,9 +125,8 @@ __global__ void __launch_bounds__(kRowThreads) nvfp4_quantize_rows_kernel(const 
         uint32_t m = amax8(x[u]);
         m = max(m, __shfl_xor_sync(kFullMask, m, 1));
         const uint32_t s = block_scale_code(m, k);
-        const float inv = block_inverse(s, global);
         if (valid[u]) {
-          dst[v] = quantize8(x[u], inv);
+          dst[v] = quantize8(x[u], inv_table[s]);
           if ((tid & 1) == 0) {
             if (kWideScales) scale_bytes[v >> 1] = static_cast<uint8_t>(s);
             else srow[v >> 1] = static_cast<uint8_t>(s);
@@ -133,7 +138,6 @@ __global__ void __launch_bounds__(kRowThreads) nvfp4_quantize_rows_kernel(const 
       __syncthreads();
       for (int i = tid; i < row_vectors / 32; i += kRowThreads)
         reinterpret_cast<uint4*>(srow)[i] = reinterpret_cast<const uint4*>(scale_bytes)[i];
-      __syncthreads();
     }
   }
 }
@@ -235,16 +239,17 @@ void enqueue_quantize(const uint16_t* in, size_t rows, size_t cols, size_t rows_
   }
   if (aligned16(in) && (reinterpret_cast<uintptr_t>(codes) & 3u) == 0 && cols / 8 <= 0x7fffffffu) {
     const int row_vectors = static_cast<int>(cols / 8);
-    const unsigned grid = grid_for(rows, 1, 16);
     const bool wide = aligned16(scales) && (cols / 16) % 16 == 0 && cols / 16 <= kMaxRowScaleBytes;
     auto I = reinterpret_cast<const uint4*>(in);
     auto C = reinterpret_cast<uint32_t*>(codes);
     if (wide)
-      nvfp4_quantize_rows_kernel<true><<<grid, kRowThreads, 0, s>>>(I, rows, row_vectors, rows_per_scale,
+      nvfp4_quantize_rows_kernel<true><<<wave_grid(nvfp4_quantize_rows_kernel<true>, kRowThreads, rows, 1),
+                                         kRowThreads, 0, s>>>(I, rows, row_vectors, rows_per_scale,
                                                                     global_scales, amax_bits, global_scales_out, C,
                                                                     scales);
     else
-      nvfp4_quantize_rows_kernel<false><<<grid, kRowThreads, 0, s>>>(I, rows, row_vectors, rows_per_scale,
+      nvfp4_quantize_rows_kernel<false><<<wave_grid(nvfp4_quantize_rows_kernel<false>, kRowThreads, rows, 1),
+                                          kRowThreads, 0, s>>>(I, rows, row_vectors, rows_per_scale,
                                                                      global_scales, amax_bits, global_scales_out, C,
                                                                      scales);
   } else {

@@ -145,13 +145,14 @@ int launch_binary(const uint16_t* a, const uint16_t* b, size_t count, uint16_t* 
   size_t done = 0;
   if (aligned16(a) && aligned16(b) && aligned16(out) && count >= 8) {
     const size_t nvec = count / 8;
-    const unsigned grid = grid_for(nvec, kThreads * kUnroll, 8);
     if (in_place)
-      binary_vec_kernel<Op, true><<<grid, kThreads, 0, s>>>(reinterpret_cast<const uint4*>(a),
+      binary_vec_kernel<Op, true><<<wave_grid(binary_vec_kernel<Op, true>, kThreads, nvec, kThreads * kUnroll),
+                                    kThreads, 0, s>>>(reinterpret_cast<const uint4*>(a),
                                                             reinterpret_cast<const uint4*>(b),
                                                             reinterpret_cast<uint4*>(out), nvec);
     else
-      binary_vec_kernel<Op, false><<<grid, kThreads, 0, s>>>(reinterpret_cast<const uint4*>(a),
+      binary_vec_kernel<Op, false><<<wave_grid(binary_vec_kernel<Op, false>, kThreads, nvec, kThreads * kUnroll),
+                                     kThreads, 0, s>>>(reinterpret_cast<const uint4*>(a),
                                                              reinterpret_cast<const uint4*>(b),
                                                              reinterpret_cast<uint4*>(out), nvec);
     done = nvec * 8;
@@ -196,7 +197,8 @@ extern "C" int q3x_b200_silu_mul_merged(const uint16_t* merged, size_t tokens, s
   clear_stale_error();
   if (intermediate % 8 == 0 && intermediate / 8 <= 0xffffffffu && aligned16(merged) && aligned16(out)) {
     const size_t nvec = count / 8;
-    silu_mul_merged_vec_kernel<<<grid_for(nvec, kThreads * kUnroll, 8), kThreads, 0, s>>>(
+    silu_mul_merged_vec_kernel<<<wave_grid(silu_mul_merged_vec_kernel, kThreads, nvec, kThreads * kUnroll), kThreads,
+                                 0, s>>>(
         reinterpret_cast<const uint4*>(merged), reinterpret_cast<uint4*>(out), nvec,
         static_cast<unsigned>(intermediate / 8));
   } else {

@@ -87,10 +87,10 @@ __global__ void __launch_bounds__(256) head_rows_kernel(const uint4* in, const u
       const float sum = group_sum<LANES>(sum_squares8(x[p]));
       float inv;
       if (MODE == NormMode::kL2) {
-        inv = 1.0f / sqrtf(__fadd_rn(sum, eps));
+        inv = inverse_l2(sum, eps);
         if (l2_scale != 1.0f) inv = inv * l2_scale;
       } else {
-        inv = inverse_rms(sum, static_cast<float>(LANES * 8), eps);
+        inv = inverse_rms(sum, 1.0f / static_cast<float>(LANES * 8), eps);
       }
       if (valid[p]) {
         const size_t row = base + p * kRowsPerPass + slot;
@@ -148,7 +148,7 @@ __global__ void __launch_bounds__(128) hidden_rows_kernel(const uint4* a, const 
   for (int k = 0; k < VPT; ++k) partial += sum_squares8(x[k]);
   if (normalized_out == nullptr) return;
   const float total = block_sum<4>(partial, scratch);
-  const float inv = inverse_rms(total, width, eps);
+  const float inv = inverse_rms(total, 1.0f / width, eps);
   uint32_t top = 0;
 #pragma unroll
   for (int k = 0; k < VPT; ++k) {
@@ -196,10 +196,10 @@ __global__ void __launch_bounds__(256) generic_rows_kernel(const uint16_t* a, co
   const float total = block_sum<8>(partial, scratch);
   float inv;
   if (MODE == NormMode::kL2) {
-    inv = 1.0f / sqrtf(__fadd_rn(total, eps));
+    inv = inverse_l2(total, eps);
     if (l2_scale != 1.0f) inv = inv * l2_scale;
   } else {
-    inv = inverse_rms(total, static_cast<float>(width), eps);
+    inv = inverse_rms(total, 1.0f / static_cast<float>(width), eps);
   }
   for (size_t i = threadIdx.x; i < width; i += 256) {
     const float v = bf16_to_float(x[i]);  // a thread re-reads only what it wrote itself
@@ -220,7 +220,13 @@ void launch_head_rows(const uint16_t* in, const uint16_t* weight, const uint16_t
                       float l2_scale, uint16_t* out, bool coherent, uint32_t* amax_bits, size_t rows_per_amax_group,
                       cudaStream_t s) {
   constexpr size_t kRowsPerIter = 2 * (256 / LANES);
-  const unsigned grid = host::grid_for(rows, kRowsPerIter, 16);
+  // contiguous row ranges, a whole number of resident waves (at most four) so no partial wave idles
+  const unsigned resident = amax_bits ? host::resident_grid(head_rows_kernel<LANES, MODE, true>, 256)
+                                      : host::resident_grid(head_rows_kernel<LANES, MODE, false>, 256);
+  const size_t iterations = (rows + kRowsPerIter - 1) / kRowsPerIter;
+  size_t waves = iterations / (static_cast<size_t>(resident) * 8);  // >= 8 iterations per CTA
+  waves = waves < 1 ? 1 : (waves > 4 ? 4 : waves);
+  const size_t grid = iterations < resident * waves ? iterations : resident * waves;
   size_t rows_per_cta = (rows + grid - 1) / grid;
   rows_per_cta = (rows_per_cta + kRowsPerIter - 1) / kRowsPerIter * kRowsPerIter;
   const unsigned ctas = static_cast<unsigned>((rows + rows_per_cta - 1) / rows_per_cta);
