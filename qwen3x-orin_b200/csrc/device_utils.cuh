@@ -168,4 +168,22 @@ __device__ __forceinline__ uint32_t amax8(const uint4& v) {
   return max(m & 0xffffu, m >> 16);
 }
 
+// The same amax from FP32 values, eight at a time, for kernels that hold the values as floats anyway
+// (seven FMNMX instead of the packed-integer sequence).  Two facts make it exact:
+//   * fmaxf ignores NaN operands, which is the "finite elements only" rule for NaN;
+//   * round-to-nearest-even is monotonic and symmetric, so the largest ROUNDED magnitude equals the
+//     rounding of the largest unrounded magnitude.
+// What is left is a magnitude that is, or rounds to, infinity: it has to be excluded, and the next
+// largest is not known from a running maximum, so that (rare) case is recomputed from the packed
+// bf16 bits with the integer sequence above.  `packed` holds the eight values after rounding.
+constexpr float kRoundsToBf16Inf = 3.3961775e38f;  // midpoint of the largest finite bf16 and 2^128
+__device__ __forceinline__ float amax8_float(const float (&f)[8], const uint4& packed) {
+  float t = fmaxf(fmaxf(fmaxf(fabsf(f[0]), fabsf(f[1])), fmaxf(fabsf(f[2]), fabsf(f[3]))),
+                  fmaxf(fmaxf(fabsf(f[4]), fabsf(f[5])), fmaxf(fabsf(f[6]), fabsf(f[7]))));
+  if (t >= kRoundsToBf16Inf) t = __uint_as_float(amax8(packed) << 16);
+  return t;
+}
+// bf16 magnitude bits of a non-negative amax accumulated with amax8_float
+__device__ __forceinline__ uint32_t amax_bits_of(float t) { return float_to_bf16(t); }
+
 }  // namespace q3x

@@ -123,12 +123,14 @@ __device__ __forceinline__ void quantize_ring_row(const uint4* slot, int row_vec
     const int v = tid + i * kTeam;
     const bool valid = v < row_vectors;  // lane pairs are valid together (row_vectors is even)
     const uint4 y = valid ? slot[v] : make_uint4(0, 0, 0, 0);
-    uint32_t m = amax8(y);
-    m = max(m, __shfl_xor_sync(kFullMask, m, 1));
+    float f[8];
+    unpack8(y, f);
+    float m = amax8_float(f, y);
+    m = fmaxf(m, __shfl_xor_sync(kFullMask, m, 1));
     const uint32_t s = block_scale_code(m, k);
     const float inv = block_inverse(s, global);
     if (valid) {
-      codes_row[v] = quantize8(y, inv);
+      codes_row[v] = quantize8(f, inv);
       if ((tid & 1) == 0) {
         if (wide_scale_stores) ts.scale_bytes[v >> 1] = static_cast<uint8_t>(s);
         else scales_row[v >> 1] = static_cast<uint8_t>(s);
@@ -222,18 +224,18 @@ __global__ void __launch_bounds__(kTeam) residual_norm_nvfp4_kernel(
       const float total = ts.sums[0] + ts.sums[1] + ts.sums[2] + ts.sums[3];
       const float inv = inverse_rms(total, inv_width, eps);
       uint4* slot = Carve<VPT>::ring(smem, static_cast<int>(it % depth));
-      uint32_t top = 0;
+      float top = 0.0f;
 #pragma unroll
       for (int i = 0; i < VPT; ++i) {
         const int v = tid + i * kTeam;
         if (v < row_vectors) {
-          const uint4 y = scale8<NormMode::kCentered>(x[i], ld_weight(weight + v), make_uint4(0, 0, 0, 0), inv);
+          const uint4 y =
+              scale8<NormMode::kCentered, true>(x[i], ld_weight(weight + v), make_uint4(0, 0, 0, 0), inv, &top);
           st_vec(normalized_out + base + v, y);
           slot[v] = y;
-          top = max(top, amax8(y));
         }
       }
-      publish_row(board, ts, tid, row, top);
+      publish_row(board, ts, tid, row, amax_bits_of(top));
     }
     if (has_old) {
       const size_t old_it = it - lag;
@@ -285,20 +287,19 @@ __global__ void __launch_bounds__(kTeam) gated_norm_nvfp4_kernel(
       if (row + teams < board.rows)
         stage_row<VPT>(smem, in, gate, (row + teams) * static_cast<size_t>(row_vectors), row_vectors, tid);
       uint4* slot = Carve<VPT>::ring(smem, static_cast<int>(it % depth));
-      uint32_t top = 0;
+      float top = 0.0f;
 #pragma unroll
       for (int i = 0; i < VPT; ++i) {
         const int v = tid + i * kTeam;  // head = v / 16: the 16 lanes of a head sit in one warp
         const float sum = group_sum<kLanes>(sum_squares8(x[i]));
         const float inv = inverse_rms(sum, 1.0f / static_cast<float>(Q3X_B200_GDN_HEAD_DIM), eps);
         if (v < row_vectors) {
-          const uint4 y = scale8<NormMode::kPlainSiluGate>(x[i], w, z[i], inv);
+          const uint4 y = scale8<NormMode::kPlainSiluGate, true>(x[i], w, z[i], inv, &top);
           st_vec(out + base + v, y);
           slot[v] = y;
-          top = max(top, amax8(y));
         }
       }
-      publish_row(board, ts, tid, row, top);
+      publish_row(board, ts, tid, row, amax_bits_of(top));
     }
     if (has_old) {
       const size_t old_it = it - lag;

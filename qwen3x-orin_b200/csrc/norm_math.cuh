@@ -36,8 +36,11 @@ __device__ __forceinline__ float inverse_rms(float sum, float inv_n, float eps) 
 // inverse L2 norm: 1 / sqrt(sum + eps)  (decode_ops.cpp:369)
 __device__ __forceinline__ float inverse_l2(float sum, float eps) { return refined_rsqrt(sum + eps); }
 
-template <NormMode MODE>
-__device__ __forceinline__ uint4 scale8(const uint4& x, const uint4& w, const uint4& z, float inv) {
+// Scales eight elements; *top (when given) is raised to the largest finite magnitude of the result
+// after rounding (see amax8_float).
+template <NormMode MODE, bool kTrackAmax = false>
+__device__ __forceinline__ uint4 scale8(const uint4& x, const uint4& w, const uint4& z, float inv,
+                                        float* top = nullptr) {
   float xf[8], wf[8], zf[8], y[8];
   unpack8(x, xf);
   if (MODE != NormMode::kL2) unpack8(w, wf);
@@ -52,7 +55,9 @@ __device__ __forceinline__ uint4 scale8(const uint4& x, const uint4& w, const ui
       if (MODE == NormMode::kPlainSiluGate) y[i] *= silu(zf[i]);
     }
   }
-  return pack8(y);
+  const uint4 packed = pack8(y);
+  if (kTrackAmax) *top = fmaxf(*top, amax8_float(y, packed));
+  return packed;
 }
 
 }  // namespace q3x

@@ -122,11 +122,13 @@ __global__ void __launch_bounds__(kRowThreads) nvfp4_quantize_rows_kernel(const 
 #pragma unroll
       for (int u = 0; u < 2; ++u) {
         const int v = base + u * kRowThreads + tid;
-        uint32_t m = amax8(x[u]);
-        m = max(m, __shfl_xor_sync(kFullMask, m, 1));
+        float f[8];
+        unpack8(x[u], f);
+        float m = amax8_float(f, x[u]);
+        m = fmaxf(m, __shfl_xor_sync(kFullMask, m, 1));
         const uint32_t s = block_scale_code(m, k);
         if (valid[u]) {
-          dst[v] = quantize8(x[u], inv_table[s]);
+          dst[v] = quantize8(f, inv_table[s]);
           if ((tid & 1) == 0) {
             if (kWideScales) scale_bytes[v >> 1] = static_cast<uint8_t>(s);
             else srow[v >> 1] = static_cast<uint8_t>(s);

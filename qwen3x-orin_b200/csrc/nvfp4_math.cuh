@@ -48,9 +48,12 @@ __device__ __forceinline__ float global_scale_from_amax_bits(uint32_t amax_bits)
 __device__ __forceinline__ float block_scale_factor(float global) {
   return __fdiv_rn(1.0f, __fmul_rn(global, 6.0f));
 }
-// E4M3 code of one block scale from the block's amax bits (bf16 magnitude of the largest finite element)
+// E4M3 code of one block scale from the block's amax (magnitude of its largest finite element)
+__device__ __forceinline__ uint32_t block_scale_code(float amax, float k) {
+  return amax == 0.0f ? 0u : encode_e4m3(__fmul_rn(amax, k));
+}
 __device__ __forceinline__ uint32_t block_scale_code(uint32_t amax_bits, float k) {
-  return amax_bits == 0 ? 0u : encode_e4m3(__fmul_rn(__uint_as_float(amax_bits << 16), k));
+  return block_scale_code(__uint_as_float(amax_bits << 16), k);
 }
 // inv = d == 0 ? 0 : min(1 / d, FLT_MAX) with d = decode(scale) * global
 __device__ __forceinline__ float block_inverse(uint32_t scale_code, float global) {
@@ -58,12 +61,16 @@ __device__ __forceinline__ float block_inverse(uint32_t scale_code, float global
   return d == 0.0f ? 0.0f : fminf(__frcp_rn(d), FLT_MAX);
 }
 // the eight codes of one vector under a block's reciprocal
+__device__ __forceinline__ uint32_t quantize8(const float (&x)[8], float inv) {
+  float f[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) f[i] = __fmul_rn(x[i], inv);
+  return encode_e2m1x8(f);
+}
 __device__ __forceinline__ uint32_t quantize8(const uint4& x, float inv) {
   float f[8];
   unpack8(x, f);
-#pragma unroll
-  for (int i = 0; i < 8; ++i) f[i] = __fmul_rn(f[i], inv);
-  return encode_e2m1x8(f);
+  return quantize8(f, inv);
 }
 
 }  // namespace q3x

@@ -24,29 +24,30 @@ namespace {
 // Accumulates a running group amax in registers and flushes it with one atomic when the group
 // changes; rows are visited in increasing order so a thread flushes a handful of times at most.
 struct AmaxTracker {
-  uint32_t value = 0;
+  float value = 0.0f;  // running amax (see amax8_float); converted to bf16 bits when flushed
   size_t group = 0;
   size_t boundary = 0;  // first row of the next group; rows arrive in increasing order
   bool live = false;
-  __device__ __forceinline__ void add(uint32_t* amax_bits, size_t row, size_t rows_per_group, uint32_t m) {
+  // call BEFORE accumulating the values of `row`
+  __device__ __forceinline__ void enter_row(uint32_t* amax_bits, size_t row, size_t rows_per_group) {
     if (!live || row >= boundary) {  // the division runs once per group a thread visits, not per row
-      if (live && value != 0) atomicMax(amax_bits + group, value);
-      value = 0;
+      if (live && value != 0.0f) atomicMax(amax_bits + group, amax_bits_of(value));
+      value = 0.0f;
       group = row / rows_per_group;
       boundary = (group + 1) * rows_per_group;
       live = true;
     }
-    value = max(value, m);
   }
   __device__ __forceinline__ void flush(uint32_t* amax_bits) {
     // fast path: the whole warp ends in the same group -> one atomic per warp
     const size_t g0 = static_cast<size_t>(__shfl_sync(kFullMask, static_cast<unsigned long long>(group), 0));
     const bool uniform = __all_sync(kFullMask, live && group == g0);
+    const uint32_t bits = amax_bits_of(value);
     if (uniform) {
-      const uint32_t m = group_max_u32<32>(value);
+      const uint32_t m = group_max_u32<32>(bits);
       if ((threadIdx.x & 31) == 0 && m != 0) atomicMax(amax_bits + g0, m);
-    } else if (live && value != 0) {
-      atomicMax(amax_bits + group, value);
+    } else if (live && bits != 0) {
+      atomicMax(amax_bits + group, bits);
     }
   }
 };
@@ -94,9 +95,9 @@ __global__ void __launch_bounds__(256) head_rows_kernel(const uint4* in, const u
       }
       if (valid[p]) {
         const size_t row = base + p * kRowsPerPass + slot;
-        const uint4 y = scale8<MODE>(x[p], w, z[p], inv);
+        if (kAmax) tracker.enter_row(amax_bits, row, rows_per_amax_group);
+        const uint4 y = scale8<MODE, kAmax>(x[p], w, z[p], inv, &tracker.value);
         st_vec(out + row * LANES + lane, y);
-        if (kAmax) tracker.add(amax_bits, row, rows_per_amax_group, amax8(y));
       }
     }
   }
@@ -149,18 +150,17 @@ __global__ void __launch_bounds__(128) hidden_rows_kernel(const uint4* a, const 
   if (normalized_out == nullptr) return;
   const float total = block_sum<4>(partial, scratch);
   const float inv = inverse_rms(total, 1.0f / width, eps);
-  uint32_t top = 0;
+  float top_f = 0.0f;
 #pragma unroll
   for (int k = 0; k < VPT; ++k) {
     const int v = threadIdx.x + k * 128;
     if (v < row_vectors) {
-      const uint4 y = scale8<MODE>(x[k], ld_weight(weight + v), make_uint4(0, 0, 0, 0), inv);
+      const uint4 y = scale8<MODE, kAmax>(x[k], ld_weight(weight + v), make_uint4(0, 0, 0, 0), inv, &top_f);
       st_vec(normalized_out + row_base + v, y);
-      if (kAmax) top = max(top, amax8(y));
     }
   }
   if (kAmax) {
-    top = group_max_u32<32>(top);
+    uint32_t top = group_max_u32<32>(amax_bits_of(top_f));
     if ((threadIdx.x & 31) == 0) amax_scratch[threadIdx.x >> 5] = top;
     __syncthreads();
     if (threadIdx.x == 0) {
