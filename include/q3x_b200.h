@@ -169,6 +169,31 @@ int q3x_b200_rms_norm_silu_gate_nvfp4_single_pass(const uint16_t* in, const uint
                                                   uint32_t* scratch, float* global_scales_out,
                                                   uint8_t* codes, uint8_t* scales, void* stream);
 
+/* No counterpart in the reference.  q3x_b200_residual_add_rms_norm_nvfp4 for callers that cannot
+ * hand over scratch memory because they cannot allocate any: code that runs while a stream is being
+ * captured into a CUDA graph or inside a stream callback, a plugin whose host gives it the input
+ * and output tensors and nothing more, a service whose device allocator is closed once it is
+ * serving.  The scratch words are a fixed array inside the library (64 KB of device memory on
+ * every GPU that loads the library, held until the process exits), so there is no `scratch`
+ * argument; inputs and outputs are still the caller's.
+ *   - tokens must not exceed Q3X_B200_STATIC_SCRATCH_MAX_TOKENS (and the scale groups must fit the
+ *     same array, which they do for rows_per_scale = 0 or >= 2): larger calls return
+ *     cudaErrorInvalidValue before anything is enqueued.  q3x_b200_static_scratch_max_tokens()
+ *     returns the limit of the library actually loaded.
+ *   - The call allocates nothing and frees nothing.  The FIRST call on a device looks up the
+ *     array's device address (once per device, with that device current); make that first call
+ *     before any stream capture begins.
+ *   - All calls share the one array and it keeps the previous call's contents; each call clears
+ *     the words it uses, on `stream`, before its kernels.  Two calls that overlap on the GPU
+ *     (different streams, or graphs replayed concurrently) race on it: keep them ordered.
+ * Outputs are bit-identical to q3x_b200_residual_add_rms_norm_nvfp4 on the same inputs. */
+#define Q3X_B200_STATIC_SCRATCH_MAX_TOKENS 16384
+size_t q3x_b200_static_scratch_max_tokens(void);
+int q3x_b200_residual_add_rms_norm_nvfp4_static_scratch(
+    const uint16_t* left, const uint16_t* right, const uint16_t* weight, size_t tokens, size_t hidden,
+    float eps, size_t rows_per_scale, uint16_t* residual_out, uint16_t* normalized_out,
+    float* global_scales_out, uint8_t* codes, uint8_t* scales, void* stream);
+
 /* Diagnostics (no counterpart in the reference): the two narrow conversions the quantiser uses,
  * one value per output byte.  format 0 = E4M3 round-to-nearest-even with saturation at 448,
  * format 1 = E2M1 (code in the low nibble). */

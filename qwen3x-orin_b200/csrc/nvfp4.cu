@@ -449,6 +449,68 @@ extern "C" int q3x_b200_rms_norm_silu_gate_nvfp4_single_pass(const uint16_t* in,
                           global_scales_out, codes, scales, stream, true);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Residual add + RMSNorm + NVFP4 for callers that cannot allocate device memory.
+//
+// The regular entry point takes its scratch words from the caller.  Some callers have no way to
+// provide them: code running inside a CUDA-graph capture or a stream callback, a plugin that is
+// handed input and output tensors by its host and nothing else, a real-time loop whose allocator
+// is closed after start-up.  For them the scratch lives in the library itself, in the device array
+// below; every GPU that loads the library carries these 64 KB until the process exits.
+//
+// The array's name is only a host-side handle for the symbol, not a device address, so the device
+// address is looked up with cudaGetSymbolAddress, once per device and with that device current, and
+// it is that pointer the kernels receive.
+constexpr size_t kStaticScratchMaxTokens = Q3X_B200_STATIC_SCRATCH_MAX_TOKENS;
+constexpr size_t kStaticScratchWords = kStaticScratchMaxTokens + 2;  // fused_scratch_words(max, groups <= max / 2)
+static __device__ __align__(256) uint32_t g_static_scratch[kStaticScratchWords];
+
+namespace {
+
+// Device address of g_static_scratch on the current device, or nullptr with *status set.
+uint32_t* static_scratch_address(int* status) {
+  constexpr int kMaxDevices = 64;
+  static std::mutex mu;
+  static uint32_t* address[kMaxDevices] = {};
+  int dev = 0;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    *status = static_cast<int>(err != cudaSuccess ? err : cudaErrorInvalidDevice);
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lock(mu);
+  if (address[dev] == nullptr) {
+    void* p = nullptr;
+    err = cudaGetSymbolAddress(&p, g_static_scratch);
+    if (err != cudaSuccess || p == nullptr) {
+      *status = static_cast<int>(err != cudaSuccess ? err : cudaErrorInvalidSymbol);
+      return nullptr;
+    }
+    address[dev] = static_cast<uint32_t*>(p);
+  }
+  *status = kOk;
+  return address[dev];
+}
+
+}  // namespace
+
+extern "C" size_t q3x_b200_static_scratch_max_tokens(void) { return kStaticScratchMaxTokens; }
+
+extern "C" int q3x_b200_residual_add_rms_norm_nvfp4_static_scratch(
+    const uint16_t* left, const uint16_t* right, const uint16_t* weight, size_t tokens, size_t hidden, float eps,
+    size_t rows_per_scale, uint16_t* residual_out, uint16_t* normalized_out, float* global_scales_out, uint8_t* codes,
+    uint8_t* scales, void* stream) {
+  // more rows than the built-in scratch has words for: refuse before touching anything
+  if (tokens > kStaticScratchMaxTokens) return kInvalid;
+  if (fused_scratch_words(tokens, group_count(tokens, rows_per_scale)) > kStaticScratchWords) return kInvalid;
+  int status = kOk;
+  uint32_t* scratch = static_scratch_address(&status);
+  if (scratch == nullptr) return status;
+  // from here on this is the regular two-kernel path; it clears the scratch words it uses itself
+  return residual_norm_nvfp4(left, right, weight, tokens, hidden, eps, rows_per_scale, residual_out, normalized_out,
+                             scratch, global_scales_out, codes, scales, stream, false);
+}
+
 // Diagnostics: the two narrow conversions on their own, so that tests can sweep them against the
 // CPU definition.  format 0 = E4M3 (one byte per value), 1 = E2M1 (one nibble per value, in a byte).
 extern "C" int q3x_b200_debug_encode(const float* in, size_t count, int format, uint8_t* out, void* stream) {
