@@ -61,6 +61,11 @@ int q3x_b200_embedding_gather(const uint16_t* table, size_t vocab, size_t hidden
                               const uint32_t* token_ids, size_t token_count, uint16_t* out,
                               void* stream);
 
+/* launch_embedding_gather_reference_cuda (decode_ops.h:178-181): the single-token decode form with
+ * the id passed by value; an id >= vocab is rejected on the host (cudaErrorInvalidValue). */
+int q3x_b200_embedding_gather_one(const uint16_t* table, size_t vocab, size_t hidden,
+                                  size_t token_id, uint16_t* out, void* stream);
+
 /* ---------------------------------------------------------------- RMS norms */
 
 /* launch_centered_rms_norm_reference_cuda / launch_plain_rms_norm_reference_cuda (rows = 1)

@@ -24,6 +24,7 @@ SIGNATURES = {
     "q3x_b200_abi_version": (_i, []),
     "q3x_b200_error_string": (C.c_char_p, [_i]),
     "q3x_b200_embedding_gather": (_i, [_p, _z, _z, _p, _z, _p, _p]),
+    "q3x_b200_embedding_gather_one": (_i, [_p, _z, _z, _z, _p, _p]),
     "q3x_b200_rms_norm": (_i, [_p, _p, _z, _z, _f, _i, _p, _p]),
     "q3x_b200_rms_norm_silu_gate": (_i, [_p, _p, _p, _z, _z, _f, _p, _p]),
     "q3x_b200_l2_normalize_heads": (_i, [_p, _z, _z, _f, _f, _p, _p]),

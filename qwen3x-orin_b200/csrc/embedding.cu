@@ -18,9 +18,10 @@ template <int VPT>
 __global__ void __launch_bounds__(kThreads) embedding_rows_kernel(const uint4* __restrict__ table, size_t vocab,
                                                                   int row_vectors,
                                                                   const uint32_t* __restrict__ token_ids,
-                                                                  uint4* __restrict__ out) {
+                                                                  size_t single_id, uint4* __restrict__ out) {
   const size_t token = blockIdx.x;
-  const size_t id = __ldg(token_ids + token);
+  // token_ids == nullptr: one row whose id was passed by value (the single-token decode form)
+  const size_t id = token_ids != nullptr ? static_cast<size_t>(__ldg(token_ids + token)) : single_id;
   if (id >= vocab) return;
   const uint4* src = table + id * static_cast<size_t>(row_vectors);
   uint4* dst = out + token * static_cast<size_t>(row_vectors);
@@ -41,9 +42,9 @@ __global__ void __launch_bounds__(kThreads) embedding_rows_kernel(const uint4* _
 
 __global__ void __launch_bounds__(kThreads) embedding_rows_scalar_kernel(const uint16_t* table, size_t vocab,
                                                                          size_t hidden, const uint32_t* token_ids,
-                                                                         uint16_t* out) {
+                                                                         size_t single_id, uint16_t* out) {
   const size_t token = blockIdx.x;
-  const size_t id = token_ids[token];
+  const size_t id = token_ids != nullptr ? static_cast<size_t>(token_ids[token]) : single_id;
   if (id >= vocab) return;
   for (size_t i = threadIdx.x; i < hidden; i += kThreads) out[token * hidden + i] = table[id * hidden + i];
 }
@@ -53,6 +54,30 @@ __global__ void __launch_bounds__(kThreads) embedding_rows_scalar_kernel(const u
 
 using namespace q3x;
 using namespace q3x::host;
+
+namespace {
+
+// token_ids == nullptr selects the by-value form (token_count must then be 1).
+int launch_embedding(const uint16_t* table, size_t vocab, size_t hidden, const uint32_t* token_ids, size_t single_id,
+                     size_t token_count, uint16_t* out, void* stream) {
+  cudaStream_t s = as_stream(stream);
+  const unsigned grid = static_cast<unsigned>(token_count);
+  clear_stale_error();
+  if (hidden % 8 == 0 && hidden / 8 <= 0x7fffffffu && aligned16(table) && aligned16(out)) {
+    const int row_vectors = static_cast<int>(hidden / 8);
+    auto T = reinterpret_cast<const uint4*>(table);
+    auto O = reinterpret_cast<uint4*>(out);
+    if (row_vectors > 3 * kThreads)
+      embedding_rows_kernel<5><<<grid, kThreads, 0, s>>>(T, vocab, row_vectors, token_ids, single_id, O);
+    else
+      embedding_rows_kernel<2><<<grid, kThreads, 0, s>>>(T, vocab, row_vectors, token_ids, single_id, O);
+  } else {
+    embedding_rows_scalar_kernel<<<grid, kThreads, 0, s>>>(table, vocab, hidden, token_ids, single_id, out);
+  }
+  return launch_status();
+}
+
+}  // namespace
 
 extern "C" int q3x_b200_embedding_gather(const uint16_t* table, size_t vocab, size_t hidden,
                                          const uint32_t* token_ids, size_t token_count, uint16_t* out,
@@ -66,19 +91,16 @@ extern "C" int q3x_b200_embedding_gather(const uint16_t* table, size_t vocab, si
   const Span st = span(table, vocab * hidden * 2), si = span(token_ids, token_count * 4),
              so = span(out, token_count * hidden * 2);
   if (wraps(st) || wraps(si) || wraps(so) || overlap(st, si) || overlap(st, so) || overlap(si, so)) return kInvalid;
-  cudaStream_t s = as_stream(stream);
-  const unsigned grid = static_cast<unsigned>(token_count);
-  clear_stale_error();
-  if (hidden % 8 == 0 && hidden / 8 <= 0x7fffffffu && aligned16(table) && aligned16(out)) {
-    const int row_vectors = static_cast<int>(hidden / 8);
-    auto T = reinterpret_cast<const uint4*>(table);
-    auto O = reinterpret_cast<uint4*>(out);
-    if (row_vectors > 3 * kThreads)
-      embedding_rows_kernel<5><<<grid, kThreads, 0, s>>>(T, vocab, row_vectors, token_ids, O);
-    else
-      embedding_rows_kernel<2><<<grid, kThreads, 0, s>>>(T, vocab, row_vectors, token_ids, O);
-  } else {
-    embedding_rows_scalar_kernel<<<grid, kThreads, 0, s>>>(table, vocab, hidden, token_ids, out);
-  }
-  return launch_status();
+  return launch_embedding(table, vocab, hidden, token_ids, 0, token_count, out, stream);
+}
+
+extern "C" int q3x_b200_embedding_gather_one(const uint16_t* table, size_t vocab, size_t hidden, size_t token_id,
+                                             uint16_t* out, void* stream) {
+  if (mul3_overflows(vocab, hidden, sizeof(uint16_t))) return kInvalid;
+  if (token_id >= vocab) return kInvalid;  // the host knows the id here, so it is checked here
+  if (hidden == 0) return kOk;
+  if (table == nullptr || out == nullptr) return kInvalid;
+  const Span st = span(table, vocab * hidden * 2), so = span(out, hidden * 2);
+  if (wraps(st) || wraps(so) || overlap(st, so)) return kInvalid;
+  return launch_embedding(table, vocab, hidden, nullptr, token_id, 1, out, stream);
 }

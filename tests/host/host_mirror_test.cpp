@@ -1,0 +1,176 @@
+// Host-side checks of the C++ mirror (no GPU needed: every call below must be answered by the
+// argument checks before any device work).  Mirrors the style of the reference's own plain test
+// executables: counts failures, prints them, returns non-zero when any check failed.
+#include <cstdint>
+#include <cstdio>
+
+#include "q3x_b200_ops.hpp"
+
+namespace rt = q3x::runtime;
+
+static int failures = 0;
+#define EXPECT(cond)                                                  \
+  do {                                                                \
+    if (!(cond)) {                                                    \
+      ++failures;                                                     \
+      std::printf("FAIL %s:%d: %s\n", __FILE__, __LINE__, #cond);     \
+    }                                                                 \
+  } while (0)
+
+static void test_launcher_limits() {
+  auto* p = reinterpret_cast<std::uint16_t*>(0x100000);  // never dereferenced on these paths
+  auto* f = reinterpret_cast<float*>(0x900000);
+  constexpr int kInvalid = 1;
+  // M32 entry admits exactly 32 tokens; the prefill entry 1..512 tokens of width 5120
+  EXPECT(rt::launch_residual_add_headwise_centered_rms_norm_m32_5120_cuda(p, p + 0x100000, p + 0x200000, 31, 5120, 1e-6F,
+                                                                        p + 0x300000, p + 0x400000) == kInvalid);
+  EXPECT(rt::launch_residual_add_headwise_centered_rms_norm_prefill_5120_cuda(p, p + 0x100000, p + 0x200000, 513, 5120,
+                                                                            1e-6F, p + 0x300000,
+                                                                            p + 0x400000) == kInvalid);
+  EXPECT(rt::launch_residual_add_headwise_centered_rms_norm_prefill_5120_cuda(p, p + 0x100000, p + 0x200000, 0, 5120,
+                                                                            1e-6F, p + 0x300000,
+                                                                            p + 0x400000) == kInvalid);
+  EXPECT(rt::launch_residual_add_headwise_centered_rms_norm_prefill_5120_cuda(p, p + 0x100000, p + 0x200000, 8, 4096,
+                                                                            1e-6F, p + 0x300000,
+                                                                            p + 0x400000) == kInvalid);
+  EXPECT(rt::launch_qk_partial_neox_rope_tile_24_4_256_64_cuda(p, p + 0x100000, f, f + 0x1000, 0, 17) == kInvalid);
+  EXPECT(rt::launch_qk_partial_neox_rope_tile_24_4_256_64_cuda(p, p + 0x100000, f, f + 0x1000, 0, 0) == kInvalid);
+  EXPECT(rt::launch_full_attention_preprocess_24_4_256_64_cuda(p, p + 0x100000, p + 0x200000, p + 0x210000, 1e-6F,
+                                                               p + 0x300000, p + 0x800000, f, f + 0x100000, 0,
+                                                               513) == kInvalid);
+  EXPECT(rt::launch_full_attention_preprocess_24_4_256_64_prompt_wide_p8000_cuda(
+             p, p + 0x100000, p + 0x200000, p + 0x210000, 1e-6F, p + 0x300000, p + 0x800000, f, f + 0x100000, 4000,
+             8000) == kInvalid);
+  EXPECT(rt::can_launch_full_attention_preprocess_prompt_wide_p8000(32000, 8000));
+  EXPECT(!rt::can_launch_full_attention_preprocess_prompt_wide_p8000(40000, 8000));
+  rt::GdnDimensions wrong;
+  wrong.value_head_count = 32;
+  EXPECT(rt::launch_causal_conv1d_silu_update_reference_cuda(p, p + 0x100000, p + 0x200000, p + 0x300000, wrong) ==
+         kInvalid);
+  EXPECT(rt::launch_causal_conv1d_silu_update_tile_reference_cuda(p, 17, p + 0x100000, p + 0x200000, p + 0x300000) ==
+         kInvalid);
+  namespace conv = rt::gdn_prefill_whole_span_conv_detail;
+  EXPECT(conv::launch_causal_conv1d_silu_update_whole_span_exact_cuda(p, 513, p + 0x1000000, p + 0x2000000,
+                                                                      p + 0x3000000) == kInvalid);
+  EXPECT(conv::launch_causal_conv1d_silu_update_token_parallel_exact_cuda(p, 8, p + 0x1000000, p + 0x2000000, p) ==
+         kInvalid);  // this form needs a disjoint output
+  // empty shapes are successful no-ops even with null pointers; a bad epsilon is not
+  EXPECT(rt::launch_residual_add_reference_cuda(nullptr, nullptr, 0, nullptr) == 0);
+  EXPECT(rt::launch_silu_mul_reference_cuda(nullptr, nullptr, 0, nullptr) == 0);
+  EXPECT(rt::launch_centered_rms_norm_reference_cuda(nullptr, nullptr, 0, 1e-6F, nullptr) == 0);
+  EXPECT(rt::launch_centered_rms_norm_reference_cuda(p, p + 0x1000, 8, 0.0F, p + 0x2000) == kInvalid);
+  EXPECT(rt::launch_embedding_gather_reference_cuda(p, 100, 8, 100, p + 0x100000) == kInvalid);  // id out of range
+  EXPECT(rt::launch_embedding_gather_prompt_reference_cuda(p, 100, 8, nullptr, 0, p + 0x100000) == kInvalid);
+}
+
+static void test_dispatch() {
+  using B = rt::ProjectionBackend;
+  auto* p = reinterpret_cast<std::uint16_t*>(0x100000);
+  EXPECT(rt::is_valid_projection_backend(B::kReference) && rt::is_valid_projection_backend(B::kSm87WeightOnly) &&
+         rt::is_valid_projection_backend(B::kB200LayerOps) && !rt::is_valid_projection_backend(static_cast<B>(7)));
+  EXPECT(static_cast<int>(B::kReference) == 0 && static_cast<int>(B::kSm87WeightOnly) == 1);
+  // other backends are told "not supported" so the caller falls back; junk is invalid
+  EXPECT(rt::launch_mlp_gate_up_silu_epilogue_cuda(B::kReference, p, p + 0x100000, 1, 17408) == 801);
+  EXPECT(rt::launch_mlp_gate_up_silu_epilogue_cuda(B::kSm87WeightOnly, p, p + 0x100000, 1, 17408) == 801);
+  EXPECT(rt::launch_mlp_gate_up_silu_epilogue_cuda(static_cast<B>(9), p, p + 0x100000, 1, 17408) == 1);
+  EXPECT(rt::launch_mlp_gate_up_silu_epilogue_cuda(B::kB200LayerOps, nullptr, nullptr, 0, 17408) == 0);
+  EXPECT(rt::launch_post_attention_residual_norm_prologue_cuda(B::kB200LayerOps, p, p + 0x100000, p + 0x200000, 1e-6F,
+                                                               1, 4096, p + 0x300000) == 1);
+  EXPECT(rt::launch_mlp_down_residual_norm_epilogue_cuda(B::kB200LayerOps, p, p + 0x100000, p + 0x200000, 1e-6F, 1,
+                                                         5120, p + 0x300000, nullptr) == 1);
+  EXPECT(rt::launch_mlp_down_residual_norm_epilogue_cuda(B::kB200LayerOps, p, p + 0x100000, p + 0x200000, 1e-6F, 1,
+                                                         5120, p + 0x300000, p) == 1);  // normalized == raw down
+}
+
+static void test_bindings() {
+  using Issue = rt::PrefillOperatorBindingIssue;
+  auto has = [](const rt::PrefillOperatorBindingValidation& v, Issue i) {
+    return rt::has_prefill_operator_binding_issue(v, i);
+  };
+  const auto design = rt::make_unbound_layer_major_c8192_operator_bindings();
+  EXPECT(design.binding_count == 17);
+  auto v = rt::validate_layer_major_c8192_operator_bindings(design);
+  EXPECT(v.role_coverage_complete && v.logical_capacity_complete && v.exact_numerics_complete &&
+         v.native_provider_complete && v.forbidden_boundaries_satisfied);
+  EXPECT(!v.aot_tactics_complete && !v.launcher_bindings_complete && !v.attestation_complete && !v.complete() &&
+         !v.executable());
+  EXPECT(has(v, Issue::kTacticIdentityUnbound) && has(v, Issue::kLauncherBindingIncomplete) &&
+         has(v, Issue::kC8192AttestationUnbound) && !has(v, Issue::kMissingRole));
+
+  const auto legacy = rt::make_legacy_c512_prefill_launcher_inventory();
+  v = rt::validate_layer_major_c8192_operator_bindings(legacy);
+  EXPECT(has(v, Issue::kInsufficientLogicalPanelCapacity) && has(v, Issue::kLegacyC512InventoryOnly) &&
+         !v.logical_capacity_complete);
+
+  // a fully bound, authenticated set validates (and is still not executable)
+  auto full = design;
+  std::uint64_t next = 100;
+  for (auto& b : full.bindings) {
+    const auto need = rt::prefill_operator_role_requirements(b.role);
+    b.tactic.identity = next++;
+    auto bind = [&](rt::PrefillResourceBinding& r, bool required) {
+      if (required) r = {rt::PrefillResourceBindingState::kBound, next++};
+    };
+    bind(b.weight, need.weight);
+    bind(b.sidecar, need.sidecar);
+    bind(b.workspace, need.workspace);
+    bind(b.launcher, need.launcher);
+    bind(b.completion_event, need.completion_event);
+    b.attestation = rt::PrefillBindingAttestation::kAuthenticatedC8192;
+  }
+  v = rt::validate_layer_major_c8192_operator_bindings(full);
+  EXPECT(v.issue_mask == 0 && v.complete() && !v.executable());
+
+  auto broken = full;
+  broken.bindings[1].tactic.identity = broken.bindings[0].tactic.identity;  // gate/up and down share a tactic
+  EXPECT(has(rt::validate_layer_major_c8192_operator_bindings(broken), Issue::kGateDownTacticAlias));
+  broken = full;
+  broken.bindings[3].role = rt::PrefillBindingRole::kLinearFp8Qkv;  // duplicate + missing
+  v = rt::validate_layer_major_c8192_operator_bindings(broken);
+  EXPECT(has(v, Issue::kDuplicateRole) && has(v, Issue::kMissingRole) && !v.role_coverage_complete && !v.complete());
+  broken = full;
+  broken.bindings[5].provider = rt::PrefillOperatorProvider::kCuBlasLtReference;
+  broken.bindings[6].numerical_mode = rt::PrefillNumericalMode::kApproximate;
+  broken.bindings[7].uses_mtp = true;
+  broken.bindings[8].weight = {rt::PrefillResourceBindingState::kUnbound, 5};  // identity without a binding
+  broken.bindings[9].role = static_cast<rt::PrefillBindingRole>(40);
+  v = rt::validate_layer_major_c8192_operator_bindings(broken);
+  EXPECT(has(v, Issue::kCuBlasLtForbidden) && has(v, Issue::kNonNativeProvider) &&
+         has(v, Issue::kApproximateNumericsForbidden) && has(v, Issue::kMtpForbidden) &&
+         has(v, Issue::kMalformedBindingIdentity) && has(v, Issue::kWeightBindingIncomplete) &&
+         has(v, Issue::kInvalidRole) && !v.forbidden_boundaries_satisfied);
+  broken = full;
+  broken.binding_count = 18;
+  EXPECT(has(rt::validate_layer_major_c8192_operator_bindings(broken), Issue::kInvalidRole));
+
+  // requirements table (prefill_operator_bindings.cpp:107-146)
+  auto need = rt::prefill_operator_role_requirements(rt::PrefillBindingRole::kResidual);
+  EXPECT(!need.weight && !need.sidecar && need.workspace && need.launcher && need.completion_event);
+  need = rt::prefill_operator_role_requirements(rt::PrefillBindingRole::kNvfp4Down);
+  EXPECT(need.weight && need.sidecar && need.workspace);
+  need = rt::prefill_operator_role_requirements(rt::PrefillBindingRole::kFinalHandoff);
+  EXPECT(!need.weight && !need.workspace && need.launcher);
+  need = rt::prefill_operator_role_requirements(rt::PrefillBindingRole::kInvalid);
+  EXPECT(!need.launcher && !need.completion_event);
+
+  // this library's contribution: three roles get launcher + tactic identities, nothing else
+  const auto ours = rt::make_b200_layer_op_bindings();
+  int bound = 0;
+  for (const auto& b : ours.bindings) {
+    const bool mine = b.role == rt::PrefillBindingRole::kResidual || b.role == rt::PrefillBindingRole::kNormalization ||
+                      b.role == rt::PrefillBindingRole::kEmbedding;
+    EXPECT(b.launcher.bound() == mine && b.tactic.aot_bound() == mine);
+    bound += b.launcher.bound() ? 1 : 0;
+  }
+  EXPECT(bound == 3);
+  v = rt::validate_layer_major_c8192_operator_bindings(ours);
+  EXPECT(!has(v, Issue::kMalformedBindingIdentity) && !v.complete() && has(v, Issue::kC8192AttestationUnbound));
+}
+
+int main() {
+  test_launcher_limits();
+  test_dispatch();
+  test_bindings();
+  if (failures == 0) std::printf("host mirror tests passed\n");
+  return failures == 0 ? 0 : 1;
+}

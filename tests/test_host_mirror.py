@@ -1,0 +1,46 @@
+"""The C++17 mirror of the reference operator API (qwen3x-orin_b200/host): builds, keeps the
+reference's argument limits and dispatch / binding rules (all host-side, no GPU needed), and -- where a
+reference checkout exists -- defines exactly the symbols the reference's own headers declare."""
+import importlib
+import os
+import subprocess
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+PKG = os.path.join(ROOT, "qwen3x-orin_b200")
+HOST = os.path.join(PKG, "host")
+REFERENCE = "/root/reference"
+
+
+@pytest.fixture(scope="module")
+def host_lib():
+    build = importlib.import_module("qwen3x-orin_b200.build")
+    build.build_all()
+    assert os.path.exists(build.HOST_LIB)
+    return build.HOST_LIB
+
+
+def compile_and_run(tmp_path, source, includes):
+    exe = str(tmp_path / "t")
+    cmd = ["g++", "-std=c++17", "-O1", "-Wall", "-Wextra", "-Werror", source, "-o", exe]
+    for inc in includes:
+        cmd += ["-I", inc]
+    cmd += ["-L", PKG, "-lq3x_b200_host", "-lq3x_b200", f"-Wl,-rpath,{PKG}", "-Wl,--no-undefined"]
+    subprocess.run(cmd, check=True, capture_output=True, text=True)
+    return subprocess.run([exe], capture_output=True, text=True)
+
+
+def test_mirror_argument_limits_dispatch_and_bindings(host_lib, tmp_path):
+    out = compile_and_run(tmp_path, os.path.join(ROOT, "tests", "host", "host_mirror_test.cpp"),
+                          [HOST, os.path.join(ROOT, "include")])
+    assert out.returncode == 0, out.stdout + out.stderr
+    assert "host mirror tests passed" in out.stdout
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REFERENCE, "include", "q3x")), reason="no reference checkout")
+def test_mirror_defines_the_reference_symbols(host_lib, tmp_path):
+    out = compile_and_run(tmp_path, os.path.join(ROOT, "tests", "host", "reference_symbols.cpp"),
+                          [os.path.join(REFERENCE, "include")])
+    assert out.returncode == 0, out.stdout + out.stderr
+    assert "23 reference launcher symbols resolved" in out.stdout
