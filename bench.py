@@ -349,7 +349,19 @@ def main():
     torch.cuda.set_device(local_rank)
     distributed = world > 1
     if distributed:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        # NCCL only carries the barrier and the max-over-ranks of the timings; keep its banner
+        # ("NCCL version ...") off stdout, which must hold exactly one JSON line
+        os.environ["NCCL_DEBUG"] = os.environ.get("Q3X_NCCL_DEBUG", "WARN")
+        sys.stdout.flush()
+        saved_stdout = os.dup(1)
+        os.dup2(2, 1)  # whatever the communicator set-up prints goes to stderr
+        try:
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+            dist.barrier()
+            torch.cuda.synchronize()
+        finally:
+            os.dup2(saved_stdout, 1)
+            os.close(saved_stdout)
 
     T = args.tokens
     stack = chain.LayerStack(T, first_position=rank * T, seed=1234 + rank)
