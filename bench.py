@@ -443,39 +443,83 @@ def main():
     # ---- end to end: host buffers, H2D of the step's inputs and D2H of its result inside the timing --
     e2e = None
     if not args.no_e2e:
+        # Two device input sets, each baked into its own graph: while step i computes on set i % 2,
+        # the copy engine brings step i + 1's inputs from pinned host memory into the other set and
+        # takes step i - 1's result back.  Every step's inputs and result cross PCIe inside the timing.
         names = list(stack.inputs)
         host_in = {n: torch.empty(stack.inputs[n].shape, dtype=torch.bfloat16, pin_memory=True) for n in names}
         for n in names:
             host_in[n].copy_(stack.inputs[n])
         host_ids = torch.empty(stack.token_ids.shape, dtype=torch.int32, pin_memory=True)
         host_ids.copy_(stack.token_ids)
-        host_out = torch.empty((T, 5120), dtype=torch.bfloat16, pin_memory=True)
+        host_out = [torch.empty((T, 5120), dtype=torch.bfloat16, pin_memory=True) for _ in range(2)]
+        staged_out = [torch.empty((T, 5120), dtype=torch.bfloat16, device="cuda") for _ in range(2)]
         h2d = sum(v.numel() * 2 for v in host_in.values()) + host_ids.numel() * 4
-        d2h = host_out.numel() * 2
+        d2h = host_out[0].numel() * 2
+        stack.add_input_set()
+        graphs = [graph, None]
+        if graph is not None:
+            try:
+                stack.active = 1
+                graphs[1] = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graphs[1], stream=stream_obj):
+                    stack.enqueue_step(torch.cuda.current_stream().cuda_stream)
+            except Exception as exc:
+                print(f"[bench] second graph capture failed ({exc}); e2e launches eagerly", file=sys.stderr)
+                graphs = [None, None]
+                torch.cuda.synchronize()
+            stack.active = 0
+        h2d_stream, d2h_stream = torch.cuda.Stream(), torch.cuda.Stream()
+        filled = [torch.cuda.Event() for _ in range(2)]
+        consumed = [torch.cuda.Event() for _ in range(2)]
+        staged = [torch.cuda.Event() for _ in range(2)]
+        drained = [torch.cuda.Event() for _ in range(2)]
 
-        def e2e_step():
-            for n in names:
-                stack.inputs[n].copy_(host_in[n], non_blocking=True)
-            stack.token_ids.copy_(host_ids, non_blocking=True)
-            one_step()
-            host_out.copy_(stack.residual[final_idx], non_blocking=True)
+        def e2e_steps(count):
+            for i in range(count):
+                s = i % 2
+                with torch.cuda.stream(h2d_stream):
+                    if i >= 2:
+                        h2d_stream.wait_event(consumed[s])      # step i - 2 no longer reads this set
+                    for n in names:
+                        stack.input_sets[s][n].copy_(host_in[n], non_blocking=True)
+                    stack.id_sets[s].copy_(host_ids, non_blocking=True)
+                    filled[s].record(h2d_stream)
+                with torch.cuda.stream(stream_obj):
+                    stream_obj.wait_event(filled[s])
+                    if graphs[s] is not None:
+                        graphs[s].replay()
+                    else:
+                        stack.active = s
+                        stack.enqueue_step(stream)
+                        stack.active = 0
+                    consumed[s].record(stream_obj)
+                    if i >= 2:
+                        stream_obj.wait_event(drained[s])       # the host copy of step i - 2's result is done
+                    staged_out[s].copy_(stack.residual[final_idx], non_blocking=True)
+                    staged[s].record(stream_obj)
+                with torch.cuda.stream(d2h_stream):
+                    d2h_stream.wait_event(staged[s])
+                    host_out[s].copy_(staged_out[s], non_blocking=True)
+                    drained[s].record(d2h_stream)
 
-        with torch.cuda.stream(stream_obj):
-            e2e_step()
+        e2e_steps(2)
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        with torch.cuda.stream(stream_obj):
-            e0.record(stream_obj)
-            for _ in range(args.steps):
-                e2e_step()
-            e1.record(stream_obj)
+        e0.record(h2d_stream)
+        e2e_steps(args.steps)
+        d2h_stream.wait_stream(stream_obj)
+        d2h_stream.wait_stream(h2d_stream)
+        e1.record(d2h_stream)
         barrier()
         t = torch.tensor([e0.elapsed_time(e1)], device="cuda", dtype=torch.float64)
         if distributed:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_ms = float(t.item()) / args.steps
         e2e = {"value": T * world / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-               "ms_per_step": e2e_ms, "note": "per step: pinned-host inputs -> device, 64-layer chain, final residual -> host"}
+               "ms_per_step": e2e_ms,
+               "note": "per step: pinned-host inputs -> device, 64-layer chain, final residual -> pinned host; the "
+                       "copies of neighbouring steps overlap the chain (two device input sets)"}
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:

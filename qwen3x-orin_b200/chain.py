@@ -104,9 +104,12 @@ class LayerStack:
             return (torch.randn(shape, generator=gen, device=dev, dtype=torch.float32) * std).to(torch.bfloat16)
 
         T = tokens
-        self.inputs = {n: normal((T, w)) for n, w in zip(ShardInputs.names, ShardInputs.widths)}
+        # input sets: the step reads the active one; a second set lets the next step's host->device
+        # copies overlap the current step (each set is baked into its own CUDA graph)
+        self.input_sets = [{n: normal((T, w)) for n, w in zip(ShardInputs.names, ShardInputs.widths)}]
+        self.active = 0
         self.table = normal((table_rows, HIDDEN), 0.02)
-        self.token_ids = torch.randint(0, table_rows, (T,), generator=gen, device=dev, dtype=torch.int64).to(torch.int32)
+        self.id_sets = [torch.randint(0, table_rows, (T,), generator=gen, device=dev, dtype=torch.int64).to(torch.int32)]
         # weights: distinct per layer, all tiny
         self.norm_w = normal((layers, 2, HIDDEN), 0.02)
         self.q_norm_w = normal((layers, HEAD_DIM), 0.02)
@@ -134,6 +137,20 @@ class LayerStack:
         self.gdn_codes = torch.empty((T, GDN_V // 2), device=dev, dtype=torch.uint8)
         self.gdn_scales = torch.empty((T, GDN_V // 16), device=dev, dtype=torch.uint8)
         self.q_scale = 1.0 / math.sqrt(128.0)
+
+    @property
+    def inputs(self):
+        return self.input_sets[self.active]
+
+    @property
+    def token_ids(self):
+        return self.id_sets[self.active]
+
+    def add_input_set(self) -> int:
+        """Clones input set 0 into a new device-resident set and returns its index."""
+        self.input_sets.append({n: t.clone() for n, t in self.input_sets[0].items()})
+        self.id_sets.append(self.id_sets[0].clone())
+        return len(self.input_sets) - 1
 
     # ---- individual operators (each is one C-ABI call) ------------------------------------
     def op_embedding(self, stream):

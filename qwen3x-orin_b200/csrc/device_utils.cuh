@@ -144,13 +144,17 @@ __device__ __forceinline__ float stable_sigmoid(float g) {
 // silu(g) = g / (1 + exp(-g)) (decode_ops.cpp:315-316).
 // It is evaluated in exactly that shape, g * (1 / (1 + exp(-g))), with the two fast units: for
 // g < -88.72 exp(-g) overflows to +inf, the reciprocal is 0 and the product is -0, just as in the
-// host op; for large positive g the exponential vanishes and the result is g.  The reciprocal keeps
-// subnormal results (g in (-88.7, -87.3) needs them), the exponential may flush (1 + tiny == 1).
+// host op; for large positive g the exponential vanishes and the result is g.  The exponential may
+// flush (1 + tiny == 1), but 1 / (1 + exp(-g)) is subnormal for g in (-88.7, -87.3) and must not be.
+// The denominator is carried scaled by 2^-24 so that the single-instruction (flushing) reciprocal never
+// sees or produces a subnormal; the scale is folded back into the reciprocal before it meets g, in a
+// multiply that keeps subnormals.  Six instructions, none on the integer/logic pipe.
 __device__ __forceinline__ float silu(float g) {
+  constexpr float kScale = 5.9604644775390625e-08f;  // 2^-24
   float e, r;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(g * -1.4426950408889634f));
-  asm("rcp.approx.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
-  return g * r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(fmaf(e, kScale, kScale)));  // 1 / ((1 + e) * 2^-24)
+  return g * (r * kScale);
 }
 
 // ---------------------------------------------------------------------------- bf16 amax

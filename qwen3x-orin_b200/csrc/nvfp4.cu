@@ -78,8 +78,10 @@ __global__ void amax_to_scale_kernel(const uint32_t* amax_bits, size_t groups, f
 // ---- quantiser --------------------------------------------------------------------------
 
 // One CTA per row (grid-stride over rows).  kWideScales: the row's scale bytes are a multiple of 16
-// and 16-byte aligned, so they go out as 128-bit stores from shared memory.
-template <bool kWideScales>
+// and 16-byte aligned, so they go out as 128-bit stores from shared memory.  VPT > 0: the row has at
+// most VPT * 128 vectors and a thread issues all of its loads before anything else (they are in flight
+// while the scale table is built); VPT == 0: rows of any length, streamed two vectors at a time.
+template <bool kWideScales, int VPT>
 __global__ void __launch_bounds__(kRowThreads) nvfp4_quantize_rows_kernel(const uint4* __restrict__ in, size_t rows,
                                                                           int row_vectors, size_t rows_per_scale,
                                                                           const float* __restrict__ global_scales,
@@ -90,8 +92,20 @@ __global__ void __launch_bounds__(kRowThreads) nvfp4_quantize_rows_kernel(const 
   __shared__ __align__(16) uint8_t scale_bytes[kWideScales ? kMaxRowScaleBytes : 16];
   __shared__ float inv_table[kRowThreads];  // indexed by E4M3 code 0..127
   static_assert(kRowThreads == 128, "one thread per non-negative E4M3 code");
+  constexpr int kSteps = VPT > 0 ? VPT : 2;
   const int tid = threadIdx.x;
   for (size_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const uint4* src = in + row * static_cast<size_t>(row_vectors);
+    uint32_t* dst = codes + row * static_cast<size_t>(row_vectors);
+    uint8_t* srow = scales + row * static_cast<size_t>(row_vectors / 2);
+    uint4 x[kSteps];
+    if (VPT > 0) {
+#pragma unroll
+      for (int u = 0; u < kSteps; ++u) {
+        const int v = u * kRowThreads + tid;
+        x[u] = v < row_vectors ? ld_stream(src + v) : make_uint4(0, 0, 0, 0);
+      }
+    }
     const size_t group = rows_per_scale ? row / rows_per_scale : 0;
     float global;
     if (amax_bits != nullptr) {
@@ -106,28 +120,25 @@ __global__ void __launch_bounds__(kRowThreads) nvfp4_quantize_rows_kernel(const 
     __syncthreads();  // the previous row's readers of inv_table / scale_bytes are done
     inv_table[tid] = block_inverse(static_cast<uint32_t>(tid), global);
     __syncthreads();
-    const uint4* src = in + row * static_cast<size_t>(row_vectors);
-    uint32_t* dst = codes + row * static_cast<size_t>(row_vectors);
-    uint8_t* srow = scales + row * static_cast<size_t>(row_vectors / 2);
-    // the bound is the same for all lanes of a warp, so the pair shuffle always has its partner
-    for (int base = 0; base < row_vectors; base += 2 * kRowThreads) {
-      uint4 x[2];
-      bool valid[2];
+    // the loop bound is the same for all lanes of a warp, so the pair shuffle always has its partner
+    for (int base = 0; base < row_vectors; base += kSteps * kRowThreads) {
+      if (VPT == 0) {
 #pragma unroll
-      for (int u = 0; u < 2; ++u) {
-        const int v = base + u * kRowThreads + tid;
-        valid[u] = v < row_vectors;  // lane pairs are valid together (row_vectors is even)
-        x[u] = valid[u] ? ld_stream(src + v) : make_uint4(0, 0, 0, 0);
+        for (int u = 0; u < kSteps; ++u) {
+          const int v = base + u * kRowThreads + tid;
+          x[u] = v < row_vectors ? ld_stream(src + v) : make_uint4(0, 0, 0, 0);
+        }
       }
 #pragma unroll
-      for (int u = 0; u < 2; ++u) {
+      for (int u = 0; u < kSteps; ++u) {
         const int v = base + u * kRowThreads + tid;
+        const bool valid = v < row_vectors;  // lane pairs are valid together (row_vectors is even)
         float f[8];
         unpack8(x[u], f);
         float m = amax8_float(f, x[u]);
         m = fmaxf(m, __shfl_xor_sync(kFullMask, m, 1));
         const uint32_t s = block_scale_code(m, k);
-        if (valid[u]) {
+        if (valid) {
           dst[v] = quantize8(f, inv_table[s]);
           if ((tid & 1) == 0) {
             if (kWideScales) scale_bytes[v >> 1] = static_cast<uint8_t>(s);
@@ -244,16 +255,25 @@ void enqueue_quantize(const uint16_t* in, size_t rows, size_t cols, size_t rows_
     const bool wide = aligned16(scales) && (cols / 16) % 16 == 0 && cols / 16 <= kMaxRowScaleBytes;
     auto I = reinterpret_cast<const uint4*>(in);
     auto C = reinterpret_cast<uint32_t*>(codes);
-    if (wide)
-      nvfp4_quantize_rows_kernel<true><<<wave_grid(nvfp4_quantize_rows_kernel<true>, kRowThreads, rows, 1),
-                                         kRowThreads, 0, s>>>(I, rows, row_vectors, rows_per_scale,
-                                                                    global_scales, amax_bits, global_scales_out, C,
-                                                                    scales);
-    else
-      nvfp4_quantize_rows_kernel<false><<<wave_grid(nvfp4_quantize_rows_kernel<false>, kRowThreads, rows, 1),
-                                          kRowThreads, 0, s>>>(I, rows, row_vectors, rows_per_scale,
-                                                                     global_scales, amax_bits, global_scales_out, C,
-                                                                     scales);
+    const int vpt = row_vectors <= 6 * kRowThreads ? (row_vectors + kRowThreads - 1) / kRowThreads : 0;
+#define Q3X_QUANT(WIDE, V)                                                                                    \
+  nvfp4_quantize_rows_kernel<WIDE, V><<<wave_grid(nvfp4_quantize_rows_kernel<WIDE, V>, kRowThreads, rows, 1), \
+                                        kRowThreads, 0, s>>>(I, rows, row_vectors, rows_per_scale,            \
+                                                             global_scales, amax_bits, global_scales_out, C,  \
+                                                             scales)
+#define Q3X_QUANT_VPT(WIDE)                   \
+  switch (vpt) {                              \
+    case 1: Q3X_QUANT(WIDE, 1); break;        \
+    case 2: Q3X_QUANT(WIDE, 2); break;        \
+    case 3: Q3X_QUANT(WIDE, 3); break;        \
+    case 4: Q3X_QUANT(WIDE, 4); break;        \
+    case 5: Q3X_QUANT(WIDE, 5); break;        \
+    case 6: Q3X_QUANT(WIDE, 6); break;        \
+    default: Q3X_QUANT(WIDE, 0); break;       \
+  }
+    if (wide) { Q3X_QUANT_VPT(true) } else { Q3X_QUANT_VPT(false) }
+#undef Q3X_QUANT_VPT
+#undef Q3X_QUANT
   } else {
     const size_t blocks = rows * cols / 16;
     nvfp4_quantize_scalar_kernel<<<grid_for(blocks, kThreads, 8), kThreads, 0, s>>>(in, blocks, cols / 16,
