@@ -305,9 +305,6 @@ def probe_ops(stack, chain, stream_obj, T, peak, warm, reps):
         "attention_preprocess": lambda: stack.op_preprocess(3, stream),
         "sigmoid_gate": lambda: stack.op_sigmoid_gate(stream),
         "swiglu": lambda: stack.op_swiglu(stream),
-        # the one-pass cooperative forms of the two norm + NVFP4 operators (not used by the step)
-        "residual_rmsnorm_nvfp4/single_pass": lambda: stack.op_residual_norm_single_pass(0, 0, 0, 1, stream),
-        "gated_rmsnorm_nvfp4/single_pass": lambda: stack.op_gated_norm_single_pass(0, stream),
     }
     per_op = {}
     with torch.cuda.stream(stream_obj):

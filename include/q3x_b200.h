@@ -115,8 +115,8 @@ int q3x_b200_residual_add_rms_norm(const uint16_t* left, const uint16_t* right,
 
 /* Number of scale groups of a [rows, *] tensor. */
 size_t q3x_b200_nvfp4_group_count(size_t rows, size_t rows_per_scale);
-/* Size, in uint32 words, of the `scratch` argument of the entry points below (group amax words or
- * per-row amax words, plus an error word at the end).  The caller owns the memory; every call
+/* Size, in uint32 words, of the `scratch` argument of the entry points below (group amax words and
+ * group arrival counters, plus an error word at the end).  The caller owns the memory; every call
  * clears what it uses, so stale contents do not matter. */
 size_t q3x_b200_nvfp4_scratch_words(size_t rows, size_t rows_per_scale);
 
@@ -139,19 +139,23 @@ int q3x_b200_nvfp4_quantize_dynamic(const uint16_t* in, size_t rows, size_t cols
 
 /* Residual add + centred RMSNorm + NVFP4 of the normalised rows, global scale from the group
  * amax.  normalized_out is required (it is the operand the codes are derived from, bit for
- * bit); it may be exactly `right`.  Two kernels: the norm, which also reduces each group's amax,
- * then the quantiser, which derives the scales from it. */
+ * bit); it may be exactly `right`.  One kernel that crosses HBM once where a scale group is short
+ * enough to wait in L2 (see the _single_pass form), else two kernels: the norm, which also reduces
+ * each group's amax, then the quantiser, which derives the scales from it.  Same bytes either way.
+ * After the call the last scratch word is non-zero only if a bounded wait inside the single kernel
+ * gave up (outputs then not valid). */
 int q3x_b200_residual_add_rms_norm_nvfp4(const uint16_t* left, const uint16_t* right,
                                          const uint16_t* weight, size_t tokens, size_t hidden,
                                          float eps, size_t rows_per_scale, uint16_t* residual_out,
                                          uint16_t* normalized_out, uint32_t* scratch,
                                          float* global_scales_out, uint8_t* codes, uint8_t* scales,
                                          void* stream);
-/* The same result from ONE pass over HBM: a cooperative kernel of co-resident thread teams that
- * defers each row's quantisation until the amax of its group is complete (the normalised row
- * waits in shared memory).  Returns cudaErrorNotSupported when a scale group is too long for the
- * shared-memory ring or the device cannot co-schedule the grid.  After the call the last scratch
- * word is non-zero only if a bounded wait inside the kernel gave up (outputs then not valid). */
+/* The same result, insisting on ONE pass over HBM: a single kernel whose CTAs alternate between
+ * normalising a row and quantising the row written `lag` rows earlier, which still sits in L2 and
+ * whose scale group is complete by then.  Returns cudaErrorNotSupported, with nothing enqueued,
+ * when a scale group is too long to stay in L2 (group rows x row bytes beyond a few tens of MB,
+ * e.g. rows_per_scale == 0 on a long tensor).  After the call the last scratch word is non-zero
+ * only if a bounded wait inside the kernel gave up (outputs then not valid). */
 int q3x_b200_residual_add_rms_norm_nvfp4_single_pass(const uint16_t* left, const uint16_t* right,
                                                      const uint16_t* weight, size_t tokens,
                                                      size_t hidden, float eps, size_t rows_per_scale,
@@ -160,13 +164,13 @@ int q3x_b200_residual_add_rms_norm_nvfp4_single_pass(const uint16_t* left, const
                                                      uint8_t* codes, uint8_t* scales, void* stream);
 
 /* Gated RMSNorm * silu(z) + NVFP4 of its output rows.  `heads_per_row` heads of `dim` form one
- * quantisation row (48 x 128 = 6144 for the GDN output).  Two kernels, as above. */
+ * quantisation row (48 x 128 = 6144 for the GDN output).  One kernel or two, as above. */
 int q3x_b200_rms_norm_silu_gate_nvfp4(const uint16_t* in, const uint16_t* weight,
                                       const uint16_t* gate, size_t tokens, size_t heads_per_row,
                                       size_t dim, float eps, size_t rows_per_scale, uint16_t* out,
                                       uint32_t* scratch, float* global_scales_out,
                                       uint8_t* codes, uint8_t* scales, void* stream);
-/* Single-pass form (dim must be 128; out must not alias an input). */
+/* Single-pass form (dim must be 128). */
 int q3x_b200_rms_norm_silu_gate_nvfp4_single_pass(const uint16_t* in, const uint16_t* weight,
                                                   const uint16_t* gate, size_t tokens,
                                                   size_t heads_per_row, size_t dim, float eps,

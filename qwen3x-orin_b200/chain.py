@@ -43,9 +43,10 @@ BYTES_PER_TOKEN = {
     "sigmoid_gate": 3 * Q_HEADS * HEAD_DIM * 2,
     "swiglu": 3 * INTERMEDIATE * 2,
 }
-# kernels each entry point launches (memset nodes not counted)
+# kernels each entry point launches (memset nodes not counted); the norm + NVFP4 entries run their
+# single-kernel form at the chain's scale scope of 512 tokens
 KERNELS = {
-    "embedding_gather": 1, "residual_rmsnorm_nvfp4": 2, "conv1d_silu_l2norm": 1, "gated_rmsnorm_nvfp4": 2,
+    "embedding_gather": 1, "residual_rmsnorm_nvfp4": 1, "conv1d_silu_l2norm": 1, "gated_rmsnorm_nvfp4": 1,
     "attention_preprocess": 1, "sigmoid_gate": 1, "swiglu": 1,
 }
 GDN_OPS = ["residual_rmsnorm_nvfp4", "conv1d_silu_l2norm", "gated_rmsnorm_nvfp4", "residual_rmsnorm_nvfp4", "swiglu"]
@@ -161,16 +162,6 @@ class LayerStack:
         capi.check("q3x_b200_residual_add_rms_norm_nvfp4", self.residual[src], self.inputs["proj_out"],
                    self.norm_w[layer, which], self.tokens, HIDDEN, EPS, CHUNK, self.residual[dst], self.normalized,
                    self.amax, self.global_scales, self.codes, self.scales, stream)
-
-    def op_residual_norm_single_pass(self, layer, which, src, dst, stream):
-        capi.check("q3x_b200_residual_add_rms_norm_nvfp4_single_pass", self.residual[src], self.inputs["proj_out"],
-                   self.norm_w[layer, which], self.tokens, HIDDEN, EPS, CHUNK, self.residual[dst], self.normalized,
-                   self.amax, self.global_scales, self.codes, self.scales, stream)
-
-    def op_gated_norm_single_pass(self, layer, stream):
-        capi.check("q3x_b200_rms_norm_silu_gate_nvfp4_single_pass", self.inputs["gdn_core"], self.gdn_norm_w[layer],
-                   self.inputs["gdn_z"], self.tokens, 48, 128, EPS, CHUNK, self.gdn_out, self.amax,
-                   self.global_scales, self.gdn_codes, self.gdn_scales, stream)
 
     def op_conv(self, layer, stream):
         capi.check("q3x_b200_causal_conv1d_silu_l2norm", self.inputs["conv_raw"], self.tokens, self.conv_w[layer],

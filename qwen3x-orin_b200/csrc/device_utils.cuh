@@ -80,6 +80,37 @@ __device__ __forceinline__ void st_stream(void* p, const uint4& v) {
 // Small read-mostly operands (weights, tables): keep them cached.
 __device__ __forceinline__ uint4 ld_weight(const void* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
 
+// L2 eviction policy for operands that stream through once while something else should stay cached.
+__device__ __forceinline__ uint64_t l2_evict_first_policy() {
+  uint64_t policy;
+  asm("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+  return policy;
+}
+__device__ __forceinline__ uint4 ld_stream(const void* p, uint64_t policy) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.v4.u32 {%0,%1,%2,%3}, [%4], %5;"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p), "l"(policy));
+  return v;
+}
+// Coherent load served by L2 (data another CTA of the same launch has written), then first to go.
+__device__ __forceinline__ uint4 ld_l2_once(const void* p, uint64_t policy) {
+  uint4 v;
+  asm volatile("ld.global.cg.L2::cache_hint.v4.u32 {%0,%1,%2,%3}, [%4], %5;"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p), "l"(policy)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_vec(void* p, const uint4& v, uint64_t policy) {
+  asm volatile("st.global.L2::cache_hint.v4.u32 [%0], {%1,%2,%3,%4}, %5;" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z),
+               "r"(v.w), "l"(policy)
+               : "memory");
+}
+__device__ __forceinline__ void st_u32(void* p, uint32_t v, uint64_t policy) {
+  asm volatile("st.global.L2::cache_hint.u32 [%0], %1, %2;" ::"l"(p), "r"(v), "l"(policy) : "memory");
+}
+
 // ---------------------------------------------------------------------------- reductions
 
 template <int LANES>
@@ -155,6 +186,17 @@ __device__ __forceinline__ float silu(float g) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(g * -1.4426950408889634f));
   asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(fmaf(e, kScale, kScale)));  // 1 / ((1 + e) * 2^-24)
   return g * (r * kScale);
+}
+
+// The same function with the denominator left unscaled and the reciprocal in its subnormal-keeping form
+// (MUFU.RCP plus a range fix-up).  Same accuracy class (the two can differ in the last bit of a subnormal
+// reciprocal, i.e. for g below -87); measured faster than the form above in
+// the HBM-bound SwiGLU kernel and slower in the instruction-bound conv / gated-norm kernels.
+__device__ __forceinline__ float silu_unscaled(float g) {
+  float e, r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(g * -1.4426950408889634f));
+  asm("rcp.approx.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+  return g * r;
 }
 
 // ---------------------------------------------------------------------------- bf16 amax

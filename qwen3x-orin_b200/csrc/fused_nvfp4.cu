@@ -1,31 +1,29 @@
-// Single-pass norm + NVFP4 kernels: residual add + centred RMSNorm + quantisation, and the GDN
-// gated RMSNorm * silu(z) + quantisation, each crossing HBM once.
+// Single-kernel norm + NVFP4: residual add + centred RMSNorm + quantisation, and the GDN gated
+// RMSNorm * silu(z) + quantisation, each crossing HBM once.
 //
 // The NVFP4 global scale of a group of rows is its amax, which is only known once every row of the
-// group has been normalised -- a grid-wide dependency.  It is resolved without a second pass over
-// memory by DEFERRING the quantisation of a row:
-//   * a team (one CTA of 128 threads) owns rows team, team + teams, team + 2 teams, ...; all CTAs
-//     are co-resident (cooperative launch);
-//   * the inputs of a team's NEXT row are copied global -> shared with cp.async while the current
-//     row is processed, so HBM latency is off the critical path; every thread stages, rings and
-//     later quantises the same vectors (tid + k * 128), so none of these buffers needs a barrier;
-//   * iteration i normalises row i ("phase A"): it writes the bf16 outputs, keeps the normalised
-//     row in a shared-memory ring and publishes the row's amax as ONE 32-bit word (magnitude bits
-//     plus a valid bit) -- no atomics and no fence, the word itself says that it is there;
-//   * the same iteration quantises the row of iteration i - (depth - 1) ("phase B") from the ring:
-//     the team reads the amax words of that row's whole group (<= a few KB, from L2), and only
-//     spins while a word is not valid yet.  depth is chosen so that every row of that group belongs
-//     to an iteration at least one behind the current one of its owner, so the words are normally
-//     all there.
-// Progress: the team with the smallest iteration number only ever needs words of iterations that
-// every team has already finished, so the waits cannot deadlock while all CTAs are resident.  Every
-// spin is bounded; a team that gives up sets the error word and carries on, so the kernel always
-// terminates.
+// group has been normalised -- a dependency across CTAs.  It is resolved without a second pass over
+// HBM by DEFERRING the quantisation of a row by `lag` rows, inside one launch whose CTAs (128
+// threads) alternate between two roles:
+//   * even CTAs ("phase A", CTA 2k): normalise row k exactly like the stand-alone norm kernel (whole
+//     row in registers, one trip per tensor), write the bf16 outputs, raise the group's amax word with
+//     one atomic and then count the row into the group's arrival counter (fence in between);
+//   * odd CTAs ("phase B", CTA 2k + 1): quantise row k - lag, which was written `lag` rows earlier and
+//     is still in L2 (lag x row bytes is a few tens of MB at most; the launcher refuses longer groups).
+//     They need the arrival counter of that row's group to be complete.  lag = group rows + the number
+//     of CTAs that can be resident, so every row of that group belongs to a CTA that is at least one
+//     full residency older: the counter is normally complete already and the wait is a single load.
+//   The two roles sit in different CTAs so that neither holds registers while the other waits on
+//   memory: the in-flight loads of phase A are what keeps HBM busy.
+// Progress: phase-A CTAs never wait, and the rows a phase-B CTA waits for belong to CTAs with a
+// smaller index, which the hardware has started earlier (CTAs of a 1-D grid start in index order).
+// Every wait is bounded all the same; a CTA that gives up sets the error word and carries on, so the
+// kernel always terminates and a missed dependency is reported, never silent.
+// The streamed operands (inputs, residual, codes, scales) carry an L2 evict-first policy so that the
+// normalised rows awaiting phase B are what stays cached.
 //
-// Scratch words (uint32): [0, rows) per-row amax words, last word = error flag.
-#include <atomic>
-#include <mutex>
-
+// Scratch words (uint32), cleared by the launcher: G group amax words, then G arrival counters (each
+// on an L2 line of its own when the scratch is large enough), last word = error flag.
 #include "device_utils.cuh"
 #include "host_checks.hpp"
 #include "internal.hpp"
@@ -36,101 +34,118 @@
 namespace q3x {
 namespace {
 
-constexpr int kTeam = 128;           // threads of a CTA; they own one row at a time
-constexpr int kMaxDepth = 8;         // ring slots a team may be given
-constexpr int kSpinLimit = 1 << 20;  // polls of one word before giving up (~1 s with the sleep)
-constexpr uint32_t kValid = 0x80000000u;
+constexpr int kTeam = 128;                   // threads of a CTA; they own one row per phase
+// Resident CTAs per SM the kernels are compiled for.  The launch is latency-bound (half of the CTAs sit
+// on L2 round trips), so occupancy pays: eight CTAs (64 registers) for rows of up to 768 vectors,
+// measured 17 % faster than the five the compiler would pick; wider rows need the registers.
+constexpr int min_ctas_per_sm(int vpt) { return vpt <= 6 ? 8 : 5; }
+constexpr int kSpinLimit = 1 << 20;          // polls of the arrival counter before giving up (~1 s)
+constexpr size_t kMaxLagBytes = 48u << 20;   // normalised bytes that may sit in L2 between the phases
+constexpr int kMaxRowScaleBytes = 512;       // block scales of one row (row_vectors / 2)
 
-__device__ __forceinline__ void cp_async16(void* smem_dst, const void* global_src) {
-  const unsigned dst = static_cast<unsigned>(__cvta_generic_to_shared(smem_dst));
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(global_src) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
-
-__device__ __forceinline__ uint32_t ld_volatile(const uint32_t* p) {
+__device__ __forceinline__ uint32_t ld_acquire(const uint32_t* p) {
   uint32_t v;
-  asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint32_t ld_relaxed(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
 
-struct RowBoard {
-  uint32_t* row_amax;  // [rows]: kValid | bf16 magnitude bits of the row's largest finite output
-  uint32_t* error;     // [1]
-  size_t rows, rows_per_group;
+struct Board {
+  uint32_t* amax;     // group g at amax[g * stride]
+  uint32_t* count;    // group g at count[g * stride]
+  uint32_t* error;    // [1]
+  float* global_out;  // [G] the global scales, written by the CTA that quantises a group's first row
+  size_t rows, group_rows;
+  unsigned lag;
+  unsigned stride;    // words between the slots of neighbouring groups (32 = one L2 line each, or 1)
+};
+
+struct QuantOut {
+  uint32_t* codes;  // [rows, row_vectors] words
+  uint8_t* scales;  // [rows, row_vectors / 2] bytes
+  bool wide_scale_stores;
 };
 
 struct TeamShared {
   float sums[4];
-  uint32_t tops_a[4];
-  uint32_t tops_b[4];
-  uint32_t pad[4];
-  uint8_t scale_bytes[512];  // one row of block scales (row_vectors / 2 <= 512)
+  uint32_t tops[4];
+  uint32_t group_amax;
+  float inv_table[kTeam];  // indexed by E4M3 code 0..127
+  __align__(16) uint8_t scale_bytes[kMaxRowScaleBytes];
 };
 
-// Phase A epilogue: the row's amax as one self-validating word.
-__device__ __forceinline__ void publish_row(const RowBoard& board, TeamShared& ts, int tid, size_t row,
-                                            uint32_t thread_top) {
-  const uint32_t warp_top = group_max_u32<32>(thread_top);
-  if ((tid & 31) == 0) ts.tops_a[tid >> 5] = warp_top;
+// Phase A epilogue.  The barrier orders every thread's stores of the row before thread 0's fence, the
+// fence orders them (and the amax atomic) before the arrival count at GPU scope.
+__device__ __forceinline__ void publish_row(const Board& board, TeamShared& ts, size_t row, float thread_top) {
+  const uint32_t warp_top = group_max_u32<32>(amax_bits_of(thread_top));
+  if ((threadIdx.x & 31) == 0) ts.tops[threadIdx.x >> 5] = warp_top;
   __syncthreads();
-  if (tid == 0) {
-    const uint32_t m = max(max(ts.tops_a[0], ts.tops_a[1]), max(ts.tops_a[2], ts.tops_a[3]));
-    __stcg(board.row_amax + row, m | kValid);
+  if (threadIdx.x == 0) {
+    const size_t slot = row / board.group_rows * board.stride;
+    const uint32_t m = max(max(ts.tops[0], ts.tops[1]), max(ts.tops[2], ts.tops[3]));
+    if (m != 0) atomicMax(board.amax + slot, m);
+    __threadfence();
+    atomicAdd(board.count + slot, 1u);
   }
 }
 
-// Phase B prologue: the global scale of the group of `row`, once all of the group's words are valid.
-__device__ __forceinline__ float await_group_scale(const RowBoard& board, TeamShared& ts, int tid, size_t row) {
-  const size_t group = row / board.rows_per_group;
-  const size_t first = group * board.rows_per_group;
-  const size_t count = min(board.rows_per_group, board.rows - first);
-  uint32_t top = 0;
-  for (size_t j = tid; j < count; j += kTeam) {
-    uint32_t word = ld_volatile(board.row_amax + first + j);
+// Phase B prologue: the amax bits of the group of `row`, once all of the group's rows have arrived.
+// One thread polls (a single request per CTA on the counter's L2 line); the barrier then orders its
+// acquire before every thread's loads of the row.
+__device__ __forceinline__ uint32_t await_group_amax(const Board& board, TeamShared& ts, size_t group) {
+  if (threadIdx.x == 0) {
+    const size_t first = group * board.group_rows;
+    const uint32_t need = static_cast<uint32_t>(min(board.group_rows, board.rows - first));
+    const size_t slot = group * board.stride;
     int polls = 0;
-    while ((word & kValid) == 0) {
+    while (ld_acquire(board.count + slot) < need) {
       if (++polls >= kSpinLimit) {
         atomicExch(board.error, 1u);
         break;
       }
-      __nanosleep(100);
-      word = ld_volatile(board.row_amax + first + j);
+      __nanosleep(200);
     }
-    top = max(top, word & 0xffffu);
+    ts.group_amax = ld_relaxed(board.amax + slot);
   }
-  top = group_max_u32<32>(top);
-  if ((tid & 31) == 0) ts.tops_b[tid >> 5] = top;
   __syncthreads();
-  const uint32_t m = max(max(ts.tops_b[0], ts.tops_b[1]), max(ts.tops_b[2], ts.tops_b[3]));
-  return global_scale_from_amax_bits(m);
+  return ts.group_amax;
 }
 
-struct QuantOut {
-  uint32_t* codes;   // [rows, row_vectors] words
-  uint8_t* scales;   // [rows, row_vectors / 2] bytes
-  bool wide_scale_stores;
-};
-
-// Phase B: quantises one row from the team's ring slot.  Thread tid owns vectors tid + k * 128.
+// Phase B: quantises one normalised row out of L2.  Thread tid owns vectors tid + k * 128; the loads
+// are issued first and are in flight while the reciprocal table of the row's global scale is built.
 template <int VPT>
-__device__ __forceinline__ void quantize_ring_row(const uint4* slot, int row_vectors, float global, TeamShared& ts,
-                                                  int tid, uint32_t* codes_row, uint8_t* scales_row,
-                                                  bool wide_scale_stores) {
+__device__ __forceinline__ void quantize_cached_row(const uint4* row_in, int row_vectors, const Board& board,
+                                                    TeamShared& ts, size_t row, uint32_t* codes_row,
+                                                    uint8_t* scales_row, bool wide_scale_stores, uint64_t policy) {
+  const int tid = threadIdx.x;
+  const size_t group = row / board.group_rows;
+  const uint32_t amax_bits = await_group_amax(board, ts, group);
+  uint4 y[VPT];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = tid + i * kTeam;
+    y[i] = v < row_vectors ? ld_l2_once(row_in + v, policy) : make_uint4(0, 0, 0, 0);
+  }
+  const float global = global_scale_from_amax_bits(amax_bits);
+  if (tid == 0 && row == group * board.group_rows) board.global_out[group] = global;
   const float k = block_scale_factor(global);
+  ts.inv_table[tid] = block_inverse(static_cast<uint32_t>(tid), global);
+  __syncthreads();
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const int v = tid + i * kTeam;
     const bool valid = v < row_vectors;  // lane pairs are valid together (row_vectors is even)
-    const uint4 y = valid ? slot[v] : make_uint4(0, 0, 0, 0);
     float f[8];
-    unpack8(y, f);
-    float m = amax8_float(f, y);
+    unpack8(y[i], f);
+    float m = amax8_float(f, y[i]);
     m = fmaxf(m, __shfl_xor_sync(kFullMask, m, 1));
     const uint32_t s = block_scale_code(m, k);
-    const float inv = block_inverse(s, global);
     if (valid) {
-      codes_row[v] = quantize8(f, inv);
+      st_u32(codes_row + v, quantize8(f, ts.inv_table[s]), policy);
       if ((tid & 1) == 0) {
         if (wide_scale_stores) ts.scale_bytes[v >> 1] = static_cast<uint8_t>(s);
         else scales_row[v >> 1] = static_cast<uint8_t>(s);
@@ -139,267 +154,150 @@ __device__ __forceinline__ void quantize_ring_row(const uint4* slot, int row_vec
   }
   if (wide_scale_stores) {  // row_vectors / 2 bytes, a multiple of 16, written as 128-bit stores
     __syncthreads();
-    const int n = row_vectors / 32;
-    if (tid < n) reinterpret_cast<uint4*>(scales_row)[tid] = reinterpret_cast<const uint4*>(ts.scale_bytes)[tid];
+    if (tid < row_vectors / 32)
+      st_vec(reinterpret_cast<uint4*>(scales_row) + tid, reinterpret_cast<const uint4*>(ts.scale_bytes)[tid], policy);
   }
 }
 
-// Shared-memory carve-up: [2 staging rows][depth ring rows][TeamShared]
+// Phase B of either kernel: CTA 2k + 1 quantises row k - lag of `normalized`.
 template <int VPT>
-struct Carve {
-  static constexpr int kRowVectors = VPT * kTeam;
-  __device__ static uint4* stage(unsigned char* smem, int which) {
-    return reinterpret_cast<uint4*>(smem) + which * kRowVectors;
-  }
-  __device__ static uint4* ring(unsigned char* smem, int slot) {
-    return reinterpret_cast<uint4*>(smem) + (2 + slot) * kRowVectors;
-  }
-  __device__ static TeamShared& shared(unsigned char* smem, int depth) {
-    return *reinterpret_cast<TeamShared*>(smem + sizeof(uint4) * (2 + depth) * kRowVectors);
-  }
-};
+__device__ __forceinline__ void phase_b(const uint4* normalized, int row_vectors, const Board& board, TeamShared& ts,
+                                        const QuantOut& q, uint64_t policy) {
+  const size_t idx = blockIdx.x >> 1;
+  if (idx < board.lag || idx - board.lag >= board.rows) return;
+  const size_t row = idx - board.lag;
+  quantize_cached_row<VPT>(normalized + row * static_cast<size_t>(row_vectors), row_vectors, board, ts, row,
+                           q.codes + row * static_cast<size_t>(row_vectors),
+                           q.scales + row * static_cast<size_t>(row_vectors / 2), q.wide_scale_stores, policy);
+}
 
+// ---- residual add + centred RMSNorm + NVFP4 ------------------------------------------------
+// `coherent`: an output aliases an input exactly (row i is read and written by the same CTA only).
 template <int VPT>
-__device__ __forceinline__ void stage_row(unsigned char* smem, const uint4* a, const uint4* b, size_t base,
-                                          int row_vectors, int tid) {
+__global__ void __launch_bounds__(kTeam, min_ctas_per_sm(VPT)) residual_norm_nvfp4_kernel(
+    const uint4* left, const uint4* right, const uint4* __restrict__ weight, int row_vectors, float width, float eps,
+    uint4* residual_out, uint4* normalized_out, bool coherent, Board board, QuantOut q) {
+  __shared__ TeamShared ts;
+  const int tid = threadIdx.x;
+  const uint64_t policy = l2_evict_first_policy();
+  if (blockIdx.x & 1u) {
+    phase_b<VPT>(normalized_out, row_vectors, board, ts, q, policy);
+    return;
+  }
+  const size_t row = blockIdx.x >> 1;
+  if (row >= board.rows) return;
+  const size_t base = row * static_cast<size_t>(row_vectors);
+  uint4 x[VPT], r[VPT];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = tid + i * kTeam;
+    x[i] = make_uint4(0, 0, 0, 0);
+    if (v < row_vectors) x[i] = coherent ? ld_vec(left + base + v) : ld_stream(left + base + v, policy);
+  }
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = tid + i * kTeam;
+    r[i] = make_uint4(0, 0, 0, 0);
+    if (v < row_vectors) r[i] = coherent ? ld_vec(right + base + v) : ld_stream(right + base + v, policy);
+  }
+  float partial = 0.0f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    float a[8], b[8];
+    unpack8(x[i], a);
+    unpack8(r[i], b);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) a[j] = a[j] + b[j];
+    x[i] = pack8(a);
+    const int v = tid + i * kTeam;
+    if (v < row_vectors) st_vec(residual_out + base + v, x[i], policy);
+    partial += sum_squares8(x[i]);
+  }
+  const float total = block_sum<4>(partial, ts.sums);
+  const float inv = inverse_rms(total, 1.0f / width, eps);
+  float top = 0.0f;
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const int v = tid + i * kTeam;
     if (v < row_vectors) {
-      cp_async16(Carve<VPT>::stage(smem, 0) + v, a + base + v);
-      cp_async16(Carve<VPT>::stage(smem, 1) + v, b + base + v);
+      const uint4 y = scale8<NormMode::kCentered, true>(x[i], ld_weight(weight + v), make_uint4(0, 0, 0, 0), inv,
+                                                        &top);
+      st_vec(normalized_out + base + v, y);  // default policy: this is what phase B finds in L2
     }
   }
-  cp_async_commit();
+  publish_row(board, ts, row, top);
 }
 
-// ---- residual add + centred RMSNorm + NVFP4 ------------------------------------------------
+// ---- gated RMSNorm * silu(z) over heads of 128 + NVFP4 ----------------------------------------
+// A row is one token: heads_per_row heads of 16 vectors; 16 consecutive lanes own one head.
 template <int VPT>
-__global__ void __launch_bounds__(kTeam) residual_norm_nvfp4_kernel(
-    const uint4* left, const uint4* right, const uint4* __restrict__ weight, int row_vectors, float width, float eps,
-    uint4* residual_out, uint4* normalized_out, int depth, RowBoard board, QuantOut q) {
-  extern __shared__ __align__(16) unsigned char smem[];
-  const int tid = threadIdx.x;
-  TeamShared& ts = Carve<VPT>::shared(smem, depth);
-  const size_t teams = gridDim.x;
-  const size_t first = blockIdx.x;
-  const size_t lag = static_cast<size_t>(depth - 1);
-  const float inv_width = 1.0f / width;
-  if (first < board.rows) stage_row<VPT>(smem, left, right, first * static_cast<size_t>(row_vectors), row_vectors, tid);
-
-  for (size_t it = 0;; ++it) {
-    const size_t row = first + it * teams;
-    const bool has_row = row < board.rows;
-    const bool has_old = it >= lag && first + (it - lag) * teams < board.rows;
-    if (!has_row && !has_old) {
-      if (it >= lag) break;  // nothing left in the ring either
-      continue;              // rows are exhausted but the ring still drains
-    }
-    if (has_row) {
-      const size_t base = row * static_cast<size_t>(row_vectors);
-      uint4 x[VPT];
-      cp_async_wait_all();
-      float partial = 0.0f;
-#pragma unroll
-      for (int i = 0; i < VPT; ++i) {
-        const int v = tid + i * kTeam;
-        x[i] = make_uint4(0, 0, 0, 0);
-        if (v < row_vectors) {
-          float a[8], b[8];
-          unpack8(Carve<VPT>::stage(smem, 0)[v], a);
-          unpack8(Carve<VPT>::stage(smem, 1)[v], b);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) a[j] = a[j] + b[j];
-          x[i] = pack8(a);
-          st_vec(residual_out + base + v, x[i]);
-        }
-        partial += sum_squares8(x[i]);
-      }
-      // this thread has consumed its staged vectors: refill them with the next row's
-      if (row + teams < board.rows)
-        stage_row<VPT>(smem, left, right, (row + teams) * static_cast<size_t>(row_vectors), row_vectors, tid);
-      partial = group_sum<32>(partial);
-      if ((tid & 31) == 0) ts.sums[tid >> 5] = partial;
-      __syncthreads();
-      const float total = ts.sums[0] + ts.sums[1] + ts.sums[2] + ts.sums[3];
-      const float inv = inverse_rms(total, inv_width, eps);
-      uint4* slot = Carve<VPT>::ring(smem, static_cast<int>(it % depth));
-      float top = 0.0f;
-#pragma unroll
-      for (int i = 0; i < VPT; ++i) {
-        const int v = tid + i * kTeam;
-        if (v < row_vectors) {
-          const uint4 y =
-              scale8<NormMode::kCentered, true>(x[i], ld_weight(weight + v), make_uint4(0, 0, 0, 0), inv, &top);
-          st_vec(normalized_out + base + v, y);
-          slot[v] = y;
-        }
-      }
-      publish_row(board, ts, tid, row, amax_bits_of(top));
-    }
-    if (has_old) {
-      const size_t old_it = it - lag;
-      const size_t old_row = first + old_it * teams;
-      const float global = await_group_scale(board, ts, tid, old_row);
-      quantize_ring_row<VPT>(Carve<VPT>::ring(smem, static_cast<int>(old_it % depth)), row_vectors, global, ts, tid,
-                             q.codes + old_row * static_cast<size_t>(row_vectors),
-                             q.scales + old_row * static_cast<size_t>(row_vectors / 2), q.wide_scale_stores);
-    }
-  }
-}
-
-// ---- gated RMSNorm * silu(z) + NVFP4: one row = one token = heads_per_row heads of 128 -------
-template <int VPT>
-__global__ void __launch_bounds__(kTeam) gated_norm_nvfp4_kernel(
+__global__ void __launch_bounds__(kTeam, min_ctas_per_sm(VPT)) gated_norm_nvfp4_kernel(
     const uint4* in, const uint4* gate, const uint4* __restrict__ weight, int row_vectors, float eps, uint4* out,
-    int depth, RowBoard board, QuantOut q) {
-  constexpr int kLanes = Q3X_B200_GDN_HEAD_DIM / 8;  // 16 lanes own one head
-  extern __shared__ __align__(16) unsigned char smem[];
+    bool coherent, Board board, QuantOut q) {
+  __shared__ TeamShared ts;
   const int tid = threadIdx.x;
-  TeamShared& ts = Carve<VPT>::shared(smem, depth);
-  const size_t teams = gridDim.x;
-  const size_t first = blockIdx.x;
-  const size_t lag = static_cast<size_t>(depth - 1);
-  const uint4 w = ld_weight(weight + (tid % kLanes));
-  if (first < board.rows) stage_row<VPT>(smem, in, gate, first * static_cast<size_t>(row_vectors), row_vectors, tid);
-
-  for (size_t it = 0;; ++it) {
-    const size_t row = first + it * teams;
-    const bool has_row = row < board.rows;
-    const bool has_old = it >= lag && first + (it - lag) * teams < board.rows;
-    if (!has_row && !has_old) {
-      if (it >= lag) break;
-      continue;
-    }
-    if (has_row) {
-      const size_t base = row * static_cast<size_t>(row_vectors);
-      uint4 x[VPT], z[VPT];
-      cp_async_wait_all();
+  const uint64_t policy = l2_evict_first_policy();
+  if (blockIdx.x & 1u) {
+    phase_b<VPT>(out, row_vectors, board, ts, q, policy);
+    return;
+  }
+  const size_t row = blockIdx.x >> 1;
+  if (row >= board.rows) return;
+  const size_t base = row * static_cast<size_t>(row_vectors);
+  const uint4 w = ld_weight(weight + (tid & 15));
+  uint4 x[VPT], z[VPT];
 #pragma unroll
-      for (int i = 0; i < VPT; ++i) {
-        const int v = tid + i * kTeam;
-        x[i] = z[i] = make_uint4(0, 0, 0, 0);
-        if (v < row_vectors) {
-          x[i] = Carve<VPT>::stage(smem, 0)[v];
-          z[i] = Carve<VPT>::stage(smem, 1)[v];
-        }
-      }
-      if (row + teams < board.rows)
-        stage_row<VPT>(smem, in, gate, (row + teams) * static_cast<size_t>(row_vectors), row_vectors, tid);
-      uint4* slot = Carve<VPT>::ring(smem, static_cast<int>(it % depth));
-      float top = 0.0f;
+  for (int i = 0; i < VPT; ++i) {
+    const int v = tid + i * kTeam;
+    x[i] = z[i] = make_uint4(0, 0, 0, 0);
+    if (v < row_vectors) {
+      x[i] = coherent ? ld_vec(in + base + v) : ld_stream(in + base + v, policy);
+      z[i] = coherent ? ld_vec(gate + base + v) : ld_stream(gate + base + v, policy);
+    }
+  }
+  float top = 0.0f;
 #pragma unroll
-      for (int i = 0; i < VPT; ++i) {
-        const int v = tid + i * kTeam;  // head = v / 16: the 16 lanes of a head sit in one warp
-        const float sum = group_sum<kLanes>(sum_squares8(x[i]));
-        const float inv = inverse_rms(sum, 1.0f / static_cast<float>(Q3X_B200_GDN_HEAD_DIM), eps);
-        if (v < row_vectors) {
-          const uint4 y = scale8<NormMode::kPlainSiluGate, true>(x[i], w, z[i], inv, &top);
-          st_vec(out + base + v, y);
-          slot[v] = y;
-        }
-      }
-      publish_row(board, ts, tid, row, amax_bits_of(top));
-    }
-    if (has_old) {
-      const size_t old_it = it - lag;
-      const size_t old_row = first + old_it * teams;
-      const float global = await_group_scale(board, ts, tid, old_row);
-      quantize_ring_row<VPT>(Carve<VPT>::ring(smem, static_cast<int>(old_it % depth)), row_vectors, global, ts, tid,
-                             q.codes + old_row * static_cast<size_t>(row_vectors),
-                             q.scales + old_row * static_cast<size_t>(row_vectors / 2), q.wide_scale_stores);
+  for (int i = 0; i < VPT; ++i) {
+    const int v = tid + i * kTeam;
+    const float sum = group_sum<16>(sum_squares8(x[i]));  // every lane takes part; idle heads sum zeros
+    const float inv = inverse_rms(sum, 1.0f / 128.0f, eps);
+    if (v < row_vectors) {
+      const uint4 y = scale8<NormMode::kPlainSiluGate, true>(x[i], w, z[i], inv, &top);
+      st_vec(out + base + v, y);
     }
   }
+  publish_row(board, ts, row, top);
 }
 
-// One CTA per group: global scale = f(max of the group's row words).
-__global__ void __launch_bounds__(kTeam) finish_scales_kernel(const uint32_t* row_amax, size_t rows,
-                                                              size_t rows_per_group, float* global_scales) {
-  __shared__ uint32_t tops[4];
-  const size_t first = static_cast<size_t>(blockIdx.x) * rows_per_group;
-  const size_t count = min(rows_per_group, rows - first);
-  uint32_t top = 0;
-  for (size_t j = threadIdx.x; j < count; j += kTeam) top = max(top, row_amax[first + j] & 0xffffu);
-  top = group_max_u32<32>(top);
-  if ((threadIdx.x & 31) == 0) tops[threadIdx.x >> 5] = top;
-  __syncthreads();
-  if (threadIdx.x == 0)
-    global_scales[blockIdx.x] = global_scale_from_amax_bits(max(max(tops[0], tops[1]), max(tops[2], tops[3])));
-}
-
-size_t smem_bytes(int vpt, int depth) {
-  return sizeof(uint4) * static_cast<size_t>(2 + depth) * vpt * kTeam + sizeof(TeamShared);
-}
-
-// Resident CTAs of `kernel` with `smem` bytes on the current device (0 = cannot be configured).
-// Cached per (device, kernel family, vectors per thread, depth): a pure function of them.
+// Lag and grid of one launch; false when the deferred scheme does not apply (a group so long that its
+// rows would not stay in L2 until they are quantised).
 template <typename K>
-int resident_ctas(K kernel, size_t smem, int family, int vpt, int depth) {
-  constexpr int kMaxDevices = 64;
-  static std::atomic<int> cache[kMaxDevices][2][9][kMaxDepth + 1];
-  static std::once_flag once;
-  std::call_once(once, [] {
-    for (auto& d : cache)
-      for (auto& f : d)
-        for (auto& v : f)
-          for (auto& e : v) e.store(-1);
-  });
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess) return 0;
-  const bool cacheable = dev >= 0 && dev < kMaxDevices;
-  if (cacheable) {
-    const int hit = cache[dev][family][vpt][depth].load();
-    if (hit >= 0) return hit;
-  }
-  int sms = 0, per_sm = 0, total = 0, limit = 0;
-  if (cudaDeviceGetAttribute(&limit, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) == cudaSuccess &&
-      smem <= static_cast<size_t>(limit) &&
-      cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, limit) == cudaSuccess &&
-      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess &&
-      cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kTeam, smem) == cudaSuccess)
-    total = sms * per_sm;
-  if (cacheable) cache[dev][family][vpt][depth].store(total);
-  return total;
+bool plan_launch(K kernel, size_t rows, size_t group_rows, size_t row_bytes, unsigned* lag_out, unsigned* grid_out) {
+  const size_t resident = host::resident_grid(kernel, kTeam);
+  const size_t lag = group_rows + resident;
+  if (lag * row_bytes > kMaxLagBytes || 2 * (rows + lag) > 0x7fffffffu) return false;
+  *lag_out = static_cast<unsigned>(lag);
+  *grid_out = static_cast<unsigned>(2 * (rows + lag));
+  return true;
 }
 
-// Picks the ring depth and grid: depth = 2 + ceil(group rows / teams) so that every row of the group
-// being quantised belongs to an iteration its owner has left behind; more ring slots cost shared
-// memory and so teams, hence the small search.  Returns false when no configuration fits.
-template <typename K>
-bool plan_launch(K kernel, int family, int vpt, size_t rows, size_t rows_per_group, int* depth_out,
-                 unsigned* grid_out, size_t* smem_out) {
-  for (int depth = 3; depth <= kMaxDepth; ++depth) {
-    const size_t smem = smem_bytes(vpt, depth);
-    const int cap = resident_ctas(kernel, smem, family, vpt, depth);
-    if (cap <= 0) return false;
-    const size_t grid = rows < static_cast<size_t>(cap) ? rows : static_cast<size_t>(cap);
-    const size_t group_rows = rows_per_group < rows ? rows_per_group : rows;
-    const size_t sweeps = (group_rows + grid - 1) / grid;  // iterations a group can reach past one of its rows
-    if (static_cast<size_t>(depth) >= 2 + sweeps) {
-      *depth_out = depth;
-      *grid_out = static_cast<unsigned>(grid);
-      *smem_out = smem;
-      return true;
-    }
-  }
-  return false;
-}
-
-template <typename K, typename... Args>
-bool launch_cooperative(K kernel, unsigned grid, size_t smem, cudaStream_t s, Args... args) {
-  void* params[] = {static_cast<void*>(&args)...};
-  return cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(kernel), dim3(grid), dim3(kTeam), params, smem,
-                                     s) == cudaSuccess;
+// One L2 line per group and per kind of word when the scratch has room for it (it has whenever a group
+// spans 64 rows or more): the amax and arrival words of different groups then live in different L2
+// slices instead of all on one hot line.
+Board make_board(uint32_t* scratch, size_t words, size_t groups, float* global_out, size_t rows, size_t group_rows,
+                 unsigned lag) {
+  const unsigned stride = 64 * groups + 1 <= words ? 32u : 1u;
+  return Board{scratch, scratch + groups * stride, scratch + words - 1, global_out, rows, group_rows, lag, stride};
 }
 
 }  // namespace
 
-// [0, rows) row words or [0, groups) group amax words, whichever path runs, + error word + spare
+// [0, groups) amax words, [groups, 2 groups) arrival counters, spare, error word; never fewer than
+// rows + 2 so that callers sized for one word per row keep working
 size_t fused_scratch_words(size_t rows, size_t groups) { return (rows > 2 * groups ? rows : 2 * groups) + 2; }
 
-// Both launchers return false when the fused path does not apply (shape, alignment, a group too long
-// for the ring, or the cooperative launch is refused); nothing has been enqueued then and the
-// caller takes the multi-kernel path.
+// Both launchers return false when the single-kernel path does not apply (shape, alignment, a group
+// too long to stay cached); nothing has been enqueued then and the caller takes the multi-kernel path.
 bool launch_residual_norm_nvfp4_fused(const uint16_t* left, const uint16_t* right, const uint16_t* weight,
                                       size_t tokens, size_t hidden, float eps, size_t rows_per_scale,
                                       uint16_t* residual_out, uint16_t* normalized_out, uint32_t* scratch,
@@ -411,10 +309,11 @@ bool launch_residual_norm_nvfp4_fused(const uint16_t* left, const uint16_t* righ
     return false;
   const int row_vectors = static_cast<int>(hidden / 8);
   const int vpt = (row_vectors + kTeam - 1) / kTeam;
-  const size_t rps = rows_per_scale ? rows_per_scale : tokens;
+  const size_t rps = rows_per_scale ? (rows_per_scale < tokens ? rows_per_scale : tokens) : tokens;
   const size_t groups = (tokens + rps - 1) / rps;
   const size_t words = fused_scratch_words(tokens, groups);
-  RowBoard board{scratch, scratch + words - 1, tokens, rps};
+  const bool coherent = residual_out == left || residual_out == right || normalized_out == left ||
+                        normalized_out == right;
   QuantOut q{reinterpret_cast<uint32_t*>(codes), scales,
              row_vectors % 32 == 0 && aligned16(scales) && (row_vectors / 2) % 16 == 0};
   const float width = static_cast<float>(hidden);
@@ -424,25 +323,20 @@ bool launch_residual_norm_nvfp4_fused(const uint16_t* left, const uint16_t* righ
   auto RO = reinterpret_cast<uint4*>(residual_out);
   auto NO = reinterpret_cast<uint4*>(normalized_out);
   bool ok = false;
-  int depth = 0;
-  unsigned grid = 0;
-  size_t smem = 0;
-#define Q3X_TRY(V)                                                                                             \
-  case V:                                                                                                      \
-    if (plan_launch(residual_norm_nvfp4_kernel<V>, 0, V, tokens, rps, &depth, &grid, &smem)) {                 \
-      cudaMemsetAsync(scratch, 0, words * sizeof(uint32_t), s);                                                \
-      ok = launch_cooperative(residual_norm_nvfp4_kernel<V>, grid, smem, s, L, R, W, row_vectors, width, eps,  \
-                              RO, NO, depth, board, q);                                                        \
-    }                                                                                                          \
+  unsigned lag = 0, grid = 0;
+#define Q3X_TRY(V)                                                                                              \
+  case V:                                                                                                       \
+    if (plan_launch(residual_norm_nvfp4_kernel<V>, tokens, rps, hidden * 2, &lag, &grid)) {                     \
+      cudaMemsetAsync(scratch, 0, words * sizeof(uint32_t), s);                                                 \
+      residual_norm_nvfp4_kernel<V><<<grid, kTeam, 0, s>>>(                                                     \
+          L, R, W, row_vectors, width, eps, RO, NO, coherent,                                                   \
+          make_board(scratch, words, groups, global_scales_out, tokens, rps, lag), q);                          \
+      ok = true;                                                                                                \
+    }                                                                                                           \
     break;
   switch (vpt) { Q3X_TRY(1) Q3X_TRY(2) Q3X_TRY(3) Q3X_TRY(4) Q3X_TRY(5) Q3X_TRY(6) Q3X_TRY(7) Q3X_TRY(8) }
 #undef Q3X_TRY
-  if (!ok) {
-    (void)cudaGetLastError();
-    return false;
-  }
-  finish_scales_kernel<<<static_cast<unsigned>(groups), kTeam, 0, s>>>(scratch, tokens, rps, global_scales_out);
-  return true;
+  return ok;
 }
 
 bool launch_gated_norm_nvfp4_fused(const uint16_t* in, const uint16_t* weight, const uint16_t* gate, size_t tokens,
@@ -452,17 +346,15 @@ bool launch_gated_norm_nvfp4_fused(const uint16_t* in, const uint16_t* weight, c
   using namespace host;
   const size_t cols = heads_per_row * dim;
   if (dim != Q3X_B200_GDN_HEAD_DIM || cols > 8192 || tokens == 0) return false;
-  // in-place forms would let a staged copy of the next row race with this row's stores
-  if (out == in || out == gate) return false;
   if (!aligned16(in) || !aligned16(gate) || !aligned16(weight) || !aligned16(out) ||
       (reinterpret_cast<uintptr_t>(codes) & 3u) != 0)
     return false;
   const int row_vectors = static_cast<int>(cols / 8);
   const int vpt = (row_vectors + kTeam - 1) / kTeam;
-  const size_t rps = rows_per_scale ? rows_per_scale : tokens;
+  const size_t rps = rows_per_scale ? (rows_per_scale < tokens ? rows_per_scale : tokens) : tokens;
   const size_t groups = (tokens + rps - 1) / rps;
   const size_t words = fused_scratch_words(tokens, groups);
-  RowBoard board{scratch, scratch + words - 1, tokens, rps};
+  const bool coherent = out == in || out == gate;
   QuantOut q{reinterpret_cast<uint32_t*>(codes), scales,
              row_vectors % 32 == 0 && aligned16(scales) && (row_vectors / 2) % 16 == 0};
   auto X = reinterpret_cast<const uint4*>(in);
@@ -470,25 +362,20 @@ bool launch_gated_norm_nvfp4_fused(const uint16_t* in, const uint16_t* weight, c
   auto W = reinterpret_cast<const uint4*>(weight);
   auto O = reinterpret_cast<uint4*>(out);
   bool ok = false;
-  int depth = 0;
-  unsigned grid = 0;
-  size_t smem = 0;
-#define Q3X_TRY(V)                                                                                          \
-  case V:                                                                                                   \
-    if (plan_launch(gated_norm_nvfp4_kernel<V>, 1, V, tokens, rps, &depth, &grid, &smem)) {                 \
-      cudaMemsetAsync(scratch, 0, words * sizeof(uint32_t), s);                                             \
-      ok = launch_cooperative(gated_norm_nvfp4_kernel<V>, grid, smem, s, X, Z, W, row_vectors, eps, O,      \
-                              depth, board, q);                                                             \
-    }                                                                                                       \
+  unsigned lag = 0, grid = 0;
+#define Q3X_TRY(V)                                                                                              \
+  case V:                                                                                                       \
+    if (plan_launch(gated_norm_nvfp4_kernel<V>, tokens, rps, cols * 2, &lag, &grid)) {                          \
+      cudaMemsetAsync(scratch, 0, words * sizeof(uint32_t), s);                                                 \
+      gated_norm_nvfp4_kernel<V><<<grid, kTeam, 0, s>>>(                                                        \
+          X, Z, W, row_vectors, eps, O, coherent,                                                               \
+          make_board(scratch, words, groups, global_scales_out, tokens, rps, lag), q);                          \
+      ok = true;                                                                                                \
+    }                                                                                                           \
     break;
   switch (vpt) { Q3X_TRY(1) Q3X_TRY(2) Q3X_TRY(3) Q3X_TRY(4) Q3X_TRY(5) Q3X_TRY(6) Q3X_TRY(7) Q3X_TRY(8) }
 #undef Q3X_TRY
-  if (!ok) {
-    (void)cudaGetLastError();
-    return false;
-  }
-  finish_scales_kernel<<<static_cast<unsigned>(groups), kTeam, 0, s>>>(scratch, tokens, rps, global_scales_out);
-  return true;
+  return ok;
 }
 
 }  // namespace q3x

@@ -78,10 +78,8 @@ __global__ void amax_to_scale_kernel(const uint32_t* amax_bits, size_t groups, f
 // ---- quantiser --------------------------------------------------------------------------
 
 // One CTA per row (grid-stride over rows).  kWideScales: the row's scale bytes are a multiple of 16
-// and 16-byte aligned, so they go out as 128-bit stores from shared memory.  VPT > 0: the row has at
-// most VPT * 128 vectors and a thread issues all of its loads before anything else (they are in flight
-// while the scale table is built); VPT == 0: rows of any length, streamed two vectors at a time.
-template <bool kWideScales, int VPT>
+// and 16-byte aligned, so they go out as 128-bit stores from shared memory.
+template <bool kWideScales>
 __global__ void __launch_bounds__(kRowThreads) nvfp4_quantize_rows_kernel(const uint4* __restrict__ in, size_t rows,
                                                                           int row_vectors, size_t rows_per_scale,
                                                                           const float* __restrict__ global_scales,
@@ -92,20 +90,8 @@ __global__ void __launch_bounds__(kRowThreads) nvfp4_quantize_rows_kernel(const 
   __shared__ __align__(16) uint8_t scale_bytes[kWideScales ? kMaxRowScaleBytes : 16];
   __shared__ float inv_table[kRowThreads];  // indexed by E4M3 code 0..127
   static_assert(kRowThreads == 128, "one thread per non-negative E4M3 code");
-  constexpr int kSteps = VPT > 0 ? VPT : 2;
   const int tid = threadIdx.x;
   for (size_t row = blockIdx.x; row < rows; row += gridDim.x) {
-    const uint4* src = in + row * static_cast<size_t>(row_vectors);
-    uint32_t* dst = codes + row * static_cast<size_t>(row_vectors);
-    uint8_t* srow = scales + row * static_cast<size_t>(row_vectors / 2);
-    uint4 x[kSteps];
-    if (VPT > 0) {
-#pragma unroll
-      for (int u = 0; u < kSteps; ++u) {
-        const int v = u * kRowThreads + tid;
-        x[u] = v < row_vectors ? ld_stream(src + v) : make_uint4(0, 0, 0, 0);
-      }
-    }
     const size_t group = rows_per_scale ? row / rows_per_scale : 0;
     float global;
     if (amax_bits != nullptr) {
@@ -120,25 +106,28 @@ __global__ void __launch_bounds__(kRowThreads) nvfp4_quantize_rows_kernel(const 
     __syncthreads();  // the previous row's readers of inv_table / scale_bytes are done
     inv_table[tid] = block_inverse(static_cast<uint32_t>(tid), global);
     __syncthreads();
-    // the loop bound is the same for all lanes of a warp, so the pair shuffle always has its partner
-    for (int base = 0; base < row_vectors; base += kSteps * kRowThreads) {
-      if (VPT == 0) {
+    const uint4* src = in + row * static_cast<size_t>(row_vectors);
+    uint32_t* dst = codes + row * static_cast<size_t>(row_vectors);
+    uint8_t* srow = scales + row * static_cast<size_t>(row_vectors / 2);
+    // the bound is the same for all lanes of a warp, so the pair shuffle always has its partner
+    for (int base = 0; base < row_vectors; base += 2 * kRowThreads) {
+      uint4 x[2];
+      bool valid[2];
 #pragma unroll
-        for (int u = 0; u < kSteps; ++u) {
-          const int v = base + u * kRowThreads + tid;
-          x[u] = v < row_vectors ? ld_stream(src + v) : make_uint4(0, 0, 0, 0);
-        }
+      for (int u = 0; u < 2; ++u) {
+        const int v = base + u * kRowThreads + tid;
+        valid[u] = v < row_vectors;  // lane pairs are valid together (row_vectors is even)
+        x[u] = valid[u] ? ld_stream(src + v) : make_uint4(0, 0, 0, 0);
       }
 #pragma unroll
-      for (int u = 0; u < kSteps; ++u) {
+      for (int u = 0; u < 2; ++u) {
         const int v = base + u * kRowThreads + tid;
-        const bool valid = v < row_vectors;  // lane pairs are valid together (row_vectors is even)
         float f[8];
         unpack8(x[u], f);
         float m = amax8_float(f, x[u]);
         m = fmaxf(m, __shfl_xor_sync(kFullMask, m, 1));
         const uint32_t s = block_scale_code(m, k);
-        if (valid) {
+        if (valid[u]) {
           dst[v] = quantize8(f, inv_table[s]);
           if ((tid & 1) == 0) {
             if (kWideScales) scale_bytes[v >> 1] = static_cast<uint8_t>(s);
@@ -255,25 +244,16 @@ void enqueue_quantize(const uint16_t* in, size_t rows, size_t cols, size_t rows_
     const bool wide = aligned16(scales) && (cols / 16) % 16 == 0 && cols / 16 <= kMaxRowScaleBytes;
     auto I = reinterpret_cast<const uint4*>(in);
     auto C = reinterpret_cast<uint32_t*>(codes);
-    const int vpt = row_vectors <= 6 * kRowThreads ? (row_vectors + kRowThreads - 1) / kRowThreads : 0;
-#define Q3X_QUANT(WIDE, V)                                                                                    \
-  nvfp4_quantize_rows_kernel<WIDE, V><<<wave_grid(nvfp4_quantize_rows_kernel<WIDE, V>, kRowThreads, rows, 1), \
-                                        kRowThreads, 0, s>>>(I, rows, row_vectors, rows_per_scale,            \
-                                                             global_scales, amax_bits, global_scales_out, C,  \
-                                                             scales)
-#define Q3X_QUANT_VPT(WIDE)                   \
-  switch (vpt) {                              \
-    case 1: Q3X_QUANT(WIDE, 1); break;        \
-    case 2: Q3X_QUANT(WIDE, 2); break;        \
-    case 3: Q3X_QUANT(WIDE, 3); break;        \
-    case 4: Q3X_QUANT(WIDE, 4); break;        \
-    case 5: Q3X_QUANT(WIDE, 5); break;        \
-    case 6: Q3X_QUANT(WIDE, 6); break;        \
-    default: Q3X_QUANT(WIDE, 0); break;       \
-  }
-    if (wide) { Q3X_QUANT_VPT(true) } else { Q3X_QUANT_VPT(false) }
-#undef Q3X_QUANT_VPT
-#undef Q3X_QUANT
+    if (wide)
+      nvfp4_quantize_rows_kernel<true><<<wave_grid(nvfp4_quantize_rows_kernel<true>, kRowThreads, rows, 1),
+                                         kRowThreads, 0, s>>>(I, rows, row_vectors, rows_per_scale,
+                                                                    global_scales, amax_bits, global_scales_out, C,
+                                                                    scales);
+    else
+      nvfp4_quantize_rows_kernel<false><<<wave_grid(nvfp4_quantize_rows_kernel<false>, kRowThreads, rows, 1),
+                                          kRowThreads, 0, s>>>(I, rows, row_vectors, rows_per_scale,
+                                                                     global_scales, amax_bits, global_scales_out, C,
+                                                                     scales);
   } else {
     const size_t blocks = rows * cols / 16;
     nvfp4_quantize_scalar_kernel<<<grid_for(blocks, kThreads, 8), kThreads, 0, s>>>(in, blocks, cols / 16,
@@ -357,12 +337,16 @@ extern "C" int q3x_b200_nvfp4_quantize_dynamic(const uint16_t* in, size_t rows, 
 
 namespace {
 
-// Shared body of the residual + norm + NVFP4 entry points.  single_pass: the cooperative kernel with
-// deferred quantisation; otherwise two kernels (norm with group amax, then the quantiser).
+// Which kernels an NVFP4 entry point may run: the single kernel with deferred quantisation
+// (fused_nvfp4.cu), or the norm kernel with group amax followed by the quantiser.  Same bytes either way.
+enum class Path { kAuto, kSingleKernel, kTwoKernels };
+
+// Shared body of the residual + norm + NVFP4 entry points.  kAuto takes the single kernel where it
+// applies and the two kernels otherwise; kSingleKernel refuses instead of falling back.
 int residual_norm_nvfp4(const uint16_t* left, const uint16_t* right, const uint16_t* weight, size_t tokens,
                         size_t hidden, float eps, size_t rows_per_scale, uint16_t* residual_out,
                         uint16_t* normalized_out, uint32_t* scratch, float* global_scales_out, uint8_t* codes,
-                        uint8_t* scales, void* stream, bool single_pass) {
+                        uint8_t* scales, void* stream, Path path) {
   bool done;
   int st = check_residual_norm(left, right, weight, tokens, hidden, eps, residual_out, normalized_out, &done);
   if (st != kOk) return st;
@@ -375,11 +359,11 @@ int residual_norm_nvfp4(const uint16_t* left, const uint16_t* right, const uint1
   const size_t groups = group_count(tokens, rows_per_scale);
   cudaStream_t s = as_stream(stream);
   clear_stale_error();
-  if (single_pass) {
-    if (!launch_residual_norm_nvfp4_fused(left, right, weight, tokens, hidden, eps, rows_per_scale, residual_out,
-                                          normalized_out, scratch, global_scales_out, codes, scales, s))
-      return kNotSupported;
-    return launch_status();
+  if (path != Path::kTwoKernels) {
+    if (launch_residual_norm_nvfp4_fused(left, right, weight, tokens, hidden, eps, rows_per_scale, residual_out,
+                                         normalized_out, scratch, global_scales_out, codes, scales, s))
+      return launch_status();
+    if (path == Path::kSingleKernel) return kNotSupported;
   }
   cudaMemsetAsync(scratch, 0, fused_scratch_words(tokens, groups) * sizeof(uint32_t), s);
   launch_norm_rows(NormMode::kCentered, left, right, weight, nullptr, tokens, hidden, eps, 1.0f, residual_out,
@@ -393,7 +377,7 @@ int residual_norm_nvfp4(const uint16_t* left, const uint16_t* right, const uint1
 int gated_norm_nvfp4(const uint16_t* in, const uint16_t* weight, const uint16_t* gate, size_t tokens,
                      size_t heads_per_row, size_t dim, float eps, size_t rows_per_scale, uint16_t* out,
                      uint32_t* scratch, float* global_scales_out, uint8_t* codes, uint8_t* scales, void* stream,
-                     bool single_pass) {
+                     Path path) {
   if (!valid_epsilon(eps)) return kInvalid;
   if (mul3_overflows(tokens, heads_per_row, dim) || mul_overflows(tokens * heads_per_row * dim, 2)) return kInvalid;
   const size_t cols = heads_per_row * dim;
@@ -415,11 +399,11 @@ int gated_norm_nvfp4(const uint16_t* in, const uint16_t* weight, const uint16_t*
   const size_t token_group = rows_per_scale ? rows_per_scale : tokens;
   cudaStream_t s = as_stream(stream);
   clear_stale_error();
-  if (single_pass) {
-    if (!launch_gated_norm_nvfp4_fused(in, weight, gate, tokens, heads_per_row, dim, eps, rows_per_scale, out,
-                                       scratch, global_scales_out, codes, scales, s))
-      return kNotSupported;
-    return launch_status();
+  if (path != Path::kTwoKernels) {
+    if (launch_gated_norm_nvfp4_fused(in, weight, gate, tokens, heads_per_row, dim, eps, rows_per_scale, out, scratch,
+                                      global_scales_out, codes, scales, s))
+      return launch_status();
+    if (path == Path::kSingleKernel) return kNotSupported;
   }
   cudaMemsetAsync(scratch, 0, fused_scratch_words(tokens, groups) * sizeof(uint32_t), s);
   launch_norm_rows(NormMode::kPlainSiluGate, in, nullptr, weight, gate, tokens * heads_per_row, dim, eps, 1.0f,
@@ -437,7 +421,7 @@ extern "C" int q3x_b200_residual_add_rms_norm_nvfp4(const uint16_t* left, const 
                                                     float* global_scales_out, uint8_t* codes, uint8_t* scales,
                                                     void* stream) {
   return residual_norm_nvfp4(left, right, weight, tokens, hidden, eps, rows_per_scale, residual_out, normalized_out,
-                             scratch, global_scales_out, codes, scales, stream, false);
+                             scratch, global_scales_out, codes, scales, stream, Path::kAuto);
 }
 
 extern "C" int q3x_b200_residual_add_rms_norm_nvfp4_single_pass(const uint16_t* left, const uint16_t* right,
@@ -447,7 +431,7 @@ extern "C" int q3x_b200_residual_add_rms_norm_nvfp4_single_pass(const uint16_t* 
                                                                 uint32_t* scratch, float* global_scales_out,
                                                                 uint8_t* codes, uint8_t* scales, void* stream) {
   return residual_norm_nvfp4(left, right, weight, tokens, hidden, eps, rows_per_scale, residual_out, normalized_out,
-                             scratch, global_scales_out, codes, scales, stream, true);
+                             scratch, global_scales_out, codes, scales, stream, Path::kSingleKernel);
 }
 
 extern "C" int q3x_b200_rms_norm_silu_gate_nvfp4(const uint16_t* in, const uint16_t* weight, const uint16_t* gate,
@@ -456,7 +440,7 @@ extern "C" int q3x_b200_rms_norm_silu_gate_nvfp4(const uint16_t* in, const uint1
                                                  float* global_scales_out, uint8_t* codes, uint8_t* scales,
                                                  void* stream) {
   return gated_norm_nvfp4(in, weight, gate, tokens, heads_per_row, dim, eps, rows_per_scale, out, scratch,
-                          global_scales_out, codes, scales, stream, false);
+                          global_scales_out, codes, scales, stream, Path::kAuto);
 }
 
 extern "C" int q3x_b200_rms_norm_silu_gate_nvfp4_single_pass(const uint16_t* in, const uint16_t* weight,
@@ -466,7 +450,7 @@ extern "C" int q3x_b200_rms_norm_silu_gate_nvfp4_single_pass(const uint16_t* in,
                                                              float* global_scales_out, uint8_t* codes,
                                                              uint8_t* scales, void* stream) {
   return gated_norm_nvfp4(in, weight, gate, tokens, heads_per_row, dim, eps, rows_per_scale, out, scratch,
-                          global_scales_out, codes, scales, stream, true);
+                          global_scales_out, codes, scales, stream, Path::kSingleKernel);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -528,7 +512,7 @@ extern "C" int q3x_b200_residual_add_rms_norm_nvfp4_static_scratch(
   if (scratch == nullptr) return status;
   // from here on this is the regular two-kernel path; it clears the scratch words it uses itself
   return residual_norm_nvfp4(left, right, weight, tokens, hidden, eps, rows_per_scale, residual_out, normalized_out,
-                             scratch, global_scales_out, codes, scales, stream, false);
+                             scratch, global_scales_out, codes, scales, stream, Path::kTwoKernels);
 }
 
 // Diagnostics: the two narrow conversions on their own, so that tests can sweep them against the

@@ -21,7 +21,7 @@ struct ResidualAdd {
   static __device__ __forceinline__ float apply(float l, float r) { return l + r; }
 };
 struct SiluMul {  // first operand = gate, second = up
-  static __device__ __forceinline__ float apply(float g, float u) { return silu(g) * u; }
+  static __device__ __forceinline__ float apply(float g, float u) { return silu_unscaled(g) * u; }
 };
 struct SigmoidGate {  // first operand = value, second = gate
   static __device__ __forceinline__ float apply(float v, float g) { return v * stable_sigmoid(g); }
