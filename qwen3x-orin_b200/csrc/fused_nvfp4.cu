@@ -34,11 +34,11 @@
 namespace q3x {
 namespace {
 
-constexpr int kTeam = 128;                   // threads of a CTA; they own one row per phase
+constexpr int kMaxWarps = 16;                // warps of the largest CTA shape
 // Resident CTAs per SM the kernels are compiled for.  The launch is latency-bound (half of the CTAs sit
 // on L2 round trips), so occupancy pays: eight CTAs (64 registers) for rows of up to 768 vectors,
 // measured 17 % faster than the five the compiler would pick; wider rows need the registers.
-constexpr int min_ctas_per_sm(int vpt) { return vpt <= 6 ? 8 : 5; }
+constexpr int min_ctas_per_sm(int team, int vpt) { return team == 128 && vpt <= 6 ? 8 : 5 * 128 / team; }
 constexpr int kSpinLimit = 1 << 20;          // polls of the arrival counter before giving up (~1 s)
 constexpr size_t kMaxLagBytes = 48u << 20;   // normalised bytes that may sit in L2 between the phases
 constexpr int kMaxRowScaleBytes = 512;       // block scales of one row (row_vectors / 2)
@@ -71,22 +71,25 @@ struct QuantOut {
 };
 
 struct TeamShared {
-  float sums[4];
-  uint32_t tops[4];
+  float sums[kMaxWarps];
+  uint32_t tops[kMaxWarps];
   uint32_t group_amax;
-  float inv_table[kTeam];  // indexed by E4M3 code 0..127
+  float inv_table[128];  // indexed by E4M3 code 0..127
   __align__(16) uint8_t scale_bytes[kMaxRowScaleBytes];
 };
 
 // Phase A epilogue.  The barrier orders every thread's stores of the row before thread 0's fence, the
 // fence orders them (and the amax atomic) before the arrival count at GPU scope.
+template <int WARPS>
 __device__ __forceinline__ void publish_row(const Board& board, TeamShared& ts, size_t row, float thread_top) {
   const uint32_t warp_top = group_max_u32<32>(amax_bits_of(thread_top));
   if ((threadIdx.x & 31) == 0) ts.tops[threadIdx.x >> 5] = warp_top;
   __syncthreads();
   if (threadIdx.x == 0) {
     const size_t slot = row / board.group_rows * board.stride;
-    const uint32_t m = max(max(ts.tops[0], ts.tops[1]), max(ts.tops[2], ts.tops[3]));
+    uint32_t m = 0;
+#pragma unroll
+    for (int w = 0; w < WARPS; ++w) m = max(m, ts.tops[w]);
     if (m != 0) atomicMax(board.amax + slot, m);
     __threadfence();
     atomicAdd(board.count + slot, 1u);
@@ -117,7 +120,7 @@ __device__ __forceinline__ uint32_t await_group_amax(const Board& board, TeamSha
 
 // Phase B: quantises one normalised row out of L2.  Thread tid owns vectors tid + k * 128; the loads
 // are issued first and are in flight while the reciprocal table of the row's global scale is built.
-template <int VPT>
+template <int TEAM, int VPT, bool FAST>
 __device__ __forceinline__ void quantize_cached_row(const uint4* row_in, int row_vectors, const Board& board,
                                                     TeamShared& ts, size_t row, uint32_t* codes_row,
                                                     uint8_t* scales_row, bool wide_scale_stores, uint64_t policy) {
@@ -127,18 +130,18 @@ __device__ __forceinline__ void quantize_cached_row(const uint4* row_in, int row
   uint4 y[VPT];
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
-    const int v = tid + i * kTeam;
-    y[i] = v < row_vectors ? ld_l2_once(row_in + v, policy) : make_uint4(0, 0, 0, 0);
+    const int v = tid + i * TEAM;
+    y[i] = FAST || v < row_vectors ? ld_l2_once(row_in + v, policy) : make_uint4(0, 0, 0, 0);
   }
   const float global = global_scale_from_amax_bits(amax_bits);
   if (tid == 0 && row == group * board.group_rows) board.global_out[group] = global;
   const float k = block_scale_factor(global);
-  ts.inv_table[tid] = block_inverse(static_cast<uint32_t>(tid), global);
+  if (tid < 128) ts.inv_table[tid] = block_inverse(static_cast<uint32_t>(tid), global);
   __syncthreads();
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
-    const int v = tid + i * kTeam;
-    const bool valid = v < row_vectors;  // lane pairs are valid together (row_vectors is even)
+    const int v = tid + i * TEAM;
+    const bool valid = FAST || v < row_vectors;  // lane pairs are valid together (row_vectors is even)
     float f[8];
     unpack8(y[i], f);
     float m = amax8_float(f, y[i]);
@@ -147,12 +150,12 @@ __device__ __forceinline__ void quantize_cached_row(const uint4* row_in, int row
     if (valid) {
       st_u32(codes_row + v, quantize8(f, ts.inv_table[s]), policy);
       if ((tid & 1) == 0) {
-        if (wide_scale_stores) ts.scale_bytes[v >> 1] = static_cast<uint8_t>(s);
+        if (FAST || wide_scale_stores) ts.scale_bytes[v >> 1] = static_cast<uint8_t>(s);
         else scales_row[v >> 1] = static_cast<uint8_t>(s);
       }
     }
   }
-  if (wide_scale_stores) {  // row_vectors / 2 bytes, a multiple of 16, written as 128-bit stores
+  if (FAST || wide_scale_stores) {  // row_vectors / 2 bytes, a multiple of 16, written as 128-bit stores
     __syncthreads();
     if (tid < row_vectors / 32)
       st_vec(reinterpret_cast<uint4*>(scales_row) + tid, reinterpret_cast<const uint4*>(ts.scale_bytes)[tid], policy);
@@ -160,28 +163,31 @@ __device__ __forceinline__ void quantize_cached_row(const uint4* row_in, int row
 }
 
 // Phase B of either kernel: CTA 2k + 1 quantises row k - lag of `normalized`.
-template <int VPT>
+template <int TEAM, int VPT, bool FAST>
 __device__ __forceinline__ void phase_b(const uint4* normalized, int row_vectors, const Board& board, TeamShared& ts,
                                         const QuantOut& q, uint64_t policy) {
   const size_t idx = blockIdx.x >> 1;
   if (idx < board.lag || idx - board.lag >= board.rows) return;
   const size_t row = idx - board.lag;
-  quantize_cached_row<VPT>(normalized + row * static_cast<size_t>(row_vectors), row_vectors, board, ts, row,
+  quantize_cached_row<TEAM, VPT, FAST>(normalized + row * static_cast<size_t>(row_vectors), row_vectors, board, ts, row,
                            q.codes + row * static_cast<size_t>(row_vectors),
                            q.scales + row * static_cast<size_t>(row_vectors / 2), q.wide_scale_stores, policy);
 }
 
 // ---- residual add + centred RMSNorm + NVFP4 ------------------------------------------------
 // `coherent`: an output aliases an input exactly (row i is read and written by the same CTA only).
-template <int VPT>
-__global__ void __launch_bounds__(kTeam, min_ctas_per_sm(VPT)) residual_norm_nvfp4_kernel(
+// FAST: the row fills the CTA exactly (row_vectors == TEAM * VPT), nothing aliases and the scale bytes go
+// out as 128-bit stores -- the bounds checks, zero fills and per-load branches of the general form
+// (a fifth of its instructions) are compiled out.
+template <int TEAM, int VPT, bool FAST>
+__global__ void __launch_bounds__(TEAM, min_ctas_per_sm(TEAM, VPT)) residual_norm_nvfp4_kernel(
     const uint4* left, const uint4* right, const uint4* __restrict__ weight, int row_vectors, float width, float eps,
     uint4* residual_out, uint4* normalized_out, bool coherent, Board board, QuantOut q) {
   __shared__ TeamShared ts;
   const int tid = threadIdx.x;
   const uint64_t policy = l2_evict_first_policy();
   if (blockIdx.x & 1u) {
-    phase_b<VPT>(normalized_out, row_vectors, board, ts, q, policy);
+    phase_b<TEAM, VPT, FAST>(normalized_out, row_vectors, board, ts, q, policy);
     return;
   }
   const size_t row = blockIdx.x >> 1;
@@ -190,15 +196,23 @@ __global__ void __launch_bounds__(kTeam, min_ctas_per_sm(VPT)) residual_norm_nvf
   uint4 x[VPT], r[VPT];
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
-    const int v = tid + i * kTeam;
-    x[i] = make_uint4(0, 0, 0, 0);
-    if (v < row_vectors) x[i] = coherent ? ld_vec(left + base + v) : ld_stream(left + base + v, policy);
+    const int v = tid + i * TEAM;
+    if (FAST) {
+      x[i] = ld_stream(left + base + v, policy);
+    } else {
+      x[i] = make_uint4(0, 0, 0, 0);
+      if (v < row_vectors) x[i] = coherent ? ld_vec(left + base + v) : ld_stream(left + base + v, policy);
+    }
   }
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
-    const int v = tid + i * kTeam;
-    r[i] = make_uint4(0, 0, 0, 0);
-    if (v < row_vectors) r[i] = coherent ? ld_vec(right + base + v) : ld_stream(right + base + v, policy);
+    const int v = tid + i * TEAM;
+    if (FAST) {
+      r[i] = ld_stream(right + base + v, policy);
+    } else {
+      r[i] = make_uint4(0, 0, 0, 0);
+      if (v < row_vectors) r[i] = coherent ? ld_vec(right + base + v) : ld_stream(right + base + v, policy);
+    }
   }
   float partial = 0.0f;
 #pragma unroll
@@ -209,36 +223,36 @@ __global__ void __launch_bounds__(kTeam, min_ctas_per_sm(VPT)) residual_norm_nvf
 #pragma unroll
     for (int j = 0; j < 8; ++j) a[j] = a[j] + b[j];
     x[i] = pack8(a);
-    const int v = tid + i * kTeam;
-    if (v < row_vectors) st_vec(residual_out + base + v, x[i], policy);
+    const int v = tid + i * TEAM;
+    if (FAST || v < row_vectors) st_vec(residual_out + base + v, x[i], policy);
     partial += sum_squares8(x[i]);
   }
-  const float total = block_sum<4>(partial, ts.sums);
+  const float total = block_sum<TEAM / 32>(partial, ts.sums);
   const float inv = inverse_rms(total, 1.0f / width, eps);
   float top = 0.0f;
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
-    const int v = tid + i * kTeam;
-    if (v < row_vectors) {
+    const int v = tid + i * TEAM;
+    if (FAST || v < row_vectors) {
       const uint4 y = scale8<NormMode::kCentered, true>(x[i], ld_weight(weight + v), make_uint4(0, 0, 0, 0), inv,
                                                         &top);
       st_vec(normalized_out + base + v, y);  // default policy: this is what phase B finds in L2
     }
   }
-  publish_row(board, ts, row, top);
+  publish_row<TEAM / 32>(board, ts, row, top);
 }
 
 // ---- gated RMSNorm * silu(z) over heads of 128 + NVFP4 ----------------------------------------
 // A row is one token: heads_per_row heads of 16 vectors; 16 consecutive lanes own one head.
-template <int VPT>
-__global__ void __launch_bounds__(kTeam, min_ctas_per_sm(VPT)) gated_norm_nvfp4_kernel(
+template <int TEAM, int VPT, bool FAST>
+__global__ void __launch_bounds__(TEAM, min_ctas_per_sm(TEAM, VPT)) gated_norm_nvfp4_kernel(
     const uint4* in, const uint4* gate, const uint4* __restrict__ weight, int row_vectors, float eps, uint4* out,
     bool coherent, Board board, QuantOut q) {
   __shared__ TeamShared ts;
   const int tid = threadIdx.x;
   const uint64_t policy = l2_evict_first_policy();
   if (blockIdx.x & 1u) {
-    phase_b<VPT>(out, row_vectors, board, ts, q, policy);
+    phase_b<TEAM, VPT, FAST>(out, row_vectors, board, ts, q, policy);
     return;
   }
   const size_t row = blockIdx.x >> 1;
@@ -248,32 +262,44 @@ __global__ void __launch_bounds__(kTeam, min_ctas_per_sm(VPT)) gated_norm_nvfp4_
   uint4 x[VPT], z[VPT];
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
-    const int v = tid + i * kTeam;
-    x[i] = z[i] = make_uint4(0, 0, 0, 0);
-    if (v < row_vectors) {
-      x[i] = coherent ? ld_vec(in + base + v) : ld_stream(in + base + v, policy);
-      z[i] = coherent ? ld_vec(gate + base + v) : ld_stream(gate + base + v, policy);
+    const int v = tid + i * TEAM;
+    if (FAST) {
+      x[i] = ld_stream(in + base + v, policy);
+      z[i] = ld_stream(gate + base + v, policy);
+    } else {
+      x[i] = z[i] = make_uint4(0, 0, 0, 0);
+      if (v < row_vectors) {
+        x[i] = coherent ? ld_vec(in + base + v) : ld_stream(in + base + v, policy);
+        z[i] = coherent ? ld_vec(gate + base + v) : ld_stream(gate + base + v, policy);
+      }
     }
   }
   float top = 0.0f;
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
-    const int v = tid + i * kTeam;
+    const int v = tid + i * TEAM;
     const float sum = group_sum<16>(sum_squares8(x[i]));  // every lane takes part; idle heads sum zeros
     const float inv = inverse_rms(sum, 1.0f / 128.0f, eps);
-    if (v < row_vectors) {
+    if (FAST || v < row_vectors) {
       const uint4 y = scale8<NormMode::kPlainSiluGate, true>(x[i], w, z[i], inv, &top);
       st_vec(out + base + v, y);
     }
   }
-  publish_row(board, ts, row, top);
+  publish_row<TEAM / 32>(board, ts, row, top);
 }
+
+// CTA shapes (threads, vectors per thread), tried in this order: the first one that holds a row wins.
+// 128 threads with the whole row in registers measured fastest for 5120- and 6144-wide rows; wider
+// CTAs with fewer vectors per thread (160 x 4, 256 x 3, 320 x 2) were 2 - 25 % slower.
+#define Q3X_FUSED_SHAPES Q3X_SHAPE(128, 1) Q3X_SHAPE(128, 2) Q3X_SHAPE(128, 3) Q3X_SHAPE(128, 4) Q3X_SHAPE(128, 5) \
+    Q3X_SHAPE(128, 6) Q3X_SHAPE(128, 7) Q3X_SHAPE(128, 8)
 
 // Lag and grid of one launch; false when the deferred scheme does not apply (a group so long that its
 // rows would not stay in L2 until they are quantised).
 template <typename K>
-bool plan_launch(K kernel, size_t rows, size_t group_rows, size_t row_bytes, unsigned* lag_out, unsigned* grid_out) {
-  const size_t resident = host::resident_grid(kernel, kTeam);
+bool plan_launch(K kernel, int team, size_t rows, size_t group_rows, size_t row_bytes, unsigned* lag_out,
+                 unsigned* grid_out) {
+  const size_t resident = host::resident_grid(kernel, team);
   const size_t lag = group_rows + resident;
   if (lag * row_bytes > kMaxLagBytes || 2 * (rows + lag) > 0x7fffffffu) return false;
   *lag_out = static_cast<unsigned>(lag);
@@ -308,7 +334,6 @@ bool launch_residual_norm_nvfp4_fused(const uint16_t* left, const uint16_t* righ
       !aligned16(normalized_out) || (reinterpret_cast<uintptr_t>(codes) & 3u) != 0)
     return false;
   const int row_vectors = static_cast<int>(hidden / 8);
-  const int vpt = (row_vectors + kTeam - 1) / kTeam;
   const size_t rps = rows_per_scale ? (rows_per_scale < tokens ? rows_per_scale : tokens) : tokens;
   const size_t groups = (tokens + rps - 1) / rps;
   const size_t words = fused_scratch_words(tokens, groups);
@@ -322,21 +347,24 @@ bool launch_residual_norm_nvfp4_fused(const uint16_t* left, const uint16_t* righ
   auto W = reinterpret_cast<const uint4*>(weight);
   auto RO = reinterpret_cast<uint4*>(residual_out);
   auto NO = reinterpret_cast<uint4*>(normalized_out);
-  bool ok = false;
   unsigned lag = 0, grid = 0;
-#define Q3X_TRY(V)                                                                                              \
-  case V:                                                                                                       \
-    if (plan_launch(residual_norm_nvfp4_kernel<V>, tokens, rps, hidden * 2, &lag, &grid)) {                     \
-      cudaMemsetAsync(scratch, 0, words * sizeof(uint32_t), s);                                                 \
-      residual_norm_nvfp4_kernel<V><<<grid, kTeam, 0, s>>>(                                                     \
-          L, R, W, row_vectors, width, eps, RO, NO, coherent,                                                   \
-          make_board(scratch, words, groups, global_scales_out, tokens, rps, lag), q);                          \
-      ok = true;                                                                                                \
-    }                                                                                                           \
-    break;
-  switch (vpt) { Q3X_TRY(1) Q3X_TRY(2) Q3X_TRY(3) Q3X_TRY(4) Q3X_TRY(5) Q3X_TRY(6) Q3X_TRY(7) Q3X_TRY(8) }
-#undef Q3X_TRY
-  return ok;
+#define Q3X_SHAPE(TEAM, V)                                                                                      \
+  if (row_vectors <= TEAM * V) {                                                                                \
+    if (!plan_launch(residual_norm_nvfp4_kernel<TEAM, V, true>, TEAM, tokens, rps, hidden * 2, &lag, &grid))          \
+      return false;                                                                                             \
+    cudaMemsetAsync(scratch, 0, words * sizeof(uint32_t), s);                                                   \
+    const Board board = make_board(scratch, words, groups, global_scales_out, tokens, rps, lag);                \
+    if (row_vectors == TEAM * V && !coherent && q.wide_scale_stores)                                            \
+      residual_norm_nvfp4_kernel<TEAM, V, true><<<grid, TEAM, 0, s>>>(L, R, W, row_vectors, width, eps, RO, NO, \
+                                                                      coherent, board, q);                      \
+    else                                                                                                        \
+      residual_norm_nvfp4_kernel<TEAM, V, false><<<grid, TEAM, 0, s>>>(L, R, W, row_vectors, width, eps, RO,    \
+                                                                       NO, coherent, board, q);                 \
+    return true;                                                                                                \
+  }
+  Q3X_FUSED_SHAPES
+#undef Q3X_SHAPE
+  return false;
 }
 
 bool launch_gated_norm_nvfp4_fused(const uint16_t* in, const uint16_t* weight, const uint16_t* gate, size_t tokens,
@@ -350,7 +378,6 @@ bool launch_gated_norm_nvfp4_fused(const uint16_t* in, const uint16_t* weight, c
       (reinterpret_cast<uintptr_t>(codes) & 3u) != 0)
     return false;
   const int row_vectors = static_cast<int>(cols / 8);
-  const int vpt = (row_vectors + kTeam - 1) / kTeam;
   const size_t rps = rows_per_scale ? (rows_per_scale < tokens ? rows_per_scale : tokens) : tokens;
   const size_t groups = (tokens + rps - 1) / rps;
   const size_t words = fused_scratch_words(tokens, groups);
@@ -361,21 +388,24 @@ bool launch_gated_norm_nvfp4_fused(const uint16_t* in, const uint16_t* weight, c
   auto Z = reinterpret_cast<const uint4*>(gate);
   auto W = reinterpret_cast<const uint4*>(weight);
   auto O = reinterpret_cast<uint4*>(out);
-  bool ok = false;
   unsigned lag = 0, grid = 0;
-#define Q3X_TRY(V)                                                                                              \
-  case V:                                                                                                       \
-    if (plan_launch(gated_norm_nvfp4_kernel<V>, tokens, rps, cols * 2, &lag, &grid)) {                          \
-      cudaMemsetAsync(scratch, 0, words * sizeof(uint32_t), s);                                                 \
-      gated_norm_nvfp4_kernel<V><<<grid, kTeam, 0, s>>>(                                                        \
-          X, Z, W, row_vectors, eps, O, coherent,                                                               \
-          make_board(scratch, words, groups, global_scales_out, tokens, rps, lag), q);                          \
-      ok = true;                                                                                                \
-    }                                                                                                           \
-    break;
-  switch (vpt) { Q3X_TRY(1) Q3X_TRY(2) Q3X_TRY(3) Q3X_TRY(4) Q3X_TRY(5) Q3X_TRY(6) Q3X_TRY(7) Q3X_TRY(8) }
-#undef Q3X_TRY
-  return ok;
+#define Q3X_SHAPE(TEAM, V)                                                                                      \
+  if (row_vectors <= TEAM * V) {                                                                                \
+    if (!plan_launch(gated_norm_nvfp4_kernel<TEAM, V, true>, TEAM, tokens, rps, cols * 2, &lag, &grid))         \
+      return false;                                                                                             \
+    cudaMemsetAsync(scratch, 0, words * sizeof(uint32_t), s);                                                   \
+    const Board board = make_board(scratch, words, groups, global_scales_out, tokens, rps, lag);                \
+    if (row_vectors == TEAM * V && !coherent && q.wide_scale_stores)                                            \
+      gated_norm_nvfp4_kernel<TEAM, V, true><<<grid, TEAM, 0, s>>>(X, Z, W, row_vectors, eps, O, coherent,      \
+                                                                   board, q);                                   \
+    else                                                                                                        \
+      gated_norm_nvfp4_kernel<TEAM, V, false><<<grid, TEAM, 0, s>>>(X, Z, W, row_vectors, eps, O, coherent,     \
+                                                                    board, q);                                  \
+    return true;                                                                                                \
+  }
+  Q3X_FUSED_SHAPES
+#undef Q3X_SHAPE
+  return false;
 }
 
 }  // namespace q3x
