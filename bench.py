@@ -35,6 +35,14 @@ METRIC = "prefill tokens/s through the fused layer-op chain (embedding + 64 laye
 UNIT = "tokens/s"
 
 
+# DRAM traffic of the dominant kernel (SwiGLU), from one ncu capture of an 8192-token launch:
+# dram__bytes.sum.per_second x gpu__time_duration = 803.1 MB read + written, i.e. 98035 bytes per token
+# against 104448 algorithmic ones (the tail of the output is still dirty in L2 when the kernel ends).
+# Traffic grows in proportion to the tokens, so a launch of T tokens is reported as this figure x T.
+SWIGLU_DRAM_BYTES_PER_TOKEN = 98035
+SWIGLU_TRAFFIC_SOURCE = "ncu, 8192-token launch scaled by tokens (profiles/layer_ops_8192_tokens_ncu_sections.md)"
+
+
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -430,7 +438,8 @@ def main():
         sw = per_op["swiglu"]
         roofline = {"bound": "hbm", "kernel": "binary_vec_kernel<SiluMul> (SwiGLU)", "achieved": sw["algorithmic_GBs"],
                     "peak": peak, "unit": "GB/s", "frac": round(sw["algorithmic_GBs"] / peak, 4), "peak_source": peak_kind,
-                    "traffic": None, "algorithmic_bytes_per_launch": chain.BYTES_PER_TOKEN["swiglu"] * T,
+                    "traffic": SWIGLU_DRAM_BYTES_PER_TOKEN * T, "traffic_source": SWIGLU_TRAFFIC_SOURCE,
+                    "algorithmic_bytes_per_launch": chain.BYTES_PER_TOKEN["swiglu"] * T,
                     "us_per_launch": sw["us"]}
         step_bytes = chain.bytes_per_token_per_step() * T
         roofline["whole_step"] = {"algorithmic_GBs": round(step_bytes / (ms_per_step * 1e-3) / 1e9, 1),
