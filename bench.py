@@ -535,6 +535,7 @@ def main():
                "sample": f"{args.cpu_sample_tokens} tokens x 4-layer pattern timed, x16 for 64 layers, + embedding gather "
                          f"({secs:.2f} s extrapolated per pass)"}
 
+    validation = validate_shards(rank, world, dist) if distributed else None
     if rank == 0:
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
@@ -543,11 +544,25 @@ def main():
             "roofline": roofline, "per_op": per_op, "cpu_baseline": cpu, "e2e": e2e,
             "gpu_launches": chain.kernels_per_step() * args.steps, "cuda_graph": graph is not None, "clocks": clocks,
         }
+        if validation is not None:
+            line["validation"] = validation
         print(json.dumps(line), flush=True)
     if distributed:
         dist.barrier()
         dist.destroy_process_group()
     return 0
+
+
+def validate_shards(rank, world, dist):
+    """Untimed: the shards' outputs all-gathered over NVLink and compared with an unsharded run."""
+    import torch
+
+    shard = importlib.import_module("qwen3x-orin_b200.shard")
+    report = shard.validate_sharded_chain(rank, world)
+    ok = torch.tensor([int(report["local_equals_unsharded"] and report["gathered_equals_unsharded"])], device="cuda")
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    report["all_ranks_bit_exact"] = bool(ok.item())
+    return report
 
 
 if __name__ == "__main__":

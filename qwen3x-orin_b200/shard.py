@@ -63,6 +63,8 @@ def gather_rows(local_rows, shard: Shard, total_tokens: int, group=None):
     import torch.distributed as dist
 
     world = shard.world
+    if world == 1:
+        return local_rows
     parts = partition(total_tokens, world)
     longest = max(p.tokens for p in parts)
     width = local_rows.shape[1]
@@ -71,3 +73,60 @@ def gather_rows(local_rows, shard: Shard, total_tokens: int, group=None):
     out = [torch.empty_like(padded) for _ in range(world)]
     dist.all_gather(out, padded, group=group)
     return torch.cat([o[:p.tokens] for o, p in zip(out, parts)], dim=0)
+
+
+def validate_sharded_chain(rank: int, world: int, tokens_per_rank: int = 1024, layers: int = 8, group=None) -> dict:
+    """Validation only (never timed): every rank runs the operator chain on its token shard of one
+    shared synthetic prompt, the shards' outputs are all-gathered over NCCL / NVLink, and each rank
+    compares them bit for bit with its own unsharded run of the whole prompt.  Checks the two
+    cross-row dependencies of the path: the conv halo (three raw rows before the shard) and the
+    NVFP4 scale groups (chunk-aligned shards never split one).  Returns a small report."""
+    import importlib
+
+    import torch
+
+    chain = importlib.import_module(__package__ + ".chain")
+    total = tokens_per_rank * world
+    me = shard_for(total, rank, world)
+    lo, hi = me.first_token, me.end_token
+    rows = 4096  # a small embedding table is enough here
+    whole = chain.LayerStack(total, first_position=0, seed=99, layers=layers, table_rows=rows)
+    local = chain.LayerStack(me.tokens, first_position=lo, seed=7, layers=layers, table_rows=rows)
+    # same prompt, same weights: the shard's inputs are row slices of the whole prompt's
+    for name in whole.inputs:
+        local.inputs[name].copy_(whole.inputs[name][lo:hi])
+    local.token_ids.copy_(whole.token_ids[lo:hi])
+    for name in ("table", "norm_w", "q_norm_w", "k_norm_w", "gdn_norm_w", "conv_w"):
+        setattr(local, name, getattr(whole, name))
+    if me.halo_first < lo:  # raw rows just before the shard become its conv history (oldest first)
+        halo = whole.inputs["conv_raw"][me.halo_first:lo].t().contiguous()
+        local.conv_hist[:, :, CONV_HALO - halo.shape[1]:] = halo[None]
+    stream = torch.cuda.current_stream().cuda_stream
+    final_whole = whole.residual[whole.enqueue_step(stream)]
+    final_local = local.residual[local.enqueue_step(stream)]
+    torch.cuda.synchronize()
+
+    def same(a, b):
+        return bool(torch.equal(a.contiguous().view(torch.uint8), b.contiguous().view(torch.uint8)))
+
+    first_group = lo // CHUNK
+    report = {
+        "tokens": total, "layers": layers, "rank_rows": [lo, hi],
+        "local_equals_unsharded": all([
+            same(final_local, final_whole[lo:hi]), same(local.normalized, whole.normalized[lo:hi]),
+            same(local.codes, whole.codes[lo:hi]), same(local.scales, whole.scales[lo:hi]),
+            same(local.conv_out, whole.conv_out[lo:hi]), same(local.gdn_out, whole.gdn_out[lo:hi]),
+            same(local.gdn_codes, whole.gdn_codes[lo:hi]), same(local.q_out, whole.q_out[lo:hi]),
+            same(local.attn_out, whole.attn_out[lo:hi]), same(local.mlp_out, whole.mlp_out[lo:hi]),
+            same(local.global_scales, whole.global_scales[first_group:first_group + local.groups]),
+        ]),
+    }
+    gathered_bytes = 0
+    ok = True
+    for mine, full in ((final_local, final_whole), (local.codes, whole.codes), (local.scales, whole.scales)):
+        gathered = gather_rows(mine, me, total, group)
+        gathered_bytes += gathered.numel() * gathered.element_size()
+        ok = ok and same(gathered, full)
+    report["gathered_bytes"] = gathered_bytes
+    report["gathered_equals_unsharded"] = ok
+    return report
