@@ -313,6 +313,8 @@ def probe_ops(stack, chain, stream_obj, T, peak, warm, reps):
         "attention_preprocess": lambda: stack.op_preprocess(3, stream),
         "sigmoid_gate": lambda: stack.op_sigmoid_gate(stream),
         "swiglu": lambda: stack.op_swiglu(stream),
+        # extra operator, not part of the step: SwiGLU with the NVFP4 operand of the down projection
+        "swiglu_nvfp4": lambda: stack.op_swiglu_nvfp4(stream),
     }
     per_op = {}
     with torch.cuda.stream(stream_obj):
@@ -331,6 +333,34 @@ def probe_ops(stack, chain, stream_obj, T, peak, warm, reps):
             per_op[name] = {"us": round(us, 2), "algorithmic_GBs": round(gbs, 1), "frac_of_peak": round(gbs / peak, 4),
                             "bytes_per_token": chain.BYTES_PER_TOKEN[base], "kernels": chain.KERNELS[base]}
     return per_op
+
+
+def decode_step_probe(chain, position=131071, reps=20):
+    """The same 64-layer operator chain for ONE token at `position` (batch-one decode runs on one GPU):
+    microseconds per step of a CUDA-graph replay.  Launch-latency bound, reported for completeness."""
+    import torch
+
+    stack = chain.LayerStack(1, first_position=position, seed=5, table_rows=8192)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        stack.enqueue_step(side.cuda_stream)
+    side.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        stack.enqueue_step(torch.cuda.current_stream().cuda_stream)
+    with torch.cuda.stream(side):
+        graph.replay()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(side)
+        for _ in range(reps):
+            graph.replay()
+        e1.record(side)
+    side.synchronize()
+    if int(stack.amax[-1].item()) != 0:
+        raise SystemExit("a bounded device-side wait gave up during the decode probe")
+    return {"tokens": 1, "position": position, "us_per_step": round(e0.elapsed_time(e1) * 1e3 / reps, 1),
+            "kernels_per_step": chain.kernels_per_step()}
 
 
 def main():
@@ -538,6 +568,7 @@ def main():
                "sample": f"{args.cpu_sample_tokens} tokens x 4-layer pattern timed, x16 for 64 layers, + embedding gather "
                          f"({secs:.2f} s extrapolated per pass)"}
 
+    decode = decode_step_probe(chain) if rank == 0 else None
     validation = validate_shards(rank, world, dist) if distributed else None
     if rank == 0:
         line = {
@@ -547,6 +578,7 @@ def main():
             "roofline": roofline, "per_op": per_op, "cpu_baseline": cpu, "e2e": e2e,
             "gpu_launches": chain.kernels_per_step() * args.steps, "cuda_graph": graph is not None, "clocks": clocks,
         }
+        line["decode_step"] = decode
         if validation is not None:
             line["validation"] = validation
         print(json.dumps(line), flush=True)

@@ -178,6 +178,18 @@ int q3x_b200_rms_norm_silu_gate_nvfp4_single_pass(const uint16_t* in, const uint
                                                   uint32_t* scratch, float* global_scales_out,
                                                   uint8_t* codes, uint8_t* scales, void* stream);
 
+/* SwiGLU (launch_silu_mul_reference_cuda, decode_ops.h:290-293) + NVFP4 of its output, the operand
+ * of the MLP down projection: out = bf16(silu(gate) * up) over [tokens, intermediate], then codes
+ * [tokens, intermediate / 2], block scales [tokens, intermediate / 16] and one global scale per
+ * rows_per_scale rows, derived from `out` bit for bit.  out may be exactly gate or exactly up.
+ * One kernel where a scale group is a whole number of 4096-element chunks and short enough to wait
+ * in L2 (17408 x 512 is), else three (SwiGLU, group amax, quantiser).  Scratch and error word as
+ * above.  The quantisation half has no counterpart in the reference. */
+int q3x_b200_silu_mul_nvfp4(const uint16_t* gate, const uint16_t* up, size_t tokens,
+                            size_t intermediate, size_t rows_per_scale, uint16_t* out,
+                            uint32_t* scratch, float* global_scales_out, uint8_t* codes,
+                            uint8_t* scales, void* stream);
+
 /* No counterpart in the reference.  q3x_b200_residual_add_rms_norm_nvfp4 for callers that cannot
  * hand over scratch memory because they cannot allocate any: code that runs while a stream is being
  * captured into a CUDA graph or inside a stream callback, a plugin whose host gives it the input

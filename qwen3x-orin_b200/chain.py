@@ -42,12 +42,15 @@ BYTES_PER_TOKEN = {
     "attention_preprocess": (2 * Q_HEADS + KV_HEADS) * HEAD_DIM * 2 + 256 + (2 * Q_HEADS + KV_HEADS) * HEAD_DIM * 2,
     "sigmoid_gate": 3 * Q_HEADS * HEAD_DIM * 2,
     "swiglu": 3 * INTERMEDIATE * 2,
+    # not part of the step (the benchmark configurations quantise the norm outputs only): SwiGLU with
+    # the NVFP4 operand of the down projection produced in the same kernel
+    "swiglu_nvfp4": 3 * INTERMEDIATE * 2 + INTERMEDIATE // 2 + INTERMEDIATE // 16,
 }
 # kernels each entry point launches (memset nodes not counted); the norm + NVFP4 entries run their
 # single-kernel form at the chain's scale scope of 512 tokens
 KERNELS = {
     "embedding_gather": 1, "residual_rmsnorm_nvfp4": 1, "conv1d_silu_l2norm": 1, "gated_rmsnorm_nvfp4": 1,
-    "attention_preprocess": 1, "sigmoid_gate": 1, "swiglu": 1,
+    "attention_preprocess": 1, "sigmoid_gate": 1, "swiglu": 1, "swiglu_nvfp4": 1,
 }
 GDN_OPS = ["residual_rmsnorm_nvfp4", "conv1d_silu_l2norm", "gated_rmsnorm_nvfp4", "residual_rmsnorm_nvfp4", "swiglu"]
 FA_OPS = ["residual_rmsnorm_nvfp4", "attention_preprocess", "sigmoid_gate", "residual_rmsnorm_nvfp4", "swiglu"]
@@ -184,6 +187,15 @@ class LayerStack:
     def op_swiglu(self, stream):
         capi.check("q3x_b200_silu_mul", self.inputs["mlp_gate"], self.inputs["mlp_up"], self.tokens * INTERMEDIATE,
                    self.mlp_out, stream)
+
+    def op_swiglu_nvfp4(self, stream):
+        """SwiGLU + NVFP4 of its output (extra operator, not in the step); allocates its code buffers once."""
+        if not hasattr(self, "mlp_codes"):
+            dev = self.mlp_out.device
+            self.mlp_codes = torch.empty((self.tokens, INTERMEDIATE // 2), device=dev, dtype=torch.uint8)
+            self.mlp_scales = torch.empty((self.tokens, INTERMEDIATE // 16), device=dev, dtype=torch.uint8)
+        capi.check("q3x_b200_silu_mul_nvfp4", self.inputs["mlp_gate"], self.inputs["mlp_up"], self.tokens, INTERMEDIATE,
+                   CHUNK, self.mlp_out, self.amax, self.global_scales, self.mlp_codes, self.mlp_scales, stream)
 
     # ---- the whole step ------------------------------------------------------------------------
     def enqueue_step(self, stream) -> int:

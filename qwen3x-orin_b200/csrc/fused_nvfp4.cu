@@ -288,6 +288,63 @@ __global__ void __launch_bounds__(TEAM, min_ctas_per_sm(TEAM, VPT)) gated_norm_n
   publish_row<TEAM / 32>(board, ts, row, top);
 }
 
+// ---- SwiGLU + NVFP4 ---------------------------------------------------------------------------
+// silu(gate) * up is pointwise, so the unit of work is not a row but a CHUNK of TEAM * VPT consecutive
+// vectors of the flattened [tokens, intermediate] tensor; the launcher only takes this path when a full
+// scale group is a whole number of chunks, so a chunk belongs to exactly one group.  Everything else
+// (roles, lag, arrival counters) is the scheme above with "row" read as "chunk".  `count` is the number
+// of valid vectors of the tensor; only the last chunk can be short.
+template <int TEAM, int VPT, bool FAST>
+__global__ void __launch_bounds__(TEAM, min_ctas_per_sm(TEAM, VPT)) silu_mul_nvfp4_kernel(
+    const uint4* gate, const uint4* up, uint4* out, size_t count, bool coherent, Board board, QuantOut q) {
+  __shared__ TeamShared ts;
+  constexpr int kChunk = TEAM * VPT;
+  const int tid = threadIdx.x;
+  const uint64_t policy = l2_evict_first_policy();
+  const size_t idx = blockIdx.x >> 1;
+  if (blockIdx.x & 1u) {
+    if (idx < board.lag || idx - board.lag >= board.rows) return;
+    const size_t chunk = idx - board.lag;
+    const size_t base = chunk * kChunk;
+    const int n = FAST ? kChunk : static_cast<int>(min(static_cast<size_t>(kChunk), count - base));
+    quantize_cached_row<TEAM, VPT, FAST>(out + base, n, board, ts, chunk, q.codes + base, q.scales + base / 2,
+                                         q.wide_scale_stores, policy);
+    return;
+  }
+  if (idx >= board.rows) return;
+  const size_t base = idx * kChunk;
+  const int n = FAST ? kChunk : static_cast<int>(min(static_cast<size_t>(kChunk), count - base));
+  uint4 g[VPT], u[VPT];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = tid + i * TEAM;
+    if (FAST) {
+      g[i] = ld_stream(gate + base + v, policy);
+      u[i] = ld_stream(up + base + v, policy);
+    } else {
+      g[i] = u[i] = make_uint4(0, 0, 0, 0);
+      if (v < n) {
+        g[i] = coherent ? ld_vec(gate + base + v) : ld_stream(gate + base + v, policy);
+        u[i] = coherent ? ld_vec(up + base + v) : ld_stream(up + base + v, policy);
+      }
+    }
+  }
+  float top = 0.0f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = tid + i * TEAM;
+    float a[8], b[8];
+    unpack8(g[i], a);
+    unpack8(u[i], b);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) a[j] = silu_unscaled(a[j]) * b[j];
+    const uint4 y = pack8(a);
+    top = fmaxf(top, amax8_float(a, y));
+    if (FAST || v < n) st_vec(out + base + v, y);  // default policy: phase B finds it in L2
+  }
+  publish_row<TEAM / 32>(board, ts, idx, top);
+}
+
 // CTA shapes (threads, vectors per thread), tried in this order: the first one that holds a row wins.
 // 128 threads with the whole row in registers measured fastest for 5120- and 6144-wide rows; wider
 // CTAs with fewer vectors per thread (160 x 4, 256 x 3, 320 x 2) were 2 - 25 % slower.
@@ -406,6 +463,44 @@ bool launch_gated_norm_nvfp4_fused(const uint16_t* in, const uint16_t* weight, c
   Q3X_FUSED_SHAPES
 #undef Q3X_SHAPE
   return false;
+}
+
+// SwiGLU + NVFP4 over [tokens, intermediate]; chunks of 512 vectors (4096 elements).  False when the
+// shape does not fit the chunk scheme (a scale group that is not a whole number of chunks, misaligned
+// pointers); the caller then runs the separate kernels.
+bool launch_silu_mul_nvfp4_fused(const uint16_t* gate, const uint16_t* up, size_t tokens, size_t intermediate,
+                                 size_t rows_per_scale, uint16_t* out, uint32_t* scratch, float* global_scales_out,
+                                 uint8_t* codes, uint8_t* scales, cudaStream_t s) {
+  using namespace host;
+  constexpr int kTeam = 128, kVpt = 4, kChunk = kTeam * kVpt;
+  if (tokens == 0 || intermediate % 16 != 0) return false;
+  if (!aligned16(gate) || !aligned16(up) || !aligned16(out) || (reinterpret_cast<uintptr_t>(codes) & 3u) != 0)
+    return false;
+  const size_t row_vectors = intermediate / 8;
+  const size_t rps = rows_per_scale ? (rows_per_scale < tokens ? rows_per_scale : tokens) : tokens;
+  const size_t groups = (tokens + rps - 1) / rps;
+  const size_t group_vectors = rps * row_vectors;
+  if (groups > 1 && group_vectors % kChunk != 0) return false;
+  const size_t count = tokens * row_vectors;
+  const size_t chunks_per_group = (group_vectors + kChunk - 1) / kChunk;
+  const size_t chunks = (count + kChunk - 1) / kChunk;
+  const size_t words = fused_scratch_words(tokens, groups);
+  const bool coherent = out == gate || out == up;
+  const bool full = count % kChunk == 0;
+  QuantOut q{reinterpret_cast<uint32_t*>(codes), scales, aligned16(scales) && (count % kChunk) % 32 == 0};
+  unsigned lag = 0, grid = 0;
+  if (!plan_launch(silu_mul_nvfp4_kernel<kTeam, kVpt, true>, kTeam, chunks, chunks_per_group, kChunk * 16, &lag, &grid))
+    return false;
+  cudaMemsetAsync(scratch, 0, words * sizeof(uint32_t), s);
+  const Board board = make_board(scratch, words, groups, global_scales_out, chunks, chunks_per_group, lag);
+  auto G = reinterpret_cast<const uint4*>(gate);
+  auto U = reinterpret_cast<const uint4*>(up);
+  auto O = reinterpret_cast<uint4*>(out);
+  if (full && !coherent && q.wide_scale_stores)
+    silu_mul_nvfp4_kernel<kTeam, kVpt, true><<<grid, kTeam, 0, s>>>(G, U, O, count, coherent, board, q);
+  else
+    silu_mul_nvfp4_kernel<kTeam, kVpt, false><<<grid, kTeam, 0, s>>>(G, U, O, count, coherent, board, q);
+  return true;
 }
 
 }  // namespace q3x

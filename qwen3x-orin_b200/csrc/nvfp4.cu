@@ -434,6 +434,37 @@ extern "C" int q3x_b200_residual_add_rms_norm_nvfp4_single_pass(const uint16_t* 
                              scratch, global_scales_out, codes, scales, stream, Path::kSingleKernel);
 }
 
+extern "C" int q3x_b200_silu_mul_nvfp4(const uint16_t* gate, const uint16_t* up, size_t tokens, size_t intermediate,
+                                       size_t rows_per_scale, uint16_t* out, uint32_t* scratch,
+                                       float* global_scales_out, uint8_t* codes, uint8_t* scales, void* stream) {
+  if (mul3_overflows(tokens, intermediate, sizeof(uint16_t))) return kInvalid;
+  if (intermediate % Q3X_B200_NVFP4_BLOCK != 0) return kInvalid;
+  if (tokens == 0 || intermediate == 0) return kOk;
+  if (gate == nullptr || up == nullptr || out == nullptr || scratch == nullptr || global_scales_out == nullptr)
+    return kInvalid;
+  const size_t bytes = tokens * intermediate * sizeof(uint16_t);
+  const Span sg = span(gate, bytes), su = span(up, bytes), so = span(out, bytes);
+  // out may be exactly gate or exactly up (the reference's in-place form); any partial overlap is refused
+  if (wraps(sg) || wraps(su) || wraps(so) || partial_overlap(so, sg) || partial_overlap(so, su)) return kInvalid;
+  int st = check_quant_outputs(out, tokens, intermediate, codes, scales);
+  if (st != kOk) return st;
+  if (overlap(sg, span(codes, bytes / 4)) || overlap(su, span(codes, bytes / 4)) ||
+      overlap(sg, span(scales, bytes / 32)) || overlap(su, span(scales, bytes / 32)))
+    return kInvalid;
+  cudaStream_t s = as_stream(stream);
+  clear_stale_error();
+  if (launch_silu_mul_nvfp4_fused(gate, up, tokens, intermediate, rows_per_scale, out, scratch, global_scales_out,
+                                  codes, scales, s))
+    return launch_status();
+  // separate kernels: SwiGLU, group amax of its output, quantiser
+  st = q3x_b200_silu_mul(gate, up, tokens * intermediate, out, stream);
+  if (st != kOk) return st;
+  cudaMemsetAsync(scratch, 0, fused_scratch_words(tokens, group_count(tokens, rows_per_scale)) * sizeof(uint32_t), s);
+  enqueue_amax(out, tokens, intermediate, rows_per_scale, scratch, s);
+  enqueue_quantize(out, tokens, intermediate, rows_per_scale, nullptr, scratch, global_scales_out, codes, scales, s);
+  return launch_status();
+}
+
 extern "C" int q3x_b200_rms_norm_silu_gate_nvfp4(const uint16_t* in, const uint16_t* weight, const uint16_t* gate,
                                                  size_t tokens, size_t heads_per_row, size_t dim, float eps,
                                                  size_t rows_per_scale, uint16_t* out, uint32_t* scratch,

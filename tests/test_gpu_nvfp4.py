@@ -200,3 +200,63 @@ def test_gated_norm_nvfp4(g, tokens, rps, single_pass):
     assert np.array_equal(gs.get().view(np.uint32), want_g.view(np.uint32))
     g.assert_bits_equal(scales.get(), want_s, "block scales")
     g.assert_bits_equal(codes.get(), want_c, "codes")
+
+
+@pytest.mark.parametrize("tokens,inter,rps", [(1, 17408, 512), (3, 17408, 0), (64, 17408, 512), (512, 17408, 512),
+                                              (600, 17408, 512), (1030, 17408, 512), (40, 4096, 8), (33, 1040, 16),
+                                              (2000, 17408, 0), (96, 512, 32)])
+def test_silu_mul_nvfp4(g, tokens, inter, rps):
+    rng = np.random.default_rng([tokens, inter, rps, 5])
+    gate, up = fx.normal_bf16(rng, (tokens, inter)), fx.normal_bf16(rng, (tokens, inter))
+    if tokens >= 33:
+        fx.sprinkle_specials(rng, gate[-2:], 0.002)
+    groups = 1 if rps == 0 else (tokens + rps - 1) // rps
+    dg, du = g.Dev(gate), g.Dev(up)
+    out = g.empty_like_dev((tokens, inter))
+    scratch = g.scratch_for(tokens, rps, fill=0x13572468)
+    gs = g.empty_like_dev((groups,), dtype=np.float32)
+    codes = g.empty_like_dev((tokens, inter // 2), dtype=np.uint8)
+    scales = g.empty_like_dev((tokens, inter // 16), dtype=np.uint8)
+    g.capi.check("q3x_b200_silu_mul_nvfp4", dg, du, tokens, inter, rps, out, scratch, gs, codes, scales, None)
+    g.sync()
+    assert scratch.get()[-1] == 0, "a bounded wait inside the kernel gave up"
+    got = out.get()
+    g.assert_bf16_within(got, orc.silu_mul(gate, up), 1, 0.98, "SwiGLU")
+    # the same bytes as the stand-alone SwiGLU entry, and codes / scales derived from them bit for bit
+    plain = g.empty_like_dev((tokens, inter))
+    g.capi.check("q3x_b200_silu_mul", dg, du, tokens * inter, plain, None)
+    g.sync()
+    g.assert_bits_equal(got, plain.get(), "fused SwiGLU == stand-alone SwiGLU")
+    want_c, want_s, want_g = orc.nvfp4_quantize(got, rps)
+    assert np.array_equal(gs.get().view(np.uint32), want_g.view(np.uint32)), "global scales"
+    g.assert_bits_equal(scales.get(), want_s, "block scales")
+    g.assert_bits_equal(codes.get(), want_c, "codes")
+    for d in (out, codes, scales, gs, scratch):
+        assert d.guards_intact()
+    assert np.array_equal(dg.get(), gate) and np.array_equal(du.get(), up)
+
+
+def test_silu_mul_nvfp4_in_place_and_rejections(g):
+    rng = np.random.default_rng(77)
+    tokens, inter = 520, 17408
+    gate, up = fx.normal_bf16(rng, (tokens, inter)), fx.normal_bf16(rng, (tokens, inter))
+    dg, du = g.Dev(gate), g.Dev(up)
+    scratch = g.scratch_for(tokens, 512)
+    gs = g.empty_like_dev((2,), dtype=np.float32)
+    codes = g.empty_like_dev((tokens, inter // 2), dtype=np.uint8)
+    scales = g.empty_like_dev((tokens, inter // 16), dtype=np.uint8)
+    g.capi.check("q3x_b200_silu_mul_nvfp4", dg, du, tokens, inter, 512, dg, scratch, gs, codes, scales, None)  # out == gate
+    g.sync()
+    got = dg.get()
+    g.assert_bf16_within(got, orc.silu_mul(gate, up), 1, 0.98, "in-place SwiGLU")
+    want_c, want_s, want_g = orc.nvfp4_quantize(got, 512)
+    g.assert_bits_equal(codes.get(), want_c, "codes")
+    g.assert_bits_equal(scales.get(), want_s, "scales")
+    assert np.array_equal(gs.get().view(np.uint32), want_g.view(np.uint32))
+    # host-visible argument errors are refused before anything is enqueued
+    inv = g.capi.CUDA_ERROR_INVALID_VALUE
+    assert g.capi.call("q3x_b200_silu_mul_nvfp4", dg, du, tokens, 17400, 512, dg, scratch, gs, codes, scales, None) == inv
+    assert g.capi.call("q3x_b200_silu_mul_nvfp4", dg, du, tokens, inter, 512, dg.ptr_at(8), scratch, gs, codes, scales,
+                       None) == inv
+    assert g.capi.call("q3x_b200_silu_mul_nvfp4", dg, du, tokens, inter, 512, None, scratch, gs, codes, scales, None) == inv
+    assert g.capi.call("q3x_b200_silu_mul_nvfp4", None, None, 0, inter, 512, None, None, None, None, None, None) == 0
