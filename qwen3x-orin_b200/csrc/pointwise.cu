@@ -14,16 +14,26 @@ namespace q3x {
 namespace {
 
 constexpr int kThreads = 256;
-constexpr int kUnroll = 4;
 
 // ---- element functors: the arithmetic of src/runtime/reference/decode_ops.cpp:268-342 ----
+// kDepth = independent 128-bit loads per operand a thread keeps in flight; kStreamingStore = the output
+// goes out with st.global.cs.  Both are per operator because they were measured per operator at 16384
+// tokens: SwiGLU runs 272 -> 257 us with depth 2 and streaming stores (depth 1: 298 us, depth 4 or 8 with
+// streaming stores: 266 - 269 us), the sigmoid gate is fastest as it is (depth 4, plain stores: 100 us
+// against 104 us for depth 2 with streaming stores).
 struct ResidualAdd {
+  static constexpr int kDepth = 4;
+  static constexpr bool kStreamingStore = false;
   static __device__ __forceinline__ float apply(float l, float r) { return l + r; }
 };
 struct SiluMul {  // first operand = gate, second = up
+  static constexpr int kDepth = 2;
+  static constexpr bool kStreamingStore = true;
   static __device__ __forceinline__ float apply(float g, float u) { return silu_unscaled(g) * u; }
 };
 struct SigmoidGate {  // first operand = value, second = gate
+  static constexpr int kDepth = 4;
+  static constexpr bool kStreamingStore = false;
   static __device__ __forceinline__ float apply(float v, float g) { return v * stable_sigmoid(g); }
 };
 
@@ -42,22 +52,27 @@ template <class Op, bool kInPlace>
 __global__ void __launch_bounds__(kThreads) binary_vec_kernel(const uint4* __restrict__ a,
                                                               const uint4* __restrict__ b,
                                                               uint4* out, size_t nvec) {
+  constexpr int kDepth = Op::kDepth;
+  auto store = [](uint4* p, const uint4& v) {
+    if (Op::kStreamingStore) st_stream(p, v);
+    else st_vec(p, v);
+  };
   const size_t stride = static_cast<size_t>(gridDim.x) * kThreads;
   size_t i = static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x;
-  for (; i + (kUnroll - 1) * stride < nvec; i += kUnroll * stride) {
-    uint4 va[kUnroll], vb[kUnroll];
+  for (; i + (kDepth - 1) * stride < nvec; i += kDepth * stride) {
+    uint4 va[kDepth], vb[kDepth];
 #pragma unroll
-    for (int k = 0; k < kUnroll; ++k) {
+    for (int k = 0; k < kDepth; ++k) {
       va[k] = kInPlace ? ld_vec(a + i + k * stride) : ld_stream(a + i + k * stride);
       vb[k] = kInPlace ? ld_vec(b + i + k * stride) : ld_stream(b + i + k * stride);
     }
 #pragma unroll
-    for (int k = 0; k < kUnroll; ++k) st_vec(out + i + k * stride, apply8<Op>(va[k], vb[k]));
+    for (int k = 0; k < kDepth; ++k) store(out + i + k * stride, apply8<Op>(va[k], vb[k]));
   }
   for (; i < nvec; i += stride) {
     const uint4 va = kInPlace ? ld_vec(a + i) : ld_stream(a + i);
     const uint4 vb = kInPlace ? ld_vec(b + i) : ld_stream(b + i);
-    st_vec(out + i, apply8<Op>(va, vb));
+    store(out + i, apply8<Op>(va, vb));
   }
 }
 
@@ -76,10 +91,10 @@ __global__ void __launch_bounds__(kThreads) silu_mul_merged_vec_kernel(const uin
                                                                        unsigned vectors_per_row) {
   const size_t stride = static_cast<size_t>(gridDim.x) * kThreads;
   size_t i = static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x;
-  for (; i < nvec; i += kUnroll * stride) {
-    uint4 g[kUnroll], u[kUnroll];
+  for (; i < nvec; i += SiluMul::kDepth * stride) {
+    uint4 g[SiluMul::kDepth], u[SiluMul::kDepth];
 #pragma unroll
-    for (int k = 0; k < kUnroll; ++k) {
+    for (int k = 0; k < SiluMul::kDepth; ++k) {
       const size_t j = i + k * stride;
       if (j < nvec) {
         const size_t row = j / vectors_per_row;
@@ -90,9 +105,9 @@ __global__ void __launch_bounds__(kThreads) silu_mul_merged_vec_kernel(const uin
       }
     }
 #pragma unroll
-    for (int k = 0; k < kUnroll; ++k) {
+    for (int k = 0; k < SiluMul::kDepth; ++k) {
       const size_t j = i + k * stride;
-      if (j < nvec) st_vec(out + j, apply8<SiluMul>(g[k], u[k]));
+      if (j < nvec) st_stream(out + j, apply8<SiluMul>(g[k], u[k]));
     }
   }
 }
@@ -146,12 +161,12 @@ int launch_binary(const uint16_t* a, const uint16_t* b, size_t count, uint16_t* 
   if (aligned16(a) && aligned16(b) && aligned16(out) && count >= 8) {
     const size_t nvec = count / 8;
     if (in_place)
-      binary_vec_kernel<Op, true><<<wave_grid(binary_vec_kernel<Op, true>, kThreads, nvec, kThreads * kUnroll),
+      binary_vec_kernel<Op, true><<<wave_grid(binary_vec_kernel<Op, true>, kThreads, nvec, kThreads * Op::kDepth),
                                     kThreads, 0, s>>>(reinterpret_cast<const uint4*>(a),
                                                             reinterpret_cast<const uint4*>(b),
                                                             reinterpret_cast<uint4*>(out), nvec);
     else
-      binary_vec_kernel<Op, false><<<wave_grid(binary_vec_kernel<Op, false>, kThreads, nvec, kThreads * kUnroll),
+      binary_vec_kernel<Op, false><<<wave_grid(binary_vec_kernel<Op, false>, kThreads, nvec, kThreads * Op::kDepth),
                                      kThreads, 0, s>>>(reinterpret_cast<const uint4*>(a),
                                                              reinterpret_cast<const uint4*>(b),
                                                              reinterpret_cast<uint4*>(out), nvec);
@@ -197,7 +212,7 @@ extern "C" int q3x_b200_silu_mul_merged(const uint16_t* merged, size_t tokens, s
   clear_stale_error();
   if (intermediate % 8 == 0 && intermediate / 8 <= 0xffffffffu && aligned16(merged) && aligned16(out)) {
     const size_t nvec = count / 8;
-    silu_mul_merged_vec_kernel<<<wave_grid(silu_mul_merged_vec_kernel, kThreads, nvec, kThreads * kUnroll), kThreads,
+    silu_mul_merged_vec_kernel<<<wave_grid(silu_mul_merged_vec_kernel, kThreads, nvec, kThreads * SiluMul::kDepth), kThreads,
                                  0, s>>>(
         reinterpret_cast<const uint4*>(merged), reinterpret_cast<uint4*>(out), nvec,
         static_cast<unsigned>(intermediate / 8));
