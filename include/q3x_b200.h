@@ -117,7 +117,8 @@ int q3x_b200_residual_add_rms_norm(const uint16_t* left, const uint16_t* right,
 size_t q3x_b200_nvfp4_group_count(size_t rows, size_t rows_per_scale);
 /* Size, in uint32 words, of the `scratch` argument of the entry points below (group amax words and
  * group arrival counters, plus an error word at the end).  The caller owns the memory; every call
- * clears what it uses, so stale contents do not matter. */
+ * clears what it uses, so stale contents do not matter.  Calls that share one scratch buffer must
+ * not overlap on the GPU (same stream, or ordered by events). */
 size_t q3x_b200_nvfp4_scratch_words(size_t rows, size_t rows_per_scale);
 
 /* amax_bits[g] = largest finite |x| of group g as bf16 magnitude bits (uint32), group_count words.
