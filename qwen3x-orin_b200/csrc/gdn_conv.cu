@@ -13,6 +13,8 @@
 //   acc = fma(h0,w0,0); acc = fma(h1,w1,acc); acc = fma(h2,w2,acc); acc = fma(x,w3,acc)
 // history [channels,3] holds RAW inputs, oldest first; the CTA of the first run reads it before any
 // write and is also the one that publishes the new history, so the update is race-free in place.
+#include <type_traits>
+
 #include "device_utils.cuh"
 #include "host_checks.hpp"
 #include "norm_math.cuh"
@@ -83,8 +85,8 @@ __global__ void __launch_bounds__(kThreads, kInPlace ? 1 : 4)
     run = rest / plan.plain_blocks;
   }
   const size_t run_tokens = plan.run_tokens;
-  const int cv = channel_block * kThreads + threadIdx.x;  // channel vector: channels 8cv .. 8cv+7
-  const bool active = cv < channel_vectors;
+  // channel vector: channels 8cv .. 8cv+7 (the launcher admits only widths that fill every CTA)
+  const int cv = channel_block * kThreads + threadIdx.x;
   const size_t t0 = static_cast<size_t>(run) * run_tokens;
   const size_t t1 = min(tokens, t0 + run_tokens);
 
@@ -97,7 +99,7 @@ __global__ void __launch_bounds__(kThreads, kInPlace ? 1 : 4)
     uint4 rows[3];
 #pragma unroll
     for (int r = 0; r < 3; ++r) rows[r] = make_uint4(0, 0, 0, 0);
-    if (active) {
+    {
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
         float f[8];
@@ -127,20 +129,31 @@ __global__ void __launch_bounds__(kThreads, kInPlace ? 1 : 4)
     }
   }
 
-  const bool is_q = kL2 && cv < kQkVectors / 2;
-  const bool is_qk = kL2 && cv < kQkVectors;  // uniform per CTA: 128 vectors per CTA divide 256
+  // uniform per CTA: 128 vectors per CTA divide the 256 of q and the 256 of k
+  const bool is_qk = kL2 && cv < kQkVectors;
+  const float head_scale = (kL2 && cv < kQkVectors / 2) ? q_scale : 1.0f;  // q heads carry the extra scale
+  const size_t row_stride = static_cast<size_t>(channel_vectors);
+  const uint4* raw_col = raw + cv;
+  uint4* out_col = out + cv;
 
   __shared__ __align__(16) uint4 stage[2][kBatch][kThreads];
   auto issue_batch = [&](size_t first_token, int buffer) {
+    const uint4* src = raw_col + first_token * row_stride;
+    if (first_token + kBatch <= t1) {
 #pragma unroll
-    for (int u = 0; u < kBatch; ++u)
-      if (active && first_token + u < t1)
-        cp_async16(&stage[buffer][u][threadIdx.x], raw + (first_token + u) * channel_vectors + cv);
+      for (int u = 0; u < kBatch; ++u) cp_async16(&stage[buffer][u][threadIdx.x], src + u * row_stride);
+    } else {
+#pragma unroll
+      for (int u = 0; u < kBatch; ++u)
+        if (first_token + u < t1) cp_async16(&stage[buffer][u][threadIdx.x], src + u * row_stride);
+    }
     cp_async_commit();
   };
-  // One token: the four-tap chain on rows h0 (oldest) .. h2 and x, SiLU, rounding, optional L2 norm.
-  auto emit_token = [&](const float (&h0)[8], const float (&h1)[8], const float (&h2)[8], const float (&x)[8],
-                        size_t token) {
+  // One token: the four-tap chain on rows h0 (oldest) .. h2 and x, SiLU, rounding, optional L2 norm
+  // (kNorm is a compile-time copy of is_qk, so the token loop carries no branch for it).
+  auto emit_token = [&](auto norm_tag, const float (&h0)[8], const float (&h1)[8], const float (&h2)[8],
+                        const float (&x)[8], uint4* dst) {
+    constexpr bool kNorm = decltype(norm_tag)::value;
     float y[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
@@ -151,7 +164,7 @@ __global__ void __launch_bounds__(kThreads, kInPlace ? 1 : 4)
       y[j] = silu(acc);
     }
     uint4 packed = pack8(y);
-    if (is_qk) {
+    if (kNorm) {
       // L2 norm of the ROUNDED conv output over the 128 channels of this head (16 lanes)
       float r[8];
       unpack8(packed, r);
@@ -159,67 +172,71 @@ __global__ void __launch_bounds__(kThreads, kInPlace ? 1 : 4)
 #pragma unroll
       for (int j = 0; j < 8; ++j) partial = fmaf(r[j], r[j], partial);
       const float sum = group_sum<kHeadVectors>(partial);
-      float inv = inverse_l2(sum, l2_eps);
-      if (is_q && q_scale != 1.0f) inv = inv * q_scale;
+      const float inv = inverse_l2(sum, l2_eps) * head_scale;  // (* 1.0f is exact for the k heads)
 #pragma unroll
       for (int j = 0; j < 8; ++j) r[j] = r[j] * inv;
       packed = pack8(r);
     }
-    if (active) st_vec(out + token * channel_vectors + cv, packed);
+    st_vec(dst, packed);
   };
 
-  issue_batch(t0, 0);
-  int buffer = 0;
-  for (size_t t = t0; t < t1; t += kBatch, buffer ^= 1) {
-    if (t + kBatch < t1) {
-      issue_batch(t + kBatch, buffer ^ 1);
-      cp_async_wait<1>();  // everything but the batch just issued has landed
-    } else {
-      cp_async_wait<0>();
-    }
-    if (t + kBatch <= t1) {
-      // A full batch: rows[0..2] are the carried window, rows[3 + u] the batch's tokens.  Every index
-      // is a compile-time constant, so the sliding window costs no register moves inside the batch.
-      float rows[kBatch + 3][8];
-#pragma unroll
-      for (int r = 0; r < 3; ++r)
-#pragma unroll
-        for (int j = 0; j < 8; ++j) rows[r][j] = win[r][j];
-#pragma unroll
-      for (int u = 0; u < kBatch; ++u) {
-        const uint4 x_bits = active ? stage[buffer][u][threadIdx.x] : make_uint4(0, 0, 0, 0);
-        unpack8(x_bits, rows[u + 3]);
-        emit_token(rows[u], rows[u + 1], rows[u + 2], rows[u + 3], t + u);
-        if (kInPlace && u >= kBatch - 3) keep[u - (kBatch - 3)] = x_bits;
+  auto run_tokens_loop = [&](auto norm_tag) {
+    issue_batch(t0, 0);
+    int buffer = 0;
+    for (size_t t = t0; t < t1; t += kBatch, buffer ^= 1) {
+      if (t + kBatch < t1) {
+        issue_batch(t + kBatch, buffer ^ 1);
+        cp_async_wait<1>();  // everything but the batch just issued has landed
+      } else {
+        cp_async_wait<0>();
       }
+      uint4* dst = out_col + t * row_stride;
+      if (t + kBatch <= t1) {
+        // A full batch: rows[0..2] are the carried window, rows[3 + u] the batch's tokens.  Every index
+        // is a compile-time constant, so the sliding window costs no register moves inside the batch.
+        float rows[kBatch + 3][8];
 #pragma unroll
-      for (int r = 0; r < 3; ++r)
+        for (int r = 0; r < 3; ++r)
 #pragma unroll
-        for (int j = 0; j < 8; ++j) win[r][j] = rows[kBatch + r][j];
-    } else {
-      // the ragged last batch of the last run: one token at a time, shifting the window
-      for (int u = 0; u < kBatch && t + u < t1; ++u) {
-        const uint4 x_bits = active ? stage[buffer][u][threadIdx.x] : make_uint4(0, 0, 0, 0);
-        float x[8];
-        unpack8(x_bits, x);
-        emit_token(win[0], win[1], win[2], x, t + u);
+          for (int j = 0; j < 8; ++j) rows[r][j] = win[r][j];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          win[0][j] = win[1][j];
-          win[1][j] = win[2][j];
-          win[2][j] = x[j];
+        for (int u = 0; u < kBatch; ++u) {
+          const uint4 x_bits = stage[buffer][u][threadIdx.x];
+          unpack8(x_bits, rows[u + 3]);
+          emit_token(norm_tag, rows[u], rows[u + 1], rows[u + 2], rows[u + 3], dst + u * row_stride);
+          if (kInPlace && u >= kBatch - 3) keep[u - (kBatch - 3)] = x_bits;
         }
-        if (kInPlace) {
-          keep[0] = keep[1];
-          keep[1] = keep[2];
-          keep[2] = x_bits;
+#pragma unroll
+        for (int r = 0; r < 3; ++r)
+#pragma unroll
+          for (int j = 0; j < 8; ++j) win[r][j] = rows[kBatch + r][j];
+      } else {
+        // the ragged last batch of the last run: one token at a time, shifting the window
+        for (int u = 0; u < kBatch && t + u < t1; ++u) {
+          const uint4 x_bits = stage[buffer][u][threadIdx.x];
+          float x[8];
+          unpack8(x_bits, x);
+          emit_token(norm_tag, win[0], win[1], win[2], x, dst + u * row_stride);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            win[0][j] = win[1][j];
+            win[1][j] = win[2][j];
+            win[2][j] = x[j];
+          }
+          if (kInPlace) {
+            keep[0] = keep[1];
+            keep[1] = keep[2];
+            keep[2] = x_bits;
+          }
         }
       }
     }
-  }
+  };
+  if (is_qk) run_tokens_loop(std::true_type{});
+  else run_tokens_loop(std::false_type{});
 
   // New history = the last three rows of (old history ++ raw), published by the first run's CTA.
-  if (run == 0 && active) {
+  if (run == 0) {
     uint4 rows[3];
     if (kInPlace) {
 #pragma unroll
@@ -261,6 +278,7 @@ int launch_conv(const uint16_t* raw, size_t tokens, size_t channels, const uint1
   if (tokens == 0 || channels == 0) return kOk;
   if (raw == nullptr || weight == nullptr || history == nullptr || out == nullptr) return kInvalid;
   if (channels != Q3X_B200_GDN_CHANNELS) return kInvalid;  // the reference's only geometry
+  static_assert(Q3X_B200_GDN_CHANNELS % (8 * kThreads) == 0, "every CTA must be filled with channel vectors");
   const size_t bytes = tokens * channels * sizeof(uint16_t);
   const Span sr = span(raw, bytes), so = span(out, bytes), sw = span(weight, channels * 4 * 2),
              sh = span(history, channels * 3 * 2);
