@@ -1,0 +1,52 @@
+// Thin forwards from the C++ front end of the NVFP4 activation operators to the C ABI.
+#include "q3x_b200_nvfp4.hpp"
+
+#include "q3x_b200.h"
+
+namespace q3x::quantization {
+
+std::size_t nvfp4_activation_scale_groups(std::size_t rows, std::size_t rows_per_scale) noexcept {
+  return q3x_b200_nvfp4_group_count(rows, rows_per_scale);
+}
+
+std::size_t nvfp4_activation_scratch_words(std::size_t rows, std::size_t rows_per_scale) noexcept {
+  return q3x_b200_nvfp4_scratch_words(rows, rows_per_scale);
+}
+
+int launch_nvfp4_quantize_activations_cuda(const std::uint16_t* input, std::size_t rows, std::size_t cols,
+                                           std::size_t rows_per_scale, NvFp4ActivationBuffers b,
+                                           void* cuda_stream) noexcept {
+  return q3x_b200_nvfp4_quantize_dynamic(input, rows, cols, rows_per_scale, b.scratch, b.global_scales, b.codes,
+                                         b.block_scales, cuda_stream);
+}
+
+int launch_residual_add_centered_rms_norm_nvfp4_cuda(const std::uint16_t* left, const std::uint16_t* right,
+                                                     const std::uint16_t* weight, std::size_t token_count,
+                                                     std::size_t hidden_size, float epsilon,
+                                                     std::size_t rows_per_scale, std::uint16_t* residual_output,
+                                                     std::uint16_t* normalized_output, NvFp4ActivationBuffers b,
+                                                     void* cuda_stream) noexcept {
+  return q3x_b200_residual_add_rms_norm_nvfp4(left, right, weight, token_count, hidden_size, epsilon, rows_per_scale,
+                                              residual_output, normalized_output, b.scratch, b.global_scales, b.codes,
+                                              b.block_scales, cuda_stream);
+}
+
+int launch_headwise_plain_rms_norm_silu_gate_nvfp4_cuda(const std::uint16_t* input, const std::uint16_t* weight,
+                                                        const std::uint16_t* gate, std::size_t token_count,
+                                                        std::size_t heads_per_token, std::size_t head_dimension,
+                                                        float epsilon, std::size_t rows_per_scale,
+                                                        std::uint16_t* output, NvFp4ActivationBuffers b,
+                                                        void* cuda_stream) noexcept {
+  return q3x_b200_rms_norm_silu_gate_nvfp4(input, weight, gate, token_count, heads_per_token, head_dimension, epsilon,
+                                           rows_per_scale, output, b.scratch, b.global_scales, b.codes,
+                                           b.block_scales, cuda_stream);
+}
+
+int launch_silu_mul_nvfp4_cuda(const std::uint16_t* gate, const std::uint16_t* up, std::size_t token_count,
+                               std::size_t intermediate_size, std::size_t rows_per_scale, std::uint16_t* output,
+                               NvFp4ActivationBuffers b, void* cuda_stream) noexcept {
+  return q3x_b200_silu_mul_nvfp4(gate, up, token_count, intermediate_size, rows_per_scale, output, b.scratch,
+                                 b.global_scales, b.codes, b.block_scales, cuda_stream);
+}
+
+}  // namespace q3x::quantization

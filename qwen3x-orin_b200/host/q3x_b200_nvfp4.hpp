@@ -1,0 +1,54 @@
+// C++17 front end of the NVFP4 activation operators of libq3x_b200.so.
+//
+// The reference project has no activation quantiser (its NVFP4 code decodes checkpoint weights,
+// include/q3x/quantization/nvfp4.h), so these functions have no declaration to mirror; they follow
+// the conventions of the reference's launchers all the same (decode_ops.h:172-176): `int` is a
+// cudaError_t, pointers are device pointers, the caller owns every buffer including the scratch,
+// nothing is allocated, copied or synchronised, `cuda_stream` is a cudaStream_t.
+#pragma once
+
+#include <cstddef>
+#include <cstdint>
+
+namespace q3x::quantization {
+
+inline constexpr std::size_t kNvFp4ActivationBlock = 16U;       // elements per E4M3 block scale (nvfp4.h:8)
+inline constexpr std::size_t kNvFp4PrefillScaleScope = 512U;    // rows per global scale: one prefill chunk
+
+// Caller-owned buffers of one call on a [rows, cols] tensor.
+struct NvFp4ActivationBuffers {
+  std::uint32_t* scratch = nullptr;       // nvfp4_activation_scratch_words(rows, rows_per_scale) words
+  float* global_scales = nullptr;         // nvfp4_activation_scale_groups(rows, rows_per_scale) floats
+  std::uint8_t* codes = nullptr;          // rows * cols / 2 bytes, even column in the low nibble
+  std::uint8_t* block_scales = nullptr;   // rows * cols / 16 E4M3 bytes, row-major, un-swizzled
+};
+
+[[nodiscard]] std::size_t nvfp4_activation_scale_groups(std::size_t rows, std::size_t rows_per_scale) noexcept;
+[[nodiscard]] std::size_t nvfp4_activation_scratch_words(std::size_t rows, std::size_t rows_per_scale) noexcept;
+
+// Any bf16 tensor: group amax -> global scales -> codes and block scales.
+[[nodiscard]] int launch_nvfp4_quantize_activations_cuda(const std::uint16_t* input, std::size_t rows, std::size_t cols,
+                                                         std::size_t rows_per_scale, NvFp4ActivationBuffers buffers,
+                                                         void* cuda_stream = nullptr) noexcept;
+
+// launch_residual_add_centered_rms_norm_*_5120_cuda (decode_ops.h:238-272) with the NVFP4 operand of the
+// next projection produced in the same kernel; normalized_output is required.
+[[nodiscard]] int launch_residual_add_centered_rms_norm_nvfp4_cuda(
+    const std::uint16_t* left, const std::uint16_t* right, const std::uint16_t* weight, std::size_t token_count,
+    std::size_t hidden_size, float epsilon, std::size_t rows_per_scale, std::uint16_t* residual_output,
+    std::uint16_t* normalized_output, NvFp4ActivationBuffers buffers, void* cuda_stream = nullptr) noexcept;
+
+// launch_headwise_plain_rms_norm_silu_gate_reference_cuda (decode_ops.h:218-222) over tokens of
+// `heads_per_token` heads, plus NVFP4 of each token's row.
+[[nodiscard]] int launch_headwise_plain_rms_norm_silu_gate_nvfp4_cuda(
+    const std::uint16_t* input, const std::uint16_t* weight, const std::uint16_t* gate, std::size_t token_count,
+    std::size_t heads_per_token, std::size_t head_dimension, float epsilon, std::size_t rows_per_scale,
+    std::uint16_t* output, NvFp4ActivationBuffers buffers, void* cuda_stream = nullptr) noexcept;
+
+// launch_silu_mul_reference_cuda (decode_ops.h:290-293) plus NVFP4 of its output (the down projection's operand).
+[[nodiscard]] int launch_silu_mul_nvfp4_cuda(const std::uint16_t* gate, const std::uint16_t* up,
+                                             std::size_t token_count, std::size_t intermediate_size,
+                                             std::size_t rows_per_scale, std::uint16_t* output,
+                                             NvFp4ActivationBuffers buffers, void* cuda_stream = nullptr) noexcept;
+
+}  // namespace q3x::quantization

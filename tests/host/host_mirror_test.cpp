@@ -4,6 +4,7 @@
 #include <cstdint>
 #include <cstdio>
 
+#include "q3x_b200_nvfp4.hpp"
 #include "q3x_b200_ops.hpp"
 
 namespace rt = q3x::runtime;
@@ -167,8 +168,30 @@ static void test_bindings() {
   EXPECT(!has(v, Issue::kMalformedBindingIdentity) && !v.complete() && has(v, Issue::kC8192AttestationUnbound));
 }
 
+static void test_nvfp4_front_end() {
+  namespace qz = q3x::quantization;
+  auto* p = reinterpret_cast<std::uint16_t*>(0x100000);
+  qz::NvFp4ActivationBuffers b{reinterpret_cast<std::uint32_t*>(0x40000000), reinterpret_cast<float*>(0x41000000),
+                               reinterpret_cast<std::uint8_t*>(0x42000000), reinterpret_cast<std::uint8_t*>(0x48000000)};
+  EXPECT(qz::nvfp4_activation_scale_groups(16384, 512) == 32 && qz::nvfp4_activation_scale_groups(513, 512) == 2 &&
+         qz::nvfp4_activation_scale_groups(7, 0) == 1 && qz::nvfp4_activation_scale_groups(0, 512) == 0);
+  EXPECT(qz::nvfp4_activation_scratch_words(16384, 512) >= 2 * 32 + 2);
+  // empty shapes succeed with null buffers; bad shapes and missing buffers are refused on the host
+  EXPECT(qz::launch_silu_mul_nvfp4_cuda(nullptr, nullptr, 0, 17408, 512, nullptr, {}) == 0);
+  EXPECT(qz::launch_silu_mul_nvfp4_cuda(p, p + 0x1000000, 4, 17400, 512, p + 0x2000000, b) == 1);   // not a block multiple
+  EXPECT(qz::launch_silu_mul_nvfp4_cuda(p, p + 0x1000000, 4, 17408, 512, p + 0x2000000, {}) == 1);  // no buffers
+  EXPECT(qz::launch_residual_add_centered_rms_norm_nvfp4_cuda(p, p + 0x1000000, p + 0x2000000, 4, 5120, 0.0F, 512,
+                                                              p + 0x3000000, p + 0x4000000, b) == 1);  // epsilon
+  EXPECT(qz::launch_residual_add_centered_rms_norm_nvfp4_cuda(p, p + 0x1000000, p + 0x2000000, 4, 5120, 1e-6F, 512,
+                                                              p + 0x3000000, nullptr, b) == 1);  // normalised rows required
+  EXPECT(qz::launch_headwise_plain_rms_norm_silu_gate_nvfp4_cuda(p, p + 0x1000000, p + 0x2000000, 4, 48, 128, 1e-6F, 512,
+                                                                 p + 0x2000008, b) == 1);  // partial overlap with the gate
+  EXPECT(qz::launch_nvfp4_quantize_activations_cuda(p, 4, 5128, 512, b) == 1);             // not a block multiple
+}
+
 int main() {
   test_launcher_limits();
+  test_nvfp4_front_end();
   test_dispatch();
   test_bindings();
   if (failures == 0) std::printf("host mirror tests passed\n");
