@@ -260,3 +260,35 @@ def test_silu_mul_nvfp4_in_place_and_rejections(g):
                        None) == inv
     assert g.capi.call("q3x_b200_silu_mul_nvfp4", dg, du, tokens, inter, 512, None, scratch, gs, codes, scales, None) == inv
     assert g.capi.call("q3x_b200_silu_mul_nvfp4", None, None, 0, inter, 512, None, None, None, None, None, None) == 0
+
+
+def test_single_kernel_path_matches_two_kernel_path_over_many_launches(g):
+    """The single-kernel form orders its two phases with device-side counters; the two-kernel form
+    (reached through the entry with built-in scratch) uses stream order.  Same bytes, every time."""
+    import torch
+
+    T, H = 16384, 5120
+    gen = torch.Generator(device="cuda").manual_seed(2024)
+    bf = dict(device="cuda", dtype=torch.bfloat16)
+    words = g.capi.lib().q3x_b200_nvfp4_scratch_words(T, 512)
+    scratch = torch.full((words,), 0x55AA55AA, device="cuda", dtype=torch.int32)
+    w = (torch.randn((H,), generator=gen, device="cuda") * 0.02).to(torch.bfloat16)
+    outs = []
+    for _ in range(2):
+        outs.append(dict(res=torch.empty((T, H), **bf), nrm=torch.empty((T, H), **bf),
+                         gs=torch.empty(32, device="cuda", dtype=torch.float32),
+                         codes=torch.empty((T, H // 2), device="cuda", dtype=torch.uint8),
+                         scales=torch.empty((T, H // 16), device="cuda", dtype=torch.uint8)))
+    for it in range(24):
+        if it % 4 == 0:
+            left = (torch.randn((T, H), generator=gen, device="cuda") * (1.0 + it)).to(torch.bfloat16)
+            right = torch.randn((T, H), generator=gen, device="cuda").to(torch.bfloat16)
+        a, b = outs
+        g.capi.check("q3x_b200_residual_add_rms_norm_nvfp4", left, right, w, T, H, EPS, 512, a["res"], a["nrm"], scratch,
+                     a["gs"], a["codes"], a["scales"], None)
+        g.capi.check("q3x_b200_residual_add_rms_norm_nvfp4_static_scratch", left, right, w, T, H, EPS, 512, b["res"],
+                     b["nrm"], b["gs"], b["codes"], b["scales"], None)
+        g.sync()
+        assert int(scratch[-1].item()) == 0, f"launch {it}: a bounded wait gave up"
+        for name in a:
+            assert torch.equal(a[name].view(torch.uint8), b[name].view(torch.uint8)), f"launch {it}: {name} differs"
