@@ -50,7 +50,7 @@ def parse_args():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--tokens", type=int, default=16384, help="token rows per GPU")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--cpu-sample-tokens", type=int, default=4096)
+    ap.add_argument("--cpu-sample-tokens", type=int, default=8192)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
@@ -117,10 +117,11 @@ class ClockSampler:
 
 # ------------------------------------------------------------------------------------ CPU arm
 
-def cpu_chain_seconds(sample_tokens: int, threads: int):
-    """Wall time of the reference's host reference ops over `sample_tokens` rows of the 4-layer
-    pattern (GDN, GDN, GDN, full attention) plus the embedding gather, rows split over `threads`
-    host threads.  Returns (seconds for 4 layers, seconds for the embedding, kind)."""
+def cpu_chain_runner(sample_tokens: int, threads: int):
+    """Sets up the reference's host reference ops over `sample_tokens` rows of the 4-layer pattern
+    (GDN, GDN, GDN, full attention) plus the embedding gather, rows split over `threads` host threads.
+    Returns (run, kind); every run() call is one timed pass over the same inputs and returns
+    (seconds for 4 layers, seconds for the embedding)."""
     import ctypes as C
 
     import numpy as np
@@ -136,7 +137,13 @@ def cpu_chain_seconds(sample_tokens: int, threads: int):
     T, H, I = sample_tokens, 5120, 17408
 
     def bf(shape, std=1.0):
-        return orc.bf16_encode((rng.standard_normal(shape) * std).astype(np.float32))
+        # N(0, std) values; long tensors repeat a 256-row block (the ops are row-local and their cost
+        # does not depend on the values, and drawing a billion normals would take longer than the timing)
+        rows = shape[0] if len(shape) > 1 else 1
+        if rows <= 256:
+            return orc.bf16_encode((rng.standard_normal(shape) * std).astype(np.float32))
+        block = orc.bf16_encode((rng.standard_normal((256,) + tuple(shape[1:])) * std).astype(np.float32))
+        return np.ascontiguousarray(np.tile(block, (-(-rows // 256),) + (1,) * (len(shape) - 1))[:rows])
 
     inp = dict(proj=bf((T, H)), raw=bf((T, 10240)), core=bf((T, 6144)), z=bf((T, 6144)), qg=bf((T, 12288)),
                key=bf((T, 1024)), val=bf((T, 6144)), gate=bf((T, I)), up=bf((T, I)))
@@ -228,10 +235,6 @@ def cpu_chain_seconds(sample_tokens: int, threads: int):
         fa_layer(0, 1, lo, hi)
 
     gs[:] = 0.0025
-    t0 = time.perf_counter()
-    orc.parallel_rows(four_layers, T, threads)
-    t_layers = time.perf_counter() - t0
-
     table = bf((4096, H), 0.02)
     ids = rng.integers(0, 4096, size=T, dtype=np.uint32)
     emb = np.empty((T, H), np.uint16)
@@ -243,16 +246,22 @@ def cpu_chain_seconds(sample_tokens: int, threads: int):
         else:
             L.embedding(at(table, 0), 4096, H, C.cast(ids.ctypes.data + lo * 4, u32p), hi - lo, at(emb, lo))
 
-    t0 = time.perf_counter()
-    orc.parallel_rows(embed, T, threads)
-    t_embed = time.perf_counter() - t0
-    return t_layers, t_embed, kind
+    def run():
+        t0 = time.perf_counter()
+        orc.parallel_rows(four_layers, T, threads)
+        t_layers = time.perf_counter() - t0
+        t0 = time.perf_counter()
+        orc.parallel_rows(embed, T, threads)
+        return t_layers, time.perf_counter() - t0
+
+    return run, kind
 
 
 def cpu_tokens_per_second(sample_tokens: int, threads: int, repeats: int = 1):
+    run, kind = cpu_chain_runner(sample_tokens, threads)
     best = None
     for _ in range(max(1, repeats)):
-        t_layers, t_embed, kind = cpu_chain_seconds(sample_tokens, threads)
+        t_layers, t_embed = run()
         total = t_layers * 16 + t_embed  # 4-layer pattern x 16 = 64 layers
         best = total if best is None else min(best, total)
     return sample_tokens / best, best, kind
@@ -264,9 +273,9 @@ def run_reference_arm(args):
         return 0
     threads = os.cpu_count() or 1
     times = []
-    kind = "port"
+    run, kind = cpu_chain_runner(args.cpu_sample_tokens, threads)
     for i in range(args.warmup + args.steps):
-        t_layers, t_embed, kind = cpu_chain_seconds(args.cpu_sample_tokens, threads)
+        t_layers, t_embed = run()
         if i >= args.warmup:
             times.append(t_layers * 16 + t_embed)
     per_step = sum(times) / len(times)
