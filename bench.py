@@ -324,6 +324,7 @@ def probe_ops(stack, chain, stream_obj, T, peak, warm, reps):
         "swiglu": lambda: stack.op_swiglu(stream),
         # extra operator, not part of the step: SwiGLU with the NVFP4 operand of the down projection
         "swiglu_nvfp4": lambda: stack.op_swiglu_nvfp4(stream),
+        "sigmoid_gate_nvfp4": lambda: stack.op_sigmoid_gate_nvfp4(stream),
     }
     per_op = {}
     with torch.cuda.stream(stream_obj):

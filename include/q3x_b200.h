@@ -191,6 +191,15 @@ int q3x_b200_silu_mul_nvfp4(const uint16_t* gate, const uint16_t* up, size_t tok
                             uint32_t* scratch, float* global_scales_out, uint8_t* codes,
                             uint8_t* scales, void* stream);
 
+/* The attention sigmoid output gate (launch_sigmoid_gate_reference_cuda, decode_ops.h:295-298) +
+ * NVFP4 of its output, the operand of the attention output projection: out = bf16(value *
+ * sigmoid(gate)) over [tokens, width], codes, block scales and global scales as above.  out may be
+ * exactly value or exactly gate.  One kernel or three, as for q3x_b200_silu_mul_nvfp4. */
+int q3x_b200_sigmoid_gate_nvfp4(const uint16_t* value, const uint16_t* gate, size_t tokens,
+                                size_t width, size_t rows_per_scale, uint16_t* out,
+                                uint32_t* scratch, float* global_scales_out, uint8_t* codes,
+                                uint8_t* scales, void* stream);
+
 /* No counterpart in the reference.  q3x_b200_residual_add_rms_norm_nvfp4 for callers that cannot
  * hand over scratch memory because they cannot allocate any: code that runs while a stream is being
  * captured into a CUDA graph or inside a stream callback, a plugin whose host gives it the input

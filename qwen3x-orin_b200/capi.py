@@ -40,6 +40,7 @@ SIGNATURES = {
     "q3x_b200_rms_norm_silu_gate_nvfp4": (_i, [_p, _p, _p, _z, _z, _z, _f, _z, _p, _p, _p, _p, _p, _p]),
     "q3x_b200_residual_add_rms_norm_nvfp4_single_pass": (_i, [_p, _p, _p, _z, _z, _f, _z, _p, _p, _p, _p, _p, _p, _p]),
     "q3x_b200_silu_mul_nvfp4": (_i, [_p, _p, _z, _z, _z, _p, _p, _p, _p, _p, _p]),
+    "q3x_b200_sigmoid_gate_nvfp4": (_i, [_p, _p, _z, _z, _z, _p, _p, _p, _p, _p, _p]),
     "q3x_b200_rms_norm_silu_gate_nvfp4_single_pass": (_i, [_p, _p, _p, _z, _z, _z, _f, _z, _p, _p, _p, _p, _p, _p]),
     "q3x_b200_static_scratch_max_tokens": (_z, []),
     "q3x_b200_residual_add_rms_norm_nvfp4_static_scratch": (_i, [_p, _p, _p, _z, _z, _f, _z, _p, _p, _p, _p, _p, _p]),

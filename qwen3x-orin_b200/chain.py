@@ -45,12 +45,15 @@ BYTES_PER_TOKEN = {
     # not part of the step (the benchmark configurations quantise the norm outputs only): SwiGLU with
     # the NVFP4 operand of the down projection produced in the same kernel
     "swiglu_nvfp4": 3 * INTERMEDIATE * 2 + INTERMEDIATE // 2 + INTERMEDIATE // 16,
+    # likewise: the sigmoid gate with the NVFP4 operand of the attention output projection
+    "sigmoid_gate_nvfp4": 3 * Q_HEADS * HEAD_DIM * 2 + Q_HEADS * HEAD_DIM // 2 + Q_HEADS * HEAD_DIM // 16,
 }
 # kernels each entry point launches (memset nodes not counted); the norm + NVFP4 entries run their
 # single-kernel form at the chain's scale scope of 512 tokens
 KERNELS = {
     "embedding_gather": 1, "residual_rmsnorm_nvfp4": 1, "conv1d_silu_l2norm": 1, "gated_rmsnorm_nvfp4": 1,
     "attention_preprocess": 1, "sigmoid_gate": 1, "swiglu": 1, "swiglu_nvfp4": 1,
+    "sigmoid_gate_nvfp4": 1,
 }
 GDN_OPS = ["residual_rmsnorm_nvfp4", "conv1d_silu_l2norm", "gated_rmsnorm_nvfp4", "residual_rmsnorm_nvfp4", "swiglu"]
 FA_OPS = ["residual_rmsnorm_nvfp4", "attention_preprocess", "sigmoid_gate", "residual_rmsnorm_nvfp4", "swiglu"]
@@ -196,6 +199,13 @@ class LayerStack:
             self.mlp_scales = torch.empty((self.tokens, INTERMEDIATE // 16), device=dev, dtype=torch.uint8)
         capi.check("q3x_b200_silu_mul_nvfp4", self.inputs["mlp_gate"], self.inputs["mlp_up"], self.tokens, INTERMEDIATE,
                    CHUNK, self.mlp_out, self.amax, self.global_scales, self.mlp_codes, self.mlp_scales, stream)
+
+    def op_sigmoid_gate_nvfp4(self, stream):
+        """Sigmoid gate + NVFP4 of its output (extra operator, not in the step); reuses the GDN code buffers,
+        which have the same [tokens, 6144] geometry."""
+        capi.check("q3x_b200_sigmoid_gate_nvfp4", self.inputs["attn_value"], self.gate_out, self.tokens,
+                   Q_HEADS * HEAD_DIM, CHUNK, self.attn_out, self.amax, self.global_scales, self.gdn_codes,
+                   self.gdn_scales, stream)
 
     # ---- the whole step ------------------------------------------------------------------------
     def enqueue_step(self, stream) -> int:

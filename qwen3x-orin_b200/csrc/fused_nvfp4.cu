@@ -29,6 +29,7 @@
 #include "internal.hpp"
 #include "norm_math.cuh"
 #include "nvfp4_math.cuh"
+#include "pointwise_ops.cuh"
 #include "q3x_b200.h"
 
 namespace q3x {
@@ -368,14 +369,14 @@ __global__ void __launch_bounds__(TEAM) small_norm_nvfp4_kernel(const uint4* a, 
   }
 }
 
-// ---- SwiGLU + NVFP4 ---------------------------------------------------------------------------
-// silu(gate) * up is pointwise, so the unit of work is not a row but a CHUNK of TEAM * VPT consecutive
+// ---- pointwise operator (SwiGLU, sigmoid gate) + NVFP4 ------------------------------------------
+// The operator is pointwise, so the unit of work is not a row but a CHUNK of TEAM * VPT consecutive
 // vectors of the flattened [tokens, intermediate] tensor; the launcher only takes this path when a full
 // scale group is a whole number of chunks, so a chunk belongs to exactly one group.  Everything else
 // (roles, lag, arrival counters) is the scheme above with "row" read as "chunk".  `count` is the number
 // of valid vectors of the tensor; only the last chunk can be short.
-template <int TEAM, int VPT, bool FAST>
-__global__ void __launch_bounds__(TEAM, min_ctas_per_sm(TEAM, VPT)) silu_mul_nvfp4_kernel(
+template <class Op, int TEAM, int VPT, bool FAST>
+__global__ void __launch_bounds__(TEAM, min_ctas_per_sm(TEAM, VPT)) pointwise_nvfp4_kernel(
     const uint4* gate, const uint4* up, uint4* out, size_t count, bool coherent, Board board, QuantOut q) {
   __shared__ TeamShared ts;
   constexpr int kChunk = TEAM * VPT;
@@ -417,7 +418,7 @@ __global__ void __launch_bounds__(TEAM, min_ctas_per_sm(TEAM, VPT)) silu_mul_nvf
     unpack8(g[i], a);
     unpack8(u[i], b);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) a[j] = silu_unscaled(a[j]) * b[j];
+    for (int j = 0; j < 8; ++j) a[j] = Op::apply(a[j], b[j]);
     const uint4 y = pack8(a);
     top = fmaxf(top, amax8_float(a, y));
     if (FAST || v < n) st_vec(out + base + v, y);  // default policy: phase B finds it in L2
@@ -569,12 +570,15 @@ bool launch_gated_norm_nvfp4_fused(const uint16_t* in, const uint16_t* weight, c
   return false;
 }
 
-// SwiGLU + NVFP4 over [tokens, intermediate]; chunks of 512 vectors (4096 elements).  False when the
-// shape does not fit the chunk scheme (a scale group that is not a whole number of chunks, misaligned
-// pointers); the caller then runs the separate kernels.
-bool launch_silu_mul_nvfp4_fused(const uint16_t* gate, const uint16_t* up, size_t tokens, size_t intermediate,
-                                 size_t rows_per_scale, uint16_t* out, uint32_t* scratch, float* global_scales_out,
-                                 uint8_t* codes, uint8_t* scales, cudaStream_t s) {
+namespace {
+
+// out = Op(first, second) + NVFP4 over [tokens, width]; chunks of 512 vectors (4096 elements).  False
+// when the shape does not fit the chunk scheme (a scale group that is not a whole number of chunks,
+// misaligned pointers); the caller then runs the separate kernels.
+template <class Op>
+bool launch_pointwise_nvfp4(const uint16_t* gate, const uint16_t* up, size_t tokens, size_t intermediate,
+                            size_t rows_per_scale, uint16_t* out, uint32_t* scratch, float* global_scales_out,
+                            uint8_t* codes, uint8_t* scales, cudaStream_t s) {
   using namespace host;
   constexpr int kTeam = 128, kVpt = 4, kChunk = kTeam * kVpt;
   if (tokens == 0 || intermediate % 16 != 0) return false;
@@ -593,7 +597,7 @@ bool launch_silu_mul_nvfp4_fused(const uint16_t* gate, const uint16_t* up, size_
   const bool full = count % kChunk == 0;
   QuantOut q{reinterpret_cast<uint32_t*>(codes), scales, aligned16(scales) && (count % kChunk) % 32 == 0};
   unsigned lag = 0, grid = 0;
-  if (!plan_launch(silu_mul_nvfp4_kernel<kTeam, kVpt, true>, kTeam, chunks, chunks_per_group, kChunk * 16, &lag, &grid))
+  if (!plan_launch(pointwise_nvfp4_kernel<Op, kTeam, kVpt, true>, kTeam, chunks, chunks_per_group, kChunk * 16, &lag, &grid))
     return false;
   cudaMemsetAsync(scratch, 0, words * sizeof(uint32_t), s);
   const Board board = make_board(scratch, words, groups, global_scales_out, chunks, chunks_per_group, lag);
@@ -601,10 +605,26 @@ bool launch_silu_mul_nvfp4_fused(const uint16_t* gate, const uint16_t* up, size_
   auto U = reinterpret_cast<const uint4*>(up);
   auto O = reinterpret_cast<uint4*>(out);
   if (full && !coherent && q.wide_scale_stores)
-    silu_mul_nvfp4_kernel<kTeam, kVpt, true><<<grid, kTeam, 0, s>>>(G, U, O, count, coherent, board, q);
+    pointwise_nvfp4_kernel<Op, kTeam, kVpt, true><<<grid, kTeam, 0, s>>>(G, U, O, count, coherent, board, q);
   else
-    silu_mul_nvfp4_kernel<kTeam, kVpt, false><<<grid, kTeam, 0, s>>>(G, U, O, count, coherent, board, q);
+    pointwise_nvfp4_kernel<Op, kTeam, kVpt, false><<<grid, kTeam, 0, s>>>(G, U, O, count, coherent, board, q);
   return true;
+}
+
+}  // namespace
+
+bool launch_silu_mul_nvfp4_fused(const uint16_t* gate, const uint16_t* up, size_t tokens, size_t intermediate,
+                                 size_t rows_per_scale, uint16_t* out, uint32_t* scratch, float* global_scales_out,
+                                 uint8_t* codes, uint8_t* scales, cudaStream_t s) {
+  return launch_pointwise_nvfp4<SiluMul>(gate, up, tokens, intermediate, rows_per_scale, out, scratch,
+                                         global_scales_out, codes, scales, s);
+}
+
+bool launch_sigmoid_gate_nvfp4_fused(const uint16_t* value, const uint16_t* gate, size_t tokens, size_t width,
+                                     size_t rows_per_scale, uint16_t* out, uint32_t* scratch,
+                                     float* global_scales_out, uint8_t* codes, uint8_t* scales, cudaStream_t s) {
+  return launch_pointwise_nvfp4<SigmoidGate>(value, gate, tokens, width, rows_per_scale, out, scratch,
+                                             global_scales_out, codes, scales, s);
 }
 
 }  // namespace q3x

@@ -51,6 +51,9 @@ bool launch_residual_norm_nvfp4_fused(const uint16_t* left, const uint16_t* righ
 bool launch_silu_mul_nvfp4_fused(const uint16_t* gate, const uint16_t* up, size_t tokens, size_t intermediate,
                                  size_t rows_per_scale, uint16_t* out, uint32_t* scratch, float* global_scales_out,
                                  uint8_t* codes, uint8_t* scales, cudaStream_t s);
+bool launch_sigmoid_gate_nvfp4_fused(const uint16_t* value, const uint16_t* gate, size_t tokens, size_t width,
+                                     size_t rows_per_scale, uint16_t* out, uint32_t* scratch,
+                                     float* global_scales_out, uint8_t* codes, uint8_t* scales, cudaStream_t s);
 bool launch_gated_norm_nvfp4_fused(const uint16_t* in, const uint16_t* weight, const uint16_t* gate, size_t tokens,
                                    size_t heads_per_row, size_t dim, float eps, size_t rows_per_scale, uint16_t* out,
                                    uint32_t* scratch, float* global_scales_out, uint8_t* codes, uint8_t* scales,

@@ -434,35 +434,58 @@ extern "C" int q3x_b200_residual_add_rms_norm_nvfp4_single_pass(const uint16_t* 
                              scratch, global_scales_out, codes, scales, stream, Path::kSingleKernel);
 }
 
-extern "C" int q3x_b200_silu_mul_nvfp4(const uint16_t* gate, const uint16_t* up, size_t tokens, size_t intermediate,
-                                       size_t rows_per_scale, uint16_t* out, uint32_t* scratch,
-                                       float* global_scales_out, uint8_t* codes, uint8_t* scales, void* stream) {
-  if (mul3_overflows(tokens, intermediate, sizeof(uint16_t))) return kInvalid;
-  if (intermediate % Q3X_B200_NVFP4_BLOCK != 0) return kInvalid;
-  if (tokens == 0 || intermediate == 0) return kOk;
-  if (gate == nullptr || up == nullptr || out == nullptr || scratch == nullptr || global_scales_out == nullptr)
+namespace {
+
+// Shared body of the pointwise + NVFP4 entry points: out = op(first, second) over [tokens, width], then
+// its codes and scales.  `swiglu` selects silu(first) * second, else first * sigmoid(second).
+int pointwise_nvfp4(bool swiglu, const uint16_t* first, const uint16_t* second, size_t tokens, size_t width,
+                    size_t rows_per_scale, uint16_t* out, uint32_t* scratch, float* global_scales_out, uint8_t* codes,
+                    uint8_t* scales, void* stream) {
+  if (mul3_overflows(tokens, width, sizeof(uint16_t))) return kInvalid;
+  if (width % Q3X_B200_NVFP4_BLOCK != 0) return kInvalid;
+  if (tokens == 0 || width == 0) return kOk;
+  if (first == nullptr || second == nullptr || out == nullptr || scratch == nullptr || global_scales_out == nullptr)
     return kInvalid;
-  const size_t bytes = tokens * intermediate * sizeof(uint16_t);
-  const Span sg = span(gate, bytes), su = span(up, bytes), so = span(out, bytes);
-  // out may be exactly gate or exactly up (the reference's in-place form); any partial overlap is refused
-  if (wraps(sg) || wraps(su) || wraps(so) || partial_overlap(so, sg) || partial_overlap(so, su)) return kInvalid;
-  int st = check_quant_outputs(out, tokens, intermediate, codes, scales);
+  const size_t bytes = tokens * width * sizeof(uint16_t);
+  const Span sa = span(first, bytes), sb = span(second, bytes), so = span(out, bytes);
+  // out may be exactly one of the inputs (the reference's in-place forms); any partial overlap is refused
+  if (wraps(sa) || wraps(sb) || wraps(so) || partial_overlap(so, sa) || partial_overlap(so, sb)) return kInvalid;
+  int st = check_quant_outputs(out, tokens, width, codes, scales);
   if (st != kOk) return st;
-  if (overlap(sg, span(codes, bytes / 4)) || overlap(su, span(codes, bytes / 4)) ||
-      overlap(sg, span(scales, bytes / 32)) || overlap(su, span(scales, bytes / 32)))
+  if (overlap(sa, span(codes, bytes / 4)) || overlap(sb, span(codes, bytes / 4)) ||
+      overlap(sa, span(scales, bytes / 32)) || overlap(sb, span(scales, bytes / 32)))
     return kInvalid;
   cudaStream_t s = as_stream(stream);
   clear_stale_error();
-  if (launch_silu_mul_nvfp4_fused(gate, up, tokens, intermediate, rows_per_scale, out, scratch, global_scales_out,
-                                  codes, scales, s))
-    return launch_status();
-  // separate kernels: SwiGLU, group amax of its output, quantiser
-  st = q3x_b200_silu_mul(gate, up, tokens * intermediate, out, stream);
+  const bool fused = swiglu ? launch_silu_mul_nvfp4_fused(first, second, tokens, width, rows_per_scale, out, scratch,
+                                                          global_scales_out, codes, scales, s)
+                            : launch_sigmoid_gate_nvfp4_fused(first, second, tokens, width, rows_per_scale, out,
+                                                              scratch, global_scales_out, codes, scales, s);
+  if (fused) return launch_status();
+  // separate kernels: the pointwise operator, the group amax of its output, the quantiser
+  st = swiglu ? q3x_b200_silu_mul(first, second, tokens * width, out, stream)
+              : q3x_b200_sigmoid_gate(first, second, tokens * width, out, stream);
   if (st != kOk) return st;
   cudaMemsetAsync(scratch, 0, fused_scratch_words(tokens, group_count(tokens, rows_per_scale)) * sizeof(uint32_t), s);
-  enqueue_amax(out, tokens, intermediate, rows_per_scale, scratch, s);
-  enqueue_quantize(out, tokens, intermediate, rows_per_scale, nullptr, scratch, global_scales_out, codes, scales, s);
+  enqueue_amax(out, tokens, width, rows_per_scale, scratch, s);
+  enqueue_quantize(out, tokens, width, rows_per_scale, nullptr, scratch, global_scales_out, codes, scales, s);
   return launch_status();
+}
+
+}  // namespace
+
+extern "C" int q3x_b200_silu_mul_nvfp4(const uint16_t* gate, const uint16_t* up, size_t tokens, size_t intermediate,
+                                       size_t rows_per_scale, uint16_t* out, uint32_t* scratch,
+                                       float* global_scales_out, uint8_t* codes, uint8_t* scales, void* stream) {
+  return pointwise_nvfp4(true, gate, up, tokens, intermediate, rows_per_scale, out, scratch, global_scales_out, codes,
+                         scales, stream);
+}
+
+extern "C" int q3x_b200_sigmoid_gate_nvfp4(const uint16_t* value, const uint16_t* gate, size_t tokens, size_t width,
+                                           size_t rows_per_scale, uint16_t* out, uint32_t* scratch,
+                                           float* global_scales_out, uint8_t* codes, uint8_t* scales, void* stream) {
+  return pointwise_nvfp4(false, value, gate, tokens, width, rows_per_scale, out, scratch, global_scales_out, codes,
+                         scales, stream);
 }
 
 extern "C" int q3x_b200_rms_norm_silu_gate_nvfp4(const uint16_t* in, const uint16_t* weight, const uint16_t* gate,

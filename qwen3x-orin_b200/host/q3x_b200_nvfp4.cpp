@@ -49,4 +49,11 @@ int launch_silu_mul_nvfp4_cuda(const std::uint16_t* gate, const std::uint16_t* u
                                  b.global_scales, b.codes, b.block_scales, cuda_stream);
 }
 
+int launch_sigmoid_gate_nvfp4_cuda(const std::uint16_t* value, const std::uint16_t* gate, std::size_t token_count,
+                                   std::size_t width, std::size_t rows_per_scale, std::uint16_t* output,
+                                   NvFp4ActivationBuffers b, void* cuda_stream) noexcept {
+  return q3x_b200_sigmoid_gate_nvfp4(value, gate, token_count, width, rows_per_scale, output, b.scratch,
+                                     b.global_scales, b.codes, b.block_scales, cuda_stream);
+}
+
 }  // namespace q3x::quantization

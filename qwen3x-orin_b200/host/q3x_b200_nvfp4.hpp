@@ -51,4 +51,11 @@ struct NvFp4ActivationBuffers {
                                              std::size_t rows_per_scale, std::uint16_t* output,
                                              NvFp4ActivationBuffers buffers, void* cuda_stream = nullptr) noexcept;
 
+// launch_sigmoid_gate_reference_cuda (decode_ops.h:295-298) plus NVFP4 of its output (the attention output
+// projection's operand).
+[[nodiscard]] int launch_sigmoid_gate_nvfp4_cuda(const std::uint16_t* value, const std::uint16_t* gate,
+                                                 std::size_t token_count, std::size_t width,
+                                                 std::size_t rows_per_scale, std::uint16_t* output,
+                                                 NvFp4ActivationBuffers buffers, void* cuda_stream = nullptr) noexcept;
+
 }  // namespace q3x::quantization

@@ -187,6 +187,8 @@ static void test_nvfp4_front_end() {
   EXPECT(qz::launch_headwise_plain_rms_norm_silu_gate_nvfp4_cuda(p, p + 0x1000000, p + 0x2000000, 4, 48, 128, 1e-6F, 512,
                                                                  p + 0x2000008, b) == 1);  // partial overlap with the gate
   EXPECT(qz::launch_nvfp4_quantize_activations_cuda(p, 4, 5128, 512, b) == 1);             // not a block multiple
+  EXPECT(qz::launch_sigmoid_gate_nvfp4_cuda(nullptr, nullptr, 0, 6144, 512, nullptr, {}) == 0);
+  EXPECT(qz::launch_sigmoid_gate_nvfp4_cuda(p, p + 0x1000000, 4, 6144, 512, p + 8, b) == 1);  // partial overlap
 }
 
 int main() {

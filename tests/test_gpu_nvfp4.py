@@ -292,3 +292,34 @@ def test_single_kernel_path_matches_two_kernel_path_over_many_launches(g):
         assert int(scratch[-1].item()) == 0, f"launch {it}: a bounded wait gave up"
         for name in a:
             assert torch.equal(a[name].view(torch.uint8), b[name].view(torch.uint8)), f"launch {it}: {name} differs"
+
+
+@pytest.mark.parametrize("tokens,width,rps", [(1, 6144, 512), (5, 6144, 0), (512, 6144, 512), (700, 6144, 512),
+                                              (64, 1024, 16), (33, 1040, 16), (3000, 6144, 0)])
+def test_sigmoid_gate_nvfp4(g, tokens, width, rps):
+    rng = np.random.default_rng([tokens, width, rps, 6])
+    value, gate = fx.normal_bf16(rng, (tokens, width)), fx.normal_bf16(rng, (tokens, width), 3.0)
+    if tokens >= 33:
+        fx.sprinkle_specials(rng, gate[-2:], 0.002)
+    groups = 1 if rps == 0 else (tokens + rps - 1) // rps
+    dv, dg = g.Dev(value), g.Dev(gate)
+    out = g.empty_like_dev((tokens, width))
+    scratch = g.scratch_for(tokens, rps, fill=0x0BADF00D)
+    gs = g.empty_like_dev((groups,), dtype=np.float32)
+    codes = g.empty_like_dev((tokens, width // 2), dtype=np.uint8)
+    scales = g.empty_like_dev((tokens, width // 16), dtype=np.uint8)
+    g.capi.check("q3x_b200_sigmoid_gate_nvfp4", dv, dg, tokens, width, rps, out, scratch, gs, codes, scales, None)
+    g.sync()
+    assert scratch.get()[-1] == 0, "a bounded wait inside the kernel gave up"
+    got = out.get()
+    g.assert_bf16_within(got, orc.sigmoid_gate(value, gate), 1, 0.98, "sigmoid gate")
+    plain = g.empty_like_dev((tokens, width))
+    g.capi.check("q3x_b200_sigmoid_gate", dv, dg, tokens * width, plain, None)
+    g.sync()
+    g.assert_bits_equal(got, plain.get(), "fused gate == stand-alone gate")
+    want_c, want_s, want_g = orc.nvfp4_quantize(got, rps)
+    assert np.array_equal(gs.get().view(np.uint32), want_g.view(np.uint32)), "global scales"
+    g.assert_bits_equal(scales.get(), want_s, "block scales")
+    g.assert_bits_equal(codes.get(), want_c, "codes")
+    for d in (out, codes, scales, gs, scratch):
+        assert d.guards_intact()
