@@ -1,5 +1,6 @@
-// Single-kernel norm + NVFP4: residual add + centred RMSNorm + quantisation, and the GDN gated
-// RMSNorm * silu(z) + quantisation, each crossing HBM once.
+// Single-kernel operator + NVFP4: residual add + centred RMSNorm + quantisation, the GDN gated
+// RMSNorm * silu(z) + quantisation, and SwiGLU / sigmoid gate + quantisation, each crossing HBM once.
+// (One or two rows take a single-CTA form instead, see "a handful of rows" below.)
 //
 // The NVFP4 global scale of a group of rows is its amax, which is only known once every row of the
 // group has been normalised -- a dependency across CTAs.  It is resolved without a second pass over
