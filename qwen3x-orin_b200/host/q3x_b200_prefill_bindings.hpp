@@ -51,12 +51,9 @@ struct PrefillTacticBinding {
     return mode == PrefillTacticMode::kAheadOfTime && identity != 0U;
   }
 };
-struct PrefillOperatorRoleRequirements {
-  bool weight = false;
-  bool sidecar = false;
-  bool workspace = false;
-  bool launcher = true;
-  bool completion_event = true;
+struct PrefillOperatorRoleRequirements {  // which resources a role must have bound
+  bool weight = false, sidecar = false, workspace = false;
+  bool launcher = true, completion_event = true;
 };
 struct PrefillOperatorBinding {
   PrefillBindingRole role = PrefillBindingRole::kInvalid;
@@ -64,11 +61,7 @@ struct PrefillOperatorBinding {
   PrefillNumericalMode numerical_mode = PrefillNumericalMode::kUnbound;
   PrefillOperatorProvider provider = PrefillOperatorProvider::kUnbound;
   PrefillTacticBinding tactic;
-  PrefillResourceBinding weight;
-  PrefillResourceBinding sidecar;
-  PrefillResourceBinding workspace;
-  PrefillResourceBinding launcher;
-  PrefillResourceBinding completion_event;
+  PrefillResourceBinding weight, sidecar, workspace, launcher, completion_event;  // in this order
   PrefillBindingAttestation attestation = PrefillBindingAttestation::kUnboundDesign;
   bool uses_mtp = false;
 };
@@ -80,45 +73,30 @@ struct PrefillOperatorBindingSet {
 // prefill_operator_bindings.h:86-110 -- bit positions are ABI
 enum class PrefillOperatorBindingIssue : std::uint64_t {
   kNone = 0U,
-  kInvalidRole = 1ULL << 0U,
-  kMissingRole = 1ULL << 1U,
-  kDuplicateRole = 1ULL << 2U,
+  // roles and capacity
+  kInvalidRole = 1ULL << 0U, kMissingRole = 1ULL << 1U, kDuplicateRole = 1ULL << 2U,
   kInsufficientLogicalPanelCapacity = 1ULL << 3U,
-  kNumericalModeUnbound = 1ULL << 4U,
-  kApproximateNumericsForbidden = 1ULL << 5U,
-  kProviderUnbound = 1ULL << 6U,
-  kNonNativeProvider = 1ULL << 7U,
-  kCuBlasLtForbidden = 1ULL << 8U,
-  kMtpForbidden = 1ULL << 9U,
-  kTacticNotAot = 1ULL << 10U,
-  kTacticIdentityUnbound = 1ULL << 11U,
-  kGateDownTacticAlias = 1ULL << 12U,
-  kWeightBindingIncomplete = 1ULL << 13U,
-  kSidecarBindingIncomplete = 1ULL << 14U,
-  kWorkspaceBindingIncomplete = 1ULL << 15U,
-  kLauncherBindingIncomplete = 1ULL << 16U,
-  kCompletionEventBindingIncomplete = 1ULL << 17U,
-  kMalformedBindingIdentity = 1ULL << 18U,
-  kC8192AttestationUnbound = 1ULL << 19U,
-  kLegacyC512InventoryOnly = 1ULL << 20U,
-  kMalformedEnumEncoding = 1ULL << 21U,
+  // numerics, provider, forbidden boundaries
+  kNumericalModeUnbound = 1ULL << 4U, kApproximateNumericsForbidden = 1ULL << 5U, kProviderUnbound = 1ULL << 6U,
+  kNonNativeProvider = 1ULL << 7U, kCuBlasLtForbidden = 1ULL << 8U, kMtpForbidden = 1ULL << 9U,
+  // tactics
+  kTacticNotAot = 1ULL << 10U, kTacticIdentityUnbound = 1ULL << 11U, kGateDownTacticAlias = 1ULL << 12U,
+  // resources
+  kWeightBindingIncomplete = 1ULL << 13U, kSidecarBindingIncomplete = 1ULL << 14U,
+  kWorkspaceBindingIncomplete = 1ULL << 15U, kLauncherBindingIncomplete = 1ULL << 16U,
+  kCompletionEventBindingIncomplete = 1ULL << 17U, kMalformedBindingIdentity = 1ULL << 18U,
+  // attestation and encoding
+  kC8192AttestationUnbound = 1ULL << 19U, kLegacyC512InventoryOnly = 1ULL << 20U, kMalformedEnumEncoding = 1ULL << 21U,
 };
 
 struct PrefillOperatorBindingValidation {
   std::uint64_t issue_mask = 0U;
   std::array<std::uint8_t, kLayerMajorPrefillRequiredOperatorRoleCount> role_counts{};
-  bool role_coverage_complete = false;
-  bool logical_capacity_complete = false;
-  bool exact_numerics_complete = false;
-  bool native_provider_complete = false;
-  bool aot_tactics_complete = false;
-  bool artifact_bindings_complete = false;
-  bool workspace_bindings_complete = false;
-  bool launcher_bindings_complete = false;
-  bool completion_events_complete = false;
-  bool forbidden_boundaries_satisfied = false;
-  bool attestation_complete = false;
-  bool operator_bindings_complete = false;
+  // one verdict per aspect; operator_bindings_complete is their conjunction
+  bool role_coverage_complete = false, logical_capacity_complete = false, exact_numerics_complete = false;
+  bool native_provider_complete = false, aot_tactics_complete = false, artifact_bindings_complete = false;
+  bool workspace_bindings_complete = false, launcher_bindings_complete = false, completion_events_complete = false;
+  bool forbidden_boundaries_satisfied = false, attestation_complete = false, operator_bindings_complete = false;
   [[nodiscard]] constexpr bool complete() const noexcept { return operator_bindings_complete; }
   // a descriptor is never a launchable plan (prefill_operator_bindings.h:139-142)
   [[nodiscard]] constexpr bool executable() const noexcept { return false; }
