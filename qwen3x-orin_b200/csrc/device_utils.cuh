@@ -199,6 +199,59 @@ __device__ __forceinline__ float silu_unscaled(float g) {
   return g * r;
 }
 
+// ---------------------------------------------------------------------------- packed FP32 pairs
+// sm_100 executes FP32 add / mul / fma on two independent values per instruction (operands in 64-bit
+// register pairs).  Each half is the ordinary round-to-nearest IEEE operation with denormals kept, so
+// results are bit-identical to the scalar instructions; what halves is the number of issue slots, which
+// is what bounds the instruction-heavy kernels here (conv, gated norm, quantiser).
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
+  uint64_t v;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "f"(lo), "f"(hi));
+  return v;
+}
+__device__ __forceinline__ float2 unpack_f32x2(uint64_t v) {
+  float2 f;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(f.x), "=f"(f.y) : "l"(v));
+  return f;
+}
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(pack_f32x2(a.x, a.y)), "l"(pack_f32x2(b.x, b.y)),
+      "l"(pack_f32x2(c.x, c.y)));
+  return unpack_f32x2(d);
+}
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
+  uint64_t d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(pack_f32x2(a.x, a.y)), "l"(pack_f32x2(b.x, b.y)));
+  return unpack_f32x2(d);
+}
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(pack_f32x2(a.x, a.y)), "l"(pack_f32x2(b.x, b.y)));
+  return unpack_f32x2(d);
+}
+// a[i] += b[i] for eight values, two per instruction
+__device__ __forceinline__ void add8(float (&a)[8], const float (&b)[8]) {
+#pragma unroll
+  for (int i = 0; i < 8; i += 2) {
+    const float2 s = add2(make_float2(a[i], a[i + 1]), make_float2(b[i], b[i + 1]));
+    a[i] = s.x;
+    a[i + 1] = s.y;
+  }
+}
+// silu of two values: the scalar form above with its multiplies and its fma issued pairwise
+__device__ __forceinline__ float2 silu2(float2 g) {
+  constexpr float kScale = 5.9604644775390625e-08f;  // 2^-24
+  const float2 arg = mul2(g, make_float2(-1.4426950408889634f, -1.4426950408889634f));
+  float2 e, r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e.x) : "f"(arg.x));
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e.y) : "f"(arg.y));
+  const float2 den = fma2(e, make_float2(kScale, kScale), make_float2(kScale, kScale));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r.x) : "f"(den.x));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r.y) : "f"(den.y));
+  return mul2(g, mul2(r, make_float2(kScale, kScale)));
+}
+
 // ---------------------------------------------------------------------------- bf16 amax
 
 // Magnitude bits of the finite halves of a packed bf16 pair, non-finite halves give 0; bf16

@@ -222,8 +222,7 @@ __device__ __forceinline__ float residual_norm_row(const uint4* left, const uint
     float a[8], b[8];
     unpack8(x[i], a);
     unpack8(r[i], b);
-#pragma unroll
-    for (int j = 0; j < 8; ++j) a[j] = a[j] + b[j];
+    add8(a, b);
     x[i] = pack8(a);
     const int v = tid + i * TEAM;
     if (FAST || v < row_vectors) st_vec(residual_out + base + v, x[i], policy);

@@ -156,12 +156,14 @@ __global__ void __launch_bounds__(kThreads, kInPlace ? 1 : 4)
     constexpr bool kNorm = decltype(norm_tag)::value;
     float y[8];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      float acc = fmaf(h0[j], w[j][0], 0.0f);
-      acc = fmaf(h1[j], w[j][1], acc);
-      acc = fmaf(h2[j], w[j][2], acc);
-      acc = fmaf(x[j], w[j][3], acc);
-      y[j] = silu(acc);
+    for (int j = 0; j < 8; j += 2) {
+      float2 acc = fma2(make_float2(h0[j], h0[j + 1]), make_float2(w[j][0], w[j + 1][0]), make_float2(0.0f, 0.0f));
+      acc = fma2(make_float2(h1[j], h1[j + 1]), make_float2(w[j][1], w[j + 1][1]), acc);
+      acc = fma2(make_float2(h2[j], h2[j + 1]), make_float2(w[j][2], w[j + 1][2]), acc);
+      acc = fma2(make_float2(x[j], x[j + 1]), make_float2(w[j][3], w[j + 1][3]), acc);
+      const float2 s2 = silu2(acc);
+      y[j] = s2.x;
+      y[j + 1] = s2.y;
     }
     uint4 packed = pack8(y);
     if (kNorm) {
@@ -174,7 +176,11 @@ __global__ void __launch_bounds__(kThreads, kInPlace ? 1 : 4)
       const float sum = group_sum<kHeadVectors>(partial);
       const float inv = inverse_l2(sum, l2_eps) * head_scale;  // (* 1.0f is exact for the k heads)
 #pragma unroll
-      for (int j = 0; j < 8; ++j) r[j] = r[j] * inv;
+      for (int j = 0; j < 8; j += 2) {
+        const float2 p = mul2(make_float2(r[j], r[j + 1]), make_float2(inv, inv));
+        r[j] = p.x;
+        r[j + 1] = p.y;
+      }
       packed = pack8(r);
     }
     st_vec(dst, packed);

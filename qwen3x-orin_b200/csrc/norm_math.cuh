@@ -45,15 +45,19 @@ __device__ __forceinline__ uint4 scale8(const uint4& x, const uint4& w, const ui
   unpack8(x, xf);
   if (MODE != NormMode::kL2) unpack8(w, wf);
   if (MODE == NormMode::kPlainSiluGate) unpack8(z, zf);
+  // two elements per instruction (fma2 / mul2 / add2 round each half like the scalar operation)
+  const float2 inv2 = make_float2(inv, inv);
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    if (MODE == NormMode::kL2) {
-      y[i] = xf[i] * inv;
-    } else {
-      const float gamma = MODE == NormMode::kCentered ? wf[i] + 1.0f : wf[i];
-      y[i] = xf[i] * inv * gamma;  // (x * inv) * gamma, the reference's product order
-      if (MODE == NormMode::kPlainSiluGate) y[i] *= silu(zf[i]);
+  for (int i = 0; i < 8; i += 2) {
+    float2 v = mul2(make_float2(xf[i], xf[i + 1]), inv2);
+    if (MODE != NormMode::kL2) {
+      float2 gamma = make_float2(wf[i], wf[i + 1]);
+      if (MODE == NormMode::kCentered) gamma = add2(gamma, make_float2(1.0f, 1.0f));
+      v = mul2(v, gamma);  // (x * inv) * gamma, the reference's product order
+      if (MODE == NormMode::kPlainSiluGate) v = mul2(v, silu2(make_float2(zf[i], zf[i + 1])));
     }
+    y[i] = v.x;
+    y[i + 1] = v.y;
   }
   const uint4 packed = pack8(y);
   if (kTrackAmax) *top = fmaxf(*top, amax8_float(y, packed));

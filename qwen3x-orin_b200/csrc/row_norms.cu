@@ -138,8 +138,7 @@ __global__ void __launch_bounds__(128) hidden_rows_kernel(const uint4* a, const 
       float l[8], rr[8];
       unpack8(x[k], l);
       unpack8(r[k], rr);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) l[i] = l[i] + rr[i];
+      add8(l, rr);
       x[k] = pack8(l);
       const int v = threadIdx.x + k * 128;
       if (v < row_vectors) st_vec(residual_out + row_base + v, x[k]);
