@@ -36,10 +36,10 @@ UNIT = "tokens/s"
 
 
 # DRAM traffic of the dominant kernel (SwiGLU), from one ncu capture of an 8192-token launch:
-# dram__bytes.sum.per_second x gpu__time_duration = 803.1 MB read + written, i.e. 98035 bytes per token
+# dram__bytes.sum.per_second x gpu__time_duration = 817.9 MB read + written, i.e. 99841 bytes per token
 # against 104448 algorithmic ones (the tail of the output is still dirty in L2 when the kernel ends).
 # Traffic grows in proportion to the tokens, so a launch of T tokens is reported as this figure x T.
-SWIGLU_DRAM_BYTES_PER_TOKEN = 98035
+SWIGLU_DRAM_BYTES_PER_TOKEN = 99841
 SWIGLU_TRAFFIC_SOURCE = "ncu, 8192-token launch scaled by tokens (profiles/layer_ops_8192_tokens_ncu_sections.md)"
 
 
