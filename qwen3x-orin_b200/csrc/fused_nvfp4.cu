@@ -8,7 +8,7 @@
 // threads) alternate between two roles:
 //   * even CTAs ("phase A", CTA 2k): normalise row k exactly like the stand-alone norm kernel (whole
 //     row in registers, one trip per tensor), write the bf16 outputs, raise the group's amax word with
-//     one atomic and then count the row into the group's arrival counter (fence in between);
+//     one atomic and then count the row into the group's arrival counter (a release reduction);
 //   * odd CTAs ("phase B", CTA 2k + 1): quantise row k - lag, which was written `lag` rows earlier and
 //     is still in L2 (lag x row bytes is a few tens of MB at most; the launcher refuses longer groups).
 //     They need the arrival counter of that row's group to be complete.  lag = group rows + the number
@@ -80,8 +80,8 @@ struct TeamShared {
   __align__(16) uint8_t scale_bytes[kMaxRowScaleBytes];
 };
 
-// Phase A epilogue.  The barrier orders every thread's stores of the row before thread 0's fence, the
-// fence orders them (and the amax atomic) before the arrival count at GPU scope.
+// Phase A epilogue.  The barrier orders every thread's stores of the row before thread 0's arrival
+// count, whose release semantics order them (and the amax atomic) before it at GPU scope.
 template <int WARPS>
 __device__ __forceinline__ void publish_row(const Board& board, TeamShared& ts, size_t row, float thread_top) {
   const uint32_t warp_top = group_max_u32<32>(amax_bits_of(thread_top));
@@ -93,8 +93,7 @@ __device__ __forceinline__ void publish_row(const Board& board, TeamShared& ts, 
 #pragma unroll
     for (int w = 0; w < WARPS; ++w) m = max(m, ts.tops[w]);
     if (m != 0) atomicMax(board.amax + slot, m);
-    __threadfence();
-    atomicAdd(board.count + slot, 1u);
+    asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(board.count + slot) : "memory");
   }
 }
 
