@@ -80,36 +80,16 @@ __device__ __forceinline__ void st_stream(void* p, const uint4& v) {
 // Small read-mostly operands (weights, tables): keep them cached.
 __device__ __forceinline__ uint4 ld_weight(const void* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
 
-// L2 eviction policy for operands that stream through once while something else should stay cached.
-__device__ __forceinline__ uint64_t l2_evict_first_policy() {
-  uint64_t policy;
-  asm("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
-  return policy;
-}
-__device__ __forceinline__ uint4 ld_stream(const void* p, uint64_t policy) {
+// Coherent load served by L2 (data another CTA of the same launch has written): bypasses L1.
+__device__ __forceinline__ uint4 ld_l2(const void* p) {
   uint4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.v4.u32 {%0,%1,%2,%3}, [%4], %5;"
+  asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];"
                : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p), "l"(policy));
-  return v;
-}
-// Coherent load served by L2 (data another CTA of the same launch has written), then first to go.
-__device__ __forceinline__ uint4 ld_l2_once(const void* p, uint64_t policy) {
-  uint4 v;
-  asm volatile("ld.global.cg.L2::cache_hint.v4.u32 {%0,%1,%2,%3}, [%4], %5;"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p), "l"(policy)
+               : "l"(p)
                : "memory");
   return v;
 }
-__device__ __forceinline__ void st_vec(void* p, const uint4& v, uint64_t policy) {
-  asm volatile("st.global.L2::cache_hint.v4.u32 [%0], {%1,%2,%3,%4}, %5;" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z),
-               "r"(v.w), "l"(policy)
-               : "memory");
-}
-__device__ __forceinline__ void st_u32(void* p, uint32_t v, uint64_t policy) {
-  asm volatile("st.global.L2::cache_hint.u32 [%0], %1, %2;" ::"l"(p), "r"(v), "l"(policy) : "memory");
-}
+__device__ __forceinline__ void st_u32(void* p, uint32_t v) { *reinterpret_cast<uint32_t*>(p) = v; }
 
 // ---------------------------------------------------------------------------- reductions
 

@@ -20,8 +20,9 @@
 // smaller index, which the hardware has started earlier (CTAs of a 1-D grid start in index order).
 // Every wait is bounded all the same; a CTA that gives up sets the error word and carries on, so the
 // kernel always terminates and a missed dependency is reported, never silent.
-// The streamed operands (inputs, residual, codes, scales) carry an L2 evict-first policy so that the
-// normalised rows awaiting phase B are what stays cached.
+// No L2 eviction hints: marking the streamed operands evict-first (so that the normalised rows awaiting
+// phase B would be what stays cached) measured 2 - 5 % SLOWER than plain accesses; lag x row bytes is
+// small against the L2 as it is.
 //
 // Scratch words (uint32), cleared by the launcher: G group amax words, then G arrival counters (each
 // on an L2 line of its own when the scratch is large enough), last word = error flag.
@@ -124,14 +125,13 @@ __device__ __forceinline__ uint32_t await_group_amax(const Board& board, TeamSha
 // the global scale is built.
 template <int TEAM, int VPT, bool FAST>
 __device__ __forceinline__ void quantize_row(const uint4* row_in, int row_vectors, uint32_t amax_bits, TeamShared& ts,
-                                             uint32_t* codes_row, uint8_t* scales_row, bool wide_scale_stores,
-                                             uint64_t policy) {
+                                             uint32_t* codes_row, uint8_t* scales_row, bool wide_scale_stores) {
   const int tid = threadIdx.x;
   uint4 y[VPT];
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const int v = tid + i * TEAM;
-    y[i] = FAST || v < row_vectors ? ld_l2_once(row_in + v, policy) : make_uint4(0, 0, 0, 0);
+    y[i] = FAST || v < row_vectors ? ld_l2(row_in + v) : make_uint4(0, 0, 0, 0);
   }
   const float global = global_scale_from_amax_bits(amax_bits);
   const float k = block_scale_factor(global);
@@ -147,7 +147,7 @@ __device__ __forceinline__ void quantize_row(const uint4* row_in, int row_vector
     m = fmaxf(m, __shfl_xor_sync(kFullMask, m, 1));
     const uint32_t s = block_scale_code(m, k);
     if (valid) {
-      st_u32(codes_row + v, quantize8(f, ts.inv_table[s]), policy);
+      st_u32(codes_row + v, quantize8(f, ts.inv_table[s]));
       if ((tid & 1) == 0) {
         if (FAST || wide_scale_stores) ts.scale_bytes[v >> 1] = static_cast<uint8_t>(s);
         else scales_row[v >> 1] = static_cast<uint8_t>(s);
@@ -157,7 +157,7 @@ __device__ __forceinline__ void quantize_row(const uint4* row_in, int row_vector
   if (FAST || wide_scale_stores) {  // row_vectors / 2 bytes, a multiple of 16, written as 128-bit stores
     __syncthreads();
     if (tid < row_vectors / 32)
-      st_vec(reinterpret_cast<uint4*>(scales_row) + tid, reinterpret_cast<const uint4*>(ts.scale_bytes)[tid], policy);
+      st_vec(reinterpret_cast<uint4*>(scales_row) + tid, reinterpret_cast<const uint4*>(ts.scale_bytes)[tid]);
   }
 }
 
@@ -165,24 +165,24 @@ __device__ __forceinline__ void quantize_row(const uint4* row_in, int row_vector
 template <int TEAM, int VPT, bool FAST>
 __device__ __forceinline__ void quantize_cached_row(const uint4* row_in, int row_vectors, const Board& board,
                                                     TeamShared& ts, size_t row, uint32_t* codes_row,
-                                                    uint8_t* scales_row, bool wide_scale_stores, uint64_t policy) {
+                                                    uint8_t* scales_row, bool wide_scale_stores) {
   const size_t group = row / board.group_rows;
   const uint32_t amax_bits = await_group_amax(board, ts, group);
   if (threadIdx.x == 0 && row == group * board.group_rows)
     board.global_out[group] = global_scale_from_amax_bits(amax_bits);
-  quantize_row<TEAM, VPT, FAST>(row_in, row_vectors, amax_bits, ts, codes_row, scales_row, wide_scale_stores, policy);
+  quantize_row<TEAM, VPT, FAST>(row_in, row_vectors, amax_bits, ts, codes_row, scales_row, wide_scale_stores);
 }
 
 // Phase B of either kernel: CTA 2k + 1 quantises row k - lag of `normalized`.
 template <int TEAM, int VPT, bool FAST>
 __device__ __forceinline__ void phase_b(const uint4* normalized, int row_vectors, const Board& board, TeamShared& ts,
-                                        const QuantOut& q, uint64_t policy) {
+                                        const QuantOut& q) {
   const size_t idx = blockIdx.x >> 1;
   if (idx < board.lag || idx - board.lag >= board.rows) return;
   const size_t row = idx - board.lag;
   quantize_cached_row<TEAM, VPT, FAST>(normalized + row * static_cast<size_t>(row_vectors), row_vectors, board, ts, row,
                            q.codes + row * static_cast<size_t>(row_vectors),
-                           q.scales + row * static_cast<size_t>(row_vectors / 2), q.wide_scale_stores, policy);
+                           q.scales + row * static_cast<size_t>(row_vectors / 2), q.wide_scale_stores);
 }
 
 // Phase A of the residual operator on one row: residual add, rounding, centred RMSNorm, both stores.
@@ -191,7 +191,7 @@ template <int TEAM, int VPT, bool FAST>
 __device__ __forceinline__ float residual_norm_row(const uint4* left, const uint4* right,
                                                    const uint4* __restrict__ weight, size_t row, int row_vectors,
                                                    float width, float eps, uint4* residual_out, uint4* normalized_out,
-                                                   bool coherent, uint64_t policy, TeamShared& ts) {
+                                                   bool coherent, TeamShared& ts) {
   const int tid = threadIdx.x;
   const size_t base = row * static_cast<size_t>(row_vectors);
   uint4 x[VPT], r[VPT];
@@ -199,20 +199,20 @@ __device__ __forceinline__ float residual_norm_row(const uint4* left, const uint
   for (int i = 0; i < VPT; ++i) {
     const int v = tid + i * TEAM;
     if (FAST) {
-      x[i] = ld_stream(left + base + v, policy);
+      x[i] = ld_stream(left + base + v);
     } else {
       x[i] = make_uint4(0, 0, 0, 0);
-      if (v < row_vectors) x[i] = coherent ? ld_vec(left + base + v) : ld_stream(left + base + v, policy);
+      if (v < row_vectors) x[i] = coherent ? ld_vec(left + base + v) : ld_stream(left + base + v);
     }
   }
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const int v = tid + i * TEAM;
     if (FAST) {
-      r[i] = ld_stream(right + base + v, policy);
+      r[i] = ld_stream(right + base + v);
     } else {
       r[i] = make_uint4(0, 0, 0, 0);
-      if (v < row_vectors) r[i] = coherent ? ld_vec(right + base + v) : ld_stream(right + base + v, policy);
+      if (v < row_vectors) r[i] = coherent ? ld_vec(right + base + v) : ld_stream(right + base + v);
     }
   }
   float partial = 0.0f;
@@ -224,7 +224,7 @@ __device__ __forceinline__ float residual_norm_row(const uint4* left, const uint
     add8(a, b);
     x[i] = pack8(a);
     const int v = tid + i * TEAM;
-    if (FAST || v < row_vectors) st_vec(residual_out + base + v, x[i], policy);
+    if (FAST || v < row_vectors) st_vec(residual_out + base + v, x[i]);
     partial += sum_squares8(x[i]);
   }
   const float total = block_sum<TEAM / 32>(partial, ts.sums);
@@ -236,7 +236,7 @@ __device__ __forceinline__ float residual_norm_row(const uint4* left, const uint
     if (FAST || v < row_vectors) {
       const uint4 y = scale8<NormMode::kCentered, true>(x[i], ld_weight(weight + v), make_uint4(0, 0, 0, 0), inv,
                                                         &top);
-      st_vec(normalized_out + base + v, y);  // default policy: this is what phase B finds in L2
+      st_vec(normalized_out + base + v, y);  // this is what phase B finds in L2
     }
   }
   return top;
@@ -252,23 +252,21 @@ __global__ void __launch_bounds__(TEAM, min_ctas_per_sm(TEAM, VPT)) residual_nor
     const uint4* left, const uint4* right, const uint4* __restrict__ weight, int row_vectors, float width, float eps,
     uint4* residual_out, uint4* normalized_out, bool coherent, Board board, QuantOut q) {
   __shared__ TeamShared ts;
-  const uint64_t policy = l2_evict_first_policy();
   if (blockIdx.x & 1u) {
-    phase_b<TEAM, VPT, FAST>(normalized_out, row_vectors, board, ts, q, policy);
+    phase_b<TEAM, VPT, FAST>(normalized_out, row_vectors, board, ts, q);
     return;
   }
   const size_t row = blockIdx.x >> 1;
   if (row >= board.rows) return;
   const float top = residual_norm_row<TEAM, VPT, FAST>(left, right, weight, row, row_vectors, width, eps, residual_out,
-                                                       normalized_out, coherent, policy, ts);
+                                                       normalized_out, coherent, ts);
   publish_row<TEAM / 32>(board, ts, row, top);
 }
 
 // Phase A of the gated-norm operator on one token: per-head RMSNorm * weight * silu(z), store.
 template <int TEAM, int VPT, bool FAST>
 __device__ __forceinline__ float gated_norm_row(const uint4* in, const uint4* gate, const uint4* __restrict__ weight,
-                                                size_t row, int row_vectors, float eps, uint4* out, bool coherent,
-                                                uint64_t policy) {
+                                                size_t row, int row_vectors, float eps, uint4* out, bool coherent) {
   const int tid = threadIdx.x;
   const size_t base = row * static_cast<size_t>(row_vectors);
   const uint4 w = ld_weight(weight + (tid & 15));
@@ -277,13 +275,13 @@ __device__ __forceinline__ float gated_norm_row(const uint4* in, const uint4* ga
   for (int i = 0; i < VPT; ++i) {
     const int v = tid + i * TEAM;
     if (FAST) {
-      x[i] = ld_stream(in + base + v, policy);
-      z[i] = ld_stream(gate + base + v, policy);
+      x[i] = ld_stream(in + base + v);
+      z[i] = ld_stream(gate + base + v);
     } else {
       x[i] = z[i] = make_uint4(0, 0, 0, 0);
       if (v < row_vectors) {
-        x[i] = coherent ? ld_vec(in + base + v) : ld_stream(in + base + v, policy);
-        z[i] = coherent ? ld_vec(gate + base + v) : ld_stream(gate + base + v, policy);
+        x[i] = coherent ? ld_vec(in + base + v) : ld_stream(in + base + v);
+        z[i] = coherent ? ld_vec(gate + base + v) : ld_stream(gate + base + v);
       }
     }
   }
@@ -308,14 +306,13 @@ __global__ void __launch_bounds__(TEAM, min_ctas_per_sm(TEAM, VPT)) gated_norm_n
     const uint4* in, const uint4* gate, const uint4* __restrict__ weight, int row_vectors, float eps, uint4* out,
     bool coherent, Board board, QuantOut q) {
   __shared__ TeamShared ts;
-  const uint64_t policy = l2_evict_first_policy();
   if (blockIdx.x & 1u) {
-    phase_b<TEAM, VPT, FAST>(out, row_vectors, board, ts, q, policy);
+    phase_b<TEAM, VPT, FAST>(out, row_vectors, board, ts, q);
     return;
   }
   const size_t row = blockIdx.x >> 1;
   if (row >= board.rows) return;
-  const float top = gated_norm_row<TEAM, VPT, FAST>(in, gate, weight, row, row_vectors, eps, out, coherent, policy);
+  const float top = gated_norm_row<TEAM, VPT, FAST>(in, gate, weight, row, row_vectors, eps, out, coherent);
   publish_row<TEAM / 32>(board, ts, row, top);
 }
 
@@ -346,15 +343,14 @@ __global__ void __launch_bounds__(TEAM) small_norm_nvfp4_kernel(const uint4* a, 
                                                                  size_t group_rows, float* global_out, uint32_t* error,
                                                                  QuantOut q) {
   __shared__ TeamShared ts;
-  const uint64_t policy = l2_evict_first_policy();
   const size_t first = blockIdx.x * group_rows;
   const size_t last = min(rows, first + group_rows);
   if (blockIdx.x == 0 && threadIdx.x == 0) *error = 0u;
   float top = 0.0f;
   for (size_t row = first; row < last; ++row) {
-    const float t = GATED ? gated_norm_row<TEAM, VPT, false>(a, b, weight, row, row_vectors, eps, out, coherent, policy)
+    const float t = GATED ? gated_norm_row<TEAM, VPT, false>(a, b, weight, row, row_vectors, eps, out, coherent)
                           : residual_norm_row<TEAM, VPT, false>(a, b, weight, row, row_vectors, width, eps,
-                                                                residual_out, out, coherent, policy, ts);
+                                                                residual_out, out, coherent, ts);
     top = fmaxf(top, t);
     __syncthreads();  // the reduction scratch is reused by the next row
   }
@@ -363,7 +359,7 @@ __global__ void __launch_bounds__(TEAM) small_norm_nvfp4_kernel(const uint4* a, 
   for (size_t row = first; row < last; ++row) {
     quantize_row<TEAM, VPT, false>(out + row * static_cast<size_t>(row_vectors), row_vectors, amax_bits, ts,
                                    q.codes + row * static_cast<size_t>(row_vectors),
-                                   q.scales + row * static_cast<size_t>(row_vectors / 2), q.wide_scale_stores, policy);
+                                   q.scales + row * static_cast<size_t>(row_vectors / 2), q.wide_scale_stores);
     __syncthreads();  // the reciprocal table and the scale bytes are reused by the next row
   }
 }
@@ -380,7 +376,6 @@ __global__ void __launch_bounds__(TEAM, min_ctas_per_sm(TEAM, VPT)) pointwise_nv
   __shared__ TeamShared ts;
   constexpr int kChunk = TEAM * VPT;
   const int tid = threadIdx.x;
-  const uint64_t policy = l2_evict_first_policy();
   const size_t idx = blockIdx.x >> 1;
   if (blockIdx.x & 1u) {
     if (idx < board.lag || idx - board.lag >= board.rows) return;
@@ -388,7 +383,7 @@ __global__ void __launch_bounds__(TEAM, min_ctas_per_sm(TEAM, VPT)) pointwise_nv
     const size_t base = chunk * kChunk;
     const int n = FAST ? kChunk : static_cast<int>(min(static_cast<size_t>(kChunk), count - base));
     quantize_cached_row<TEAM, VPT, FAST>(out + base, n, board, ts, chunk, q.codes + base, q.scales + base / 2,
-                                         q.wide_scale_stores, policy);
+                                         q.wide_scale_stores);
     return;
   }
   if (idx >= board.rows) return;
@@ -399,13 +394,13 @@ __global__ void __launch_bounds__(TEAM, min_ctas_per_sm(TEAM, VPT)) pointwise_nv
   for (int i = 0; i < VPT; ++i) {
     const int v = tid + i * TEAM;
     if (FAST) {
-      g[i] = ld_stream(gate + base + v, policy);
-      u[i] = ld_stream(up + base + v, policy);
+      g[i] = ld_stream(gate + base + v);
+      u[i] = ld_stream(up + base + v);
     } else {
       g[i] = u[i] = make_uint4(0, 0, 0, 0);
       if (v < n) {
-        g[i] = coherent ? ld_vec(gate + base + v) : ld_stream(gate + base + v, policy);
-        u[i] = coherent ? ld_vec(up + base + v) : ld_stream(up + base + v, policy);
+        g[i] = coherent ? ld_vec(gate + base + v) : ld_stream(gate + base + v);
+        u[i] = coherent ? ld_vec(up + base + v) : ld_stream(up + base + v);
       }
     }
   }
@@ -420,7 +415,7 @@ __global__ void __launch_bounds__(TEAM, min_ctas_per_sm(TEAM, VPT)) pointwise_nv
     for (int j = 0; j < 8; ++j) a[j] = Op::apply(a[j], b[j]);
     const uint4 y = pack8(a);
     top = fmaxf(top, amax8_float(a, y));
-    if (FAST || v < n) st_vec(out + base + v, y);  // default policy: phase B finds it in L2
+    if (FAST || v < n) st_vec(out + base + v, y);  // phase B finds it in L2
   }
   publish_row<TEAM / 32>(board, ts, idx, top);
 }
