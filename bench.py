@@ -1,30 +1,36 @@
 #!/usr/bin/env python
 """Benchmark of the fused per-layer operator path.
 
-A *step* is one pass of the hot path over one batch: the embedding gather followed by the operator
-chains of all 64 layers (48 gated-delta-net + 16 full-attention) over this rank's token shard.  The
-default shard is 16384 tokens per GPU, i.e. the 8-way share of the 131072-token long-context
-configuration, so N GPUs process N x 16384 tokens per step (weak scaling, no collective on the data
-path).  Every tensor is far larger than the 126 MB L2, so no flush is needed between iterations.
+A *step* is one pass of the hot path over one prompt: the embedding gather followed by the operator
+chains of all 64 layers (48 gated-delta-net + 16 full-attention) over every token row of the prompt.
+The prompt is the long-context configuration, 131072 tokens (``--config 3`` selects the 60000-token
+row-partition configuration instead); with N GPUs its rows are cut into N contiguous chunk-aligned
+shards, one per rank, with no collective on the data path (strong scaling: the prompt is the same at
+every N).  Every tensor is far larger than the 126 MB L2, so no flush is needed between iterations.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--tokens T] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--config 4|3] [--impl ours|reference]
 
 Prints ONE JSON line (rank 0): whole-job tokens/s with inputs resident in HBM (`value`), the same
-through the C ABI with host buffers and the copies inside the timed region (`e2e`), the roofline of
-the dominant kernel, a per-operator table, the CPU baseline and the clocks seen under load.
+through the C ABI with host buffers and the copies inside the timed region (`e2e`, with the bound the
+copies alone set), the roofline of the dominant kernel, a per-operator table (microseconds, GB/s,
+fraction of the HBM peak, and microseconds x SM MHz so that runs under different power-cap states can
+be compared), the CPU baseline and the clocks seen under load.
 
 `--impl reference` times the reference's own host reference ops (oracle/_ref when it was built, else
-the C restatement) on all host cores, on a bounded sample of the same workload.
+the C restatement) on all host cores, every step a pass of all 64 layers over a bounded sample of the
+prompt's rows.
 """
 from __future__ import annotations
 
 import argparse
 import importlib
 import json
+import math
 import os
 import statistics
 import subprocess
 import sys
+import threading
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
@@ -33,14 +39,8 @@ if ROOT not in sys.path:
 
 METRIC = "prefill tokens/s through the fused layer-op chain (embedding + 64 layers)"
 UNIT = "tokens/s"
-
-
-# DRAM traffic of the dominant kernel (SwiGLU), from one ncu capture of an 8192-token launch:
-# dram__bytes.sum.per_second x gpu__time_duration = 817.9 MB read + written, i.e. 99841 bytes per token
-# against 104448 algorithmic ones (the tail of the output is still dirty in L2 when the kernel ends).
-# Traffic grows in proportion to the tokens, so a launch of T tokens is reported as this figure x T.
-SWIGLU_DRAM_BYTES_PER_TOKEN = 99841
-SWIGLU_TRAFFIC_SOURCE = "ncu, 8192-token launch scaled by tokens (profiles/layer_ops_8192_tokens_ncu_sections.md)"
+CONFIG_TOKENS = {4: 131072, 3: 60000}
+TRAFFIC_FILE = os.path.join(ROOT, "profiles", "swiglu_dram_traffic.txt")
 
 
 def parse_args():
@@ -48,15 +48,18 @@ def parse_args():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--tokens", type=int, default=16384, help="token rows per GPU")
+    ap.add_argument("--config", type=int, default=4, choices=sorted(CONFIG_TOKENS),
+                    help="4 = the 131072-token long-context prompt (default), 3 = the 60000-token row partition")
+    ap.add_argument("--total-tokens", type=int, default=None, help="prompt length (overrides --config)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--cpu-sample-tokens", type=int, default=8192)
+    ap.add_argument("--cpu-sample-tokens", type=int, default=1024)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
-    ap.add_argument("--probe-reps", type=int, default=3)
+    ap.add_argument("--probe-ms", type=float, default=120.0, help="aimed-at duration of one operator probe")
     ap.add_argument("--probe-only", action="store_true",
                     help="time each operator alone (few launches; the form profiled under ncu) and exit")
+    ap.add_argument("--probe-reps", type=int, default=3)
     return ap.parse_args()
 
 
@@ -66,62 +69,130 @@ def measured_peak():
         with open(path) as f:
             return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
     except Exception:
-        return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+        return 6650.0, "fallback (6.65 TB/s, the recipe's stated figure)"
+
+
+def swiglu_traffic():
+    """DRAM bytes per token of the dominant kernel from the tracked ncu summary (None when absent)."""
+    info = {}
+    try:
+        with open(TRAFFIC_FILE) as f:
+            for line in f:
+                if ":" in line and not line.lstrip().startswith("#"):
+                    k, v = line.split(":", 1)
+                    info[k.strip()] = v.strip()
+        return float(info["dram_bytes_per_token"]), info.get("captured_at_commit"), info.get("capture_tokens")
+    except Exception:
+        return None, None, None
 
 
 # ------------------------------------------------------------------------------------ clocks
 
 class ClockSampler:
+    """Samples SM clock, power and throttle reasons of one GPU while a region runs: NVML in a thread of
+    this process when pynvml is importable (a few hundred samples per second), else an `nvidia-smi -lms`
+    child.  Read-only: no clock or limit is ever set."""
+
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    _nvml = None
+    _handles = {}
 
-    def __init__(self, gpu_index: int):
+    @classmethod
+    def _handle(cls, cuda_index):
+        if cls._nvml is None:
+            import pynvml
+
+            pynvml.nvmlInit()
+            cls._nvml = pynvml
+        if cuda_index not in cls._handles:
+            import torch
+
+            uuid = str(torch.cuda.get_device_properties(cuda_index).uuid)
+            if not uuid.startswith("GPU-"):
+                uuid = "GPU-" + uuid
+            cls._handles[cuda_index] = cls._nvml.nvmlDeviceGetHandleByUUID(uuid.encode())
+        return cls._handles[cuda_index]
+
+    def __init__(self, cuda_index: int, period_s: float = 0.004):
+        self.sm, self.power, self.reasons = [], [], set()
+        self.max_mhz = None
         self.proc = None
-        self.gpu = gpu_index
+        self.thread = None
+        self._stop = threading.Event()
         try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
-                 "-i", str(gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            h = self._handle(cuda_index)
+            n = self._nvml
+            self.max_mhz = float(n.nvmlDeviceGetMaxClockInfo(h, n.NVML_CLOCK_SM))
+
+            def loop():
+                while not self._stop.is_set():
+                    try:
+                        self.sm.append(float(n.nvmlDeviceGetClockInfo(h, n.NVML_CLOCK_SM)))
+                        self.power.append(n.nvmlDeviceGetPowerUsage(h) / 1000.0)
+                        mask = int(n.nvmlDeviceGetCurrentClocksThrottleReasons(h))
+                        for bit, name in self.REASONS.items():
+                            if mask & bit:
+                                self.reasons.add(name)
+                    except Exception:
+                        pass
+                    time.sleep(period_s)
+
+            self.thread = threading.Thread(target=loop, daemon=True)
+            self.thread.start()
         except Exception:
-            self.proc = None
+            self.thread = None
+            try:
+                self.proc = subprocess.Popen(
+                    ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                     "-i", str(cuda_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            except Exception:
+                self.proc = None
 
     def stop(self):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
-        self.proc.terminate()
-        try:
-            out, _ = self.proc.communicate(timeout=5)
-        except Exception:
-            self.proc.kill()
-            out = ""
-        sm, mx, reasons, power = [], [], set(), []
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in out.splitlines():
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 9:
-                continue
+        if self.thread is not None:
+            self._stop.set()
+            self.thread.join(timeout=2)
+        elif self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
             try:
-                sm.append(float(parts[1]))
-                mx.append(float(parts[2]))
-                power.append(float(parts[3]))
-            except ValueError:
-                continue
-            for n, v in zip(names, parts[5:9]):
-                if v.lower().startswith("active"):
-                    reasons.add(n)
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+                out, _ = self.proc.communicate(timeout=5)
+            except Exception:
+                self.proc.kill()
+                out = ""
+            names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+            mx = []
+            for line in out.splitlines():
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) < 9:
+                    continue
+                try:
+                    self.sm.append(float(parts[1]))
+                    mx.append(float(parts[2]))
+                    self.power.append(float(parts[3]))
+                except ValueError:
+                    continue
+                for nme, v in zip(names, parts[5:9]):
+                    if v.lower().startswith("active"):
+                        self.reasons.add(nme)
+            self.max_mhz = max(mx) if mx else None
+        else:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no clock source"]}
+        return {"sm_mhz": statistics.median(self.sm) if self.sm else None, "sm_max_mhz": self.max_mhz,
+                "power_w_max": max(self.power) if self.power else None, "samples": len(self.sm),
+                "reasons": sorted(self.reasons)}
 
 
 # ------------------------------------------------------------------------------------ CPU arm
 
 def cpu_chain_runner(sample_tokens: int, threads: int):
-    """Sets up the reference's host reference ops over `sample_tokens` rows of the 4-layer pattern
-    (GDN, GDN, GDN, full attention) plus the embedding gather, rows split over `threads` host threads.
-    Returns (run, kind); every run() call is one timed pass over the same inputs and returns
-    (seconds for 4 layers, seconds for the embedding)."""
+    """Sets up the reference's host reference ops over `sample_tokens` token rows: the embedding gather and
+    all 64 layers in the model's pattern (GDN, GDN, GDN, full attention, x16), rows split over `threads`
+    host threads.  Returns (run, kind); every run() call is one timed pass over the same inputs and returns
+    its wall-clock seconds."""
     import ctypes as C
 
     import numpy as np
@@ -137,8 +208,8 @@ def cpu_chain_runner(sample_tokens: int, threads: int):
     T, H, I = sample_tokens, 5120, 17408
 
     def bf(shape, std=1.0):
-        # N(0, std) values; long tensors repeat a 256-row block (the ops are row-local and their cost
-        # does not depend on the values, and drawing a billion normals would take longer than the timing)
+        # N(0, std) values; long tensors repeat a 256-row block (the ops are row-local and their cost does
+        # not depend on the values)
         rows = shape[0] if len(shape) > 1 else 1
         if rows <= 256:
             return orc.bf16_encode((rng.standard_normal(shape) * std).astype(np.float32))
@@ -152,14 +223,18 @@ def cpu_chain_runner(sample_tokens: int, threads: int):
     res = [bf((T, H)), np.empty((T, H), np.uint16)]
     nrm = np.empty((T, H), np.uint16)
     conv_out = np.empty((T, 10240), np.uint16)
+    q_l2, k_l2 = np.empty((T, 2048), np.uint16), np.empty((T, 2048), np.uint16)
     gdn_out = np.empty((T, 6144), np.uint16)
     q_out, gate_out = np.empty((T, 6144), np.uint16), np.empty((T, 6144), np.uint16)
     attn_out, mlp_out = np.empty((T, 6144), np.uint16), np.empty((T, I), np.uint16)
     codes, scales = np.empty((T, H // 2), np.uint8), np.empty((T, H // 16), np.uint8)
     gcodes, gscales = np.empty((T, 3072), np.uint8), np.empty((T, 384), np.uint8)
-    gs = np.empty(max(1, -(-T // 512)), np.float32)
+    gs = np.full(max(1, -(-T // 512)), 0.0025, np.float32)
     qscale = float(np.float32(1.0) / np.sqrt(np.float32(128.0)))
     eps = 1e-6
+    table = bf((4096, H), 0.02)
+    ids = rng.integers(0, 4096, size=T, dtype=np.uint32)
+    emb = np.empty((T, H), np.uint16)
 
     def at(a, row, ty=u16p):
         return C.cast(a.ctypes.data + row * a.strides[0], ty)
@@ -172,99 +247,80 @@ def cpu_chain_runner(sample_tokens: int, threads: int):
         else:
             L.residual_norm(at(res[src], lo), at(inp["proj"], lo), at(w["norm"], 0), n, H, eps, at(res[dst], lo),
                             at(nrm, lo))
-
-    def quantize(x, c, s, cols, lo, hi):
         # the NVFP4 activation encoder has no reference implementation: the restatement is timed
-        L.quant_ws(at(x, lo), hi - lo, cols, 0, gs.ctypes.data_as(f32p), at(c, lo, u8p), at(s, lo, u8p))
+        L.quant_ws(at(nrm, lo), n, H, 0, gs.ctypes.data_as(f32p), at(codes, lo, u8p), at(scales, lo, u8p))
+
+    def mlp(lo, hi):
+        (R.silu_mul if R is not None else L.silu_mul)(at(inp["gate"], lo), at(inp["up"], lo), (hi - lo) * I,
+                                                     at(mlp_out, lo))
 
     def gdn_layer(src, dst, lo, hi):
         n = hi - lo
         residual_norm(src, dst, lo, hi)
-        quantize(nrm, codes, scales, H, lo, hi)
         hist = np.zeros((10240, 3), np.uint16)
         if lo >= 3:
             hist[:] = inp["raw"][lo - 3:lo].T
         if R is not None:
-            for t in range(lo, hi):
-                R.conv(at(inp["raw"], t), at(w["conv"], 0), at(hist, 0), at(conv_out, t))
+            R.conv_rows(at(inp["raw"], lo), n, at(w["conv"], 0), at(hist, 0), at(conv_out, lo))
         else:
             L.conv(at(inp["raw"], lo), n, 10240, at(w["conv"], 0), at(hist, 0), at(conv_out, lo))
-        for off, sc in ((0, qscale), (2048, 1.0)):
-            blk = np.ascontiguousarray(conv_out[lo:hi, off:off + 2048])
-            L.l2(at(blk, 0), n * 16, 128, eps, sc, at(blk, 0))
-            conv_out[lo:hi, off:off + 2048] = blk
+        # q/k L2 norm over the heads of each row (strided views are gathered into compact buffers first,
+        # outside the op; the reference's op has no q scale, which costs nothing either way)
+        q_l2[lo:hi] = conv_out[lo:hi, :2048]
+        k_l2[lo:hi] = conv_out[lo:hi, 2048:4096]
+        for blk, sc in ((q_l2, qscale), (k_l2, 1.0)):
+            if R is not None:
+                R.l2(at(blk, lo), n * 16, 128, eps, at(blk, lo))
+            else:
+                L.l2(at(blk, lo), n * 16, 128, eps, sc, at(blk, lo))
         if R is not None:
             R.head_plain_gate(at(inp["core"], lo), at(w["gn"], 0), at(inp["z"], lo), n * 48, 128, eps, at(gdn_out, lo))
         else:
             L.headwise(at(inp["core"], lo), at(w["gn"], 0), at(inp["z"], lo), n * 48, 128, eps, 0, at(gdn_out, lo))
-        quantize(gdn_out, gcodes, gscales, 6144, lo, hi)
+        L.quant_ws(at(gdn_out, lo), n, 6144, 0, gs.ctypes.data_as(f32p), at(gcodes, lo, u8p), at(gscales, lo, u8p))
         residual_norm(dst, src, lo, hi)
-        quantize(nrm, codes, scales, H, lo, hi)
-        (R.silu_mul if R is not None else L.silu_mul)(at(inp["gate"], lo), at(inp["up"], lo), n * I, at(mlp_out, lo))
+        mlp(lo, hi)
 
     def fa_layer(src, dst, lo, hi):
         n = hi - lo
         residual_norm(src, dst, lo, hi)
-        quantize(nrm, codes, scales, H, lo, hi)
-        if R is not None:
-            ref_preprocess(lo, hi)
-        else:
-            L.preprocess(at(inp["qg"], lo), at(inp["key"], lo), at(w["qn"], 0), at(w["kn"], 0), eps, at(q_out, lo),
-                         at(gate_out, lo), cos.ctypes.data_as(f32p), sin.ctypes.data_as(f32p), lo, n)
+        fn = R.preprocess_rows if R is not None else L.preprocess
+        fn(at(inp["qg"], lo), at(inp["key"], lo), at(w["qn"], 0), at(w["kn"], 0), eps, at(q_out, lo), at(gate_out, lo),
+           cos.ctypes.data_as(f32p), sin.ctypes.data_as(f32p), lo, n)
         (R.sigmoid_gate if R is not None else L.sigmoid_gate)(at(inp["val"], lo), at(gate_out, lo), n * 6144,
                                                              at(attn_out, lo))
         residual_norm(dst, src, lo, hi)
-        quantize(nrm, codes, scales, H, lo, hi)
-        (R.silu_mul if R is not None else L.silu_mul)(at(inp["gate"], lo), at(inp["up"], lo), n * I, at(mlp_out, lo))
+        mlp(lo, hi)
 
-    def ref_preprocess(lo, hi):
-        n = hi - lo
-        for t in range(lo, hi):
-            R.split(at(inp["qg"], t), 24, 256, at(q_out, t), at(gate_out, t))
-        R.head_centered(at(q_out, lo), at(w["qn"], 0), n * 24, 256, eps, at(q_out, lo))
-        R.head_centered(at(inp["key"], lo), at(w["kn"], 0), n * 4, 256, eps, at(inp["key"], lo))
-        for t in range(lo, hi):
-            c, s = C.cast(cos.ctypes.data + t * 128, f32p), C.cast(sin.ctypes.data + t * 128, f32p)
-            R.rope(at(q_out, t), c, s, 24, at(q_out, t))
-            R.rope(at(inp["key"], t), c, s, 4, at(inp["key"], t))
-
-    def four_layers(lo, hi):
-        gdn_layer(0, 1, lo, hi)
-        gdn_layer(0, 1, lo, hi)
-        gdn_layer(0, 1, lo, hi)
-        fa_layer(0, 1, lo, hi)
-
-    gs[:] = 0.0025
-    table = bf((4096, H), 0.02)
-    ids = rng.integers(0, 4096, size=T, dtype=np.uint32)
-    emb = np.empty((T, H), np.uint16)
-
-    def embed(lo, hi):
+    def whole_chain(lo, hi):
         if R is not None:
-            for t in range(lo, hi):
-                R.embedding(at(table, 0), 4096, H, int(ids[t]), at(emb, t))
+            R.embedding_rows(at(table, 0), 4096, H, C.cast(ids.ctypes.data + lo * 4, u32p), hi - lo, at(emb, lo))
         else:
             L.embedding(at(table, 0), 4096, H, C.cast(ids.ctypes.data + lo * 4, u32p), hi - lo, at(emb, lo))
+        for layer in range(64):
+            (fa_layer if (layer + 1) % 4 == 0 else gdn_layer)(0, 1, lo, hi)
 
     def run():
         t0 = time.perf_counter()
-        orc.parallel_rows(four_layers, T, threads)
-        t_layers = time.perf_counter() - t0
-        t0 = time.perf_counter()
-        orc.parallel_rows(embed, T, threads)
-        return t_layers, time.perf_counter() - t0
+        orc.parallel_rows(whole_chain, T, threads)
+        return time.perf_counter() - t0
 
     return run, kind
 
 
-def cpu_tokens_per_second(sample_tokens: int, threads: int, repeats: int = 1):
+CPU_SAMPLE_NOTE = ("{n}-token sample of the prompt, embedding gather + all 64 layers (GDN,GDN,GDN,FA x16) through the "
+                   "reference's host ops, rows over {c} threads; NVFP4 encoder from the C restatement; "
+                   "tokens/s = sample tokens / wall time of the pass (the ops are row-local, so the rate does not "
+                   "depend on the prompt length)")
+
+
+def cpu_tokens_per_second(sample_tokens: int, threads: int, warmup: int = 1, repeats: int = 3):
     run, kind = cpu_chain_runner(sample_tokens, threads)
-    best = None
-    for _ in range(max(1, repeats)):
-        t_layers, t_embed = run()
-        total = t_layers * 16 + t_embed  # 4-layer pattern x 16 = 64 layers
-        best = total if best is None else min(best, total)
-    return sample_tokens / best, best, kind
+    for _ in range(warmup):
+        run()
+    times = [run() for _ in range(max(1, repeats))]
+    mean = sum(times) / len(times)
+    return sample_tokens / mean, mean, kind
 
 
 def run_reference_arm(args):
@@ -272,22 +328,23 @@ def run_reference_arm(args):
     if rank != 0:
         return 0
     threads = os.cpu_count() or 1
-    times = []
     run, kind = cpu_chain_runner(args.cpu_sample_tokens, threads)
+    times = []
     for i in range(args.warmup + args.steps):
-        t_layers, t_embed = run()
+        t = run()
         if i >= args.warmup:
-            times.append(t_layers * 16 + t_embed)
+            times.append(t)
     per_step = sum(times) / len(times)
     value = args.cpu_sample_tokens / per_step
-    sample = (f"{args.cpu_sample_tokens} tokens x the 4-layer pattern (GDN,GDN,GDN,FA) timed, x16 for 64 layers, "
-              f"+ embedding gather; NVFP4 encoder from the C restatement")
+    total = args.total_tokens or CONFIG_TOKENS[args.config]
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": per_step * 1e3, "higher_is_better": True, "scaling": "weak",
+        "warmup": args.warmup, "ms_per_step": per_step * 1e3, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16 storage, fp32 arithmetic", "data": "synthetic",
-        "config": workload_config(args.tokens, args.gpus),
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": kind, "sample": sample},
+        "config": workload_config(total, args.gpus, None),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": kind, "extrapolated": False,
+                         "sample_tokens": args.cpu_sample_tokens,
+                         "sample": CPU_SAMPLE_NOTE.format(n=args.cpu_sample_tokens, c=threads)},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -295,22 +352,28 @@ def run_reference_arm(args):
     return 0
 
 
-def workload_config(tokens, gpus):
-    return {
-        "workload": ("configs[4] long-context shard: 131072-token prompt token-sharded 8-way = 16384 tokens per GPU"
-                     if tokens == 16384 else f"{tokens}-token shard per GPU") +
-                    ", embedding gather + 64 layers (48 GDN + 16 full-attention) of fused layer ops",
-        "tokens_per_gpu": tokens, "total_tokens": tokens * gpus, "layers": 64, "hidden": 5120,
-        "intermediate": 17408, "nvfp4_scale_scope_tokens": 512, "parallelism": f"token-row shards x{gpus}, no collective",
-        "l2_policy": "every tensor is larger than L2 (>= 168 MB per operand at 16384 tokens); no flush",
+def workload_config(total_tokens, gpus, tokens_this_rank):
+    name = {131072: "configs[4] long context: the 131072-token synthetic prompt",
+            60000: "configs[3]: 60000 uniformly drawn token ids"}.get(total_tokens, f"{total_tokens}-token prompt")
+    cfg = {
+        "workload": name + ", embedding gather + 64 layers (48 GDN + 16 full-attention) of fused layer ops, "
+                           f"token rows partitioned over {gpus} GPU(s) in 512-token chunks",
+        "total_tokens": total_tokens, "layers": 64, "hidden": 5120, "intermediate": 17408,
+        "nvfp4_scale_scope_tokens": 512, "parallelism": f"token-row shards x{gpus}, no collective",
+        "l2_policy": "every tensor is larger than L2 (>= 140 MB per operand at the smallest shard); no flush",
     }
+    if tokens_this_rank is not None:
+        cfg["tokens_rank0"] = tokens_this_rank
+    return cfg
 
 
 # ------------------------------------------------------------------------------------ GPU arm
 
-def probe_ops(stack, chain, stream_obj, T, peak, warm, reps):
+def probe_ops(stack, chain, stream_obj, T, peak, warm, reps=None, aim_ms=120.0, cuda_index=0, sample_clocks=True):
     """Times every fused operator alone with CUDA events on its own stream: microseconds per call,
-    algorithmic GB/s and the fraction of the HBM peak."""
+    algorithmic GB/s, the fraction of the HBM peak, and the SM clock sampled while the probe ran
+    (us x MHz compares runs whose power-cap state differs).  Each probe repeats its operator for about
+    `aim_ms` so that the clock samples fall inside it."""
     import torch
 
     stream = stream_obj.cuda_stream
@@ -322,26 +385,35 @@ def probe_ops(stack, chain, stream_obj, T, peak, warm, reps):
         "attention_preprocess": lambda: stack.op_preprocess(3, stream),
         "sigmoid_gate": lambda: stack.op_sigmoid_gate(stream),
         "swiglu": lambda: stack.op_swiglu(stream),
-        # extra operator, not part of the step: SwiGLU with the NVFP4 operand of the down projection
+        # extra operators, not part of the step: the pointwise ops with the NVFP4 operand of the next projection
         "swiglu_nvfp4": lambda: stack.op_swiglu_nvfp4(stream),
         "sigmoid_gate_nvfp4": lambda: stack.op_sigmoid_gate_nvfp4(stream),
     }
     per_op = {}
     with torch.cuda.stream(stream_obj):
         for name, fn in probes.items():
-            for _ in range(warm):
-                fn()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            for _ in range(warm - 1):
+                fn()
             e0.record(stream_obj)
-            for _ in range(reps):
+            fn()
+            e1.record(stream_obj)
+            stream_obj.synchronize()
+            n = reps if reps else max(5, min(2000, int(math.ceil(aim_ms / max(e0.elapsed_time(e1), 1e-3)))))
+            sampler = ClockSampler(cuda_index) if sample_clocks else None
+            e0.record(stream_obj)
+            for _ in range(n):
                 fn()
             e1.record(stream_obj)
             stream_obj.synchronize()
-            us = e0.elapsed_time(e1) * 1e3 / reps
-            base = name.split("/")[0]
-            gbs = chain.BYTES_PER_TOKEN[base] * T / (us * 1e-6) / 1e9
+            clk = sampler.stop() if sampler else {"sm_mhz": None}
+            us = e0.elapsed_time(e1) * 1e3 / n
+            gbs = chain.BYTES_PER_TOKEN[name] * T / (us * 1e-6) / 1e9
             per_op[name] = {"us": round(us, 2), "algorithmic_GBs": round(gbs, 1), "frac_of_peak": round(gbs / peak, 4),
-                            "bytes_per_token": chain.BYTES_PER_TOKEN[base], "kernels": chain.KERNELS[base]}
+                            "bytes_per_token": chain.BYTES_PER_TOKEN[name], "kernels": chain.KERNELS[name],
+                            "launches_timed": n, "sm_mhz": clk.get("sm_mhz"),
+                            "us_x_mhz": round(us * clk["sm_mhz"], 0) if clk.get("sm_mhz") else None}
+    stack.check_error("operator probes")
     return per_op
 
 
@@ -367,10 +439,51 @@ def decode_step_probe(chain, position=131071, reps=20):
             graph.replay()
         e1.record(side)
     side.synchronize()
-    if int(stack.amax[-1].item()) != 0:
-        raise SystemExit("a bounded device-side wait gave up during the decode probe")
+    stack.check_error("decode probe")
     return {"tokens": 1, "position": position, "us_per_step": round(e0.elapsed_time(e1) * 1e3 / reps, 1),
             "kernels_per_step": chain.kernels_per_step()}
+
+
+def host_memory_available_bytes():
+    """What this process may still take from host memory: MemAvailable, capped by the cgroup limit."""
+    avail = None
+    try:
+        with open("/proc/meminfo") as f:
+            for line in f:
+                if line.startswith("MemAvailable:"):
+                    avail = int(line.split()[1]) * 1024
+    except Exception:
+        pass
+    for limit_path, usage_path in (("/sys/fs/cgroup/memory.max", "/sys/fs/cgroup/memory.current"),
+                                   ("/sys/fs/cgroup/memory/memory.limit_in_bytes",
+                                    "/sys/fs/cgroup/memory/memory.usage_in_bytes")):
+        try:
+            with open(limit_path) as f:
+                raw = f.read().strip()
+            if raw != "max":
+                with open(usage_path) as f:
+                    used = int(f.read().strip())
+                room = int(raw) - used
+                avail = room if avail is None else min(avail, room)
+        except Exception:
+            pass
+    return avail
+
+
+def pinned_empty(shape, dtype):
+    """A page-locked host tensor of exactly the asked size (cudaHostRegister on ordinary memory; torch's own
+    pinned allocator rounds every block up to a power of two, a third more than this workload needs)."""
+    import torch
+
+    t = torch.empty(shape, dtype=dtype)
+    nbytes = t.numel() * t.element_size()
+    if nbytes == 0:
+        return t, False
+    err = torch.cuda.cudart().cudaHostRegister(t.data_ptr(), nbytes, 0)
+    code = int(getattr(err, "value", err))
+    if code != 0:
+        return torch.empty(shape, dtype=dtype, pin_memory=True), False
+    return t, True
 
 
 def main():
@@ -383,6 +496,7 @@ def main():
 
     pkg = importlib.import_module("qwen3x-orin_b200")
     chain = importlib.import_module("qwen3x-orin_b200.chain")
+    shard_mod = importlib.import_module("qwen3x-orin_b200.shard")
     capi = pkg.capi
     capi.load()  # raises when the CUDA library is missing: there is no other implementation
 
@@ -394,12 +508,12 @@ def main():
     torch.cuda.set_device(local_rank)
     distributed = world > 1
     if distributed:
-        # NCCL only carries the barrier and the max-over-ranks of the timings; keep its banner
-        # ("NCCL version ...") off stdout, which must hold exactly one JSON line
-        os.environ["NCCL_DEBUG"] = os.environ.get("Q3X_NCCL_DEBUG", "WARN")
+        # NCCL only carries the barrier, the max-over-ranks of the timings and the untimed validation
+        # gather.  Whatever the communicator set-up prints (its banner, NCCL_DEBUG output) is sent to
+        # stderr so that stdout holds exactly one JSON line.
         sys.stdout.flush()
         saved_stdout = os.dup(1)
-        os.dup2(2, 1)  # whatever the communicator set-up prints goes to stderr
+        os.dup2(2, 1)
         try:
             dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
             dist.barrier()
@@ -408,8 +522,12 @@ def main():
             os.dup2(saved_stdout, 1)
             os.close(saved_stdout)
 
-    T = args.tokens
-    stack = chain.LayerStack(T, first_position=rank * T, seed=1234 + rank)
+    total = args.total_tokens or CONFIG_TOKENS[args.config]
+    mine = shard_mod.shard_for(total, rank, world)
+    T = mine.tokens
+    if T == 0:
+        raise SystemExit(f"rank {rank} owns no rows of a {total}-token prompt over {world} ranks")
+    stack = chain.LayerStack(T, first_position=mine.first_token, seed=1234 + rank)
     stream_obj = torch.cuda.Stream()
     stream = stream_obj.cuda_stream
 
@@ -419,10 +537,17 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    def max_over_ranks(ms):
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        if distributed:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
     if args.probe_only:
         peak, _ = measured_peak()
-        print(json.dumps({"probe_only": True, "tokens": T, "per_op": probe_ops(stack, chain, stream_obj, T, peak, 1, args.probe_reps)}),
-              flush=True)
+        print(json.dumps({"probe_only": True, "tokens": T,
+                          "per_op": probe_ops(stack, chain, stream_obj, T, peak, 1, reps=args.probe_reps,
+                                              cuda_index=local_rank, sample_clocks=False)}), flush=True)
         return 0
 
     # ---- warm-up (eager), then capture one step into a CUDA graph ------------------------------
@@ -446,8 +571,9 @@ def main():
         else:
             stack.enqueue_step(stream)
 
+    warmup = max(args.warmup, 3)
     with torch.cuda.stream(stream_obj):
-        for _ in range(max(args.warmup, 3)):
+        for _ in range(warmup):
             one_step()
     barrier()
 
@@ -460,131 +586,57 @@ def main():
             one_step()
         stop.record(stream_obj)
     barrier()
-    elapsed_ms = start.elapsed_time(stop)
     clocks = sampler.stop() if sampler else None
-    # the single-kernel NVFP4 operators report a bounded wait that gave up in the last scratch word
-    if int(stack.amax[-1].item()) != 0:
-        raise SystemExit("a bounded device-side wait gave up during the timed steps: results invalid")
-    t = torch.tensor([elapsed_ms], device="cuda", dtype=torch.float64)
-    if distributed:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    elapsed_ms = float(t.item())
-    ms_per_step = elapsed_ms / args.steps
-    value = T * world / (ms_per_step * 1e-3)
+    stack.check_error("timed steps")  # sticky flag: covers every NVFP4 call since the stack was built
+    ms_per_step = max_over_ranks(start.elapsed_time(stop)) / args.steps
+    value = total / (ms_per_step * 1e-3)
 
     # ---- per-operator timing (each op alone, CUDA events on its stream) --------------------------
     peak, peak_kind = measured_peak()
-    per_op = probe_ops(stack, chain, stream_obj, T, peak, 3, 10) if rank == 0 else {}
+    per_op = probe_ops(stack, chain, stream_obj, T, peak, 3, aim_ms=args.probe_ms, cuda_index=local_rank) if rank == 0 else {}
     # dominant kernel = the SwiGLU stream (the largest share of the step's bytes, one kernel per launch)
     roofline = None
     if rank == 0:
         sw = per_op["swiglu"]
+        per_token, traffic_commit, capture_tokens = swiglu_traffic()
         roofline = {"bound": "hbm", "kernel": "binary_vec_kernel<SiluMul> (SwiGLU)", "achieved": sw["algorithmic_GBs"],
                     "peak": peak, "unit": "GB/s", "frac": round(sw["algorithmic_GBs"] / peak, 4), "peak_source": peak_kind,
-                    "traffic": SWIGLU_DRAM_BYTES_PER_TOKEN * T, "traffic_source": SWIGLU_TRAFFIC_SOURCE,
+                    "traffic": per_token * T if per_token else None,
+                    "traffic_source": (f"ncu dram__bytes_read.sum + dram__bytes_write.sum of a {capture_tokens}-token "
+                                       f"launch, scaled by tokens (profiles/{os.path.basename(TRAFFIC_FILE)})"
+                                       if per_token else None),
+                    "traffic_commit": traffic_commit,
                     "algorithmic_bytes_per_launch": chain.BYTES_PER_TOKEN["swiglu"] * T,
-                    "us_per_launch": sw["us"]}
+                    "us_per_launch": sw["us"], "launch_tokens": T}
         step_bytes = chain.bytes_per_token_per_step() * T
-        roofline["whole_step"] = {"algorithmic_GBs": round(step_bytes / (ms_per_step * 1e-3) / 1e9, 1),
-                                  "frac": round(step_bytes / (ms_per_step * 1e-3) / 1e9 / peak, 4),
-                                  "bytes_per_token": chain.bytes_per_token_per_step()}
+        rank_ms = start.elapsed_time(stop) / args.steps
+        roofline["whole_step"] = {"algorithmic_GBs": round(step_bytes / (rank_ms * 1e-3) / 1e9, 1),
+                                  "frac": round(step_bytes / (rank_ms * 1e-3) / 1e9 / peak, 4),
+                                  "bytes_per_token": chain.bytes_per_token_per_step(),
+                                  "sum_of_per_op_ms": round(sum(per_op[o]["us"] for l in range(64) for o in chain.layer_ops(l)) / 1e3
+                                                            + per_op["embedding_gather"]["us"] / 1e3, 3),
+                                  "ms_per_step_rank0": round(rank_ms, 3)}
 
     # ---- end to end: host buffers, H2D of the step's inputs and D2H of its result inside the timing --
     e2e = None
     if not args.no_e2e:
-        # Two device input sets, each baked into its own graph: while step i computes on set i % 2,
-        # the copy engine brings step i + 1's inputs from pinned host memory into the other set and
-        # takes step i - 1's result back.  Every step's inputs and result cross PCIe inside the timing.
-        names = list(stack.inputs)
-        host_in = {n: torch.empty(stack.inputs[n].shape, dtype=torch.bfloat16, pin_memory=True) for n in names}
-        for n in names:
-            host_in[n].copy_(stack.inputs[n])
-        host_ids = torch.empty(stack.token_ids.shape, dtype=torch.int32, pin_memory=True)
-        host_ids.copy_(stack.token_ids)
-        host_out = [torch.empty((T, 5120), dtype=torch.bfloat16, pin_memory=True) for _ in range(2)]
-        staged_out = [torch.empty((T, 5120), dtype=torch.bfloat16, device="cuda") for _ in range(2)]
-        h2d = sum(v.numel() * 2 for v in host_in.values()) + host_ids.numel() * 4
-        d2h = host_out[0].numel() * 2
-        stack.add_input_set()
-        graphs = [graph, None]
-        if graph is not None:
-            try:
-                stack.active = 1
-                graphs[1] = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(graphs[1], stream=stream_obj):
-                    stack.enqueue_step(torch.cuda.current_stream().cuda_stream)
-            except Exception as exc:
-                print(f"[bench] second graph capture failed ({exc}); e2e launches eagerly", file=sys.stderr)
-                graphs = [None, None]
-                torch.cuda.synchronize()
-            stack.active = 0
-        h2d_stream, d2h_stream = torch.cuda.Stream(), torch.cuda.Stream()
-        filled = [torch.cuda.Event() for _ in range(2)]
-        consumed = [torch.cuda.Event() for _ in range(2)]
-        staged = [torch.cuda.Event() for _ in range(2)]
-        drained = [torch.cuda.Event() for _ in range(2)]
-
-        def e2e_steps(count):
-            for i in range(count):
-                s = i % 2
-                with torch.cuda.stream(h2d_stream):
-                    if i >= 2:
-                        h2d_stream.wait_event(consumed[s])      # step i - 2 no longer reads this set
-                    for n in names:
-                        stack.input_sets[s][n].copy_(host_in[n], non_blocking=True)
-                    stack.id_sets[s].copy_(host_ids, non_blocking=True)
-                    filled[s].record(h2d_stream)
-                with torch.cuda.stream(stream_obj):
-                    stream_obj.wait_event(filled[s])
-                    if graphs[s] is not None:
-                        graphs[s].replay()
-                    else:
-                        stack.active = s
-                        stack.enqueue_step(stream)
-                        stack.active = 0
-                    consumed[s].record(stream_obj)
-                    if i >= 2:
-                        stream_obj.wait_event(drained[s])       # the host copy of step i - 2's result is done
-                    staged_out[s].copy_(stack.residual[final_idx], non_blocking=True)
-                    staged[s].record(stream_obj)
-                with torch.cuda.stream(d2h_stream):
-                    d2h_stream.wait_event(staged[s])
-                    host_out[s].copy_(staged_out[s], non_blocking=True)
-                    drained[s].record(d2h_stream)
-
-        e2e_steps(2)
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(h2d_stream)
-        e2e_steps(args.steps)
-        d2h_stream.wait_stream(stream_obj)
-        d2h_stream.wait_stream(h2d_stream)
-        e1.record(d2h_stream)
-        barrier()
-        t = torch.tensor([e0.elapsed_time(e1)], device="cuda", dtype=torch.float64)
-        if distributed:
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = float(t.item()) / args.steps
-        e2e = {"value": T * world / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-               "ms_per_step": e2e_ms,
-               "note": "per step: pinned-host inputs -> device, 64-layer chain, final residual -> pinned host; the "
-                       "copies of neighbouring steps overlap the chain (two device input sets)"}
+        e2e = run_e2e(args, torch, dist, stack, graph, stream_obj, final_idx, T, total, world, barrier, max_over_ranks)
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         threads = os.cpu_count() or 1
         v, secs, kind = cpu_tokens_per_second(args.cpu_sample_tokens, threads)
-        cpu = {"value": v, "unit": UNIT, "cores": threads, "kind": kind,
-               "sample": f"{args.cpu_sample_tokens} tokens x 4-layer pattern timed, x16 for 64 layers, + embedding gather "
-                         f"({secs:.2f} s extrapolated per pass)"}
+        cpu = {"value": v, "unit": UNIT, "cores": threads, "kind": kind, "extrapolated": False,
+               "sample_tokens": args.cpu_sample_tokens, "seconds_per_pass": round(secs, 3),
+               "sample": CPU_SAMPLE_NOTE.format(n=args.cpu_sample_tokens, c=threads)}
 
     decode = decode_step_probe(chain) if rank == 0 else None
     validation = validate_shards(rank, world, dist) if distributed else None
     if rank == 0:
         line = {
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
-            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "bf16 storage, fp32 arithmetic", "data": "synthetic", "config": workload_config(T, world),
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warmup,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16 storage, fp32 arithmetic", "data": "synthetic", "config": workload_config(total, world, T),
             "roofline": roofline, "per_op": per_op, "cpu_baseline": cpu, "e2e": e2e,
             "gpu_launches": chain.kernels_per_step() * args.steps, "cuda_graph": graph is not None, "clocks": clocks,
         }
@@ -592,10 +644,124 @@ def main():
         if validation is not None:
             line["validation"] = validation
         print(json.dumps(line), flush=True)
+    failed = validation is not None and not validation.get("all_ranks_bit_exact", False)
     if distributed:
         dist.barrier()
         dist.destroy_process_group()
+    if failed:
+        print("[bench] the sharded run is NOT bit-identical to the unsharded run", file=sys.stderr)
+        return 3
     return 0
+
+
+def run_e2e(args, torch, dist, stack, graph, stream_obj, final_idx, T, total, world, barrier, max_over_ranks):
+    """The step through the C ABI from pinned host buffers: two device input sets, each baked into its own
+    graph; while step i computes on set i % 2 the copy engine brings step i + 1's nine synthetic projection
+    outputs + ids in from pinned host memory and takes step i - 1's final residual out.  Every step's inputs
+    and result cross PCIe inside the timed region.  Then the same loop with the kernels left out gives the
+    bound the copies alone set on this host (all ranks copying at once)."""
+    names = list(stack.inputs)
+    need = sum(stack.inputs[n].numel() * 2 for n in names) + 2 * T * 5120 * 2
+    avail = host_memory_available_bytes()
+    # collective decision, so that every rank takes the same branch
+    ok = torch.tensor([int(avail is None or need * 1.5 < avail / max(1, min(world, 8)))], device="cuda")
+    if dist.is_initialized():
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    if not bool(ok.item()):
+        return {"value": None, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
+                "skipped": f"host memory: {need / 1e9:.1f} GB of pinned buffers needed per rank, "
+                           f"{(avail or 0) / 1e9:.1f} GB available"}
+    stream = stream_obj.cuda_stream
+    host_in, registered = {}, []
+    for n in names:
+        host_in[n], reg = pinned_empty(stack.inputs[n].shape, torch.bfloat16)
+        registered.append(reg)
+        host_in[n].copy_(stack.inputs[n])
+    host_ids, _ = pinned_empty(stack.token_ids.shape, torch.int32)
+    host_ids.copy_(stack.token_ids)
+    host_out = [pinned_empty((T, 5120), torch.bfloat16)[0] for _ in range(2)]
+    staged_out = [torch.empty((T, 5120), dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+    h2d = sum(v.numel() * 2 for v in host_in.values()) + host_ids.numel() * 4
+    d2h = host_out[0].numel() * 2
+    stack.add_input_set()
+    graphs = [graph, None]
+    if graph is not None:
+        try:
+            stack.active = 1
+            graphs[1] = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graphs[1], stream=stream_obj):
+                stack.enqueue_step(torch.cuda.current_stream().cuda_stream)
+        except Exception as exc:
+            print(f"[bench] second graph capture failed ({exc}); e2e launches eagerly", file=sys.stderr)
+            graphs = [None, None]
+            torch.cuda.synchronize()
+        stack.active = 0
+    h2d_stream, d2h_stream = torch.cuda.Stream(), torch.cuda.Stream()
+    filled = [torch.cuda.Event() for _ in range(2)]
+    consumed = [torch.cuda.Event() for _ in range(2)]
+    staged = [torch.cuda.Event() for _ in range(2)]
+    drained = [torch.cuda.Event() for _ in range(2)]
+
+    def e2e_steps(count, compute=True):
+        for i in range(count):
+            s = i % 2
+            with torch.cuda.stream(h2d_stream):
+                if i >= 2:
+                    h2d_stream.wait_event(consumed[s])      # step i - 2 no longer reads this set
+                for n in names:
+                    stack.input_sets[s][n].copy_(host_in[n], non_blocking=True)
+                stack.id_sets[s].copy_(host_ids, non_blocking=True)
+                filled[s].record(h2d_stream)
+            with torch.cuda.stream(stream_obj):
+                stream_obj.wait_event(filled[s])
+                if compute:
+                    if graphs[s] is not None:
+                        graphs[s].replay()
+                    else:
+                        stack.active = s
+                        stack.enqueue_step(stream)
+                        stack.active = 0
+                consumed[s].record(stream_obj)
+                if i >= 2:
+                    stream_obj.wait_event(drained[s])       # the host copy of step i - 2's result is done
+                staged_out[s].copy_(stack.residual[final_idx], non_blocking=True)
+                staged[s].record(stream_obj)
+            with torch.cuda.stream(d2h_stream):
+                d2h_stream.wait_event(staged[s])
+                host_out[s].copy_(staged_out[s], non_blocking=True)
+                drained[s].record(d2h_stream)
+
+    def timed(count, compute):
+        e2e_steps(2, compute)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(h2d_stream)
+        e2e_steps(count, compute)
+        d2h_stream.wait_stream(stream_obj)
+        d2h_stream.wait_stream(h2d_stream)
+        e1.record(d2h_stream)
+        barrier()
+        return max_over_ranks(e0.elapsed_time(e1)) / count
+
+    e2e_ms = timed(args.steps, True)
+    stack.check_error("end-to-end steps")
+    copy_ms = timed(max(2, min(args.steps, 5)), False)
+    out = {"value": total / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+           "ms_per_step": e2e_ms,
+           "copy_bound_tokens_per_s": total / (copy_ms * 1e-3), "copy_only_ms_per_step": copy_ms,
+           "frac_of_copy_bound": round(copy_ms / e2e_ms, 4),
+           "copy_GBs_per_gpu": round((h2d + d2h) / (copy_ms * 1e-3) / 1e9, 1),
+           "host_buffers": "cudaHostRegister" if all(registered) else "torch pinned allocator",
+           "note": "per step: pinned-host inputs -> device, 64-layer chain, final residual -> pinned host; the "
+                   "copies of neighbouring steps overlap the chain (two device input sets); copy_bound = the same "
+                   "loop with the kernels left out, all ranks copying at once (what this host's PCIe / memory "
+                   "delivers), bytes counted per rank"}
+    for t in list(host_in.values()) + [host_ids] + host_out:
+        try:
+            torch.cuda.cudart().cudaHostUnregister(t.data_ptr())
+        except Exception:
+            pass
+    return out
 
 
 def validate_shards(rank, world, dist):

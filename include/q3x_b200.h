@@ -21,6 +21,9 @@
  * Aliasing: an output may be EXACTLY an input where stated; every partial overlap is rejected.
  * Any alignment is accepted; 16-byte aligned pointers with widths that are multiples of 8
  * elements take the 128-bit fast paths, everything else a scalar path with identical results.
+ * Exceptions, which have 128-bit kernels only and return cudaErrorNotSupported for a pointer that is
+ * not 16-byte aligned: the causal conv, the full-attention pre-processing, and the operators fused
+ * with NVFP4 quantisation.
  */
 #ifndef Q3X_B200_H_
 #define Q3X_B200_H_
@@ -116,9 +119,14 @@ int q3x_b200_residual_add_rms_norm(const uint16_t* left, const uint16_t* right,
 /* Number of scale groups of a [rows, *] tensor. */
 size_t q3x_b200_nvfp4_group_count(size_t rows, size_t rows_per_scale);
 /* Size, in uint32 words, of the `scratch` argument of the entry points below (group amax words and
- * group arrival counters, plus an error word at the end).  The caller owns the memory; every call
- * clears what it uses, so stale contents do not matter.  Calls that share one scratch buffer must
- * not overlap on the GPU (same stream, or ordered by events). */
+ * group arrival counters, plus an error word at the end).  The caller owns the memory and ZEROES IT
+ * ONCE, when it is allocated (cudaMemsetAsync); every call leaves the words it used zero again, so one
+ * buffer serves any sequence of calls, of any shapes, with no clearing in between (the single-kernel
+ * forms put no memset node in front of their kernel).  Calls that share one scratch buffer must not
+ * overlap on the GPU (same stream, or ordered by events).
+ * The LAST word is a sticky error flag: the library only ever sets bits in it, and only when a bounded
+ * wait inside a single-kernel form gave up (the outputs of that call are then not valid and the scratch
+ * must be zeroed again).  Clear it once, run any number of calls, read it once. */
 size_t q3x_b200_nvfp4_scratch_words(size_t rows, size_t rows_per_scale);
 
 /* amax_bits[g] = largest finite |x| of group g as bf16 magnitude bits (uint32), group_count words.
@@ -143,8 +151,7 @@ int q3x_b200_nvfp4_quantize_dynamic(const uint16_t* in, size_t rows, size_t cols
  * bit); it may be exactly `right`.  One kernel that crosses HBM once where a scale group is short
  * enough to wait in L2 (see the _single_pass form), else two kernels: the norm, which also reduces
  * each group's amax, then the quantiser, which derives the scales from it.  Same bytes either way.
- * After the call the last scratch word is non-zero only if a bounded wait inside the single kernel
- * gave up (outputs then not valid). */
+ * codes, scales, global_scales_out and scratch must not overlap each other nor any other operand. */
 int q3x_b200_residual_add_rms_norm_nvfp4(const uint16_t* left, const uint16_t* right,
                                          const uint16_t* weight, size_t tokens, size_t hidden,
                                          float eps, size_t rows_per_scale, uint16_t* residual_out,
@@ -155,8 +162,7 @@ int q3x_b200_residual_add_rms_norm_nvfp4(const uint16_t* left, const uint16_t* r
  * normalising a row and quantising the row written `lag` rows earlier, which still sits in L2 and
  * whose scale group is complete by then.  Returns cudaErrorNotSupported, with nothing enqueued,
  * when a scale group is too long to stay in L2 (group rows x row bytes beyond a few tens of MB,
- * e.g. rows_per_scale == 0 on a long tensor).  After the call the last scratch word is non-zero
- * only if a bounded wait inside the kernel gave up (outputs then not valid). */
+ * e.g. rows_per_scale == 0 on a long tensor). */
 int q3x_b200_residual_add_rms_norm_nvfp4_single_pass(const uint16_t* left, const uint16_t* right,
                                                      const uint16_t* weight, size_t tokens,
                                                      size_t hidden, float eps, size_t rows_per_scale,
@@ -229,6 +235,13 @@ int q3x_b200_residual_add_rms_norm_nvfp4_static_scratch(
  * one value per output byte.  format 0 = E4M3 round-to-nearest-even with saturation at 448,
  * format 1 = E2M1 (code in the low nibble). */
 int q3x_b200_debug_encode(const float* in, size_t count, int format, uint8_t* out, void* stream);
+/* Diagnostics (no counterpart in the reference): the FP32 building blocks of the operators, out[i] =
+ * f(in[i]), so that their error against the host reference's libm expressions can be measured.
+ * function 0 = inverse RMS 1/sqrt(in/p0 + p1) (p0 = row width, p1 = epsilon), 1 = inverse L2 norm
+ * 1/sqrt(in + p1), 2 = silu, 3 = silu in the form the SwiGLU stream uses, 4 = branch-stable sigmoid,
+ * 5 = exp(-|in|). */
+int q3x_b200_debug_intermediate(const float* in, size_t count, int function, float p0, float p1,
+                                float* out, void* stream);
 /* Diagnostics: returns the CUDA last-error pending in this library's runtime without clearing it;
  * with plant != 0 first leaves a stale host-side argument error there (nothing reaches the GPU),
  * which the next entry point must clear before its own launch
@@ -290,7 +303,8 @@ int q3x_b200_fp32_to_bf16(const float* in, size_t count, uint16_t* out, void* st
  * (src/kernels/reference/gdn_prefill_whole_span_conv_sm87.h), for any token count:
  * out[t,c] = bf16(silu(fma chain over raw[t-3..t,c] and w[c,0..3])), history [channels,3]
  * (oldest first) supplies rows before t = 0 and receives the last three RAW rows.
- * channels must be 10240 and every pointer 16-byte aligned (else cudaErrorNotSupported).
+ * channels must be 10240 (else cudaErrorInvalidValue: it is the reference's only geometry) and every
+ * pointer 16-byte aligned (else cudaErrorNotSupported).
  * raw may be exactly out (serial path: one token run per channel block). */
 int q3x_b200_causal_conv1d_silu(const uint16_t* raw, size_t tokens, size_t channels,
                                 const uint16_t* conv_weight, uint16_t* history_in_out,

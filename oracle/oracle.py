@@ -40,14 +40,22 @@ _f32p = C.POINTER(C.c_float)
 _sz = C.c_size_t
 
 
+def reference_dir() -> str:
+    """Where a checkout of the reference project is looked for: ``$Q3X_REFERENCE_DIR``, else the
+    directory ``reference`` beside this repository (the Makefile's default)."""
+    return os.environ.get("Q3X_REFERENCE_DIR") or os.path.abspath(os.path.join(_HERE, "..", "..", "reference"))
+
+
 def build(force: bool = False) -> None:
     """Compile the restatement (and, where a reference checkout exists, ``_ref``)."""
     if force or not os.path.exists(_ORACLE_SO) or (
         os.path.getmtime(_ORACLE_SO) < os.path.getmtime(os.path.join(_HERE, "q3x_oracle.c"))
     ):
         subprocess.run(["make", "-C", _HERE, "oracle"], check=True, capture_output=True)
-    if os.path.isdir("/root/reference/src/runtime/reference") and (force or not os.path.exists(_REF_SO)):
-        subprocess.run(["make", "-C", _HERE, "ref"], check=True, capture_output=True)
+    shim = os.path.join(_HERE, "ref_shim.cpp")
+    if os.path.isdir(os.path.join(reference_dir(), "src", "runtime", "reference")) and (
+            force or not os.path.exists(_REF_SO) or os.path.getmtime(_REF_SO) < os.path.getmtime(shim)):
+        subprocess.run(["make", "-C", _HERE, "ref", f"REFERENCE={reference_dir()}"], check=True, capture_output=True)
 
 
 def _p(a, ty):
@@ -150,6 +158,13 @@ def ref_lib():
         L.unpack = L.fn("ref_unpack_e2m1_nibble", C.c_uint8, C.c_uint8, i)
         L.dequant = L.fn("ref_dequantize_nvfp4", i, _u8p, _u8p, f, _sz, _sz, _f32p)
         L.e4m3_value = L.fn("ref_e4m3_quantised_value", i, C.c_uint16, f, _f32p)
+        L.gdn_update = L.fn("ref_gated_delta_net_update", i, _u16p, _u16p, _u16p, _u16p, _u16p, _u16p, _u16p, f, _u16p)
+        L.softmax = L.fn("ref_softmax", i, _f32p, _sz, _sz, _f32p)
+        L.gqa = L.fn("ref_gqa_attention", i, _u16p, _u16p, _u16p, _sz, _sz, _sz, _sz, f, _f32p, _sz, _u16p)
+        L.embedding_rows = L.fn("ref_embedding_gather_rows", i, _u16p, _sz, _sz, _u32p, _sz, _u16p)
+        L.conv_rows = L.fn("ref_causal_conv1d_silu_update_rows", i, _u16p, _sz, _u16p, _u16p, _u16p)
+        L.preprocess_rows = L.fn("ref_full_attention_preprocess_rows", i, _u16p, _u16p, _u16p, _u16p, f, _u16p,
+                                 _u16p, _f32p, _f32p, _sz, _sz)
         _ref = L
     return _ref
 

@@ -93,4 +93,67 @@ int ref_e4m3_quantised_value(std::uint16_t activation_bf16, float input_scale, f
                                                                        &activation_bf16, 1U, 1U, out));
 }
 
+
+// ---- the GDN recurrence, GQA attention and softmax host ops ---------------------------------------
+int ref_gated_delta_net_update(const std::uint16_t* conv_qkv, const std::uint16_t* a, const std::uint16_t* b,
+                               const std::uint16_t* A_log, const std::uint16_t* dt_bias,
+                               const std::uint16_t* state_in, std::uint16_t* state_out, float l2_eps,
+                               std::uint16_t* out) {
+  return static_cast<int>(
+      rt::gated_delta_net_update_reference_cpu(conv_qkv, a, b, A_log, dt_bias, state_in, state_out, l2_eps, out));
+}
+int ref_softmax(const float* in, std::size_t rows, std::size_t cols, float* out) {
+  return static_cast<int>(rt::softmax_reference_cpu(in, rows, cols, out));
+}
+int ref_gqa_attention(const std::uint16_t* q, const std::uint16_t* k_cache, const std::uint16_t* v_cache,
+                      std::size_t q_heads, std::size_t kv_heads, std::size_t length, std::size_t dim, float scale,
+                      float* scratch, std::size_t scratch_elements, std::uint16_t* out) {
+  return static_cast<int>(rt::gqa_attention_reference_cpu(q, k_cache, v_cache, q_heads, kv_heads, length, dim, scale,
+                                                          scratch, scratch_elements, out));
+}
+
+// ---- per-token host ops applied to a run of token rows --------------------------------------------
+// The reference's host ops for the embedding, the conv, the q|gate split and the rotation take ONE token;
+// its runner loops over tokens around them.  These wrappers are that loop, in C++, so that a timing of
+// the host path spends its time in the reference's functions and not in the caller's per-token loop.
+int ref_embedding_gather_rows(const std::uint16_t* table, std::size_t vocab, std::size_t hidden,
+                              const std::uint32_t* ids, std::size_t tokens, std::uint16_t* out) {
+  for (std::size_t t = 0; t < tokens; ++t) {
+    const int st = static_cast<int>(rt::embedding_gather_reference_cpu(table, vocab, hidden, ids[t], out + t * hidden));
+    if (st != 0) return st;
+  }
+  return 0;
+}
+int ref_causal_conv1d_silu_update_rows(const std::uint16_t* raw, std::size_t tokens, const std::uint16_t* w,
+                                       std::uint16_t* history, std::uint16_t* out) {
+  for (std::size_t t = 0; t < tokens; ++t) {
+    const int st = static_cast<int>(rt::causal_conv1d_silu_update_reference_cpu(
+        raw + t * rt::kGdnQkvChannels, w, history, out + t * rt::kGdnQkvChannels));
+    if (st != 0) return st;
+  }
+  return 0;
+}
+// split + centred q/k head norm + partial RoPE of `tokens` rows starting at `first_position`: the
+// call sequence of the full-attention pre-processing, token by token.
+int ref_full_attention_preprocess_rows(const std::uint16_t* q_gate, std::uint16_t* key, const std::uint16_t* q_w,
+                                       const std::uint16_t* k_w, float eps, std::uint16_t* q_out,
+                                       std::uint16_t* gate_out, const float* cosines, const float* sines,
+                                       std::size_t first_position, std::size_t tokens) {
+  constexpr std::size_t Q = 24U, KV = 4U, D = 256U;
+  for (std::size_t t = 0; t < tokens; ++t) {
+    std::uint16_t* q = q_out + t * Q * D;
+    std::uint16_t* k = key + t * KV * D;
+    int st = static_cast<int>(rt::split_interleaved_q_gate_reference_cpu(q_gate + t * 2U * Q * D, Q, D, q,
+                                                                         gate_out + t * Q * D));
+    if (st == 0) st = static_cast<int>(rt::headwise_centered_rms_norm_reference_cpu(q, q_w, Q, D, eps, q));
+    if (st == 0) st = static_cast<int>(rt::headwise_centered_rms_norm_reference_cpu(k, k_w, KV, D, eps, k));
+    const float* c = cosines + (first_position + t) * 32U;
+    const float* s = sines + (first_position + t) * 32U;
+    if (st == 0) st = static_cast<int>(rt::partial_neox_rope_256_64_reference_cpu(q, c, s, Q, q));
+    if (st == 0) st = static_cast<int>(rt::partial_neox_rope_256_64_reference_cpu(k, c, s, KV, k));
+    if (st != 0) return st;
+  }
+  return 0;
+}
+
 }  // extern "C"

@@ -45,6 +45,7 @@ SIGNATURES = {
     "q3x_b200_static_scratch_max_tokens": (_z, []),
     "q3x_b200_residual_add_rms_norm_nvfp4_static_scratch": (_i, [_p, _p, _p, _z, _z, _f, _z, _p, _p, _p, _p, _p, _p]),
     "q3x_b200_debug_encode": (_i, [_p, _z, _i, _p, _p]),
+    "q3x_b200_debug_intermediate": (_i, [_p, _z, _i, _f, _f, _p, _p]),
     "q3x_b200_debug_stale_error": (_i, [_i]),
     "q3x_b200_split_interleaved_q_gate": (_i, [_p, _z, _z, _p, _p, _p]),
     "q3x_b200_partial_neox_rope_256_64": (_i, [_p, _p, _p, _z, _p, _p]),

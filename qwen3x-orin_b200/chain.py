@@ -137,6 +137,7 @@ class LayerStack:
         self.mlp_out = torch.empty((T, INTERMEDIATE), **bf)
         groups = max(1, math.ceil(T / CHUNK))
         self.groups = groups
+        # NVFP4 scratch: zeroed once here, left zero by every call; the last word is the sticky error flag
         self.amax = torch.zeros(capi.lib().q3x_b200_nvfp4_scratch_words(T, CHUNK), device=dev, dtype=torch.int32)
         self.global_scales = torch.empty(groups, device=dev, dtype=torch.float32)
         self.codes = torch.empty((T, HIDDEN // 2), device=dev, dtype=torch.uint8)
@@ -158,6 +159,16 @@ class LayerStack:
         self.input_sets.append({n: t.clone() for n, t in self.input_sets[0].items()})
         self.id_sets.append(self.id_sets[0].clone())
         return len(self.input_sets) - 1
+
+    def check_error(self, what: str = "the operator chain") -> None:
+        """Synchronises and raises when a bounded device-side wait of a single-kernel NVFP4 operator gave up
+        at any point since the scratch was allocated (the flag is sticky), or when a call left scratch words
+        behind; the outputs are not valid then."""
+        words = self.amax.cpu()
+        if int(words[-1]) != 0:
+            raise RuntimeError(f"{what}: a bounded device-side wait gave up (error word {int(words[-1]):#x})")
+        if bool(words[:-1].any()):
+            raise RuntimeError(f"{what}: NVFP4 scratch words were left non-zero")
 
     # ---- individual operators (each is one C-ABI call) ------------------------------------
     def op_embedding(self, stream):

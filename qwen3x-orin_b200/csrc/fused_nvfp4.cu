@@ -19,13 +19,18 @@
 // Progress: phase-A CTAs never wait, and the rows a phase-B CTA waits for belong to CTAs with a
 // smaller index, which the hardware has started earlier (CTAs of a 1-D grid start in index order).
 // Every wait is bounded all the same; a CTA that gives up sets the error word and carries on, so the
-// kernel always terminates and a missed dependency is reported, never silent.
+// kernel always terminates and a missed dependency is reported, never silent.  The error word is
+// STICKY: the library only ever ORs into it, so a caller clears it once, runs any number of calls and
+// reads it once.
 // No L2 eviction hints: marking the streamed operands evict-first (so that the normalised rows awaiting
 // phase B would be what stays cached) measured 2 - 5 % SLOWER than plain accesses; lag x row bytes is
 // small against the L2 as it is.
 //
-// Scratch words (uint32), cleared by the launcher: G group amax words, then G arrival counters (each
-// on an L2 line of its own when the scratch is large enough), last word = error flag.
+// Scratch words (uint32): G group amax words, then G arrival counters (each on an L2 line of its own
+// when the scratch is large enough), last word = error flag.  The words must be ZERO when a launch
+// starts and the launch leaves them zero again, so no memset node precedes the kernel: the phase-B CTAs
+// of a group count themselves into the group's arrival counter after they have read its amax, and the
+// one that brings the counter to twice the group's rows -- the last reader -- clears both words.
 #include "device_utils.cuh"
 #include "host_checks.hpp"
 #include "internal.hpp"
@@ -56,6 +61,13 @@ __device__ __forceinline__ uint32_t ld_relaxed(const uint32_t* p) {
   asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
+// counts the caller into *p and returns the previous value; orders the caller's earlier loads before the
+// addition and the addition before its later stores, at GPU scope
+__device__ __forceinline__ uint32_t add_acq_rel(uint32_t* p) {
+  uint32_t old;
+  asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(old) : "l"(p) : "memory");
+  return old;
+}
 
 struct Board {
   uint32_t* amax;     // group g at amax[g * stride]
@@ -72,6 +84,8 @@ struct QuantOut {
   uint8_t* scales;  // [rows, row_vectors / 2] bytes
   bool wide_scale_stores;
 };
+
+constexpr uint32_t kNoTicket = 0xffffffffu;
 
 struct TeamShared {
   float sums[kMaxWarps];
@@ -100,24 +114,46 @@ __device__ __forceinline__ void publish_row(const Board& board, TeamShared& ts, 
 
 // Phase B prologue: the amax bits of the group of `row`, once all of the group's rows have arrived.
 // One thread polls (a single request per CTA on the counter's L2 line); the barrier then orders its
-// acquire before every thread's loads of the row.
-__device__ __forceinline__ uint32_t await_group_amax(const Board& board, TeamShared& ts, size_t group) {
+// acquire before every thread's loads of the row.  Thread 0 also counts itself into the arrival counter
+// as a reader (after its load of the amax word); *ticket receives the counter's previous value, which
+// retire_group() looks at once the row is quantised -- the round trip of that atomic is hidden behind
+// the quantisation.  kNoTicket = the wait gave up (or not thread 0): nothing to retire.
+__device__ __forceinline__ uint32_t await_group_amax(const Board& board, TeamShared& ts, size_t group,
+                                                     uint32_t* ticket) {
+  *ticket = kNoTicket;
   if (threadIdx.x == 0) {
     const size_t first = group * board.group_rows;
     const uint32_t need = static_cast<uint32_t>(min(board.group_rows, board.rows - first));
     const size_t slot = group * board.stride;
     int polls = 0;
+    bool complete = true;
     while (ld_acquire(board.count + slot) < need) {
       if (++polls >= kSpinLimit) {
-        atomicExch(board.error, 1u);
+        atomicOr(board.error, 1u);
+        complete = false;
         break;
       }
       __nanosleep(200);
     }
     ts.group_amax = ld_relaxed(board.amax + slot);
+    if (complete) *ticket = add_acq_rel(board.count + slot);
   }
   __syncthreads();
   return ts.group_amax;
+}
+
+// Phase B epilogue (thread 0): the reader that finds the counter at 2 x rows - 1 is the group's last
+// one -- every other reader has loaded the amax word before its own addition -- and returns both words
+// to zero for the next launch that uses this scratch.
+__device__ __forceinline__ void retire_group(const Board& board, size_t group, uint32_t ticket) {
+  if (threadIdx.x != 0 || ticket == kNoTicket) return;
+  const size_t first = group * board.group_rows;
+  const uint32_t need = static_cast<uint32_t>(min(board.group_rows, board.rows - first));
+  if (ticket == 2u * need - 1u) {
+    const size_t slot = group * board.stride;
+    board.amax[slot] = 0u;
+    board.count[slot] = 0u;
+  }
 }
 
 // Quantises one normalised row (out of L2) under the global scale of `amax_bits`.  Thread tid owns
@@ -167,10 +203,12 @@ __device__ __forceinline__ void quantize_cached_row(const uint4* row_in, int row
                                                     TeamShared& ts, size_t row, uint32_t* codes_row,
                                                     uint8_t* scales_row, bool wide_scale_stores) {
   const size_t group = row / board.group_rows;
-  const uint32_t amax_bits = await_group_amax(board, ts, group);
+  uint32_t ticket;
+  const uint32_t amax_bits = await_group_amax(board, ts, group, &ticket);
   if (threadIdx.x == 0 && row == group * board.group_rows)
     board.global_out[group] = global_scale_from_amax_bits(amax_bits);
   quantize_row<TEAM, VPT, FAST>(row_in, row_vectors, amax_bits, ts, codes_row, scales_row, wide_scale_stores);
+  retire_group(board, group, ticket);
 }
 
 // Phase B of either kernel: CTA 2k + 1 quantises row k - lag of `normalized`.
@@ -318,8 +356,8 @@ __global__ void __launch_bounds__(TEAM, min_ctas_per_sm(TEAM, VPT)) gated_norm_n
 
 // ---- a handful of rows (decode) ------------------------------------------------------------------
 // Up to kSmallRows rows: one CTA per scale group walks its rows twice -- normalise them all, reduce the
-// group amax inside the CTA, quantise them all -- so nothing crosses CTAs: no counters, no waits and no
-// scratch to clear (one launch, no memset before it).  CTA 0 clears the error word the callers inspect.
+// group amax inside the CTA, quantise them all -- so nothing crosses CTAs: no counters, no waits, and
+// the scratch is not touched at all.
 // Measured per call inside a CUDA graph: 4.3 us against 8.2 us for one row; from four rows on the rows'
 // serial walk costs more than the cleared scratch, so the limit is two.
 constexpr size_t kSmallRows = 2;
@@ -340,12 +378,10 @@ __global__ void __launch_bounds__(TEAM) small_norm_nvfp4_kernel(const uint4* a, 
                                                                  const uint4* __restrict__ weight, int row_vectors,
                                                                  float width, float eps, uint4* residual_out,
                                                                  uint4* out, bool coherent, size_t rows,
-                                                                 size_t group_rows, float* global_out, uint32_t* error,
-                                                                 QuantOut q) {
+                                                                 size_t group_rows, float* global_out, QuantOut q) {
   __shared__ TeamShared ts;
   const size_t first = blockIdx.x * group_rows;
   const size_t last = min(rows, first + group_rows);
-  if (blockIdx.x == 0 && threadIdx.x == 0) *error = 0u;
   float top = 0.0f;
   for (size_t row = first; row < last; ++row) {
     const float t = GATED ? gated_norm_row<TEAM, VPT, false>(a, b, weight, row, row_vectors, eps, out, coherent)
@@ -481,11 +517,10 @@ bool launch_residual_norm_nvfp4_fused(const uint16_t* left, const uint16_t* righ
   auto NO = reinterpret_cast<uint4*>(normalized_out);
   unsigned lag = 0, grid = 0;
   if (tokens <= kSmallRows) {
-    uint32_t* error = scratch + words - 1;
 #define Q3X_SHAPE(TEAM, V)                                                                                      \
   if (row_vectors <= TEAM * V) {                                                                                \
     small_norm_nvfp4_kernel<TEAM, V, false><<<static_cast<unsigned>(groups), TEAM, 0, s>>>(                     \
-        L, R, W, row_vectors, width, eps, RO, NO, coherent, tokens, rps, global_scales_out, error, q);          \
+        L, R, W, row_vectors, width, eps, RO, NO, coherent, tokens, rps, global_scales_out, q);                 \
     return true;                                                                                                \
   }
     Q3X_FUSED_SHAPES
@@ -496,7 +531,6 @@ bool launch_residual_norm_nvfp4_fused(const uint16_t* left, const uint16_t* righ
   if (row_vectors <= TEAM * V) {                                                                                \
     if (!plan_launch(residual_norm_nvfp4_kernel<TEAM, V, true>, TEAM, tokens, rps, hidden * 2, &lag, &grid))          \
       return false;                                                                                             \
-    cudaMemsetAsync(scratch, 0, words * sizeof(uint32_t), s);                                                   \
     const Board board = make_board(scratch, words, groups, global_scales_out, tokens, rps, lag);                \
     if (row_vectors == TEAM * V && !coherent && q.wide_scale_stores)                                            \
       residual_norm_nvfp4_kernel<TEAM, V, true><<<grid, TEAM, 0, s>>>(L, R, W, row_vectors, width, eps, RO, NO, \
@@ -534,11 +568,10 @@ bool launch_gated_norm_nvfp4_fused(const uint16_t* in, const uint16_t* weight, c
   auto O = reinterpret_cast<uint4*>(out);
   unsigned lag = 0, grid = 0;
   if (tokens <= kSmallRows) {
-    uint32_t* error = scratch + words - 1;
 #define Q3X_SHAPE(TEAM, V)                                                                                      \
   if (row_vectors <= TEAM * V) {                                                                                \
     small_norm_nvfp4_kernel<TEAM, V, true><<<static_cast<unsigned>(groups), TEAM, 0, s>>>(                      \
-        X, Z, W, row_vectors, 128.0f, eps, nullptr, O, coherent, tokens, rps, global_scales_out, error, q);     \
+        X, Z, W, row_vectors, 128.0f, eps, nullptr, O, coherent, tokens, rps, global_scales_out, q);            \
     return true;                                                                                                \
   }
     Q3X_FUSED_SHAPES
@@ -549,7 +582,6 @@ bool launch_gated_norm_nvfp4_fused(const uint16_t* in, const uint16_t* weight, c
   if (row_vectors <= TEAM * V) {                                                                                \
     if (!plan_launch(gated_norm_nvfp4_kernel<TEAM, V, true>, TEAM, tokens, rps, cols * 2, &lag, &grid))         \
       return false;                                                                                             \
-    cudaMemsetAsync(scratch, 0, words * sizeof(uint32_t), s);                                                   \
     const Board board = make_board(scratch, words, groups, global_scales_out, tokens, rps, lag);                \
     if (row_vectors == TEAM * V && !coherent && q.wide_scale_stores)                                            \
       gated_norm_nvfp4_kernel<TEAM, V, true><<<grid, TEAM, 0, s>>>(X, Z, W, row_vectors, eps, O, coherent,      \
@@ -593,7 +625,6 @@ bool launch_pointwise_nvfp4(const uint16_t* gate, const uint16_t* up, size_t tok
   unsigned lag = 0, grid = 0;
   if (!plan_launch(pointwise_nvfp4_kernel<Op, kTeam, kVpt, true>, kTeam, chunks, chunks_per_group, kChunk * 16, &lag, &grid))
     return false;
-  cudaMemsetAsync(scratch, 0, words * sizeof(uint32_t), s);
   const Board board = make_board(scratch, words, groups, global_scales_out, chunks, chunks_per_group, lag);
   auto G = reinterpret_cast<const uint4*>(gate);
   auto U = reinterpret_cast<const uint4*>(up);

@@ -56,20 +56,25 @@ constexpr int kInvalid = static_cast<int>(cudaErrorInvalidValue);
 constexpr int kNotSupported = static_cast<int>(cudaErrorNotSupported);
 constexpr int kOk = static_cast<int>(cudaSuccess);
 
-// Grid sizing: enough CTAs to fill the machine a few times over without exceeding what the work
-// needs.  148 SMs on B200; the multiplier is the number of resident CTAs per SM we aim for.
-inline unsigned grid_for(size_t work_items, unsigned items_per_cta, unsigned ctas_per_sm_target) {
-  static int sm_count = 0;
-  if (sm_count == 0) {
-    int dev = 0, n = 0;
-    if (cudaGetDevice(&dev) == cudaSuccess &&
-        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0)
-      sm_count = n;
-    else
-      sm_count = 148;
+// SM count of the current device (cached per device ordinal; 148 on B200).
+inline int current_device_sm_count() {
+  constexpr int kMaxDevices = 64;
+  static std::atomic<int> cache[kMaxDevices] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 148;
+  int n = cache[dev].load(std::memory_order_relaxed);
+  if (n == 0) {
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cache[dev].store(n, std::memory_order_relaxed);
   }
+  return n;
+}
+
+// Grid sizing: enough CTAs to fill the machine a few times over without exceeding what the work
+// needs.  The multiplier is the number of resident CTAs per SM we aim for.
+inline unsigned grid_for(size_t work_items, unsigned items_per_cta, unsigned ctas_per_sm_target) {
   const size_t needed = (work_items + items_per_cta - 1) / items_per_cta;
-  const size_t cap = static_cast<size_t>(sm_count) * ctas_per_sm_target;
+  const size_t cap = static_cast<size_t>(current_device_sm_count()) * ctas_per_sm_target;
   const size_t g = needed < cap ? needed : cap;
   return static_cast<unsigned>(g == 0 ? 1 : g);
 }
@@ -77,34 +82,35 @@ inline unsigned grid_for(size_t work_items, unsigned items_per_cta, unsigned cta
 // CTAs of `kernel` (with `threads` threads and `smem` dynamic bytes) that are resident at once on the
 // current device: occupancy per SM x SM count.  A grid-stride kernel launched with exactly this many
 // CTAs runs as one full wave; a larger grid would leave a partial last wave that idles most SMs.
-// The answer is cached per kernel (a few dozen entries; lock-free reads).
+// The answer is cached per (kernel, device) pair (a few dozen entries; lock-free reads).
 template <typename Kernel>
 inline unsigned resident_grid(Kernel kernel, int threads, size_t smem = 0) {
   struct Entry {
     const void* key;
+    int device;
     unsigned value;
   };
-  constexpr int kSlots = 128;
+  constexpr int kSlots = 512;
   static Entry table[kSlots] = {};
   static std::atomic<int> used{0};
   const void* key = reinterpret_cast<const void*>(kernel);
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) dev = 0;
   const int n = used.load(std::memory_order_acquire);
   for (int i = 0; i < n; ++i)
-    if (table[i].key == key) return table[i].value;
-  int dev = 0, sms = 0, per_sm = 0;
-  unsigned value = 148u * 4u;
-  if (cudaGetDevice(&dev) == cudaSuccess &&
-      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess &&
-      cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, smem) == cudaSuccess && sms > 0 &&
-      per_sm > 0)
+    if (table[i].key == key && table[i].device == dev) return table[i].value;
+  int per_sm = 0;
+  const int sms = current_device_sm_count();
+  unsigned value = static_cast<unsigned>(sms) * 4u;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, smem) == cudaSuccess && per_sm > 0)
     value = static_cast<unsigned>(sms) * static_cast<unsigned>(per_sm);
   static std::mutex mu;
   std::lock_guard<std::mutex> lock(mu);
   const int m = used.load(std::memory_order_relaxed);
   for (int i = 0; i < m; ++i)
-    if (table[i].key == key) return table[i].value;
+    if (table[i].key == key && table[i].device == dev) return table[i].value;
   if (m < kSlots) {
-    table[m] = Entry{key, value};
+    table[m] = Entry{key, dev, value};
     used.store(m + 1, std::memory_order_release);
   }
   return value;

@@ -262,6 +262,40 @@ void enqueue_quantize(const uint16_t* in, size_t rows, size_t cols, size_t rows_
   }
 }
 
+// Clears the scratch words of a call, the sticky error word (the last one) excepted.  The multi-kernel
+// paths clear before their first kernel (their amax words are raised with atomicMax) and again after their
+// last one, so that every entry point leaves the scratch zero, which is what the single-kernel forms
+// expect to find.
+void clear_board(uint32_t* scratch, size_t rows, size_t groups, cudaStream_t s) {
+  cudaMemsetAsync(scratch, 0, (fused_scratch_words(rows, groups) - 1) * sizeof(uint32_t), s);
+}
+
+// Every operand of an NVFP4 entry point besides the tensor being quantised: the three byte outputs and the
+// scratch must not overlap each other nor any of `others` (inputs, weights and bf16 outputs).
+struct QuantSpans {
+  host::Span codes, scales, globals, scratch;
+};
+QuantSpans quant_spans(size_t rows, size_t cols, size_t groups, const void* codes, const void* scales,
+                       const void* global_scales_out, const void* scratch) {
+  using namespace host;
+  return QuantSpans{span(codes, rows * cols / 2), span(scales, rows * cols / 16),
+                    span(global_scales_out, groups * sizeof(float)),
+                    span(scratch, scratch ? fused_scratch_words(rows, groups) * sizeof(uint32_t) : 0)};
+}
+template <size_t N>
+bool quant_spans_collide(const QuantSpans& q, const host::Span (&others)[N]) {
+  using namespace host;
+  const Span mine[4] = {q.codes, q.scales, q.globals, q.scratch};
+  for (int i = 0; i < 4; ++i) {
+    if (wraps(mine[i])) return true;
+    for (int j = i + 1; j < 4; ++j)
+      if (overlap(mine[i], mine[j])) return true;
+    for (size_t k = 0; k < N; ++k)
+      if (overlap(mine[i], others[k])) return true;
+  }
+  return false;
+}
+
 int check_quant_outputs(const uint16_t* in, size_t rows, size_t cols, const void* codes, const void* scales) {
   using namespace host;
   if (codes == nullptr || scales == nullptr) return kInvalid;
@@ -327,11 +361,16 @@ extern "C" int q3x_b200_nvfp4_quantize_dynamic(const uint16_t* in, size_t rows, 
   if (scratch == nullptr || global_scales_out == nullptr) return kInvalid;
   if ((st = check_quant_outputs(in, rows, cols, codes, scales)) != kOk) return st;
   const size_t groups = group_count(rows, rows_per_scale);
+  {
+    const Span others[] = {span(in, rows * cols * 2)};
+    if (quant_spans_collide(quant_spans(rows, cols, groups, codes, scales, global_scales_out, scratch), others))
+      return kInvalid;
+  }
   cudaStream_t s = as_stream(stream);
   clear_stale_error();
-  (void)groups;
   enqueue_amax(in, rows, cols, rows_per_scale, scratch, s);
   enqueue_quantize(in, rows, cols, rows_per_scale, nullptr, scratch, global_scales_out, codes, scales, s);
+  clear_board(scratch, rows, groups, s);
   return launch_status();
 }
 
@@ -343,20 +382,37 @@ enum class Path { kAuto, kSingleKernel, kTwoKernels };
 
 // Shared body of the residual + norm + NVFP4 entry points.  kAuto takes the single kernel where it
 // applies and the two kernels otherwise; kSingleKernel refuses instead of falling back.
+// `late_scratch`, when given, supplies the scratch after every argument check has passed (and is not
+// called at all for a rejected or empty call); `scratch` is ignored then.
+using ScratchProvider = uint32_t* (*)(int* status);
 int residual_norm_nvfp4(const uint16_t* left, const uint16_t* right, const uint16_t* weight, size_t tokens,
                         size_t hidden, float eps, size_t rows_per_scale, uint16_t* residual_out,
                         uint16_t* normalized_out, uint32_t* scratch, float* global_scales_out, uint8_t* codes,
-                        uint8_t* scales, void* stream, Path path) {
+                        uint8_t* scales, void* stream, Path path, ScratchProvider late_scratch = nullptr) {
   bool done;
   int st = check_residual_norm(left, right, weight, tokens, hidden, eps, residual_out, normalized_out, &done);
   if (st != kOk) return st;
   if (hidden % Q3X_B200_NVFP4_BLOCK != 0) return kInvalid;
   if (done) return kOk;
-  if (normalized_out == nullptr || scratch == nullptr || global_scales_out == nullptr) return kInvalid;
+  if (late_scratch != nullptr) scratch = nullptr;
+  if (normalized_out == nullptr || (scratch == nullptr && late_scratch == nullptr) || global_scales_out == nullptr)
+    return kInvalid;
   if ((st = check_quant_outputs(normalized_out, tokens, hidden, codes, scales)) != kOk) return st;
+  const size_t groups = group_count(tokens, rows_per_scale);
+  {
+    const size_t bytes = tokens * hidden * 2;
+    const Span others[] = {span(left, bytes), span(right, bytes), span(weight, hidden * 2), span(residual_out, bytes),
+                           span(normalized_out, bytes)};
+    if (quant_spans_collide(quant_spans(tokens, hidden, groups, codes, scales, global_scales_out, scratch), others))
+      return kInvalid;
+  }
   if (!norm_rows_vector_path(left, right, weight, nullptr, hidden, residual_out, normalized_out, NormMode::kCentered))
     return kNotSupported;
-  const size_t groups = group_count(tokens, rows_per_scale);
+  if (late_scratch != nullptr) {
+    int status = kOk;
+    scratch = late_scratch(&status);
+    if (scratch == nullptr) return status;
+  }
   cudaStream_t s = as_stream(stream);
   clear_stale_error();
   if (path != Path::kTwoKernels) {
@@ -365,12 +421,13 @@ int residual_norm_nvfp4(const uint16_t* left, const uint16_t* right, const uint1
       return launch_status();
     if (path == Path::kSingleKernel) return kNotSupported;
   }
-  cudaMemsetAsync(scratch, 0, fused_scratch_words(tokens, groups) * sizeof(uint32_t), s);
+  clear_board(scratch, tokens, groups, s);
   launch_norm_rows(NormMode::kCentered, left, right, weight, nullptr, tokens, hidden, eps, 1.0f, residual_out,
                    normalized_out, /*coherent=*/normalized_out == right, scratch,
                    rows_per_scale ? rows_per_scale : tokens, s);
   enqueue_quantize(normalized_out, tokens, hidden, rows_per_scale, nullptr, scratch, global_scales_out, codes, scales,
                    s);
+  clear_board(scratch, tokens, groups, s);
   return launch_status();
 }
 
@@ -392,10 +449,15 @@ int gated_norm_nvfp4(const uint16_t* in, const uint16_t* weight, const uint16_t*
     return kInvalid;
   int st = check_quant_outputs(out, tokens, cols, codes, scales);
   if (st != kOk) return st;
+  const size_t groups = group_count(tokens, rows_per_scale);
+  {
+    const Span others[] = {si, sg, so, sw};
+    if (quant_spans_collide(quant_spans(tokens, cols, groups, codes, scales, global_scales_out, scratch), others))
+      return kInvalid;
+  }
   if (!norm_rows_vector_path(in, nullptr, weight, gate, dim, nullptr, out, NormMode::kPlainSiluGate) ||
       !(dim == 64 || dim == 128 || dim == 256))
     return kNotSupported;
-  const size_t groups = group_count(tokens, rows_per_scale);
   const size_t token_group = rows_per_scale ? rows_per_scale : tokens;
   cudaStream_t s = as_stream(stream);
   clear_stale_error();
@@ -405,10 +467,11 @@ int gated_norm_nvfp4(const uint16_t* in, const uint16_t* weight, const uint16_t*
       return launch_status();
     if (path == Path::kSingleKernel) return kNotSupported;
   }
-  cudaMemsetAsync(scratch, 0, fused_scratch_words(tokens, groups) * sizeof(uint32_t), s);
+  clear_board(scratch, tokens, groups, s);
   launch_norm_rows(NormMode::kPlainSiluGate, in, nullptr, weight, gate, tokens * heads_per_row, dim, eps, 1.0f,
                    nullptr, out, /*coherent=*/out == in || out == gate, scratch, token_group * heads_per_row, s);
   enqueue_quantize(out, tokens, cols, rows_per_scale, nullptr, scratch, global_scales_out, codes, scales, s);
+  clear_board(scratch, tokens, groups, s);
   return launch_status();
 }
 
@@ -452,9 +515,12 @@ int pointwise_nvfp4(bool swiglu, const uint16_t* first, const uint16_t* second, 
   if (wraps(sa) || wraps(sb) || wraps(so) || partial_overlap(so, sa) || partial_overlap(so, sb)) return kInvalid;
   int st = check_quant_outputs(out, tokens, width, codes, scales);
   if (st != kOk) return st;
-  if (overlap(sa, span(codes, bytes / 4)) || overlap(sb, span(codes, bytes / 4)) ||
-      overlap(sa, span(scales, bytes / 32)) || overlap(sb, span(scales, bytes / 32)))
-    return kInvalid;
+  const size_t groups = group_count(tokens, rows_per_scale);
+  {
+    const Span others[] = {sa, sb, so};
+    if (quant_spans_collide(quant_spans(tokens, width, groups, codes, scales, global_scales_out, scratch), others))
+      return kInvalid;
+  }
   cudaStream_t s = as_stream(stream);
   clear_stale_error();
   const bool fused = swiglu ? launch_silu_mul_nvfp4_fused(first, second, tokens, width, rows_per_scale, out, scratch,
@@ -466,9 +532,10 @@ int pointwise_nvfp4(bool swiglu, const uint16_t* first, const uint16_t* second, 
   st = swiglu ? q3x_b200_silu_mul(first, second, tokens * width, out, stream)
               : q3x_b200_sigmoid_gate(first, second, tokens * width, out, stream);
   if (st != kOk) return st;
-  cudaMemsetAsync(scratch, 0, fused_scratch_words(tokens, group_count(tokens, rows_per_scale)) * sizeof(uint32_t), s);
+  clear_board(scratch, tokens, groups, s);
   enqueue_amax(out, tokens, width, rows_per_scale, scratch, s);
   enqueue_quantize(out, tokens, width, rows_per_scale, nullptr, scratch, global_scales_out, codes, scales, s);
+  clear_board(scratch, tokens, groups, s);
   return launch_status();
 }
 
@@ -561,12 +628,12 @@ extern "C" int q3x_b200_residual_add_rms_norm_nvfp4_static_scratch(
   // more rows than the built-in scratch has words for: refuse before touching anything
   if (tokens > kStaticScratchMaxTokens) return kInvalid;
   if (fused_scratch_words(tokens, group_count(tokens, rows_per_scale)) > kStaticScratchWords) return kInvalid;
-  int status = kOk;
-  uint32_t* scratch = static_scratch_address(&status);
-  if (scratch == nullptr) return status;
-  // from here on this is the regular two-kernel path; it clears the scratch words it uses itself
+  // From here on this is the regular two-kernel path; it clears the scratch words it uses itself.  The
+  // array's address is only looked up once every argument check has passed, so a rejected or empty call
+  // touches no CUDA state.
   return residual_norm_nvfp4(left, right, weight, tokens, hidden, eps, rows_per_scale, residual_out, normalized_out,
-                             scratch, global_scales_out, codes, scales, stream, Path::kTwoKernels);
+                             nullptr, global_scales_out, codes, scales, stream, Path::kTwoKernels,
+                             &static_scratch_address);
 }
 
 // Diagnostics: the two narrow conversions on their own, so that tests can sweep them against the

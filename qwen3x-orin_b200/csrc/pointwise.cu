@@ -8,6 +8,7 @@
 // that are not 16-byte aligned, go through a scalar kernel computing the same values.
 #include "device_utils.cuh"
 #include "host_checks.hpp"
+#include "norm_math.cuh"
 #include "pointwise_ops.cuh"
 #include "q3x_b200.h"
 
@@ -26,11 +27,12 @@ __device__ __forceinline__ uint4 apply8(const uint4& a, const uint4& b) {
   return o;
 }
 
-// kInPlace: the output is exactly one of the inputs, so loads must be coherent ones.
+// kInPlace: the output is exactly one of the inputs, so loads must be coherent ones and the input
+// pointers carry no __restrict__ (the out-of-place instantiation reads through ld.global.nc explicitly,
+// so it loses nothing by that).
 template <class Op, bool kInPlace>
-__global__ void __launch_bounds__(kThreads) binary_vec_kernel(const uint4* __restrict__ a,
-                                                              const uint4* __restrict__ b,
-                                                              uint4* out, size_t nvec) {
+__global__ void __launch_bounds__(kThreads) binary_vec_kernel(const uint4* a, const uint4* b, uint4* out,
+                                                              size_t nvec) {
   constexpr int kDepth = Op::kDepth;
   auto store = [](uint4* p, const uint4& v) {
     if (Op::kStreamingStore) st_stream(p, v);
@@ -106,6 +108,25 @@ __global__ void __launch_bounds__(kThreads) fp32_to_bf16_kernel(const float* __r
   const size_t stride = static_cast<size_t>(gridDim.x) * kThreads;
   for (size_t i = static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x; i < count; i += stride)
     out[i] = float_to_bf16_exact(in[i]);
+}
+
+// Diagnostics: the FP32 building blocks of the operators, one value in, one value out, so that tests can
+// bound their error against the host reference's libm forms.
+__global__ void __launch_bounds__(kThreads) debug_intermediate_kernel(const float* in, size_t count, int function,
+                                                                      float p0, float p1, float* out) {
+  const size_t i = static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x;
+  if (i >= count) return;
+  const float x = in[i];
+  float y;
+  switch (function) {
+    case 0: y = inverse_rms(x, 1.0f / p0, p1); break;
+    case 1: y = inverse_l2(x, p1); break;
+    case 2: y = silu(x); break;
+    case 3: y = silu_unscaled(x); break;
+    case 4: y = stable_sigmoid(x); break;
+    default: y = exp_neg_abs(x); break;
+  }
+  out[i] = y;
 }
 
 // q|gate de-interleave: in [heads, 2, dim] -> q [heads, dim], gate [heads, dim]; raw bits.
@@ -231,5 +252,17 @@ extern "C" int q3x_b200_split_interleaved_q_gate(const uint16_t* in, size_t head
     const size_t total = heads * dim;
     split_q_gate_kernel<uint16_t><<<grid_for(total, kThreads, 8), kThreads, 0, s>>>(in, q_out, gate_out, total, dim);
   }
+  return launch_status();
+}
+
+extern "C" int q3x_b200_debug_intermediate(const float* in, size_t count, int function, float p0, float p1,
+                                           float* out, void* stream) {
+  if (count == 0) return kOk;
+  if (in == nullptr || out == nullptr || function < 0 || function > 5 || mul_overflows(count, sizeof(float)))
+    return kInvalid;
+  if (function == 0 && !(p0 > 0.0f)) return kInvalid;
+  clear_stale_error();
+  debug_intermediate_kernel<<<static_cast<unsigned>((count + kThreads - 1) / kThreads), kThreads, 0,
+                              as_stream(stream)>>>(in, count, function, p0, p1, out);
   return launch_status();
 }

@@ -105,6 +105,8 @@ def validate_sharded_chain(rank: int, world: int, tokens_per_rank: int = 1024, l
     final_whole = whole.residual[whole.enqueue_step(stream)]
     final_local = local.residual[local.enqueue_step(stream)]
     torch.cuda.synchronize()
+    whole.check_error("unsharded validation run")
+    local.check_error("sharded validation run")
 
     def same(a, b):
         return bool(torch.equal(a.contiguous().view(torch.uint8), b.contiguous().view(torch.uint8)))

@@ -67,11 +67,18 @@ def empty_like_dev(shape, dtype=np.uint16, misalign=0, fill=None):
     return Dev(a, misalign)
 
 
-def scratch_for(rows, rows_per_scale, fill=0x7FFFFFFF):
-    """The caller-owned scratch of the NVFP4 entry points, pre-filled with garbage: stale contents
-    must not matter."""
+def scratch_for(rows, rows_per_scale, fill=0):
+    """The caller-owned scratch of the NVFP4 entry points, zeroed once as the contract asks (every call
+    leaves it zero again; the last word is the sticky error flag)."""
     words = capi.lib().q3x_b200_nvfp4_scratch_words(rows, rows_per_scale)
-    return empty_like_dev((words,), dtype=np.uint32, fill=fill)
+    return empty_like_dev((words,), dtype=np.uint32, fill=0)
+
+
+def assert_scratch_clean(scratch, what=""):
+    """After any NVFP4 call: every scratch word is zero again and no bounded wait gave up."""
+    words = scratch.get()
+    assert words[-1] == 0, f"{what}: a bounded device-side wait gave up (error word {words[-1]:#x})"
+    assert not words.any(), f"{what}: the call left {int(np.count_nonzero(words))} scratch words non-zero"
 
 
 def sync():
@@ -92,6 +99,24 @@ def assert_bf16_within(got, want, max_ulp=1, min_exact=0.0, what=""):
     assert worst <= max_ulp, f"{what}: max distance {worst} ulp (allowed {max_ulp}), exact fraction {exact:.6f}"
     assert exact >= min_exact, f"{what}: only {exact:.6f} of the elements are bit-exact"
     return worst, exact
+
+
+def assert_reference_tolerance(got, want, what=""):
+    """The reference's own acceptance rule for a bf16 result (expect_bf16_match,
+    tests/decode_ops_cuda_test.cu:432-450): NaN matches NaN, an infinity matches the same infinity, every
+    other value within max(2e-3, 8e-3 * |expected|).  Applied as a hard bound on the chains of two
+    roundings, where the 1-ulp bound only holds stage by stage."""
+    a = orc.bf16_decode(np.asarray(got)).astype(np.float64).reshape(-1)
+    e = orc.bf16_decode(np.asarray(want)).astype(np.float64).reshape(-1)
+    nan_e, inf_e = np.isnan(e), np.isinf(e)
+    assert np.array_equal(np.isnan(a), nan_e), f"{what}: NaN classification differs"
+    assert np.array_equal(a[inf_e], e[inf_e]), f"{what}: infinity classification differs"
+    fin = ~(nan_e | inf_e)
+    tol = np.maximum(2.0e-3, np.abs(e[fin]) * 8.0e-3)
+    err = np.abs(a[fin] - e[fin])
+    bad = np.nonzero(err > tol)[0]
+    assert bad.size == 0, (f"{what}: {bad.size} elements beyond max(2e-3, 8e-3|e|); worst {err[bad].max():.3e} "
+                           f"at expected {e[fin][bad[np.argmax(err[bad])]]:.6g}")
 
 
 def assert_bits_equal(got, want, what=""):

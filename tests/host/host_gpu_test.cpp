@@ -1,0 +1,287 @@
+// Drives the C++ mirror of the reference operator API (libq3x_b200_host.so) ON A GPU: one launcher of
+// every family is called through its q3x::runtime name with real device buffers, and its output bytes
+// are compared with the same operation requested straight from the C ABI (libq3x_b200.so), whose
+// parity with the CPU oracle the Python tests establish.  A wrong argument order or a dropped argument
+// in the mirror's forwarding code shows up here as a byte mismatch.
+//
+// Plain executable in the style of the reference's own tests: prints failures, returns their count;
+// exit code 77 = no sm_100 device (skipped).
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <vector>
+
+#include "q3x_b200.h"
+#include "q3x_b200_nvfp4.hpp"
+#include "q3x_b200_ops.hpp"
+
+namespace rt = q3x::runtime;
+
+static int failures = 0;
+#define EXPECT(cond)                                              \
+  do {                                                            \
+    if (!(cond)) {                                                \
+      ++failures;                                                 \
+      std::printf("FAIL %s:%d: %s\n", __FILE__, __LINE__, #cond); \
+    }                                                             \
+  } while (0)
+#define CUDA_OK(call) EXPECT((call) == cudaSuccess)
+
+// deterministic pseudo-random bf16 bits: N(0,1)-like magnitudes, both signs, no specials
+static std::uint16_t bf16_of(float v) {
+  std::uint32_t u;
+  std::memcpy(&u, &v, 4);
+  u += 0x7fffu + ((u >> 16) & 1u);
+  return static_cast<std::uint16_t>(u >> 16);
+}
+static std::uint32_t lcg_state = 12345u;
+static float uniform() {
+  lcg_state = lcg_state * 1664525u + 1013904223u;
+  return static_cast<float>(lcg_state >> 8) / 16777216.0f;
+}
+static std::vector<std::uint16_t> random_bf16(std::size_t n, float scale) {
+  std::vector<std::uint16_t> v(n);
+  for (auto& x : v) x = bf16_of((uniform() + uniform() + uniform() - 1.5f) * 2.0f * scale);
+  return v;
+}
+
+template <typename T>
+struct DeviceBuffer {
+  T* p = nullptr;
+  std::size_t n = 0;
+  explicit DeviceBuffer(std::size_t count, int fill = 0x5a) : n(count) {
+    CUDA_OK(cudaMalloc(&p, count * sizeof(T)));
+    CUDA_OK(cudaMemset(p, fill, count * sizeof(T)));
+  }
+  explicit DeviceBuffer(const std::vector<T>& host) : n(host.size()) {
+    CUDA_OK(cudaMalloc(&p, n * sizeof(T)));
+    CUDA_OK(cudaMemcpy(p, host.data(), n * sizeof(T), cudaMemcpyHostToDevice));
+  }
+  ~DeviceBuffer() { cudaFree(p); }
+  DeviceBuffer(const DeviceBuffer&) = delete;
+  DeviceBuffer& operator=(const DeviceBuffer&) = delete;
+  std::vector<T> get() const {
+    std::vector<T> h(n);
+    CUDA_OK(cudaMemcpy(h.data(), p, n * sizeof(T), cudaMemcpyDeviceToHost));
+    return h;
+  }
+};
+using Bf16 = DeviceBuffer<std::uint16_t>;
+
+template <typename T>
+static bool same(const DeviceBuffer<T>& a, const DeviceBuffer<T>& b) {
+  CUDA_OK(cudaDeviceSynchronize());
+  const auto x = a.get(), y = b.get();
+  return x.size() == y.size() && std::memcmp(x.data(), y.data(), x.size() * sizeof(T)) == 0;
+}
+// not everything still the fill pattern: the launcher really wrote
+template <typename T>
+static bool written(const DeviceBuffer<T>& a) {
+  const auto x = a.get();
+  std::size_t untouched = 0;
+  for (const T& v : x) {
+    T fill;
+    std::memset(&fill, 0x5a, sizeof(T));
+    untouched += std::memcmp(&v, &fill, sizeof(T)) == 0 ? 1 : 0;
+  }
+  return untouched * 10 < x.size();
+}
+
+static void test_pointwise_and_embedding(cudaStream_t s) {
+  const std::size_t n = 3 * 17408 + 5;  // not a multiple of eight: vector body and scalar tail
+  Bf16 gate(random_bf16(n, 2.0f)), up(random_bf16(n, 1.0f)), a(n), b(n);
+  EXPECT(rt::launch_silu_mul_reference_cuda(gate.p, up.p, n, a.p, s) == 0);
+  EXPECT(q3x_b200_silu_mul(gate.p, up.p, n, b.p, s) == 0);
+  EXPECT(same(a, b) && written(a));
+  EXPECT(rt::launch_sigmoid_gate_reference_cuda(up.p, gate.p, n, a.p, s) == 0);
+  EXPECT(q3x_b200_sigmoid_gate(up.p, gate.p, n, b.p, s) == 0);
+  EXPECT(same(a, b));
+  EXPECT(rt::launch_residual_add_reference_cuda(gate.p, up.p, n, a.p, s) == 0);
+  EXPECT(q3x_b200_residual_add(gate.p, up.p, n, b.p, s) == 0);
+  EXPECT(same(a, b));
+
+  const std::size_t vocab = 300, hidden = 5120, tokens = 37;
+  Bf16 table(random_bf16(vocab * hidden, 0.02f));
+  std::vector<std::uint32_t> ids(tokens);
+  for (std::size_t t = 0; t < tokens; ++t) ids[t] = static_cast<std::uint32_t>((t * 97u + 11u) % vocab);
+  DeviceBuffer<std::uint32_t> d_ids(ids);
+  Bf16 e1(tokens * hidden), e2(tokens * hidden);
+  EXPECT(rt::launch_embedding_gather_prompt_reference_cuda(table.p, vocab, hidden, d_ids.p, tokens, e1.p, s) == 0);
+  EXPECT(q3x_b200_embedding_gather(table.p, vocab, hidden, d_ids.p, tokens, e2.p, s) == 0);
+  EXPECT(same(e1, e2) && written(e1));
+  // by-value form: one row, against the table itself
+  Bf16 one(hidden);
+  EXPECT(rt::launch_embedding_gather_reference_cuda(table.p, vocab, hidden, 123, one.p, s) == 0);
+  CUDA_OK(cudaDeviceSynchronize());
+  const auto row = one.get(), tab = table.get();
+  EXPECT(std::memcmp(row.data(), tab.data() + 123 * hidden, hidden * 2) == 0);
+
+  std::vector<float> f(4099);
+  for (auto& x : f) x = (uniform() - 0.5f) * 100.0f;
+  DeviceBuffer<float> d_f(f);
+  Bf16 c1(f.size()), c2(f.size());
+  EXPECT(rt::launch_fp32_to_bf16_reference_cuda(d_f.p, f.size(), c1.p, s) == 0);
+  EXPECT(q3x_b200_fp32_to_bf16(d_f.p, f.size(), c2.p, s) == 0);
+  EXPECT(same(c1, c2) && written(c1));
+}
+
+static void test_norms(cudaStream_t s) {
+  const float eps = 1e-6f;
+  const std::size_t tokens = 77, hidden = 5120;
+  Bf16 left(random_bf16(tokens * hidden, 1.0f)), right(random_bf16(tokens * hidden, 1.0f)),
+      w(random_bf16(hidden, 0.02f));
+  Bf16 r1(tokens * hidden), n1(tokens * hidden), r2(tokens * hidden), n2(tokens * hidden);
+  EXPECT(rt::launch_residual_add_headwise_centered_rms_norm_prefill_5120_cuda(left.p, right.p, w.p, tokens, hidden, eps,
+                                                                            r1.p, n1.p, s) == 0);
+  EXPECT(q3x_b200_residual_add_rms_norm(left.p, right.p, w.p, tokens, hidden, eps, r2.p, n2.p, s) == 0);
+  EXPECT(same(r1, r2) && same(n1, n2) && written(n1));
+  // decode form: one token, weight and epsilon in their own positions
+  Bf16 r3(hidden), n3(hidden), r4(hidden), n4(hidden);
+  EXPECT(rt::launch_residual_add_centered_rms_norm_5120_cuda(left.p, right.p, w.p, eps, r3.p, n3.p, s) == 0);
+  EXPECT(q3x_b200_residual_add_rms_norm(left.p, right.p, w.p, 1, hidden, eps, r4.p, n4.p, s) == 0);
+  EXPECT(same(r3, r4) && same(n3, n4));
+  // M32 form
+  Bf16 r5(32 * hidden), n5(32 * hidden), r6(32 * hidden), n6(32 * hidden);
+  EXPECT(rt::launch_residual_add_headwise_centered_rms_norm_m32_5120_cuda(left.p, right.p, w.p, 32, hidden, eps, r5.p,
+                                                                        n5.p, s) == 0);
+  EXPECT(q3x_b200_residual_add_rms_norm(left.p, right.p, w.p, 32, hidden, eps, r6.p, n6.p, s) == 0);
+  EXPECT(same(r5, r6) && same(n5, n6));
+
+  // single-row and head-wise norms, centred and plain; gated; L2
+  Bf16 o1(tokens * hidden), o2(tokens * hidden);
+  EXPECT(rt::launch_centered_rms_norm_reference_cuda(left.p, w.p, hidden, eps, o1.p, s) == 0);
+  EXPECT(q3x_b200_rms_norm(left.p, w.p, 1, hidden, eps, 1, o2.p, s) == 0);
+  EXPECT(same(o1, o2));
+  EXPECT(rt::launch_plain_rms_norm_reference_cuda(left.p, w.p, hidden, eps, o1.p, s) == 0);
+  EXPECT(q3x_b200_rms_norm(left.p, w.p, 1, hidden, eps, 0, o2.p, s) == 0);
+  EXPECT(same(o1, o2));
+  const std::size_t heads = 24 * 9, dim = 256;
+  Bf16 hw(random_bf16(dim, 0.02f));
+  EXPECT(rt::launch_headwise_centered_rms_norm_reference_cuda(left.p, hw.p, heads, dim, eps, o1.p, s) == 0);
+  EXPECT(q3x_b200_rms_norm(left.p, hw.p, heads, dim, eps, 1, o2.p, s) == 0);
+  EXPECT(same(o1, o2));
+  EXPECT(rt::launch_headwise_plain_rms_norm_reference_cuda(left.p, hw.p, 48 * 5, 128, eps, o1.p, s) == 0);
+  EXPECT(q3x_b200_rms_norm(left.p, hw.p, 48 * 5, 128, eps, 0, o2.p, s) == 0);
+  EXPECT(same(o1, o2));
+  EXPECT(rt::launch_headwise_plain_rms_norm_silu_gate_reference_cuda(left.p, hw.p, right.p, 48 * 5, 128, eps, o1.p,
+                                                                     s) == 0);
+  EXPECT(q3x_b200_rms_norm_silu_gate(left.p, hw.p, right.p, 48 * 5, 128, eps, o2.p, s) == 0);
+  EXPECT(same(o1, o2));
+  EXPECT(rt::launch_l2_normalize_heads_reference_cuda(left.p, 16 * 7, 128, eps, o1.p, s) == 0);
+  EXPECT(q3x_b200_l2_normalize_heads(left.p, 16 * 7, 128, eps, 1.0f, o2.p, s) == 0);
+  EXPECT(same(o1, o2));
+}
+
+static void test_full_attention(cudaStream_t s) {
+  const float eps = 1e-6f;
+  const std::size_t tokens = 19, first = 40, positions = first + tokens;
+  std::vector<float> cosv(positions * 32), sinv(positions * 32);
+  for (std::size_t p = 0; p < positions; ++p)
+    for (std::size_t i = 0; i < 32; ++i) {
+      const float angle = static_cast<float>(p) / std::pow(1.0e7f, 2.0f * static_cast<float>(i) / 64.0f);
+      cosv[p * 32 + i] = std::cos(angle);
+      sinv[p * 32 + i] = std::sin(angle);
+    }
+  DeviceBuffer<float> cosd(cosv), sind(sinv);
+  const auto qg_host = random_bf16(tokens * 24 * 2 * 256, 1.0f);
+  const auto key_host = random_bf16(tokens * 4 * 256, 1.0f);
+  Bf16 qg(qg_host), k1(key_host), k2(key_host), qw(random_bf16(256, 0.02f)), kw(random_bf16(256, 0.02f));
+  Bf16 q1(tokens * 24 * 256), g1(tokens * 24 * 256), q2(tokens * 24 * 256), g2(tokens * 24 * 256);
+  EXPECT(rt::launch_full_attention_preprocess_24_4_256_64_cuda(qg.p, k1.p, qw.p, kw.p, eps, q1.p, g1.p, cosd.p, sind.p,
+                                                               first, tokens, s) == 0);
+  EXPECT(q3x_b200_full_attention_preprocess(qg.p, k2.p, qw.p, kw.p, eps, q2.p, g2.p, cosd.p, sind.p, first, tokens,
+                                            s) == 0);
+  EXPECT(same(q1, q2) && same(g1, g2) && same(k1, k2) && written(q1));
+  // the split and the stand-alone rotations
+  Bf16 sq1(tokens * 24 * 256), sg1(tokens * 24 * 256), sq2(tokens * 24 * 256), sg2(tokens * 24 * 256);
+  EXPECT(rt::launch_split_interleaved_q_gate_reference_cuda(qg.p, tokens * 24, 256, sq1.p, sg1.p, s) == 0);
+  EXPECT(q3x_b200_split_interleaved_q_gate(qg.p, tokens * 24, 256, sq2.p, sg2.p, s) == 0);
+  EXPECT(same(sq1, sq2) && same(sg1, sg2) && same(sg1, g1));
+  Bf16 k3(key_host), k4(key_host);
+  const std::size_t tile = 16;
+  EXPECT(rt::launch_qk_partial_neox_rope_tile_24_4_256_64_cuda(sq1.p, k3.p, cosd.p, sind.p, first, tile, s) == 0);
+  EXPECT(q3x_b200_qk_partial_neox_rope(sq2.p, k4.p, cosd.p, sind.p, first, tile, s) == 0);
+  EXPECT(same(sq1, sq2) && same(k3, k4));
+  Bf16 ro1(24 * 256), ro2(24 * 256);
+  EXPECT(rt::launch_partial_neox_rope_256_64_reference_cuda(sg1.p, cosd.p + 32 * first, sind.p + 32 * first, 24, ro1.p,
+                                                            s) == 0);
+  EXPECT(q3x_b200_partial_neox_rope_256_64(sg1.p, cosd.p + 32 * first, sind.p + 32 * first, 24, ro2.p, s) == 0);
+  EXPECT(same(ro1, ro2) && written(ro1));
+}
+
+static void test_conv(cudaStream_t s) {
+  const std::size_t channels = 10240;
+  const auto raw_host = random_bf16(16 * channels, 1.0f);
+  const auto hist_host = random_bf16(channels * 3, 1.0f);
+  Bf16 raw(raw_host), w(random_bf16(channels * 4, 0.5f));
+  for (std::size_t tokens : {std::size_t{1}, std::size_t{7}, std::size_t{16}}) {
+    Bf16 h1(hist_host), h2(hist_host), o1(tokens * channels), o2(tokens * channels);
+    if (tokens == 1)
+      EXPECT(rt::launch_causal_conv1d_silu_update_reference_cuda(raw.p, w.p, h1.p, o1.p, rt::GdnDimensions{}, s) == 0);
+    else
+      EXPECT(rt::launch_causal_conv1d_silu_update_tile_reference_cuda(raw.p, tokens, w.p, h1.p, o1.p,
+                                                                      rt::GdnDimensions{}, s) == 0);
+    EXPECT(q3x_b200_causal_conv1d_silu(raw.p, tokens, channels, w.p, h2.p, o2.p, s) == 0);
+    EXPECT(same(o1, o2) && same(h1, h2) && written(o1));
+  }
+  namespace conv = rt::gdn_prefill_whole_span_conv_detail;
+  Bf16 h1(hist_host), h2(hist_host), h3(hist_host), o1(16 * channels), o2(16 * channels), o3(16 * channels);
+  EXPECT(conv::launch_causal_conv1d_silu_update_whole_span_exact_cuda(raw.p, 16, w.p, h1.p, o1.p, s) == 0);
+  EXPECT(conv::launch_causal_conv1d_silu_update_token_parallel_exact_cuda(raw.p, 16, w.p, h2.p, o2.p, s) == 0);
+  EXPECT(q3x_b200_causal_conv1d_silu(raw.p, 16, channels, w.p, h3.p, o3.p, s) == 0);
+  EXPECT(same(o1, o3) && same(o2, o3) && same(h1, h3) && same(h2, h3));
+}
+
+static void test_dispatch_halves(cudaStream_t s) {
+  const float eps = 1e-6f;
+  const std::size_t tokens = 9, hidden = 5120, inter = 17408;
+  const auto gate_host = random_bf16(tokens * inter, 1.5f);
+  Bf16 g1(gate_host), g2(gate_host), up(random_bf16(tokens * inter, 1.0f));
+  EXPECT(rt::launch_mlp_gate_up_silu_epilogue_cuda(rt::ProjectionBackend::kB200LayerOps, g1.p, up.p, tokens, inter,
+                                                   s) == 0);
+  EXPECT(q3x_b200_silu_mul(g2.p, up.p, tokens * inter, g2.p, s) == 0);
+  EXPECT(same(g1, g2));
+  EXPECT(rt::launch_mlp_gate_up_silu_epilogue_cuda(rt::ProjectionBackend::kReference, g1.p, up.p, tokens, inter, s) ==
+         static_cast<int>(cudaErrorNotSupported));
+  const auto right_host = random_bf16(tokens * hidden, 1.0f);
+  Bf16 left(random_bf16(tokens * hidden, 1.0f)), w(random_bf16(hidden, 0.02f)), ra(right_host), rb(right_host);
+  Bf16 res1(tokens * hidden), res2(tokens * hidden);
+  EXPECT(rt::launch_post_attention_residual_norm_prologue_cuda(rt::ProjectionBackend::kB200LayerOps, left.p, ra.p, w.p,
+                                                               eps, tokens, hidden, res1.p, s) == 0);
+  EXPECT(q3x_b200_residual_add_rms_norm(left.p, rb.p, w.p, tokens, hidden, eps, res2.p, rb.p, s) == 0);
+  EXPECT(same(res1, res2) && same(ra, rb));
+  Bf16 n1(tokens * hidden), n2(tokens * hidden);
+  EXPECT(rt::launch_mlp_down_residual_norm_epilogue_cuda(rt::ProjectionBackend::kB200LayerOps, ra.p, left.p, w.p, eps,
+                                                         tokens, hidden, res1.p, n1.p, s) == 0);
+  EXPECT(q3x_b200_residual_add_rms_norm(left.p, ra.p, w.p, tokens, hidden, eps, res2.p, n2.p, s) == 0);
+  EXPECT(same(res1, res2) && same(n1, n2));
+}
+
+int main() {
+  int device_count = 0;
+  if (cudaGetDeviceCount(&device_count) != cudaSuccess || device_count == 0) {
+    std::printf("no CUDA device: skipped\n");
+    return 77;
+  }
+  cudaDeviceProp prop{};
+  CUDA_OK(cudaGetDeviceProperties(&prop, 0));
+  if (prop.major != 10) {
+    std::printf("device is sm_%d%d, the library is built for sm_100a: skipped\n", prop.major, prop.minor);
+    return 77;
+  }
+  cudaStream_t s = nullptr;
+  CUDA_OK(cudaStreamCreate(&s));
+  test_pointwise_and_embedding(s);
+  test_norms(s);
+  test_full_attention(s);
+  test_conv(s);
+  test_dispatch_halves(s);
+  CUDA_OK(cudaStreamSynchronize(s));
+  CUDA_OK(cudaGetLastError());
+  CUDA_OK(cudaStreamDestroy(s));
+  if (failures == 0) std::printf("host mirror GPU tests passed\n");
+  return failures;
+}

@@ -23,10 +23,11 @@ def test_reference_arm_prints_one_json_line_with_the_contract_keys():
     assert len(lines) == 1
     d = json.loads(lines[0])
     assert d["impl"] == "reference" and d["unit"] == "tokens/s" and d["higher_is_better"] is True
-    assert d["value"] > 0 and d["ms_per_step"] > 0 and d["scaling"] == "weak" and d["vs_baseline"] is None
+    assert d["value"] > 0 and d["ms_per_step"] > 0 and d["scaling"] == "strong" and d["vs_baseline"] is None
     assert d["config"]["workload"] and "model" not in d["config"]
     cpu = d["cpu_baseline"]
-    assert cpu["kind"] in ("reference", "port") and cpu["cores"] >= 1 and "64 tokens" in cpu["sample"]
+    assert cpu["kind"] in ("reference", "port") and cpu["cores"] >= 1 and "64-token sample" in cpu["sample"]
+    assert cpu["extrapolated"] is False and cpu["sample_tokens"] == 64
     assert cpu["value"] == d["value"]
     assert d["e2e"] == {"value": d["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
     assert d["gpu_launches"] == 0

@@ -78,7 +78,7 @@ def test_quantize_dynamic(g, rows, cols, rps, misalign):
     x = make_input(rows, cols, 1)
     groups = 1 if rps == 0 else (rows + rps - 1) // rps
     dx = g.Dev(x, misalign)
-    amax = g.scratch_for(rows, rps)  # stale contents must not matter
+    amax = g.scratch_for(rows, rps)
     gs = g.empty_like_dev((groups,), dtype=np.float32)
     codes = g.empty_like_dev((rows, cols // 2), dtype=np.uint8, misalign=misalign)
     scales = g.empty_like_dev((rows, cols // 16), dtype=np.uint8)
@@ -86,12 +86,12 @@ def test_quantize_dynamic(g, rows, cols, rps, misalign):
     g.sync()
     want_c, want_s, want_g = orc.nvfp4_quantize(x, rps)
     assert np.array_equal(gs.get().view(np.uint32), want_g.view(np.uint32)), "global scales"
-    assert np.array_equal(amax.get()[:groups] << 16, orc.group_amax(x, rps).view(np.uint32)), "group amax bits"
+    g.assert_scratch_clean(amax, "quantize_dynamic")
     g.assert_bits_equal(scales.get(), want_s, "E4M3 block scales")
     g.assert_bits_equal(codes.get(), want_c, "E2M1 codes")
     assert codes.guards_intact() and scales.guards_intact() and gs.guards_intact() and amax.guards_intact()
     # the pieces, called one by one, give the same bytes
-    amax2 = g.empty_like_dev((groups,), dtype=np.uint32, fill=77)
+    amax2 = g.empty_like_dev((groups,), dtype=np.uint32, fill=77)  # an output here: the call zeroes it itself
     gs2 = g.empty_like_dev((groups,), dtype=np.float32)
     c2 = g.empty_like_dev((rows, cols // 2), dtype=np.uint8)
     s2 = g.empty_like_dev((rows, cols // 16), dtype=np.uint8)
@@ -100,6 +100,7 @@ def test_quantize_dynamic(g, rows, cols, rps, misalign):
     g.capi.check("q3x_b200_amax_to_global_scale", amax2, groups, gs2, None)
     g.capi.check("q3x_b200_nvfp4_quantize", dx, rows, cols, rps, gs2, c2, s2, None)
     g.sync()
+    assert np.array_equal(amax2.get() << 16, orc.group_amax(x, rps).view(np.uint32)), "group amax bits"
     g.assert_bits_equal(c2.get(), want_c, "codes (stepwise)")
     g.assert_bits_equal(s2.get(), want_s, "scales (stepwise)")
 
@@ -149,7 +150,7 @@ def test_residual_norm_nvfp4(g, tokens, rps, single_pass):
         pytest.skip("scale group too long for the single-kernel form")
     assert st == 0
     g.sync()
-    assert amax.get()[-1] == 0, "a bounded wait inside the single-pass kernel gave up"
+    g.assert_scratch_clean(amax, entry)
     want_r, want_n = orc.residual_add_rms_norm(left, right, w, EPS)
     g.assert_bits_equal(res.get(), want_r, "residual")
     g.assert_bf16_within(nrm.get(), want_n, 1, 0.98, "normalized")
@@ -193,7 +194,7 @@ def test_gated_norm_nvfp4(g, tokens, rps, single_pass):
         pytest.skip("scale group too long for the single-kernel form")
     assert st == 0
     g.sync()
-    assert amax.get()[-1] == 0, "a bounded wait inside the single-pass kernel gave up"
+    g.assert_scratch_clean(amax, entry)
     want = orc.rms_norm_rows(x, w, EPS, centered=False, gate=z).reshape(tokens, heads * dim)
     g.assert_bf16_within(out.get(), want, 1, 0.98, "gated norm")
     want_c, want_s, want_g = orc.nvfp4_quantize(out.get(), rps)
@@ -219,7 +220,7 @@ def test_silu_mul_nvfp4(g, tokens, inter, rps):
     scales = g.empty_like_dev((tokens, inter // 16), dtype=np.uint8)
     g.capi.check("q3x_b200_silu_mul_nvfp4", dg, du, tokens, inter, rps, out, scratch, gs, codes, scales, None)
     g.sync()
-    assert scratch.get()[-1] == 0, "a bounded wait inside the kernel gave up"
+    g.assert_scratch_clean(scratch, "pointwise + NVFP4")
     got = out.get()
     g.assert_bf16_within(got, orc.silu_mul(gate, up), 1, 0.98, "SwiGLU")
     # the same bytes as the stand-alone SwiGLU entry, and codes / scales derived from them bit for bit
@@ -271,7 +272,7 @@ def test_single_kernel_path_matches_two_kernel_path_over_many_launches(g):
     gen = torch.Generator(device="cuda").manual_seed(2024)
     bf = dict(device="cuda", dtype=torch.bfloat16)
     words = g.capi.lib().q3x_b200_nvfp4_scratch_words(T, 512)
-    scratch = torch.full((words,), 0x55AA55AA, device="cuda", dtype=torch.int32)
+    scratch = torch.zeros((words,), device="cuda", dtype=torch.int32)
     w = (torch.randn((H,), generator=gen, device="cuda") * 0.02).to(torch.bfloat16)
     outs = []
     for _ in range(2):
@@ -289,7 +290,7 @@ def test_single_kernel_path_matches_two_kernel_path_over_many_launches(g):
         g.capi.check("q3x_b200_residual_add_rms_norm_nvfp4_static_scratch", left, right, w, T, H, EPS, 512, b["res"],
                      b["nrm"], b["gs"], b["codes"], b["scales"], None)
         g.sync()
-        assert int(scratch[-1].item()) == 0, f"launch {it}: a bounded wait gave up"
+        assert not bool(scratch.any().item()), f"launch {it}: scratch not left zero (or a bounded wait gave up)"
         for name in a:
             assert torch.equal(a[name].view(torch.uint8), b[name].view(torch.uint8)), f"launch {it}: {name} differs"
 
@@ -310,7 +311,7 @@ def test_sigmoid_gate_nvfp4(g, tokens, width, rps):
     scales = g.empty_like_dev((tokens, width // 16), dtype=np.uint8)
     g.capi.check("q3x_b200_sigmoid_gate_nvfp4", dv, dg, tokens, width, rps, out, scratch, gs, codes, scales, None)
     g.sync()
-    assert scratch.get()[-1] == 0, "a bounded wait inside the kernel gave up"
+    g.assert_scratch_clean(scratch, "pointwise + NVFP4")
     got = out.get()
     g.assert_bf16_within(got, orc.sigmoid_gate(value, gate), 1, 0.98, "sigmoid gate")
     plain = g.empty_like_dev((tokens, width))
@@ -323,3 +324,55 @@ def test_sigmoid_gate_nvfp4(g, tokens, width, rps):
     g.assert_bits_equal(codes.get(), want_c, "codes")
     for d in (out, codes, scales, gs, scratch):
         assert d.guards_intact()
+
+
+def test_one_scratch_serves_calls_of_any_shape_and_the_error_word_is_sticky(g):
+    """The scratch contract: zeroed once by the caller, left zero by every call, so differently shaped
+    calls share one buffer back to back with nothing cleared in between; the last word is only ever
+    set by the library, never cleared, so a flag planted by the caller survives every call."""
+    rng = np.random.default_rng(808)
+    H, I = 5120, 17408
+    big = 3000
+    scratch = g.scratch_for(big, 1)  # the largest any of the calls below needs
+    flag = 0x40
+    scratch.t[-1] = flag  # planted: must still be there at the end
+    plan = [("res", 700, 512), ("gated", 600, 512), ("swiglu", 520, 512), ("res", 2, 0), ("res", 1300, 0),
+            ("sig", 700, 512), ("dyn", 33, 16), ("res", 3000, 0), ("gated", 9, 4), ("res", 513, 512)]
+    for kind, tokens, rps in plan:
+        groups = 1 if rps == 0 else (tokens + rps - 1) // rps
+        gs = g.empty_like_dev((groups,), dtype=np.float32)
+        if kind == "res":
+            left, right = fx.normal_bf16(rng, (tokens, H)), fx.normal_bf16(rng, (tokens, H))
+            w = fx.normal_bf16(rng, (H,), 0.02)
+            res, out = g.empty_like_dev((tokens, H)), g.empty_like_dev((tokens, H))
+            codes, scales = g.empty_like_dev((tokens, H // 2), dtype=np.uint8), g.empty_like_dev((tokens, H // 16), dtype=np.uint8)
+            g.capi.check("q3x_b200_residual_add_rms_norm_nvfp4", g.Dev(left), g.Dev(right), g.Dev(w), tokens, H, EPS, rps,
+                         res, out, scratch, gs, codes, scales, None)
+        elif kind == "gated":
+            x, z = fx.normal_bf16(rng, (tokens, 48, 128)), fx.normal_bf16(rng, (tokens, 48, 128))
+            w = orc.bf16_encode((0.75 + rng.random(128) * 0.5).astype(np.float32))
+            out = g.empty_like_dev((tokens, 6144))
+            codes, scales = g.empty_like_dev((tokens, 3072), dtype=np.uint8), g.empty_like_dev((tokens, 384), dtype=np.uint8)
+            g.capi.check("q3x_b200_rms_norm_silu_gate_nvfp4", g.Dev(x), g.Dev(w), g.Dev(z), tokens, 48, 128, EPS, rps, out,
+                         scratch, gs, codes, scales, None)
+        elif kind in ("swiglu", "sig"):
+            width = I if kind == "swiglu" else 6144
+            a, b = fx.normal_bf16(rng, (tokens, width)), fx.normal_bf16(rng, (tokens, width))
+            out = g.empty_like_dev((tokens, width))
+            codes = g.empty_like_dev((tokens, width // 2), dtype=np.uint8)
+            scales = g.empty_like_dev((tokens, width // 16), dtype=np.uint8)
+            g.capi.check("q3x_b200_silu_mul_nvfp4" if kind == "swiglu" else "q3x_b200_sigmoid_gate_nvfp4", g.Dev(a),
+                         g.Dev(b), tokens, width, rps, out, scratch, gs, codes, scales, None)
+        else:
+            x = fx.normal_bf16(rng, (tokens, H))
+            out = g.Dev(x)
+            codes, scales = g.empty_like_dev((tokens, H // 2), dtype=np.uint8), g.empty_like_dev((tokens, H // 16), dtype=np.uint8)
+            g.capi.check("q3x_b200_nvfp4_quantize_dynamic", out, tokens, H, rps, scratch, gs, codes, scales, None)
+        g.sync()
+        words = scratch.get()
+        assert words[-1] == flag, f"{kind} {tokens}/{rps}: the sticky error word was touched ({words[-1]:#x})"
+        assert not words[:-1].any(), f"{kind} {tokens}/{rps}: scratch words left non-zero"
+        want_c, want_s, want_g = orc.nvfp4_quantize(out.get(), rps)
+        g.assert_bits_equal(codes.get(), want_c, f"{kind} {tokens}/{rps}: codes")
+        g.assert_bits_equal(scales.get(), want_s, f"{kind} {tokens}/{rps}: scales")
+        assert np.array_equal(gs.get().view(np.uint32), want_g.view(np.uint32)), f"{kind} {tokens}/{rps}: global scales"

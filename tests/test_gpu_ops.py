@@ -319,6 +319,9 @@ def test_full_attention_preprocess(g, tokens, first):
     _, exact_q = g.ulp_report(q.get()[:, :, :64], want_q[:, :, :64])
     _, exact_k = g.ulp_report(d_key.get()[:, :, :64], want_k[:, :, :64])
     assert exact_q > 0.97 and exact_k > 0.97
+    # hard bound on the rotated dims end to end: the reference's own tolerance for this operator
+    g.assert_reference_tolerance(q.get(), want_q, "q end to end")
+    g.assert_reference_tolerance(d_key.get(), want_k, "k end to end")
 
 
 @pytest.mark.parametrize("heads,misalign", [(3, 0), (28, 0), (24, 1)])
@@ -421,6 +424,9 @@ def test_causal_conv_l2norm(g, tokens):
     cq = orc.l2_normalize_heads(cpu_conv[:, :2048].reshape(-1, 128), EPS, qs).reshape(tokens, 2048)
     worst, exact = g.ulp_report(got[:, :2048], cq)
     assert worst <= 2 and exact > 0.97  # two roundings in a row: each within 1 ulp
+    ck = orc.l2_normalize_heads(cpu_conv[:, 2048:4096].reshape(-1, 128), EPS, 1.0).reshape(tokens, 2048)
+    g.assert_reference_tolerance(got[:, :2048], cq, "conv -> L2 (q) end to end")
+    g.assert_reference_tolerance(got[:, 2048:4096], ck, "conv -> L2 (k) end to end")
     g.assert_bits_equal(d_h.get(), want_h, "history")
     assert out.guards_intact()
 

@@ -10,7 +10,7 @@ import pytest
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 PKG = os.path.join(ROOT, "qwen3x-orin_b200")
 HOST = os.path.join(PKG, "host")
-REFERENCE = "/root/reference"
+REFERENCE = os.environ.get("Q3X_REFERENCE_DIR") or os.path.abspath(os.path.join(ROOT, "..", "reference"))
 
 
 @pytest.fixture(scope="module")
@@ -44,3 +44,22 @@ def test_mirror_defines_the_reference_symbols(host_lib, tmp_path):
                           [os.path.join(REFERENCE, "include")])
     assert out.returncode == 0, out.stdout + out.stderr
     assert "23 reference launcher symbols resolved" in out.stdout
+
+
+@pytest.mark.gpu
+def test_mirror_launchers_on_the_gpu_match_the_c_abi(host_lib, tmp_path):
+    """One launcher of every family called through libq3x_b200_host.so with real device buffers; the
+    bytes must equal those of the same call made on the C ABI (a wrong argument order in the forwarding
+    code cannot pass)."""
+    cuda_home = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+    exe = str(tmp_path / "host_gpu_test")
+    cmd = ["g++", "-std=c++17", "-O1", "-Wall", "-Wextra", os.path.join(ROOT, "tests", "host", "host_gpu_test.cpp"),
+           "-o", exe, "-I", HOST, "-I", os.path.join(ROOT, "include"), "-I", os.path.join(cuda_home, "include"),
+           "-L", PKG, "-lq3x_b200_host", "-lq3x_b200", f"-Wl,-rpath,{PKG}",
+           "-L", os.path.join(cuda_home, "lib64"), "-lcudart", f"-Wl,-rpath,{os.path.join(cuda_home, 'lib64')}"]
+    subprocess.run(cmd, check=True, capture_output=True, text=True)
+    out = subprocess.run([exe], capture_output=True, text=True, timeout=600)
+    if out.returncode == 77:
+        pytest.skip(out.stdout.strip())
+    assert out.returncode == 0, out.stdout[-4000:] + out.stderr[-2000:]
+    assert "host mirror GPU tests passed" in out.stdout
