@@ -48,9 +48,8 @@ def reference_dir() -> str:
 
 def build(force: bool = False) -> None:
     """Compile the restatement (and, where a reference checkout exists, ``_ref``)."""
-    if force or not os.path.exists(_ORACLE_SO) or (
-        os.path.getmtime(_ORACLE_SO) < os.path.getmtime(os.path.join(_HERE, "q3x_oracle.c"))
-    ):
+    sources = [os.path.join(_HERE, n) for n in ("q3x_oracle.c", "q3x_oracle_core.c", "q3x_oracle.h")]
+    if force or not os.path.exists(_ORACLE_SO) or os.path.getmtime(_ORACLE_SO) < max(map(os.path.getmtime, sources)):
         subprocess.run(["make", "-C", _HERE, "oracle"], check=True, capture_output=True)
     shim = os.path.join(_HERE, "ref_shim.cpp")
     if os.path.isdir(os.path.join(reference_dir(), "src", "runtime", "reference")) and (
@@ -121,6 +120,15 @@ def oracle_lib():
         L.quant_ws = L.fn("q3x_oracle_nvfp4_quantize_with_scales", i, _u16p, _sz, _sz, _sz, _f32p, _u8p,
                           _u8p)
         L.group_amax = L.fn("q3x_oracle_group_amax", i, _u16p, _sz, _sz, _sz, _f32p)
+        L.gdn_update = L.fn("q3x_oracle_gated_delta_net_update", i, _u16p, _sz, _u16p, _u16p, _u16p, _u16p, _u16p,
+                            _u16p, f, _u16p)
+        L.softmax = L.fn("q3x_oracle_softmax", i, _f32p, _sz, _sz, _f32p)
+        L.gqa = L.fn("q3x_oracle_gqa_attention", i, _u16p, _u16p, _u16p, _sz, _sz, _sz, _sz, f, _f32p, _u16p)
+        L.gqa_gate = L.fn("q3x_oracle_gqa_attention_sigmoid_gate", i, _u16p, _u16p, _u16p, _sz, _sz, _sz, _sz, f,
+                          _f32p, _u16p, _u16p)
+        L.argmax = L.fn("q3x_oracle_bf16_greedy_argmax", i, _u16p, _sz, _u32p, _u16p, _u16p)
+        L.bf16_gemv = L.fn("q3x_oracle_bf16_gemv", i, _u16p, _u16p, _sz, _sz, _f32p)
+        L.nvfp4_gemv = L.fn("q3x_oracle_nvfp4_gemv", i, _u8p, _u8p, f, _u16p, _sz, _sz, _f32p)
         _oracle = L
     return _oracle
 
@@ -161,6 +169,8 @@ def ref_lib():
         L.gdn_update = L.fn("ref_gated_delta_net_update", i, _u16p, _u16p, _u16p, _u16p, _u16p, _u16p, _u16p, f, _u16p)
         L.softmax = L.fn("ref_softmax", i, _f32p, _sz, _sz, _f32p)
         L.gqa = L.fn("ref_gqa_attention", i, _u16p, _u16p, _u16p, _sz, _sz, _sz, _sz, f, _f32p, _sz, _u16p)
+        L.bf16_gemv = L.fn("ref_bf16_gemv", i, _u16p, _u16p, _sz, _sz, _f32p)
+        L.nvfp4_gemv = L.fn("ref_nvfp4_gemv", i, _u8p, _u8p, f, _u16p, _sz, _sz, _f32p)
         L.embedding_rows = L.fn("ref_embedding_gather_rows", i, _u16p, _sz, _sz, _u32p, _sz, _u16p)
         L.conv_rows = L.fn("ref_causal_conv1d_silu_update_rows", i, _u16p, _sz, _u16p, _u16p, _u16p)
         L.preprocess_rows = L.fn("ref_full_attention_preprocess_rows", i, _u16p, _u16p, _u16p, _u16p, f, _u16p,
@@ -391,6 +401,75 @@ def group_amax(x, rows_per_scale=0):
     groups = 1 if rows_per_scale == 0 else (rows + rows_per_scale - 1) // rows_per_scale
     out = np.empty(groups, dtype=np.float32)
     _check(L.group_amax(_p(x, _u16p), rows, cols, rows_per_scale, _p(out, _f32p)))
+    return out
+
+
+# ------------------------------------------------------------------ operators between the fused layer ops
+
+def gated_delta_net_update(conv_qkv, a, b, A_log, dt_bias, state, l2_eps):
+    """Token-sequential GDN recurrence.  conv_qkv [T,10240], a / b [T,48], A_log / dt_bias [48],
+    state [48,128,128].  Returns (out [T,6144], new_state)."""
+    L = oracle_lib()
+    conv_qkv, a, b = _u16(conv_qkv).reshape(-1, 10240), _u16(a).reshape(-1, 48), _u16(b).reshape(-1, 48)
+    tokens = conv_qkv.shape[0]
+    new_state = _u16(state).copy()
+    out = np.empty((tokens, 6144), dtype=np.uint16)
+    _check(L.gdn_update(_p(conv_qkv, _u16p), tokens, _p(a, _u16p), _p(b, _u16p), _p(_u16(A_log), _u16p),
+                        _p(_u16(dt_bias), _u16p), _p(new_state, _u16p), _p(new_state, _u16p), l2_eps, _p(out, _u16p)))
+    return out, new_state
+
+
+def softmax(x):
+    L = oracle_lib()
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    out = np.empty_like(x)
+    _check(L.softmax(_p(x, _f32p), x.shape[0], x.shape[1], _p(out, _f32p)))
+    return out
+
+
+def gqa_attention(q, k_cache, v_cache, scale, gate=None):
+    """One query token [q_heads, dim] against caches [length, kv_heads, dim]; with `gate` the sigmoid output
+    gate follows across a bf16 boundary.  Returns (out [q_heads, dim], probabilities [q_heads, length])."""
+    L = oracle_lib()
+    q, k_cache, v_cache = _u16(q), _u16(k_cache), _u16(v_cache)
+    q_heads, dim = q.shape
+    length, kv_heads, _ = k_cache.shape
+    probs = np.empty((q_heads, length), dtype=np.float32)
+    out = np.empty_like(q)
+    if gate is None:
+        _check(L.gqa(_p(q, _u16p), _p(k_cache, _u16p), _p(v_cache, _u16p), q_heads, kv_heads, length, dim, scale,
+                     _p(probs, _f32p), _p(out, _u16p)))
+    else:
+        _check(L.gqa_gate(_p(q, _u16p), _p(k_cache, _u16p), _p(v_cache, _u16p), q_heads, kv_heads, length, dim, scale,
+                          _p(probs, _f32p), _p(_u16(gate), _u16p), _p(out, _u16p)))
+    return out, probs
+
+
+def greedy_argmax(logits):
+    """(index, value bits, has_nonfinite) of a bf16 vector."""
+    L = oracle_lib()
+    logits = _u16(logits).reshape(-1)
+    idx, bits, bad = C.c_uint32(), C.c_uint16(), C.c_uint16()
+    _check(L.argmax(_p(logits, _u16p), logits.size, C.byref(idx), C.byref(bits), C.byref(bad)))
+    return idx.value, bits.value, bad.value
+
+
+def bf16_gemv(w, x):
+    L = oracle_lib()
+    w, x = _u16(w), _u16(x)
+    out = np.empty(w.shape[0], dtype=np.float32)
+    _check(L.bf16_gemv(_p(w, _u16p), _p(x, _u16p), w.shape[0], w.shape[1], _p(out, _f32p)))
+    return out
+
+
+def nvfp4_gemv(packed, block_scales, weight_scale_2, x):
+    L = oracle_lib()
+    packed = np.ascontiguousarray(packed, dtype=np.uint8)
+    block_scales = np.ascontiguousarray(block_scales, dtype=np.uint8)
+    rows, cols = packed.shape[0], packed.shape[1] * 2
+    out = np.empty(rows, dtype=np.float32)
+    _check(L.nvfp4_gemv(_p(packed, _u8p), _p(block_scales, _u8p), float(weight_scale_2), _p(_u16(x), _u16p), rows, cols,
+                        _p(out, _f32p)))
     return out
 
 

@@ -159,6 +159,34 @@ int q3x_oracle_nvfp4_quantize_with_scales(const uint16_t* in, size_t rows, size_
 int q3x_oracle_group_amax(const uint16_t* in, size_t rows, size_t cols, size_t rows_per_scale,
                           float* amax_out);
 
+/* ---- the operators between the fused layer ops (q3x_oracle_core.c) --------------------------------- */
+
+/* gated_delta_net_update_reference_cpu (src/runtime/reference/gdn_decode.cpp:186-293), applied to
+ * `tokens` consecutive rows the way the tile launchers define it (include/q3x/runtime/gdn_decode.h:95-110):
+ * conv_qkv [tokens,10240], a / b [tokens,48], A_log / dt_bias [48], state [48,128,128] bf16 (state_out may be
+ * state_in), out [tokens,6144]. */
+int q3x_oracle_gated_delta_net_update(const uint16_t* conv_qkv, size_t tokens, const uint16_t* a,
+                                      const uint16_t* b, const uint16_t* A_log, const uint16_t* dt_bias,
+                                      const uint16_t* state_in, uint16_t* state_out, float l2_eps,
+                                      uint16_t* out);
+/* softmax_reference_cpu (src/runtime/reference/decode_ops.cpp:413-443); out may be in. */
+int q3x_oracle_softmax(const float* in, size_t rows, size_t cols, float* out);
+/* gqa_attention_reference_cpu (decode_ops.cpp:445-508); scratch [q_heads, length] floats. */
+int q3x_oracle_gqa_attention(const uint16_t* q, const uint16_t* k_cache, const uint16_t* v_cache, size_t q_heads,
+                             size_t kv_heads, size_t length, size_t dim, float scale, float* scratch,
+                             uint16_t* out);
+/* ... followed by the sigmoid output gate across a bf16 boundary (include/q3x/runtime/decode_ops.h:384-395). */
+int q3x_oracle_gqa_attention_sigmoid_gate(const uint16_t* q, const uint16_t* k_cache, const uint16_t* v_cache,
+                                          size_t q_heads, size_t kv_heads, size_t length, size_t dim, float scale,
+                                          float* scratch, const uint16_t* gate, uint16_t* out);
+/* The selection rule of bf16_greedy_argmax_kernel (src/kernels/reference/decode_ops.cu:246-345). */
+int q3x_oracle_bf16_greedy_argmax(const uint16_t* in, size_t count, uint32_t* index, uint16_t* value_bits,
+                                  uint16_t* has_nonfinite);
+/* bf16_gemv_reference_cpu / nvfp4_gemv_reference_cpu (src/kernels/reference/gemv_reference.cpp:84-110,179-225). */
+int q3x_oracle_bf16_gemv(const uint16_t* w, const uint16_t* x, size_t rows, size_t cols, float* out);
+int q3x_oracle_nvfp4_gemv(const uint8_t* packed, const uint8_t* block_scales, float weight_scale_2,
+                          const uint16_t* x, size_t rows, size_t cols, float* out);
+
 #ifdef __cplusplus
 }
 #endif

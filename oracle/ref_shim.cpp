@@ -112,6 +112,14 @@ int ref_gqa_attention(const std::uint16_t* q, const std::uint16_t* k_cache, cons
                                                           scratch, scratch_elements, out));
 }
 
+int ref_bf16_gemv(const std::uint16_t* w, const std::uint16_t* x, std::size_t rows, std::size_t cols, float* out) {
+  return static_cast<int>(q3x::kernels::bf16_gemv_reference_cpu(w, x, rows, cols, out));
+}
+int ref_nvfp4_gemv(const std::uint8_t* packed, const std::uint8_t* scales, float scale_2, const std::uint16_t* x,
+                   std::size_t rows, std::size_t cols, float* out) {
+  return static_cast<int>(q3x::kernels::nvfp4_gemv_reference_cpu(packed, scales, scale_2, x, rows, cols, out));
+}
+
 // ---- per-token host ops applied to a run of token rows --------------------------------------------
 // The reference's host ops for the embedding, the conv, the q|gate split and the rotation take ONE token;
 // its runner loops over tokens around them.  These wrappers are that loop, in C++, so that a timing of
