@@ -318,6 +318,79 @@ int q3x_b200_causal_conv1d_silu_l2norm(const uint16_t* raw, size_t tokens,
                                        const uint16_t* conv_weight, uint16_t* history_in_out,
                                        float l2_eps, float q_scale, uint16_t* out, void* stream);
 
+/* launch_causal_conv1d_silu_update_token_parallel_compact_qk_exact_cuda
+ * (src/kernels/reference/gdn_prefill_whole_span_conv_sm87.h:59-67), for any token count: the conv as above,
+ * `out` receiving the plain conv output of EVERY channel, plus the L2-normalised q and k heads (q additionally
+ * times q_scale; the reference uses 1/sqrt(128)) in the operand layout of the chunked GDN prefill:
+ * compact_q / compact_k [ceil(tokens / 64), 16 heads, 64, 128] bf16, the rows of the last chunk beyond `tokens`
+ * zeroed.  raw and out must be disjoint; the compact tensors must be disjoint from every other operand. */
+int q3x_b200_causal_conv1d_silu_compact_qk(const uint16_t* raw, size_t tokens, const uint16_t* conv_weight,
+                                           uint16_t* history_in_out, uint16_t* out, float l2_eps, float q_scale,
+                                           uint16_t* compact_q, uint16_t* compact_k, void* stream);
+
+/* ---------------------------------------------------------------- between the fused operators
+ * The stateful / contracting steps that sit between the operators above in a layer, in their batch-one
+ * (decode) and short-tile forms, which are HBM-bound streams like the rest of this library. */
+
+/* launch_gated_delta_net_update_reference_cuda (tokens = 1) and ..._tile_reference_cuda / the
+ * warp-parallel forms (include/q3x/runtime/gdn_decode.h:85-140), for any token count: the gated-delta-net
+ * recurrence, token by token.  conv_qkv [tokens, 10240] (the conv output: q 2048 | k 2048 | v 6144), a and b
+ * [tokens, 48], A_log and dt_bias [48], state [48, 128(v), 128(k)] bf16, out [tokens, 48 * 128].  The q / k L2
+ * norm (q additionally times 1/sqrt(128)), the gates and the sums are FP32; the state is rounded to bf16 after
+ * every token, the output uses the state before that rounding.  state_out may be exactly state_in; every other
+ * overlap of a written range is rejected.  Pointers must be 16-byte aligned (else cudaErrorNotSupported). */
+int q3x_b200_gated_delta_net_update(const uint16_t* conv_qkv, size_t tokens, const uint16_t* a,
+                                    const uint16_t* b, const uint16_t* A_log, const uint16_t* dt_bias,
+                                    const uint16_t* state_in, uint16_t* state_out, float l2_eps,
+                                    uint16_t* out, void* stream);
+/* launch_gated_delta_net_update_plain_rms_norm_silu_gate_cuda (gdn_decode.h:171-188): the recurrence with the
+ * GDN output's gated RMSNorm as its epilogue -- the raw output is rounded to bf16, then
+ * out = bf16(rmsnorm_128(raw) * norm_weight * silu(silu_gate)); norm_weight [128], silu_gate [tokens, 6144]. */
+int q3x_b200_gated_delta_net_update_rms_norm_silu_gate(
+    const uint16_t* conv_qkv, size_t tokens, const uint16_t* a, const uint16_t* b, const uint16_t* A_log,
+    const uint16_t* dt_bias, const uint16_t* state_in, uint16_t* state_out, float l2_eps,
+    const uint16_t* norm_weight, const uint16_t* silu_gate, float norm_eps, uint16_t* out, void* stream);
+
+/* launch_gqa_attention_splitkv_sigmoid_gate_24_4_256_cuda and
+ * gqa_attention_splitkv_sigmoid_gate_24_4_256_workspace_elements (include/q3x/runtime/decode_ops.h:397-423),
+ * for any sequence_length >= 1: one query token [24, 256] against key / value caches [sequence_length, 4, 256],
+ * softmax in FP32, attention rounded to bf16, times sigmoid(gate) [24, 256], rounded again.  gate == NULL gives
+ * the attention output itself (launch_gqa_attention_reference_cuda without its probabilities).  workspace is
+ * caller-owned FP32 scratch of at least q3x_b200_gqa_decode_workspace_floats(sequence_length) elements;
+ * stale contents do not matter. */
+size_t q3x_b200_gqa_decode_workspace_floats(size_t sequence_length);
+int q3x_b200_gqa_attention_decode_sigmoid_gate(const uint16_t* query, const uint16_t* key_cache,
+                                               const uint16_t* value_cache, size_t sequence_length,
+                                               float attention_scale, float* workspace, size_t workspace_floats,
+                                               const uint16_t* gate, uint16_t* out, void* stream);
+
+/* launch_bf16_gemv_reference_cuda / launch_bf16_gemv_bf16_cuda, launch_fp8_gemv_reference_cuda and
+ * launch_nvfp4_gemv_reference_cuda (include/q3x/kernels/reference_gemv.h:64-130): batch-one projections
+ * out[r] = sum_c W[r,c] * x[c], FP32 accumulation, x [cols] bf16.  The result is written as FP32 (out_f32), as
+ * bf16 rounded to nearest even (out_bf16), or both; at least one must be given.  bf16 weights [rows, cols];
+ * FP8 weights E4M3 [rows, cols] with a per-tensor weight_scale; NVFP4 weights in the canonical layout (packed
+ * [rows, cols / 2], even column in the low nibble; E4M3 block scales [rows, cols / 16]; FP32 weight_scale_2).
+ * Outputs must be disjoint from every input; read-only operands may alias.  Any shape and alignment. */
+int q3x_b200_bf16_gemv(const uint16_t* weights, const uint16_t* activation, size_t rows, size_t cols,
+                       float* out_f32, uint16_t* out_bf16, void* stream);
+int q3x_b200_fp8_gemv(const uint8_t* weights, float weight_scale, const uint16_t* activation, size_t rows,
+                      size_t cols, float* out_f32, uint16_t* out_bf16, void* stream);
+int q3x_b200_nvfp4_gemv(const uint8_t* packed_weights, const uint8_t* block_scales, float weight_scale_2,
+                        const uint16_t* activation, size_t rows, size_t cols, float* out_f32,
+                        uint16_t* out_bf16, void* stream);
+
+/* launch_softmax_reference_cuda (decode_ops.h:372-374), the FP32 row softmax of softmax_reference_cpu
+ * (src/runtime/reference/decode_ops.cpp:413-443): out may be exactly in. */
+int q3x_b200_softmax(const float* in, size_t rows, size_t cols, float* out, void* stream);
+
+/* launch_bf16_greedy_argmax_cuda (decode_ops.h:277-280): result_workspace holds
+ * Q3X_B200_ARGMAX_WORKSPACE_RESULTS records of {uint32 index, uint16 value_bits, uint16 has_nonfinite}
+ * (Bf16GreedyArgmaxResult, decode_ops.h:61-69); record 0 receives the answer, the rest is scratch.  Non-finite
+ * logits are skipped and flagged; equal maxima (signed zeros included) select the smallest index; no finite
+ * logit at all gives index 0xffffffff. */
+#define Q3X_B200_ARGMAX_WORKSPACE_RESULTS 33
+int q3x_b200_bf16_greedy_argmax(const uint16_t* in, size_t count, void* result_workspace, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

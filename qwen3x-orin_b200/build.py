@@ -15,7 +15,7 @@ LIB = os.path.join(PKG, "libq3x_b200.so")
 HOST_LIB = os.path.join(PKG, "libq3x_b200_host.so")
 
 CUDA_SOURCES = ["pointwise.cu", "row_norms.cu", "attention_preprocess.cu", "gdn_conv.cu", "embedding.cu", "nvfp4.cu",
-                "fused_nvfp4.cu"]
+                "fused_nvfp4.cu", "gdn_recurrence.cu", "gqa_decode.cu", "logits_ops.cu", "gemv.cu"]
 NVCC_FLAGS = [
     "-std=c++17", "-O3", "-lineinfo",
     "-gencode", "arch=compute_100a,code=sm_100a",

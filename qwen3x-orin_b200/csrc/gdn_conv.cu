@@ -70,10 +70,16 @@ struct ConvPlan {
 
 // kInPlace: raw == out with a single token run; the last three raw rows are then kept as bits in
 // registers because memory no longer holds them when the history is published.
-template <bool kL2, bool kInPlace>
+// kCompact (with kL2): `out` receives the plain conv output for every channel, and the normalised q / k heads
+// go to compact_q / compact_k instead, laid out [chunk of 64 tokens, qk head (16), token in chunk (64), 128]
+// with the rows of the last chunk beyond `tokens` zeroed -- the operand layout of the reference's chunked
+// GDN prefill (src/kernels/reference/gdn_prefill_whole_span_conv_sm87.cu:210-373).
+constexpr int kCompactChunk = 64;
+template <bool kL2, bool kInPlace, bool kCompact = false>
 __global__ void __launch_bounds__(kThreads, kInPlace ? 1 : 4)
     causal_conv_kernel(const uint4* raw, size_t tokens, int channel_vectors, const uint4* __restrict__ weight,
-                       uint4* history, uint4* out, ConvPlan plan, float l2_eps, float q_scale) {
+                       uint4* history, uint4* out, ConvPlan plan, float l2_eps, float q_scale,
+                       uint4* compact_q = nullptr, uint4* compact_k = nullptr) {
   // CTA index -> (channel block, token run); the blocks that carry the L2 norm come first
   unsigned channel_block, run;
   if (blockIdx.x < plan.norm_ctas) {
@@ -151,8 +157,15 @@ __global__ void __launch_bounds__(kThreads, kInPlace ? 1 : 4)
   };
   // One token: the four-tap chain on rows h0 (oldest) .. h2 and x, SiLU, rounding, optional L2 norm
   // (kNorm is a compile-time copy of is_qk, so the token loop carries no branch for it).
+  // compact layout: the lane's vector of head `cv / 16` (q heads first, then k heads) for token t
+  uint4* const compact_base = kCompact ? (cv < kQkVectors / 2 ? compact_q : compact_k) : nullptr;
+  const int compact_head = (cv % (kQkVectors / 2)) / kHeadVectors, compact_lane = cv % kHeadVectors;
+  auto compact_slot = [&](size_t t) {
+    return compact_base + ((t / kCompactChunk * Q3X_B200_GDN_QK_HEADS + compact_head) * kCompactChunk +
+                           t % kCompactChunk) * kHeadVectors + compact_lane;
+  };
   auto emit_token = [&](auto norm_tag, const float (&h0)[8], const float (&h1)[8], const float (&h2)[8],
-                        const float (&x)[8], uint4* dst) {
+                        const float (&x)[8], uint4* dst, size_t t) {
     constexpr bool kNorm = decltype(norm_tag)::value;
     float y[8];
 #pragma unroll
@@ -166,6 +179,7 @@ __global__ void __launch_bounds__(kThreads, kInPlace ? 1 : 4)
       y[j + 1] = s2.y;
     }
     uint4 packed = pack8(y);
+    if (kNorm && kCompact) st_vec(dst, packed);  // the conv output itself stays un-normalised in `out`
     if (kNorm) {
       // L2 norm of the ROUNDED conv output over the 128 channels of this head (16 lanes)
       float r[8];
@@ -182,6 +196,10 @@ __global__ void __launch_bounds__(kThreads, kInPlace ? 1 : 4)
         r[j + 1] = p.y;
       }
       packed = pack8(r);
+      if (kCompact) {
+        st_vec(compact_slot(t), packed);
+        return;
+      }
     }
     st_vec(dst, packed);
   };
@@ -209,7 +227,7 @@ __global__ void __launch_bounds__(kThreads, kInPlace ? 1 : 4)
         for (int u = 0; u < kBatch; ++u) {
           const uint4 x_bits = stage[buffer][u][threadIdx.x];
           unpack8(x_bits, rows[u + 3]);
-          emit_token(norm_tag, rows[u], rows[u + 1], rows[u + 2], rows[u + 3], dst + u * row_stride);
+          emit_token(norm_tag, rows[u], rows[u + 1], rows[u + 2], rows[u + 3], dst + u * row_stride, t + u);
           if (kInPlace && u >= kBatch - 3) keep[u - (kBatch - 3)] = x_bits;
         }
 #pragma unroll
@@ -222,7 +240,7 @@ __global__ void __launch_bounds__(kThreads, kInPlace ? 1 : 4)
           const uint4 x_bits = stage[buffer][u][threadIdx.x];
           float x[8];
           unpack8(x_bits, x);
-          emit_token(norm_tag, win[0], win[1], win[2], x, dst + u * row_stride);
+          emit_token(norm_tag, win[0], win[1], win[2], x, dst + u * row_stride, t + u);
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             win[0][j] = win[1][j];
@@ -240,6 +258,10 @@ __global__ void __launch_bounds__(kThreads, kInPlace ? 1 : 4)
   };
   if (is_qk) run_tokens_loop(std::true_type{});
   else run_tokens_loop(std::false_type{});
+  if (kCompact && is_qk && t1 == tokens) {  // the run that ends the span zeroes the tail of the last chunk
+    const size_t padded = (tokens + kCompactChunk - 1) / kCompactChunk * kCompactChunk;
+    for (size_t t = tokens; t < padded; ++t) st_vec(compact_slot(t), make_uint4(0, 0, 0, 0));
+  }
 
   // New history = the last three rows of (old history ++ raw), published by the first run's CTA.
   if (run == 0) {
@@ -278,7 +300,8 @@ __global__ void __launch_bounds__(kThreads, kInPlace ? 1 : 4)
 }
 
 int launch_conv(const uint16_t* raw, size_t tokens, size_t channels, const uint16_t* weight, uint16_t* history,
-                uint16_t* out, bool l2, float l2_eps, float q_scale, void* stream) {
+                uint16_t* out, bool l2, float l2_eps, float q_scale, void* stream, uint16_t* compact_q = nullptr,
+                uint16_t* compact_k = nullptr) {
   using namespace host;
   if (mul3_overflows(tokens, channels, sizeof(uint16_t))) return kInvalid;
   if (tokens == 0 || channels == 0) return kOk;
@@ -294,6 +317,19 @@ int launch_conv(const uint16_t* raw, size_t tokens, size_t channels, const uint1
       partial_overlap(sr, so))
     return kInvalid;
   if (l2 && raw == out) return kInvalid;
+  const bool compact = compact_q != nullptr || compact_k != nullptr;
+  if (compact) {
+    if (!l2 || compact_q == nullptr || compact_k == nullptr) return kInvalid;
+    const size_t chunks = (tokens + kCompactChunk - 1) / kCompactChunk;
+    if (mul3_overflows(chunks, static_cast<size_t>(kCompactChunk) * Q3X_B200_GDN_QK_HEADS, Q3X_B200_GDN_HEAD_DIM * 2))
+      return kInvalid;
+    const size_t compact_bytes = chunks * kCompactChunk * Q3X_B200_GDN_QK_HEADS * Q3X_B200_GDN_HEAD_DIM * 2;
+    const Span cq = span(compact_q, compact_bytes), ck = span(compact_k, compact_bytes);
+    if (wraps(cq) || wraps(ck) || overlap(cq, ck)) return kInvalid;
+    for (const Span& other : {sr, so, sw, sh})
+      if (overlap(cq, other) || overlap(ck, other)) return kInvalid;
+    if (!aligned16(compact_q) || !aligned16(compact_k)) return kNotSupported;
+  }
   if (!aligned16(raw) || !aligned16(out) || !aligned16(weight) || !aligned16(history)) return kNotSupported;
   const int channel_vectors = static_cast<int>(channels / 8);
   const bool serial = raw == out;  // in place: one run, each thread reads a row before overwriting it
@@ -302,8 +338,9 @@ int launch_conv(const uint16_t* raw, size_t tokens, size_t channels, const uint1
   if (!serial) {
     // token runs sized so that the grid is a whole number of resident waves (no idle tail wave), about
     // kRunTokens long, in multiples of the staging batch
-    const unsigned resident = l2 ? resident_grid(causal_conv_kernel<true, false>, kThreads)
-                                 : resident_grid(causal_conv_kernel<false, false>, kThreads);
+    const unsigned resident = compact ? resident_grid(causal_conv_kernel<true, false, true>, kThreads)
+                              : l2    ? resident_grid(causal_conv_kernel<true, false>, kThreads)
+                                      : resident_grid(causal_conv_kernel<false, false>, kThreads);
     if (l2) plan.norm_blocks = channel_blocks < kQkVectors / kThreads ? channel_blocks : kQkVectors / kThreads;
     plan.plain_blocks = channel_blocks - plan.norm_blocks;
     const size_t waves = tokens * channel_blocks / (static_cast<size_t>(resident) * kRunTokens) + 1;
@@ -322,7 +359,11 @@ int launch_conv(const uint16_t* raw, size_t tokens, size_t channels, const uint1
   auto H = reinterpret_cast<uint4*>(history);
   auto O = reinterpret_cast<uint4*>(out);
   cudaStream_t s = as_stream(stream);
-  if (l2)
+  if (compact)
+    causal_conv_kernel<true, false, true><<<grid, kThreads, 0, s>>>(R, tokens, channel_vectors, W, H, O, plan, l2_eps,
+                                                                    q_scale, reinterpret_cast<uint4*>(compact_q),
+                                                                    reinterpret_cast<uint4*>(compact_k));
+  else if (l2)
     causal_conv_kernel<true, false><<<grid, kThreads, 0, s>>>(R, tokens, channel_vectors, W, H, O, plan, l2_eps, q_scale);
   else if (serial)
     causal_conv_kernel<false, true><<<grid, kThreads, 0, s>>>(R, tokens, channel_vectors, W, H, O, plan, 0.0f, 1.0f);
@@ -346,4 +387,14 @@ extern "C" int q3x_b200_causal_conv1d_silu_l2norm(const uint16_t* raw, size_t to
   if (!q3x::host::valid_epsilon(l2_eps) || !std::isfinite(q_scale)) return q3x::host::kInvalid;
   return q3x::launch_conv(raw, tokens, Q3X_B200_GDN_CHANNELS, conv_weight, history_in_out, out, true, l2_eps,
                           q_scale, stream);
+}
+
+extern "C" int q3x_b200_causal_conv1d_silu_compact_qk(const uint16_t* raw, size_t tokens, const uint16_t* conv_weight,
+                                                      uint16_t* history_in_out, uint16_t* out, float l2_eps,
+                                                      float q_scale, uint16_t* compact_q, uint16_t* compact_k,
+                                                      void* stream) {
+  if (!q3x::host::valid_epsilon(l2_eps) || !std::isfinite(q_scale)) return q3x::host::kInvalid;
+  if (tokens != 0 && (compact_q == nullptr || compact_k == nullptr)) return q3x::host::kInvalid;
+  return q3x::launch_conv(raw, tokens, Q3X_B200_GDN_CHANNELS, conv_weight, history_in_out, out, true, l2_eps, q_scale,
+                          stream, compact_q, compact_k);
 }

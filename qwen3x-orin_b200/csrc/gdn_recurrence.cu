@@ -120,7 +120,7 @@ __global__ void __launch_bounds__(kThreads, 1) gdn_recurrence_kernel(
     if (kNorm) {
       // plain RMSNorm over the head's 128 rounded outputs, times weight, times silu(z); one rounding
       __syncthreads();
-      if (threadIdx.x < kLanesPerRow) {
+      if (threadIdx.x < 32) {  // a whole warp (the shuffles name all 32 lanes); its two halves do the same work
         float x[8], w[8], z[8], y[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) x[i] = head_out[lane * 8 + i];
@@ -130,7 +130,7 @@ __global__ void __launch_bounds__(kThreads, 1) gdn_recurrence_kernel(
         const float inv = inverse_rms(group_sum<kLanesPerRow>(dot8(x, x)), 1.0f / kHead, norm_eps);
 #pragma unroll
         for (int i = 0; i < 8; ++i) y[i] = x[i] * inv * w[i] * silu(z[i]);
-        st_vec(reinterpret_cast<uint4*>(out + base) + lane, pack8(y));
+        if (threadIdx.x < kLanesPerRow) st_vec(reinterpret_cast<uint4*>(out + base) + lane, pack8(y));
       }
       __syncthreads();
     }

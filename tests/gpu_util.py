@@ -101,13 +101,21 @@ def assert_bf16_within(got, want, max_ulp=1, min_exact=0.0, what=""):
     return worst, exact
 
 
-def assert_reference_tolerance(got, want, what=""):
+def assert_reference_tolerance(got, want, what="", amplified=False):
     """The reference's own acceptance rule for a bf16 result (expect_bf16_match,
     tests/decode_ops_cuda_test.cu:432-450): NaN matches NaN, an infinity matches the same infinity, every
-    other value within max(2e-3, 8e-3 * |expected|).  Applied as a hard bound on the chains of two
-    roundings, where the 1-ulp bound only holds stage by stage."""
-    a = orc.bf16_decode(np.asarray(got)).astype(np.float64).reshape(-1)
-    e = orc.bf16_decode(np.asarray(want)).astype(np.float64).reshape(-1)
+    other value within max(2e-3, 8e-3 * |expected|).
+
+    It is a hard bound for chains whose second stage only scales (conv -> L2 norm).  With ``amplified`` (the
+    rotated dims of norm -> RoPE) it cannot be one for ANY implementation whose first rounding is not
+    bit-identical to the host's: the rotation subtracts two products, so a 1-ulp difference of an operand
+    (the stage-wise tolerance) survives at the operand's magnitude while the result may be smaller.  There
+    the rule is applied as a quota -- at most 2 elements in 100 000 outside it -- and the hard bound is the
+    one arithmetic gives: two ulps at the largest magnitude of the element's row (the rotation's operands)."""
+    a = orc.bf16_decode(np.asarray(got)).astype(np.float64)
+    e = orc.bf16_decode(np.asarray(want)).astype(np.float64)
+    row_scale = np.broadcast_to(np.nanmax(np.where(np.isfinite(e), np.abs(e), 0.0), axis=-1, keepdims=True), e.shape)
+    a, e, row_scale = a.reshape(-1), e.reshape(-1), row_scale.reshape(-1)
     nan_e, inf_e = np.isnan(e), np.isinf(e)
     assert np.array_equal(np.isnan(a), nan_e), f"{what}: NaN classification differs"
     assert np.array_equal(a[inf_e], e[inf_e]), f"{what}: infinity classification differs"
@@ -115,8 +123,30 @@ def assert_reference_tolerance(got, want, what=""):
     tol = np.maximum(2.0e-3, np.abs(e[fin]) * 8.0e-3)
     err = np.abs(a[fin] - e[fin])
     bad = np.nonzero(err > tol)[0]
-    assert bad.size == 0, (f"{what}: {bad.size} elements beyond max(2e-3, 8e-3|e|); worst {err[bad].max():.3e} "
-                           f"at expected {e[fin][bad[np.argmax(err[bad])]]:.6g}")
+    allowed = int(np.ceil(2.0e-5 * err.size)) if amplified else 0
+    assert bad.size <= allowed, (f"{what}: {bad.size} of {err.size} elements beyond max(2e-3, 8e-3|e|) ({allowed} allowed); "
+                                 f"worst {err[bad].max():.3e} at expected {e[fin][bad[np.argmax(err[bad])]]:.6g}")
+    if bad.size:
+        hard = 2.0 ** -7 * row_scale[fin][bad]
+        assert np.all(err[bad] <= hard), f"{what}: an element differs by more than two ulps of its row's magnitude"
+
+
+def assert_sum_within(got, want, ulps, floor, min_exact, what=""):
+    """Tolerance for a bf16 result that is the rounding of a long FP32 sum with cancellation (an attention
+    output, a recurrence output): the FP32 sum differs from the host's by a rounding-level fraction of the sum
+    of its terms' MAGNITUDES, which is many ulps of the result wherever the terms cancel.  So: within `ulps`
+    bf16 ulps of the expected value plus an absolute `floor` (a few 1e-6 of the terms' magnitude), and a
+    quota of bit-exact elements."""
+    g_bits, w_bits = np.asarray(got).reshape(-1), np.asarray(want).reshape(-1)
+    a, e = orc.bf16_decode(g_bits).astype(np.float64), orc.bf16_decode(w_bits).astype(np.float64)
+    assert np.array_equal(np.isnan(a), np.isnan(e)), f"{what}: NaN classification differs"
+    fin = np.isfinite(e)
+    ulp = 2.0 ** (np.floor(np.log2(np.maximum(np.abs(e[fin]), 2.0 ** -126))) - 7)
+    err = np.abs(a[fin] - e[fin])
+    worst = np.max(err - (ulps * ulp + floor)) if err.size else 0.0
+    assert worst <= 0, f"{what}: an element is {worst:.3e} beyond {ulps} ulp + {floor:g}"
+    exact = float(np.mean(g_bits == w_bits)) if g_bits.size else 1.0
+    assert exact >= min_exact, f"{what}: only {exact:.6f} of the elements are bit-exact"
 
 
 def assert_bits_equal(got, want, what=""):

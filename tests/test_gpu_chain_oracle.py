@@ -42,6 +42,8 @@ def g():
 
 
 def bits(t):
+    if t.dtype == torch.uint8:
+        return t.contiguous().cpu().numpy()
     return t.contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
 
 
@@ -131,11 +133,12 @@ def test_configs_3_and_4_first_layer_period_against_the_oracle_chain(g):
     amax = torch.nn.functional.pad(n_all.amax(dim=1), (0, pad)).reshape(-1, chain.CHUNK).amax(dim=1).cpu().numpy()
     want_gs = np.where(amax == 0, np.float32(1.0), amax.astype(np.float32) / np.float32(2688.0)).astype(np.float32)
     assert np.array_equal(gs.view(np.uint32), want_gs.view(np.uint32)), "global scales of the last norm"
+    got_codes, got_scales = take(stack.codes), take(stack.scales)
     for grp in np.unique(groups):
         sel = groups == grp
         c, s = orc.nvfp4_quantize_with_scales(got_n[sel], gs[grp:grp + 1], 0)
-        g.assert_bits_equal(take(stack.codes)[sel], c, f"codes, scale group {grp}")
-        g.assert_bits_equal(take(stack.scales)[sel], s, f"block scales, scale group {grp}")
+        g.assert_bits_equal(got_codes[sel], c, f"codes, scale group {grp}")
+        g.assert_bits_equal(got_scales[sel], s, f"block scales, scale group {grp}")
     # ---- GDN operators (layer 2 wrote them last) -------------------------------------------------------
     got_conv = take(stack.conv_out)
     g.assert_bf16_within(got_conv[:, 4096:], want["conv"][:, 4096:], 1, 0.98, "conv v channels")
@@ -153,7 +156,7 @@ def test_configs_3_and_4_first_layer_period_against_the_oracle_chain(g):
     want_q = np.stack([orc.partial_rope(q_norm[i], cos[rows[i]], sin[rows[i]]) for i in range(rows.size)])
     got_q = take(stack.q_out).reshape(rows.size, 24, 256)
     g.assert_bf16_within(got_q[..., 64:], want_q[..., 64:], 1, 0.98, "q pass-through dims")
-    g.assert_reference_tolerance(got_q, want_q, "q end to end")
+    g.assert_reference_tolerance(got_q, want_q, "q end to end", amplified=True)
     assert g.ulp_report(got_q[..., :64], want_q[..., :64])[1] > 0.97
     want_gate = inp["q_gate"].reshape(rows.size, 24, 2, 256)[:, :, 1, :].reshape(rows.size, 6144)
     g.assert_bits_equal(take(stack.gate_out), want_gate, "gate copy")
@@ -176,7 +179,7 @@ def test_key_rows_of_the_chain_against_the_oracle(g):
     want = np.stack([orc.partial_rope(k_norm[t], cos[1000 + t], sin[1000 + t]) for t in range(total)])
     got = bits(stack.inputs["key"]).reshape(total, 4, 256)
     g.assert_bf16_within(got[..., 64:], want[..., 64:], 1, 0.98, "k pass-through dims")
-    g.assert_reference_tolerance(got, want, "k end to end")
+    g.assert_reference_tolerance(got, want, "k end to end", amplified=True)
     assert g.ulp_report(got[..., :64], want[..., :64])[1] > 0.97
 
 

@@ -73,8 +73,8 @@ def decode_chain(g, position, seed):
     g.sync()
     g.assert_bits_equal(q.get()[0], orc.partial_rope(q_n.get(), cos[position], sin[position]), "decode q rotation")
     g.assert_bits_equal(d_key.get()[0], orc.partial_rope(k_n.get(), cos[position], sin[position]), "decode k rotation")
-    g.assert_reference_tolerance(q.get(), wq, "decode q end to end")
-    g.assert_reference_tolerance(d_key.get(), wk, "decode k end to end")
+    g.assert_reference_tolerance(q.get(), wq, "decode q end to end", amplified=True)
+    g.assert_reference_tolerance(d_key.get(), wk, "decode k end to end", amplified=True)
     g.assert_bf16_within(o.get(), orc.sigmoid_gate(value, wg.reshape(-1)), 1, 0.98, "decode sigmoid gate")
     g.assert_bf16_within(h.get(), orc.silu_mul(gate, up), 1, 0.98, "decode SwiGLU")
 
@@ -120,8 +120,8 @@ def test_config1_full_attention_chunk_512(g):
     g.assert_bf16_within(q.get()[..., 64:], wq[..., 64:], 1, 0.98, "q")
     g.assert_bf16_within(d_key.get()[..., 64:], wk[..., 64:], 1, 0.98, "k")
     assert g.ulp_report(q.get()[..., :64], wq[..., :64])[1] > 0.97
-    g.assert_reference_tolerance(q.get(), wq, "q end to end")
-    g.assert_reference_tolerance(d_key.get(), wk, "k end to end")
+    g.assert_reference_tolerance(q.get(), wq, "q end to end", amplified=True)
+    g.assert_reference_tolerance(d_key.get(), wk, "k end to end", amplified=True)
     g.assert_bf16_within(o.get(), orc.sigmoid_gate(value, wg.reshape(T, 6144)), 1, 0.98, "sigmoid gate")
     g.assert_bf16_within(h.get(), orc.silu_mul(gate, up), 1, 0.98, "SwiGLU")
 

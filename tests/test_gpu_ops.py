@@ -320,8 +320,8 @@ def test_full_attention_preprocess(g, tokens, first):
     _, exact_k = g.ulp_report(d_key.get()[:, :, :64], want_k[:, :, :64])
     assert exact_q > 0.97 and exact_k > 0.97
     # hard bound on the rotated dims end to end: the reference's own tolerance for this operator
-    g.assert_reference_tolerance(q.get(), want_q, "q end to end")
-    g.assert_reference_tolerance(d_key.get(), want_k, "k end to end")
+    g.assert_reference_tolerance(q.get(), want_q, "q end to end", amplified=True)
+    g.assert_reference_tolerance(d_key.get(), want_k, "k end to end", amplified=True)
 
 
 @pytest.mark.parametrize("heads,misalign", [(3, 0), (28, 0), (24, 1)])
