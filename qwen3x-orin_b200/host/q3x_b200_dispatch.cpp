@@ -1,4 +1,12 @@
+// Definitions of the projection composites (see q3x_b200_dispatch.hpp): argument checks in the spirit of the
+// reference's validators (src/kernels/reference/projection_dispatch.cpp:483-622, 1434-1509 -- every weight
+// payload and scale valid, hidden size 5120 where the residual boundary is involved, no writable range
+// overlapping any other operand, everything rejected before the first enqueue), then the C ABI.
 #include "q3x_b200_dispatch.hpp"
+
+#include <cmath>
+#include <type_traits>
+#include <variant>
 
 #include "q3x_b200.h"
 
@@ -9,16 +17,211 @@ constexpr int kNotSupported = 801;  // cudaErrorNotSupported
 constexpr std::size_t kHidden = 5120U;
 
 // Invalid backend -> invalid value; a valid backend this library does not serve -> not supported.
-int route(const ProjectionBackend backend) noexcept {
-  if (!is_valid_projection_backend(backend)) return kInvalidValue;
-  return projection_backend_uses_b200_layer_ops(backend) ? 0 : kNotSupported;
+int route_half(const ProjectionBackend backend) noexcept {
+  if (!projection_backend_served_by_b200(backend)) return kInvalidValue;
+  return backend == kProjectionBackendB200LayerOps ? 0 : kNotSupported;
 }
+
+bool valid_scale(const float v) noexcept { return std::isfinite(v) && v >= 0.0F; }
+
+struct Shape {
+  std::size_t rows = 0U, cols = 0U;
+  const void* payload = nullptr;
+  std::size_t payload_bytes = 0U;
+  const void* scales = nullptr;
+  std::size_t scale_bytes = 0U;
+  bool valid = false;
+};
+
+// Shape and payload of a weight, with the reference's payload rules (projection_dispatch.cpp:646-690).
+Shape describe(const LinearWeight& weight) noexcept {
+  return std::visit(
+      [](const auto& w) noexcept -> Shape {
+        using W = std::decay_t<decltype(w)>;
+        Shape s;
+        s.rows = w.output_size;
+        s.cols = w.input_size;
+        if (s.rows == 0U || s.cols == 0U || s.rows > static_cast<std::size_t>(-1) / s.cols / 2U) return s;
+        if constexpr (std::is_same_v<W, Bf16LinearWeight>) {
+          s.payload = w.weight;
+          s.payload_bytes = s.rows * s.cols * 2U;
+          s.valid = w.weight != nullptr;
+        } else if constexpr (std::is_same_v<W, Fp8LinearWeight>) {
+          s.payload = w.weight;
+          s.payload_bytes = s.rows * s.cols;
+          s.valid = w.weight != nullptr && w.weight_scale_device != nullptr && w.input_scale_device != nullptr &&
+                    valid_scale(w.weight_scale) && valid_scale(w.input_scale);
+        } else {
+          s.payload = w.packed_weight;
+          s.payload_bytes = s.rows * s.cols / 2U;
+          s.scales = w.block_scale;
+          s.scale_bytes = s.rows * s.cols / 16U;
+          s.valid = w.packed_weight != nullptr && w.block_scale != nullptr && w.weight_scale_2_device != nullptr &&
+                    w.input_scale_device != nullptr && valid_scale(w.weight_scale_2) && valid_scale(w.input_scale) &&
+                    s.cols % 16U == 0U;
+        }
+        return s;
+      },
+      weight);
+}
+
+bool overlaps(const void* a, std::size_t a_bytes, const void* b, std::size_t b_bytes) noexcept {
+  if (a == nullptr || b == nullptr || a_bytes == 0U || b_bytes == 0U) return false;
+  const auto x = reinterpret_cast<std::uintptr_t>(a), y = reinterpret_cast<std::uintptr_t>(b);
+  return x < y + b_bytes && y < x + a_bytes;
+}
+// a writable range against a weight's payload and block scales
+bool touches_weight(const void* p, std::size_t bytes, const Shape& w) noexcept {
+  return overlaps(p, bytes, w.payload, w.payload_bytes) || overlaps(p, bytes, w.scales, w.scale_bytes);
+}
+
+// out[rows] = bf16(W x): the batch-one projection of any weight kind.
+int project(const LinearWeight& weight, const std::uint16_t* input, std::uint16_t* output, void* stream) noexcept {
+  return std::visit(
+      [&](const auto& w) noexcept -> int {
+        using W = std::decay_t<decltype(w)>;
+        if constexpr (std::is_same_v<W, Bf16LinearWeight>)
+          return q3x_b200_bf16_gemv(w.weight, input, w.output_size, w.input_size, nullptr, output, stream);
+        else if constexpr (std::is_same_v<W, Fp8LinearWeight>)
+          return q3x_b200_fp8_gemv(w.weight, w.weight_scale, input, w.output_size, w.input_size, nullptr, output, stream);
+        else
+          return q3x_b200_nvfp4_gemv(w.packed_weight, w.block_scale, w.weight_scale_2, input, w.output_size,
+                                     w.input_size, nullptr, output, stream);
+      },
+      weight);
+}
+
+// Shared checks of the gate / up pair: same input width, same output width, outputs disjoint from each
+// other, from the input and from both weights.
+int check_gate_up(const ProjectionBackend backend, const Shape& gate, const Shape& up, const std::uint16_t* input,
+                  const std::uint16_t* gate_output, const std::uint16_t* up_output) noexcept {
+  if (!projection_backend_served_by_b200(backend)) return kInvalidValue;
+  if (!gate.valid || !up.valid || gate.cols != up.cols || gate.rows != up.rows) return kInvalidValue;
+  if (input == nullptr || gate_output == nullptr || up_output == nullptr) return kInvalidValue;
+  const std::size_t out_bytes = gate.rows * 2U, in_bytes = gate.cols * 2U;
+  if (overlaps(gate_output, out_bytes, up_output, out_bytes) || overlaps(gate_output, out_bytes, input, in_bytes) ||
+      overlaps(up_output, out_bytes, input, in_bytes) || touches_weight(gate_output, out_bytes, gate) ||
+      touches_weight(gate_output, out_bytes, up) || touches_weight(up_output, out_bytes, gate) ||
+      touches_weight(up_output, out_bytes, up))
+    return kInvalidValue;
+  return 0;
+}
+
+int gate_up_silu(const LinearWeight& gate_weight, const LinearWeight& up_weight, const std::size_t rows,
+                 const std::uint16_t* input, std::uint16_t* gate_output, std::uint16_t* up_output,
+                 void* stream) noexcept {
+  int st = project(gate_weight, input, gate_output, stream);
+  if (st != 0) return st;
+  st = project(up_weight, input, up_output, stream);
+  if (st != 0) return st;
+  return q3x_b200_silu_mul(gate_output, up_output, rows, gate_output, stream);
+}
+
+int post_attention(const ProjectionBackend backend, const LinearWeight& gate_weight, const LinearWeight& up_weight,
+                   const std::uint16_t* residual_left, std::uint16_t* residual_right_and_normalized,
+                   const std::uint16_t* norm_weight, const float epsilon, std::uint16_t* residual_output,
+                   std::uint16_t* gate_output, std::uint16_t* up_output, void* stream) noexcept {
+  const Shape gate = describe(gate_weight), up = describe(up_weight);
+  if (const int st = check_gate_up(backend, gate, up, residual_right_and_normalized, gate_output, up_output); st != 0)
+    return st;
+  if (gate.cols != kHidden || residual_left == nullptr || norm_weight == nullptr || residual_output == nullptr ||
+      !(std::isfinite(epsilon) && epsilon > 0.0F))
+    return kInvalidValue;
+  const std::size_t hidden_bytes = kHidden * 2U, out_bytes = gate.rows * 2U;
+  if (overlaps(residual_output, hidden_bytes, gate_output, out_bytes) ||
+      overlaps(residual_output, hidden_bytes, up_output, out_bytes) ||
+      overlaps(residual_left, hidden_bytes, gate_output, out_bytes) ||
+      overlaps(residual_left, hidden_bytes, up_output, out_bytes) ||
+      overlaps(norm_weight, hidden_bytes, gate_output, out_bytes) ||
+      overlaps(norm_weight, hidden_bytes, up_output, out_bytes) ||
+      touches_weight(residual_output, hidden_bytes, gate) || touches_weight(residual_output, hidden_bytes, up) ||
+      touches_weight(residual_right_and_normalized, hidden_bytes, gate) ||
+      touches_weight(residual_right_and_normalized, hidden_bytes, up))
+    return kInvalidValue;
+  // residual add + centred norm: the normalised row replaces the right operand (its remaining alias rules
+  // are the fused operator's own)
+  const int st = q3x_b200_residual_add_rms_norm(residual_left, residual_right_and_normalized, norm_weight, 1U, kHidden,
+                                                epsilon, residual_output, residual_right_and_normalized, stream);
+  if (st != 0) return st;
+  return gate_up_silu(gate_weight, up_weight, gate.rows, residual_right_and_normalized, gate_output, up_output, stream);
+}
+
 }  // namespace
+
+int launch_projection_to_bf16_cuda(const ProjectionBackend backend, const LinearWeight& weight,
+                                   const std::uint16_t* input, float* /*fp32_scratch*/,
+                                   std::size_t /*scratch_elements*/, std::uint16_t* output, void* cuda_stream) noexcept {
+  // (the FP32 scratch of the reference's two-step path is not needed: the GEMV rounds its own result)
+  if (!projection_backend_served_by_b200(backend)) return kInvalidValue;
+  const Shape s = describe(weight);
+  if (!s.valid || input == nullptr || output == nullptr) return kInvalidValue;
+  if (overlaps(output, s.rows * 2U, input, s.cols * 2U) || touches_weight(output, s.rows * 2U, s)) return kInvalidValue;
+  return project(weight, input, output, cuda_stream);
+}
+
+int launch_mlp_gate_up_silu_to_bf16_cuda(const ProjectionBackend backend, const LinearWeight& gate_weight,
+                                         const LinearWeight& up_weight, const std::uint16_t* input,
+                                         float* /*fp32_scratch*/, std::size_t /*scratch_elements*/,
+                                         std::uint16_t* gate_output, std::uint16_t* up_output,
+                                         void* cuda_stream) noexcept {
+  const Shape gate = describe(gate_weight), up = describe(up_weight);
+  if (const int st = check_gate_up(backend, gate, up, input, gate_output, up_output); st != 0) return st;
+  return gate_up_silu(gate_weight, up_weight, gate.rows, input, gate_output, up_output, cuda_stream);
+}
+
+int launch_post_attention_residual_norm_mlp_gate_up_silu_to_bf16_cuda(
+    const ProjectionBackend backend, const LinearWeight& gate_weight, const LinearWeight& up_weight,
+    const std::uint16_t* residual_left, std::uint16_t* residual_right_and_normalized, const std::uint16_t* norm_weight,
+    const float epsilon, float* /*fp32_scratch*/, std::size_t /*scratch_elements*/, std::uint16_t* residual_output,
+    std::uint16_t* gate_output, std::uint16_t* up_output, void* cuda_stream) noexcept {
+  return post_attention(backend, gate_weight, up_weight, residual_left, residual_right_and_normalized, norm_weight,
+                        epsilon, residual_output, gate_output, up_output, cuda_stream);
+}
+
+int launch_decode_runner_post_attention_residual_norm_mlp_gate_up_silu_dead_up_to_bf16_cuda(
+    const ProjectionBackend backend, const LinearWeight& gate_weight, const LinearWeight& up_weight,
+    const std::uint16_t* residual_left, std::uint16_t* residual_right_and_normalized, const std::uint16_t* norm_weight,
+    const float epsilon, float* /*fp32_scratch*/, std::size_t /*scratch_elements*/, std::uint16_t* residual_output,
+    std::uint16_t* gate_output, std::uint16_t* up_workspace, void* cuda_stream) noexcept {
+  // same work: here the rounded up projection is written to up_workspace, which the caller treats as dead
+  return post_attention(backend, gate_weight, up_weight, residual_left, residual_right_and_normalized, norm_weight,
+                        epsilon, residual_output, gate_output, up_workspace, cuda_stream);
+}
+
+int launch_mlp_down_residual_norm_to_bf16_cuda(const ProjectionBackend backend, const LinearWeight& down_weight,
+                                               const std::uint16_t* activation, const std::uint16_t* residual_left,
+                                               const std::uint16_t* norm_weight, const float epsilon,
+                                               float* /*fp32_scratch*/, std::size_t /*scratch_elements*/,
+                                               std::uint16_t* raw_down_output, std::uint16_t* residual_output,
+                                               std::uint16_t* normalized_output, void* cuda_stream) noexcept {
+  if (!projection_backend_served_by_b200(backend)) return kInvalidValue;
+  const Shape down = describe(down_weight);
+  if (!down.valid || down.rows != kHidden || activation == nullptr || residual_left == nullptr ||
+      norm_weight == nullptr || raw_down_output == nullptr || residual_output == nullptr ||
+      normalized_output == nullptr || !(std::isfinite(epsilon) && epsilon > 0.0F))
+    return kInvalidValue;
+  // three distinct output boundaries (model_weights.h:977-988); no writable range overlaps any other operand
+  const std::size_t hidden_bytes = kHidden * 2U, in_bytes = down.cols * 2U;
+  std::uint16_t* const outs[] = {raw_down_output, residual_output, normalized_output};
+  for (int i = 0; i < 3; ++i) {
+    for (int j = i + 1; j < 3; ++j)
+      if (overlaps(outs[i], hidden_bytes, outs[j], hidden_bytes)) return kInvalidValue;
+    if (overlaps(outs[i], hidden_bytes, activation, in_bytes) || overlaps(outs[i], hidden_bytes, residual_left, hidden_bytes) ||
+        overlaps(outs[i], hidden_bytes, norm_weight, hidden_bytes) || touches_weight(outs[i], hidden_bytes, down))
+      return kInvalidValue;
+  }
+  const int st = project(down_weight, activation, raw_down_output, cuda_stream);
+  if (st != 0) return st;
+  return q3x_b200_residual_add_rms_norm(residual_left, raw_down_output, norm_weight, 1U, kHidden, epsilon, residual_output,
+                                        normalized_output, cuda_stream);
+}
+
+// ---- the elementwise halves ----------------------------------------------------------------------------
 
 int launch_mlp_gate_up_silu_epilogue_cuda(const ProjectionBackend backend, std::uint16_t* gate_output,
                                           const std::uint16_t* up_output, const std::size_t token_count,
                                           const std::size_t intermediate_size, void* cuda_stream) noexcept {
-  if (const int r = route(backend); r != 0) return r;
+  if (const int r = route_half(backend); r != 0) return r;
   if (intermediate_size != 0U && token_count > static_cast<std::size_t>(-1) / intermediate_size) return kInvalidValue;
   return q3x_b200_silu_mul(gate_output, up_output, token_count * intermediate_size, gate_output, cuda_stream);
 }
@@ -29,7 +232,7 @@ int launch_post_attention_residual_norm_prologue_cuda(const ProjectionBackend ba
                                                       const std::uint16_t* norm_weight, const float epsilon,
                                                       const std::size_t token_count, const std::size_t hidden_size,
                                                       std::uint16_t* residual_output, void* cuda_stream) noexcept {
-  if (const int r = route(backend); r != 0) return r;
+  if (const int r = route_half(backend); r != 0) return r;
   if (hidden_size != kHidden || token_count == 0U) return kInvalidValue;  // projection_dispatch.cpp:483-534
   return q3x_b200_residual_add_rms_norm(residual_left, residual_right_and_normalized, norm_weight, token_count,
                                         hidden_size, epsilon, residual_output, residual_right_and_normalized,
@@ -41,7 +244,7 @@ int launch_mlp_down_residual_norm_epilogue_cuda(const ProjectionBackend backend,
                                                 const float epsilon, const std::size_t token_count,
                                                 const std::size_t hidden_size, std::uint16_t* residual_output,
                                                 std::uint16_t* normalized_output, void* cuda_stream) noexcept {
-  if (const int r = route(backend); r != 0) return r;
+  if (const int r = route_half(backend); r != 0) return r;
   // three distinct boundaries (model_weights.h:977-983): raw down stays observable
   if (hidden_size != kHidden || token_count == 0U || normalized_output == nullptr ||
       normalized_output == raw_down_output)

@@ -184,7 +184,122 @@ int launch_causal_conv1d_silu_update_tile_reference_cuda(const std::uint16_t* ra
   return q3x_b200_causal_conv1d_silu(raw, tokens, kGdnQkvChannels, weight, history, out, stream);
 }
 
+// ---- decode attention, softmax, argmax ------------------------------------------------------------------
+
+int launch_softmax_reference_cuda(const float* input, std::size_t rows, std::size_t columns, float* output,
+                                  void* stream) noexcept {
+  return q3x_b200_softmax(input, rows, columns, output, stream);
+}
+
+std::size_t gqa_attention_splitkv_sigmoid_gate_24_4_256_workspace_elements(std::size_t sequence_length) noexcept {
+  if (sequence_length <= kFusedGqaMaximumSequenceLength || sequence_length > kDecodeGqaSplitKvMaximumSequenceLength)
+    return 0U;  // outside the entry point's range there is nothing to size
+  return q3x_b200_gqa_decode_workspace_floats(sequence_length);
+}
+
+int launch_gqa_attention_splitkv_sigmoid_gate_24_4_256_cuda(const std::uint16_t* query, const std::uint16_t* key_cache,
+                                                            const std::uint16_t* value_cache,
+                                                            std::size_t sequence_length, float attention_scale,
+                                                            float* workspace, std::size_t workspace_elements,
+                                                            const std::uint16_t* gate, std::uint16_t* output,
+                                                            void* stream) noexcept {
+  // the reference admits (64, 4096] here and requires the gate (decode_ops.h:405-410)
+  if (sequence_length <= kFusedGqaMaximumSequenceLength || sequence_length > kDecodeGqaSplitKvMaximumSequenceLength ||
+      gate == nullptr)
+    return kInvalidValue;
+  return q3x_b200_gqa_attention_decode_sigmoid_gate(query, key_cache, value_cache, sequence_length, attention_scale,
+                                                    workspace, workspace_elements, gate, output, stream);
+}
+
+int launch_bf16_greedy_argmax_cuda(const std::uint16_t* input, std::size_t element_count,
+                                   Bf16GreedyArgmaxResult* result_workspace, void* stream) noexcept {
+  return q3x_b200_bf16_greedy_argmax(input, element_count, result_workspace, stream);
+}
+
+// ---- gated-delta-net recurrence ----------------------------------------------------------------------------
+
+bool supports_gated_delta_net_update_plain_rms_norm_silu_gate_fusion(std::size_t token_count, GdnDimensions dimensions,
+                                                                     std::size_t norm_head_count,
+                                                                     std::size_t norm_head_dimension) noexcept {
+  return token_count == 1U && default_gdn(dimensions) && norm_head_count == kGdnValueHeadCount &&
+         norm_head_dimension == kGdnHeadDimension;
+}
+
+int launch_gated_delta_net_update_reference_cuda(const std::uint16_t* conv_qkv, const std::uint16_t* a,
+                                                 const std::uint16_t* b, const std::uint16_t* A_log,
+                                                 const std::uint16_t* dt_bias, const std::uint16_t* state_input,
+                                                 std::uint16_t* state_output, float l2_epsilon, std::uint16_t* output,
+                                                 GdnDimensions dimensions, void* stream) noexcept {
+  if (!default_gdn(dimensions)) return kInvalidValue;
+  return q3x_b200_gated_delta_net_update(conv_qkv, 1U, a, b, A_log, dt_bias, state_input, state_output, l2_epsilon,
+                                         output, stream);
+}
+
+int launch_gated_delta_net_update_tile_reference_cuda(const std::uint16_t* conv_qkv, std::size_t token_count,
+                                                      const std::uint16_t* a, const std::uint16_t* b,
+                                                      const std::uint16_t* A_log, const std::uint16_t* dt_bias,
+                                                      const std::uint16_t* state_input, std::uint16_t* state_output,
+                                                      float l2_epsilon, std::uint16_t* output, GdnDimensions dimensions,
+                                                      void* stream) noexcept {
+  if (!default_gdn(dimensions) || token_count == 0U || token_count > kGdnMaximumTileTokenCount) return kInvalidValue;
+  return q3x_b200_gated_delta_net_update(conv_qkv, token_count, a, b, A_log, dt_bias, state_input, state_output,
+                                         l2_epsilon, output, stream);
+}
+
+int launch_gated_delta_net_update_warp_parallel_cuda(const std::uint16_t* conv_qkv, const std::uint16_t* a,
+                                                     const std::uint16_t* b, const std::uint16_t* A_log,
+                                                     const std::uint16_t* dt_bias, const std::uint16_t* state_input,
+                                                     std::uint16_t* state_output, float l2_epsilon,
+                                                     std::uint16_t* output, GdnDimensions dimensions,
+                                                     void* stream) noexcept {
+  return launch_gated_delta_net_update_reference_cuda(conv_qkv, a, b, A_log, dt_bias, state_input, state_output,
+                                                      l2_epsilon, output, dimensions, stream);
+}
+
+int launch_gated_delta_net_update_tile_warp_parallel_cuda(const std::uint16_t* conv_qkv, std::size_t token_count,
+                                                          const std::uint16_t* a, const std::uint16_t* b,
+                                                          const std::uint16_t* A_log, const std::uint16_t* dt_bias,
+                                                          const std::uint16_t* state_input,
+                                                          std::uint16_t* state_output, float l2_epsilon,
+                                                          std::uint16_t* output, GdnDimensions dimensions,
+                                                          void* stream) noexcept {
+  return launch_gated_delta_net_update_tile_reference_cuda(conv_qkv, token_count, a, b, A_log, dt_bias, state_input,
+                                                           state_output, l2_epsilon, output, dimensions, stream);
+}
+
+int launch_gated_delta_net_update_plain_rms_norm_silu_gate_cuda(
+    const std::uint16_t* conv_qkv, const std::uint16_t* a, const std::uint16_t* b, const std::uint16_t* A_log,
+    const std::uint16_t* dt_bias, const std::uint16_t* state_input, std::uint16_t* state_output, float l2_epsilon,
+    const std::uint16_t* norm_weight, const std::uint16_t* silu_gate, std::size_t norm_head_count,
+    std::size_t norm_head_dimension, float norm_epsilon, std::uint16_t* output, GdnDimensions dimensions,
+    void* stream) noexcept {
+  if (!default_gdn(dimensions) || norm_head_count == 0U || norm_head_dimension == 0U ||
+      norm_head_count > kGdnValueHeadCount * kGdnHeadDimension ||
+      norm_head_count * norm_head_dimension != kGdnValueHeadCount * kGdnHeadDimension)
+    return kInvalidValue;
+  if (supports_gated_delta_net_update_plain_rms_norm_silu_gate_fusion(1U, dimensions, norm_head_count,
+                                                                      norm_head_dimension))
+    return q3x_b200_gated_delta_net_update_rms_norm_silu_gate(conv_qkv, 1U, a, b, A_log, dt_bias, state_input,
+                                                              state_output, l2_epsilon, norm_weight, silu_gate,
+                                                              norm_epsilon, output, stream);
+  // any other norm partition of the 6144 outputs: the recurrence, then the gated norm in place (gdn_decode.h:171-178)
+  const int st = q3x_b200_gated_delta_net_update(conv_qkv, 1U, a, b, A_log, dt_bias, state_input, state_output,
+                                                 l2_epsilon, output, stream);
+  if (st != 0) return st;
+  return q3x_b200_rms_norm_silu_gate(output, norm_weight, silu_gate, norm_head_count, norm_head_dimension, norm_epsilon,
+                                     output, stream);
+}
+
 namespace gdn_prefill_whole_span_conv_detail {
+
+int launch_causal_conv1d_silu_update_token_parallel_compact_qk_exact_cuda(
+    const std::uint16_t* raw, std::size_t tokens, const std::uint16_t* weight, std::uint16_t* history,
+    std::uint16_t* out, float l2_epsilon, std::uint16_t* compact_q, std::uint16_t* compact_k, void* stream) noexcept {
+  if (tokens == 0U || tokens > kMaximumTokenCount || raw == out) return kInvalidValue;
+  // q carries the extra 1 / sqrt(128) in this layout (gdn_prefill_whole_span_conv_sm87.cu:355-357)
+  return q3x_b200_causal_conv1d_silu_compact_qk(raw, tokens, weight, history, out, l2_epsilon, 0.08838834764831845F,
+                                                compact_q, compact_k, stream);
+}
 
 int launch_causal_conv1d_silu_update_whole_span_exact_cuda(const std::uint16_t* raw, std::size_t tokens,
                                                            const std::uint16_t* weight, std::uint16_t* history,
@@ -203,3 +318,30 @@ int launch_causal_conv1d_silu_update_token_parallel_exact_cuda(const std::uint16
 
 }  // namespace gdn_prefill_whole_span_conv_detail
 }  // namespace q3x::runtime
+
+namespace q3x::kernels {
+
+int launch_bf16_gemv_reference_cuda(const std::uint16_t* weights, const std::uint16_t* activation, std::size_t rows,
+                                    std::size_t columns, float* output, void* stream) noexcept {
+  if (rows != 0U && columns != 0U && output == nullptr) return 1;
+  return q3x_b200_bf16_gemv(weights, activation, rows, columns, output, nullptr, stream);
+}
+int launch_bf16_gemv_bf16_cuda(const std::uint16_t* weights, const std::uint16_t* activation, std::size_t rows,
+                               std::size_t columns, std::uint16_t* output, void* stream) noexcept {
+  if (rows != 0U && columns != 0U && output == nullptr) return 1;
+  return q3x_b200_bf16_gemv(weights, activation, rows, columns, nullptr, output, stream);
+}
+int launch_fp8_gemv_reference_cuda(const std::uint8_t* weights, float weight_scale, const std::uint16_t* activation,
+                                   std::size_t rows, std::size_t columns, float* output, void* stream) noexcept {
+  if (rows != 0U && columns != 0U && output == nullptr) return 1;
+  return q3x_b200_fp8_gemv(weights, weight_scale, activation, rows, columns, output, nullptr, stream);
+}
+int launch_nvfp4_gemv_reference_cuda(const std::uint8_t* packed_weights, const std::uint8_t* block_scales,
+                                     float weight_scale_2, const std::uint16_t* activation, std::size_t rows,
+                                     std::size_t columns, float* output, void* stream) noexcept {
+  if (rows != 0U && columns != 0U && output == nullptr) return 1;
+  return q3x_b200_nvfp4_gemv(packed_weights, block_scales, weight_scale_2, activation, rows, columns, output, nullptr,
+                             stream);
+}
+
+}  // namespace q3x::kernels

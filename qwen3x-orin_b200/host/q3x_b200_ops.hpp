@@ -28,6 +28,18 @@ inline constexpr std::size_t kFullAttentionPreprocessPromptWideP8000PanelCount =
 inline constexpr std::size_t kResidualNormPrefillMaximumTokens = 512U;  // decode_ops.cu:1913-1953
 inline constexpr std::size_t kResidualNormHiddenSize = 5'120U;
 
+inline constexpr std::size_t kFusedGqaMaximumSequenceLength = 64U;            // decode_ops.h:10
+inline constexpr std::size_t kDecodeGqaSplitKvMaximumSequenceLength = 4'096U;  // decode_ops.h:11
+
+// decode_ops.h:61-69
+struct Bf16GreedyArgmaxResult {
+  std::uint32_t index = 0U;
+  std::uint16_t value_bits = 0U;
+  std::uint16_t has_nonfinite = 0U;
+};
+static_assert(sizeof(Bf16GreedyArgmaxResult) == 8U);
+inline constexpr std::size_t kBf16GreedyArgmaxWorkspaceResults = 33U;
+
 inline constexpr std::size_t kGdnQkHeadCount = 16U;
 inline constexpr std::size_t kGdnValueHeadCount = 48U;
 inline constexpr std::size_t kGdnHeadDimension = 128U;
@@ -138,6 +150,19 @@ struct GdnDimensions {
     const float* cosines, const float* sines, std::size_t first_position, std::size_t token_count,
     void* cuda_stream = nullptr) noexcept;
 
+[[nodiscard]] int launch_softmax_reference_cuda(const float* input, std::size_t rows, std::size_t columns,
+                                                float* output, void* cuda_stream = nullptr) noexcept;
+// decode_ops.h:397-423: sequence_length in (64, 4096]
+[[nodiscard]] std::size_t gqa_attention_splitkv_sigmoid_gate_24_4_256_workspace_elements(
+    std::size_t sequence_length) noexcept;
+[[nodiscard]] int launch_gqa_attention_splitkv_sigmoid_gate_24_4_256_cuda(
+    const std::uint16_t* query, const std::uint16_t* key_cache, const std::uint16_t* value_cache,
+    std::size_t sequence_length, float attention_scale, float* workspace, std::size_t workspace_elements,
+    const std::uint16_t* gate, std::uint16_t* output, void* cuda_stream = nullptr) noexcept;
+[[nodiscard]] int launch_bf16_greedy_argmax_cuda(const std::uint16_t* input, std::size_t element_count,
+                                                 Bf16GreedyArgmaxResult* result_workspace,
+                                                 void* cuda_stream = nullptr) noexcept;
+
 // ---- layout_ops.h -------------------------------------------------------------------------------
 [[nodiscard]] int launch_split_interleaved_q_gate_reference_cuda(const std::uint16_t* input, std::size_t head_count,
                                                                  std::size_t head_dimension,
@@ -157,8 +182,42 @@ struct GdnDimensions {
     std::uint16_t* history_in_out, std::uint16_t* conv_qkv_output, GdnDimensions dimensions = {},
     void* cuda_stream = nullptr) noexcept;
 
+// ---- gdn_decode.h (recurrence launchers, :85-188) ----------------------------------------------------------
+[[nodiscard]] bool supports_gated_delta_net_update_plain_rms_norm_silu_gate_fusion(
+    std::size_t token_count, GdnDimensions dimensions, std::size_t norm_head_count,
+    std::size_t norm_head_dimension) noexcept;
+[[nodiscard]] int launch_gated_delta_net_update_reference_cuda(
+    const std::uint16_t* conv_qkv, const std::uint16_t* a, const std::uint16_t* b, const std::uint16_t* A_log,
+    const std::uint16_t* dt_bias, const std::uint16_t* state_input, std::uint16_t* state_output, float l2_epsilon,
+    std::uint16_t* output, GdnDimensions dimensions = {}, void* cuda_stream = nullptr) noexcept;
+[[nodiscard]] int launch_gated_delta_net_update_tile_reference_cuda(
+    const std::uint16_t* conv_qkv, std::size_t token_count, const std::uint16_t* a, const std::uint16_t* b,
+    const std::uint16_t* A_log, const std::uint16_t* dt_bias, const std::uint16_t* state_input,
+    std::uint16_t* state_output, float l2_epsilon, std::uint16_t* output, GdnDimensions dimensions = {},
+    void* cuda_stream = nullptr) noexcept;
+[[nodiscard]] int launch_gated_delta_net_update_warp_parallel_cuda(
+    const std::uint16_t* conv_qkv, const std::uint16_t* a, const std::uint16_t* b, const std::uint16_t* A_log,
+    const std::uint16_t* dt_bias, const std::uint16_t* state_input, std::uint16_t* state_output, float l2_epsilon,
+    std::uint16_t* output, GdnDimensions dimensions = {}, void* cuda_stream = nullptr) noexcept;
+[[nodiscard]] int launch_gated_delta_net_update_tile_warp_parallel_cuda(
+    const std::uint16_t* conv_qkv, std::size_t token_count, const std::uint16_t* a, const std::uint16_t* b,
+    const std::uint16_t* A_log, const std::uint16_t* dt_bias, const std::uint16_t* state_input,
+    std::uint16_t* state_output, float l2_epsilon, std::uint16_t* output, GdnDimensions dimensions = {},
+    void* cuda_stream = nullptr) noexcept;
+[[nodiscard]] int launch_gated_delta_net_update_plain_rms_norm_silu_gate_cuda(
+    const std::uint16_t* conv_qkv, const std::uint16_t* a, const std::uint16_t* b, const std::uint16_t* A_log,
+    const std::uint16_t* dt_bias, const std::uint16_t* state_input, std::uint16_t* state_output, float l2_epsilon,
+    const std::uint16_t* norm_weight, const std::uint16_t* silu_gate, std::size_t norm_head_count,
+    std::size_t norm_head_dimension, float norm_epsilon, std::uint16_t* output, GdnDimensions dimensions = {},
+    void* cuda_stream = nullptr) noexcept;
+
 namespace gdn_prefill_whole_span_conv_detail {
 inline constexpr std::size_t kMaximumTokenCount = 512U;
+// src/kernels/reference/gdn_prefill_whole_span_conv_sm87.h:59-67
+[[nodiscard]] int launch_causal_conv1d_silu_update_token_parallel_compact_qk_exact_cuda(
+    const std::uint16_t* raw_qkv, std::size_t token_count, const std::uint16_t* conv_weight,
+    std::uint16_t* history_in_out, std::uint16_t* conv_qkv_output, float l2_epsilon, std::uint16_t* compact_q,
+    std::uint16_t* compact_k, void* cuda_stream = nullptr) noexcept;
 [[nodiscard]] int launch_causal_conv1d_silu_update_whole_span_exact_cuda(
     const std::uint16_t* raw_qkv, std::size_t token_count, const std::uint16_t* conv_weight,
     std::uint16_t* history_in_out, std::uint16_t* conv_qkv_output, void* cuda_stream = nullptr) noexcept;
@@ -168,6 +227,25 @@ inline constexpr std::size_t kMaximumTokenCount = 512U;
 }  // namespace gdn_prefill_whole_span_conv_detail
 
 }  // namespace q3x::runtime
+
+// ---- include/q3x/kernels/reference_gemv.h:64-130: the batch-one projection launchers ------------------------
+namespace q3x::kernels {
+[[nodiscard]] int launch_bf16_gemv_reference_cuda(const std::uint16_t* weights, const std::uint16_t* activation,
+                                                  std::size_t rows, std::size_t columns, float* output,
+                                                  void* cuda_stream = nullptr) noexcept;
+[[nodiscard]] int launch_bf16_gemv_bf16_cuda(const std::uint16_t* weights, const std::uint16_t* activation,
+                                             std::size_t rows, std::size_t columns, std::uint16_t* output,
+                                             void* cuda_stream = nullptr) noexcept;
+[[nodiscard]] int launch_fp8_gemv_reference_cuda(const std::uint8_t* weights, float weight_scale,
+                                                 const std::uint16_t* activation, std::size_t rows,
+                                                 std::size_t columns, float* output,
+                                                 void* cuda_stream = nullptr) noexcept;
+[[nodiscard]] int launch_nvfp4_gemv_reference_cuda(const std::uint8_t* packed_weights,
+                                                   const std::uint8_t* block_scales, float weight_scale_2,
+                                                   const std::uint16_t* activation, std::size_t rows,
+                                                   std::size_t columns, float* output,
+                                                   void* cuda_stream = nullptr) noexcept;
+}  // namespace q3x::kernels
 
 #include "q3x_b200_dispatch.hpp"
 #include "q3x_b200_prefill_bindings.hpp"

@@ -260,6 +260,127 @@ static void test_dispatch_halves(cudaStream_t s) {
   EXPECT(same(res1, res2) && same(n1, n2));
 }
 
+// The projection composites with real weights: outputs must equal the GEMV + fused-operator sequence requested
+// from the C ABI, for the three weight kinds.
+static std::vector<std::uint8_t> random_bytes(std::size_t n, std::uint8_t lo, std::uint8_t hi) {
+  std::vector<std::uint8_t> v(n);
+  for (auto& x : v) x = static_cast<std::uint8_t>(lo + static_cast<unsigned>(uniform() * (hi - lo)));
+  return v;
+}
+
+static void test_composites(cudaStream_t s) {
+  const float eps = 1e-6f;
+  const std::size_t hidden = 5120, inter = 1024;  // a narrow MLP keeps the test quick; hidden is the model's
+  DeviceBuffer<float> dev_scalar(std::vector<float>{0.01f});
+  // NVFP4 gate / up [inter, hidden], bf16 down [hidden, inter]
+  DeviceBuffer<std::uint8_t> gate_w(random_bytes(inter * hidden / 2, 0, 255)), up_w(random_bytes(inter * hidden / 2, 0, 255));
+  DeviceBuffer<std::uint8_t> gate_s(random_bytes(inter * hidden / 16, 0x20, 0x48)), up_s(random_bytes(inter * hidden / 16, 0x20, 0x48));
+  rt::NvFp4LinearWeight gate{}, up{};
+  gate.packed_weight = gate_w.p; gate.block_scale = gate_s.p; gate.weight_scale_2_device = dev_scalar.p;
+  gate.input_scale_device = dev_scalar.p; gate.weight_scale_2 = 0.01f; gate.input_scale = 1.0f;
+  gate.output_size = inter; gate.input_size = hidden;
+  up = gate; up.packed_weight = up_w.p; up.block_scale = up_s.p;
+  const rt::LinearWeight gate_lw = gate, up_lw = up;
+  Bf16 left(random_bf16(hidden, 1.0f)), w(random_bf16(hidden, 0.02f));
+  const auto right_host = random_bf16(hidden, 1.0f);
+  Bf16 ra(right_host), rb(right_host), res1(hidden), res2(hidden);
+  Bf16 g1(inter), u1(inter), g2(inter), u2(inter);
+  EXPECT(rt::launch_post_attention_residual_norm_mlp_gate_up_silu_to_bf16_cuda(
+             rt::ProjectionBackend::kSm87WeightOnly, gate_lw, up_lw, left.p, ra.p, w.p, eps, nullptr, 0, res1.p, g1.p, u1.p,
+             s) == 0);
+  EXPECT(q3x_b200_residual_add_rms_norm(left.p, rb.p, w.p, 1, hidden, eps, res2.p, rb.p, s) == 0);
+  EXPECT(q3x_b200_nvfp4_gemv(gate_w.p, gate_s.p, 0.01f, rb.p, inter, hidden, nullptr, g2.p, s) == 0);
+  EXPECT(q3x_b200_nvfp4_gemv(up_w.p, up_s.p, 0.01f, rb.p, inter, hidden, nullptr, u2.p, s) == 0);
+  EXPECT(q3x_b200_silu_mul(g2.p, u2.p, inter, g2.p, s) == 0);
+  EXPECT(same(res1, res2) && same(ra, rb) && same(g1, g2) && same(u1, u2) && written(g1));
+  // the decode-runner twin and the plain gate / up composite give the same gate output
+  Bf16 rc(right_host), res3(hidden), g3(inter), u3(inter), g4(inter), u4(inter);
+  EXPECT(rt::launch_decode_runner_post_attention_residual_norm_mlp_gate_up_silu_dead_up_to_bf16_cuda(
+             rt::kProjectionBackendB200LayerOps, gate_lw, up_lw, left.p, rc.p, w.p, eps, nullptr, 0, res3.p, g3.p, u3.p, s) == 0);
+  EXPECT(rt::launch_mlp_gate_up_silu_to_bf16_cuda(rt::ProjectionBackend::kReference, gate_lw, up_lw, rb.p, nullptr, 0, g4.p,
+                                                  u4.p, s) == 0);
+  EXPECT(same(g3, g1) && same(res3, res1) && same(g4, g1) && same(u4, u1));
+  // down projection (bf16 weights) + residual + norm: three distinct boundaries
+  Bf16 down_w(random_bf16(hidden * inter, 0.03f));
+  rt::Bf16LinearWeight down{};
+  down.weight = down_w.p; down.output_size = hidden; down.input_size = inter;
+  const rt::LinearWeight down_lw = down;
+  Bf16 raw1(hidden), r1(hidden), n1(hidden), raw2(hidden), r2(hidden), n2(hidden);
+  EXPECT(rt::launch_mlp_down_residual_norm_to_bf16_cuda(rt::ProjectionBackend::kReference, down_lw, g1.p, left.p, w.p, eps,
+                                                        nullptr, 0, raw1.p, r1.p, n1.p, s) == 0);
+  EXPECT(q3x_b200_bf16_gemv(down_w.p, g1.p, hidden, inter, nullptr, raw2.p, s) == 0);
+  EXPECT(q3x_b200_residual_add_rms_norm(left.p, raw2.p, w.p, 1, hidden, eps, r2.p, n2.p, s) == 0);
+  EXPECT(same(raw1, raw2) && same(r1, r2) && same(n1, n2) && written(n1));
+  // FP8 weights through the single projection entry
+  DeviceBuffer<std::uint8_t> fp8_w(random_bytes(inter * hidden, 0x10, 0x60));
+  rt::Fp8LinearWeight f8{};
+  f8.weight = fp8_w.p; f8.weight_scale_device = dev_scalar.p; f8.input_scale_device = dev_scalar.p;
+  f8.weight_scale = 0.02f; f8.input_scale = 1.0f; f8.output_size = inter; f8.input_size = hidden;
+  const rt::LinearWeight f8_lw = f8;
+  Bf16 p1(inter), p2(inter);
+  EXPECT(rt::launch_projection_to_bf16_cuda(rt::ProjectionBackend::kSm87WeightOnly, f8_lw, left.p, nullptr, 0, p1.p, s) == 0);
+  EXPECT(q3x_b200_fp8_gemv(fp8_w.p, 0.02f, left.p, inter, hidden, nullptr, p2.p, s) == 0);
+  EXPECT(same(p1, p2) && written(p1));
+  // rejections, all before any enqueue
+  constexpr int kInvalid = 1;
+  EXPECT(rt::launch_projection_to_bf16_cuda(static_cast<rt::ProjectionBackend>(9), f8_lw, left.p, nullptr, 0, p1.p, s) == kInvalid);
+  EXPECT(rt::launch_projection_to_bf16_cuda(rt::ProjectionBackend::kReference, f8_lw, left.p, nullptr, 0, left.p, s) == kInvalid);
+  rt::NvFp4LinearWeight broken = gate;
+  broken.block_scale = nullptr;
+  EXPECT(rt::launch_mlp_gate_up_silu_to_bf16_cuda(rt::ProjectionBackend::kReference, rt::LinearWeight{broken}, up_lw, rb.p,
+                                                  nullptr, 0, g4.p, u4.p, s) == kInvalid);
+  EXPECT(rt::launch_mlp_gate_up_silu_to_bf16_cuda(rt::ProjectionBackend::kReference, gate_lw, up_lw, rb.p, nullptr, 0, g4.p,
+                                                  g4.p, s) == kInvalid);  // gate and up outputs alias
+  EXPECT(rt::launch_mlp_down_residual_norm_to_bf16_cuda(rt::ProjectionBackend::kReference, down_lw, g1.p, left.p, w.p, eps,
+                                                        nullptr, 0, raw1.p, raw1.p, n1.p, s) == kInvalid);
+  EXPECT(rt::launch_mlp_down_residual_norm_to_bf16_cuda(rt::ProjectionBackend::kReference, gate_lw, g1.p, left.p, w.p, eps,
+                                                        nullptr, 0, raw1.p, r1.p, n1.p, s) == kInvalid);  // rows != 5120
+}
+
+// The launchers of the operators between the fused layer ops, through their q3x::runtime / q3x::kernels names.
+static void test_core_launchers(cudaStream_t s) {
+  const float eps = 1e-6f;
+  Bf16 conv(random_bf16(16 * 10240, 1.0f)), a(random_bf16(16 * 48, 1.0f)), b(random_bf16(16 * 48, 1.0f)),
+      A_log(random_bf16(48, 1.0f)), dt(random_bf16(48, 1.0f));
+  const auto state_host = random_bf16(48 * 128 * 128, 0.05f);
+  Bf16 s1(state_host), s2(state_host), o1(16 * 6144), o2(16 * 6144);
+  EXPECT(rt::launch_gated_delta_net_update_tile_reference_cuda(conv.p, 16, a.p, b.p, A_log.p, dt.p, s1.p, s1.p, eps, o1.p,
+                                                               rt::GdnDimensions{}, s) == 0);
+  EXPECT(q3x_b200_gated_delta_net_update(conv.p, 16, a.p, b.p, A_log.p, dt.p, s2.p, s2.p, eps, o2.p, s) == 0);
+  EXPECT(same(s1, s2) && same(o1, o2) && written(o1));
+  EXPECT(rt::launch_gated_delta_net_update_tile_reference_cuda(conv.p, 17, a.p, b.p, A_log.p, dt.p, s1.p, s1.p, eps, o1.p,
+                                                               rt::GdnDimensions{}, s) == 1);
+  Bf16 z(random_bf16(6144, 1.0f)), nw(random_bf16(128, 1.0f)), f1(6144), f2(6144), s3(state_host), s4(state_host);
+  EXPECT(rt::launch_gated_delta_net_update_plain_rms_norm_silu_gate_cuda(conv.p, a.p, b.p, A_log.p, dt.p, s3.p, s3.p, eps, nw.p,
+                                                                         z.p, 48, 128, eps, f1.p, rt::GdnDimensions{}, s) == 0);
+  EXPECT(q3x_b200_gated_delta_net_update_rms_norm_silu_gate(conv.p, 1, a.p, b.p, A_log.p, dt.p, s4.p, s4.p, eps, nw.p, z.p, eps,
+                                                            f2.p, s) == 0);
+  EXPECT(same(f1, f2) && same(s3, s4) && written(f1));
+  // decode attention
+  const std::size_t length = 300;
+  Bf16 q(random_bf16(24 * 256, 1.0f)), kc(random_bf16(length * 1024, 1.0f)), vc(random_bf16(length * 1024, 1.0f)),
+      gate(random_bf16(24 * 256, 2.0f)), a1(24 * 256), a2(24 * 256);
+  const std::size_t need = rt::gqa_attention_splitkv_sigmoid_gate_24_4_256_workspace_elements(length);
+  EXPECT(need == q3x_b200_gqa_decode_workspace_floats(length) && need > 0);
+  DeviceBuffer<float> ws(need);
+  EXPECT(rt::launch_gqa_attention_splitkv_sigmoid_gate_24_4_256_cuda(q.p, kc.p, vc.p, length, 0.0625f, ws.p, need, gate.p, a1.p,
+                                                                     s) == 0);
+  CUDA_OK(cudaStreamSynchronize(s));
+  EXPECT(q3x_b200_gqa_attention_decode_sigmoid_gate(q.p, kc.p, vc.p, length, 0.0625f, ws.p, need, gate.p, a2.p, s) == 0);
+  EXPECT(same(a1, a2) && written(a1));
+  EXPECT(rt::launch_gqa_attention_splitkv_sigmoid_gate_24_4_256_cuda(q.p, kc.p, vc.p, 64, 0.0625f, ws.p, need, gate.p, a1.p, s) == 1);
+  // argmax and the FP32 GEMV launchers
+  DeviceBuffer<rt::Bf16GreedyArgmaxResult> r1(rt::kBf16GreedyArgmaxWorkspaceResults), r2(rt::kBf16GreedyArgmaxWorkspaceResults);
+  EXPECT(rt::launch_bf16_greedy_argmax_cuda(kc.p, length * 1024, r1.p, s) == 0);
+  EXPECT(q3x_b200_bf16_greedy_argmax(kc.p, length * 1024, r2.p, s) == 0);
+  CUDA_OK(cudaDeviceSynchronize());
+  EXPECT(std::memcmp(r1.get().data(), r2.get().data(), 8) == 0);
+  DeviceBuffer<float> y1(24), y2(24);
+  EXPECT(q3x::kernels::launch_bf16_gemv_reference_cuda(q.p, gate.p, 24, 256, y1.p, s) == 0);
+  EXPECT(q3x_b200_bf16_gemv(q.p, gate.p, 24, 256, y2.p, nullptr, s) == 0);
+  EXPECT(same(y1, y2) && written(y1));
+}
+
 int main() {
   int device_count = 0;
   if (cudaGetDeviceCount(&device_count) != cudaSuccess || device_count == 0) {
@@ -279,6 +400,8 @@ int main() {
   test_full_attention(s);
   test_conv(s);
   test_dispatch_halves(s);
+  test_composites(s);
+  test_core_launchers(s);
   CUDA_OK(cudaStreamSynchronize(s));
   CUDA_OK(cudaGetLastError());
   CUDA_OK(cudaStreamDestroy(s));

@@ -1,14 +1,21 @@
 // Compiled against the REFERENCE project's own headers (only where a reference checkout exists) and
 // linked against libq3x_b200_host.so: taking the address of every launcher through the reference's
 // declarations proves that the mirror defines exactly those symbols (same mangled names, i.e. same
-// namespaces, names and parameter types).
+// namespaces, names and parameter types).  The projection composites take the reference's LinearWeight; the
+// test links them from q3x_b200_dispatch.cpp compiled against the reference's model_weights.h
+// (-DQ3X_B200_USE_REFERENCE_HEADERS), the way a reference build would compile that file.
 #include <cstdio>
 
+#include "gdn_prefill_whole_span_conv_sm87.h"  // src/kernels/reference (source-private header)
+#include "q3x/kernels/reference_gemv.h"
 #include "q3x/runtime/decode_ops.h"
 #include "q3x/runtime/gdn_decode.h"
 #include "q3x/runtime/layout_ops.h"
+#include "q3x/runtime/model_weights.h"
 
 namespace rt = q3x::runtime;
+namespace kn = q3x::kernels;
+namespace conv = q3x::runtime::gdn_prefill_whole_span_conv_detail;
 
 int main() {
   const void* symbols[] = {
@@ -35,6 +42,32 @@ int main() {
       reinterpret_cast<const void*>(&rt::launch_split_interleaved_q_gate_reference_cuda),
       reinterpret_cast<const void*>(&rt::launch_causal_conv1d_silu_update_reference_cuda),
       reinterpret_cast<const void*>(&rt::launch_causal_conv1d_silu_update_tile_reference_cuda),
+      // the prefill conv forms (source-private header of the reference)
+      reinterpret_cast<const void*>(&conv::launch_causal_conv1d_silu_update_whole_span_exact_cuda),
+      reinterpret_cast<const void*>(&conv::launch_causal_conv1d_silu_update_token_parallel_exact_cuda),
+      reinterpret_cast<const void*>(&conv::launch_causal_conv1d_silu_update_token_parallel_compact_qk_exact_cuda),
+      // the operators between the fused layer ops
+      reinterpret_cast<const void*>(&rt::launch_gated_delta_net_update_reference_cuda),
+      reinterpret_cast<const void*>(&rt::launch_gated_delta_net_update_tile_reference_cuda),
+      reinterpret_cast<const void*>(&rt::launch_gated_delta_net_update_warp_parallel_cuda),
+      reinterpret_cast<const void*>(&rt::launch_gated_delta_net_update_tile_warp_parallel_cuda),
+      reinterpret_cast<const void*>(&rt::launch_gated_delta_net_update_plain_rms_norm_silu_gate_cuda),
+      reinterpret_cast<const void*>(&rt::supports_gated_delta_net_update_plain_rms_norm_silu_gate_fusion),
+      reinterpret_cast<const void*>(&rt::launch_softmax_reference_cuda),
+      reinterpret_cast<const void*>(&rt::gqa_attention_splitkv_sigmoid_gate_24_4_256_workspace_elements),
+      reinterpret_cast<const void*>(&rt::launch_gqa_attention_splitkv_sigmoid_gate_24_4_256_cuda),
+      reinterpret_cast<const void*>(&rt::launch_bf16_greedy_argmax_cuda),
+      reinterpret_cast<const void*>(&kn::launch_bf16_gemv_reference_cuda),
+      reinterpret_cast<const void*>(&kn::launch_bf16_gemv_bf16_cuda),
+      reinterpret_cast<const void*>(&kn::launch_fp8_gemv_reference_cuda),
+      reinterpret_cast<const void*>(&kn::launch_nvfp4_gemv_reference_cuda),
+      // the projection composites, declared by the reference's model_weights.h with its own LinearWeight
+      reinterpret_cast<const void*>(&rt::launch_projection_to_bf16_cuda),
+      reinterpret_cast<const void*>(&rt::launch_mlp_gate_up_silu_to_bf16_cuda),
+      reinterpret_cast<const void*>(&rt::launch_post_attention_residual_norm_mlp_gate_up_silu_to_bf16_cuda),
+      reinterpret_cast<const void*>(
+          &rt::launch_decode_runner_post_attention_residual_norm_mlp_gate_up_silu_dead_up_to_bf16_cuda),
+      reinterpret_cast<const void*>(&rt::launch_mlp_down_residual_norm_to_bf16_cuda),
   };
   int missing = 0;
   for (const void* s : symbols) missing += s == nullptr ? 1 : 0;

@@ -66,7 +66,9 @@ def test_gdn_recurrence(g, tokens, in_place):
     _, exact = g.ulp_report(got_state, want_state)
     assert exact > (0.999 if tokens == 1 else 0.99), exact
     a_, e_ = orc.bf16_decode(got_state).astype(np.float64), orc.bf16_decode(want_state).astype(np.float64)
-    assert np.max(np.abs(a_ - e_)) <= 2.0 ** -9 * np.max(np.abs(e_)), np.max(np.abs(a_ - e_))
+    worst_abs, top = float(np.max(np.abs(a_ - e_))), float(np.max(np.abs(e_)))
+    # (one step: half an ulp at the largest magnitude; many steps: the bf16 state feeds back, one to two ulps)
+    assert worst_abs <= (2.0 ** -9 if tokens == 1 else 2.0 ** -7) * top, (worst_abs, top)
     _, exact_out = g.ulp_report(got_out, want_out)
     assert exact_out > 0.90, exact_out
 

@@ -38,12 +38,41 @@ def test_mirror_argument_limits_dispatch_and_bindings(host_lib, tmp_path):
     assert "host mirror tests passed" in out.stdout
 
 
-@pytest.mark.skipif(not os.path.isdir(os.path.join(REFERENCE, "include", "q3x")), reason="no reference checkout")
+HAVE_REFERENCE = os.path.isdir(os.path.join(REFERENCE, "include", "q3x"))
+
+
+@pytest.mark.skipif(not HAVE_REFERENCE, reason="no reference checkout")
 def test_mirror_defines_the_reference_symbols(host_lib, tmp_path):
-    out = compile_and_run(tmp_path, os.path.join(ROOT, "tests", "host", "reference_symbols.cpp"),
-                          [os.path.join(REFERENCE, "include")])
+    """Every launcher address is taken through the REFERENCE's declarations and must resolve at link time; the
+    projection composites come from q3x_b200_dispatch.cpp compiled against the reference's own model_weights.h."""
+    ref_inc = os.path.join(REFERENCE, "include")
+    obj = str(tmp_path / "dispatch_ref.o")
+    subprocess.run(["g++", "-std=c++17", "-O1", "-Wall", "-Wextra", "-Werror", "-DQ3X_B200_USE_REFERENCE_HEADERS", "-I", ref_inc,
+                    "-I", HOST, "-I", os.path.join(ROOT, "include"), "-c", os.path.join(HOST, "q3x_b200_dispatch.cpp"),
+                    "-o", obj], check=True, capture_output=True, text=True)
+    exe = str(tmp_path / "t")
+    cmd = ["g++", "-std=c++17", "-O1", "-Wall", "-Wextra", "-Werror", os.path.join(ROOT, "tests", "host", "reference_symbols.cpp"),
+           obj, "-o", exe, "-I", ref_inc, "-I", os.path.join(REFERENCE, "src", "kernels", "reference"),
+           "-L", PKG, "-lq3x_b200_host", "-lq3x_b200", f"-Wl,-rpath,{PKG}", "-Wl,--no-undefined"]
+    subprocess.run(cmd, check=True, capture_output=True, text=True)
+    out = subprocess.run([exe], capture_output=True, text=True)
     assert out.returncode == 0, out.stdout + out.stderr
-    assert "23 reference launcher symbols resolved" in out.stdout
+    assert "45 reference launcher symbols resolved" in out.stdout
+
+
+@pytest.mark.skipif(not HAVE_REFERENCE, reason="no reference checkout")
+def test_binding_types_have_the_reference_layout(tmp_path):
+    """Enumerator values, struct sizes, alignments and field offsets of the prefill operator binding types: the
+    same 110 numbers from the mirror header and from the reference's own headers."""
+    src = os.path.join(ROOT, "tests", "host", "bindings_layout_dump.cpp")
+    outputs = []
+    for name, flags in (("mirror", ["-I", HOST]), ("reference", ["-DUSE_REFERENCE_HEADERS", "-I", os.path.join(REFERENCE, "include")])):
+        exe = str(tmp_path / name)
+        subprocess.run(["g++", "-std=c++17", "-Wno-invalid-offsetof", *flags, src, "-o", exe], check=True, capture_output=True,
+                       text=True)
+        outputs.append(subprocess.run([exe], capture_output=True, text=True, check=True).stdout)
+    assert outputs[0] == outputs[1]
+    assert len(outputs[0].splitlines()) >= 100
 
 
 @pytest.mark.gpu
