@@ -60,6 +60,10 @@ def parse_args():
     ap.add_argument("--probe-only", action="store_true",
                     help="time each operator alone (few launches; the form profiled under ncu) and exit")
     ap.add_argument("--probe-reps", type=int, default=3)
+    ap.add_argument("--no-probes", action="store_true",
+                    help="skip the per-operator and decode probes (the form whose launch list is profiled)")
+    ap.add_argument("--decode-only", action="store_true",
+                    help="time only the batch-one (decode) step and operators and exit")
     return ap.parse_args()
 
 
@@ -444,6 +448,111 @@ def decode_step_probe(chain, position=131071, reps=20):
             "kernels_per_step": chain.kernels_per_step()}
 
 
+def probe_decode_ops(peak, cuda_index=0, aim_ms=60.0):
+    """The batch-one (decode) operators that sit between the fused layer ops, each alone at the model's shapes,
+    timed like the per-operator table: the GDN recurrence step with its gated-norm epilogue (state 48 x 128 x 128
+    bf16 in and out), split-KV attention + sigmoid gate at position 131071 (K and V caches read once), the
+    MLP-sized NVFP4 / FP8 / bf16 GEMVs (weights read once) and the greedy argmax over the vocabulary.  Bytes are
+    algorithmic: every operand crosses HBM once.  Operands are rotated over several copies so that the 126 MB L2
+    cannot serve a repeat."""
+    import torch
+
+    pkg = importlib.import_module("qwen3x-orin_b200")
+    capi = pkg.capi
+    dev = torch.device("cuda", cuda_index)
+    gen = torch.Generator(device=dev).manual_seed(77)
+    stream_obj = torch.cuda.Stream()
+    stream = stream_obj.cuda_stream
+
+    def bf(shape, std=1.0):
+        return (torch.randn(shape, generator=gen, device=dev, dtype=torch.float32) * std).to(torch.bfloat16)
+
+    def u8(shape, lo=0, hi=256):
+        return torch.randint(lo, hi, shape, generator=gen, device=dev, dtype=torch.int32).to(torch.uint8)
+
+    out = {}
+
+    def timed(name, calls, nbytes):
+        """calls: list of zero-argument launches (rotating operand copies); nbytes: bytes one launch moves.
+        The launches are captured into one CUDA graph (a Python call costs more than the shortest of these
+        kernels runs) and the graph is replayed for about aim_ms."""
+        with torch.cuda.stream(stream_obj):
+            for c in calls:
+                c()
+        stream_obj.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream_obj):
+            for c in calls:
+                c()
+        with torch.cuda.stream(stream_obj):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream_obj)
+            graph.replay()
+            e1.record(stream_obj)
+            stream_obj.synchronize()
+            reps = max(3, min(4000, int(math.ceil(aim_ms / max(e0.elapsed_time(e1), 1e-3)))))
+            sampler = ClockSampler(cuda_index)
+            e0.record(stream_obj)
+            for _ in range(reps):
+                graph.replay()
+            e1.record(stream_obj)
+            stream_obj.synchronize()
+            clk = sampler.stop()
+        n = reps * len(calls)
+        us = e0.elapsed_time(e1) * 1e3 / n
+        gbs = nbytes / (us * 1e-6) / 1e9
+        out[name] = {"us": round(us, 2), "bytes": nbytes, "algorithmic_GBs": round(gbs, 1), "frac_of_peak": round(gbs / peak, 4),
+                     "launches_timed": n, "sm_mhz": clk.get("sm_mhz")}
+
+    # --- GDN recurrence step + gated norm (decode): 40 state copies = 126 MB
+    copies = 40
+    conv, a, b = bf((1, 10240)), bf((1, 48)), bf((1, 48))
+    A_log, dt = bf((48,)), bf((48,))
+    states = [bf((48, 128, 128), 0.05) for _ in range(copies)]
+    z, w = bf((1, 6144)), bf((128,))
+    y = torch.empty((1, 6144), device=dev, dtype=torch.bfloat16)
+    timed("gdn_update_rmsnorm_gate", [lambda s=s: capi.check("q3x_b200_gated_delta_net_update_rms_norm_silu_gate", conv, 1, a, b,
+                                                             A_log, dt, s, s, 1e-6, w, z, 1e-6, y, stream) for s in states],
+          2 * 48 * 128 * 128 * 2 + 10240 * 2 + 2 * 6144 * 2 + 4 * 48 * 2 + 256)
+    del states
+    # --- split-KV decode attention + sigmoid gate at position 131071 (one layer's cache: 537 MB, larger than L2)
+    length = 131072
+    q, gate = bf((24, 256)), bf((24, 256))
+    kc, vc = bf((length, 4, 256)), bf((length, 4, 256))
+    words = capi.lib().q3x_b200_gqa_decode_workspace_floats(length)
+    ws = torch.empty(words, device=dev, dtype=torch.float32)
+    o = torch.empty((24, 256), device=dev, dtype=torch.bfloat16)
+    timed("gqa_decode_sigmoid_gate_131072", [lambda: capi.check("q3x_b200_gqa_attention_decode_sigmoid_gate", q, kc, vc, length,
+                                                                0.0625, ws, words, gate, o, stream)],
+          2 * length * 4 * 256 * 2 + 3 * 24 * 256 * 2)
+    del kc, vc
+    # --- batch-one projections: weights rotated over copies totalling > L2
+    x5120, x17408 = bf((5120,)), bf((17408,))
+    for name, rows, cols, x in (("nvfp4_gemv_17408x5120", 17408, 5120, x5120), ("nvfp4_gemv_5120x17408", 5120, 17408, x17408)):
+        packs = [(u8((rows, cols // 2)), u8((rows, cols // 16), 0x20, 0x50)) for _ in range(4)]
+        yb = torch.empty(rows, device=dev, dtype=torch.bfloat16)
+        timed(name, [lambda p=p, x=x, yb=yb, rows=rows, cols=cols: capi.check("q3x_b200_nvfp4_gemv", p[0], p[1], 0.01, x, rows, cols,
+                                                                              None, yb, stream) for p in packs],
+              rows * cols // 2 + rows * cols // 16 + cols * 2 + rows * 2)
+        del packs
+    w8 = [u8((12288, 5120), 0x10, 0x70) for _ in range(3)]
+    yb = torch.empty(12288, device=dev, dtype=torch.bfloat16)
+    timed("fp8_gemv_12288x5120", [lambda p=p: capi.check("q3x_b200_fp8_gemv", p, 0.02, x5120, 12288, 5120, None, yb, stream)
+                                  for p in w8], 12288 * 5120 + 5120 * 2 + 12288 * 2)
+    del w8
+    wb = [bf((6144, 5120), 0.05) for _ in range(3)]
+    yb = torch.empty(6144, device=dev, dtype=torch.bfloat16)
+    timed("bf16_gemv_6144x5120", [lambda p=p: capi.check("q3x_b200_bf16_gemv", p, x5120, 6144, 5120, None, yb, stream) for p in wb],
+          6144 * 5120 * 2 + 5120 * 2 + 6144 * 2)
+    del wb
+    logits = [bf((248320,), 3.0) for _ in range(8)]
+    rec = torch.empty(66, device=dev, dtype=torch.int32)
+    timed("greedy_argmax_248320", [lambda p=p: capi.check("q3x_b200_bf16_greedy_argmax", p, 248320, rec, stream) for p in logits],
+          248320 * 2)
+    torch.cuda.empty_cache()
+    return out
+
+
 def host_memory_available_bytes():
     """What this process may still take from host memory: MemAvailable, capped by the cgroup limit."""
     avail = None
@@ -522,6 +631,12 @@ def main():
             os.dup2(saved_stdout, 1)
             os.close(saved_stdout)
 
+    if args.decode_only:
+        peak, _ = measured_peak()
+        print(json.dumps({"decode_only": True, "decode_step": decode_step_probe(chain),
+                          "decode_ops": probe_decode_ops(peak, local_rank)}), flush=True)
+        return 0
+
     total = args.total_tokens or CONFIG_TOKENS[args.config]
     mine = shard_mod.shard_for(total, rank, world)
     T = mine.tokens
@@ -593,10 +708,11 @@ def main():
 
     # ---- per-operator timing (each op alone, CUDA events on its stream) --------------------------
     peak, peak_kind = measured_peak()
-    per_op = probe_ops(stack, chain, stream_obj, T, peak, 3, aim_ms=args.probe_ms, cuda_index=local_rank) if rank == 0 else {}
+    probing = rank == 0 and not args.no_probes
+    per_op = probe_ops(stack, chain, stream_obj, T, peak, 3, aim_ms=args.probe_ms, cuda_index=local_rank) if probing else {}
     # dominant kernel = the SwiGLU stream (the largest share of the step's bytes, one kernel per launch)
     roofline = None
-    if rank == 0:
+    if probing:
         sw = per_op["swiglu"]
         per_token, traffic_commit, capture_tokens = swiglu_traffic()
         roofline = {"bound": "hbm", "kernel": "binary_vec_kernel<SiluMul> (SwiGLU)", "achieved": sw["algorithmic_GBs"],
@@ -630,7 +746,8 @@ def main():
                "sample_tokens": args.cpu_sample_tokens, "seconds_per_pass": round(secs, 3),
                "sample": CPU_SAMPLE_NOTE.format(n=args.cpu_sample_tokens, c=threads)}
 
-    decode = decode_step_probe(chain) if rank == 0 else None
+    decode = decode_step_probe(chain) if probing else None
+    decode_ops = probe_decode_ops(peak, local_rank) if probing else None
     validation = validate_shards(rank, world, dist) if distributed else None
     if rank == 0:
         line = {
@@ -641,6 +758,7 @@ def main():
             "gpu_launches": chain.kernels_per_step() * args.steps, "cuda_graph": graph is not None, "clocks": clocks,
         }
         line["decode_step"] = decode
+        line["decode_ops"] = decode_ops
         if validation is not None:
             line["validation"] = validation
         print(json.dumps(line), flush=True)

@@ -7,7 +7,8 @@ import ctypes as C
 import os
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG, "libq3x_b200.so")
+# the in-tree build, unless Q3X_B200_LIBRARY names another build of the same library
+LIB_PATH = os.environ.get("Q3X_B200_LIBRARY") or os.path.join(_PKG, "libq3x_b200.so")
 HOST_LIB_PATH = os.path.join(_PKG, "libq3x_b200_host.so")
 
 CUDA_SUCCESS = 0

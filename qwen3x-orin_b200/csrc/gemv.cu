@@ -130,20 +130,36 @@ __global__ void __launch_bounds__(kThreads) gemv_kernel(Format fmt, const uint4*
 #pragma unroll
   for (int r = 0; r < kRows; ++r) acc[r] = 0.0f;
 
-  for (int v = lane; v < row_vectors; v += 32) {
-    uint4 w[kRows];
-    uint32_t sp[kRows];
+  // kDepth trips are requested before the first is used: 2 x kDepth 128-bit loads per lane in flight
+  constexpr int kDepth = 4;
+  for (int base = lane; base < row_vectors; base += 32 * kDepth) {
+    uint4 w[kDepth][kRows];
+    uint32_t sp[kDepth][kRows];
 #pragma unroll
-    for (int r = 0; r < kRows; ++r) {
-      w[r] = ld_stream(row_ptr[r] + v);
-      sp[r] = 0;
-      if constexpr (std::is_same<Format, NvFp4Weights>::value) sp[r] = __ldg(scale_ptr[r] + v);
+    for (int d = 0; d < kDepth; ++d) {
+      const int v = base + 32 * d;
+#pragma unroll
+      for (int r = 0; r < kRows; ++r) {
+        w[d][r] = make_uint4(0, 0, 0, 0);
+        sp[d][r] = 0;
+        if (v < row_vectors) {
+          w[d][r] = ld_stream(row_ptr[r] + v);
+          if constexpr (std::is_same<Format, NvFp4Weights>::value) sp[d][r] = __ldg(scale_ptr[r] + v);
+        }
+      }
     }
-    float xf[kXVectors * 8];
 #pragma unroll
-    for (int k = 0; k < kXVectors; ++k) unpack8(ld_weight(x + static_cast<size_t>(v) * kXVectors + k), *reinterpret_cast<float(*)[8]>(xf + 8 * k));
+    for (int d = 0; d < kDepth; ++d) {
+      const int v = base + 32 * d;
+      if (v < row_vectors) {
+        float xf[kXVectors * 8];
 #pragma unroll
-    for (int r = 0; r < kRows; ++r) acc[r] = accumulate(fmt, w[r], sp[r], xf, acc[r]);
+        for (int k = 0; k < kXVectors; ++k)
+          unpack8(ld_weight(x + static_cast<size_t>(v) * kXVectors + k), *reinterpret_cast<float(*)[8]>(xf + 8 * k));
+#pragma unroll
+        for (int r = 0; r < kRows; ++r) acc[r] = accumulate(fmt, w[d][r], sp[d][r], xf, acc[r]);
+      }
+    }
   }
 #pragma unroll
   for (int r = 0; r < kRows; ++r) {

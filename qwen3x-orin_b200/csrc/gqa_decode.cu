@@ -19,8 +19,9 @@
 //     lanes through shared memory for the P.V accumulation (6 heads x 8 dims of FP32 accumulators per lane);
 //   * the V rows of the batch and the K rows of the NEXT batch are requested before the reduction starts,
 //     so sixteen 512-byte loads per warp are in flight while the arithmetic runs;
-//   * every warp writes its (max, denominator, accumulator) to the workspace; a second small kernel merges
-//     the partial states of each head, rounds, applies the gate and rounds again.
+//   * at the end a CTA merges its warps' (max, denominator, accumulator) states through shared memory and
+//     writes one partial state per head to the workspace; a second small kernel merges the splits of each
+//     head, rounds, applies the gate and rounds again.
 #include "device_utils.cuh"
 #include "host_checks.hpp"
 #include "q3x_b200.h"
@@ -33,9 +34,21 @@ constexpr int kKvHeads = Q3X_B200_KV_HEADS;        // 4
 constexpr int kGroup = kQHeads / kKvHeads;         // 6 query heads per KV head
 constexpr int kDim = Q3X_B200_ATTN_HEAD_DIM;       // 256
 constexpr int kRowVectors = kDim / 8;              // 32: one vector per lane
-constexpr int kWarps = 8;
+#ifndef Q3X_GQA_WARPS
+#define Q3X_GQA_WARPS 8
+#endif
+#ifndef Q3X_GQA_BATCH
+#define Q3X_GQA_BATCH 8
+#endif
+constexpr int kWarps = Q3X_GQA_WARPS;
 constexpr int kThreads = kWarps * 32;
-constexpr int kBatch = 8;                          // positions per warp iteration
+constexpr int kBatch = Q3X_GQA_BATCH;              // positions per warp iteration (8 or 4)
+static_assert(kBatch == 8 || kBatch == 4, "the reduce-scatter below is written for 8 or 4 positions");
+constexpr int kSums = kBatch * kGroup;             // partial sums a lane holds before the reduction
+// After the reduce-scatter a lane's top log2(kBatch) index bits name its position, the next bit the half of the
+// heads (three each), and the remaining low bits are replicas.
+constexpr int kHalfMask = 16 / kBatch;             // 2 (batch 8) or 4 (batch 4)
+constexpr int kPosShift = kBatch == 8 ? 2 : 3;
 constexpr int kMaxSplits = 37;                     // 37 x 4 KV heads = 148 CTAs, one per SM
 constexpr int kPartialFloats = 2 + kDim;           // max, denominator, accumulator
 constexpr float kLog2e = 1.4426950408889634f;
@@ -50,7 +63,7 @@ __device__ __forceinline__ float ex2(float x) {
 // chosen by the lane's bit `mask`: lanes with the bit clear keep the lower half, lanes with it set the
 // upper half.  One shuffle per surviving value.
 template <int N>
-__device__ __forceinline__ void halve(float (&v)[48], int mask) {
+__device__ __forceinline__ void halve(float (&v)[kSums], int mask) {
   const bool upper = (threadIdx.x & mask) != 0;
 #pragma unroll
   for (int i = 0; i < N / 2; ++i) {
@@ -61,7 +74,7 @@ __device__ __forceinline__ void halve(float (&v)[48], int mask) {
 }
 
 // Partial attention state of one KV head over positions [first, last), one CTA; warp w takes the batches
-// w, w + 8, ... of that range.  workspace: [kv head][split][warp][query head in group][kPartialFloats].
+// w, w + 8, ... of that range.  workspace: [kv head][split][query head in group][kPartialFloats].
 __global__ void __launch_bounds__(kThreads, 1) gqa_decode_partial_kernel(
     const uint16_t* __restrict__ query, const uint4* __restrict__ key_cache, const uint4* __restrict__ value_cache,
     size_t length, size_t positions_per_split, float scale, float* __restrict__ workspace) {
@@ -85,7 +98,7 @@ __global__ void __launch_bounds__(kThreads, 1) gqa_decode_partial_kernel(
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc[h][i] = 0.0f;
   // running maximum (in the scaled-score domain) and denominator of the three heads this lane looks after
-  // during the softmax step: heads 3 * ((lane >> 1) & 1) + {0, 1, 2}
+  // during the softmax step: heads 3 * (bit kHalfMask of the lane) + {0, 1, 2}
   float run_max[3] = {-INFINITY, -INFINITY, -INFINITY};
   float run_sum[3] = {0.0f, 0.0f, 0.0f};
 
@@ -106,7 +119,7 @@ __global__ void __launch_bounds__(kThreads, 1) gqa_decode_partial_kernel(
   if (start < last) load_rows(k_base, start, k_rows);
   for (; start < last; start += stride) {
     // ---- partial dot products: sums[p * 6 + h] over the lane's eight dims ------------------------------
-    float sums[48];
+    float sums[kSums];
 #pragma unroll
     for (int p = 0; p < kBatch; ++p) {
       float k[8];
@@ -124,13 +137,24 @@ __global__ void __launch_bounds__(kThreads, 1) gqa_decode_partial_kernel(
     if (start + stride < last) load_rows(k_base, start + stride, k_rows);
 
     // ---- reduce-scatter: lane bits 4..2 select the position, bit 1 the half of the heads -----------------
-    halve<48>(sums, 16);
-    halve<24>(sums, 8);
-    halve<12>(sums, 4);
-    halve<6>(sums, 2);
+    if constexpr (kBatch == 8) {
+      halve<48>(sums, 16);
+      halve<24>(sums, 8);
+      halve<12>(sums, 4);
+      halve<6>(sums, 2);
 #pragma unroll
-    for (int i = 0; i < 3; ++i) sums[i] += __shfl_xor_sync(kFullMask, sums[i], 1);
-    const int my_pos = lane >> 2;
+      for (int i = 0; i < 3; ++i) sums[i] += __shfl_xor_sync(kFullMask, sums[i], 1);
+    } else {
+      halve<24>(sums, 16);
+      halve<12>(sums, 8);
+      halve<6>(sums, 4);
+#pragma unroll
+      for (int i = 0; i < 3; ++i) {
+        sums[i] += __shfl_xor_sync(kFullMask, sums[i], 2);
+        sums[i] += __shfl_xor_sync(kFullMask, sums[i], 1);
+      }
+    }
+    const int my_pos = lane >> kPosShift;
     const bool valid = start + my_pos < last;
     // ---- online softmax for the lane's three heads ----------------------------------------------------------
     float p_val[3], rescale[3];
@@ -138,14 +162,14 @@ __global__ void __launch_bounds__(kThreads, 1) gqa_decode_partial_kernel(
     for (int i = 0; i < 3; ++i) {
       const float s = valid ? sums[i] * scale : -INFINITY;
       float batch_max = s;
-      batch_max = fmaxf(batch_max, __shfl_xor_sync(kFullMask, batch_max, 4));
+      if (kBatch == 8) batch_max = fmaxf(batch_max, __shfl_xor_sync(kFullMask, batch_max, 4));
       batch_max = fmaxf(batch_max, __shfl_xor_sync(kFullMask, batch_max, 8));
       batch_max = fmaxf(batch_max, __shfl_xor_sync(kFullMask, batch_max, 16));
       const float new_max = fmaxf(run_max[i], batch_max);  // finite: every batch has a valid position
       rescale[i] = ex2((run_max[i] - new_max) * kLog2e);   // 0 on the first batch (run_max = -inf)
       p_val[i] = ex2((s - new_max) * kLog2e);              // 0 for a masked position
       float batch_sum = p_val[i];
-      batch_sum += __shfl_xor_sync(kFullMask, batch_sum, 4);
+      if (kBatch == 8) batch_sum += __shfl_xor_sync(kFullMask, batch_sum, 4);
       batch_sum += __shfl_xor_sync(kFullMask, batch_sum, 8);
       batch_sum += __shfl_xor_sync(kFullMask, batch_sum, 16);
       run_sum[i] = fmaf(run_sum[i], rescale[i], batch_sum);
@@ -153,8 +177,8 @@ __global__ void __launch_bounds__(kThreads, 1) gqa_decode_partial_kernel(
     }
     // ---- probabilities and rescale factors to every lane ---------------------------------------------------------
     __syncwarp();  // the previous batch's readers are done
-    if ((lane & 1) == 0) {
-      const int half = (lane >> 1) & 1;
+    if ((lane & (kHalfMask - 1)) == 0) {
+      const int half = (lane & kHalfMask) ? 1 : 0;
 #pragma unroll
       for (int i = 0; i < 3; ++i) probs[warp][my_pos * kGroup + half * 3 + i] = p_val[i];
       if (my_pos == 0) {
@@ -188,25 +212,57 @@ __global__ void __launch_bounds__(kThreads, 1) gqa_decode_partial_kernel(
     }
   }
 
-  // ---- this warp's partial state: (max, denominator) from the lanes that own them, accumulators from all ----
-  float* out = workspace + ((static_cast<size_t>(kv) * gridDim.x + blockIdx.x) * kWarps + warp) * kGroup * kPartialFloats;
-  if (lane < 4 && (lane & 1) == 0) {  // lanes 0 and 2: position slot 0, both head halves
-    const int half = (lane >> 1) & 1;
+  // ---- the CTA's partial state: its warps' (max, denominator, accumulator) merged through shared memory ----
+  // (three heads per round, so that the staging fits the static 48 KB: 8 warps x 3 heads x 256 floats)
+  __shared__ float warp_max[kWarps][kGroup], warp_sum[kWarps][kGroup];
+  __shared__ float stage[kWarps][3][kDim];
+  if (lane == 0 || lane == kHalfMask) {  // position slot 0, both head halves
+    const int half = lane == 0 ? 0 : 1;
 #pragma unroll
     for (int i = 0; i < 3; ++i) {
-      out[(half * 3 + i) * kPartialFloats + 0] = run_max[i];
-      out[(half * 3 + i) * kPartialFloats + 1] = run_sum[i];
+      warp_max[warp][half * 3 + i] = run_max[i];
+      warp_sum[warp][half * 3 + i] = run_sum[i];
     }
   }
+  __syncthreads();
+  float* out = workspace + (static_cast<size_t>(kv) * gridDim.x + blockIdx.x) * kGroup * kPartialFloats;
 #pragma unroll
-  for (int h = 0; h < kGroup; ++h) {
-    float* dst = out + h * kPartialFloats + 2 + lane * 8;
+  for (int round = 0; round < 2; ++round) {
+    // this warp's accumulators of the round's three heads, rescaled to the CTA-wide maximum of each head
 #pragma unroll
-    for (int i = 0; i < 8; ++i) dst[i] = acc[h][i];
+    for (int j = 0; j < 3; ++j) {
+      const int h = round * 3 + j;
+      float top = warp_max[0][h];
+#pragma unroll
+      for (int w = 1; w < kWarps; ++w) top = fmaxf(top, warp_max[w][h]);
+      // an idle warp holds (-inf, 0, zeros); a CTA with no position at all keeps top = -inf and writes zeros
+      const float f = warp_sum[warp][h] == 0.0f ? 0.0f : ex2((warp_max[warp][h] - top) * kLog2e);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) stage[warp][j][lane * 8 + i] = acc[h][i] * f;
+    }
+    __syncthreads();
+    for (int item = threadIdx.x; item < 3 * kDim; item += kThreads) {
+      const int j = item / kDim, d = item - j * kDim;
+      float total = 0.0f;
+#pragma unroll
+      for (int w = 0; w < kWarps; ++w) total += stage[w][j][d];
+      out[(round * 3 + j) * kPartialFloats + 2 + d] = total;
+    }
+    if (threadIdx.x < 3) {
+      const int h = round * 3 + threadIdx.x;
+      float top = warp_max[0][h];
+      for (int w = 1; w < kWarps; ++w) top = fmaxf(top, warp_max[w][h]);
+      float den = 0.0f;
+      for (int w = 0; w < kWarps; ++w)
+        den += warp_sum[w][h] == 0.0f ? 0.0f : warp_sum[w][h] * ex2((warp_max[w][h] - top) * kLog2e);
+      out[h * kPartialFloats + 0] = top;
+      out[h * kPartialFloats + 1] = den;
+    }
+    __syncthreads();
   }
 }
 
-// Merges the `partials` states of one query head, rounds to bf16, applies the sigmoid gate (when given) and
+// Merges the per-split states of one query head, rounds to bf16, applies the sigmoid gate (when given) and
 // rounds again.  One CTA per query head, one thread per dim.
 __global__ void __launch_bounds__(kDim) gqa_decode_merge_kernel(const float* __restrict__ workspace, int splits,
                                                                const uint16_t* __restrict__ gate,
@@ -214,7 +270,7 @@ __global__ void __launch_bounds__(kDim) gqa_decode_merge_kernel(const float* __r
   const int head = blockIdx.x;
   const int kv = head / kGroup, h = head % kGroup;
   const int d = threadIdx.x;
-  const int partials = splits * kWarps;
+  const int partials = splits;
   const float* base = workspace + (static_cast<size_t>(kv) * partials * kGroup + h) * kPartialFloats;
   const size_t step = static_cast<size_t>(kGroup) * kPartialFloats;
   float top = -INFINITY;
@@ -222,7 +278,7 @@ __global__ void __launch_bounds__(kDim) gqa_decode_merge_kernel(const float* __r
   float den = 0.0f, num = 0.0f;
   for (int s = 0; s < partials; ++s) {
     const float* p = base + s * step;
-    const float w = p[1] == 0.0f ? 0.0f : ex2((p[0] - top) * kLog2e);  // an idle warp left (-inf, 0, zeros)
+    const float w = p[1] == 0.0f ? 0.0f : ex2((p[0] - top) * kLog2e);  // an empty split left (-inf, 0, zeros)
     den = fmaf(p[1], w, den);
     num = fmaf(p[2 + d], w, num);
   }
@@ -248,7 +304,7 @@ using namespace q3x;
 using namespace q3x::host;
 
 extern "C" size_t q3x_b200_gqa_decode_workspace_floats(size_t sequence_length) {
-  return static_cast<size_t>(plan_splits(sequence_length)) * kWarps * kQHeads * kPartialFloats;
+  return static_cast<size_t>(plan_splits(sequence_length)) * kQHeads * kPartialFloats;
 }
 
 extern "C" int q3x_b200_gqa_attention_decode_sigmoid_gate(const uint16_t* query, const uint16_t* key_cache,

@@ -90,15 +90,28 @@ __global__ void __launch_bounds__(kThreads) argmax_partial_kernel(const uint16_t
                                                                   ArgmaxResult* workspace) {
   Best mine{-INFINITY, kNoIndex, 0u, 0u};
   const size_t stride = static_cast<size_t>(gridDim.x) * kThreads;
-  for (size_t i = static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x; i < count; i += stride) {
-    const uint32_t bits = in[i];
+  auto visit = [&](uint32_t bits, size_t i) {
     if ((bits & 0x7f80u) == 0x7f80u) {
       mine.nonfinite = 1u;
-      continue;
+    } else {
+      const float v = bf16_to_float(static_cast<uint16_t>(bits));
+      if (mine.index == kNoIndex || v > mine.value) mine = Best{v, static_cast<uint32_t>(i), bits, mine.nonfinite};
     }
-    const float v = bf16_to_float(static_cast<uint16_t>(bits));
-    if (mine.index == kNoIndex || v > mine.value) mine = Best{v, static_cast<uint32_t>(i), bits, mine.nonfinite};
+  };
+  // eight logits per 128-bit load where the vector is aligned (a thread still meets its indices in increasing
+  // order, which is what keeps the earliest of equal maxima); the ragged end one element at a time
+  const size_t vectors = (reinterpret_cast<uintptr_t>(in) & 15u) == 0 ? count / 8 : 0;
+  for (size_t v = static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x; v < vectors; v += stride) {
+    const uint4 q = ld_stream(reinterpret_cast<const uint4*>(in) + v);
+    const uint32_t words[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      visit(words[k] & 0xffffu, v * 8 + 2 * k);
+      visit(words[k] >> 16, v * 8 + 2 * k + 1);
+    }
   }
+  for (size_t i = vectors * 8 + static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x; i < count; i += stride)
+    visit(in[i], i);
   const Best r = block_best(mine);
   if (threadIdx.x == 0)
     workspace[1 + blockIdx.x] = ArgmaxResult{r.index, static_cast<uint16_t>(r.bits), static_cast<uint16_t>(r.nonfinite)};
