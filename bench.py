@@ -634,7 +634,7 @@ def main():
     if args.decode_only:
         peak, _ = measured_peak()
         print(json.dumps({"decode_only": True, "decode_step": decode_step_probe(chain),
-                          "decode_ops": probe_decode_ops(peak, local_rank)}), flush=True)
+                          "decode_ops": probe_decode_ops(peak, local_rank, aim_ms=args.probe_ms / 2)}), flush=True)
         return 0
 
     total = args.total_tokens or CONFIG_TOKENS[args.config]
@@ -747,7 +747,7 @@ def main():
                "sample": CPU_SAMPLE_NOTE.format(n=args.cpu_sample_tokens, c=threads)}
 
     decode = decode_step_probe(chain) if probing else None
-    decode_ops = probe_decode_ops(peak, local_rank) if probing else None
+    decode_ops = probe_decode_ops(peak, local_rank, aim_ms=args.probe_ms / 2) if probing else None
     validation = validate_shards(rank, world, dist) if distributed else None
     if rank == 0:
         line = {

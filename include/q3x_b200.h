@@ -146,6 +146,16 @@ int q3x_b200_nvfp4_quantize_dynamic(const uint16_t* in, size_t rows, size_t cols
                                     float* global_scales_out, uint8_t* codes, uint8_t* scales,
                                     void* stream);
 
+/* The block scales of a [rows, cols] tensor re-laid out for block-scaled tensor-core MMA (tcgen05.mma with
+ * 16-element E4M3 scale vectors): 512-byte tiles of 128 rows x 4 blocks, the byte of (row r, block b) at
+ * tile (r / 128, b / 4), offset (r % 32) * 16 + (r % 128 / 32) * 4 + b % 4, tiles row-tile major, ragged edges
+ * padded with zero bytes.  Every quantiser entry point writes the canonical row-major view
+ * (include/q3x/quantization/nvfp4.h:50-55); this call converts it (a bit-exact permutation).
+ * q3x_b200_nvfp4_swizzled_scale_bytes gives the size of `swizzled`.  No counterpart in the reference. */
+size_t q3x_b200_nvfp4_swizzled_scale_bytes(size_t rows, size_t cols);
+int q3x_b200_nvfp4_swizzle_block_scales(const uint8_t* row_major, size_t rows, size_t cols, uint8_t* swizzled,
+                                        void* stream);
+
 /* Residual add + centred RMSNorm + NVFP4 of the normalised rows, global scale from the group
  * amax.  normalized_out is required (it is the operand the codes are derived from, bit for
  * bit); it may be exactly `right`.  One kernel that crosses HBM once where a scale group is short

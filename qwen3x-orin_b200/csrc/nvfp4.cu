@@ -171,6 +171,24 @@ __global__ void __launch_bounds__(kThreads) nvfp4_quantize_scalar_kernel(const u
   }
 }
 
+// ---- block scales in the tiled layout of block-scaled tensor-core MMA ------------------------------------
+// A block-scaled tcgen05.mma reads its scale factors from 512-byte tiles that cover 128 rows x 4 blocks
+// (64 columns): inside a tile the byte of (row r, block b) sits at (r % 32) * 16 + (r % 128 / 32) * 4 + b % 4,
+// tiles are ordered row-tile major, and a ragged edge is padded with zero bytes to whole tiles.  The quantiser
+// writes the canonical row-major [rows, cols / 16] view (the checkpoint layout,
+// include/q3x/quantization/nvfp4.h:50-55); this kernel re-lays it out, one thread per destination byte.
+__global__ void __launch_bounds__(kThreads) swizzle_scales_kernel(const uint8_t* __restrict__ row_major, size_t rows,
+                                                                  size_t row_blocks, size_t block_tiles,
+                                                                  size_t out_bytes, uint8_t* __restrict__ swizzled) {
+  const size_t stride = static_cast<size_t>(gridDim.x) * kThreads;
+  for (size_t o = static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x; o < out_bytes; o += stride) {
+    const size_t tile = o / 512, in_tile = o % 512;
+    const size_t row = tile / block_tiles * 128 + in_tile % 16 / 4 * 32 + in_tile / 16;
+    const size_t block = tile % block_tiles * 4 + in_tile % 4;
+    swizzled[o] = (row < rows && block < row_blocks) ? row_major[row * row_blocks + block] : uint8_t{0};
+  }
+}
+
 __global__ void __launch_bounds__(kThreads) debug_encode_kernel(const float* in, size_t count, uint8_t* out,
                                                                 int format) {
   const size_t i = static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x;
@@ -634,6 +652,27 @@ extern "C" int q3x_b200_residual_add_rms_norm_nvfp4_static_scratch(
   return residual_norm_nvfp4(left, right, weight, tokens, hidden, eps, rows_per_scale, residual_out, normalized_out,
                              nullptr, global_scales_out, codes, scales, stream, Path::kTwoKernels,
                              &static_scratch_address);
+}
+
+extern "C" size_t q3x_b200_nvfp4_swizzled_scale_bytes(size_t rows, size_t cols) {
+  if (rows == 0 || cols == 0) return 0;
+  const size_t row_tiles = (rows + 127) / 128, block_tiles = (cols / Q3X_B200_NVFP4_BLOCK + 3) / 4;
+  return mul3_overflows(row_tiles, block_tiles, 512) ? 0 : row_tiles * block_tiles * 512;
+}
+
+extern "C" int q3x_b200_nvfp4_swizzle_block_scales(const uint8_t* row_major, size_t rows, size_t cols, uint8_t* swizzled,
+                                                   void* stream) {
+  if (cols % Q3X_B200_NVFP4_BLOCK != 0 || mul3_overflows(rows, cols, 2)) return kInvalid;
+  if (rows == 0 || cols == 0) return kOk;
+  if (row_major == nullptr || swizzled == nullptr) return kInvalid;
+  const size_t out_bytes = q3x_b200_nvfp4_swizzled_scale_bytes(rows, cols);
+  if (out_bytes == 0) return kInvalid;
+  const size_t row_blocks = cols / Q3X_B200_NVFP4_BLOCK;
+  if (overlap(span(row_major, rows * row_blocks), span(swizzled, out_bytes))) return kInvalid;
+  clear_stale_error();
+  swizzle_scales_kernel<<<grid_for(out_bytes, kThreads, 8), kThreads, 0, as_stream(stream)>>>(
+      row_major, rows, row_blocks, (row_blocks + 3) / 4, out_bytes, swizzled);
+  return launch_status();
 }
 
 // Diagnostics: the two narrow conversions on their own, so that tests can sweep them against the

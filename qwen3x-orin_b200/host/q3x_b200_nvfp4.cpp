@@ -5,6 +5,31 @@
 
 namespace q3x::quantization {
 
+const char* nvfp4_status_string(const NvFp4Status status) noexcept {
+  switch (status) {
+    case NvFp4Status::kSuccess: return "success";
+    case NvFp4Status::kInvalidArgument: return "invalid argument";
+    case NvFp4Status::kInvalidColumnCount: return "column count is not a multiple of the NVFP4 group size";
+    case NvFp4Status::kSizeOverflow: return "NVFP4 tensor element count overflows size_t";
+  }
+  return "unknown NVFP4 status";
+}
+
+NvFp4Status validate_nvfp4_activation_shape(const std::size_t rows, const std::size_t cols) noexcept {
+  if (cols % kNvFp4ActivationBlock != 0U) return NvFp4Status::kInvalidColumnCount;
+  if (cols != 0U && rows > static_cast<std::size_t>(-1) / cols / 2U) return NvFp4Status::kSizeOverflow;
+  return NvFp4Status::kSuccess;
+}
+
+std::size_t nvfp4_swizzled_block_scale_bytes(std::size_t rows, std::size_t cols) noexcept {
+  return q3x_b200_nvfp4_swizzled_scale_bytes(rows, cols);
+}
+
+int launch_nvfp4_swizzle_block_scales_cuda(const std::uint8_t* row_major, std::size_t rows, std::size_t cols,
+                                           std::uint8_t* swizzled, void* cuda_stream) noexcept {
+  return q3x_b200_nvfp4_swizzle_block_scales(row_major, rows, cols, swizzled, cuda_stream);
+}
+
 std::size_t nvfp4_activation_scale_groups(std::size_t rows, std::size_t rows_per_scale) noexcept {
   return q3x_b200_nvfp4_group_count(rows, rows_per_scale);
 }

@@ -15,6 +15,18 @@ namespace q3x::quantization {
 inline constexpr std::size_t kNvFp4ActivationBlock = 16U;       // elements per E4M3 block scale (nvfp4.h:8)
 inline constexpr std::size_t kNvFp4PrefillScaleScope = 512U;    // rows per global scale: one prefill chunk
 
+// include/q3x/quantization/nvfp4.h:41-46, same enumerators and values
+enum class NvFp4Status : std::uint8_t {
+  kSuccess = 0,
+  kInvalidArgument,
+  kInvalidColumnCount,
+  kSizeOverflow,
+};
+[[nodiscard]] const char* nvfp4_status_string(NvFp4Status status) noexcept;
+// Host-side shape check of a [rows, cols] activation tensor, in the reference's status vocabulary: cols must be
+// a multiple of 16 (kInvalidColumnCount), rows * cols * 2 must fit size_t (kSizeOverflow).
+[[nodiscard]] NvFp4Status validate_nvfp4_activation_shape(std::size_t rows, std::size_t cols) noexcept;
+
 // Caller-owned buffers of one call on a [rows, cols] tensor.
 struct NvFp4ActivationBuffers {
   std::uint32_t* scratch = nullptr;       // nvfp4_activation_scratch_words(rows, rows_per_scale) words
@@ -22,6 +34,12 @@ struct NvFp4ActivationBuffers {
   std::uint8_t* codes = nullptr;          // rows * cols / 2 bytes, even column in the low nibble
   std::uint8_t* block_scales = nullptr;   // rows * cols / 16 E4M3 bytes, row-major, un-swizzled
 };
+
+// Block scales re-laid out in the 128 x 4 tiles block-scaled tensor-core MMA reads (see q3x_b200.h).
+[[nodiscard]] std::size_t nvfp4_swizzled_block_scale_bytes(std::size_t rows, std::size_t cols) noexcept;
+[[nodiscard]] int launch_nvfp4_swizzle_block_scales_cuda(const std::uint8_t* row_major, std::size_t rows,
+                                                         std::size_t cols, std::uint8_t* swizzled,
+                                                         void* cuda_stream = nullptr) noexcept;
 
 [[nodiscard]] std::size_t nvfp4_activation_scale_groups(std::size_t rows, std::size_t rows_per_scale) noexcept;
 [[nodiscard]] std::size_t nvfp4_activation_scratch_words(std::size_t rows, std::size_t rows_per_scale) noexcept;

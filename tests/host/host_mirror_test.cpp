@@ -176,6 +176,17 @@ static void test_nvfp4_front_end() {
   EXPECT(qz::nvfp4_activation_scale_groups(16384, 512) == 32 && qz::nvfp4_activation_scale_groups(513, 512) == 2 &&
          qz::nvfp4_activation_scale_groups(7, 0) == 1 && qz::nvfp4_activation_scale_groups(0, 512) == 0);
   EXPECT(qz::nvfp4_activation_scratch_words(16384, 512) >= 2 * 32 + 2);
+  auto* p8 = reinterpret_cast<std::uint8_t*>(0x50000000);
+  // the reference's status vocabulary (include/q3x/quantization/nvfp4.h:41-46)
+  EXPECT(static_cast<int>(qz::NvFp4Status::kInvalidColumnCount) == 2 && static_cast<int>(qz::NvFp4Status::kSizeOverflow) == 3);
+  EXPECT(qz::validate_nvfp4_activation_shape(512, 5120) == qz::NvFp4Status::kSuccess);
+  EXPECT(qz::validate_nvfp4_activation_shape(512, 5128) == qz::NvFp4Status::kInvalidColumnCount);
+  EXPECT(qz::validate_nvfp4_activation_shape(static_cast<std::size_t>(-1) / 32, 64) == qz::NvFp4Status::kSizeOverflow);
+  EXPECT(qz::nvfp4_status_string(qz::NvFp4Status::kSuccess)[0] == 's');
+  // 128 x 4 scale tiles: 512 rows x 5120 columns = 4 row tiles x 80 block tiles; ragged edges round up
+  EXPECT(qz::nvfp4_swizzled_block_scale_bytes(512, 5120) == 4 * 80 * 512);
+  EXPECT(qz::nvfp4_swizzled_block_scale_bytes(130, 48) == 2 * 1 * 512);
+  EXPECT(qz::launch_nvfp4_swizzle_block_scales_cuda(p8, 4, 24, p8 + 0x100000) == 1);  // not a block multiple
   // empty shapes succeed with null buffers; bad shapes and missing buffers are refused on the host
   EXPECT(qz::launch_silu_mul_nvfp4_cuda(nullptr, nullptr, 0, 17408, 512, nullptr, {}) == 0);
   EXPECT(qz::launch_silu_mul_nvfp4_cuda(p, p + 0x1000000, 4, 17400, 512, p + 0x2000000, b) == 1);   // not a block multiple

@@ -376,3 +376,26 @@ def test_one_scratch_serves_calls_of_any_shape_and_the_error_word_is_sticky(g):
         g.assert_bits_equal(codes.get(), want_c, f"{kind} {tokens}/{rps}: codes")
         g.assert_bits_equal(scales.get(), want_s, f"{kind} {tokens}/{rps}: scales")
         assert np.array_equal(gs.get().view(np.uint32), want_g.view(np.uint32)), f"{kind} {tokens}/{rps}: global scales"
+
+
+@pytest.mark.parametrize("rows,cols", [(1, 16), (33, 80), (128, 64), (130, 5120), (512, 6144), (700, 17408)])
+def test_swizzled_block_scale_layout_is_a_permutation_of_the_row_major_bytes(g, rows, cols):
+    """The 128 x 4 tile layout block-scaled tensor-core MMA reads, against a numpy re-layout of the same
+    row-major bytes: every byte lands at tile (r / 128, b / 4), offset (r % 32) * 16 + (r % 128 / 32) * 4 + b % 4;
+    the ragged edges are zero."""
+    rng = np.random.default_rng([rows, cols, 66])
+    blocks = cols // 16
+    src = rng.integers(1, 256, size=(rows, blocks), dtype=np.uint8)
+    nbytes = g.capi.lib().q3x_b200_nvfp4_swizzled_scale_bytes(rows, cols)
+    row_tiles, block_tiles = -(-rows // 128), -(-blocks // 4)
+    assert nbytes == row_tiles * block_tiles * 512
+    out = g.empty_like_dev((nbytes,), dtype=np.uint8, fill=0xEE)
+    g.capi.check("q3x_b200_nvfp4_swizzle_block_scales", g.Dev(src), rows, cols, out, None)
+    g.sync()
+    want = np.zeros(nbytes, np.uint8)
+    r, b = np.meshgrid(np.arange(rows), np.arange(blocks), indexing="ij")
+    off = ((r // 128) * block_tiles + b // 4) * 512 + (r % 32) * 16 + (r % 128) // 32 * 4 + b % 4
+    want[off.reshape(-1)] = src.reshape(-1)
+    g.assert_bits_equal(out.get(), want, "swizzled block scales")
+    assert out.guards_intact()
+    assert np.array_equal(np.sort(out.get()[out.get() != 0]), np.sort(src.reshape(-1)))  # a permutation plus zero padding
