@@ -218,6 +218,48 @@ class LayerStack:
                    Q_HEADS * HEAD_DIM, CHUNK, self.attn_out, self.amax, self.global_scales, self.gdn_codes,
                    self.gdn_scales, stream)
 
+    def enqueue_step_branched(self, main, side_a, side_b) -> int:
+        """The same step with the operators that do not depend on one another placed on three streams
+        (torch.cuda.Stream objects): the residual stream's chain of residual + norm + NVFP4 operators stays on
+        `main` (it is the only true dependency chain between the operators of this path: every other operator
+        reads projection outputs), the mixer operators of a layer (conv + gated norm, or pre-processing + sigmoid
+        gate) go to `side_a` and SwiGLU to `side_b`.  Captured into a CUDA graph this gives three parallel
+        branches, which is what a batch-one (launch-latency-bound) step wants; the two norm operators of a layer
+        do not share their NVFP4 scratch with the side branches (those get scratch of their own).  Returns the
+        index of the residual buffer that holds the final residual stream."""
+        import torch
+
+        if not hasattr(self, "amax_side"):
+            self.amax_side = torch.zeros_like(self.amax)
+            self.global_scales_side = torch.empty_like(self.global_scales)
+        fork = torch.cuda.Event()
+        fork.record(main)
+        side_a.wait_event(fork)
+        side_b.wait_event(fork)
+        m, a, b = main.cuda_stream, side_a.cuda_stream, side_b.cuda_stream
+        self.op_embedding(m)
+        cur = 0
+        for layer in range(self.layers):
+            self.op_residual_norm(layer, 0, cur, 1 - cur, m)
+            cur = 1 - cur
+            if is_full_attention(layer):
+                self.op_preprocess(layer, a)
+                self.op_sigmoid_gate(a)
+            else:
+                self.op_conv(layer, a)
+                capi.check("q3x_b200_rms_norm_silu_gate_nvfp4", self.inputs["gdn_core"], self.gdn_norm_w[layer],
+                           self.inputs["gdn_z"], self.tokens, 48, 128, EPS, CHUNK, self.gdn_out, self.amax_side,
+                           self.global_scales_side, self.gdn_codes, self.gdn_scales, a)
+            self.op_residual_norm(layer, 1, cur, 1 - cur, m)
+            cur = 1 - cur
+            self.op_swiglu(b)
+        join_a, join_b = torch.cuda.Event(), torch.cuda.Event()
+        join_a.record(side_a)
+        join_b.record(side_b)
+        main.wait_event(join_a)
+        main.wait_event(join_b)
+        return cur
+
     # ---- the whole step ------------------------------------------------------------------------
     def enqueue_step(self, stream) -> int:
         """Embedding gather + every layer's chain on `stream` (a raw cudaStream_t).  Returns the
