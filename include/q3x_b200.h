@@ -217,10 +217,9 @@ int q3x_b200_sigmoid_gate_nvfp4(const uint16_t* value, const uint16_t* gate, siz
                                 uint8_t* scales, void* stream);
 
 /* No counterpart in the reference.  q3x_b200_residual_add_rms_norm_nvfp4 for callers that cannot
- * hand over scratch memory because they cannot allocate any: code that runs while a stream is being
- * captured into a CUDA graph or inside a stream callback, a plugin whose host gives it the input
- * and output tensors and nothing more, a service whose device allocator is closed once it is
- * serving.  The scratch words are a fixed array inside the library (64 KB of device memory on
+ * hand over scratch memory because they cannot allocate any: code that runs inside a stream
+ * callback, a plugin whose host gives it the input and output tensors and nothing more, a service
+ * whose device allocator is closed once it is serving.  The scratch words are a fixed array inside the library (64 KB of device memory on
  * every GPU that loads the library, held until the process exits), so there is no `scratch`
  * argument; inputs and outputs are still the caller's.
  *   - tokens must not exceed Q3X_B200_STATIC_SCRATCH_MAX_TOKENS (and the scale groups must fit the
@@ -228,8 +227,7 @@ int q3x_b200_sigmoid_gate_nvfp4(const uint16_t* value, const uint16_t* gate, siz
  *     cudaErrorInvalidValue before anything is enqueued.  q3x_b200_static_scratch_max_tokens()
  *     returns the limit of the library actually loaded.
  *   - The call allocates nothing and frees nothing.  The FIRST call on a device looks up the
- *     array's device address (once per device, with that device current); make that first call
- *     before any stream capture begins.
+ *     array's device address (once per device, with that device current).
  *   - All calls share the one array and it keeps the previous call's contents; each call clears
  *     the words it uses, on `stream`, before its kernels.  Two calls that overlap on the GPU
  *     (different streams, or graphs replayed concurrently) race on it: keep them ordered.

@@ -596,7 +596,7 @@ extern "C" int q3x_b200_rms_norm_silu_gate_nvfp4_single_pass(const uint16_t* in,
 // Residual add + RMSNorm + NVFP4 for callers that cannot allocate device memory.
 //
 // The regular entry point takes its scratch words from the caller.  Some callers have no way to
-// provide them: code running inside a CUDA-graph capture or a stream callback, a plugin that is
+// provide them: code running inside a stream callback, a plugin that is
 // handed input and output tensors by its host and nothing else, a real-time loop whose allocator
 // is closed after start-up.  For them the scratch lives in the library itself, in the device array
 // below; every GPU that loads the library carries these 64 KB until the process exits.

@@ -267,6 +267,16 @@ int launch_gated_delta_net_update_tile_warp_parallel_cuda(const std::uint16_t* c
                                                            state_output, l2_epsilon, output, dimensions, stream);
 }
 
+int gdn_decode_detail::launch_gated_delta_net_update_plain_rms_norm_silu_gate_exact_cuda(
+    const std::uint16_t* conv_qkv, const std::uint16_t* a, const std::uint16_t* b, const std::uint16_t* A_log,
+    const std::uint16_t* dt_bias, const std::uint16_t* state_input, std::uint16_t* state_output, float l2_epsilon,
+    const std::uint16_t* norm_weight, const std::uint16_t* silu_gate, float norm_epsilon, std::uint16_t* output,
+    void* stream) noexcept {
+  return q3x_b200_gated_delta_net_update_rms_norm_silu_gate(conv_qkv, 1U, a, b, A_log, dt_bias, state_input,
+                                                            state_output, l2_epsilon, norm_weight, silu_gate,
+                                                            norm_epsilon, output, stream);
+}
+
 int launch_gated_delta_net_update_plain_rms_norm_silu_gate_cuda(
     const std::uint16_t* conv_qkv, const std::uint16_t* a, const std::uint16_t* b, const std::uint16_t* A_log,
     const std::uint16_t* dt_bias, const std::uint16_t* state_input, std::uint16_t* state_output, float l2_epsilon,
@@ -297,6 +307,16 @@ int launch_causal_conv1d_silu_update_token_parallel_compact_qk_exact_cuda(
     std::uint16_t* out, float l2_epsilon, std::uint16_t* compact_q, std::uint16_t* compact_k, void* stream) noexcept {
   if (tokens == 0U || tokens > kMaximumTokenCount || raw == out) return kInvalidValue;
   // q carries the extra 1 / sqrt(128) in this layout (gdn_prefill_whole_span_conv_sm87.cu:355-357)
+  return q3x_b200_causal_conv1d_silu_compact_qk(raw, tokens, weight, history, out, l2_epsilon, 0.08838834764831845F,
+                                                compact_q, compact_k, stream);
+}
+
+int launch_causal_conv1d_silu_update_prompt_wide_p40_compact_qk_exact_cuda(
+    const std::uint16_t* raw, std::size_t tokens, const std::uint16_t* weight, std::uint16_t* history,
+    std::uint16_t* out, float l2_epsilon, std::uint16_t* compact_q, std::uint16_t* compact_k, void* stream) noexcept {
+  // admits exactly the prompt-wide length (gdn_prefill_whole_span_conv_sm87.cu:612-619); here it is one launch of
+  // the same kernel as every other length
+  if (tokens != kPromptWideP40TokenCount || raw == out) return kInvalidValue;
   return q3x_b200_causal_conv1d_silu_compact_qk(raw, tokens, weight, history, out, l2_epsilon, 0.08838834764831845F,
                                                 compact_q, compact_k, stream);
 }

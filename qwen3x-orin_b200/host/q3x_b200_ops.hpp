@@ -204,6 +204,14 @@ struct GdnDimensions {
     const std::uint16_t* A_log, const std::uint16_t* dt_bias, const std::uint16_t* state_input,
     std::uint16_t* state_output, float l2_epsilon, std::uint16_t* output, GdnDimensions dimensions = {},
     void* cuda_stream = nullptr) noexcept;
+namespace gdn_decode_detail {
+// gdn_decode.h:152-168: the exact-shape (one token, 48 heads of 128) form behind the composite below
+[[nodiscard]] int launch_gated_delta_net_update_plain_rms_norm_silu_gate_exact_cuda(
+    const std::uint16_t* conv_qkv, const std::uint16_t* a, const std::uint16_t* b, const std::uint16_t* A_log,
+    const std::uint16_t* dt_bias, const std::uint16_t* state_input, std::uint16_t* state_output, float l2_epsilon,
+    const std::uint16_t* norm_weight, const std::uint16_t* silu_gate, float norm_epsilon, std::uint16_t* output,
+    void* cuda_stream = nullptr) noexcept;
+}  // namespace gdn_decode_detail
 [[nodiscard]] int launch_gated_delta_net_update_plain_rms_norm_silu_gate_cuda(
     const std::uint16_t* conv_qkv, const std::uint16_t* a, const std::uint16_t* b, const std::uint16_t* A_log,
     const std::uint16_t* dt_bias, const std::uint16_t* state_input, std::uint16_t* state_output, float l2_epsilon,
@@ -215,6 +223,12 @@ namespace gdn_prefill_whole_span_conv_detail {
 inline constexpr std::size_t kMaximumTokenCount = 512U;
 // src/kernels/reference/gdn_prefill_whole_span_conv_sm87.h:59-67
 [[nodiscard]] int launch_causal_conv1d_silu_update_token_parallel_compact_qk_exact_cuda(
+    const std::uint16_t* raw_qkv, std::size_t token_count, const std::uint16_t* conv_weight,
+    std::uint16_t* history_in_out, std::uint16_t* conv_qkv_output, float l2_epsilon, std::uint16_t* compact_q,
+    std::uint16_t* compact_k, void* cuda_stream = nullptr) noexcept;
+// :69-80: the same operator for the one prompt length (40000 tokens) of the reference's prompt-wide chunk graph
+inline constexpr std::size_t kPromptWideP40TokenCount = 40'000U;
+[[nodiscard]] int launch_causal_conv1d_silu_update_prompt_wide_p40_compact_qk_exact_cuda(
     const std::uint16_t* raw_qkv, std::size_t token_count, const std::uint16_t* conv_weight,
     std::uint16_t* history_in_out, std::uint16_t* conv_qkv_output, float l2_epsilon, std::uint16_t* compact_q,
     std::uint16_t* compact_k, void* cuda_stream = nullptr) noexcept;

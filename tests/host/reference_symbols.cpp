@@ -46,12 +46,15 @@ int main() {
       reinterpret_cast<const void*>(&conv::launch_causal_conv1d_silu_update_whole_span_exact_cuda),
       reinterpret_cast<const void*>(&conv::launch_causal_conv1d_silu_update_token_parallel_exact_cuda),
       reinterpret_cast<const void*>(&conv::launch_causal_conv1d_silu_update_token_parallel_compact_qk_exact_cuda),
+      reinterpret_cast<const void*>(&conv::launch_causal_conv1d_silu_update_prompt_wide_p40_compact_qk_exact_cuda),
       // the operators between the fused layer ops
       reinterpret_cast<const void*>(&rt::launch_gated_delta_net_update_reference_cuda),
       reinterpret_cast<const void*>(&rt::launch_gated_delta_net_update_tile_reference_cuda),
       reinterpret_cast<const void*>(&rt::launch_gated_delta_net_update_warp_parallel_cuda),
       reinterpret_cast<const void*>(&rt::launch_gated_delta_net_update_tile_warp_parallel_cuda),
       reinterpret_cast<const void*>(&rt::launch_gated_delta_net_update_plain_rms_norm_silu_gate_cuda),
+      reinterpret_cast<const void*>(
+          &rt::gdn_decode_detail::launch_gated_delta_net_update_plain_rms_norm_silu_gate_exact_cuda),
       reinterpret_cast<const void*>(&rt::supports_gated_delta_net_update_plain_rms_norm_silu_gate_fusion),
       reinterpret_cast<const void*>(&rt::launch_softmax_reference_cuda),
       reinterpret_cast<const void*>(&rt::gqa_attention_splitkv_sigmoid_gate_24_4_256_workspace_elements),

@@ -1,8 +1,7 @@
 """The entry point for callers that cannot allocate device memory
 (q3x_b200_residual_add_rms_norm_nvfp4_static_scratch): its scratch words live in a fixed device
 array inside the library instead of coming from the caller.  Such callers are, for example, code
-running during a CUDA-graph capture or in a stream callback, and plugins that only ever receive
-their input and output tensors.
+running in a stream callback, and plugins that only ever receive their input and output tensors.
 
 The test calls it through the C ABI twice in a row on different inputs (the array keeps the first
 call's contents, so the second call shows that stale words do no harm) and requires every output to
