@@ -83,6 +83,8 @@ __global__ void __launch_bounds__(kPreThreads) attention_preprocess_kernel(
     const uint4* __restrict__ q_gate, uint4* key, const uint4* __restrict__ q_weight,
     const uint4* __restrict__ k_weight, float eps, uint4* __restrict__ q_out, uint4* __restrict__ gate_out,
     const float* __restrict__ cosines, const float* __restrict__ sines, size_t first_position, size_t tokens) {
+  release_next_kernel();
+  wait_for_prior_kernels();
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   const bool is_q = warp < kPreWarps - 1;
@@ -209,11 +211,12 @@ extern "C" int q3x_b200_full_attention_preprocess(const uint16_t* interleaved_q_
       !aligned16(q_out) || !aligned16(gate_out) || !aligned16(cosines) || !aligned16(sines))
     return kNotSupported;
   clear_stale_error();
-  attention_preprocess_kernel<<<wave_grid(attention_preprocess_kernel, kPreThreads, tokens, 1), kPreThreads, 0,
-                                as_stream(stream)>>>(
-      reinterpret_cast<const uint4*>(interleaved_q_gate), reinterpret_cast<uint4*>(key),
-      reinterpret_cast<const uint4*>(q_weight), reinterpret_cast<const uint4*>(k_weight), eps,
-      reinterpret_cast<uint4*>(q_out), reinterpret_cast<uint4*>(gate_out), cosines, sines, first_position, tokens);
+  const unsigned grid = wave_grid(attention_preprocess_kernel, kPreThreads, tokens, 1);
+  launch_kernel(attention_preprocess_kernel, grid, kPreThreads, 0, as_stream(stream), latency_bound_launch(grid),
+                reinterpret_cast<const uint4*>(interleaved_q_gate), reinterpret_cast<uint4*>(key),
+                reinterpret_cast<const uint4*>(q_weight), reinterpret_cast<const uint4*>(k_weight), eps,
+                reinterpret_cast<uint4*>(q_out), reinterpret_cast<uint4*>(gate_out), cosines, sines, first_position,
+                tokens);
   return launch_status();
 }
 

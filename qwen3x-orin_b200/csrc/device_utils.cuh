@@ -91,6 +91,16 @@ __device__ __forceinline__ uint4 ld_l2(const void* p) {
 }
 __device__ __forceinline__ void st_u32(void* p, uint32_t v) { *reinterpret_cast<uint32_t*>(p) = v; }
 
+// ---------------------------------------------------------------------------- kernel overlap
+// Programmatic dependent launch, for the batch-one operators whose cost is mostly the gap between two
+// kernels.  A kernel launched with the stream-serialisation attribute (host::launch_kernel) may start
+// while the kernel before it in the stream is still running; wait_for_prior_kernels() then blocks until
+// that kernel has completed and its writes are visible, and it must come before the kernel's first
+// access to global memory.  release_next_kernel() lets the NEXT kernel of the stream start early (it will
+// sit in its own wait).  Both are no-ops in a kernel launched the ordinary way.
+__device__ __forceinline__ void wait_for_prior_kernels() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void release_next_kernel() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---------------------------------------------------------------------------- reductions
 
 template <int LANES>

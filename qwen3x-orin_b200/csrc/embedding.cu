@@ -19,6 +19,8 @@ __global__ void __launch_bounds__(kThreads) embedding_rows_kernel(const uint4* _
                                                                   int row_vectors,
                                                                   const uint32_t* __restrict__ token_ids,
                                                                   size_t single_id, uint4* __restrict__ out) {
+  release_next_kernel();
+  wait_for_prior_kernels();
   const size_t token = blockIdx.x;
   // token_ids == nullptr: one row whose id was passed by value (the single-token decode form)
   const size_t id = token_ids != nullptr ? static_cast<size_t>(__ldg(token_ids + token)) : single_id;
@@ -67,10 +69,8 @@ int launch_embedding(const uint16_t* table, size_t vocab, size_t hidden, const u
     const int row_vectors = static_cast<int>(hidden / 8);
     auto T = reinterpret_cast<const uint4*>(table);
     auto O = reinterpret_cast<uint4*>(out);
-    if (row_vectors > 3 * kThreads)
-      embedding_rows_kernel<5><<<grid, kThreads, 0, s>>>(T, vocab, row_vectors, token_ids, single_id, O);
-    else
-      embedding_rows_kernel<2><<<grid, kThreads, 0, s>>>(T, vocab, row_vectors, token_ids, single_id, O);
+    launch_kernel(row_vectors > 3 * kThreads ? embedding_rows_kernel<5> : embedding_rows_kernel<2>, grid, kThreads, 0, s,
+                  latency_bound_launch(grid), T, vocab, row_vectors, token_ids, single_id, O);
   } else {
     embedding_rows_scalar_kernel<<<grid, kThreads, 0, s>>>(table, vocab, hidden, token_ids, single_id, out);
   }

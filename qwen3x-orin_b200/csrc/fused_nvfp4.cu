@@ -156,19 +156,13 @@ __device__ __forceinline__ void retire_group(const Board& board, size_t group, u
   }
 }
 
-// Quantises one normalised row (out of L2) under the global scale of `amax_bits`.  Thread tid owns
-// vectors tid + k * TEAM; the loads are issued first and are in flight while the reciprocal table of
-// the global scale is built.
+// Quantises one normalised row, held in registers (thread tid owns vectors tid + k * TEAM), under the global
+// scale of `amax_bits`.
 template <int TEAM, int VPT, bool FAST>
-__device__ __forceinline__ void quantize_row(const uint4* row_in, int row_vectors, uint32_t amax_bits, TeamShared& ts,
-                                             uint32_t* codes_row, uint8_t* scales_row, bool wide_scale_stores) {
+__device__ __forceinline__ void quantize_held(const uint4 (&y)[VPT], int row_vectors, uint32_t amax_bits,
+                                              TeamShared& ts, uint32_t* codes_row, uint8_t* scales_row,
+                                              bool wide_scale_stores) {
   const int tid = threadIdx.x;
-  uint4 y[VPT];
-#pragma unroll
-  for (int i = 0; i < VPT; ++i) {
-    const int v = tid + i * TEAM;
-    y[i] = FAST || v < row_vectors ? ld_l2(row_in + v) : make_uint4(0, 0, 0, 0);
-  }
   const float global = global_scale_from_amax_bits(amax_bits);
   const float k = block_scale_factor(global);
   if (tid < 128) ts.inv_table[tid] = block_inverse(static_cast<uint32_t>(tid), global);
@@ -195,6 +189,21 @@ __device__ __forceinline__ void quantize_row(const uint4* row_in, int row_vector
     if (tid < row_vectors / 32)
       st_vec(reinterpret_cast<uint4*>(scales_row) + tid, reinterpret_cast<const uint4*>(ts.scale_bytes)[tid]);
   }
+}
+
+// The same for a row that waits in L2: the loads are issued first and are in flight while the reciprocal
+// table of the global scale is built.
+template <int TEAM, int VPT, bool FAST>
+__device__ __forceinline__ void quantize_row(const uint4* row_in, int row_vectors, uint32_t amax_bits, TeamShared& ts,
+                                             uint32_t* codes_row, uint8_t* scales_row, bool wide_scale_stores) {
+  const int tid = threadIdx.x;
+  uint4 y[VPT];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = tid + i * TEAM;
+    y[i] = FAST || v < row_vectors ? ld_l2(row_in + v) : make_uint4(0, 0, 0, 0);
+  }
+  quantize_held<TEAM, VPT, FAST>(y, row_vectors, amax_bits, ts, codes_row, scales_row, wide_scale_stores);
 }
 
 // Phase B proper: waits for the group of `row`, publishes its global scale (first row only), quantises.
@@ -224,15 +233,18 @@ __device__ __forceinline__ void phase_b(const uint4* normalized, int row_vectors
 }
 
 // Phase A of the residual operator on one row: residual add, rounding, centred RMSNorm, both stores.
-// Returns the calling thread's share of the row's amax (see amax8_float).
-template <int TEAM, int VPT, bool FAST>
+// Returns the calling thread's share of the row's amax (see amax8_float).  SINGLE: the form for a CTA that
+// handles a row or two and nothing else -- the weights are requested together with the row (a fresh CTA
+// finds them in L2, not in L1, and would otherwise wait for them after the reduction) and `held` receives
+// the thread's normalised vectors (zeros beyond the row).
+template <int TEAM, int VPT, bool FAST, bool SINGLE = false>
 __device__ __forceinline__ float residual_norm_row(const uint4* left, const uint4* right,
                                                    const uint4* __restrict__ weight, size_t row, int row_vectors,
                                                    float width, float eps, uint4* residual_out, uint4* normalized_out,
-                                                   bool coherent, TeamShared& ts) {
+                                                   bool coherent, TeamShared& ts, uint4* held = nullptr) {
   const int tid = threadIdx.x;
   const size_t base = row * static_cast<size_t>(row_vectors);
-  uint4 x[VPT], r[VPT];
+  uint4 x[VPT], r[VPT], w[SINGLE ? VPT : 1];
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const int v = tid + i * TEAM;
@@ -251,6 +263,13 @@ __device__ __forceinline__ float residual_norm_row(const uint4* left, const uint
     } else {
       r[i] = make_uint4(0, 0, 0, 0);
       if (v < row_vectors) r[i] = coherent ? ld_vec(right + base + v) : ld_stream(right + base + v);
+    }
+  }
+  if (SINGLE) {
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int v = tid + i * TEAM;
+      w[i] = v < row_vectors ? ld_weight(weight + v) : make_uint4(0, 0, 0, 0);
     }
   }
   float partial = 0.0f;
@@ -272,9 +291,12 @@ __device__ __forceinline__ float residual_norm_row(const uint4* left, const uint
   for (int i = 0; i < VPT; ++i) {
     const int v = tid + i * TEAM;
     if (FAST || v < row_vectors) {
-      const uint4 y = scale8<NormMode::kCentered, true>(x[i], ld_weight(weight + v), make_uint4(0, 0, 0, 0), inv,
-                                                        &top);
+      const uint4 gamma = SINGLE ? w[i] : ld_weight(weight + v);
+      const uint4 y = scale8<NormMode::kCentered, true>(x[i], gamma, make_uint4(0, 0, 0, 0), inv, &top);
       st_vec(normalized_out + base + v, y);  // this is what phase B finds in L2
+      if (SINGLE) held[i] = y;
+    } else if (SINGLE) {
+      held[i] = make_uint4(0, 0, 0, 0);
     }
   }
   return top;
@@ -304,7 +326,8 @@ __global__ void __launch_bounds__(TEAM, min_ctas_per_sm(TEAM, VPT)) residual_nor
 // Phase A of the gated-norm operator on one token: per-head RMSNorm * weight * silu(z), store.
 template <int TEAM, int VPT, bool FAST>
 __device__ __forceinline__ float gated_norm_row(const uint4* in, const uint4* gate, const uint4* __restrict__ weight,
-                                                size_t row, int row_vectors, float eps, uint4* out, bool coherent) {
+                                                size_t row, int row_vectors, float eps, uint4* out, bool coherent,
+                                                uint4* held = nullptr) {
   const int tid = threadIdx.x;
   const size_t base = row * static_cast<size_t>(row_vectors);
   const uint4 w = ld_weight(weight + (tid & 15));
@@ -332,6 +355,9 @@ __device__ __forceinline__ float gated_norm_row(const uint4* in, const uint4* ga
     if (FAST || v < row_vectors) {
       const uint4 y = scale8<NormMode::kPlainSiluGate, true>(x[i], w, z[i], inv, &top);
       st_vec(out + base + v, y);
+      if (held != nullptr) held[i] = y;
+    } else if (held != nullptr) {
+      held[i] = make_uint4(0, 0, 0, 0);
     }
   }
   return top;
@@ -355,18 +381,20 @@ __global__ void __launch_bounds__(TEAM, min_ctas_per_sm(TEAM, VPT)) gated_norm_n
 }
 
 // ---- a handful of rows (decode) ------------------------------------------------------------------
-// Up to kSmallRows rows: one CTA per scale group walks its rows twice -- normalise them all, reduce the
-// group amax inside the CTA, quantise them all -- so nothing crosses CTAs: no counters, no waits, and
-// the scratch is not touched at all.
+// Up to kSmallRows rows: one CTA per scale group normalises its rows, keeps the results in registers,
+// reduces the group amax inside the CTA and quantises what it holds -- nothing crosses CTAs: no counters,
+// no waits, the scratch is not touched at all, and the normalised rows are not read back.
 // Measured per call inside a CUDA graph: 4.3 us against 8.2 us for one row; from four rows on the rows'
 // serial walk costs more than the cleared scratch, so the limit is two.
+// The kernel may be launched to overlap the end of the kernel before it in the stream (programmatic
+// dependent launch): it touches no memory before wait_for_prior_kernels().
 constexpr size_t kSmallRows = 2;
 
 template <int WARPS>
 __device__ __forceinline__ uint32_t cta_amax_bits(TeamShared& ts, float thread_top) {
   const uint32_t warp_top = group_max_u32<32>(amax_bits_of(thread_top));
   if ((threadIdx.x & 31) == 0) ts.tops[threadIdx.x >> 5] = warp_top;
-  __syncthreads();  // also makes this CTA's stores of the rows visible to all of its threads
+  __syncthreads();
   uint32_t m = 0;
 #pragma unroll
   for (int w = 0; w < WARPS; ++w) m = max(m, ts.tops[w]);
@@ -380,23 +408,33 @@ __global__ void __launch_bounds__(TEAM) small_norm_nvfp4_kernel(const uint4* a, 
                                                                  uint4* out, bool coherent, size_t rows,
                                                                  size_t group_rows, float* global_out, QuantOut q) {
   __shared__ TeamShared ts;
+  release_next_kernel();
+  wait_for_prior_kernels();
   const size_t first = blockIdx.x * group_rows;
-  const size_t last = min(rows, first + group_rows);
+  const size_t last = min(rows, first + group_rows);  // at most kSmallRows rows
+  uint4 held[kSmallRows][VPT];
   float top = 0.0f;
-  for (size_t row = first; row < last; ++row) {
-    const float t = GATED ? gated_norm_row<TEAM, VPT, false>(a, b, weight, row, row_vectors, eps, out, coherent)
-                          : residual_norm_row<TEAM, VPT, false>(a, b, weight, row, row_vectors, width, eps,
-                                                                residual_out, out, coherent, ts);
-    top = fmaxf(top, t);
-    __syncthreads();  // the reduction scratch is reused by the next row
+#pragma unroll
+  for (size_t r = 0; r < kSmallRows; ++r) {
+    const size_t row = first + r;
+    if (row < last) {
+      const float t = GATED ? gated_norm_row<TEAM, VPT, false>(a, b, weight, row, row_vectors, eps, out, coherent, held[r])
+                            : residual_norm_row<TEAM, VPT, false, true>(a, b, weight, row, row_vectors, width,
+                                                                        eps, residual_out, out, coherent, ts, held[r]);
+      top = fmaxf(top, t);
+      __syncthreads();  // the reduction scratch is reused by the next row
+    }
   }
   const uint32_t amax_bits = cta_amax_bits<TEAM / 32>(ts, top);
   if (threadIdx.x == 0) global_out[blockIdx.x] = global_scale_from_amax_bits(amax_bits);
-  for (size_t row = first; row < last; ++row) {
-    quantize_row<TEAM, VPT, false>(out + row * static_cast<size_t>(row_vectors), row_vectors, amax_bits, ts,
-                                   q.codes + row * static_cast<size_t>(row_vectors),
-                                   q.scales + row * static_cast<size_t>(row_vectors / 2), q.wide_scale_stores);
-    __syncthreads();  // the reciprocal table and the scale bytes are reused by the next row
+#pragma unroll
+  for (size_t r = 0; r < kSmallRows; ++r) {
+    const size_t row = first + r;
+    if (row < last) {
+      quantize_held<TEAM, VPT, false>(held[r], row_vectors, amax_bits, ts, q.codes + row * static_cast<size_t>(row_vectors),
+                                      q.scales + row * static_cast<size_t>(row_vectors / 2), q.wide_scale_stores);
+      __syncthreads();  // the reciprocal table and the scale bytes are reused by the next row
+    }
   }
 }
 
@@ -519,8 +557,8 @@ bool launch_residual_norm_nvfp4_fused(const uint16_t* left, const uint16_t* righ
   if (tokens <= kSmallRows) {
 #define Q3X_SHAPE(TEAM, V)                                                                                      \
   if (row_vectors <= TEAM * V) {                                                                                \
-    small_norm_nvfp4_kernel<TEAM, V, false><<<static_cast<unsigned>(groups), TEAM, 0, s>>>(                     \
-        L, R, W, row_vectors, width, eps, RO, NO, coherent, tokens, rps, global_scales_out, q);                 \
+    launch_kernel(small_norm_nvfp4_kernel<TEAM, V, false>, static_cast<unsigned>(groups), TEAM, 0, s, true,     \
+                  L, R, W, row_vectors, width, eps, RO, NO, coherent, tokens, rps, global_scales_out, q);       \
     return true;                                                                                                \
   }
     Q3X_FUSED_SHAPES
@@ -570,8 +608,9 @@ bool launch_gated_norm_nvfp4_fused(const uint16_t* in, const uint16_t* weight, c
   if (tokens <= kSmallRows) {
 #define Q3X_SHAPE(TEAM, V)                                                                                      \
   if (row_vectors <= TEAM * V) {                                                                                \
-    small_norm_nvfp4_kernel<TEAM, V, true><<<static_cast<unsigned>(groups), TEAM, 0, s>>>(                      \
-        X, Z, W, row_vectors, 128.0f, eps, nullptr, O, coherent, tokens, rps, global_scales_out, q);            \
+    launch_kernel(small_norm_nvfp4_kernel<TEAM, V, true>, static_cast<unsigned>(groups), TEAM, 0, s, true,      \
+                  X, Z, W, row_vectors, 128.0f, eps, static_cast<uint4*>(nullptr), O, coherent, tokens, rps,    \
+                  global_scales_out, q);                                                                        \
     return true;                                                                                                \
   }
     Q3X_FUSED_SHAPES

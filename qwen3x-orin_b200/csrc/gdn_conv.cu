@@ -80,6 +80,8 @@ __global__ void __launch_bounds__(kThreads, kInPlace ? 1 : 4)
     causal_conv_kernel(const uint4* raw, size_t tokens, int channel_vectors, const uint4* __restrict__ weight,
                        uint4* history, uint4* out, ConvPlan plan, float l2_eps, float q_scale,
                        uint4* compact_q = nullptr, uint4* compact_k = nullptr) {
+  release_next_kernel();
+  wait_for_prior_kernels();
   // CTA index -> (channel block, token run); the blocks that carry the L2 norm come first
   unsigned channel_block, run;
   if (blockIdx.x < plan.norm_ctas) {
@@ -359,16 +361,13 @@ int launch_conv(const uint16_t* raw, size_t tokens, size_t channels, const uint1
   auto H = reinterpret_cast<uint4*>(history);
   auto O = reinterpret_cast<uint4*>(out);
   cudaStream_t s = as_stream(stream);
-  if (compact)
-    causal_conv_kernel<true, false, true><<<grid, kThreads, 0, s>>>(R, tokens, channel_vectors, W, H, O, plan, l2_eps,
-                                                                    q_scale, reinterpret_cast<uint4*>(compact_q),
-                                                                    reinterpret_cast<uint4*>(compact_k));
-  else if (l2)
-    causal_conv_kernel<true, false><<<grid, kThreads, 0, s>>>(R, tokens, channel_vectors, W, H, O, plan, l2_eps, q_scale);
-  else if (serial)
-    causal_conv_kernel<false, true><<<grid, kThreads, 0, s>>>(R, tokens, channel_vectors, W, H, O, plan, 0.0f, 1.0f);
-  else
-    causal_conv_kernel<false, false><<<grid, kThreads, 0, s>>>(R, tokens, channel_vectors, W, H, O, plan, 0.0f, 1.0f);
+  auto kernel = compact ? causal_conv_kernel<true, false, true>
+                : l2    ? causal_conv_kernel<true, false>
+                : serial ? causal_conv_kernel<false, true>
+                         : causal_conv_kernel<false, false>;
+  launch_kernel(kernel, grid, kThreads, 0, s, latency_bound_launch(grid.x), R, tokens, channel_vectors, W, H, O, plan,
+                l2 ? l2_eps : 0.0f, l2 ? q_scale : 1.0f, reinterpret_cast<uint4*>(compact_q),
+                reinterpret_cast<uint4*>(compact_k));
   return launch_status();
 }
 

@@ -8,6 +8,7 @@
 #include <cuda_runtime.h>
 
 #include <atomic>
+#include <cstdlib>
 #include <cmath>
 #include <cstddef>
 #include <cstdint>
@@ -56,6 +57,27 @@ constexpr int kInvalid = static_cast<int>(cudaErrorInvalidValue);
 constexpr int kNotSupported = static_cast<int>(cudaErrorNotSupported);
 constexpr int kOk = static_cast<int>(cudaSuccess);
 
+// Kernel launch with an explicit choice of programmatic stream serialisation: with `overlap` the kernel may
+// start before the previous kernel of the stream has finished (it must then call wait_for_prior_kernels()
+// before it touches global memory); without it this is the ordinary <<< >>> launch.  Works under stream
+// capture (the graph gets a programmatic edge).
+template <typename... Params, typename... Args>
+inline void launch_kernel(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                          bool overlap, Args&&... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  static const bool allowed = std::getenv("Q3X_B200_NO_OVERLAP") == nullptr;
+  config.numAttrs = overlap && allowed ? 1u : 0u;
+  (void)cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
+}
+
 // SM count of the current device (cached per device ordinal; 148 on B200).
 inline int current_device_sm_count() {
   constexpr int kMaxDevices = 64;
@@ -69,6 +91,10 @@ inline int current_device_sm_count() {
   }
   return n;
 }
+
+// A launch of at most one CTA per SM costs mostly its start-up and the gap to its neighbours in the stream:
+// such launches are made with programmatic stream serialisation (see launch_kernel).
+inline bool latency_bound_launch(size_t ctas) { return ctas <= static_cast<size_t>(current_device_sm_count()); }
 
 // Grid sizing: enough CTAs to fill the machine a few times over without exceeding what the work
 // needs.  The multiplier is the number of resident CTAs per SM we aim for.

@@ -34,6 +34,8 @@ template <class Op, bool kInPlace>
 __global__ void __launch_bounds__(kThreads) binary_vec_kernel(const uint4* a, const uint4* b, uint4* out,
                                                               size_t nvec) {
   constexpr int kDepth = Op::kDepth;
+  release_next_kernel();
+  wait_for_prior_kernels();
   auto store = [](uint4* p, const uint4& v) {
     if (Op::kStreamingStore) st_stream(p, v);
     else st_vec(p, v);
@@ -160,16 +162,11 @@ int launch_binary(const uint16_t* a, const uint16_t* b, size_t count, uint16_t* 
   size_t done = 0;
   if (aligned16(a) && aligned16(b) && aligned16(out) && count >= 8) {
     const size_t nvec = count / 8;
-    if (in_place)
-      binary_vec_kernel<Op, true><<<wave_grid(binary_vec_kernel<Op, true>, kThreads, nvec, kThreads * Op::kDepth),
-                                    kThreads, 0, s>>>(reinterpret_cast<const uint4*>(a),
-                                                            reinterpret_cast<const uint4*>(b),
-                                                            reinterpret_cast<uint4*>(out), nvec);
-    else
-      binary_vec_kernel<Op, false><<<wave_grid(binary_vec_kernel<Op, false>, kThreads, nvec, kThreads * Op::kDepth),
-                                     kThreads, 0, s>>>(reinterpret_cast<const uint4*>(a),
-                                                             reinterpret_cast<const uint4*>(b),
-                                                             reinterpret_cast<uint4*>(out), nvec);
+    const unsigned grid = in_place ? wave_grid(binary_vec_kernel<Op, true>, kThreads, nvec, kThreads * Op::kDepth)
+                                   : wave_grid(binary_vec_kernel<Op, false>, kThreads, nvec, kThreads * Op::kDepth);
+    launch_kernel(in_place ? binary_vec_kernel<Op, true> : binary_vec_kernel<Op, false>, grid, kThreads, 0, s,
+                  latency_bound_launch(grid), reinterpret_cast<const uint4*>(a), reinterpret_cast<const uint4*>(b),
+                  reinterpret_cast<uint4*>(out), nvec);
     done = nvec * 8;
   }
   if (done < count) {

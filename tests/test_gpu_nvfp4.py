@@ -129,7 +129,7 @@ def test_quantize_round_trip_and_static_scale(g):
 
 
 @pytest.mark.parametrize("tokens,rps", [(1, 0), (2, 0), (2, 1), (7, 0), (7, 512), (33, 16), (512, 512), (513, 512), (1024, 512), (2048, 512),
-                                        (5000, 512), (1500, 0), (3000, 0), (6000, 0)])
+                                        (5000, 512), (8200, 512), (4096, 64), (1500, 0), (3000, 0), (6000, 0)])
 @pytest.mark.parametrize("single_pass", [False, True])
 def test_residual_norm_nvfp4(g, tokens, rps, single_pass):
     hidden = 5120
@@ -173,7 +173,8 @@ def test_residual_norm_nvfp4(g, tokens, rps, single_pass):
         assert d.guards_intact()
 
 
-@pytest.mark.parametrize("tokens,rps", [(1, 0), (2, 512), (2, 1), (9, 4), (512, 512), (600, 512), (2048, 512), (1300, 0), (4000, 0)])
+@pytest.mark.parametrize("tokens,rps", [(1, 0), (2, 512), (2, 1), (9, 4), (512, 512), (600, 512), (2048, 512), (4608, 512), (9001, 512),
+                                        (4100, 96), (1300, 0), (4000, 0)])
 @pytest.mark.parametrize("single_pass", [False, True])
 def test_gated_norm_nvfp4(g, tokens, rps, single_pass):
     heads, dim = 48, 128
