@@ -286,6 +286,48 @@ def test_gemvs(g, rows, cols, misalign):
     assert o32.guards_intact() and o16.guards_intact()
 
 
+@pytest.mark.parametrize("rows,cols", [(40, 5120), (16, 192), (33, 17408)])
+def test_gemvs_over_the_activation_range(g, rows, cols):
+    """The narrow-weight GEMVs over the activation's range: very large, very small and widely spread activations
+    keep the norm-wise accuracy, and non-finite activations give the oracle's non-finite results."""
+    rng = np.random.default_rng([rows, cols, 98])
+    packed = rng.integers(0, 256, size=(rows, cols // 2), dtype=np.uint8)
+    scales = rng.integers(0x18, 0x58, size=(rows, cols // 16), dtype=np.uint8)
+    w8 = rng.integers(0, 256, size=(rows, cols), dtype=np.uint8)
+    w8[(w8 & 0x7F) == 0x7F] = 0x3C
+    L = orc.oracle_lib()
+    e4 = np.array([L.decode_e4m3(i) for i in range(256)], dtype=np.float32)
+    d_p, d_s, d_w8 = g.Dev(packed), g.Dev(scales), g.Dev(w8)
+    o32 = g.empty_like_dev((rows,), dtype=np.float32)
+    base = rng.standard_normal(cols).astype(np.float32)
+    spread = base * np.exp2(rng.integers(-40, 1, size=cols)).astype(np.float32)
+    for name, xf in (("huge", base * np.float32(1e30)), ("tiny", base * np.float32(1e-30)), ("spread", spread),
+                     ("zero", np.zeros(cols, np.float32))):
+        x = orc.bf16_encode(xf)
+        xd = orc.bf16_decode(x).astype(np.float64)
+        d_x = g.Dev(x)
+        g.capi.check("q3x_b200_nvfp4_gemv", d_p, d_s, 0.004, d_x, rows, cols, o32, None, None)
+        g.sync()
+        deq = orc.nvfp4_dequantize(packed, scales, 0.004).astype(np.float64)
+        assert np.all(np.abs(o32.get() - deq @ xd) <= 1e-5 * (np.abs(deq) @ np.abs(xd)) + 1e-37), f"NVFP4, {name} activation"
+        g.capi.check("q3x_b200_fp8_gemv", d_w8, 0.0123, d_x, rows, cols, o32, None, None)
+        g.sync()
+        wf = (e4[w8] * np.float32(0.0123)).astype(np.float64)
+        assert np.all(np.abs(o32.get() - wf @ xd) <= 2e-5 * (np.abs(wf) @ np.abs(xd)) + 1e-37), f"FP8, {name} activation"
+    x = orc.bf16_encode(base)
+    x[5], x[cols - 3] = 0x7F80, 0x7FC0  # +inf and a NaN
+    g.capi.check("q3x_b200_nvfp4_gemv", d_p, d_s, 0.004, g.Dev(x), rows, cols, o32, None, None)
+    g.sync()
+    want = orc.nvfp4_gemv(packed, scales, 0.004, x)
+    assert np.array_equal(np.isnan(o32.get()), np.isnan(want)) and np.all(np.isnan(want))
+    x[cols - 3] = 0x3F80  # only the infinity is left: rows whose weight at column 5 is zero give NaN, the others +-inf
+    g.capi.check("q3x_b200_nvfp4_gemv", d_p, d_s, 0.004, g.Dev(x), rows, cols, o32, None, None)
+    g.sync()
+    want = orc.nvfp4_gemv(packed, scales, 0.004, x)
+    assert np.array_equal(np.isnan(o32.get()), np.isnan(want))
+    assert np.array_equal(o32.get()[~np.isnan(want)], want[~np.isnan(want)])
+
+
 def test_gemv_consumes_the_quantisers_layout(g):
     """Codes and block scales written by the library's own NVFP4 quantiser are the GEMV's weight layout: a
     matrix quantised row-wise by q3x_b200_nvfp4_quantize_dynamic and multiplied by a vector through
