@@ -156,6 +156,26 @@ size_t q3x_b200_nvfp4_swizzled_scale_bytes(size_t rows, size_t cols);
 int q3x_b200_nvfp4_swizzle_block_scales(const uint8_t* row_major, size_t rows, size_t cols, uint8_t* swizzled,
                                         void* stream);
 
+/* The projection that consumes the NVFP4 activations: out[tokens, out_features] (bf16, row-major) =
+ * A x W^T with A = [tokens, in_features] and W = [out_features, in_features] both NVFP4 -- packed E2M1
+ * codes (in_features / 2 bytes per row, even column in the low nibble), block scales in the swizzled layout
+ * above, FP32 second-level scales: one per activation scale group of rows_per_scale rows (0 = one group; with
+ * more than one group rows_per_scale must be a multiple of 128), as the quantiser entry points write them, and
+ * one for the weights.  Runs on the block-scaled tensor cores (FP32 accumulation, one rounding to bf16).
+ * in_features must be a multiple of 64, out_features of 8; pointers 16-byte aligned.  `workspace` holds
+ * q3x_b200_nvfp4_gemm_workspace_bytes(...) bytes (never 0 for a non-empty problem); nothing is allocated.
+ * The reference's prefill projection multiplies bf16 activations with NVFP4 weights
+ * (launch_projection_to_bf16_cuda, include/q3x/runtime/model_weights.h:794-841, kernel
+ * src/kernels/sm87/nvfp4_marlin_w4a16.cu); this is that projection with the activation operand taken from
+ * this library's quantiser, so it has the reference's shape contract but not its numerics. */
+size_t q3x_b200_nvfp4_gemm_workspace_bytes(size_t tokens, size_t out_features, size_t in_features,
+                                           size_t rows_per_scale);
+int q3x_b200_nvfp4_gemm_bf16(const uint8_t* activation_codes, const uint8_t* activation_scales_swizzled,
+                             const float* activation_global_scales, size_t rows_per_scale,
+                             const uint8_t* weight_codes, const uint8_t* weight_scales_swizzled,
+                             float weight_scale_2, size_t tokens, size_t out_features, size_t in_features,
+                             uint16_t* out, void* workspace, size_t workspace_bytes, void* stream);
+
 /* Residual add + centred RMSNorm + NVFP4 of the normalised rows, global scale from the group
  * amax.  normalized_out is required (it is the operand the codes are derived from, bit for
  * bit); it may be exactly `right`.  One kernel that crosses HBM once where a scale group is short

@@ -14,8 +14,11 @@ HOST = os.path.join(PKG, "host")
 LIB = os.path.join(PKG, "libq3x_b200.so")
 HOST_LIB = os.path.join(PKG, "libq3x_b200_host.so")
 
+OBJ = os.path.join(PKG, "_build")
 CUDA_SOURCES = ["pointwise.cu", "row_norms.cu", "attention_preprocess.cu", "gdn_conv.cu", "embedding.cu", "nvfp4.cu",
-                "fused_nvfp4.cu", "gdn_recurrence.cu", "gqa_decode.cu", "logits_ops.cu", "gemv.cu"]
+                "fused_nvfp4.cu", "gdn_recurrence.cu", "gqa_decode.cu", "logits_ops.cu", "gemv.cu", "nvfp4_gemm.cu"]
+# sources instantiated from the CUTLASS / CuTe header tree (found inside an installed Python package, see _cutlass)
+CUTLASS_SOURCES = {"nvfp4_gemm.cu"}
 NVCC_FLAGS = [
     "-std=c++17", "-O3", "-lineinfo",
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -32,6 +35,22 @@ def _nvcc() -> str:
     raise RuntimeError("nvcc not found: the CUDA library cannot be built")
 
 
+def _cutlass() -> str:
+    """Root of a CUTLASS tree (include/ and tools/util/include/) with the sm100 block-scaled collectives:
+    Q3X_B200_CUTLASS, else the tree vendored inside the flashinfer package."""
+    import importlib.util
+
+    candidates = [os.environ.get("Q3X_B200_CUTLASS")]
+    spec = importlib.util.find_spec("flashinfer")
+    if spec is not None and spec.submodule_search_locations:
+        candidates.append(os.path.join(list(spec.submodule_search_locations)[0], "data", "cutlass"))
+    for root in candidates:
+        if root and os.path.exists(os.path.join(root, "include", "cutlass", "gemm", "collective", "builders",
+                                                "sm100_blockscaled_umma_builder.inl")):
+            return root
+    raise RuntimeError("no CUTLASS tree with the sm100 block-scaled builders found (set Q3X_B200_CUTLASS)")
+
+
 def _stale(target: str, sources: list[str]) -> bool:
     if not os.path.exists(target):
         return True
@@ -43,11 +62,26 @@ def build_cuda(force: bool = False, verbose: bool = False) -> str:
     sources = [os.path.join(CSRC, s) for s in CUDA_SOURCES]
     deps = sources + [os.path.join(CSRC, h) for h in os.listdir(CSRC) if h.endswith((".cuh", ".hpp"))]
     deps.append(os.path.join(ROOT, "include", "q3x_b200.h"))
-    if force or _stale(LIB, deps):
-        cmd = [_nvcc(), *NVCC_FLAGS, "-I", os.path.join(ROOT, "include"), "-I", CSRC, "-shared", "-o", LIB, *sources]
-        if verbose:
-            cmd.insert(1, "-Xptxas=-v")
-        subprocess.run(cmd, check=True)
+    headers = deps[len(sources):]
+    os.makedirs(OBJ, exist_ok=True)
+    objects, jobs = [], []
+    for name, src in zip(CUDA_SOURCES, sources):
+        obj = os.path.join(OBJ, name[:-3] + ".o")
+        objects.append(obj)
+        if force or _stale(obj, [src] + headers):
+            cmd = [_nvcc(), *NVCC_FLAGS, "-I", os.path.join(ROOT, "include"), "-I", CSRC, "-c", src, "-o", obj]
+            if name in CUTLASS_SOURCES:
+                root = _cutlass()
+                cmd[1:1] = ["--expt-relaxed-constexpr", "-diag-suppress", "20012", "-I", os.path.join(root, "include"),
+                            "-I", os.path.join(root, "tools", "util", "include")]
+            if verbose:
+                cmd.insert(1, "-Xptxas=-v")
+            jobs.append(subprocess.Popen(cmd))
+    failed = [j.args for j in jobs if j.wait() != 0]
+    if failed:
+        raise RuntimeError(f"nvcc failed: {failed[0]}")
+    if force or jobs or _stale(LIB, objects):
+        subprocess.run([_nvcc(), *NVCC_FLAGS, "-shared", "-o", LIB, *objects], check=True)
     return LIB
 
 
