@@ -568,6 +568,77 @@ def probe_decode_ops(peak, cuda_index=0, aim_ms=60.0):
     return out
 
 
+def probe_projection_ops(cuda_index=0, aim_ms=60.0, tokens=8192):
+    """The prefill projection that consumes the NVFP4 activations (q3x_b200_nvfp4_gemm_bf16: block-scaled tensor
+    cores, one 512-row launch per activation scale group), alone at the model's MLP and GDN-input shapes over a
+    panel of `tokens` rows.  flops = 2 x tokens x out_features x in_features per call; the fractions are against
+    the nominal dense FP4 rate of the part and against the measured dense bf16 GEMM of this pool (the driver
+    measures no FP4 figure), both named in the record."""
+    import torch
+
+    pkg = importlib.import_module("qwen3x-orin_b200")
+    capi = pkg.capi
+    dev = torch.device("cuda", cuda_index)
+    gen = torch.Generator(device=dev).manual_seed(78)
+    stream_obj = torch.cuda.Stream()
+    stream = stream_obj.cuda_stream
+    bf16_peak = None
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            bf16_peak = float(json.load(f)["bf16_tflops"])
+    except Exception:
+        pass
+
+    def u8(shape, lo=0, hi=256):
+        return torch.randint(lo, hi, shape, generator=gen, device=dev, dtype=torch.int32).to(torch.uint8)
+
+    out = {}
+    for name, n, k in (("nvfp4_gemm_17408x5120", 17408, 5120), ("nvfp4_gemm_5120x17408", 5120, 17408),
+                       ("nvfp4_gemm_10240x5120", 10240, 5120)):
+        a_codes, w_codes = u8((tokens, k // 2)), u8((n, k // 2))
+        a_scales = u8((capi.lib().q3x_b200_nvfp4_swizzled_scale_bytes(tokens, k),), 0x28, 0x48)
+        w_scales = u8((capi.lib().q3x_b200_nvfp4_swizzled_scale_bytes(n, k),), 0x28, 0x48)
+        groups = tokens // 512
+        a_gs = torch.full((groups,), 0.01, device=dev, dtype=torch.float32)
+        need = capi.lib().q3x_b200_nvfp4_gemm_workspace_bytes(tokens, n, k, 512)
+        ws = torch.empty(need, device=dev, dtype=torch.uint8)
+        y = torch.empty((tokens, n), device=dev, dtype=torch.bfloat16)
+
+        def call():
+            capi.check("q3x_b200_nvfp4_gemm_bf16", a_codes, a_scales, a_gs, 512, w_codes, w_scales, 0.01, tokens, n, k, y, ws,
+                       need, stream)
+
+        with torch.cuda.stream(stream_obj):
+            call()
+        stream_obj.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream_obj):
+            call()
+        with torch.cuda.stream(stream_obj):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream_obj)
+            graph.replay()
+            e1.record(stream_obj)
+            stream_obj.synchronize()
+            reps = max(3, min(2000, int(math.ceil(aim_ms / max(e0.elapsed_time(e1), 1e-3)))))
+            sampler = ClockSampler(cuda_index)
+            e0.record(stream_obj)
+            for _ in range(reps):
+                graph.replay()
+            e1.record(stream_obj)
+            stream_obj.synchronize()
+            clk = sampler.stop()
+        us = e0.elapsed_time(e1) * 1e3 / reps
+        tflops = 2.0 * tokens * n * k / (us * 1e-6) / 1e12
+        out[name] = {"tokens": tokens, "launches_per_call": 2, "us": round(us, 1), "TFLOPs": round(tflops, 1),
+                     "frac_of_nominal_fp4_dense_9000": round(tflops / 9000.0, 4),
+                     "frac_of_measured_bf16_dense": round(tflops / bf16_peak, 3) if bf16_peak else None,
+                     "sm_mhz": clk.get("sm_mhz"), "reasons": clk.get("reasons")}
+        del a_codes, w_codes, a_scales, w_scales, ws, y
+    torch.cuda.empty_cache()
+    return out
+
+
 def host_memory_available_bytes():
     """What this process may still take from host memory: MemAvailable, capped by the cgroup limit."""
     avail = None
@@ -649,7 +720,8 @@ def main():
     if args.decode_only:
         peak, _ = measured_peak()
         print(json.dumps({"decode_only": True, "decode_step": decode_step_probe(chain),
-                          "decode_ops": probe_decode_ops(peak, local_rank, aim_ms=args.probe_ms / 2)}), flush=True)
+                          "decode_ops": probe_decode_ops(peak, local_rank, aim_ms=args.probe_ms / 2),
+                          "projection_ops": probe_projection_ops(local_rank, aim_ms=args.probe_ms / 2)}), flush=True)
         return 0
 
     total = args.total_tokens or CONFIG_TOKENS[args.config]
@@ -763,6 +835,7 @@ def main():
 
     decode = decode_step_probe(chain) if probing else None
     decode_ops = probe_decode_ops(peak, local_rank, aim_ms=args.probe_ms / 2) if probing else None
+    projection_ops = probe_projection_ops(local_rank, aim_ms=args.probe_ms / 2) if probing else None
     validation = validate_shards(rank, world, dist) if distributed else None
     if rank == 0:
         line = {
@@ -774,6 +847,7 @@ def main():
         }
         line["decode_step"] = decode
         line["decode_ops"] = decode_ops
+        line["projection_ops"] = projection_ops
         if validation is not None:
             line["validation"] = validation
         print(json.dumps(line), flush=True)

@@ -159,9 +159,8 @@ int q3x_b200_nvfp4_swizzle_block_scales(const uint8_t* row_major, size_t rows, s
 /* The projection that consumes the NVFP4 activations: out[tokens, out_features] (bf16, row-major) =
  * A x W^T with A = [tokens, in_features] and W = [out_features, in_features] both NVFP4 -- packed E2M1
  * codes (in_features / 2 bytes per row, even column in the low nibble), block scales in the swizzled layout
- * above, FP32 second-level scales: one per activation scale group of rows_per_scale rows (0 = one group; with
- * more than one group rows_per_scale must be a multiple of 128), as the quantiser entry points write them, and
- * one for the weights.  Runs on the block-scaled tensor cores (FP32 accumulation, one rounding to bf16).
+ * above, FP32 second-level scales: one per activation scale group of rows_per_scale rows (0 = one group), as
+ * the quantiser entry points write them, and one for the weights.  Runs on the block-scaled tensor cores (FP32 accumulation, one rounding to bf16).
  * in_features must be a multiple of 64, out_features of 8; pointers 16-byte aligned.  `workspace` holds
  * q3x_b200_nvfp4_gemm_workspace_bytes(...) bytes (never 0 for a non-empty problem); nothing is allocated.
  * The reference's prefill projection multiplies bf16 activations with NVFP4 weights

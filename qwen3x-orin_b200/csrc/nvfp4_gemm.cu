@@ -11,9 +11,9 @@
 //
 // The kernel is CUTLASS's sm100 block-scaled collective (mainloop and epilogue builders) instantiated here for
 // one tile shape, with a 1 x 1 x 1 cluster: every TMA load is an ordinary one that reads this GPU's own memory.
-// An activation scale group has its own second-level scale, which enters as the epilogue's alpha; one GEMM is
-// enqueued per scale group (a group is 512 rows in the prefill chain, so each launch is a
-// 512 x N x K problem), with alpha read from device memory.
+// An activation scale group has its own second-level scale, so the epilogue's alpha is per ROW: a small kernel
+// expands (group scale x weight scale) to one float per token in the workspace, and one persistent GEMM covers
+// all tokens.
 #include <cuda_runtime.h>
 
 #include <cstddef>
@@ -23,6 +23,8 @@
 #include "cutlass/cutlass.h"
 #include "cutlass/detail/sm100_blockscaled_layout.hpp"
 #include "cutlass/epilogue/collective/collective_builder.hpp"
+#include "cutlass/epilogue/fusion/operations.hpp"
+#include "cutlass/epilogue/thread/activation.h"
 #include "cutlass/gemm/collective/collective_builder.hpp"
 #include "cutlass/gemm/device/gemm_universal_adapter.h"
 #include "cutlass/gemm/kernel/gemm_universal.hpp"
@@ -49,10 +51,14 @@ constexpr int kAlignmentD = 128 / cutlass::sizeof_bits<ElementD>::value;  // 8 b
 using MmaTileShape = Shape<_128, _128, _256>;
 using ClusterShape = Shape<_1, _1, _1>;
 
+// D = alpha[row] x accumulator, rounded once to bf16 (no source tensor, no bias)
+using RowScale = cutlass::epilogue::fusion::PerRowLinCombPerRowBiasEltAct<cutlass::epilogue::thread::Identity, ElementD,
+                                                                         ElementAccumulator, ElementD, void,
+                                                                         ElementAccumulator>;
 using CollectiveEpilogue = typename cutlass::epilogue::collective::CollectiveBuilder<
     cutlass::arch::Sm100, cutlass::arch::OpClassBlockScaledTensorOp, MmaTileShape, ClusterShape,
     cutlass::epilogue::collective::EpilogueTileAuto, ElementAccumulator, ElementAccumulator, void, LayoutD, kAlignmentD,
-    ElementD, LayoutD, kAlignmentD, cutlass::epilogue::collective::EpilogueScheduleAuto>::CollectiveOp;
+    ElementD, LayoutD, kAlignmentD, cutlass::epilogue::collective::EpilogueScheduleAuto, RowScale>::CollectiveOp;
 
 using CollectiveMainloop = typename cutlass::gemm::collective::CollectiveBuilder<
     cutlass::arch::Sm100, cutlass::arch::OpClassBlockScaledTensorOp, ElementA, LayoutA, kAlignmentAB, ElementB, LayoutB,
@@ -69,10 +75,11 @@ using StrideA = typename GemmKernel::StrideA;
 using StrideB = typename GemmKernel::StrideB;
 using StrideD = typename GemmKernel::StrideD;
 
-// alpha[g] = activation global scale of group g x the weights' second-level scale
-__global__ void group_alpha_kernel(const float* activation_scales, float weight_scale_2, size_t groups, float* alpha) {
-  const size_t g = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (g < groups) alpha[g] = activation_scales[g] * weight_scale_2;
+// alpha[t] = global scale of token t's scale group x the weights' second-level scale
+__global__ void row_alpha_kernel(const float* group_scales, float weight_scale_2, size_t tokens, size_t rows_per_scale,
+                                 float* alpha) {
+  const size_t t = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (t < tokens) alpha[t] = group_scales[t / rows_per_scale] * weight_scale_2;
 }
 
 Gemm::Arguments make_arguments(const uint8_t* a, const uint8_t* a_scales, const uint8_t* w, const uint8_t* w_scales, int m,
@@ -88,8 +95,8 @@ Gemm::Arguments make_arguments(const uint8_t* a, const uint8_t* a_scales, const 
                         reinterpret_cast<const typename ElementB::DataType*>(w), stride_b,
                         reinterpret_cast<const ScaleElement*>(a_scales), layout_sfa,
                         reinterpret_cast<const ScaleElement*>(w_scales), layout_sfb},
-                       {{1.0f, 0.0f}, nullptr, stride_d, reinterpret_cast<ElementD*>(out), stride_d}};
-  args.epilogue.thread.alpha_ptr = alpha;
+                       {{}, nullptr, stride_d, reinterpret_cast<ElementD*>(out), stride_d}};
+  args.epilogue.thread.alpha_ptr = alpha;  // one per row (the default stride of this fusion)
   return args;
 }
 
@@ -99,16 +106,17 @@ Gemm::Arguments make_arguments(const uint8_t* a, const uint8_t* a_scales, const 
 using namespace q3x;
 using namespace q3x::host;
 
+namespace {
+size_t alpha_bytes(size_t tokens) { return (tokens * sizeof(float) + 255) / 256 * 256; }
+}  // namespace
+
 extern "C" size_t q3x_b200_nvfp4_gemm_workspace_bytes(size_t tokens, size_t out_features, size_t in_features,
-                                                      size_t rows_per_scale) {
+                                                      size_t /*rows_per_scale*/) {
   if (tokens == 0 || out_features == 0 || in_features == 0) return 0;
-  const size_t rps = rows_per_scale == 0 || rows_per_scale > tokens ? tokens : rows_per_scale;
-  const size_t groups = (tokens + rps - 1) / rps;
-  if (rps > 0x7fffffffu || out_features > 0x7fffffffu || in_features > 0x7fffffffu) return 0;
-  const auto args = make_arguments(nullptr, nullptr, nullptr, nullptr, static_cast<int>(rps), static_cast<int>(out_features),
+  if (tokens > 0x7fffffffu || out_features > 0x7fffffffu || in_features > 0x7fffffffu) return 0;
+  const auto args = make_arguments(nullptr, nullptr, nullptr, nullptr, static_cast<int>(tokens), static_cast<int>(out_features),
                                    static_cast<int>(in_features), nullptr, nullptr);
-  const size_t per_launch = (Gemm::get_workspace_size(args) + 255) / 256 * 256;
-  return (groups * sizeof(float) + 255) / 256 * 256 + per_launch * groups;
+  return alpha_bytes(tokens) + (Gemm::get_workspace_size(args) + 255) / 256 * 256;
 }
 
 extern "C" int q3x_b200_nvfp4_gemm_bf16(const uint8_t* activation_codes, const uint8_t* activation_scales_swizzled,
@@ -125,17 +133,16 @@ extern "C" int q3x_b200_nvfp4_gemm_bf16(const uint8_t* activation_codes, const u
     return kInvalid;
   const size_t rps = rows_per_scale == 0 || rows_per_scale > tokens ? tokens : rows_per_scale;
   const size_t groups = (tokens + rps - 1) / rps;
-  // a scale group starts on a tile of the swizzled block-scale layout (128 rows)
-  if (groups > 1 && rps % 128 != 0) return kInvalid;
   const size_t need = q3x_b200_nvfp4_gemm_workspace_bytes(tokens, out_features, in_features, rows_per_scale);
   if (workspace == nullptr || workspace_bytes < need || !aligned16(workspace)) return kInvalid;
   if (!aligned16(activation_codes) || !aligned16(weight_codes) || !aligned16(activation_scales_swizzled) ||
       !aligned16(weight_scales_swizzled) || !aligned16(out))
     return kNotSupported;
-  const size_t out_bytes = tokens * out_features * 2;
-  const Span so = span(out, out_bytes), sw = span(workspace, need);
+  const Span so = span(out, tokens * out_features * 2), sw = span(workspace, need);
   const Span inputs[] = {span(activation_codes, tokens * in_features / 2), span(weight_codes, out_features * in_features / 2),
-                         span(activation_global_scales, groups * sizeof(float))};
+                         span(activation_global_scales, groups * sizeof(float)),
+                         span(activation_scales_swizzled, q3x_b200_nvfp4_swizzled_scale_bytes(tokens, in_features)),
+                         span(weight_scales_swizzled, q3x_b200_nvfp4_swizzled_scale_bytes(out_features, in_features))};
   for (const Span& in : inputs)
     if (overlap(so, in) || overlap(sw, in)) return kInvalid;
   if (overlap(so, sw)) return kInvalid;
@@ -143,27 +150,18 @@ extern "C" int q3x_b200_nvfp4_gemm_bf16(const uint8_t* activation_codes, const u
   cudaStream_t s = as_stream(stream);
   clear_stale_error();
   float* const alpha = static_cast<float*>(workspace);
-  uint8_t* const launch_space = static_cast<uint8_t*>(workspace) + (groups * sizeof(float) + 255) / 256 * 256;
-  const size_t per_launch = (need - (groups * sizeof(float) + 255) / 256 * 256) / groups;
-  group_alpha_kernel<<<static_cast<unsigned>((groups + 127) / 128), 128, 0, s>>>(activation_global_scales, weight_scale_2,
-                                                                                groups, alpha);
-  const size_t scale_tile_bytes = 512;                        // 128 rows x 4 blocks
-  const size_t scale_tiles_per_row_tile = (in_features / 16 + 3) / 4;
-  for (size_t g = 0; g < groups; ++g) {
-    const size_t first = g * rps;
-    const size_t m = tokens - first < rps ? tokens - first : rps;
-    const auto args = make_arguments(activation_codes + first * (in_features / 2),
-                                     activation_scales_swizzled + first / 128 * scale_tiles_per_row_tile * scale_tile_bytes,
-                                     weight_codes, weight_scales_swizzled, static_cast<int>(m),
-                                     static_cast<int>(out_features), static_cast<int>(in_features), alpha + g,
-                                     out + first * out_features);
-    Gemm gemm;
-    if (gemm.can_implement(args) != cutlass::Status::kSuccess) return kNotSupported;
-    if (gemm.initialize(args, launch_space + g * per_launch, s) != cutlass::Status::kSuccess) return kNotSupported;
-    if (gemm.run(s) != cutlass::Status::kSuccess) {
-      const int status = launch_status();
-      return status != kOk ? status : static_cast<int>(cudaErrorLaunchFailure);
-    }
+  row_alpha_kernel<<<static_cast<unsigned>((tokens + 255) / 256), 256, 0, s>>>(activation_global_scales, weight_scale_2,
+                                                                              tokens, rps, alpha);
+  const auto args = make_arguments(activation_codes, activation_scales_swizzled, weight_codes, weight_scales_swizzled,
+                                   static_cast<int>(tokens), static_cast<int>(out_features), static_cast<int>(in_features),
+                                   alpha, out);
+  Gemm gemm;
+  if (gemm.can_implement(args) != cutlass::Status::kSuccess) return kNotSupported;
+  if (gemm.initialize(args, static_cast<uint8_t*>(workspace) + alpha_bytes(tokens), s) != cutlass::Status::kSuccess)
+    return kNotSupported;
+  if (gemm.run(s) != cutlass::Status::kSuccess) {
+    const int status = launch_status();
+    return status != kOk ? status : static_cast<int>(cudaErrorLaunchFailure);
   }
   return launch_status();
 }
