@@ -635,6 +635,39 @@ def probe_projection_ops(cuda_index=0, aim_ms=60.0, tokens=8192):
                      "frac_of_measured_bf16_dense": round(tflops / bf16_peak, 3) if bf16_peak else None,
                      "sm_mhz": clk.get("sm_mhz"), "reasons": clk.get("reasons")}
         del a_codes, w_codes, a_scales, w_scales, ws, y
+    # the MLP block with its projections: residual + norm + NVFP4 -> gate / up -> SwiGLU + NVFP4 -> down
+    chain = importlib.import_module("qwen3x-orin_b200.chain")
+    block = chain.ProjectedMlp(tokens, dev)
+    with torch.cuda.stream(stream_obj):
+        block.enqueue(stream)
+    stream_obj.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=stream_obj):
+        block.enqueue(stream)
+    with torch.cuda.stream(stream_obj):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream_obj)
+        graph.replay()
+        e1.record(stream_obj)
+        stream_obj.synchronize()
+        reps = max(3, min(500, int(math.ceil(aim_ms / max(e0.elapsed_time(e1), 1e-3)))))
+        sampler = ClockSampler(cuda_index)
+        e0.record(stream_obj)
+        for _ in range(reps):
+            graph.replay()
+        e1.record(stream_obj)
+        stream_obj.synchronize()
+        clk = sampler.stop()
+    block.check_error()
+    us = e0.elapsed_time(e1) * 1e3 / reps
+    gemm_us = 2 * out["nvfp4_gemm_17408x5120"]["us"] + out["nvfp4_gemm_5120x17408"]["us"]
+    out["mlp_block_with_projections"] = {
+        "tokens": tokens, "us": round(us, 1), "tokens_per_s": round(tokens / (us * 1e-6), 1),
+        "TFLOPs": round(block.flops() / (us * 1e-6) / 1e12, 1), "kernels": 10,
+        "share_outside_the_projections": round(1.0 - gemm_us / us, 3), "sm_mhz": clk.get("sm_mhz"),
+        "note": "residual+RMSNorm+NVFP4, scale re-layout, gate and up projections, SwiGLU+NVFP4, scale re-layout, down "
+                "projection; synthetic NVFP4 weights"}
+    del block
     torch.cuda.empty_cache()
     return out
 

@@ -281,3 +281,80 @@ class LayerStack:
             cur = 1 - cur
             self.op_swiglu(stream)
         return cur
+
+
+class ProjectedMlp:
+    """One layer's MLP block WITH its projections, every operand of every projection in NVFP4:
+
+        residual + RMSNorm + NVFP4  ->  gate, up = x W_gate^T, x W_up^T  (block-scaled tensor cores)
+        ->  SwiGLU + NVFP4  ->  down = h W_down^T  ->  (the next residual + RMSNorm takes `down` as its right operand)
+
+    which is the reference's post-attention composite followed by its MLP-down composite
+    (launch_post_attention_residual_norm_mlp_gate_up_silu_to_bf16_cuda, launch_mlp_down_residual_norm_to_bf16_cuda,
+    include/q3x/runtime/model_weights.h:928-992) for a panel of tokens.  The weights are synthetic: random bf16
+    matrices quantised row-wise by the library's own quantiser (one second-level scale per matrix)."""
+
+    def __init__(self, tokens: int, device, hidden: int = HIDDEN, intermediate: int = INTERMEDIATE, seed: int = 11):
+        self.tokens, self.hidden, self.intermediate = tokens, hidden, intermediate
+        self.device = device
+        gen = torch.Generator(device=device).manual_seed(seed)
+        L = capi.lib()
+        u8 = dict(device=device, dtype=torch.uint8)
+        bf = dict(device=device, dtype=torch.bfloat16)
+
+        def weight(rows, cols):
+            dense = (torch.randn((rows, cols), generator=gen, device=device) * 0.03).to(torch.bfloat16)
+            codes, scales = torch.empty((rows, cols // 2), **u8), torch.empty((rows, cols // 16), **u8)
+            gs = torch.empty(1, device=device, dtype=torch.float32)
+            scratch = torch.zeros(L.q3x_b200_nvfp4_scratch_words(rows, 0), device=device, dtype=torch.int32)
+            capi.check("q3x_b200_nvfp4_quantize_dynamic", dense, rows, cols, 0, scratch, gs, codes, scales, None)
+            swizzled = torch.empty(L.q3x_b200_nvfp4_swizzled_scale_bytes(rows, cols), **u8)
+            capi.check("q3x_b200_nvfp4_swizzle_block_scales", scales, rows, cols, swizzled, None)
+            torch.cuda.synchronize(device)
+            return {"codes": codes, "scales": scales, "swizzled": swizzled, "scale_2": float(gs.item()), "dense": dense}
+
+        self.w_gate, self.w_up = weight(intermediate, hidden), weight(intermediate, hidden)
+        self.w_down = weight(hidden, intermediate)
+        self.norm_w = (torch.randn(hidden, generator=gen, device=device) * 0.02).to(torch.bfloat16)
+        self.left = torch.randn((tokens, hidden), generator=gen, device=device).to(torch.bfloat16)
+        self.right = torch.randn((tokens, hidden), generator=gen, device=device).to(torch.bfloat16)
+        groups = (tokens + CHUNK - 1) // CHUNK
+        self.residual, self.normalized = torch.empty((tokens, hidden), **bf), torch.empty((tokens, hidden), **bf)
+        self.scratch = torch.zeros(L.q3x_b200_nvfp4_scratch_words(tokens, CHUNK), device=device, dtype=torch.int32)
+        self.x_gs = torch.empty(groups, device=device, dtype=torch.float32)
+        self.x_codes, self.x_scales = torch.empty((tokens, hidden // 2), **u8), torch.empty((tokens, hidden // 16), **u8)
+        self.x_swizzled = torch.empty(L.q3x_b200_nvfp4_swizzled_scale_bytes(tokens, hidden), **u8)
+        self.gate, self.up = torch.empty((tokens, intermediate), **bf), torch.empty((tokens, intermediate), **bf)
+        self.h = torch.empty((tokens, intermediate), **bf)
+        self.h_gs = torch.empty(groups, device=device, dtype=torch.float32)
+        self.h_codes = torch.empty((tokens, intermediate // 2), **u8)
+        self.h_scales = torch.empty((tokens, intermediate // 16), **u8)
+        self.h_swizzled = torch.empty(L.q3x_b200_nvfp4_swizzled_scale_bytes(tokens, intermediate), **u8)
+        self.down = torch.empty((tokens, hidden), **bf)
+        need = max(L.q3x_b200_nvfp4_gemm_workspace_bytes(tokens, intermediate, hidden, CHUNK),
+                   L.q3x_b200_nvfp4_gemm_workspace_bytes(tokens, hidden, intermediate, CHUNK))
+        self.workspace = torch.empty(need, **u8)
+
+    def flops(self) -> float:
+        return 2.0 * self.tokens * self.hidden * self.intermediate * 3
+
+    def _project(self, codes, swizzled, gs, weight, out_features, in_features, out, stream):
+        capi.check("q3x_b200_nvfp4_gemm_bf16", codes, swizzled, gs, CHUNK, weight["codes"], weight["swizzled"],
+                   weight["scale_2"], self.tokens, out_features, in_features, out, self.workspace, self.workspace.numel(),
+                   stream)
+
+    def enqueue(self, stream) -> None:
+        T, H, I = self.tokens, self.hidden, self.intermediate
+        capi.check("q3x_b200_residual_add_rms_norm_nvfp4", self.left, self.right, self.norm_w, T, H, EPS, CHUNK,
+                   self.residual, self.normalized, self.scratch, self.x_gs, self.x_codes, self.x_scales, stream)
+        capi.check("q3x_b200_nvfp4_swizzle_block_scales", self.x_scales, T, H, self.x_swizzled, stream)
+        self._project(self.x_codes, self.x_swizzled, self.x_gs, self.w_gate, I, H, self.gate, stream)
+        self._project(self.x_codes, self.x_swizzled, self.x_gs, self.w_up, I, H, self.up, stream)
+        capi.check("q3x_b200_silu_mul_nvfp4", self.gate, self.up, T, I, CHUNK, self.h, self.scratch, self.h_gs,
+                   self.h_codes, self.h_scales, stream)
+        capi.check("q3x_b200_nvfp4_swizzle_block_scales", self.h_scales, T, I, self.h_swizzled, stream)
+        self._project(self.h_codes, self.h_swizzled, self.h_gs, self.w_down, H, I, self.down, stream)
+
+    def check_error(self) -> None:
+        if int(self.scratch[-1].item()) != 0:
+            raise RuntimeError("a bounded wait of a single-kernel NVFP4 operator gave up: outputs are invalid")

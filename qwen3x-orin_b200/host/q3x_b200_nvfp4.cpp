@@ -30,6 +30,21 @@ int launch_nvfp4_swizzle_block_scales_cuda(const std::uint8_t* row_major, std::s
   return q3x_b200_nvfp4_swizzle_block_scales(row_major, rows, cols, swizzled, cuda_stream);
 }
 
+std::size_t nvfp4_projection_workspace_bytes(std::size_t token_count, std::size_t out_features, std::size_t in_features,
+                                             std::size_t rows_per_scale) noexcept {
+  return q3x_b200_nvfp4_gemm_workspace_bytes(token_count, out_features, in_features, rows_per_scale);
+}
+
+int launch_nvfp4_projection_to_bf16_cuda(const NvFp4ProjectionWeight& weight, const std::uint8_t* activation_codes,
+                                         const std::uint8_t* activation_block_scales_swizzled,
+                                         const float* activation_global_scales, std::size_t rows_per_scale,
+                                         std::size_t token_count, std::uint16_t* output, void* workspace,
+                                         std::size_t workspace_bytes, void* cuda_stream) noexcept {
+  return q3x_b200_nvfp4_gemm_bf16(activation_codes, activation_block_scales_swizzled, activation_global_scales,
+                                  rows_per_scale, weight.codes, weight.block_scales_swizzled, weight.scale_2, token_count,
+                                  weight.out_features, weight.in_features, output, workspace, workspace_bytes, cuda_stream);
+}
+
 std::size_t nvfp4_activation_scale_groups(std::size_t rows, std::size_t rows_per_scale) noexcept {
   return q3x_b200_nvfp4_group_count(rows, rows_per_scale);
 }

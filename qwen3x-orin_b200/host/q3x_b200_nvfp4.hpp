@@ -41,6 +41,27 @@ struct NvFp4ActivationBuffers {
                                                          std::size_t cols, std::uint8_t* swizzled,
                                                          void* cuda_stream = nullptr) noexcept;
 
+// The projection that consumes those operands: out [tokens, out_features] bf16 = activations x weights^T, both
+// NVFP4 (codes, swizzled block scales, FP32 second-level scales: one per activation scale group, one for the
+// weights), on the block-scaled tensor cores.  It stands where the reference's prefill arm of
+// launch_projection_to_bf16_cuda (model_weights.h:794-841) multiplies bf16 activations with NVFP4 weights.
+struct NvFp4ProjectionWeight {
+  const std::uint8_t* codes = nullptr;                  // [out_features, in_features / 2]
+  const std::uint8_t* block_scales_swizzled = nullptr;  // nvfp4_swizzled_block_scale_bytes(out_features, in_features)
+  float scale_2 = 1.0F;                                 // NvFp4LinearWeight::weight_scale_2
+  std::size_t out_features = 0U;
+  std::size_t in_features = 0U;
+};
+[[nodiscard]] std::size_t nvfp4_projection_workspace_bytes(std::size_t token_count, std::size_t out_features,
+                                                           std::size_t in_features, std::size_t rows_per_scale) noexcept;
+[[nodiscard]] int launch_nvfp4_projection_to_bf16_cuda(const NvFp4ProjectionWeight& weight,
+                                                       const std::uint8_t* activation_codes,
+                                                       const std::uint8_t* activation_block_scales_swizzled,
+                                                       const float* activation_global_scales,
+                                                       std::size_t rows_per_scale, std::size_t token_count,
+                                                       std::uint16_t* output, void* workspace,
+                                                       std::size_t workspace_bytes, void* cuda_stream = nullptr) noexcept;
+
 [[nodiscard]] std::size_t nvfp4_activation_scale_groups(std::size_t rows, std::size_t rows_per_scale) noexcept;
 [[nodiscard]] std::size_t nvfp4_activation_scratch_words(std::size_t rows, std::size_t rows_per_scale) noexcept;
 

@@ -187,6 +187,21 @@ static void test_nvfp4_front_end() {
   EXPECT(qz::nvfp4_swizzled_block_scale_bytes(512, 5120) == 4 * 80 * 512);
   EXPECT(qz::nvfp4_swizzled_block_scale_bytes(130, 48) == 2 * 1 * 512);
   EXPECT(qz::launch_nvfp4_swizzle_block_scales_cuda(p8, 4, 24, p8 + 0x100000) == 1);  // not a block multiple
+  // the projection on those operands: host-side refusals (shape, scale, workspace), empty problem, workspace query
+  {
+    qz::NvFp4ProjectionWeight weight{p8 + 0x1000000, p8 + 0x2000000, 0.5F, 64, 128};
+    EXPECT(qz::nvfp4_projection_workspace_bytes(256, 64, 128, 0) >= 256 * sizeof(float));
+    EXPECT(qz::nvfp4_projection_workspace_bytes(0, 64, 128, 0) == 0);
+    const auto fp = reinterpret_cast<const float*>(p8 + 0x3000000);
+    auto out = reinterpret_cast<std::uint16_t*>(p8 + 0x4000000);
+    EXPECT(qz::launch_nvfp4_projection_to_bf16_cuda(weight, p8, p8 + 0x100000, fp, 0, 0, out, nullptr, 0) == 0);
+    EXPECT(qz::launch_nvfp4_projection_to_bf16_cuda(weight, p8, p8 + 0x100000, fp, 0, 256, out, p8 + 0x5000000, 8) == 1);
+    weight.in_features = 96;
+    EXPECT(qz::launch_nvfp4_projection_to_bf16_cuda(weight, p8, p8 + 0x100000, fp, 0, 256, out, p8 + 0x5000000, 1 << 20) == 1);
+    weight.in_features = 128;
+    weight.scale_2 = -1.0F;
+    EXPECT(qz::launch_nvfp4_projection_to_bf16_cuda(weight, p8, p8 + 0x100000, fp, 0, 256, out, p8 + 0x5000000, 1 << 20) == 1);
+  }
   // empty shapes succeed with null buffers; bad shapes and missing buffers are refused on the host
   EXPECT(qz::launch_silu_mul_nvfp4_cuda(nullptr, nullptr, 0, 17408, 512, nullptr, {}) == 0);
   EXPECT(qz::launch_silu_mul_nvfp4_cuda(p, p + 0x1000000, 4, 17400, 512, p + 0x2000000, b) == 1);   // not a block multiple
