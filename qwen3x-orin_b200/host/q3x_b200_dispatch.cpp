@@ -159,6 +159,25 @@ int launch_projection_to_bf16_cuda(const ProjectionBackend backend, const Linear
   return project(weight, input, output, cuda_stream);
 }
 
+int launch_projection_tile_to_bf16_cuda(const ProjectionBackend backend, const LinearWeight& weight,
+                                        const std::uint16_t* input, const std::size_t token_count,
+                                        float* /*fp32_scratch*/, std::size_t /*scratch_elements*/, std::uint16_t* output,
+                                        void* cuda_stream) noexcept {
+  // The whole tile is validated before anything is enqueued (model_weights.h:824-825); the tokens then run as
+  // ordered batch-one projections, each reading the weights once (the tensor-core projection of this library
+  // takes NVFP4 activations, which this bf16-in signature does not carry).
+  if (!projection_backend_served_by_b200(backend)) return kInvalidValue;
+  const Shape s = describe(weight);
+  if (!s.valid || input == nullptr || output == nullptr || token_count == 0U ||
+      token_count > kMaximumProjectionTileTokenCount)
+    return kInvalidValue;
+  const std::size_t in_bytes = token_count * s.cols * 2U, out_bytes = token_count * s.rows * 2U;
+  if (overlaps(output, out_bytes, input, in_bytes) || touches_weight(output, out_bytes, s)) return kInvalidValue;
+  for (std::size_t t = 0U; t < token_count; ++t)
+    if (const int st = project(weight, input + t * s.cols, output + t * s.rows, cuda_stream); st != 0) return st;
+  return 0;
+}
+
 int launch_mlp_gate_up_silu_to_bf16_cuda(const ProjectionBackend backend, const LinearWeight& gate_weight,
                                          const LinearWeight& up_weight, const std::uint16_t* input,
                                          float* /*fp32_scratch*/, std::size_t /*scratch_elements*/,

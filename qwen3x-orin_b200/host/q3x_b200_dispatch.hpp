@@ -81,6 +81,12 @@ enum class ProjectionBackend : std::uint8_t {
                                                  const std::uint16_t* input, float* fp32_scratch,
                                                  std::size_t scratch_elements, std::uint16_t* output,
                                                  void* cuda_stream = nullptr) noexcept;
+// model_weights.h:387,800-826: the sequence-tile form, token_count in [1, 64]
+inline constexpr std::size_t kMaximumProjectionTileTokenCount = 64U;
+[[nodiscard]] int launch_projection_tile_to_bf16_cuda(ProjectionBackend backend, const LinearWeight& weight,
+                                                      const std::uint16_t* input, std::size_t token_count,
+                                                      float* fp32_scratch, std::size_t scratch_elements,
+                                                      std::uint16_t* output, void* cuda_stream = nullptr) noexcept;
 [[nodiscard]] int launch_mlp_gate_up_silu_to_bf16_cuda(ProjectionBackend backend, const LinearWeight& gate_weight,
                                                        const LinearWeight& up_weight, const std::uint16_t* input,
                                                        float* fp32_scratch, std::size_t scratch_elements,

@@ -321,6 +321,19 @@ static void test_composites(cudaStream_t s) {
   EXPECT(rt::launch_projection_to_bf16_cuda(rt::ProjectionBackend::kSm87WeightOnly, f8_lw, left.p, nullptr, 0, p1.p, s) == 0);
   EXPECT(q3x_b200_fp8_gemv(fp8_w.p, 0.02f, left.p, inter, hidden, nullptr, p2.p, s) == 0);
   EXPECT(same(p1, p2) && written(p1));
+  // the sequence-tile form: three tokens = three batch-one projections, token-major in and out
+  {
+    Bf16 xs3(random_bf16(3 * hidden, 1.0f)), t1(3 * inter), t2(3 * inter);
+    EXPECT(rt::launch_projection_tile_to_bf16_cuda(rt::ProjectionBackend::kSm87WeightOnly, f8_lw, xs3.p, 3, nullptr, 0, t1.p,
+                                                   s) == 0);
+    for (std::size_t t = 0; t < 3; ++t)
+      EXPECT(q3x_b200_fp8_gemv(fp8_w.p, 0.02f, xs3.p + t * hidden, inter, hidden, nullptr, t2.p + t * inter, s) == 0);
+    EXPECT(same(t1, t2) && written(t1));
+    EXPECT(rt::launch_projection_tile_to_bf16_cuda(rt::ProjectionBackend::kSm87WeightOnly, f8_lw, xs3.p, 65, nullptr, 0, t1.p,
+                                                   s) == 1);
+    EXPECT(rt::launch_projection_tile_to_bf16_cuda(rt::ProjectionBackend::kSm87WeightOnly, f8_lw, xs3.p, 0, nullptr, 0, t1.p,
+                                                   s) == 1);
+  }
   // rejections, all before any enqueue
   constexpr int kInvalid = 1;
   EXPECT(rt::launch_projection_to_bf16_cuda(static_cast<rt::ProjectionBackend>(9), f8_lw, left.p, nullptr, 0, p1.p, s) == kInvalid);

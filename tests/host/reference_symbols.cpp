@@ -66,6 +66,7 @@ int main() {
       reinterpret_cast<const void*>(&kn::launch_nvfp4_gemv_reference_cuda),
       // the projection composites, declared by the reference's model_weights.h with its own LinearWeight
       reinterpret_cast<const void*>(&rt::launch_projection_to_bf16_cuda),
+      reinterpret_cast<const void*>(&rt::launch_projection_tile_to_bf16_cuda),
       reinterpret_cast<const void*>(&rt::launch_mlp_gate_up_silu_to_bf16_cuda),
       reinterpret_cast<const void*>(&rt::launch_post_attention_residual_norm_mlp_gate_up_silu_to_bf16_cuda),
       reinterpret_cast<const void*>(
