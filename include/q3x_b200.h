@@ -167,6 +167,20 @@ int q3x_b200_nvfp4_swizzle_block_scales(const uint8_t* row_major, size_t rows, s
  * (launch_projection_to_bf16_cuda, include/q3x/runtime/model_weights.h:794-841, kernel
  * src/kernels/sm87/nvfp4_marlin_w4a16.cu); this is that projection with the activation operand taken from
  * this library's quantiser, so it has the reference's shape contract but not its numerics. */
+/* The weight-only FP8 projection of a panel of tokens: out[tokens, out_features] (bf16, row-major) =
+ * activations[tokens, in_features] (bf16) x W^T with W = [out_features, in_features] E4M3 bytes and one FP32
+ * scale for the tensor -- q3x_b200_fp8_gemv for many tokens (fp8_gemv_reference_cpu,
+ * src/kernels/reference/gemv_reference.cpp:113-140, per token), which is what
+ * launch_projection_tile_to_bf16_cuda and launch_exact_fp8_whole_chunk_projection_to_bf16_cuda
+ * (include/q3x/runtime/model_weights.h:800-870) compute for Fp8LinearWeight.  Tensor cores (the weights are
+ * widened to bf16, exactly, inside the kernel), FP32 accumulation, the scale applied to the sum, one rounding.
+ * in_features must be a multiple of 16, out_features of 8; pointers 16-byte aligned; `workspace` holds
+ * q3x_b200_fp8_gemm_workspace_bytes(...) bytes.  Nothing is allocated. */
+size_t q3x_b200_fp8_gemm_workspace_bytes(size_t tokens, size_t out_features, size_t in_features);
+int q3x_b200_fp8_gemm_bf16(const uint8_t* weights, float weight_scale, const uint16_t* activations, size_t tokens,
+                           size_t out_features, size_t in_features, uint16_t* out, void* workspace,
+                           size_t workspace_bytes, void* stream);
+
 size_t q3x_b200_nvfp4_gemm_workspace_bytes(size_t tokens, size_t out_features, size_t in_features,
                                            size_t rows_per_scale);
 int q3x_b200_nvfp4_gemm_bf16(const uint8_t* activation_codes, const uint8_t* activation_scales_swizzled,
