@@ -635,6 +635,43 @@ def probe_projection_ops(cuda_index=0, aim_ms=60.0, tokens=8192):
                      "frac_of_measured_bf16_dense": round(tflops / bf16_peak, 3) if bf16_peak else None,
                      "sm_mhz": clk.get("sm_mhz"), "reasons": clk.get("reasons")}
         del a_codes, w_codes, a_scales, w_scales, ws, y
+    # the weight-only FP8 projections (bf16 activations, E4M3 weights, per-tensor scale) at the attention / GDN shapes
+    for name, n, k in (("fp8_w8a16_gemm_10240x5120", 10240, 5120), ("fp8_w8a16_gemm_12288x5120", 12288, 5120),
+                       ("fp8_w8a16_gemm_5120x6144", 5120, 6144)):
+        x = (torch.randn((tokens, k), generator=gen, device=dev, dtype=torch.float32)).to(torch.bfloat16)
+        w8 = u8((n, k), 0x10, 0x70)
+        y = torch.empty((tokens, n), device=dev, dtype=torch.bfloat16)
+
+        def call8():
+            capi.check("q3x_b200_fp8_gemm_bf16", w8, 0.02, x, tokens, n, k, y, None, 0, stream)
+
+        with torch.cuda.stream(stream_obj):
+            call8()
+        stream_obj.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream_obj):
+            call8()
+        with torch.cuda.stream(stream_obj):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream_obj)
+            graph.replay()
+            e1.record(stream_obj)
+            stream_obj.synchronize()
+            reps = max(3, min(2000, int(math.ceil(aim_ms / max(e0.elapsed_time(e1), 1e-3)))))
+            sampler = ClockSampler(cuda_index)
+            e0.record(stream_obj)
+            for _ in range(reps):
+                graph.replay()
+            e1.record(stream_obj)
+            stream_obj.synchronize()
+            clk = sampler.stop()
+        us = e0.elapsed_time(e1) * 1e3 / reps
+        tflops = 2.0 * tokens * n * k / (us * 1e-6) / 1e12
+        out[name] = {"tokens": tokens, "launches_per_call": 1, "us": round(us, 1), "TFLOPs": round(tflops, 1),
+                     "frac_of_measured_bf16_dense": round(tflops / bf16_peak, 3) if bf16_peak else None,
+                     "frac_of_nominal_bf16_dense_2250": round(tflops / 2250.0, 4),
+                     "sm_mhz": clk.get("sm_mhz"), "reasons": clk.get("reasons")}
+        del x, w8, y
     # the MLP block with its projections: residual + norm + NVFP4 -> gate / up -> SwiGLU + NVFP4 -> down
     chain = importlib.import_module("qwen3x-orin_b200.chain")
     block = chain.ProjectedMlp(tokens, dev)

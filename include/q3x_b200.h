@@ -175,7 +175,7 @@ int q3x_b200_nvfp4_swizzle_block_scales(const uint8_t* row_major, size_t rows, s
  * (include/q3x/runtime/model_weights.h:800-870) compute for Fp8LinearWeight.  Tensor cores (the weights are
  * widened to bf16, exactly, inside the kernel), FP32 accumulation, the scale applied to the sum, one rounding.
  * in_features must be a multiple of 16, out_features of 8; pointers 16-byte aligned; `workspace` holds
- * q3x_b200_fp8_gemm_workspace_bytes(...) bytes.  Nothing is allocated. */
+ * q3x_b200_fp8_gemm_workspace_bytes(...) bytes and may be NULL when that is 0.  Nothing is allocated. */
 size_t q3x_b200_fp8_gemm_workspace_bytes(size_t tokens, size_t out_features, size_t in_features);
 int q3x_b200_fp8_gemm_bf16(const uint8_t* weights, float weight_scale, const uint16_t* activations, size_t tokens,
                            size_t out_features, size_t in_features, uint16_t* out, void* workspace,

@@ -36,7 +36,7 @@ using namespace cute;
 using ElementW = cutlass::float_e4m3_t;  // operand A: weights [N, K], K contiguous
 using ElementX = cutlass::bfloat16_t;    // operand B: activations [T, K], K contiguous
 using ElementD = cutlass::bfloat16_t;    // D^T [N, T] column-major = out [T, N] row-major
-using MmaTileShape = Shape<_128, _128, _64>;
+using MmaTileShape = Shape<_128, _128, _128>;
 using ClusterShape = Shape<_1, _1, _1>;
 
 using CollectiveEpilogue = typename cutlass::epilogue::collective::CollectiveBuilder<
@@ -82,7 +82,7 @@ extern "C" size_t q3x_b200_fp8_gemm_workspace_bytes(size_t tokens, size_t out_fe
   if (tokens > 0x7fffffffu || out_features > 0x7fffffffu || in_features > 0x7fffffffu) return 0;
   const auto args = make_arguments(nullptr, 1.0f, nullptr, static_cast<int>(tokens), static_cast<int>(out_features),
                                    static_cast<int>(in_features), nullptr);
-  return (Gemm::get_workspace_size(args) + 255) / 256 * 256 + 256;  // never 0: the caller always passes a buffer
+  return (Gemm::get_workspace_size(args) + 255) / 256 * 256;  // 0 for this kernel's static tile schedule
 }
 
 extern "C" int q3x_b200_fp8_gemm_bf16(const uint8_t* weights, float weight_scale, const uint16_t* activations,
@@ -94,9 +94,9 @@ extern "C" int q3x_b200_fp8_gemm_bf16(const uint8_t* weights, float weight_scale
   if (!(std::isfinite(weight_scale) && weight_scale >= 0.0f)) return kInvalid;
   if (weights == nullptr || activations == nullptr || out == nullptr) return kInvalid;
   const size_t need = q3x_b200_fp8_gemm_workspace_bytes(tokens, out_features, in_features);
-  if (workspace == nullptr || workspace_bytes < need || !aligned16(workspace)) return kInvalid;
+  if (need != 0 && (workspace == nullptr || workspace_bytes < need || !aligned16(workspace))) return kInvalid;
   if (!aligned16(weights) || !aligned16(activations) || !aligned16(out)) return kNotSupported;
-  const Span so = span(out, tokens * out_features * 2), sw = span(workspace, need);
+  const Span so = span(out, tokens * out_features * 2), sw = span(need != 0 ? workspace : nullptr, need);
   const Span sweights = span(weights, out_features * in_features), sx = span(activations, tokens * in_features * 2);
   if (overlap(so, sweights) || overlap(so, sx) || overlap(so, sw) || overlap(sw, sweights) || overlap(sw, sx)) return kInvalid;
 
@@ -106,7 +106,7 @@ extern "C" int q3x_b200_fp8_gemm_bf16(const uint8_t* weights, float weight_scale
                                    static_cast<int>(in_features), out);
   Gemm gemm;
   if (gemm.can_implement(args) != cutlass::Status::kSuccess) return kNotSupported;
-  if (gemm.initialize(args, workspace, s) != cutlass::Status::kSuccess) return kNotSupported;
+  if (gemm.initialize(args, need != 0 ? workspace : nullptr, s) != cutlass::Status::kSuccess) return kNotSupported;
   if (gemm.run(s) != cutlass::Status::kSuccess) {
     const int status = launch_status();
     return status != kOk ? status : static_cast<int>(cudaErrorLaunchFailure);

@@ -163,9 +163,9 @@ int launch_projection_tile_to_bf16_cuda(const ProjectionBackend backend, const L
                                         const std::uint16_t* input, const std::size_t token_count,
                                         float* /*fp32_scratch*/, std::size_t /*scratch_elements*/, std::uint16_t* output,
                                         void* cuda_stream) noexcept {
-  // The whole tile is validated before anything is enqueued (model_weights.h:824-825); the tokens then run as
-  // ordered batch-one projections, each reading the weights once (the tensor-core projection of this library
-  // takes NVFP4 activations, which this bf16-in signature does not carry).
+  // The whole tile is validated before anything is enqueued (model_weights.h:824-825).  FP8 weights of two or
+  // more tokens go to the tensor-core weight-only GEMM (one pass over the weights); everything else runs as
+  // ordered batch-one projections.
   if (!projection_backend_served_by_b200(backend)) return kInvalidValue;
   const Shape s = describe(weight);
   if (!s.valid || input == nullptr || output == nullptr || token_count == 0U ||
@@ -173,9 +173,35 @@ int launch_projection_tile_to_bf16_cuda(const ProjectionBackend backend, const L
     return kInvalidValue;
   const std::size_t in_bytes = token_count * s.cols * 2U, out_bytes = token_count * s.rows * 2U;
   if (overlaps(output, out_bytes, input, in_bytes) || touches_weight(output, out_bytes, s)) return kInvalidValue;
+  if (const auto* fp8 = std::get_if<Fp8LinearWeight>(&weight);
+      fp8 != nullptr && token_count >= 2U && s.cols % 16U == 0U && s.rows % 8U == 0U) {
+    const int st = q3x_b200_fp8_gemm_bf16(fp8->weight, fp8->weight_scale, input, token_count, s.rows, s.cols, output,
+                                          nullptr, 0U, cuda_stream);
+    if (st != kNotSupported) return st;  // a shape or alignment the GEMM does not take: token by token below
+  }
   for (std::size_t t = 0U; t < token_count; ++t)
     if (const int st = project(weight, input + t * s.cols, output + t * s.rows, cuda_stream); st != 0) return st;
   return 0;
+}
+
+int launch_exact_fp8_whole_chunk_projection_to_bf16_cuda(const ProjectionBackend backend, const LinearWeight& weight,
+                                                         const std::uint16_t* input, const std::size_t token_count,
+                                                         std::uint16_t* output, void* cuda_stream) noexcept {
+  // the reference's structural gate (projection_dispatch.cpp:1000-1024): weight-only backend, FP8 weight, a chunk
+  // of 256 or 512 tokens, one of the five attention / GDN projection shapes
+  const bool backend_ok = backend == ProjectionBackend::kSm87WeightOnly || backend == kProjectionBackendB200LayerOps;
+  if (!backend_ok || weight.valueless_by_exception() || (token_count != 256U && token_count != 512U)) return kNotSupported;
+  const auto* fp8 = std::get_if<Fp8LinearWeight>(&weight);
+  if (fp8 == nullptr) return kNotSupported;
+  const std::size_t n = fp8->output_size, k = fp8->input_size;
+  const bool shape_ok = (k == 5120U && (n == 10240U || n == 6144U || n == 12288U || n == 1024U)) || (n == 5120U && k == 6144U);
+  if (!shape_ok) return kNotSupported;
+  const Shape s = describe(weight);
+  if (!s.valid || input == nullptr || output == nullptr) return kInvalidValue;
+  const std::size_t in_bytes = token_count * k * 2U, out_bytes = token_count * n * 2U;
+  if (overlaps(output, out_bytes, input, in_bytes) || touches_weight(output, out_bytes, s)) return kInvalidValue;
+  // (a pointer that misses the GEMM's 16-byte alignment comes back as cudaErrorNotSupported, as a near miss does there)
+  return q3x_b200_fp8_gemm_bf16(fp8->weight, fp8->weight_scale, input, token_count, n, k, output, nullptr, 0U, cuda_stream);
 }
 
 int launch_mlp_gate_up_silu_to_bf16_cuda(const ProjectionBackend backend, const LinearWeight& gate_weight,

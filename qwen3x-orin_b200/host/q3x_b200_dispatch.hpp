@@ -87,6 +87,13 @@ inline constexpr std::size_t kMaximumProjectionTileTokenCount = 64U;
                                                       const std::uint16_t* input, std::size_t token_count,
                                                       float* fp32_scratch, std::size_t scratch_elements,
                                                       std::uint16_t* output, void* cuda_stream = nullptr) noexcept;
+// model_weights.h:828-847: one FP8 projection over a whole prefill chunk (256 or 512 tokens, the five attention /
+// GDN projection shapes); anything else is cudaErrorNotSupported so that the caller keeps its tiled schedule
+[[nodiscard]] int launch_exact_fp8_whole_chunk_projection_to_bf16_cuda(ProjectionBackend backend,
+                                                                       const LinearWeight& weight,
+                                                                       const std::uint16_t* input,
+                                                                       std::size_t token_count, std::uint16_t* output,
+                                                                       void* cuda_stream = nullptr) noexcept;
 [[nodiscard]] int launch_mlp_gate_up_silu_to_bf16_cuda(ProjectionBackend backend, const LinearWeight& gate_weight,
                                                        const LinearWeight& up_weight, const std::uint16_t* input,
                                                        float* fp32_scratch, std::size_t scratch_elements,

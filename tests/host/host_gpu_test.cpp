@@ -321,18 +321,58 @@ static void test_composites(cudaStream_t s) {
   EXPECT(rt::launch_projection_to_bf16_cuda(rt::ProjectionBackend::kSm87WeightOnly, f8_lw, left.p, nullptr, 0, p1.p, s) == 0);
   EXPECT(q3x_b200_fp8_gemv(fp8_w.p, 0.02f, left.p, inter, hidden, nullptr, p2.p, s) == 0);
   EXPECT(same(p1, p2) && written(p1));
-  // the sequence-tile form: three tokens = three batch-one projections, token-major in and out
+  // the sequence-tile form: FP8 weights of several tokens go through the weight-only tensor-core GEMM (same bytes
+  // as the C-ABI call), one token through the batch-one kernel; bf16 weights run token by token
   {
-    Bf16 xs3(random_bf16(3 * hidden, 1.0f)), t1(3 * inter), t2(3 * inter);
+    Bf16 xs3(random_bf16(3 * hidden, 1.0f)), t1(3 * inter), t2(3 * inter), t3(inter);
     EXPECT(rt::launch_projection_tile_to_bf16_cuda(rt::ProjectionBackend::kSm87WeightOnly, f8_lw, xs3.p, 3, nullptr, 0, t1.p,
                                                    s) == 0);
-    for (std::size_t t = 0; t < 3; ++t)
-      EXPECT(q3x_b200_fp8_gemv(fp8_w.p, 0.02f, xs3.p + t * hidden, inter, hidden, nullptr, t2.p + t * inter, s) == 0);
+    EXPECT(q3x_b200_fp8_gemm_bf16(fp8_w.p, 0.02f, xs3.p, 3, inter, hidden, t2.p, nullptr, 0, s) == 0);
     EXPECT(same(t1, t2) && written(t1));
+    EXPECT(rt::launch_projection_tile_to_bf16_cuda(rt::ProjectionBackend::kSm87WeightOnly, f8_lw, xs3.p, 1, nullptr, 0, t3.p,
+                                                   s) == 0);
+    EXPECT(q3x_b200_fp8_gemv(fp8_w.p, 0.02f, xs3.p, inter, hidden, nullptr, t2.p, s) == 0);
+    EXPECT(cudaStreamSynchronize(static_cast<cudaStream_t>(s)) == cudaSuccess);
+    {
+      std::vector<std::uint16_t> a(inter), b(inter);
+      cudaMemcpy(a.data(), t3.p, inter * 2, cudaMemcpyDeviceToHost);
+      cudaMemcpy(b.data(), t2.p, inter * 2, cudaMemcpyDeviceToHost);
+      EXPECT(a == b);
+    }
+    Bf16 d1(3 * hidden), d2(3 * hidden), acts(random_bf16(3 * inter, 0.5f));
+    EXPECT(rt::launch_projection_tile_to_bf16_cuda(rt::ProjectionBackend::kReference, down_lw, acts.p, 3, nullptr, 0, d1.p,
+                                                   s) == 0);
+    for (std::size_t t = 0; t < 3; ++t)
+      EXPECT(q3x_b200_bf16_gemv(down_w.p, acts.p + t * inter, hidden, inter, nullptr, d2.p + t * hidden, s) == 0);
+    EXPECT(same(d1, d2) && written(d1));
     EXPECT(rt::launch_projection_tile_to_bf16_cuda(rt::ProjectionBackend::kSm87WeightOnly, f8_lw, xs3.p, 65, nullptr, 0, t1.p,
                                                    s) == 1);
     EXPECT(rt::launch_projection_tile_to_bf16_cuda(rt::ProjectionBackend::kSm87WeightOnly, f8_lw, xs3.p, 0, nullptr, 0, t1.p,
                                                    s) == 1);
+  }
+  // one FP8 projection over a whole prefill chunk: the reference's structural gate, then the same GEMM
+  {
+    const std::size_t kv = 1024, chunk = 256;
+    DeviceBuffer<std::uint8_t> kv_w(random_bytes(kv * hidden, 0x10, 0x60));
+    rt::Fp8LinearWeight kvw = f8;
+    kvw.weight = kv_w.p; kvw.output_size = kv; kvw.input_size = hidden;
+    const rt::LinearWeight kv_lw = kvw;
+    Bf16 xc(random_bf16(chunk * hidden, 1.0f)), c1(chunk * kv), c2(chunk * kv);
+    EXPECT(rt::launch_exact_fp8_whole_chunk_projection_to_bf16_cuda(rt::ProjectionBackend::kSm87WeightOnly, kv_lw, xc.p, chunk,
+                                                                    c1.p, s) == 0);
+    EXPECT(q3x_b200_fp8_gemm_bf16(kv_w.p, 0.02f, xc.p, chunk, kv, hidden, c2.p, nullptr, 0, s) == 0);
+    EXPECT(same(c1, c2) && written(c1));
+    constexpr int kUnsupported = 801;
+    EXPECT(rt::launch_exact_fp8_whole_chunk_projection_to_bf16_cuda(rt::ProjectionBackend::kSm87WeightOnly, kv_lw, xc.p, 128,
+                                                                    c1.p, s) == kUnsupported);
+    EXPECT(rt::launch_exact_fp8_whole_chunk_projection_to_bf16_cuda(rt::ProjectionBackend::kReference, kv_lw, xc.p, chunk,
+                                                                    c1.p, s) == kUnsupported);
+    rt::Fp8LinearWeight odd = kvw;
+    odd.output_size = 512;  // [512, 5120] is none of the five shapes
+    EXPECT(rt::launch_exact_fp8_whole_chunk_projection_to_bf16_cuda(rt::ProjectionBackend::kSm87WeightOnly, rt::LinearWeight{odd},
+                                                                    xc.p, chunk, c1.p, s) == kUnsupported);
+    EXPECT(rt::launch_exact_fp8_whole_chunk_projection_to_bf16_cuda(rt::ProjectionBackend::kSm87WeightOnly, kv_lw, xc.p, chunk,
+                                                                    xc.p, s) == 1);             // output on the input
   }
   // rejections, all before any enqueue
   constexpr int kInvalid = 1;

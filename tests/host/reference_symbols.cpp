@@ -67,6 +67,7 @@ int main() {
       // the projection composites, declared by the reference's model_weights.h with its own LinearWeight
       reinterpret_cast<const void*>(&rt::launch_projection_to_bf16_cuda),
       reinterpret_cast<const void*>(&rt::launch_projection_tile_to_bf16_cuda),
+      reinterpret_cast<const void*>(&rt::launch_exact_fp8_whole_chunk_projection_to_bf16_cuda),
       reinterpret_cast<const void*>(&rt::launch_mlp_gate_up_silu_to_bf16_cuda),
       reinterpret_cast<const void*>(&rt::launch_post_attention_residual_norm_mlp_gate_up_silu_to_bf16_cuda),
       reinterpret_cast<const void*>(
