@@ -181,6 +181,26 @@ int q3x_b200_fp8_gemm_bf16(const uint8_t* weights, float weight_scale, const uin
                            size_t out_features, size_t in_features, uint16_t* out, void* workspace,
                            size_t workspace_bytes, void* stream);
 
+/* The weight-only NVFP4 projection of a panel of tokens: q3x_b200_nvfp4_gemv for many tokens
+ * (nvfp4_gemv_reference_cpu, src/kernels/reference/gemv_reference.cpp:179-225, per token) -- bf16 activations
+ * [tokens, in_features], packed E2M1 weights [out_features, in_features / 2] as the checkpoint holds them, block
+ * scales TRANSPOSED to [in_features / 16, out_features] and widened to bf16 (exact;
+ * q3x_b200_nvfp4_transpose_block_scales re-lays a weight's row-major E4M3 scales out, once, when the weight is
+ * loaded), FP32 second-level scale; what
+ * launch_projection_tile_to_bf16_cuda and
+ * launch_exact_nvfp4_whole_chunk_branch_to_bf16_cuda (include/q3x/runtime/model_weights.h:800-866) compute for
+ * NvFp4LinearWeight.  Tensor cores (codes x block scales become bf16 operands, exactly, inside the kernel), FP32
+ * accumulation, the second-level scale applied to the sum, one rounding.  in_features must be a multiple of 32,
+ * out_features of 8; pointers 16-byte aligned; workspace as for q3x_b200_fp8_gemm_bf16. */
+int q3x_b200_nvfp4_transpose_block_scales(const uint8_t* row_major, size_t rows, size_t cols, uint16_t* transposed,
+                                          void* stream);
+size_t q3x_b200_nvfp4_w4a16_gemm_workspace_bytes(size_t tokens, size_t out_features, size_t in_features);
+int q3x_b200_nvfp4_w4a16_gemm_bf16(const uint8_t* packed_weights, const uint16_t* block_scales_transposed,
+                                   float weight_scale_2,
+                                   const uint16_t* activations, size_t tokens, size_t out_features,
+                                   size_t in_features, uint16_t* out, void* workspace, size_t workspace_bytes,
+                                   void* stream);
+
 size_t q3x_b200_nvfp4_gemm_workspace_bytes(size_t tokens, size_t out_features, size_t in_features,
                                            size_t rows_per_scale);
 int q3x_b200_nvfp4_gemm_bf16(const uint8_t* activation_codes, const uint8_t* activation_scales_swizzled,

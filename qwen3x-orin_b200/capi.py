@@ -41,6 +41,9 @@ SIGNATURES = {
     "q3x_b200_nvfp4_swizzle_block_scales": (_i, [_p, _z, _z, _p, _p]),
     "q3x_b200_fp8_gemm_workspace_bytes": (_z, [_z, _z, _z]),
     "q3x_b200_fp8_gemm_bf16": (_i, [_p, _f, _p, _z, _z, _z, _p, _p, _z, _p]),
+    "q3x_b200_nvfp4_transpose_block_scales": (_i, [_p, _z, _z, _p, _p]),
+    "q3x_b200_nvfp4_w4a16_gemm_workspace_bytes": (_z, [_z, _z, _z]),
+    "q3x_b200_nvfp4_w4a16_gemm_bf16": (_i, [_p, _p, _f, _p, _z, _z, _z, _p, _p, _z, _p]),
     "q3x_b200_nvfp4_gemm_workspace_bytes": (_z, [_z, _z, _z, _z]),
     "q3x_b200_nvfp4_gemm_bf16": (_i, [_p, _p, _p, _z, _p, _p, _f, _z, _z, _z, _p, _p, _z, _p]),
     "q3x_b200_residual_add_rms_norm_nvfp4": (_i, [_p, _p, _p, _z, _z, _f, _z, _p, _p, _p, _p, _p, _p, _p]),

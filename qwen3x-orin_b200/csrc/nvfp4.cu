@@ -189,6 +189,20 @@ __global__ void __launch_bounds__(kThreads) swizzle_scales_kernel(const uint8_t*
   }
 }
 
+// Block scales [rows, row_blocks] E4M3 -> [row_blocks, rows] bf16: the order and the type in which the weight-only
+// tensor-core projection reads a weight's block scales (an E4M3 value is exact in bf16; one thread per destination
+// element; a weight is re-laid out once, when it is loaded).
+__global__ void __launch_bounds__(kThreads) transpose_scales_kernel(const uint8_t* __restrict__ row_major, size_t rows,
+                                                                    size_t row_blocks, uint16_t* __restrict__ transposed) {
+  const size_t total = rows * row_blocks;
+  const size_t stride = static_cast<size_t>(gridDim.x) * kThreads;
+  for (size_t o = static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x; o < total; o += stride) {
+    const uint32_t code = row_major[(o % rows) * row_blocks + o / rows];
+    const uint16_t magnitude = float_to_bf16(decode_e4m3_positive(code & 0x7fu));
+    transposed[o] = static_cast<uint16_t>(magnitude | ((code & 0x80u) << 8));
+  }
+}
+
 __global__ void __launch_bounds__(kThreads) debug_encode_kernel(const float* in, size_t count, uint8_t* out,
                                                                 int format) {
   const size_t i = static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x;
@@ -672,6 +686,19 @@ extern "C" int q3x_b200_nvfp4_swizzle_block_scales(const uint8_t* row_major, siz
   clear_stale_error();
   swizzle_scales_kernel<<<grid_for(out_bytes, kThreads, 8), kThreads, 0, as_stream(stream)>>>(
       row_major, rows, row_blocks, (row_blocks + 3) / 4, out_bytes, swizzled);
+  return launch_status();
+}
+
+extern "C" int q3x_b200_nvfp4_transpose_block_scales(const uint8_t* row_major, size_t rows, size_t cols,
+                                                     uint16_t* transposed, void* stream) {
+  if (cols % Q3X_B200_NVFP4_BLOCK != 0 || mul3_overflows(rows, cols, 2)) return kInvalid;
+  if (rows == 0 || cols == 0) return kOk;
+  if (row_major == nullptr || transposed == nullptr) return kInvalid;
+  const size_t row_blocks = cols / Q3X_B200_NVFP4_BLOCK;
+  if (overlap(span(row_major, rows * row_blocks), span(transposed, rows * row_blocks * 2))) return kInvalid;
+  clear_stale_error();
+  transpose_scales_kernel<<<grid_for(rows * row_blocks, kThreads, 8), kThreads, 0, as_stream(stream)>>>(
+      row_major, rows, row_blocks, transposed);
   return launch_status();
 }
 
