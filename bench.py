@@ -672,6 +672,45 @@ def probe_projection_ops(cuda_index=0, aim_ms=60.0, tokens=8192):
                      "frac_of_nominal_bf16_dense_2250": round(tflops / 2250.0, 4),
                      "sm_mhz": clk.get("sm_mhz"), "reasons": clk.get("reasons")}
         del x, w8, y
+    # the weight-only NVFP4 projections (bf16 activations, E2M1 weights, block scales as the transposed bf16 sidecar)
+    for name, n, k in (("nvfp4_w4a16_gemm_17408x5120", 17408, 5120), ("nvfp4_w4a16_gemm_5120x17408", 5120, 17408)):
+        x = (torch.randn((tokens, k), generator=gen, device=dev, dtype=torch.float32)).to(torch.bfloat16)
+        w4 = u8((n, k // 2))
+        row_scales = u8((n, k // 16), 0x28, 0x48)
+        sidecar = torch.empty((k // 16, n), device=dev, dtype=torch.bfloat16)
+        capi.check("q3x_b200_nvfp4_transpose_block_scales", row_scales, n, k, sidecar, stream)
+        y = torch.empty((tokens, n), device=dev, dtype=torch.bfloat16)
+
+        def call4():
+            capi.check("q3x_b200_nvfp4_w4a16_gemm_bf16", w4, sidecar, 0.01, x, tokens, n, k, y, None, 0, stream)
+
+        with torch.cuda.stream(stream_obj):
+            call4()
+        stream_obj.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream_obj):
+            call4()
+        with torch.cuda.stream(stream_obj):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream_obj)
+            graph.replay()
+            e1.record(stream_obj)
+            stream_obj.synchronize()
+            reps = max(3, min(2000, int(math.ceil(aim_ms / max(e0.elapsed_time(e1), 1e-3)))))
+            sampler = ClockSampler(cuda_index)
+            e0.record(stream_obj)
+            for _ in range(reps):
+                graph.replay()
+            e1.record(stream_obj)
+            stream_obj.synchronize()
+            clk = sampler.stop()
+        us = e0.elapsed_time(e1) * 1e3 / reps
+        tflops = 2.0 * tokens * n * k / (us * 1e-6) / 1e12
+        out[name] = {"tokens": tokens, "launches_per_call": 1, "us": round(us, 1), "TFLOPs": round(tflops, 1),
+                     "frac_of_measured_bf16_dense": round(tflops / bf16_peak, 3) if bf16_peak else None,
+                     "frac_of_nominal_bf16_dense_2250": round(tflops / 2250.0, 4),
+                     "sm_mhz": clk.get("sm_mhz"), "reasons": clk.get("reasons")}
+        del x, w4, row_scales, sidecar, y
     # the MLP block with its projections: residual + norm + NVFP4 -> gate / up -> SwiGLU + NVFP4 -> down
     chain = importlib.import_module("qwen3x-orin_b200.chain")
     block = chain.ProjectedMlp(tokens, dev)
