@@ -16,6 +16,7 @@ Per layer:
 from __future__ import annotations
 
 import math
+import os
 from dataclasses import dataclass
 
 import torch
@@ -57,6 +58,27 @@ KERNELS = {
 }
 GDN_OPS = ["residual_rmsnorm_nvfp4", "conv1d_silu_l2norm", "gated_rmsnorm_nvfp4", "residual_rmsnorm_nvfp4", "swiglu"]
 FA_OPS = ["residual_rmsnorm_nvfp4", "attention_preprocess", "sigmoid_gate", "residual_rmsnorm_nvfp4", "swiglu"]
+
+
+class profiler_range:
+    """An NVTX range around a stretch of enqueued work (the reference brackets its runner phases the same way,
+    src/runtime/reference_engine_control.cpp:38-89), so that a timeline capture of a step shows layers and
+    operators by name.  Off unless Q3X_B200_NVTX=1: a push / pop pair costs more than a batch-one launch."""
+
+    enabled = os.environ.get("Q3X_B200_NVTX", "0") not in ("", "0")
+
+    def __init__(self, name: str):
+        self.name = name
+
+    def __enter__(self):
+        if profiler_range.enabled:
+            torch.cuda.nvtx.range_push(self.name)
+        return self
+
+    def __exit__(self, *exc):
+        if profiler_range.enabled:
+            torch.cuda.nvtx.range_pop()
+        return False
 
 
 def is_full_attention(layer: int) -> bool:
@@ -266,20 +288,26 @@ class LayerStack:
         index of the residual buffer that holds the final residual stream."""
         # (the key rows are normalised and rotated in place by every full-attention layer, as the
         # reference does inside its KV cache; they stay bounded, so no reset is needed per step)
-        self.op_embedding(stream)
+        with profiler_range("embedding"):
+            self.op_embedding(stream)
         cur = 0
         for layer in range(self.layers):
-            self.op_residual_norm(layer, 0, cur, 1 - cur, stream)
-            cur = 1 - cur
-            if is_full_attention(layer):
-                self.op_preprocess(layer, stream)
-                self.op_sigmoid_gate(stream)
-            else:
-                self.op_conv(layer, stream)
-                self.op_gated_norm(layer, stream)
-            self.op_residual_norm(layer, 1, cur, 1 - cur, stream)
-            cur = 1 - cur
-            self.op_swiglu(stream)
+            with profiler_range(f"layer {layer} {'full-attention' if is_full_attention(layer) else 'gdn'}"):
+                with profiler_range("input residual+norm+nvfp4"):
+                    self.op_residual_norm(layer, 0, cur, 1 - cur, stream)
+                cur = 1 - cur
+                with profiler_range("mixer operators"):
+                    if is_full_attention(layer):
+                        self.op_preprocess(layer, stream)
+                        self.op_sigmoid_gate(stream)
+                    else:
+                        self.op_conv(layer, stream)
+                        self.op_gated_norm(layer, stream)
+                with profiler_range("post-attention residual+norm+nvfp4"):
+                    self.op_residual_norm(layer, 1, cur, 1 - cur, stream)
+                cur = 1 - cur
+                with profiler_range("swiglu"):
+                    self.op_swiglu(stream)
         return cur
 
 
