@@ -635,6 +635,47 @@ def probe_projection_ops(cuda_index=0, aim_ms=60.0, tokens=8192):
                      "frac_of_measured_bf16_dense": round(tflops / bf16_peak, 3) if bf16_peak else None,
                      "sm_mhz": clk.get("sm_mhz"), "reasons": clk.get("reasons")}
         del a_codes, w_codes, a_scales, w_scales, ws, y
+    # bulk causal attention of a 512-token tile appended at positions 0, 8192 and 65536 (one layer's cache)
+    for first in (0, 8192, 65536):
+        tile = 512
+        length = first + tile
+        q = torch.randn((tile, 24, 256), generator=gen, device=dev, dtype=torch.float32).to(torch.bfloat16)
+        gate_t = torch.randn((tile, 24, 256), generator=gen, device=dev, dtype=torch.float32).to(torch.bfloat16)
+        kc = torch.randn((length, 4, 256), generator=gen, device=dev, dtype=torch.float32).to(torch.bfloat16)
+        vc = torch.randn((length, 4, 256), generator=gen, device=dev, dtype=torch.float32).to(torch.bfloat16)
+        y = torch.empty((tile, 24, 256), device=dev, dtype=torch.bfloat16)
+
+        def attend():
+            capi.check("q3x_b200_gqa_attention_prefill_sigmoid_gate", q, kc, vc, gate_t, first, tile, 0.0625, y, stream)
+
+        with torch.cuda.stream(stream_obj):
+            attend()
+        stream_obj.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream_obj):
+            attend()
+        with torch.cuda.stream(stream_obj):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream_obj)
+            graph.replay()
+            e1.record(stream_obj)
+            stream_obj.synchronize()
+            reps = max(3, min(2000, int(math.ceil(aim_ms / max(e0.elapsed_time(e1), 1e-3)))))
+            sampler = ClockSampler(cuda_index)
+            e0.record(stream_obj)
+            for _ in range(reps):
+                graph.replay()
+            e1.record(stream_obj)
+            stream_obj.synchronize()
+            clk = sampler.stop()
+        us = e0.elapsed_time(e1) * 1e3 / reps
+        # visible (query, key) pairs x 24 heads x 256 dims x 2 products x 2 flops
+        pairs = tile * first + tile * (tile + 1) // 2
+        tflops = 4.0 * pairs * 24 * 256 / (us * 1e-6) / 1e12
+        out[f"gqa_prefill_512_tokens_at_{first}"] = {"us": round(us, 1), "TFLOPs": round(tflops, 1),
+                                                     "frac_of_measured_bf16_dense": round(tflops / bf16_peak, 3) if bf16_peak else None,
+                                                     "sm_mhz": clk.get("sm_mhz")}
+        del q, gate_t, kc, vc, y
     # the weight-only FP8 projections (bf16 activations, E4M3 weights, per-tensor scale) at the attention / GDN shapes
     for name, n, k in (("fp8_w8a16_gemm_10240x5120", 10240, 5120), ("fp8_w8a16_gemm_12288x5120", 12288, 5120),
                        ("fp8_w8a16_gemm_5120x6144", 5120, 6144)):

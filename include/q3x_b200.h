@@ -425,6 +425,20 @@ int q3x_b200_gqa_attention_decode_sigmoid_gate(const uint16_t* query, const uint
                                                float attention_scale, float* workspace, size_t workspace_floats,
                                                const uint16_t* gate, uint16_t* out, void* stream);
 
+/* Bulk causal GQA attention of a tile of `tokens` tokens appended at position `first_position`, with the sigmoid
+ * output gate: for token t and query head h, attention over cache positions 0 .. first_position + t (the caches
+ * [position, 4, 256] already hold the tile's own keys and values), rounded to bf16, times sigmoid(gate[t, h]),
+ * rounded again (gate may be NULL: plain attention).  query / gate / out are tile-local [tokens, 24, 256].
+ * gqa_attention_reference_cpu + sigmoid_gate_reference_cpu per token
+ * (src/runtime/reference/decode_ops.cpp:302-342,445-508); replaces
+ * launch_bulk_causal_gqa_sigmoid_gate_24_4_256[_fixed]_cuda and the panel form
+ * (include/q3x/runtime/decode_ops.h:419-505).  Any tokens and first_position; no scratch; pointers 16-byte aligned;
+ * out must not overlap an input. */
+int q3x_b200_gqa_attention_prefill_sigmoid_gate(const uint16_t* query, const uint16_t* key_cache,
+                                                const uint16_t* value_cache, const uint16_t* gate,
+                                                size_t first_position, size_t tokens, float scale, uint16_t* out,
+                                                void* stream);
+
 /* launch_bf16_gemv_reference_cuda / launch_bf16_gemv_bf16_cuda, launch_fp8_gemv_reference_cuda and
  * launch_nvfp4_gemv_reference_cuda (include/q3x/kernels/reference_gemv.h:64-130): batch-one projections
  * out[r] = sum_c W[r,c] * x[c], FP32 accumulation, x [cols] bf16.  The result is written as FP32 (out_f32), as

@@ -75,6 +75,7 @@ SIGNATURES = {
     "q3x_b200_gated_delta_net_update_rms_norm_silu_gate": (_i, [_p, _z, _p, _p, _p, _p, _p, _p, _f, _p, _p, _f, _p, _p]),
     "q3x_b200_gqa_decode_workspace_floats": (_z, [_z]),
     "q3x_b200_gqa_attention_decode_sigmoid_gate": (_i, [_p, _p, _p, _z, _f, _p, _z, _p, _p, _p]),
+    "q3x_b200_gqa_attention_prefill_sigmoid_gate": (_i, [_p, _p, _p, _p, _z, _z, _f, _p, _p]),
     "q3x_b200_softmax": (_i, [_p, _z, _z, _p, _p]),
     "q3x_b200_bf16_greedy_argmax": (_i, [_p, _z, _p, _p]),
 }

@@ -211,6 +211,43 @@ int launch_gqa_attention_splitkv_sigmoid_gate_24_4_256_cuda(const std::uint16_t*
                                                     workspace, workspace_elements, gate, output, stream);
 }
 
+namespace {
+// the tile forms admit 2..512 tokens, the panel form up to its own maximum (decode_ops.h:452-500); the gate is required
+int bulk_causal(const std::uint16_t* q, const std::uint16_t* k, const std::uint16_t* v, const std::uint16_t* gate,
+                std::size_t first_position, std::size_t token_count, std::size_t maximum_tokens, std::uint16_t* out,
+                void* stream) noexcept {
+  if (token_count < 2U || token_count > maximum_tokens || first_position > kBulkCausalGqaMaximumSequenceLength - token_count ||
+      gate == nullptr)
+    return kInvalidValue;
+  return q3x_b200_gqa_attention_prefill_sigmoid_gate(q, k, v, gate, first_position, token_count, 0.0625F, out, stream);
+}
+}  // namespace
+
+int launch_bulk_causal_gqa_sigmoid_gate_24_4_256_cuda(const std::uint16_t* query_tile, const std::uint16_t* key_cache,
+                                                      const std::uint16_t* value_cache, const std::uint16_t* gate_tile,
+                                                      std::size_t first_position, std::size_t token_count,
+                                                      std::uint16_t* output_tile, void* stream) noexcept {
+  return bulk_causal(query_tile, key_cache, value_cache, gate_tile, first_position, token_count, 512U, output_tile, stream);
+}
+
+int launch_bulk_causal_gqa_sigmoid_gate_24_4_256_fixed_cuda(const std::uint16_t* query_tile,
+                                                            const std::uint16_t* key_cache,
+                                                            const std::uint16_t* value_cache,
+                                                            const std::uint16_t* gate_tile, std::size_t first_position,
+                                                            std::size_t token_count, std::uint16_t* output_tile,
+                                                            void* stream) noexcept {
+  return bulk_causal(query_tile, key_cache, value_cache, gate_tile, first_position, token_count, 512U, output_tile, stream);
+}
+
+int launch_bulk_causal_gqa_sigmoid_gate_24_4_256_group_q64_panel_fixed_cuda(
+    const std::uint16_t* query_panel, const std::uint16_t* key_cache, const std::uint16_t* value_cache,
+    const std::uint16_t* gate_panel, std::size_t first_position, std::size_t token_count, std::uint16_t* output_panel,
+    void* stream) noexcept {
+  if (first_position >= (static_cast<std::size_t>(1) << 18)) return kInvalidValue;  // decode_ops.h:493-497
+  return bulk_causal(query_panel, key_cache, value_cache, gate_panel, first_position, token_count,
+                     kBulkCausalGqaGroupQ64PanelMaximumTokens, output_panel, stream);
+}
+
 int launch_bf16_greedy_argmax_cuda(const std::uint16_t* input, std::size_t element_count,
                                    Bf16GreedyArgmaxResult* result_workspace, void* stream) noexcept {
   return q3x_b200_bf16_greedy_argmax(input, element_count, result_workspace, stream);

@@ -159,6 +159,23 @@ struct GdnDimensions {
     const std::uint16_t* query, const std::uint16_t* key_cache, const std::uint16_t* value_cache,
     std::size_t sequence_length, float attention_scale, float* workspace, std::size_t workspace_elements,
     const std::uint16_t* gate, std::uint16_t* output, void* cuda_stream = nullptr) noexcept;
+// decode_ops.h:17-21,419-505: bulk causal attention of a prefill tile / panel with the sigmoid output gate.
+// token_count in [2, 512] for the tile forms; query / gate / output are tile-local [token_count, 24, 256], the caches
+// are global [position, 4, 256], first_position is the append position of the tile's first token.
+inline constexpr std::size_t kBulkCausalGqaMaximumSequenceLength = 262'144U;
+inline constexpr std::size_t kBulkCausalGqaGroupQ64PanelMaximumTokens = 8'192U;
+[[nodiscard]] int launch_bulk_causal_gqa_sigmoid_gate_24_4_256_cuda(
+    const std::uint16_t* query_tile, const std::uint16_t* key_cache, const std::uint16_t* value_cache,
+    const std::uint16_t* gate_tile, std::size_t first_position, std::size_t token_count, std::uint16_t* output_tile,
+    void* cuda_stream = nullptr) noexcept;
+[[nodiscard]] int launch_bulk_causal_gqa_sigmoid_gate_24_4_256_fixed_cuda(
+    const std::uint16_t* query_tile, const std::uint16_t* key_cache, const std::uint16_t* value_cache,
+    const std::uint16_t* gate_tile, std::size_t first_position, std::size_t token_count, std::uint16_t* output_tile,
+    void* cuda_stream = nullptr) noexcept;
+[[nodiscard]] int launch_bulk_causal_gqa_sigmoid_gate_24_4_256_group_q64_panel_fixed_cuda(
+    const std::uint16_t* query_panel, const std::uint16_t* key_cache, const std::uint16_t* value_cache,
+    const std::uint16_t* gate_panel, std::size_t first_position, std::size_t token_count, std::uint16_t* output_panel,
+    void* cuda_stream = nullptr) noexcept;
 [[nodiscard]] int launch_bf16_greedy_argmax_cuda(const std::uint16_t* input, std::size_t element_count,
                                                  Bf16GreedyArgmaxResult* result_workspace,
                                                  void* cuda_stream = nullptr) noexcept;

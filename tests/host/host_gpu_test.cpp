@@ -422,6 +422,20 @@ static void test_core_launchers(cudaStream_t s) {
   EXPECT(q3x_b200_gqa_attention_decode_sigmoid_gate(q.p, kc.p, vc.p, length, 0.0625f, ws.p, need, gate.p, a2.p, s) == 0);
   EXPECT(same(a1, a2) && written(a1));
   EXPECT(rt::launch_gqa_attention_splitkv_sigmoid_gate_24_4_256_cuda(q.p, kc.p, vc.p, 64, 0.0625f, ws.p, need, gate.p, a1.p, s) == 1);
+  // bulk causal attention of a prefill tile: 40 tokens appended at position 260 of the same caches
+  {
+    const std::size_t tile = 40, first = length - tile;
+    Bf16 qt(random_bf16(tile * 24 * 256, 1.0f)), gt(random_bf16(tile * 24 * 256, 2.0f)), o1(tile * 24 * 256), o2(tile * 24 * 256),
+        o3(tile * 24 * 256);
+    EXPECT(rt::launch_bulk_causal_gqa_sigmoid_gate_24_4_256_cuda(qt.p, kc.p, vc.p, gt.p, first, tile, o1.p, s) == 0);
+    EXPECT(rt::launch_bulk_causal_gqa_sigmoid_gate_24_4_256_group_q64_panel_fixed_cuda(qt.p, kc.p, vc.p, gt.p, first, tile, o3.p,
+                                                                                     s) == 0);
+    EXPECT(q3x_b200_gqa_attention_prefill_sigmoid_gate(qt.p, kc.p, vc.p, gt.p, first, tile, 0.0625f, o2.p, s) == 0);
+    EXPECT(same(o1, o2) && same(o3, o2) && written(o1));
+    EXPECT(rt::launch_bulk_causal_gqa_sigmoid_gate_24_4_256_fixed_cuda(qt.p, kc.p, vc.p, gt.p, first, 1, o1.p, s) == 1);
+    EXPECT(rt::launch_bulk_causal_gqa_sigmoid_gate_24_4_256_fixed_cuda(qt.p, kc.p, vc.p, gt.p, first, 513, o1.p, s) == 1);
+    EXPECT(rt::launch_bulk_causal_gqa_sigmoid_gate_24_4_256_cuda(qt.p, kc.p, vc.p, nullptr, first, tile, o1.p, s) == 1);
+  }
   // argmax and the FP32 GEMV launchers
   DeviceBuffer<rt::Bf16GreedyArgmaxResult> r1(rt::kBf16GreedyArgmaxWorkspaceResults), r2(rt::kBf16GreedyArgmaxWorkspaceResults);
   EXPECT(rt::launch_bf16_greedy_argmax_cuda(kc.p, length * 1024, r1.p, s) == 0);

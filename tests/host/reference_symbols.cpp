@@ -60,6 +60,9 @@ int main() {
       reinterpret_cast<const void*>(&rt::gqa_attention_splitkv_sigmoid_gate_24_4_256_workspace_elements),
       reinterpret_cast<const void*>(&rt::launch_gqa_attention_splitkv_sigmoid_gate_24_4_256_cuda),
       reinterpret_cast<const void*>(&rt::launch_bf16_greedy_argmax_cuda),
+      reinterpret_cast<const void*>(&rt::launch_bulk_causal_gqa_sigmoid_gate_24_4_256_cuda),
+      reinterpret_cast<const void*>(&rt::launch_bulk_causal_gqa_sigmoid_gate_24_4_256_fixed_cuda),
+      reinterpret_cast<const void*>(&rt::launch_bulk_causal_gqa_sigmoid_gate_24_4_256_group_q64_panel_fixed_cuda),
       reinterpret_cast<const void*>(&kn::launch_bf16_gemv_reference_cuda),
       reinterpret_cast<const void*>(&kn::launch_bf16_gemv_bf16_cuda),
       reinterpret_cast<const void*>(&kn::launch_fp8_gemv_reference_cuda),

@@ -1,0 +1,98 @@
+"""GPU test of the bulk causal GQA attention of a tile of tokens with the sigmoid output gate
+(q3x_b200_gqa_attention_prefill_sigmoid_gate), through the C ABI, against the oracle's attention (pinned to the
+reference's gqa_attention_reference_cpu + sigmoid_gate_reference_cpu) applied token by token: token t of the tile
+sees cache positions 0 .. first_position + t.
+
+Tolerance.  The host reference keeps the softmax probabilities in FP32; the kernel hands each one to the tensor
+cores as two bf16 operands (16 significant bits), so what separates the two is the order of the FP32 sums: the
+batch-one kernel's rule (ulps + a rounding-level floor + an exact-match quota) and the reference's acceptance rule
+max(2e-3, 8e-3 |e|) (tests/decode_ops_cuda_test.cu:432-450) as the hard bound."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as orc
+from tests import fixtures as fx
+
+pytestmark = pytest.mark.gpu
+SCALE = 0.0625
+
+
+@pytest.fixture(scope="module")
+def g():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from tests import gpu_util
+
+    orc.build()
+    gpu_util.capi.load()
+    return gpu_util
+
+
+def expected(q, kc, vc, gate, first):
+    rows = []
+    for t in range(q.shape[0]):
+        length = first + t + 1
+        out, _ = orc.gqa_attention(q[t], kc[:length], vc[:length], SCALE, gate=None if gate is None else gate[t])
+        rows.append(out)
+    return np.stack(rows)
+
+
+@pytest.mark.parametrize("tokens,first,gated,sharp", [(2, 0, True, 1.0), (16, 0, False, 1.0), (40, 0, True, 1.0),
+                                                       (37, 100, True, 1.0), (130, 63, True, 3.0), (512, 0, True, 1.0),
+                                                       (200, 512, True, 1.0), (64, 1000, False, 3.0)])
+def test_prefill_attention_matches_the_per_token_reference(g, tokens, first, gated, sharp):
+    rng = np.random.default_rng([tokens, first, int(gated), 111])
+    length = first + tokens
+    q = fx.normal_bf16(rng, (tokens, 24, 256), sharp)
+    kc, vc = fx.normal_bf16(rng, (length, 4, 256)), fx.normal_bf16(rng, (length, 4, 256))
+    gate = fx.normal_bf16(rng, (tokens, 24, 256), 2.0) if gated else None
+    out = g.empty_like_dev((tokens, 24, 256))
+    g.capi.check("q3x_b200_gqa_attention_prefill_sigmoid_gate", g.Dev(q), g.Dev(kc), g.Dev(vc),
+                 g.Dev(gate) if gated else None, first, tokens, SCALE, out, None)
+    g.sync()
+    assert out.guards_intact()
+    want = expected(q, kc, vc, gate, first)
+    got = out.get()
+    # as for the batch-one kernel: one rounding of an FP32 weighted average summed in another order (1 ulp plus a
+    # rounding-level fraction of the terms' magnitude); the gate multiplies the ROUNDED attention, so a 1-ulp
+    # difference there passes through (up to 3 ulps of the smaller gated value)
+    g.assert_sum_within(got, want, 3 if gated else 1, 1e-5, 0.98, "prefill attention")
+    # The reference's rule is a hard bound for the attention itself.  Behind the gate it is a two-rounding chain: a
+    # 1-ulp difference of the rounded attention, scaled by sigmoid(gate) and rounded again, can come out as 2 ulps
+    # of a value at the bottom of its binade (3.9e-3 at 0.48 against 8e-3 x 0.48 = 3.87e-3; about one element in a
+    # million): there the rule is the quota form (at most 2 per 100 000 outside it, two ulps of the row as the bound).
+    g.assert_reference_tolerance(got, want, "prefill attention", amplified=gated)
+
+
+def test_prefill_attention_equals_decode_attention_on_its_last_token(g):
+    """The tile's last token sees the whole cache: the same query through the batch-one kernel."""
+    rng = np.random.default_rng(112)
+    tokens, first = 48, 300
+    length = first + tokens
+    q = fx.normal_bf16(rng, (tokens, 24, 256))
+    kc, vc = fx.normal_bf16(rng, (length, 4, 256)), fx.normal_bf16(rng, (length, 4, 256))
+    gate = fx.normal_bf16(rng, (tokens, 24, 256), 2.0)
+    d_k, d_v = g.Dev(kc), g.Dev(vc)
+    out = g.empty_like_dev((tokens, 24, 256))
+    g.capi.check("q3x_b200_gqa_attention_prefill_sigmoid_gate", g.Dev(q), d_k, d_v, g.Dev(gate), first, tokens, SCALE, out, None)
+    words = g.capi.lib().q3x_b200_gqa_decode_workspace_floats(length)
+    ws = g.empty_like_dev((words,), dtype=np.float32)
+    one = g.empty_like_dev((24, 256))
+    g.capi.check("q3x_b200_gqa_attention_decode_sigmoid_gate", g.Dev(q[-1]), d_k, d_v, length, SCALE, ws, words,
+                 g.Dev(gate[-1]), one, None)
+    g.sync()
+    a = orc.bf16_decode(out.get()[-1]).astype(np.float64)
+    b = orc.bf16_decode(one.get()).astype(np.float64)
+    assert np.all(np.abs(a - b) <= np.maximum(2.0e-3, 8.0e-3 * np.abs(b)))
+
+
+def test_prefill_attention_rejections(g):
+    inv, fake = g.capi.CUDA_ERROR_INVALID_VALUE, 0x10000000
+    call = lambda **kw: g.capi.call("q3x_b200_gqa_attention_prefill_sigmoid_gate", kw.get("q", fake), fake + (1 << 26),
+                                    fake + (2 << 26), fake + (3 << 26), 0, kw.get("t", 16), kw.get("s", SCALE),
+                                    kw.get("out", fake + (4 << 26)), None)
+    assert call(q=None) == inv
+    assert call(s=0.0) == inv
+    assert call(out=fake) == inv
+    assert call(t=0) == 0
