@@ -76,6 +76,10 @@ Gemm::Arguments make_arguments(const uint8_t* codes, const uint16_t* block_scale
                        {reinterpret_cast<const ElementW*>(codes), stride_a, reinterpret_cast<const ElementX*>(activations),
                         stride_b, reinterpret_cast<const ElementS*>(block_scales), layout_s},
                        {{scale_2, 0.0f}, nullptr, stride_d, reinterpret_cast<ElementD*>(out), stride_d}};
+  // consecutive CTAs walk a band of eight tiles of the second dimension: a wave then shares a few weight row blocks and
+  // eight token blocks instead of sweeping every weight row block for each token block (measured: the plain order
+  // re-read 2.2 GB from HBM for 0.14 GB of operands)
+  args.scheduler.max_swizzle_size = 8;
   return args;
 }
 
