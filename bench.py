@@ -785,6 +785,37 @@ def probe_projection_ops(cuda_index=0, aim_ms=60.0, tokens=8192):
         "note": "residual+RMSNorm+NVFP4, scale re-layout, gate and up projections, SwiGLU+NVFP4, scale re-layout, down "
                 "projection; synthetic NVFP4 weights"}
     del block
+    # one full-attention layer end to end (FP8 projections, head norms + RoPE, bulk causal attention + gate, output
+    # projection, MLP block) for a panel of `tokens` tokens at the start of a sequence
+    layer = chain.ProjectedAttentionLayer(tokens, 0, dev)
+    with torch.cuda.stream(stream_obj):
+        layer.enqueue(stream)
+    stream_obj.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=stream_obj):
+        layer.enqueue(stream)
+    with torch.cuda.stream(stream_obj):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream_obj)
+        graph.replay()
+        e1.record(stream_obj)
+        stream_obj.synchronize()
+        reps = max(3, min(200, int(math.ceil(aim_ms / max(e0.elapsed_time(e1), 1e-3)))))
+        sampler = ClockSampler(cuda_index)
+        e0.record(stream_obj)
+        for _ in range(reps):
+            graph.replay()
+        e1.record(stream_obj)
+        stream_obj.synchronize()
+        clk = sampler.stop()
+    layer.mlp.check_error()
+    us = e0.elapsed_time(e1) * 1e3 / reps
+    out["full_attention_layer_with_projections"] = {
+        "tokens": tokens, "first_position": 0, "us": round(us, 1), "tokens_per_s": round(tokens / (us * 1e-6), 1),
+        "TFLOPs": round(layer.flops() / (us * 1e-6) / 1e12, 1), "kernels": 17, "sm_mhz": clk.get("sm_mhz"),
+        "note": "residual+RMSNorm, q|gate / k / v projections (FP8 weights) into the caches, head norms + RoPE, bulk causal "
+                "attention + sigmoid gate, output projection, MLP block; synthetic weights"}
+    del layer
     torch.cuda.empty_cache()
     return out
 

@@ -386,3 +386,77 @@ class ProjectedMlp:
     def check_error(self) -> None:
         if int(self.scratch[-1].item()) != 0:
             raise RuntimeError("a bounded wait of a single-kernel NVFP4 operator gave up: outputs are invalid")
+
+
+class ProjectedAttentionLayer:
+    """One full-attention layer of the stack for a tile of tokens appended at `first_position`, every operator and
+    every projection from this library (the call order of the reference's layer segment,
+    src/runtime/reference_runner.cpp:9565-10584):
+
+        residual + RMSNorm  ->  q|gate, k, v projections (FP8 weights, bf16 activations, tensor cores; k and v land
+        in the KV caches)  ->  q / k head norm + partial RoPE (keys in place, in the cache)  ->  bulk causal attention
+        + sigmoid gate  ->  output projection (FP8)  ->  the MLP block (ProjectedMlp: residual + RMSNorm + NVFP4,
+        gate / up, SwiGLU + NVFP4, down)
+
+    Weights are synthetic (random E4M3 bytes with a per-tensor scale; the MLP's as in ProjectedMlp); cache positions
+    before the tile hold random keys and values."""
+
+    def __init__(self, tokens: int, first_position: int, device, intermediate: int = INTERMEDIATE, seed: int = 21):
+        self.tokens, self.first_position, self.device = tokens, first_position, device
+        gen = torch.Generator(device=device).manual_seed(seed)
+        bf = dict(device=device, dtype=torch.bfloat16)
+        q_dim, kv_dim = 2 * Q_HEADS * HEAD_DIM, KV_HEADS * HEAD_DIM
+
+        def fp8_weight(rows, cols, scale):
+            codes = torch.randint(0x08, 0x70, (rows, cols), generator=gen, device=device, dtype=torch.int32)
+            signs = torch.randint(0, 2, (rows, cols), generator=gen, device=device, dtype=torch.int32) << 7
+            return {"codes": (codes | signs).to(torch.uint8), "scale": scale, "rows": rows, "cols": cols}
+
+        # scales chosen so that the projections of a unit-variance input have roughly unit variance
+        self.w_q = fp8_weight(q_dim, HIDDEN, 0.0016)
+        self.w_k = fp8_weight(kv_dim, HIDDEN, 0.0016)
+        self.w_v = fp8_weight(kv_dim, HIDDEN, 0.0016)
+        self.w_o = fp8_weight(HIDDEN, Q_HEADS * HEAD_DIM, 0.0015)
+        rand = lambda shape, std=1.0: (torch.randn(shape, generator=gen, device=device) * std).to(torch.bfloat16)
+        self.input_norm_w, self.q_norm_w, self.k_norm_w = rand((HIDDEN,), 0.02), rand((HEAD_DIM,), 0.02), rand((HEAD_DIM,), 0.02)
+        self.residual_in, self.previous_mlp_out = rand((tokens, HIDDEN)), rand((tokens, HIDDEN))
+        length = first_position + tokens
+        self.key_cache, self.value_cache = rand((length, KV_HEADS, HEAD_DIM)), rand((length, KV_HEADS, HEAD_DIM))
+        self.cos, self.sin = rope_tables(0, length, device)
+        self.residual_mid = torch.empty((tokens, HIDDEN), **bf)
+        self.normalized = torch.empty((tokens, HIDDEN), **bf)
+        self.q_gate = torch.empty((tokens, q_dim), **bf)
+        self.q_out = torch.empty((tokens, Q_HEADS, HEAD_DIM), **bf)
+        self.gate_out = torch.empty((tokens, Q_HEADS, HEAD_DIM), **bf)
+        self.attention = torch.empty((tokens, Q_HEADS, HEAD_DIM), **bf)
+        self.attention_projected = torch.empty((tokens, HIDDEN), **bf)
+        # the MLP block takes (residual_mid, attention_projected) as its (left, right)
+        self.mlp = ProjectedMlp(tokens, device, intermediate=intermediate, seed=seed + 1)
+        self.mlp.left, self.mlp.right = self.residual_mid, self.attention_projected
+
+    def _tile(self, cache):
+        return cache[self.first_position:]  # the tile's own rows of a cache: [tokens, 4, 256], contiguous
+
+    def _fp8(self, weight, x, out, stream):
+        capi.check("q3x_b200_fp8_gemm_bf16", weight["codes"], weight["scale"], x, self.tokens, weight["rows"], weight["cols"],
+                   out, None, 0, stream)
+
+    def enqueue(self, stream) -> None:
+        T = self.tokens
+        capi.check("q3x_b200_residual_add_rms_norm", self.residual_in, self.previous_mlp_out, self.input_norm_w, T, HIDDEN,
+                   EPS, self.residual_mid, self.normalized, stream)
+        self._fp8(self.w_q, self.normalized, self.q_gate, stream)
+        self._fp8(self.w_k, self.normalized, self._tile(self.key_cache), stream)
+        self._fp8(self.w_v, self.normalized, self._tile(self.value_cache), stream)
+        capi.check("q3x_b200_full_attention_preprocess", self.q_gate, self._tile(self.key_cache), self.q_norm_w,
+                   self.k_norm_w, EPS, self.q_out, self.gate_out, self.cos, self.sin, self.first_position, T, stream)
+        capi.check("q3x_b200_gqa_attention_prefill_sigmoid_gate", self.q_out, self.key_cache, self.value_cache,
+                   self.gate_out, self.first_position, T, 1.0 / math.sqrt(HEAD_DIM), self.attention, stream)
+        self._fp8(self.w_o, self.attention, self.attention_projected, stream)
+        self.mlp.enqueue(stream)
+
+    def flops(self) -> float:
+        T, first = self.tokens, self.first_position
+        projections = 2.0 * T * HIDDEN * (2 * Q_HEADS * HEAD_DIM + 2 * KV_HEADS * HEAD_DIM + Q_HEADS * HEAD_DIM)
+        pairs = T * first + T * (T + 1) // 2
+        return projections + 4.0 * pairs * Q_HEADS * HEAD_DIM + self.mlp.flops()
