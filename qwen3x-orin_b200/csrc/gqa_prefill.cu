@@ -89,7 +89,8 @@ __global__ void __launch_bounds__(kThreads, 1) gqa_prefill_kernel(const uint16_t
   const uint32_t smem = static_cast<uint32_t>(__cvta_generic_to_shared(shared));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int kv = blockIdx.y, head = kv * kGroup + warp;
-  const size_t token0 = static_cast<size_t>(blockIdx.x) * kBlockTokens;
+  // the last blocks of a tile see the most keys: they are scheduled first, so that the short ones fill the tail
+  const size_t token0 = static_cast<size_t>(gridDim.x - 1 - blockIdx.x) * kBlockTokens;
   const size_t keys = first_position + min(token0 + kBlockTokens, tokens);  // keys visible to the block's last token
   const int tiles = static_cast<int>((keys + kTileKeys - 1) / kTileKeys);
   const uint32_t q_smem = smem + warp * (kBlockTokens * kDim * 2);
