@@ -816,6 +816,42 @@ def probe_projection_ops(cuda_index=0, aim_ms=60.0, tokens=8192):
         "note": "residual+RMSNorm, q|gate / k / v projections (FP8 weights) into the caches, head norms + RoPE, bulk causal "
                 "attention + sigmoid gate, output projection, MLP block; synthetic weights"}
     del layer
+    # one gated-delta-net layer end to end (FP8 qkv / z projections, conv, token-sequential recurrence, gated norm +
+    # NVFP4, NVFP4 output projection, MLP block) for the same panel
+    gdn = chain.ProjectedGdnLayer(tokens, dev)
+    with torch.cuda.stream(stream_obj):
+        gdn.enqueue(stream)
+    stream_obj.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=stream_obj):
+        gdn.enqueue(stream)
+    with torch.cuda.stream(stream_obj):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream_obj)
+        graph.replay()
+        e1.record(stream_obj)
+        stream_obj.synchronize()
+        reps = max(3, min(200, int(math.ceil(aim_ms / max(e0.elapsed_time(e1), 1e-3)))))
+        e0.record(stream_obj)
+        for _ in range(reps):
+            graph.replay()
+        e1.record(stream_obj)
+        stream_obj.synchronize()
+        # the recurrence alone, on the conv output the layer left behind
+        r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        r0.record(stream_obj)
+        capi.check("q3x_b200_gated_delta_net_update", gdn.conv_out, tokens, gdn.a, gdn.b, gdn.A_log, gdn.dt_bias, gdn.state,
+                   gdn.state, 1e-6, gdn.core, stream)
+        r1.record(stream_obj)
+        stream_obj.synchronize()
+    gdn.check_error()
+    us = e0.elapsed_time(e1) * 1e3 / reps
+    out["gdn_layer_with_projections"] = {
+        "tokens": tokens, "us": round(us, 1), "tokens_per_s": round(tokens / (us * 1e-6), 1), "kernels": 18,
+        "recurrence_us": round(r0.elapsed_time(r1) * 1e3, 1),
+        "note": "residual+RMSNorm, qkv / z projections (FP8 weights), conv1d+SiLU, token-sequential recurrence, gated "
+                "RMSNorm+NVFP4, scale re-layout, NVFP4 output projection, MLP block; synthetic weights and gate inputs"}
+    del gdn
     torch.cuda.empty_cache()
     return out
 

@@ -460,3 +460,88 @@ class ProjectedAttentionLayer:
         projections = 2.0 * T * HIDDEN * (2 * Q_HEADS * HEAD_DIM + 2 * KV_HEADS * HEAD_DIM + Q_HEADS * HEAD_DIM)
         pairs = T * first + T * (T + 1) // 2
         return projections + 4.0 * pairs * Q_HEADS * HEAD_DIM + self.mlp.flops()
+
+
+class ProjectedGdnLayer:
+    """One gated-delta-net layer of the stack for a tile of tokens, every operator and every projection but the two
+    48-wide gate projections from this library (the reference's layer segment, src/runtime/reference_runner.cpp:
+    9565-10584):
+
+        residual + RMSNorm  ->  qkv and z projections (FP8 weights, bf16 activations, tensor cores)  ->  causal
+        conv1d + SiLU (history carried)  ->  gated-delta-net recurrence (state carried; token by token inside one
+        launch)  ->  gated RMSNorm * silu(z) + NVFP4  ->  output projection (NVFP4 x NVFP4)  ->  the MLP block
+
+    The a / b gate inputs ([tokens, 48] each, bf16 projections in the model) are synthetic.  Weights are synthetic."""
+
+    def __init__(self, tokens: int, device, intermediate: int = INTERMEDIATE, seed: int = 31):
+        self.tokens, self.device = tokens, device
+        gen = torch.Generator(device=device).manual_seed(seed)
+        L = capi.lib()
+        bf = dict(device=device, dtype=torch.bfloat16)
+        u8 = dict(device=device, dtype=torch.uint8)
+        rand = lambda shape, std=1.0: (torch.randn(shape, generator=gen, device=device) * std).to(torch.bfloat16)
+
+        def fp8_weight(rows, cols, scale):
+            codes = torch.randint(0x08, 0x70, (rows, cols), generator=gen, device=device, dtype=torch.int32)
+            signs = torch.randint(0, 2, (rows, cols), generator=gen, device=device, dtype=torch.int32) << 7
+            return {"codes": (codes | signs).to(torch.uint8), "scale": scale, "rows": rows, "cols": cols}
+
+        self.w_qkv = fp8_weight(GDN_CHANNELS, HIDDEN, 0.0003)
+        self.w_z = fp8_weight(GDN_V, HIDDEN, 0.0003)
+        dense = rand((HIDDEN, GDN_V), 0.03)  # output projection, quantised row-wise by the library's own quantiser
+        self.w_o = {"codes": torch.empty((HIDDEN, GDN_V // 2), **u8), "scales": torch.empty((HIDDEN, GDN_V // 16), **u8)}
+        gs = torch.empty(1, device=device, dtype=torch.float32)
+        scratch = torch.zeros(L.q3x_b200_nvfp4_scratch_words(HIDDEN, 0), device=device, dtype=torch.int32)
+        capi.check("q3x_b200_nvfp4_quantize_dynamic", dense, HIDDEN, GDN_V, 0, scratch, gs, self.w_o["codes"], self.w_o["scales"],
+                   None)
+        self.w_o["swizzled"] = torch.empty(L.q3x_b200_nvfp4_swizzled_scale_bytes(HIDDEN, GDN_V), **u8)
+        capi.check("q3x_b200_nvfp4_swizzle_block_scales", self.w_o["scales"], HIDDEN, GDN_V, self.w_o["swizzled"], None)
+        torch.cuda.synchronize(device)
+        self.w_o["scale_2"] = float(gs.item())
+        self.input_norm_w, self.gdn_norm_w = rand((HIDDEN,), 0.02), (0.75 + 0.5 * torch.rand(128, generator=gen, device=device)).to(torch.bfloat16)
+        self.conv_w = rand((GDN_CHANNELS, 4), 0.5)
+        self.conv_history = torch.zeros((GDN_CHANNELS, 3), **bf)
+        self.A_log = (torch.rand(48, generator=gen, device=device) * 5.5 - 4.0).to(torch.bfloat16)
+        self.dt_bias = (torch.rand(48, generator=gen, device=device) * 6.0 - 3.0).to(torch.bfloat16)
+        self.a, self.b = rand((tokens, 48), 2.0), rand((tokens, 48), 2.0)
+        self.state = rand((48, 128, 128), 0.05)
+        self.residual_in, self.previous_mlp_out = rand((tokens, HIDDEN)), rand((tokens, HIDDEN))
+        self.residual_mid, self.normalized = torch.empty((tokens, HIDDEN), **bf), torch.empty((tokens, HIDDEN), **bf)
+        self.qkv, self.conv_out = torch.empty((tokens, GDN_CHANNELS), **bf), torch.empty((tokens, GDN_CHANNELS), **bf)
+        self.z, self.core = torch.empty((tokens, GDN_V), **bf), torch.empty((tokens, GDN_V), **bf)
+        self.gated = torch.empty((tokens, GDN_V), **bf)
+        groups = (tokens + CHUNK - 1) // CHUNK
+        self.scratch = torch.zeros(L.q3x_b200_nvfp4_scratch_words(tokens, CHUNK), device=device, dtype=torch.int32)
+        self.gated_gs = torch.empty(groups, device=device, dtype=torch.float32)
+        self.gated_codes, self.gated_scales = torch.empty((tokens, GDN_V // 2), **u8), torch.empty((tokens, GDN_V // 16), **u8)
+        self.gated_swizzled = torch.empty(L.q3x_b200_nvfp4_swizzled_scale_bytes(tokens, GDN_V), **u8)
+        self.mixer_projected = torch.empty((tokens, HIDDEN), **bf)
+        self.workspace = torch.empty(L.q3x_b200_nvfp4_gemm_workspace_bytes(tokens, HIDDEN, GDN_V, CHUNK), **u8)
+        self.mlp = ProjectedMlp(tokens, device, intermediate=intermediate, seed=seed + 1)
+        self.mlp.left, self.mlp.right = self.residual_mid, self.mixer_projected
+
+    def _fp8(self, weight, x, out, stream):
+        capi.check("q3x_b200_fp8_gemm_bf16", weight["codes"], weight["scale"], x, self.tokens, weight["rows"], weight["cols"],
+                   out, None, 0, stream)
+
+    def enqueue(self, stream) -> None:
+        T = self.tokens
+        capi.check("q3x_b200_residual_add_rms_norm", self.residual_in, self.previous_mlp_out, self.input_norm_w, T, HIDDEN,
+                   EPS, self.residual_mid, self.normalized, stream)
+        self._fp8(self.w_qkv, self.normalized, self.qkv, stream)
+        self._fp8(self.w_z, self.normalized, self.z, stream)
+        capi.check("q3x_b200_causal_conv1d_silu", self.qkv, T, GDN_CHANNELS, self.conv_w, self.conv_history, self.conv_out, stream)
+        capi.check("q3x_b200_gated_delta_net_update", self.conv_out, T, self.a, self.b, self.A_log, self.dt_bias, self.state,
+                   self.state, EPS, self.core, stream)
+        capi.check("q3x_b200_rms_norm_silu_gate_nvfp4", self.core, self.gdn_norm_w, self.z, T, 48, 128, EPS, CHUNK, self.gated,
+                   self.scratch, self.gated_gs, self.gated_codes, self.gated_scales, stream)
+        capi.check("q3x_b200_nvfp4_swizzle_block_scales", self.gated_scales, T, GDN_V, self.gated_swizzled, stream)
+        capi.check("q3x_b200_nvfp4_gemm_bf16", self.gated_codes, self.gated_swizzled, self.gated_gs, CHUNK, self.w_o["codes"],
+                   self.w_o["swizzled"], self.w_o["scale_2"], T, HIDDEN, GDN_V, self.mixer_projected, self.workspace,
+                   self.workspace.numel(), stream)
+        self.mlp.enqueue(stream)
+
+    def check_error(self) -> None:
+        if int(self.scratch[-1].item()) != 0:
+            raise RuntimeError("a bounded wait of a single-kernel NVFP4 operator gave up: outputs are invalid")
+        self.mlp.check_error()

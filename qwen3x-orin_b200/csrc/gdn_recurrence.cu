@@ -142,6 +142,111 @@ __global__ void __launch_bounds__(kThreads, 1) gdn_recurrence_kernel(
   }
 }
 
+// ---- many tokens in one call ---------------------------------------------------------------------------------
+// The loop above pays, for every token, the L2 round trips of its inputs and the libm chains of its gates before the
+// state arithmetic can start.  None of that depends on the state, so for a tile of tokens it is done kGdnBatch tokens
+// at a time and in parallel: half-warps normalise q and k and derive alpha and beta of one token each (the same
+// 16-lane sums and the same expressions as above, so the same bits), every thread stages the value rows, all into
+// shared memory; then the 1024 threads run the state arithmetic of those tokens back to back out of shared memory,
+// and the rounded outputs leave as one coalesced block.  Two barriers per batch instead of a dozen dependent
+// latencies per token.
+constexpr int kGdnBatch = 16;
+
+__global__ void __launch_bounds__(kThreads, 1) gdn_recurrence_tile_kernel(
+    const uint16_t* __restrict__ conv_qkv, size_t tokens, const uint16_t* __restrict__ a,
+    const uint16_t* __restrict__ b, const uint16_t* __restrict__ A_log, const uint16_t* __restrict__ dt_bias,
+    const uint4* state_in, uint4* state_out, float l2_eps, uint16_t* out) {
+  __shared__ __align__(16) float sq[kGdnBatch][kHead];
+  __shared__ __align__(16) float sk[kGdnBatch][kHead];
+  __shared__ float sv[kGdnBatch][kHead];
+  __shared__ float s_alpha[kGdnBatch], s_beta[kGdnBatch];
+  __shared__ __align__(16) uint16_t s_out[kGdnBatch][kHead];
+  const int head = blockIdx.x;
+  const int lane = threadIdx.x & (kLanesPerRow - 1);
+  const int group = threadIdx.x / kLanesPerRow;  // 64 groups of 16 lanes
+  const int row0 = group;                        // state rows row0 and row0 + 64
+  const int qk_head = head / 3;
+
+  float S[kPasses][8];
+#pragma unroll
+  for (int p = 0; p < kPasses; ++p) {
+    const size_t vec = (static_cast<size_t>(head) * kHead + row0 + p * kRowsPerPass) * kLanesPerRow + lane;
+    unpack8(ld_vec(state_in + vec), S[p]);
+  }
+  const float a_decay = -expf(bf16_to_float(A_log[head]));
+  const float bias = bf16_to_float(dt_bias[head]);
+  const float inv_sqrt_dim = __fdiv_rn(1.0f, sqrtf(static_cast<float>(kHead)));
+
+  for (size_t t0 = 0; t0 < tokens; t0 += kGdnBatch) {
+    const int count = static_cast<int>(min(static_cast<size_t>(kGdnBatch), tokens - t0));
+    // ---- prepare: group i < 16 takes token t0 + i (whole warps, so the 16-lane shuffles name live lanes)
+    if (group < kGdnBatch) {
+      const bool live = group < count;
+      const uint16_t* row = conv_qkv + (t0 + (live ? group : 0)) * kChannels;
+      float q[8], k[8];
+      unpack8(live ? ld_weight(reinterpret_cast<const uint4*>(row + qk_head * kHead) + lane) : make_uint4(0, 0, 0, 0), q);
+      unpack8(live ? ld_weight(reinterpret_cast<const uint4*>(row + kKOffset + qk_head * kHead) + lane) : make_uint4(0, 0, 0, 0), k);
+      const float q_sum = group_sum<kLanesPerRow>(dot8(q, q));
+      const float k_sum = group_sum<kLanesPerRow>(dot8(k, k));
+      const float q_scale = __fdiv_rn(1.0f, sqrtf(q_sum + l2_eps)) * inv_sqrt_dim;
+      const float k_scale = __fdiv_rn(1.0f, sqrtf(k_sum + l2_eps));
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        sq[group][lane * 8 + i] = q[i] * q_scale;
+        sk[group][lane * 8 + i] = k[i] * k_scale;
+      }
+      if (lane == 0 && live) {
+        const float g = a_decay * softplus_ref(bf16_to_float(a[(t0 + group) * kValueHeads + head]) + bias);
+        s_alpha[group] = expf(g);
+        s_beta[group] = sigmoid_ref(bf16_to_float(b[(t0 + group) * kValueHeads + head]));
+      }
+    }
+    for (int i = threadIdx.x; i < count * kHead; i += kThreads) {
+      const int t = i / kHead, v = i % kHead;
+      sv[t][v] = bf16_to_float(conv_qkv[(t0 + t) * kChannels + kVOffset + head * kHead + v]);
+    }
+    __syncthreads();
+    // ---- the recurrence over the prepared tokens
+    for (int t = 0; t < count; ++t) {
+      float q[8], k[8];
+      *reinterpret_cast<float4*>(q) = *reinterpret_cast<const float4*>(&sq[t][lane * 8]);
+      *reinterpret_cast<float4*>(q + 4) = *reinterpret_cast<const float4*>(&sq[t][lane * 8 + 4]);
+      *reinterpret_cast<float4*>(k) = *reinterpret_cast<const float4*>(&sk[t][lane * 8]);
+      *reinterpret_cast<float4*>(k + 4) = *reinterpret_cast<const float4*>(&sk[t][lane * 8 + 4]);
+      const float alpha = s_alpha[t], beta = s_beta[t];
+#pragma unroll
+      for (int p = 0; p < kPasses; ++p) {
+        const int v = row0 + p * kRowsPerPass;
+        float decayed[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) decayed[i] = alpha * S[p][i];
+        const float pred = group_sum<kLanesPerRow>(dot8(decayed, k));
+        const float delta = (sv[t][v] - pred) * beta;
+        float updated[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) updated[i] = fmaf(delta, k[i], decayed[i]);
+        const float result = group_sum<kLanesPerRow>(dot8(updated, q));
+        const uint4 packed = pack8(updated);  // the state crosses a bf16 boundary after every step
+        unpack8(packed, S[p]);
+        if (lane == 0) s_out[t][v] = float_to_bf16(result);
+      }
+    }
+    __syncthreads();
+    // ---- the batch's outputs: count x 128 bf16 of this head, 16 bytes per thread
+    for (int i = threadIdx.x; i < count * (kHead / 8); i += kThreads) {
+      const int t = i / (kHead / 8), c = i % (kHead / 8);
+      st_vec(out + ((t0 + t) * kValueHeads + head) * kHead + c * 8, *reinterpret_cast<const uint4*>(&s_out[t][c * 8]));
+    }
+    // (the next batch's preparation writes sq / sk / sv, which every thread has finished reading at the barrier
+    // above; s_out is rewritten only after the next batch's first barrier)
+  }
+#pragma unroll
+  for (int p = 0; p < kPasses; ++p) {
+    const size_t vec = (static_cast<size_t>(head) * kHead + row0 + p * kRowsPerPass) * kLanesPerRow + lane;
+    st_vec(state_out + vec, pack8(S[p]));
+  }
+}
+
 int launch_gdn(const uint16_t* conv_qkv, size_t tokens, const uint16_t* a, const uint16_t* b, const uint16_t* A_log,
                const uint16_t* dt_bias, const uint16_t* state_in, uint16_t* state_out, float l2_eps,
                const uint16_t* norm_weight, const uint16_t* norm_gate, float norm_eps, bool norm, uint16_t* out,
@@ -178,6 +283,8 @@ int launch_gdn(const uint16_t* conv_qkv, size_t tokens, const uint16_t* a, const
     gdn_recurrence_kernel<true><<<kValueHeads, kThreads, 0, s>>>(conv_qkv, tokens, a, b, A_log, dt_bias, SI, SO,
                                                                  l2_eps, reinterpret_cast<const uint4*>(norm_weight),
                                                                  norm_gate, norm_eps, out);
+  else if (tokens >= 4)
+    gdn_recurrence_tile_kernel<<<kValueHeads, kThreads, 0, s>>>(conv_qkv, tokens, a, b, A_log, dt_bias, SI, SO, l2_eps, out);
   else
     gdn_recurrence_kernel<false><<<kValueHeads, kThreads, 0, s>>>(conv_qkv, tokens, a, b, A_log, dt_bias, SI, SO,
                                                                   l2_eps, nullptr, nullptr, 1.0f, out);
