@@ -847,10 +847,10 @@ def probe_projection_ops(cuda_index=0, aim_ms=60.0, tokens=8192):
     gdn.check_error()
     us = e0.elapsed_time(e1) * 1e3 / reps
     out["gdn_layer_with_projections"] = {
-        "tokens": tokens, "us": round(us, 1), "tokens_per_s": round(tokens / (us * 1e-6), 1), "kernels": 18,
+        "tokens": tokens, "us": round(us, 1), "tokens_per_s": round(tokens / (us * 1e-6), 1), "kernels": 20,
         "recurrence_us": round(r0.elapsed_time(r1) * 1e3, 1),
-        "note": "residual+RMSNorm, qkv / z projections (FP8 weights), conv1d+SiLU, token-sequential recurrence, gated "
-                "RMSNorm+NVFP4, scale re-layout, NVFP4 output projection, MLP block; synthetic weights and gate inputs"}
+        "note": "residual+RMSNorm, qkv / z (FP8 weights) and a / b (bf16 weights) projections, conv1d+SiLU, token-sequential recurrence, gated "
+                "RMSNorm+NVFP4, scale re-layout, NVFP4 output projection, MLP block; synthetic weights"}
     del gdn
     torch.cuda.empty_cache()
     return out

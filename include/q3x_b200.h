@@ -167,6 +167,16 @@ int q3x_b200_nvfp4_swizzle_block_scales(const uint8_t* row_major, size_t rows, s
  * (launch_projection_to_bf16_cuda, include/q3x/runtime/model_weights.h:794-841, kernel
  * src/kernels/sm87/nvfp4_marlin_w4a16.cu); this is that projection with the activation operand taken from
  * this library's quantiser, so it has the reference's shape contract but not its numerics. */
+/* The bf16 projection of a panel of tokens: out[tokens, out_features] = activations[tokens, in_features] x W^T with
+ * W = [out_features, in_features] bf16 -- q3x_b200_bf16_gemv for many tokens (bf16_gemv_reference_cpu,
+ * src/kernels/reference/gemv_reference.cpp:84-111, per token; launch_projection_tile_to_bf16_cuda for
+ * Bf16LinearWeight, include/q3x/runtime/model_weights.h:800-826).  Tensor cores, FP32 accumulation, one rounding.
+ * in_features and out_features must be multiples of 8; pointers 16-byte aligned; workspace as for
+ * q3x_b200_fp8_gemm_bf16. */
+size_t q3x_b200_bf16_gemm_workspace_bytes(size_t tokens, size_t out_features, size_t in_features);
+int q3x_b200_bf16_gemm_bf16(const uint16_t* weights, const uint16_t* activations, size_t tokens, size_t out_features,
+                            size_t in_features, uint16_t* out, void* workspace, size_t workspace_bytes, void* stream);
+
 /* The weight-only FP8 projection of a panel of tokens: out[tokens, out_features] (bf16, row-major) =
  * activations[tokens, in_features] (bf16) x W^T with W = [out_features, in_features] E4M3 bytes and one FP32
  * scale for the tensor -- q3x_b200_fp8_gemv for many tokens (fp8_gemv_reference_cpu,

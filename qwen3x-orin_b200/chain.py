@@ -463,15 +463,15 @@ class ProjectedAttentionLayer:
 
 
 class ProjectedGdnLayer:
-    """One gated-delta-net layer of the stack for a tile of tokens, every operator and every projection but the two
-    48-wide gate projections from this library (the reference's layer segment, src/runtime/reference_runner.cpp:
-    9565-10584):
+    """One gated-delta-net layer of the stack for a tile of tokens, every operator and every projection from this
+    library (the reference's layer segment, src/runtime/reference_runner.cpp:9565-10584):
 
-        residual + RMSNorm  ->  qkv and z projections (FP8 weights, bf16 activations, tensor cores)  ->  causal
+        residual + RMSNorm  ->  qkv and z projections (FP8 weights, bf16 activations, tensor cores) and the two gate
+        projections a, b (bf16 weights, 48 x 5120)  ->  causal
         conv1d + SiLU (history carried)  ->  gated-delta-net recurrence (state carried; token by token inside one
         launch)  ->  gated RMSNorm * silu(z) + NVFP4  ->  output projection (NVFP4 x NVFP4)  ->  the MLP block
 
-    The a / b gate inputs ([tokens, 48] each, bf16 projections in the model) are synthetic.  Weights are synthetic."""
+    Weights are synthetic."""
 
     def __init__(self, tokens: int, device, intermediate: int = INTERMEDIATE, seed: int = 31):
         self.tokens, self.device = tokens, device
@@ -503,7 +503,8 @@ class ProjectedGdnLayer:
         self.conv_history = torch.zeros((GDN_CHANNELS, 3), **bf)
         self.A_log = (torch.rand(48, generator=gen, device=device) * 5.5 - 4.0).to(torch.bfloat16)
         self.dt_bias = (torch.rand(48, generator=gen, device=device) * 6.0 - 3.0).to(torch.bfloat16)
-        self.a, self.b = rand((tokens, 48), 2.0), rand((tokens, 48), 2.0)
+        self.w_a, self.w_b = rand((48, HIDDEN), 0.03), rand((48, HIDDEN), 0.03)
+        self.a, self.b = torch.empty((tokens, 48), **bf), torch.empty((tokens, 48), **bf)
         self.state = rand((48, 128, 128), 0.05)
         self.residual_in, self.previous_mlp_out = rand((tokens, HIDDEN)), rand((tokens, HIDDEN))
         self.residual_mid, self.normalized = torch.empty((tokens, HIDDEN), **bf), torch.empty((tokens, HIDDEN), **bf)
@@ -530,6 +531,8 @@ class ProjectedGdnLayer:
                    EPS, self.residual_mid, self.normalized, stream)
         self._fp8(self.w_qkv, self.normalized, self.qkv, stream)
         self._fp8(self.w_z, self.normalized, self.z, stream)
+        capi.check("q3x_b200_bf16_gemm_bf16", self.w_a, self.normalized, T, 48, HIDDEN, self.a, None, 0, stream)
+        capi.check("q3x_b200_bf16_gemm_bf16", self.w_b, self.normalized, T, 48, HIDDEN, self.b, None, 0, stream)
         capi.check("q3x_b200_causal_conv1d_silu", self.qkv, T, GDN_CHANNELS, self.conv_w, self.conv_history, self.conv_out, stream)
         capi.check("q3x_b200_gated_delta_net_update", self.conv_out, T, self.a, self.b, self.A_log, self.dt_bias, self.state,
                    self.state, EPS, self.core, stream)

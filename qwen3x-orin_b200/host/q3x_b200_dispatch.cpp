@@ -163,9 +163,9 @@ int launch_projection_tile_to_bf16_cuda(const ProjectionBackend backend, const L
                                         const std::uint16_t* input, const std::size_t token_count,
                                         float* /*fp32_scratch*/, std::size_t /*scratch_elements*/, std::uint16_t* output,
                                         void* cuda_stream) noexcept {
-  // The whole tile is validated before anything is enqueued (model_weights.h:824-825).  FP8 weights of two or
-  // more tokens go to the tensor-core weight-only GEMM (one pass over the weights); everything else runs as
-  // ordered batch-one projections.
+  // The whole tile is validated before anything is enqueued (model_weights.h:824-825).  FP8 and bf16 weights of two
+  // or more tokens go to the tensor-core GEMMs (one pass over the weights); everything else runs as ordered
+  // batch-one projections.
   if (!projection_backend_served_by_b200(backend)) return kInvalidValue;
   const Shape s = describe(weight);
   if (!s.valid || input == nullptr || output == nullptr || token_count == 0U ||
@@ -178,6 +178,11 @@ int launch_projection_tile_to_bf16_cuda(const ProjectionBackend backend, const L
     const int st = q3x_b200_fp8_gemm_bf16(fp8->weight, fp8->weight_scale, input, token_count, s.rows, s.cols, output,
                                           nullptr, 0U, cuda_stream);
     if (st != kNotSupported) return st;  // a shape or alignment the GEMM does not take: token by token below
+  }
+  if (const auto* dense = std::get_if<Bf16LinearWeight>(&weight);
+      dense != nullptr && token_count >= 2U && s.cols % 8U == 0U && s.rows % 8U == 0U) {
+    const int st = q3x_b200_bf16_gemm_bf16(dense->weight, input, token_count, s.rows, s.cols, output, nullptr, 0U, cuda_stream);
+    if (st != kNotSupported) return st;
   }
   for (std::size_t t = 0U; t < token_count; ++t)
     if (const int st = project(weight, input + t * s.cols, output + t * s.rows, cuda_stream); st != 0) return st;

@@ -322,7 +322,7 @@ static void test_composites(cudaStream_t s) {
   EXPECT(q3x_b200_fp8_gemv(fp8_w.p, 0.02f, left.p, inter, hidden, nullptr, p2.p, s) == 0);
   EXPECT(same(p1, p2) && written(p1));
   // the sequence-tile form: FP8 weights of several tokens go through the weight-only tensor-core GEMM (same bytes
-  // as the C-ABI call), one token through the batch-one kernel; bf16 weights run token by token
+  // as the C-ABI call), one token through the batch-one kernel; bf16 weights likewise
   {
     Bf16 xs3(random_bf16(3 * hidden, 1.0f)), t1(3 * inter), t2(3 * inter), t3(inter);
     EXPECT(rt::launch_projection_tile_to_bf16_cuda(rt::ProjectionBackend::kSm87WeightOnly, f8_lw, xs3.p, 3, nullptr, 0, t1.p,
@@ -342,8 +342,7 @@ static void test_composites(cudaStream_t s) {
     Bf16 d1(3 * hidden), d2(3 * hidden), acts(random_bf16(3 * inter, 0.5f));
     EXPECT(rt::launch_projection_tile_to_bf16_cuda(rt::ProjectionBackend::kReference, down_lw, acts.p, 3, nullptr, 0, d1.p,
                                                    s) == 0);
-    for (std::size_t t = 0; t < 3; ++t)
-      EXPECT(q3x_b200_bf16_gemv(down_w.p, acts.p + t * inter, hidden, inter, nullptr, d2.p + t * hidden, s) == 0);
+    EXPECT(q3x_b200_bf16_gemm_bf16(down_w.p, acts.p, 3, hidden, inter, d2.p, nullptr, 0, s) == 0);
     EXPECT(same(d1, d2) && written(d1));
     EXPECT(rt::launch_projection_tile_to_bf16_cuda(rt::ProjectionBackend::kSm87WeightOnly, f8_lw, xs3.p, 65, nullptr, 0, t1.p,
                                                    s) == 1);

@@ -36,6 +36,11 @@ def test_gdn_layer_stage_by_stage():
     x = host(layer.normalized)
     assert_fp8_projection(host(layer.qkv), x, layer.w_qkv, "qkv projection")
     assert_fp8_projection(host(layer.z), x, layer.w_z, "z projection")
+    for name, got_t, w_t in (("a", layer.a, layer.w_a), ("b", layer.b, layer.w_b)):
+        wf, xf = orc.bf16_decode(host(w_t)).astype(np.float64), orc.bf16_decode(x).astype(np.float64)
+        want, mag = xf @ wf.T, np.abs(xf) @ np.abs(wf).T
+        got = orc.bf16_decode(host(got_t)).astype(np.float64)
+        assert np.all(np.abs(got - want) <= 2.0 ** -8 * np.abs(want) + 1e-5 * mag + 1e-30), f"{name} gate projection"
     # conv on the GPU's own projection, history carried out
     conv_want, hist_want = orc.causal_conv1d_silu(host(layer.qkv), host(layer.conv_w), history0)
     gpu_util.assert_bf16_within(host(layer.conv_out), conv_want, 1, 0.98, "conv")
