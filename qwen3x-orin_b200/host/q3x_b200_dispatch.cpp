@@ -5,6 +5,7 @@
 #include "q3x_b200_dispatch.hpp"
 
 #include <cmath>
+#include <string_view>
 #include <type_traits>
 #include <variant>
 
@@ -148,6 +149,117 @@ int post_attention(const ProjectionBackend backend, const LinearWeight& gate_wei
 
 }  // namespace
 
+#if defined(Q3X_B200_USE_REFERENCE_HEADERS)
+// declared (not defined) by the reference's header: model_weights.h:389-391
+bool is_valid_projection_backend(const ProjectionBackend backend) noexcept {
+  return static_cast<std::uint8_t>(backend) <= static_cast<std::uint8_t>(ProjectionBackend::kSm87WeightOnly);
+}
+std::string_view to_string(const ProjectionBackend backend) noexcept {
+  switch (static_cast<std::uint8_t>(backend)) {
+    case 0U: return "reference";
+    case 1U: return "sm87-weight-only";
+    default: return "invalid";
+  }
+}
+#endif
+
+LinearWeightKind linear_weight_kind(const LinearWeight& weight) noexcept {
+  return static_cast<LinearWeightKind>(weight.valueless_by_exception() ? 0U : weight.index());
+}
+std::size_t linear_output_size(const LinearWeight& weight) noexcept {
+  return weight.valueless_by_exception() ? 0U : std::visit([](const auto& w) noexcept { return w.output_size; }, weight);
+}
+std::size_t linear_input_size(const LinearWeight& weight) noexcept {
+  return weight.valueless_by_exception() ? 0U : std::visit([](const auto& w) noexcept { return w.input_size; }, weight);
+}
+
+namespace {
+// "the explicitly selected weight-only backend" of the predicates below; this library's own value counts too
+bool weight_only(const ProjectionBackend backend) noexcept {
+  return backend == ProjectionBackend::kSm87WeightOnly || backend == kProjectionBackendB200LayerOps;
+}
+template <class W>
+bool shaped(const LinearWeight& weight, const std::size_t rows, const std::size_t cols) noexcept {
+  if (weight.valueless_by_exception() || std::get_if<W>(&weight) == nullptr) return false;
+  const Shape s = describe(weight);
+  return s.valid && s.rows == rows && s.cols == cols;
+}
+}  // namespace
+
+bool supports_bf16_projection_pair(const ProjectionBackend backend, const LinearWeight& first,
+                                   const LinearWeight& second) noexcept {
+  return weight_only(backend) && shaped<Bf16LinearWeight>(first, 48U, kHidden) && shaped<Bf16LinearWeight>(second, 48U, kHidden);
+}
+bool supports_fp8_projection_pair(const ProjectionBackend backend, const LinearWeight& first,
+                                  const LinearWeight& second) noexcept {
+  return weight_only(backend) && shaped<Fp8LinearWeight>(first, 1024U, kHidden) && shaped<Fp8LinearWeight>(second, 1024U, kHidden);
+}
+bool supports_fp8_qkv_z_projection_pair(const ProjectionBackend backend, const LinearWeight& qkv,
+                                        const LinearWeight& z) noexcept {
+  return weight_only(backend) && shaped<Fp8LinearWeight>(qkv, 10240U, kHidden) && shaped<Fp8LinearWeight>(z, 6144U, kHidden);
+}
+bool supports_linear_attention_qkv_z_ab_projection_fusion(const ProjectionBackend backend, const LinearWeight& qkv,
+                                                          const LinearWeight& z, const LinearWeight& a,
+                                                          const LinearWeight& b) noexcept {
+  return supports_fp8_qkv_z_projection_pair(backend, qkv, z) && supports_bf16_projection_pair(backend, a, b);
+}
+bool supports_fp8_q_kv_projection_fusion(const ProjectionBackend backend, const LinearWeight& q, const LinearWeight& key,
+                                         const LinearWeight& value) noexcept {
+  return weight_only(backend) && shaped<Fp8LinearWeight>(q, 12288U, kHidden) && supports_fp8_projection_pair(backend, key, value);
+}
+bool supports_nvfp4_gate_up_silu_fusion(const ProjectionBackend backend, const LinearWeight& gate,
+                                        const LinearWeight& up) noexcept {
+  return weight_only(backend) && shaped<NvFp4LinearWeight>(gate, 17408U, kHidden) && shaped<NvFp4LinearWeight>(up, 17408U, kHidden);
+}
+bool supports_nvfp4_down_residual_norm_fusion(const ProjectionBackend backend, const LinearWeight& down) noexcept {
+  return weight_only(backend) && shaped<NvFp4LinearWeight>(down, kHidden, 17408U);
+}
+
+int launch_projection_reference_cuda(const LinearWeight& weight, const std::uint16_t* input, float* output,
+                                     void* cuda_stream) noexcept {
+  const Shape s = describe(weight);
+  if (!s.valid || input == nullptr || output == nullptr) return kInvalidValue;
+  if (overlaps(output, s.rows * 4U, input, s.cols * 2U) || touches_weight(output, s.rows * 4U, s)) return kInvalidValue;
+  return std::visit(
+      [&](const auto& w) noexcept -> int {
+        using W = std::decay_t<decltype(w)>;
+        if constexpr (std::is_same_v<W, Bf16LinearWeight>)
+          return q3x_b200_bf16_gemv(w.weight, input, w.output_size, w.input_size, output, nullptr, cuda_stream);
+        else if constexpr (std::is_same_v<W, Fp8LinearWeight>)
+          return q3x_b200_fp8_gemv(w.weight, w.weight_scale, input, w.output_size, w.input_size, output, nullptr, cuda_stream);
+        else
+          return q3x_b200_nvfp4_gemv(w.packed_weight, w.block_scale, w.weight_scale_2, input, w.output_size, w.input_size,
+                                     output, nullptr, cuda_stream);
+      },
+      weight);
+}
+
+int launch_projection_to_bf16_reference_cuda(const LinearWeight& weight, const std::uint16_t* input, float* fp32_scratch,
+                                             const std::size_t scratch_elements, std::uint16_t* output,
+                                             void* cuda_stream) noexcept {
+  // the two-stage path: the FP32 result lands in the caller's scratch, its rounding in `output` (one kernel here)
+  const Shape s = describe(weight);
+  if (!s.valid || input == nullptr || output == nullptr || fp32_scratch == nullptr || scratch_elements < s.rows)
+    return kInvalidValue;
+  if (overlaps(output, s.rows * 2U, input, s.cols * 2U) || touches_weight(output, s.rows * 2U, s) ||
+      overlaps(fp32_scratch, s.rows * 4U, input, s.cols * 2U) || touches_weight(fp32_scratch, s.rows * 4U, s) ||
+      overlaps(fp32_scratch, s.rows * 4U, output, s.rows * 2U))
+    return kInvalidValue;
+  return std::visit(
+      [&](const auto& w) noexcept -> int {
+        using W = std::decay_t<decltype(w)>;
+        if constexpr (std::is_same_v<W, Bf16LinearWeight>)
+          return q3x_b200_bf16_gemv(w.weight, input, w.output_size, w.input_size, fp32_scratch, output, cuda_stream);
+        else if constexpr (std::is_same_v<W, Fp8LinearWeight>)
+          return q3x_b200_fp8_gemv(w.weight, w.weight_scale, input, w.output_size, w.input_size, fp32_scratch, output,
+                                   cuda_stream);
+        else
+          return q3x_b200_nvfp4_gemv(w.packed_weight, w.block_scale, w.weight_scale_2, input, w.output_size, w.input_size,
+                                     fp32_scratch, output, cuda_stream);
+      },
+      weight);
+}
+
 int launch_projection_to_bf16_cuda(const ProjectionBackend backend, const LinearWeight& weight,
                                    const std::uint16_t* input, float* /*fp32_scratch*/,
                                    std::size_t /*scratch_elements*/, std::uint16_t* output, void* cuda_stream) noexcept {
@@ -186,6 +298,81 @@ int launch_projection_tile_to_bf16_cuda(const ProjectionBackend backend, const L
   }
   for (std::size_t t = 0U; t < token_count; ++t)
     if (const int st = project(weight, input + t * s.cols, output + t * s.rows, cuda_stream); st != 0) return st;
+  return 0;
+}
+
+namespace {
+// Validation of several projections over one shared activation: every weight valid, the same input width, every
+// output disjoint from the input, from every weight and from every other output -- all before the first enqueue.
+struct SharedInputProjection {
+  const LinearWeight* weight;
+  std::uint16_t* output;
+};
+template <std::size_t N>
+int check_shared_input(const ProjectionBackend backend, const SharedInputProjection (&p)[N], const std::uint16_t* input,
+                       const std::size_t token_count) noexcept {
+  if (!projection_backend_served_by_b200(backend) || input == nullptr || token_count == 0U) return kInvalidValue;
+  Shape shapes[N];
+  for (std::size_t i = 0; i < N; ++i) {
+    if (p[i].weight->valueless_by_exception() || p[i].output == nullptr) return kInvalidValue;
+    shapes[i] = describe(*p[i].weight);
+    if (!shapes[i].valid || shapes[i].cols != shapes[0].cols) return kInvalidValue;
+  }
+  const std::size_t in_bytes = token_count * shapes[0].cols * 2U;
+  for (std::size_t i = 0; i < N; ++i) {
+    const std::size_t out_bytes = token_count * shapes[i].rows * 2U;
+    if (overlaps(p[i].output, out_bytes, input, in_bytes)) return kInvalidValue;
+    for (std::size_t j = 0; j < N; ++j) {
+      if (touches_weight(p[i].output, out_bytes, shapes[j])) return kInvalidValue;
+      if (j != i && overlaps(p[i].output, out_bytes, p[j].output, token_count * shapes[j].rows * 2U)) return kInvalidValue;
+    }
+  }
+  return 0;
+}
+}  // namespace
+
+int launch_projection_pair_tile_to_bf16_cuda(const ProjectionBackend backend, const LinearWeight& first_weight,
+                                             const LinearWeight& second_weight, const std::uint16_t* input,
+                                             const std::size_t token_count, float* fp32_scratch,
+                                             const std::size_t scratch_elements, std::uint16_t* first_output,
+                                             std::uint16_t* second_output, void* cuda_stream) noexcept {
+  if (token_count > kMaximumProjectionTileTokenCount) return kInvalidValue;
+  const SharedInputProjection pair[] = {{&first_weight, first_output}, {&second_weight, second_output}};
+  if (const int st = check_shared_input(backend, pair, input, token_count); st != 0) return st;
+  if (const int st = launch_projection_tile_to_bf16_cuda(backend, first_weight, input, token_count, fp32_scratch,
+                                                         scratch_elements, first_output, cuda_stream);
+      st != 0)
+    return st;
+  return launch_projection_tile_to_bf16_cuda(backend, second_weight, input, token_count, fp32_scratch, scratch_elements,
+                                             second_output, cuda_stream);
+}
+
+int launch_linear_attention_qkv_z_ab_to_bf16_cuda(const ProjectionBackend backend, const LinearWeight& qkv_weight,
+                                                  const LinearWeight& z_weight, const LinearWeight& a_weight,
+                                                  const LinearWeight& b_weight, const std::uint16_t* input,
+                                                  std::uint16_t* qkv_output, std::uint16_t* z_output,
+                                                  std::uint16_t* a_output, std::uint16_t* b_output,
+                                                  void* cuda_stream) noexcept {
+  // structurally ineligible calls are "not supported" so that the caller keeps its two-call route (model_weights.h:892-897)
+  if (!supports_linear_attention_qkv_z_ab_projection_fusion(backend, qkv_weight, z_weight, a_weight, b_weight))
+    return kNotSupported;
+  const SharedInputProjection group[] = {{&qkv_weight, qkv_output}, {&z_weight, z_output}, {&a_weight, a_output}, {&b_weight, b_output}};
+  if (const int st = check_shared_input(backend, group, input, 1U); st != 0) return st;
+  for (const SharedInputProjection& p : group)
+    if (const int st = project(*p.weight, input, p.output, cuda_stream); st != 0) return st;
+  return 0;
+}
+
+int launch_full_attention_q_kv_to_bf16_cuda(const ProjectionBackend backend, const LinearWeight& q_weight,
+                                            const LinearWeight& key_weight, const LinearWeight& value_weight,
+                                            const std::uint16_t* input, float* /*fp32_scratch*/,
+                                            std::size_t /*scratch_elements*/, std::uint16_t* q_output,
+                                            std::uint16_t* key_output, std::uint16_t* value_output,
+                                            void* cuda_stream) noexcept {
+  const SharedInputProjection group[] = {{&q_weight, q_output}, {&key_weight, key_output}, {&value_weight, value_output}};
+  if (const int st = check_shared_input(backend, group, input, 1U); st != 0) return st;
+  for (const SharedInputProjection& p : group)
+    if (const int st = project(*p.weight, input, p.output, cuda_stream); st != 0) return st;
   return 0;
 }
 

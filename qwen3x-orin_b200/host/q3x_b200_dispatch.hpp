@@ -77,6 +77,53 @@ enum class ProjectionBackend : std::uint8_t {
   return static_cast<std::uint8_t>(backend) <= static_cast<std::uint8_t>(ProjectionBackend::kB200LayerOps);
 }
 
+// model_weights.h:393-398
+[[nodiscard]] LinearWeightKind linear_weight_kind(const LinearWeight& weight) noexcept;
+[[nodiscard]] std::size_t linear_output_size(const LinearWeight& weight) noexcept;
+[[nodiscard]] std::size_t linear_input_size(const LinearWeight& weight) noexcept;
+// model_weights.h:400-466: shape / type / payload eligibility of the fused routes (host only)
+[[nodiscard]] bool supports_bf16_projection_pair(ProjectionBackend backend, const LinearWeight& first_weight,
+                                                 const LinearWeight& second_weight) noexcept;
+[[nodiscard]] bool supports_fp8_projection_pair(ProjectionBackend backend, const LinearWeight& first_weight,
+                                                const LinearWeight& second_weight) noexcept;
+[[nodiscard]] bool supports_fp8_qkv_z_projection_pair(ProjectionBackend backend, const LinearWeight& qkv_weight,
+                                                      const LinearWeight& z_weight) noexcept;
+[[nodiscard]] bool supports_linear_attention_qkv_z_ab_projection_fusion(ProjectionBackend backend,
+                                                                        const LinearWeight& qkv_weight,
+                                                                        const LinearWeight& z_weight,
+                                                                        const LinearWeight& a_weight,
+                                                                        const LinearWeight& b_weight) noexcept;
+[[nodiscard]] bool supports_fp8_q_kv_projection_fusion(ProjectionBackend backend, const LinearWeight& q_weight,
+                                                       const LinearWeight& key_weight,
+                                                       const LinearWeight& value_weight) noexcept;
+[[nodiscard]] bool supports_nvfp4_gate_up_silu_fusion(ProjectionBackend backend, const LinearWeight& gate_weight,
+                                                      const LinearWeight& up_weight) noexcept;
+[[nodiscard]] bool supports_nvfp4_down_residual_norm_fusion(ProjectionBackend backend,
+                                                            const LinearWeight& down_weight) noexcept;
+// model_weights.h:770-787: FP32 output, and the two-step form that also leaves the FP32 result in the scratch
+[[nodiscard]] int launch_projection_reference_cuda(const LinearWeight& weight, const std::uint16_t* input, float* output,
+                                                   void* cuda_stream = nullptr) noexcept;
+[[nodiscard]] int launch_projection_to_bf16_reference_cuda(const LinearWeight& weight, const std::uint16_t* input,
+                                                           float* fp32_scratch, std::size_t scratch_elements,
+                                                           std::uint16_t* output, void* cuda_stream = nullptr) noexcept;
+// model_weights.h:885-918: two, three and four projections over one shared activation
+[[nodiscard]] int launch_projection_pair_tile_to_bf16_cuda(ProjectionBackend backend, const LinearWeight& first_weight,
+                                                           const LinearWeight& second_weight, const std::uint16_t* input,
+                                                           std::size_t token_count, float* fp32_scratch,
+                                                           std::size_t scratch_elements, std::uint16_t* first_output,
+                                                           std::uint16_t* second_output,
+                                                           void* cuda_stream = nullptr) noexcept;
+[[nodiscard]] int launch_linear_attention_qkv_z_ab_to_bf16_cuda(
+    ProjectionBackend backend, const LinearWeight& qkv_weight, const LinearWeight& z_weight, const LinearWeight& a_weight,
+    const LinearWeight& b_weight, const std::uint16_t* input, std::uint16_t* qkv_output, std::uint16_t* z_output,
+    std::uint16_t* a_output, std::uint16_t* b_output, void* cuda_stream = nullptr) noexcept;
+[[nodiscard]] int launch_full_attention_q_kv_to_bf16_cuda(ProjectionBackend backend, const LinearWeight& q_weight,
+                                                          const LinearWeight& key_weight,
+                                                          const LinearWeight& value_weight, const std::uint16_t* input,
+                                                          float* fp32_scratch, std::size_t scratch_elements,
+                                                          std::uint16_t* q_output, std::uint16_t* key_output,
+                                                          std::uint16_t* value_output,
+                                                          void* cuda_stream = nullptr) noexcept;
 [[nodiscard]] int launch_projection_to_bf16_cuda(ProjectionBackend backend, const LinearWeight& weight,
                                                  const std::uint16_t* input, float* fp32_scratch,
                                                  std::size_t scratch_elements, std::uint16_t* output,

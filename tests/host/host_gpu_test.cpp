@@ -373,6 +373,65 @@ static void test_composites(cudaStream_t s) {
     EXPECT(rt::launch_exact_fp8_whole_chunk_projection_to_bf16_cuda(rt::ProjectionBackend::kSm87WeightOnly, kv_lw, xc.p, chunk,
                                                                     xc.p, s) == 1);             // output on the input
   }
+  // FP32 output, and the two-step form that leaves the FP32 result in the scratch as well
+  {
+    DeviceBuffer<float> y1(inter), y2(inter), y3(inter);
+    Bf16 b1(inter);
+    EXPECT(rt::launch_projection_reference_cuda(f8_lw, left.p, y1.p, s) == 0);
+    EXPECT(q3x_b200_fp8_gemv(fp8_w.p, 0.02f, left.p, inter, hidden, y2.p, nullptr, s) == 0);
+    EXPECT(rt::launch_projection_to_bf16_reference_cuda(f8_lw, left.p, y3.p, inter, b1.p, s) == 0);
+    EXPECT(cudaStreamSynchronize(static_cast<cudaStream_t>(s)) == cudaSuccess);
+    std::vector<float> a(inter), b(inter), c(inter);
+    cudaMemcpy(a.data(), y1.p, inter * 4, cudaMemcpyDeviceToHost);
+    cudaMemcpy(b.data(), y2.p, inter * 4, cudaMemcpyDeviceToHost);
+    cudaMemcpy(c.data(), y3.p, inter * 4, cudaMemcpyDeviceToHost);
+    EXPECT(std::memcmp(a.data(), b.data(), inter * 4) == 0 && std::memcmp(a.data(), c.data(), inter * 4) == 0);
+    EXPECT(same(b1, p1));
+  }
+  // two, three and four projections of one activation equal the single calls
+  {
+    const std::size_t kv = 1024;
+    DeviceBuffer<std::uint8_t> k_w(random_bytes(kv * hidden, 0x10, 0x60)), v_w(random_bytes(kv * hidden, 0x10, 0x60));
+    rt::Fp8LinearWeight kw = f8, vw = f8;
+    kw.weight = k_w.p; kw.output_size = kv;
+    vw.weight = v_w.p; vw.output_size = kv;
+    const rt::LinearWeight k_lw = kw, v_lw = vw;
+    Bf16 xs3(random_bf16(3 * hidden, 1.0f)), k1(3 * kv), v1(3 * kv), k2(3 * kv), v2(3 * kv);
+    EXPECT(rt::launch_projection_pair_tile_to_bf16_cuda(rt::ProjectionBackend::kSm87WeightOnly, k_lw, v_lw, xs3.p, 3, nullptr, 0,
+                                                        k1.p, v1.p, s) == 0);
+    EXPECT(q3x_b200_fp8_gemm_bf16(k_w.p, 0.02f, xs3.p, 3, kv, hidden, k2.p, nullptr, 0, s) == 0);
+    EXPECT(q3x_b200_fp8_gemm_bf16(v_w.p, 0.02f, xs3.p, 3, kv, hidden, v2.p, nullptr, 0, s) == 0);
+    EXPECT(same(k1, k2) && same(v1, v2) && written(k1) && written(v1));
+    Bf16 q1(inter), q2(inter), k3(kv), v3(kv), k4(kv), v4(kv);
+    EXPECT(rt::launch_full_attention_q_kv_to_bf16_cuda(rt::ProjectionBackend::kSm87WeightOnly, f8_lw, k_lw, v_lw, left.p, nullptr,
+                                                       0, q1.p, k3.p, v3.p, s) == 0);
+    EXPECT(q3x_b200_fp8_gemv(fp8_w.p, 0.02f, left.p, inter, hidden, nullptr, q2.p, s) == 0);
+    EXPECT(q3x_b200_fp8_gemv(k_w.p, 0.02f, left.p, kv, hidden, nullptr, k4.p, s) == 0);
+    EXPECT(q3x_b200_fp8_gemv(v_w.p, 0.02f, left.p, kv, hidden, nullptr, v4.p, s) == 0);
+    EXPECT(same(q1, q2) && same(k3, k4) && same(v3, v4) && written(q1));
+    // the linear-attention group at its exact shapes
+    const std::size_t qkv = 10240, zr = 6144, ab = 48;
+    DeviceBuffer<std::uint8_t> qkv_w(random_bytes(qkv * hidden, 0x10, 0x60)), z_w(random_bytes(zr * hidden, 0x10, 0x60));
+    Bf16 a_w(random_bf16(ab * hidden, 0.03f)), b_w(random_bf16(ab * hidden, 0.03f));
+    rt::Fp8LinearWeight qkvw = f8, zw = f8;
+    qkvw.weight = qkv_w.p; qkvw.output_size = qkv;
+    zw.weight = z_w.p; zw.output_size = zr;
+    rt::Bf16LinearWeight aw{}, bw{};
+    aw.weight = a_w.p; aw.output_size = ab; aw.input_size = hidden;
+    bw = aw; bw.weight = b_w.p;
+    Bf16 o_qkv(qkv), o_z(zr), o_a(ab), o_b(ab), e_qkv(qkv), e_z(zr), e_a(ab), e_b(ab);
+    EXPECT(rt::launch_linear_attention_qkv_z_ab_to_bf16_cuda(rt::ProjectionBackend::kSm87WeightOnly, rt::LinearWeight{qkvw},
+                                                             rt::LinearWeight{zw}, rt::LinearWeight{aw}, rt::LinearWeight{bw},
+                                                             left.p, o_qkv.p, o_z.p, o_a.p, o_b.p, s) == 0);
+    EXPECT(q3x_b200_fp8_gemv(qkv_w.p, 0.02f, left.p, qkv, hidden, nullptr, e_qkv.p, s) == 0);
+    EXPECT(q3x_b200_fp8_gemv(z_w.p, 0.02f, left.p, zr, hidden, nullptr, e_z.p, s) == 0);
+    EXPECT(q3x_b200_bf16_gemv(a_w.p, left.p, ab, hidden, nullptr, e_a.p, s) == 0);
+    EXPECT(q3x_b200_bf16_gemv(b_w.p, left.p, ab, hidden, nullptr, e_b.p, s) == 0);
+    EXPECT(same(o_qkv, e_qkv) && same(o_z, e_z) && same(o_a, e_a) && same(o_b, e_b) && written(o_qkv) && written(o_a));
+    EXPECT(rt::launch_linear_attention_qkv_z_ab_to_bf16_cuda(rt::ProjectionBackend::kSm87WeightOnly, rt::LinearWeight{zw},
+                                                             rt::LinearWeight{qkvw}, rt::LinearWeight{aw}, rt::LinearWeight{bw},
+                                                             left.p, o_qkv.p, o_z.p, o_a.p, o_b.p, s) == 801);
+  }
   // rejections, all before any enqueue
   constexpr int kInvalid = 1;
   EXPECT(rt::launch_projection_to_bf16_cuda(static_cast<rt::ProjectionBackend>(9), f8_lw, left.p, nullptr, 0, p1.p, s) == kInvalid);

@@ -81,6 +81,68 @@ static void test_dispatch() {
                                                          5120, p + 0x300000, nullptr) == 1);
   EXPECT(rt::launch_mlp_down_residual_norm_epilogue_cuda(B::kB200LayerOps, p, p + 0x100000, p + 0x200000, 1e-6F, 1,
                                                          5120, p + 0x300000, p) == 1);  // normalized == raw down
+  // eligibility predicates of the fused projection routes: backend, weight type, the model's exact shapes, payload
+  auto* b8 = reinterpret_cast<std::uint8_t*>(0x4000000);
+  auto* sc = reinterpret_cast<float*>(0x9000000);
+  auto fp8 = [&](std::size_t rows) {
+    rt::Fp8LinearWeight w{};
+    w.weight = b8; w.weight_scale_device = sc; w.input_scale_device = sc;
+    w.weight_scale = 0.02F; w.input_scale = 1.0F; w.output_size = rows; w.input_size = 5120;
+    return rt::LinearWeight{w};
+  };
+  auto bf = [&](std::size_t rows) {
+    rt::Bf16LinearWeight w{};
+    w.weight = p; w.output_size = rows; w.input_size = 5120;
+    return rt::LinearWeight{w};
+  };
+  auto fp4 = [&](std::size_t rows, std::size_t cols) {
+    rt::NvFp4LinearWeight w{};
+    w.packed_weight = b8; w.block_scale = b8 + 0x8000000; w.weight_scale_2_device = sc; w.input_scale_device = sc;
+    w.weight_scale_2 = 0.01F; w.input_scale = 1.0F; w.output_size = rows; w.input_size = cols;
+    return rt::LinearWeight{w};
+  };
+  EXPECT(rt::linear_weight_kind(fp8(1024)) == rt::LinearWeightKind::kFp8 && rt::linear_output_size(fp8(1024)) == 1024 &&
+         rt::linear_input_size(bf(48)) == 5120 && rt::linear_weight_kind(bf(48)) == rt::LinearWeightKind::kBf16 &&
+         rt::linear_weight_kind(fp4(17408, 5120)) == rt::LinearWeightKind::kNvFp4);
+  EXPECT(rt::supports_bf16_projection_pair(B::kSm87WeightOnly, bf(48), bf(48)));
+  EXPECT(!rt::supports_bf16_projection_pair(B::kReference, bf(48), bf(48)));       // not the selected fast backend
+  EXPECT(!rt::supports_bf16_projection_pair(B::kSm87WeightOnly, bf(48), bf(64)));  // wrong rows
+  EXPECT(!rt::supports_bf16_projection_pair(B::kSm87WeightOnly, bf(48), fp8(48))); // wrong type
+  EXPECT(rt::supports_fp8_projection_pair(B::kSm87WeightOnly, fp8(1024), fp8(1024)) &&
+         !rt::supports_fp8_projection_pair(B::kSm87WeightOnly, fp8(1024), fp8(2048)));
+  EXPECT(rt::supports_fp8_qkv_z_projection_pair(B::kB200LayerOps, fp8(10240), fp8(6144)) &&
+         !rt::supports_fp8_qkv_z_projection_pair(B::kSm87WeightOnly, fp8(6144), fp8(10240)));
+  EXPECT(rt::supports_linear_attention_qkv_z_ab_projection_fusion(B::kSm87WeightOnly, fp8(10240), fp8(6144), bf(48), bf(48)) &&
+         !rt::supports_linear_attention_qkv_z_ab_projection_fusion(B::kSm87WeightOnly, fp8(10240), fp8(6144), bf(48), bf(32)));
+  EXPECT(rt::supports_fp8_q_kv_projection_fusion(B::kSm87WeightOnly, fp8(12288), fp8(1024), fp8(1024)) &&
+         !rt::supports_fp8_q_kv_projection_fusion(B::kSm87WeightOnly, fp8(6144), fp8(1024), fp8(1024)));
+  EXPECT(rt::supports_nvfp4_gate_up_silu_fusion(B::kSm87WeightOnly, fp4(17408, 5120), fp4(17408, 5120)) &&
+         !rt::supports_nvfp4_gate_up_silu_fusion(B::kSm87WeightOnly, fp4(17408, 5120), fp8(17408)));
+  EXPECT(rt::supports_nvfp4_down_residual_norm_fusion(B::kSm87WeightOnly, fp4(5120, 17408)) &&
+         !rt::supports_nvfp4_down_residual_norm_fusion(B::kSm87WeightOnly, fp4(17408, 5120)));
+  {
+    rt::Fp8LinearWeight hollow = std::get<rt::Fp8LinearWeight>(fp8(1024));
+    hollow.weight_scale_device = nullptr;  // incomplete payload
+    EXPECT(!rt::supports_fp8_projection_pair(B::kSm87WeightOnly, rt::LinearWeight{hollow}, fp8(1024)));
+  }
+  // the fused four-projection call is "not supported" off its exact group, before anything else is looked at
+  EXPECT(rt::launch_linear_attention_qkv_z_ab_to_bf16_cuda(B::kSm87WeightOnly, fp8(10240), fp8(6144), bf(48), bf(32), p, p, p,
+                                                           p, p) == 801);
+  EXPECT(rt::launch_linear_attention_qkv_z_ab_to_bf16_cuda(B::kReference, fp8(10240), fp8(6144), bf(48), bf(48), p, p, p, p,
+                                                           p) == 801);
+  // the eligible group still validates its buffers: every output here aliases the input
+  EXPECT(rt::launch_linear_attention_qkv_z_ab_to_bf16_cuda(B::kSm87WeightOnly, fp8(10240), fp8(6144), bf(48), bf(48), p, p, p,
+                                                           p, p) == 1);
+  auto* f = reinterpret_cast<float*>(0x20000000);
+  EXPECT(rt::launch_projection_reference_cuda(fp8(1024), nullptr, f) == 1);
+  EXPECT(rt::launch_projection_to_bf16_reference_cuda(fp8(1024), p, f, 1023, p + 0x800000) == 1);  // scratch too small
+  EXPECT(rt::launch_projection_to_bf16_reference_cuda(fp8(1024), p, nullptr, 1024, p + 0x800000) == 1);
+  EXPECT(rt::launch_projection_pair_tile_to_bf16_cuda(B::kSm87WeightOnly, fp8(1024), fp8(1024), p, 65, nullptr, 0,
+                                                      p + 0x800000, p + 0xa00000) == 1);  // above the tile limit
+  EXPECT(rt::launch_projection_pair_tile_to_bf16_cuda(B::kSm87WeightOnly, fp8(1024), fp8(1024), p, 4, nullptr, 0,
+                                                      p + 0x800000, p + 0x800000) == 1);  // the outputs alias
+  EXPECT(rt::launch_full_attention_q_kv_to_bf16_cuda(B::kSm87WeightOnly, fp8(12288), fp8(1024), fp8(1024), p, nullptr, 0,
+                                                     p + 0x800000, p + 0xa00000, p + 0xa00100) == 1);  // k and v overlap
 }
 
 static void test_bindings() {

@@ -70,6 +70,22 @@ int main() {
       // the projection composites, declared by the reference's model_weights.h with its own LinearWeight
       reinterpret_cast<const void*>(&rt::launch_projection_to_bf16_cuda),
       reinterpret_cast<const void*>(&rt::launch_projection_tile_to_bf16_cuda),
+      reinterpret_cast<const void*>(&rt::launch_projection_reference_cuda),
+      reinterpret_cast<const void*>(&rt::launch_projection_to_bf16_reference_cuda),
+      reinterpret_cast<const void*>(&rt::launch_projection_pair_tile_to_bf16_cuda),
+      reinterpret_cast<const void*>(&rt::launch_linear_attention_qkv_z_ab_to_bf16_cuda),
+      reinterpret_cast<const void*>(&rt::launch_full_attention_q_kv_to_bf16_cuda),
+      reinterpret_cast<const void*>(&rt::supports_bf16_projection_pair),
+      reinterpret_cast<const void*>(&rt::supports_fp8_projection_pair),
+      reinterpret_cast<const void*>(&rt::supports_fp8_qkv_z_projection_pair),
+      reinterpret_cast<const void*>(&rt::supports_linear_attention_qkv_z_ab_projection_fusion),
+      reinterpret_cast<const void*>(&rt::supports_fp8_q_kv_projection_fusion),
+      reinterpret_cast<const void*>(&rt::supports_nvfp4_gate_up_silu_fusion),
+      reinterpret_cast<const void*>(&rt::supports_nvfp4_down_residual_norm_fusion),
+      reinterpret_cast<const void*>(&rt::linear_weight_kind),
+      reinterpret_cast<const void*>(&rt::linear_output_size),
+      reinterpret_cast<const void*>(&rt::linear_input_size),
+      reinterpret_cast<const void*>(&rt::is_valid_projection_backend),
       reinterpret_cast<const void*>(&rt::launch_exact_fp8_whole_chunk_projection_to_bf16_cuda),
       reinterpret_cast<const void*>(&rt::launch_mlp_gate_up_silu_to_bf16_cuda),
       reinterpret_cast<const void*>(&rt::launch_post_attention_residual_norm_mlp_gate_up_silu_to_bf16_cuda),
