@@ -422,6 +422,22 @@ int q3x_b200_gated_delta_net_update_rms_norm_silu_gate(
     const uint16_t* dt_bias, const uint16_t* state_in, uint16_t* state_out, float l2_eps,
     const uint16_t* norm_weight, const uint16_t* silu_gate, float norm_eps, uint16_t* out, void* stream);
 
+/* gdn_prefill_chunk64_native_detail::launch without its norm epilogue
+ * (src/kernels/sm87/gdn_prefill_chunk64_native_sm87.h:98-109), for any token count: the same recurrence over a
+ * prefill span in chunks of 64 tokens (the WY form).  Everything that does not depend on the running state -- q / k
+ * normalisation, the chunk's Gram matrices, the triangular solves -- runs for all chunks at once; three small
+ * tensor-core products per chunk remain sequential.  Operands and result as q3x_b200_gated_delta_net_update.
+ * Products take bf16 operands with FP32 accumulation and the state stays FP32 between the chunks of a call
+ * (rounded to bf16 once, in state_out), so against the token-by-token entry, which rounds the state after every
+ * token, the result agrees to the level of that rounding and is not bit-identical.  workspace: caller-owned, at
+ * least q3x_b200_gated_delta_net_chunked_workspace_bytes(tokens) bytes (about 2.4 MB per 64 tokens), 16-byte
+ * aligned, disjoint from every operand; stale contents do not matter. */
+size_t q3x_b200_gated_delta_net_chunked_workspace_bytes(size_t tokens);
+int q3x_b200_gated_delta_net_update_chunked(const uint16_t* conv_qkv, size_t tokens, const uint16_t* a,
+                                            const uint16_t* b, const uint16_t* A_log, const uint16_t* dt_bias,
+                                            const uint16_t* state_in, uint16_t* state_out, float l2_eps,
+                                            uint16_t* out, void* workspace, size_t workspace_bytes, void* stream);
+
 /* launch_gqa_attention_splitkv_sigmoid_gate_24_4_256_cuda and
  * gqa_attention_splitkv_sigmoid_gate_24_4_256_workspace_elements (include/q3x/runtime/decode_ops.h:397-423),
  * for any sequence_length >= 1: one query token [24, 256] against key / value caches [sequence_length, 4, 256],

@@ -16,7 +16,7 @@ HOST_LIB = os.path.join(PKG, "libq3x_b200_host.so")
 
 OBJ = os.path.join(PKG, "_build")
 CUDA_SOURCES = ["pointwise.cu", "row_norms.cu", "attention_preprocess.cu", "gdn_conv.cu", "embedding.cu", "nvfp4.cu",
-                "fused_nvfp4.cu", "gdn_recurrence.cu", "gqa_decode.cu", "gqa_prefill.cu", "logits_ops.cu", "gemv.cu", "nvfp4_gemm.cu", "fp8_gemm.cu", "nvfp4_w4a16_gemm.cu", "bf16_gemm.cu"]
+                "fused_nvfp4.cu", "gdn_recurrence.cu", "gdn_chunked.cu", "gqa_decode.cu", "gqa_prefill.cu", "logits_ops.cu", "gemv.cu", "nvfp4_gemm.cu", "fp8_gemm.cu", "nvfp4_w4a16_gemm.cu", "bf16_gemm.cu"]
 # sources instantiated from the CUTLASS / CuTe header tree (found inside an installed Python package, see _cutlass)
 CUTLASS_SOURCES = {"nvfp4_gemm.cu", "fp8_gemm.cu", "nvfp4_w4a16_gemm.cu", "bf16_gemm.cu"}
 NVCC_FLAGS = [

@@ -1,0 +1,561 @@
+// Gated-delta-net recurrence over a prefill span in CHUNKS of 64 tokens (the WY form the reference's production
+// prefill uses: gdn_prefill_chunk64_native_detail::launch, src/kernels/sm87/gdn_prefill_chunk64_native_sm87.h:98-109;
+// token-sequential definition: gated_delta_net_update_reference_cpu, src/runtime/reference/gdn_decode.cpp:186-293).
+//
+// Per value head, with M the [dk, dv] state, G_t = exp(sum_{s<=t} g_s) inside a chunk and M_0 the state at its start,
+// the token recurrence   M_t = alpha_t M_{t-1} + k_t d_t^T,   d_t = beta_t (v_t - (alpha_t M_{t-1})^T k_t),
+// o_t = M_t^T q_t   has the closed form
+//     A[t][j] = beta_t (G_t / G_j) (k_t . k_j)   (j < t)          (I + A) W = beta G K     (I + A) U = beta V
+//     D = U - W M_0                                                (the 64 deltas of the chunk)
+//     O = diag(G) Q M_0 + P D,   P[t][j] = (q_t . k_j) G_t / G_j   (j <= t)
+//     M_64 = G_64 M_0 + (diag(G_64 / G) K)^T D
+// so everything that does not involve M_0 is computed for all chunks in parallel (first kernel: q / k normalisation,
+// the two 64 x 64 Gram matrices on the tensor cores, the triangular solves in FP32 registers, one thread per column
+// of W or U), and only three small products per chunk stay on the sequential path (second kernel: the state of a
+// head, split over two CTAs by value rows, lives in the accumulators of four warps; its operands stream through a
+// two-stage shared-memory pipeline).  Operands of the tensor-core products are bf16 with FP32 accumulation, the
+// reference's own boundaries for this form; the state between chunks stays FP32 and is rounded once, on the way out.
+// Against the token-sequential form, which rounds the state to bf16 after every token, results agree to the noise of
+// that rounding, not bit for bit (the reference reports the same comparison as a characterisation, tests/
+// reference_gdn_prefill_chunk64_reference_engine_e2e_test.cpp:1990-2080).
+#include "device_utils.cuh"
+#include "host_checks.hpp"
+#include "q3x_b200.h"
+
+namespace q3x {
+namespace {
+
+constexpr int kHead = Q3X_B200_GDN_HEAD_DIM;                 // 128
+constexpr int kValueHeads = Q3X_B200_GDN_V_HEADS;            // 48
+constexpr int kKeyHeads = Q3X_B200_GDN_QK_HEADS;             // 16
+constexpr int kChannels = Q3X_B200_GDN_CHANNELS;             // 10240
+constexpr int kKOffset = kKeyHeads * kHead;                  // 2048
+constexpr int kVOffset = 2 * kKOffset;                       // 4096
+constexpr int kChunk = 64;
+
+// ---- workspace: per chunk, images that the second kernel copies into shared memory as they are -------------------
+// (16-byte pieces of a row are permuted by the row's low three bits, so that ldmatrix reads them without conflicts)
+constexpr size_t kQkTile = static_cast<size_t>(kChunk) * kHead * 2;   // [64 tokens][128] bf16, 256-byte rows
+constexpr size_t kWTile = static_cast<size_t>(kHead) * kChunk * 2;    // [128 columns][64 tokens] bf16, 128-byte rows
+constexpr size_t kPTile = static_cast<size_t>(kChunk) * kChunk * 2;   // [64][64] bf16, 128-byte rows
+constexpr size_t kDecayTile = 3 * kChunk * sizeof(float);             // G_t, G_64 / G_t, and one spare row
+constexpr size_t kChunkBytes = 2 * kKeyHeads * kQkTile + kValueHeads * (2 * kWTile + kPTile + kDecayTile);
+
+struct Workspace {
+  unsigned char* base;
+  size_t chunks;
+  __host__ __device__ unsigned char* q(size_t c, int kh) const { return base + (c * kKeyHeads + kh) * kQkTile; }
+  __host__ __device__ unsigned char* k(size_t c, int kh) const {
+    return base + chunks * kKeyHeads * kQkTile + (c * kKeyHeads + kh) * kQkTile;
+  }
+  __host__ __device__ unsigned char* w(size_t c, int h) const {
+    return base + 2 * chunks * kKeyHeads * kQkTile + (c * kValueHeads + h) * kWTile;
+  }
+  __host__ __device__ unsigned char* u(size_t c, int h) const {
+    return base + 2 * chunks * kKeyHeads * kQkTile + chunks * kValueHeads * kWTile + (c * kValueHeads + h) * kWTile;
+  }
+  __host__ __device__ unsigned char* p(size_t c, int h) const {
+    return base + 2 * chunks * kKeyHeads * kQkTile + 2 * chunks * kValueHeads * kWTile + (c * kValueHeads + h) * kPTile;
+  }
+  __host__ __device__ unsigned char* decay(size_t c, int h) const {
+    return base + 2 * chunks * kKeyHeads * kQkTile + chunks * kValueHeads * (2 * kWTile + kPTile) +
+           (c * kValueHeads + h) * kDecayTile;
+  }
+};
+
+// byte offset of 16-byte piece `piece` of row `row` in an image with `pitch`-byte rows
+__device__ __forceinline__ uint32_t image(int row, int piece, int pitch) {
+  return static_cast<uint32_t>(row * pitch + ((piece ^ (row & 7)) << 4));
+}
+
+__device__ __forceinline__ void cp_async_16(uint32_t smem, const void* global) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem), "l"(global) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// the gate expressions of the token-sequential kernel (src/runtime/reference/gdn_decode.cpp:62-73)
+__device__ __forceinline__ float softplus_ref(float v) { return v > 20.0f ? v : log1pf(expf(v)); }
+__device__ __forceinline__ float sigmoid_ref(float v) {
+  if (v >= 0.0f) return __fdiv_rn(1.0f, 1.0f + expf(-v));
+  const float e = expf(v);
+  return __fdiv_rn(e, 1.0f + e);
+}
+__device__ __forceinline__ float dot8(const float (&a)[8], const float (&b)[8]) {
+  float s = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) s = fmaf(a[i], b[i], s);
+  return s;
+}
+
+// ================================================================================================================
+// First kernel: one CTA per (chunk, key head); the three value heads of the key head share its q, k and Gram work.
+// ================================================================================================================
+constexpr int kPrepThreads = 256;
+constexpr int kGramPitch = kChunk + 1;  // FP32 Gram rows, read down a column by consecutive threads
+struct PrepShared {
+  __align__(16) unsigned char k[kQkTile];        // normalised k, bf16, the workspace image
+  __align__(16) unsigned char q[kQkTile];        // normalised and scaled q
+  __align__(16) uint16_t v[kChunk][kHead];       // the value head's rows as they come
+  __align__(16) float lower_t[kChunk][kChunk];   // A transposed: [j][t], zero for t <= j
+  float kk[kChunk][kGramPitch];                  // k_t . k_j
+  float qk[kChunk][kGramPitch];                  // q_t . k_j
+  float cumulative[kChunk], growth[kChunk], beta[kChunk];  // log G_t, G_t, beta_t
+};
+
+__global__ void __launch_bounds__(kPrepThreads, 2) gdn_chunk_prepare_kernel(
+    const uint16_t* __restrict__ conv_qkv, size_t tokens, const uint16_t* __restrict__ a,
+    const uint16_t* __restrict__ b, const uint16_t* __restrict__ A_log, const uint16_t* __restrict__ dt_bias,
+    float l2_eps, Workspace ws) {
+  extern __shared__ __align__(128) unsigned char raw[];
+  PrepShared& sh = *reinterpret_cast<PrepShared*>(raw);
+  const size_t chunk = blockIdx.x;
+  const int key_head = blockIdx.y;
+  const size_t token0 = chunk * kChunk;
+  const int live = static_cast<int>(min(static_cast<size_t>(kChunk), tokens - token0));
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t k_smem = static_cast<uint32_t>(__cvta_generic_to_shared(sh.k));
+  const uint32_t q_smem = static_cast<uint32_t>(__cvta_generic_to_shared(sh.q));
+
+  // ---- q and k: 1 / sqrt(sum + eps) (and 1 / sqrt(128) for q) in FP32, the same expressions as the sequential
+  // kernel; 16 lanes per row, one 16-byte piece per lane; rows past the span are zero
+  {
+    const int piece = tid & 15;
+    const float inv_sqrt_dim = __fdiv_rn(1.0f, sqrtf(static_cast<float>(kHead)));
+    unsigned char* q_image = ws.q(chunk, key_head);
+    unsigned char* k_image = ws.k(chunk, key_head);
+#pragma unroll
+    for (int pass = 0; pass < kChunk / 16; ++pass) {
+      const int row = pass * 16 + (tid >> 4);
+      const bool valid = row < live;
+      const uint16_t* source = conv_qkv + (token0 + (valid ? row : 0)) * kChannels + key_head * kHead;
+      float qv[8], kv[8];
+      unpack8(valid ? ld_weight(reinterpret_cast<const uint4*>(source) + piece) : make_uint4(0, 0, 0, 0), qv);
+      unpack8(valid ? ld_weight(reinterpret_cast<const uint4*>(source + kKOffset) + piece) : make_uint4(0, 0, 0, 0), kv);
+      const float q_scale = __fdiv_rn(1.0f, sqrtf(group_sum<16>(dot8(qv, qv)) + l2_eps)) * inv_sqrt_dim;
+      const float k_scale = __fdiv_rn(1.0f, sqrtf(group_sum<16>(dot8(kv, kv)) + l2_eps));
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        qv[i] *= q_scale;
+        kv[i] *= k_scale;
+      }
+      const uint4 qp = pack8(qv), kp = pack8(kv);
+      const uint32_t at = image(row, piece, kHead * 2);
+      *reinterpret_cast<uint4*>(sh.q + at) = qp;
+      *reinterpret_cast<uint4*>(sh.k + at) = kp;
+      st_vec(q_image + at, qp);
+      st_vec(k_image + at, kp);
+    }
+  }
+  __syncthreads();
+
+  // ---- the two Gram matrices: warp (row block of 16, column half of 32), eight steps over the 128 dimensions
+  {
+    const int row_block = warp & 3, column_half = warp >> 2, g = lane >> 2, t = lane & 3;
+    float kk[4][4], qk[4][4];
+#pragma unroll
+    for (int n = 0; n < 4; ++n)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) kk[n][e] = qk[n][e] = 0.0f;
+#pragma unroll
+    for (int step = 0; step < kHead / 16; ++step) {
+      uint32_t ak[4], aq[4];
+      const uint32_t a_at = image(row_block * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, step * 2 + (lane >> 4), kHead * 2);
+      ldmatrix_x4(ak, k_smem + a_at);
+      ldmatrix_x4(aq, q_smem + a_at);
+#pragma unroll
+      for (int n2 = 0; n2 < 2; ++n2) {
+        uint32_t bk[4];
+        ldmatrix_x4(bk, k_smem + image(column_half * 32 + n2 * 16 + (lane & 7) + (lane >> 4) * 8,
+                                       step * 2 + ((lane >> 3) & 1), kHead * 2));
+        mma_bf16(kk[2 * n2], ak, bk[0], bk[1]);
+        mma_bf16(kk[2 * n2 + 1], ak, bk[2], bk[3]);
+        mma_bf16(qk[2 * n2], aq, bk[0], bk[1]);
+        mma_bf16(qk[2 * n2 + 1], aq, bk[2], bk[3]);
+      }
+    }
+#pragma unroll
+    for (int n = 0; n < 4; ++n)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int row = row_block * 16 + g + (e >> 1) * 8, column = column_half * 32 + n * 8 + 2 * t + (e & 1);
+        sh.kk[row][column] = kk[n][e];
+        sh.qk[row][column] = qk[n][e];
+      }
+  }
+
+  for (int r = 0; r < kValueHeads / kKeyHeads; ++r) {
+    const int head = key_head * (kValueHeads / kKeyHeads) + r;
+    __syncthreads();  // the Gram matrices are complete; the previous head's readers are done
+    // ---- the head's value rows, and its gates: warp 0 takes two tokens per lane and scans the log-decays
+    for (int i = tid; i < kChunk * (kHead / 8); i += kPrepThreads) {
+      const int row = i / (kHead / 8), piece = i % (kHead / 8);
+      const bool valid = row < live;
+      const uint4 value = valid ? ld_weight(reinterpret_cast<const uint4*>(
+                                                conv_qkv + (token0 + row) * kChannels + kVOffset + head * kHead) + piece)
+                                : make_uint4(0, 0, 0, 0);
+      *reinterpret_cast<uint4*>(&sh.v[row][piece * 8]) = value;
+    }
+    if (warp == 0) {
+      const float a_decay = -expf(bf16_to_float(A_log[head]));
+      const float bias = bf16_to_float(dt_bias[head]);
+      float g2[2], beta2[2];
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int row = 2 * lane + e;
+        const bool valid = row < live;  // a row past the span neither decays nor updates the state
+        g2[e] = valid ? a_decay * softplus_ref(bf16_to_float(a[(token0 + row) * kValueHeads + head]) + bias) : 0.0f;
+        beta2[e] = valid ? sigmoid_ref(bf16_to_float(b[(token0 + row) * kValueHeads + head])) : 0.0f;
+      }
+      float inclusive = g2[0] + g2[1];
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const float up = __shfl_up_sync(0xffffffffu, inclusive, d);
+        if (lane >= d) inclusive += up;
+      }
+      const float last = __shfl_sync(0xffffffffu, inclusive, 31);  // log G_64
+      float* decay = reinterpret_cast<float*>(ws.decay(chunk, head));
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int row = 2 * lane + e;
+        const float c = e == 0 ? inclusive - g2[1] : inclusive;
+        sh.cumulative[row] = c;
+        sh.growth[row] = expf(c);
+        sh.beta[row] = beta2[e];
+        decay[row] = expf(c);                 // G_t
+        decay[kChunk + row] = expf(last - c);  // G_64 / G_t
+        decay[2 * kChunk + row] = 0.0f;
+      }
+    }
+    __syncthreads();
+    // ---- A transposed (FP32, shared) and P (bf16, workspace image); consecutive threads take consecutive t
+#pragma unroll 4
+    for (int i = tid; i < kChunk * kChunk; i += kPrepThreads) {
+      const int t = i % kChunk, j = i / kChunk;
+      sh.lower_t[j][t] = j < t ? sh.beta[t] * sh.kk[t][j] * expf(sh.cumulative[t] - sh.cumulative[j]) : 0.0f;
+    }
+    {
+      unsigned char* p_image = ws.p(chunk, head);
+      for (int i = tid; i < kChunk * (kChunk / 8); i += kPrepThreads) {
+        const int t = i / (kChunk / 8), piece = i % (kChunk / 8);
+        float p[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const int j = piece * 8 + e;
+          p[e] = j <= t ? sh.qk[t][j] * expf(sh.cumulative[t] - sh.cumulative[j]) : 0.0f;
+        }
+        st_vec(p_image + image(t, piece, kChunk * 2), pack8(p));
+      }
+    }
+    __syncthreads();
+    // ---- (I + A) X = [beta G K | beta V]: thread c owns column c of X (c < 128: W, else U) in 64 registers and
+    // eliminates row by row; the coefficients are shared-memory broadcasts, four rows per load
+    {
+      float x[kChunk];
+      if (tid < kHead) {
+        const int piece = tid >> 3, within = tid & 7;
+#pragma unroll
+        for (int t = 0; t < kChunk; ++t)
+          x[t] = sh.beta[t] * sh.growth[t] *
+                 bf16_to_float(*reinterpret_cast<const uint16_t*>(sh.k + image(t, piece, kHead * 2) + within * 2));
+      } else {
+#pragma unroll
+        for (int t = 0; t < kChunk; ++t) x[t] = sh.beta[t] * bf16_to_float(sh.v[t][tid - kHead]);
+      }
+#pragma unroll
+      for (int j = 0; j < kChunk - 1; ++j) {
+        const float solved = x[j];
+#pragma unroll
+        for (int t4 = (j + 1) / 4; t4 < kChunk / 4; ++t4) {
+          // rows t <= j of this group carry a zero coefficient
+          const float4 c = *reinterpret_cast<const float4*>(&sh.lower_t[j][t4 * 4]);
+          x[t4 * 4 + 0] = fmaf(-c.x, solved, x[t4 * 4 + 0]);
+          x[t4 * 4 + 1] = fmaf(-c.y, solved, x[t4 * 4 + 1]);
+          x[t4 * 4 + 2] = fmaf(-c.z, solved, x[t4 * 4 + 2]);
+          x[t4 * 4 + 3] = fmaf(-c.w, solved, x[t4 * 4 + 3]);
+        }
+      }
+      // column c of W (or U) is row c of the transposed image: 128 contiguous bytes, pieces permuted by the row
+      const int row = tid < kHead ? tid : tid - kHead;
+      unsigned char* target = tid < kHead ? ws.w(chunk, head) : ws.u(chunk, head);
+#pragma unroll
+      for (int piece = 0; piece < kChunk / 8; ++piece) {
+        float eight[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) eight[e] = x[piece * 8 + e];
+        st_vec(target + image(row, piece, kChunk * 2), pack8(eight));
+      }
+    }
+  }
+}
+
+// ================================================================================================================
+// Second kernel: the sequential path.  One CTA per (value head, half of its 128 value rows); a warp owns 16 value
+// rows of the state, transposed ([value row][key dimension], the layout the state has in memory), as the FP32
+// accumulators of its MMAs.  An accumulator tile read as (row, column pair) is exactly the A operand of the next
+// product, so the state, the deltas and the outputs never leave registers between the products of a chunk:
+//     D^T  = U^T - S^T W^T              (A = S^T as bf16, B = W^T)
+//     O^T  = (S^T Q^T) diag(G) + D^T P^T
+//     S^T <- G_64 S^T + (D^T diag(G_64 / G)) K
+// ================================================================================================================
+constexpr int kStateThreads = 128;
+constexpr int kRowsPerCta = 64;  // value rows per CTA: 16 per warp
+constexpr int kStateSplits = kHead / kRowsPerCta;
+constexpr size_t kUSlice = static_cast<size_t>(kRowsPerCta) * kChunk * 2;
+constexpr size_t kStageW = 0, kStageQ = kStageW + kWTile, kStageK = kStageQ + kQkTile, kStageP = kStageK + kQkTile,
+                 kStageU = kStageP + kPTile, kStageDecay = kStageU + kUSlice, kStageBytes = kStageDecay + kDecayTile;
+constexpr size_t kOutStage = 2 * kStageBytes;                                // [64 tokens][64 value rows] bf16
+constexpr size_t kStateShared = kOutStage + static_cast<size_t>(kChunk) * kRowsPerCta * 2;
+static_assert(kStageBytes % 16 == 0, "stages are copied in 16-byte pieces");
+
+__device__ __forceinline__ void copy_linear(uint32_t smem, const unsigned char* global, size_t bytes) {
+  for (size_t at = static_cast<size_t>(threadIdx.x) * 16; at < bytes; at += static_cast<size_t>(kStateThreads) * 16)
+    cp_async_16(smem + static_cast<uint32_t>(at), global + at);
+}
+
+__device__ __forceinline__ void request_chunk(const Workspace& ws, size_t chunk, int head, int split, uint32_t stage) {
+  copy_linear(stage + kStageW, ws.w(chunk, head), kWTile);
+  copy_linear(stage + kStageQ, ws.q(chunk, head / (kValueHeads / kKeyHeads)), kQkTile);
+  copy_linear(stage + kStageK, ws.k(chunk, head / (kValueHeads / kKeyHeads)), kQkTile);
+  copy_linear(stage + kStageP, ws.p(chunk, head), kPTile);
+  copy_linear(stage + kStageU, ws.u(chunk, head) + split * kUSlice, kUSlice);
+  copy_linear(stage + kStageDecay, ws.decay(chunk, head), kDecayTile);
+}
+
+__global__ void __launch_bounds__(kStateThreads, 1) gdn_chunk_state_kernel(Workspace ws, size_t tokens,
+                                                                           const uint16_t* state_in, uint16_t* state_out,
+                                                                           uint16_t* __restrict__ out) {
+  extern __shared__ __align__(128) unsigned char shared[];
+  const uint32_t smem = static_cast<uint32_t>(__cvta_generic_to_shared(shared));
+  const int head = blockIdx.x, split = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int row_local = warp * 16 + g;                  // and row_local + 8
+  const int row_global = split * kRowsPerCta + row_local;
+
+  request_chunk(ws, 0, head, split, smem);
+  cp_async_commit();
+
+  // S[n][e]: rows row_global (e < 2) / row_global + 8, key dimensions n * 8 + 2t + (e & 1)
+  float S[kHead / 8][4];
+  {
+    const uint16_t* base = state_in + (static_cast<size_t>(head) * kHead + row_global) * kHead;
+#pragma unroll
+    for (int n = 0; n < kHead / 8; ++n) {
+      const uint32_t upper = *reinterpret_cast<const uint32_t*>(base + n * 8 + 2 * t);
+      const uint32_t lower = *reinterpret_cast<const uint32_t*>(base + 8 * kHead + n * 8 + 2 * t);
+      S[n][0] = bf16_lo(upper);
+      S[n][1] = bf16_hi(upper);
+      S[n][2] = bf16_lo(lower);
+      S[n][3] = bf16_hi(lower);
+    }
+  }
+
+  for (size_t chunk = 0; chunk < ws.chunks; ++chunk) {
+    const uint32_t stage = smem + static_cast<uint32_t>((chunk & 1) * kStageBytes);
+    cp_async_wait_all();
+    __syncthreads();  // this chunk's operands are in place; everybody is done with the other stage and the out tile
+    if (chunk + 1 < ws.chunks) request_chunk(ws, chunk + 1, head, split, smem + static_cast<uint32_t>(((chunk + 1) & 1) * kStageBytes));
+    cp_async_commit();
+
+    const float* growth = reinterpret_cast<const float*>(shared + (chunk & 1) * kStageBytes + kStageDecay);  // G_t
+    const float* to_end = growth + kChunk;                                                                   // G_64 / G_t
+
+    // ---- the state as a bf16 A operand: eight steps of 16 key dimensions
+    uint32_t sa[kHead / 16][4];
+#pragma unroll
+    for (int step = 0; step < kHead / 16; ++step) {
+      sa[step][0] = pack_bf16x2(S[2 * step][0], S[2 * step][1]);
+      sa[step][1] = pack_bf16x2(S[2 * step][2], S[2 * step][3]);
+      sa[step][2] = pack_bf16x2(S[2 * step + 1][0], S[2 * step + 1][1]);
+      sa[step][3] = pack_bf16x2(S[2 * step + 1][2], S[2 * step + 1][3]);
+    }
+    // ---- predicted part S^T W^T and the inter-chunk output S^T Q^T: 16 value rows x 64 tokens each
+    float pred[kChunk / 8][4], o[kChunk / 8][4];
+#pragma unroll
+    for (int n = 0; n < kChunk / 8; ++n)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) pred[n][e] = o[n][e] = 0.0f;
+#pragma unroll
+    for (int step = 0; step < kHead / 16; ++step) {
+#pragma unroll
+      for (int n2 = 0; n2 < kChunk / 16; ++n2) {
+        uint32_t bw[4], bq[4];
+        // W^T image: rows are key dimensions (the product's k), 16-byte pieces are 8 tokens (its n): transposed loads
+        ldmatrix_x4_trans(bw, stage + kStageW + image(step * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, n2 * 2 + (lane >> 4), kChunk * 2));
+        mma_bf16(pred[2 * n2], sa[step], bw[0], bw[1]);
+        mma_bf16(pred[2 * n2 + 1], sa[step], bw[2], bw[3]);
+        // Q image: rows are tokens (n), pieces are 8 key dimensions (k): plain loads
+        ldmatrix_x4(bq, stage + kStageQ + image(n2 * 16 + (lane & 7) + (lane >> 4) * 8, step * 2 + ((lane >> 3) & 1), kHead * 2));
+        mma_bf16(o[2 * n2], sa[step], bq[0], bq[1]);
+        mma_bf16(o[2 * n2 + 1], sa[step], bq[2], bq[3]);
+      }
+    }
+    // ---- D^T = U^T - pred (FP32), as two bf16 A operands over the tokens: plain, and scaled by G_64 / G_t
+    uint32_t da[kChunk / 16][4], ds[kChunk / 16][4];
+#pragma unroll
+    for (int n = 0; n < kChunk / 8; ++n) {
+      const uint32_t upper = *reinterpret_cast<const uint32_t*>(shared + (chunk & 1) * kStageBytes + kStageU +
+                                                                image(row_local, n, kChunk * 2) + 4 * t);
+      const uint32_t lower = *reinterpret_cast<const uint32_t*>(shared + (chunk & 1) * kStageBytes + kStageU +
+                                                                image(row_local + 8, n, kChunk * 2) + 4 * t);
+      const float d0 = bf16_lo(upper) - pred[n][0], d1 = bf16_hi(upper) - pred[n][1];
+      const float d2 = bf16_lo(lower) - pred[n][2], d3 = bf16_hi(lower) - pred[n][3];
+      const float2 grow = *reinterpret_cast<const float2*>(growth + n * 8 + 2 * t);
+      const float2 end = *reinterpret_cast<const float2*>(to_end + n * 8 + 2 * t);
+      // tokens n * 8 + 2t, + 1: k slots (n & 1) * 8 + 2t of step n / 2
+      da[n >> 1][(n & 1) * 2 + 0] = pack_bf16x2(d0, d1);
+      da[n >> 1][(n & 1) * 2 + 1] = pack_bf16x2(d2, d3);
+      ds[n >> 1][(n & 1) * 2 + 0] = pack_bf16x2(d0 * end.x, d1 * end.y);
+      ds[n >> 1][(n & 1) * 2 + 1] = pack_bf16x2(d2 * end.x, d3 * end.y);
+      // the inter-chunk output of token i carries G_i
+      o[n][0] *= grow.x;
+      o[n][1] *= grow.y;
+      o[n][2] *= grow.x;
+      o[n][3] *= grow.y;
+    }
+    // ---- O^T += D^T P^T  (P image: rows are output tokens (n), pieces are 8 source tokens (k): plain loads)
+#pragma unroll
+    for (int step = 0; step < kChunk / 16; ++step) {
+#pragma unroll
+      for (int n2 = 0; n2 < kChunk / 16; ++n2) {
+        uint32_t bp[4];
+        ldmatrix_x4(bp, stage + kStageP + image(n2 * 16 + (lane & 7) + (lane >> 4) * 8, step * 2 + ((lane >> 3) & 1), kChunk * 2));
+        mma_bf16(o[2 * n2], da[step], bp[0], bp[1]);
+        mma_bf16(o[2 * n2 + 1], da[step], bp[2], bp[3]);
+      }
+    }
+    // ---- S^T <- G_64 S^T + (D^T diag(G_64 / G)) K  (K image: rows are tokens (k), pieces 8 key dimensions (n))
+    {
+      const float whole = growth[kChunk - 1];
+#pragma unroll
+      for (int n = 0; n < kHead / 8; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) S[n][e] *= whole;
+    }
+#pragma unroll
+    for (int step = 0; step < kChunk / 16; ++step) {
+#pragma unroll
+      for (int n2 = 0; n2 < kHead / 16; ++n2) {
+        uint32_t bk[4];
+        ldmatrix_x4_trans(bk, stage + kStageK + image(step * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, n2 * 2 + (lane >> 4), kHead * 2));
+        mma_bf16(S[2 * n2], ds[step], bk[0], bk[1]);
+        mma_bf16(S[2 * n2 + 1], ds[step], bk[2], bk[3]);
+      }
+    }
+    // ---- the chunk's outputs: transposed through shared memory, then 128-byte rows to out[token][head][rows]
+    {
+      unsigned char* tile = shared + kOutStage;
+#pragma unroll
+      for (int n = 0; n < kChunk / 8; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int token = n * 8 + 2 * t + (e & 1), row = row_local + (e >> 1) * 8;
+          *reinterpret_cast<uint16_t*>(tile + image(token, row >> 3, kRowsPerCta * 2) + (row & 7) * 2) = float_to_bf16(o[n][e]);
+        }
+    }
+    __syncthreads();
+    {
+      const unsigned char* tile = shared + kOutStage;
+      const size_t token0 = chunk * kChunk;
+      for (int i = threadIdx.x; i < kChunk * (kRowsPerCta / 8); i += kStateThreads) {
+        const int token = i / (kRowsPerCta / 8), piece = i % (kRowsPerCta / 8);
+        if (token0 + token < tokens)
+          st_vec(out + ((token0 + token) * kValueHeads + head) * kHead + split * kRowsPerCta + piece * 8,
+                 *reinterpret_cast<const uint4*>(tile + image(token, piece, kRowsPerCta * 2)));
+      }
+    }
+  }
+  cp_async_wait_all();
+  // ---- the state leaves as bf16, rounded once
+  {
+    uint16_t* base = state_out + (static_cast<size_t>(head) * kHead + row_global) * kHead;
+#pragma unroll
+    for (int n = 0; n < kHead / 8; ++n) {
+      *reinterpret_cast<uint32_t*>(base + n * 8 + 2 * t) = pack_bf16x2(S[n][0], S[n][1]);
+      *reinterpret_cast<uint32_t*>(base + 8 * kHead + n * 8 + 2 * t) = pack_bf16x2(S[n][2], S[n][3]);
+    }
+  }
+}
+
+size_t chunks_of(size_t tokens) { return (tokens + kChunk - 1) / kChunk; }
+
+int launch_chunked(const uint16_t* conv_qkv, size_t tokens, const uint16_t* a, const uint16_t* b, const uint16_t* A_log,
+                   const uint16_t* dt_bias, const uint16_t* state_in, uint16_t* state_out, float l2_eps, uint16_t* out,
+                   void* workspace, size_t workspace_bytes, void* stream) {
+  using namespace host;
+  if (!valid_epsilon(l2_eps)) return kInvalid;
+  if (mul3_overflows(tokens, kChannels, sizeof(uint16_t)) || mul_overflows(chunks_of(tokens), kChunkBytes)) return kInvalid;
+  if (tokens == 0) return kOk;
+  if (conv_qkv == nullptr || a == nullptr || b == nullptr || A_log == nullptr || dt_bias == nullptr ||
+      state_in == nullptr || state_out == nullptr || out == nullptr || workspace == nullptr)
+    return kInvalid;
+  const size_t need = chunks_of(tokens) * kChunkBytes;
+  if (workspace_bytes < need) return kInvalid;
+  constexpr size_t kStateBytes = static_cast<size_t>(kValueHeads) * kHead * kHead * 2;
+  const size_t out_bytes = tokens * kValueHeads * kHead * 2;
+  const Span sc = span(conv_qkv, tokens * kChannels * 2), sa = span(a, tokens * kValueHeads * 2),
+             sb = span(b, tokens * kValueHeads * 2), sl = span(A_log, kValueHeads * 2),
+             sd = span(dt_bias, kValueHeads * 2), si = span(state_in, kStateBytes), so = span(state_out, kStateBytes),
+             sy = span(out, out_bytes), sw = span(workspace, need);
+  // state_in == state_out exactly is the one alias allowed, as in the token-sequential entry; the workspace and
+  // every written range are disjoint from everything else
+  if (partial_overlap(si, so)) return kInvalid;
+  const Span readers[] = {sc, sa, sb, sl, sd};
+  for (const Span& r : readers)
+    if (overlap(so, r) || overlap(sy, r) || overlap(sw, r) || wraps(r)) return kInvalid;
+  if (overlap(sy, so) || overlap(sy, si) || overlap(sw, so) || overlap(sw, si) || overlap(sw, sy) || wraps(sy) ||
+      wraps(so) || wraps(si) || wraps(sw))
+    return kInvalid;
+  if (!aligned16(conv_qkv) || !aligned16(state_in) || !aligned16(state_out) || !aligned16(out) || !aligned16(workspace))
+    return kNotSupported;
+  clear_stale_error();
+  static const int configured = [] {
+    cudaError_t e = cudaFuncSetAttribute(gdn_chunk_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(sizeof(PrepShared)));
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(gdn_chunk_state_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(kStateShared));
+    return static_cast<int>(e);
+  }();
+  if (configured != kOk) return configured;
+  cudaStream_t s = as_stream(stream);
+  const Workspace ws{static_cast<unsigned char*>(workspace), chunks_of(tokens)};
+  if (ws.chunks > 0x7fffffffu) return kInvalid;
+  gdn_chunk_prepare_kernel<<<dim3(static_cast<unsigned>(ws.chunks), kKeyHeads), kPrepThreads, sizeof(PrepShared), s>>>(
+      conv_qkv, tokens, a, b, A_log, dt_bias, l2_eps, ws);
+  gdn_chunk_state_kernel<<<dim3(kValueHeads, kStateSplits), kStateThreads, kStateShared, s>>>(ws, tokens, state_in,
+                                                                                             state_out, out);
+  return launch_status();
+}
+
+}  // namespace
+}  // namespace q3x
+
+extern "C" size_t q3x_b200_gated_delta_net_chunked_workspace_bytes(size_t tokens) {
+  const size_t chunks = q3x::chunks_of(tokens);
+  return q3x::host::mul_overflows(chunks, q3x::kChunkBytes) ? 0 : chunks * q3x::kChunkBytes;
+}
+
+extern "C" int q3x_b200_gated_delta_net_update_chunked(const uint16_t* conv_qkv, size_t tokens, const uint16_t* a,
+                                                       const uint16_t* b, const uint16_t* A_log, const uint16_t* dt_bias,
+                                                       const uint16_t* state_in, uint16_t* state_out, float l2_eps,
+                                                       uint16_t* out, void* workspace, size_t workspace_bytes,
+                                                       void* stream) {
+  return q3x::launch_chunked(conv_qkv, tokens, a, b, A_log, dt_bias, state_in, state_out, l2_eps, out, workspace,
+                             workspace_bytes, stream);
+}

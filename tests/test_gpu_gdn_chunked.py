@@ -1,0 +1,168 @@
+"""GPU tests of the chunked (64-token WY form) gated-delta-net recurrence, through the C ABI.
+
+The chunked form is not bit-comparable with the token-sequential one: the sequential definition
+(gated_delta_net_update_reference_cpu, src/runtime/reference/gdn_decode.cpp:186-293; the CPU oracle here) rounds the
+state to bf16 after EVERY token, the chunked form carries it in FP32 across a call and multiplies bf16 operands.  The
+reference compares its own chunked kernel with its sequential path by NRMSE / cosine / max-abs as a characterisation
+(tests/reference_gdn_prefill_chunk64_reference_engine_e2e_test.cpp:708-760, 1990-2080).  The tests below use the same
+three figures, and anchor them: both forms are compared with the recurrence evaluated in float64 with no rounding of
+the state at all, and the chunked result has to be at least about as close to that as the sequential oracle is.
+
+Bounds (written where they are used).  The sequential oracle itself sits 6e-3 to 1.4e-2 (NRMSE) away from the float64
+recurrence on these inputs -- that is the per-token rounding of its state -- so the distance between the two forms is
+bounded by the triangle through float64: NRMSE(chunked, oracle) <= NRMSE(chunked, f64) + 1.05 NRMSE(oracle, f64),
+cosine >= 0.9995; and the chunked form's own distance to float64 must be <= max(the oracle's, 4.5e-3): its floor is the
+rounding of six bf16 operands (k, q, W, U, the deltas, P), each 2^-9 / sqrt(3) rms, about 3e-3 together, which a span
+of one token shows in full and the oracle's per-token state rounding overtakes after a few dozen tokens.  States likewise.
+"""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as orc
+from tests import fixtures as fx
+
+pytestmark = pytest.mark.gpu
+EPS = 1e-6
+
+
+@pytest.fixture(scope="module")
+def g():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from tests import gpu_util
+
+    orc.build()
+    gpu_util.capi.load()
+    return gpu_util
+
+
+def case(rng, tokens, slow_decay):
+    conv = fx.normal_bf16(rng, (tokens, 10240))
+    a, b = fx.normal_bf16(rng, (tokens, 48), 2.0), fx.normal_bf16(rng, (tokens, 48), 2.0)
+    if slow_decay:  # long memory: the state integrates over hundreds of tokens
+        A_log = orc.bf16_encode(rng.uniform(-6.0, -3.0, 48).astype(np.float32))
+        dt_bias = orc.bf16_encode(rng.uniform(-3.0, 0.0, 48).astype(np.float32))
+    else:
+        A_log = orc.bf16_encode(rng.uniform(-4.0, 1.5, 48).astype(np.float32))
+        dt_bias = orc.bf16_encode(rng.uniform(-3.0, 3.0, 48).astype(np.float32))
+    state = fx.normal_bf16(rng, (48, 128, 128), 0.05)
+    return conv, a, b, A_log, dt_bias, state
+
+
+def float64_recurrence(conv, a, b, A_log, dt_bias, state, eps):
+    """The recurrence in float64 with NO rounding of the state: what both forms approximate."""
+    f = lambda x: orc.bf16_decode(x).astype(np.float64)
+    conv, a, b, A_log, dt_bias = f(conv), f(a), f(b), f(A_log), f(dt_bias)
+    S = f(state).copy()                                        # [48, v, k]
+    tokens = conv.shape[0]
+    q = conv[:, :2048].reshape(tokens, 16, 128)
+    k = conv[:, 2048:4096].reshape(tokens, 16, 128)
+    v = conv[:, 4096:].reshape(tokens, 48, 128)
+    q = q / np.sqrt((q * q).sum(-1, keepdims=True) + eps) / np.sqrt(128.0)
+    k = k / np.sqrt((k * k).sum(-1, keepdims=True) + eps)
+    q, k = np.repeat(q, 3, axis=1), np.repeat(k, 3, axis=1)    # value head h reads key head h // 3
+    x = a + dt_bias
+    softplus = np.where(x > 20.0, x, np.log1p(np.exp(np.minimum(x, 20.0))))
+    alpha = np.exp(-np.exp(A_log) * softplus)                  # [tokens, 48]
+    beta = 1.0 / (1.0 + np.exp(-b))
+    out = np.empty((tokens, 48, 128))
+    for t in range(tokens):
+        S *= alpha[t][:, None, None]
+        pred = np.einsum("hvk,hk->hv", S, k[t])
+        delta = (v[t] - pred) * beta[t][:, None]
+        S += delta[:, :, None] * k[t][:, None, :]
+        out[t] = np.einsum("hvk,hk->hv", S, q[t])
+    return out.reshape(tokens, 6144), S
+
+
+def figures(got, want):
+    got, want = np.asarray(got, np.float64).reshape(-1), np.asarray(want, np.float64).reshape(-1)
+    err = got - want
+    nrmse = float(np.sqrt((err * err).sum() / max((want * want).sum(), 1e-300)))
+    cosine = float((got * want).sum() / max(np.sqrt((got * got).sum() * (want * want).sum()), 1e-300))
+    return nrmse, cosine, float(np.abs(err).max())
+
+
+def run_chunked(g, conv, a, b, A_log, dt_bias, state, in_place=False):
+    tokens = conv.shape[0]
+    need = g.capi.lib().q3x_b200_gated_delta_net_chunked_workspace_bytes(tokens)
+    assert need > 0
+    ws = g.empty_like_dev((need,), dtype=np.uint8, fill=0xEE)  # stale contents must not matter
+    d_state = g.Dev(state)
+    d_new = d_state if in_place else g.empty_like_dev(state.shape)
+    out = g.empty_like_dev((tokens, 6144))
+    g.capi.check("q3x_b200_gated_delta_net_update_chunked", g.Dev(conv), tokens, g.Dev(a), g.Dev(b), g.Dev(A_log),
+                 g.Dev(dt_bias), d_state, d_new, EPS, out, ws, need, None)
+    g.sync()
+    assert out.guards_intact() and d_new.guards_intact() and ws.guards_intact()
+    if not in_place:
+        assert np.array_equal(d_state.get(), state), "the input state must stay untouched"
+    return out.get(), d_new.get()
+
+
+@pytest.mark.parametrize("tokens,slow_decay,in_place", [(64, False, False), (1, False, True), (37, True, False),
+                                                        (100, False, True), (256, True, False), (640, True, True),
+                                                        (577, False, False)])
+def test_chunked_recurrence_against_the_sequential_oracle_and_float64(g, tokens, slow_decay, in_place):
+    rng = np.random.default_rng([tokens, int(slow_decay), 171])
+    operands = case(rng, tokens, slow_decay)
+    want_out, want_state = orc.gated_delta_net_update(*operands, EPS)
+    true_out, true_state = float64_recurrence(*operands, EPS)
+    got_out, got_state = run_chunked(g, *operands, in_place=in_place)
+    dec = lambda x: orc.bf16_decode(x).astype(np.float64)
+    assert np.isfinite(dec(got_out)).all() and np.isfinite(dec(got_state)).all()
+
+    nrmse, cosine, worst = figures(dec(got_out), dec(want_out))
+    own, _, _ = figures(dec(got_out), true_out)
+    theirs, _, _ = figures(dec(want_out), true_out)
+    s_nrmse, s_cosine, _ = figures(dec(got_state), dec(want_state))
+    s_own, _, _ = figures(dec(got_state), true_state)
+    s_theirs, _, _ = figures(dec(want_state), true_state)
+    print(f"\nchunked gdn tokens={tokens} slow={slow_decay}: out nrmse={nrmse:.3e} cosine={cosine:.7f} max_abs={worst:.3e}; "
+          f"vs float64: chunked {own:.3e}, sequential oracle {theirs:.3e}; state nrmse={s_nrmse:.3e} "
+          f"vs float64: chunked {s_own:.3e}, oracle {s_theirs:.3e}")
+    assert own <= max(theirs, 4.5e-3), (own, theirs)
+    assert nrmse <= own + 1.05 * theirs and cosine >= 0.9995, (nrmse, own, theirs, cosine)
+    assert s_own <= max(s_theirs, 4.5e-3), (s_own, s_theirs)
+    assert s_nrmse <= s_own + 1.05 * s_theirs and s_cosine >= 0.9995, (s_nrmse, s_own, s_theirs, s_cosine)
+
+
+def test_chunked_recurrence_over_two_calls_continues_the_state(g):
+    """A span split at a chunk boundary into two calls (the state passing through its bf16 form in between) stays
+    within the same distance of the one-call result."""
+    rng = np.random.default_rng(173)
+    operands = case(rng, 256, True)
+    conv, a, b, A_log, dt_bias, state = operands
+    whole_out, whole_state = run_chunked(g, *operands)
+    first_out, mid_state = run_chunked(g, conv[:128], a[:128], b[:128], A_log, dt_bias, state)
+    second_out, last_state = run_chunked(g, conv[128:], a[128:], b[128:], A_log, dt_bias, mid_state)
+    assert np.array_equal(first_out, whole_out[:128]), "the first half does not depend on what follows"
+    dec = lambda x: orc.bf16_decode(x).astype(np.float64)
+    nrmse, cosine, _ = figures(dec(second_out), dec(whole_out[128:]))
+    assert nrmse <= 3e-3 and cosine >= 0.9999, (nrmse, cosine)
+    nrmse, cosine, _ = figures(dec(last_state), dec(whole_state))
+    assert nrmse <= 3e-3 and cosine >= 0.9999, (nrmse, cosine)
+
+
+def test_chunked_recurrence_argument_checks(g):
+    rng = np.random.default_rng(174)
+    conv, a, b, A_log, dt_bias, state = case(rng, 70, False)
+    need = g.capi.lib().q3x_b200_gated_delta_net_chunked_workspace_bytes(70)
+    assert need == 2 * g.capi.lib().q3x_b200_gated_delta_net_chunked_workspace_bytes(64)
+    assert g.capi.lib().q3x_b200_gated_delta_net_chunked_workspace_bytes(0) == 0
+    ws = g.empty_like_dev((need,), dtype=np.uint8)
+    d = [g.Dev(x) for x in (conv, a, b, A_log, dt_bias)]
+    s_in, s_out, out = g.Dev(state), g.empty_like_dev(state.shape), g.empty_like_dev((70, 6144))
+    inv = 1
+    call = lambda *args: g.capi.call("q3x_b200_gated_delta_net_update_chunked", *args)
+    assert call(d[0], 70, *d[1:], s_in, s_out, EPS, out, ws, need - 16, None) == inv      # workspace too small
+    assert call(d[0], 70, *d[1:], s_in, s_out, EPS, out, None, need, None) == inv          # no workspace
+    assert call(d[0], 70, *d[1:], s_in, s_out, 0.0, out, ws, need, None) == inv            # epsilon
+    assert call(d[0], 70, *d[1:], s_in, s_out, EPS, s_in, ws, need, None) == inv           # output on the state
+    assert call(d[0], 70, *d[1:], s_in, s_in.ptr_at(64), EPS, out, ws, need, None) == inv  # partial state overlap
+    assert call(d[0], 70, *d[1:], s_in, s_out, EPS, out, out, need, None) == inv           # workspace on the output
+    assert call(d[0], 0, *d[1:], s_in, s_out, EPS, out, ws, need, None) == 0               # empty span
+    assert call(d[0], 70, *d[1:], s_in, s_out.ptr_at(1), EPS, out, ws, need, None) == 801  # misaligned state
+    g.sync()
+    assert out.guards_intact() and s_out.guards_intact()
