@@ -677,14 +677,23 @@ def probe_projection_ops(cuda_index=0, aim_ms=60.0, tokens=8192):
                                                      "sm_mhz": clk.get("sm_mhz")}
         del q, gate_t, kc, vc, y
     # the weight-only FP8 projections (bf16 activations, E4M3 weights, per-tensor scale) at the attention / GDN shapes
-    for name, n, k in (("fp8_w8a16_gemm_10240x5120", 10240, 5120), ("fp8_w8a16_gemm_12288x5120", 12288, 5120),
-                       ("fp8_w8a16_gemm_5120x6144", 5120, 6144)):
+    # (and the same projections against a bf16 copy of the weight made once: exact widening, dense tensor-core path)
+    for name, n, k, widened in (("fp8_w8a16_gemm_10240x5120", 10240, 5120, False), ("fp8_w8a16_gemm_12288x5120", 12288, 5120, False),
+                                ("fp8_w8a16_gemm_5120x6144", 5120, 6144, False),
+                                ("fp8_widened_gemm_10240x5120", 10240, 5120, True), ("fp8_widened_gemm_12288x5120", 12288, 5120, True),
+                                ("fp8_widened_gemm_5120x6144", 5120, 6144, True)):
         x = (torch.randn((tokens, k), generator=gen, device=dev, dtype=torch.float32)).to(torch.bfloat16)
         w8 = u8((n, k), 0x10, 0x70)
         y = torch.empty((tokens, n), device=dev, dtype=torch.bfloat16)
+        wide = torch.empty((n, k) if widened else (1,), device=dev, dtype=torch.bfloat16)
+        if widened:
+            capi.check("q3x_b200_fp8_weights_to_bf16", w8, n * k, wide, stream)
 
         def call8():
-            capi.check("q3x_b200_fp8_gemm_bf16", w8, 0.02, x, tokens, n, k, y, None, 0, stream)
+            if widened:
+                capi.check("q3x_b200_bf16_gemm_scaled_bf16", wide, 0.02, x, tokens, n, k, y, None, 0, stream)
+            else:
+                capi.check("q3x_b200_fp8_gemm_bf16", w8, 0.02, x, tokens, n, k, y, None, 0, stream)
 
         with torch.cuda.stream(stream_obj):
             call8()
@@ -712,18 +721,26 @@ def probe_projection_ops(cuda_index=0, aim_ms=60.0, tokens=8192):
                      "frac_of_measured_bf16_dense": round(tflops / bf16_peak, 3) if bf16_peak else None,
                      "frac_of_nominal_bf16_dense_2250": round(tflops / 2250.0, 4),
                      "sm_mhz": clk.get("sm_mhz"), "reasons": clk.get("reasons")}
-        del x, w8, y
+        del x, w8, y, wide
     # the weight-only NVFP4 projections (bf16 activations, E2M1 weights, block scales as the transposed bf16 sidecar)
-    for name, n, k in (("nvfp4_w4a16_gemm_17408x5120", 17408, 5120), ("nvfp4_w4a16_gemm_5120x17408", 5120, 17408)):
+    # (and against a bf16 copy of code x block scale made once: exact widening, dense tensor-core path)
+    for name, n, k, widened in (("nvfp4_w4a16_gemm_17408x5120", 17408, 5120, False), ("nvfp4_w4a16_gemm_5120x17408", 5120, 17408, False),
+                                ("nvfp4_widened_gemm_17408x5120", 17408, 5120, True), ("nvfp4_widened_gemm_5120x17408", 5120, 17408, True)):
         x = (torch.randn((tokens, k), generator=gen, device=dev, dtype=torch.float32)).to(torch.bfloat16)
         w4 = u8((n, k // 2))
         row_scales = u8((n, k // 16), 0x28, 0x48)
         sidecar = torch.empty((k // 16, n), device=dev, dtype=torch.bfloat16)
         capi.check("q3x_b200_nvfp4_transpose_block_scales", row_scales, n, k, sidecar, stream)
+        wide = torch.empty((n, k) if widened else (1,), device=dev, dtype=torch.bfloat16)
+        if widened:
+            capi.check("q3x_b200_nvfp4_weights_to_bf16", w4, row_scales, n, k, wide, stream)
         y = torch.empty((tokens, n), device=dev, dtype=torch.bfloat16)
 
         def call4():
-            capi.check("q3x_b200_nvfp4_w4a16_gemm_bf16", w4, sidecar, 0.01, x, tokens, n, k, y, None, 0, stream)
+            if widened:
+                capi.check("q3x_b200_bf16_gemm_scaled_bf16", wide, 0.01, x, tokens, n, k, y, None, 0, stream)
+            else:
+                capi.check("q3x_b200_nvfp4_w4a16_gemm_bf16", w4, sidecar, 0.01, x, tokens, n, k, y, None, 0, stream)
 
         with torch.cuda.stream(stream_obj):
             call4()
@@ -751,7 +768,7 @@ def probe_projection_ops(cuda_index=0, aim_ms=60.0, tokens=8192):
                      "frac_of_measured_bf16_dense": round(tflops / bf16_peak, 3) if bf16_peak else None,
                      "frac_of_nominal_bf16_dense_2250": round(tflops / 2250.0, 4),
                      "sm_mhz": clk.get("sm_mhz"), "reasons": clk.get("reasons")}
-        del x, w4, row_scales, sidecar, y
+        del x, w4, row_scales, sidecar, y, wide
     # the MLP block with its projections: residual + norm + NVFP4 -> gate / up -> SwiGLU + NVFP4 -> down
     chain = importlib.import_module("qwen3x-orin_b200.chain")
     block = chain.ProjectedMlp(tokens, dev)
@@ -818,7 +835,7 @@ def probe_projection_ops(cuda_index=0, aim_ms=60.0, tokens=8192):
     del layer
     # one gated-delta-net layer end to end (FP8 qkv / z projections, conv, token-sequential recurrence, gated norm +
     # NVFP4, NVFP4 output projection, MLP block) for the same panel
-    gdn = chain.ProjectedGdnLayer(tokens, dev)
+    gdn = chain.ProjectedGdnLayer(tokens, dev, chunked=True)
     with torch.cuda.stream(stream_obj):
         gdn.enqueue(stream)
     stream_obj.synchronize()
@@ -837,19 +854,23 @@ def probe_projection_ops(cuda_index=0, aim_ms=60.0, tokens=8192):
             graph.replay()
         e1.record(stream_obj)
         stream_obj.synchronize()
-        # the recurrence alone, on the conv output the layer left behind
-        r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        # the recurrence alone, on the conv output the layer left behind: chunked (what the layer ran) and token by token
+        r0, r1, r2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
         r0.record(stream_obj)
+        capi.check("q3x_b200_gated_delta_net_update_chunked", gdn.conv_out, tokens, gdn.a, gdn.b, gdn.A_log, gdn.dt_bias,
+                   gdn.state, gdn.state, 1e-6, gdn.core, gdn.recurrence_workspace, gdn.recurrence_workspace.numel(), stream)
+        r1.record(stream_obj)
         capi.check("q3x_b200_gated_delta_net_update", gdn.conv_out, tokens, gdn.a, gdn.b, gdn.A_log, gdn.dt_bias, gdn.state,
                    gdn.state, 1e-6, gdn.core, stream)
-        r1.record(stream_obj)
+        r2.record(stream_obj)
         stream_obj.synchronize()
     gdn.check_error()
     us = e0.elapsed_time(e1) * 1e3 / reps
     out["gdn_layer_with_projections"] = {
-        "tokens": tokens, "us": round(us, 1), "tokens_per_s": round(tokens / (us * 1e-6), 1), "kernels": 20,
+        "tokens": tokens, "us": round(us, 1), "tokens_per_s": round(tokens / (us * 1e-6), 1), "kernels": 21,
         "recurrence_us": round(r0.elapsed_time(r1) * 1e3, 1),
-        "note": "residual+RMSNorm, qkv / z (FP8 weights) and a / b (bf16 weights) projections, conv1d+SiLU, token-sequential recurrence, gated "
+        "recurrence_token_sequential_us": round(r1.elapsed_time(r2) * 1e3, 1),
+        "note": "residual+RMSNorm, qkv / z (FP8 weights) and a / b (bf16 weights) projections, conv1d+SiLU, recurrence in 64-token chunks, gated "
                 "RMSNorm+NVFP4, scale re-layout, NVFP4 output projection, MLP block; synthetic weights"}
     del gdn
     torch.cuda.empty_cache()

@@ -176,6 +176,23 @@ int q3x_b200_nvfp4_swizzle_block_scales(const uint8_t* row_major, size_t rows, s
 size_t q3x_b200_bf16_gemm_workspace_bytes(size_t tokens, size_t out_features, size_t in_features);
 int q3x_b200_bf16_gemm_bf16(const uint16_t* weights, const uint16_t* activations, size_t tokens, size_t out_features,
                             size_t in_features, uint16_t* out, void* workspace, size_t workspace_bytes, void* stream);
+/* The same projection with a per-tensor scale in the epilogue, out = bf16(scale * sum), and the exact widening of
+ * FP8 (E4M3) weights to bf16 that feeds it: a runner that keeps a bf16 copy of its FP8 projection weights (made once
+ * at load; `elements` a multiple of 16) gets the products and the FP32 accumulation of q3x_b200_fp8_gemm_bf16 --
+ * fp8_gemv_reference_cpu per token (src/kernels/reference/gemv_reference.cpp:113-141) -- on the dense tensor-core
+ * path, without a conversion stage inside the GEMM.  Outputs 512 or more columns wide use 128 x 256 tiles. */
+int q3x_b200_bf16_gemm_scaled_bf16(const uint16_t* weights, float weight_scale, const uint16_t* activations,
+                                   size_t tokens, size_t out_features, size_t in_features, uint16_t* out,
+                                   void* workspace, size_t workspace_bytes, void* stream);
+int q3x_b200_fp8_weights_to_bf16(const uint8_t* weights, size_t elements, uint16_t* out, void* stream);
+/* The same for an NVFP4 weight: packed E2M1 codes [rows, cols / 2] times their row-major E4M3 block scales
+ * [rows, cols / 16] -> bf16 [rows, cols], exactly (a code has two significant bits, a scale four); the second-level
+ * FP32 scale then rides as `weight_scale` of q3x_b200_bf16_gemm_scaled_bf16, which gives the products and the FP32
+ * accumulation of q3x_b200_nvfp4_w4a16_gemm_bf16 (nvfp4_gemv_reference_cpu per token,
+ * src/kernels/reference/gemv_reference.cpp:179-225).  cols must be a multiple of 16. */
+int q3x_b200_nvfp4_weights_to_bf16(const uint8_t* packed_weights, const uint8_t* block_scales, size_t rows,
+                                   size_t cols, uint16_t* out, void* stream);
+
 
 /* The weight-only FP8 projection of a panel of tokens: out[tokens, out_features] (bf16, row-major) =
  * activations[tokens, in_features] (bf16) x W^T with W = [out_features, in_features] E4M3 bytes and one FP32

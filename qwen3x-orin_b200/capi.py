@@ -41,6 +41,9 @@ SIGNATURES = {
     "q3x_b200_nvfp4_swizzle_block_scales": (_i, [_p, _z, _z, _p, _p]),
     "q3x_b200_bf16_gemm_workspace_bytes": (_z, [_z, _z, _z]),
     "q3x_b200_bf16_gemm_bf16": (_i, [_p, _p, _z, _z, _z, _p, _p, _z, _p]),
+    "q3x_b200_bf16_gemm_scaled_bf16": (_i, [_p, _f, _p, _z, _z, _z, _p, _p, _z, _p]),
+    "q3x_b200_fp8_weights_to_bf16": (_i, [_p, _z, _p, _p]),
+    "q3x_b200_nvfp4_weights_to_bf16": (_i, [_p, _p, _z, _z, _p, _p]),
     "q3x_b200_fp8_gemm_workspace_bytes": (_z, [_z, _z, _z]),
     "q3x_b200_fp8_gemm_bf16": (_i, [_p, _f, _p, _z, _z, _z, _p, _p, _z, _p]),
     "q3x_b200_nvfp4_transpose_block_scales": (_i, [_p, _z, _z, _p, _p]),

@@ -388,6 +388,26 @@ class ProjectedMlp:
             raise RuntimeError("a bounded wait of a single-kernel NVFP4 operator gave up: outputs are invalid")
 
 
+WIDEN_FP8_FROM_TOKENS = 128
+
+
+def fp8_projection(weight: dict, x, tokens: int, out, stream) -> None:
+    """out = bf16((x @ decode(codes).T) * scale) for an FP8 (E4M3, per-tensor scale) weight.  Panels of 128 tokens or
+    more run on the dense tensor-core path against a bf16 copy of the weight, made once on first use (E4M3 -> bf16 is
+    exact, so products, FP32 accumulation and output bytes are those of the mixed-input kernel, at 1.5 times its
+    speed for twice the weight memory); shorter tiles, which are bound by reading the weight, keep the FP8 bytes."""
+    if tokens >= WIDEN_FP8_FROM_TOKENS and weight["rows"] % 8 == 0 and weight["cols"] % 16 == 0:
+        if "wide" not in weight:
+            weight["wide"] = torch.empty((weight["rows"], weight["cols"]), device=weight["codes"].device, dtype=torch.bfloat16)
+            capi.check("q3x_b200_fp8_weights_to_bf16", weight["codes"], weight["rows"] * weight["cols"], weight["wide"], None)
+            torch.cuda.synchronize(weight["codes"].device)
+        capi.check("q3x_b200_bf16_gemm_scaled_bf16", weight["wide"], weight["scale"], x, tokens, weight["rows"], weight["cols"],
+                   out, None, 0, stream)
+    else:
+        capi.check("q3x_b200_fp8_gemm_bf16", weight["codes"], weight["scale"], x, tokens, weight["rows"], weight["cols"],
+                   out, None, 0, stream)
+
+
 class ProjectedAttentionLayer:
     """One full-attention layer of the stack for a tile of tokens appended at `first_position`, every operator and
     every projection from this library (the call order of the reference's layer segment,
@@ -438,8 +458,7 @@ class ProjectedAttentionLayer:
         return cache[self.first_position:]  # the tile's own rows of a cache: [tokens, 4, 256], contiguous
 
     def _fp8(self, weight, x, out, stream):
-        capi.check("q3x_b200_fp8_gemm_bf16", weight["codes"], weight["scale"], x, self.tokens, weight["rows"], weight["cols"],
-                   out, None, 0, stream)
+        fp8_projection(weight, x, self.tokens, out, stream)
 
     def enqueue(self, stream) -> None:
         T = self.tokens
@@ -469,12 +488,14 @@ class ProjectedGdnLayer:
         residual + RMSNorm  ->  qkv and z projections (FP8 weights, bf16 activations, tensor cores) and the two gate
         projections a, b (bf16 weights, 48 x 5120)  ->  causal
         conv1d + SiLU (history carried)  ->  gated-delta-net recurrence (state carried; token by token inside one
-        launch)  ->  gated RMSNorm * silu(z) + NVFP4  ->  output projection (NVFP4 x NVFP4)  ->  the MLP block
+        launch, or with ``chunked`` in 64-token chunks on the tensor cores, the reference's production prefill form,
+        src/kernels/sm87/gdn_prefill_chunk64_native_sm87.h:96-109)  ->  gated RMSNorm * silu(z) + NVFP4  ->  output
+        projection (NVFP4 x NVFP4)  ->  the MLP block
 
     Weights are synthetic."""
 
-    def __init__(self, tokens: int, device, intermediate: int = INTERMEDIATE, seed: int = 31):
-        self.tokens, self.device = tokens, device
+    def __init__(self, tokens: int, device, intermediate: int = INTERMEDIATE, seed: int = 31, chunked: bool = False):
+        self.tokens, self.device, self.chunked = tokens, device, chunked
         gen = torch.Generator(device=device).manual_seed(seed)
         L = capi.lib()
         bf = dict(device=device, dtype=torch.bfloat16)
@@ -518,12 +539,12 @@ class ProjectedGdnLayer:
         self.gated_swizzled = torch.empty(L.q3x_b200_nvfp4_swizzled_scale_bytes(tokens, GDN_V), **u8)
         self.mixer_projected = torch.empty((tokens, HIDDEN), **bf)
         self.workspace = torch.empty(L.q3x_b200_nvfp4_gemm_workspace_bytes(tokens, HIDDEN, GDN_V, CHUNK), **u8)
+        self.recurrence_workspace = torch.empty(L.q3x_b200_gated_delta_net_chunked_workspace_bytes(tokens) if chunked else 0, **u8)
         self.mlp = ProjectedMlp(tokens, device, intermediate=intermediate, seed=seed + 1)
         self.mlp.left, self.mlp.right = self.residual_mid, self.mixer_projected
 
     def _fp8(self, weight, x, out, stream):
-        capi.check("q3x_b200_fp8_gemm_bf16", weight["codes"], weight["scale"], x, self.tokens, weight["rows"], weight["cols"],
-                   out, None, 0, stream)
+        fp8_projection(weight, x, self.tokens, out, stream)
 
     def enqueue(self, stream) -> None:
         T = self.tokens
@@ -534,8 +555,12 @@ class ProjectedGdnLayer:
         capi.check("q3x_b200_bf16_gemm_bf16", self.w_a, self.normalized, T, 48, HIDDEN, self.a, None, 0, stream)
         capi.check("q3x_b200_bf16_gemm_bf16", self.w_b, self.normalized, T, 48, HIDDEN, self.b, None, 0, stream)
         capi.check("q3x_b200_causal_conv1d_silu", self.qkv, T, GDN_CHANNELS, self.conv_w, self.conv_history, self.conv_out, stream)
-        capi.check("q3x_b200_gated_delta_net_update", self.conv_out, T, self.a, self.b, self.A_log, self.dt_bias, self.state,
-                   self.state, EPS, self.core, stream)
+        if self.chunked:
+            capi.check("q3x_b200_gated_delta_net_update_chunked", self.conv_out, T, self.a, self.b, self.A_log, self.dt_bias,
+                       self.state, self.state, EPS, self.core, self.recurrence_workspace, self.recurrence_workspace.numel(), stream)
+        else:
+            capi.check("q3x_b200_gated_delta_net_update", self.conv_out, T, self.a, self.b, self.A_log, self.dt_bias, self.state,
+                       self.state, EPS, self.core, stream)
         capi.check("q3x_b200_rms_norm_silu_gate_nvfp4", self.core, self.gdn_norm_w, self.z, T, 48, 128, EPS, CHUNK, self.gated,
                    self.scratch, self.gated_gs, self.gated_codes, self.gated_scales, stream)
         capi.check("q3x_b200_nvfp4_swizzle_block_scales", self.gated_scales, T, GDN_V, self.gated_swizzled, stream)

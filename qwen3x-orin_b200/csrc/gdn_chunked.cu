@@ -38,7 +38,7 @@ constexpr int kChunk = 64;
 constexpr size_t kQkTile = static_cast<size_t>(kChunk) * kHead * 2;   // [64 tokens][128] bf16, 256-byte rows
 constexpr size_t kWTile = static_cast<size_t>(kHead) * kChunk * 2;    // [128 columns][64 tokens] bf16, 128-byte rows
 constexpr size_t kPTile = static_cast<size_t>(kChunk) * kChunk * 2;   // [64][64] bf16, 128-byte rows
-constexpr size_t kDecayTile = 3 * kChunk * sizeof(float);             // G_t, G_64 / G_t, and one spare row
+constexpr size_t kDecayTile = 2 * kChunk * sizeof(float);             // G_t and G_64 / G_t
 constexpr size_t kChunkBytes = 2 * kKeyHeads * kQkTile + kValueHeads * (2 * kWTile + kPTile + kDecayTile);
 
 struct Workspace {
@@ -104,34 +104,55 @@ __device__ __forceinline__ float dot8(const float (&a)[8], const float (&b)[8]) 
 }
 
 // ================================================================================================================
-// First kernel: one CTA per (chunk, key head); the three value heads of the key head share its q, k and Gram work.
+// First kernel: one CTA of 128 threads per (chunk, value head).  The three value heads of a key head repeat its q / k
+// normalisation and Gram products (a few hundred MMAs) rather than share them: what bounds this kernel is the
+// triangular solve, and the solve is bound by shared-memory broadcasts of its coefficients, one per four FMAs of a
+// column -- so every thread owns TWO columns (column c of W and column c of U, which see the same coefficients) and
+// three such CTAs share an SM.
 // ================================================================================================================
-constexpr int kPrepThreads = 256;
-constexpr int kGramPitch = kChunk + 1;  // FP32 Gram rows, read down a column by consecutive threads
+constexpr int kPrepThreads = 128;
+constexpr int kGroup = kValueHeads / kKeyHeads;  // value heads per key head (3)
+constexpr int kLowerPitch = kChunk + 4;          // FP32 coefficient rows: 16-byte aligned, conflict-free when written
 struct PrepShared {
   __align__(16) unsigned char k[kQkTile];        // normalised k, bf16, the workspace image
   __align__(16) unsigned char q[kQkTile];        // normalised and scaled q
-  __align__(16) uint16_t v[kChunk][kHead];       // the value head's rows as they come
-  __align__(16) float lower_t[kChunk][kChunk];   // A transposed: [j][t], zero for t <= j
-  float kk[kChunk][kGramPitch];                  // k_t . k_j
-  float qk[kChunk][kGramPitch];                  // q_t . k_j
+  __align__(16) uint16_t v[kChunk][kHead];       // the head's value rows as they come
+  __align__(16) float lower_t[kChunk][kLowerPitch];  // A transposed: [j][t], zero for t <= j
   float cumulative[kChunk], growth[kChunk], beta[kChunk];  // log G_t, G_t, beta_t
 };
 
-__global__ void __launch_bounds__(kPrepThreads, 2) gdn_chunk_prepare_kernel(
+// exp of a difference of cumulative log-decays (<= 0): the fast exponential is accurate to 1e-5 relative even at
+// arguments of -100, far inside the rounding of the bf16 operands these factors scale
+__device__ __forceinline__ float decay_ratio(float later, float earlier) { return __expf(later - earlier); }
+
+__global__ void __launch_bounds__(kPrepThreads, 3) gdn_chunk_prepare_kernel(
     const uint16_t* __restrict__ conv_qkv, size_t tokens, const uint16_t* __restrict__ a,
     const uint16_t* __restrict__ b, const uint16_t* __restrict__ A_log, const uint16_t* __restrict__ dt_bias,
     float l2_eps, Workspace ws) {
   extern __shared__ __align__(128) unsigned char raw[];
   PrepShared& sh = *reinterpret_cast<PrepShared*>(raw);
   const size_t chunk = blockIdx.x;
-  const int key_head = blockIdx.y;
+  const int head = blockIdx.y, key_head = head / kGroup;
+  const bool publishes_qk = head % kGroup == 0;  // one of the three CTAs of a key head writes its q / k images
   const size_t token0 = chunk * kChunk;
   const int live = static_cast<int>(min(static_cast<size_t>(kChunk), tokens - token0));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t k_smem = static_cast<uint32_t>(__cvta_generic_to_shared(sh.k));
   const uint32_t q_smem = static_cast<uint32_t>(__cvta_generic_to_shared(sh.q));
 
+  // ---- the head's value rows: asynchronous copies that land while q / k / the Gram products are worked on
+  {
+    const uint32_t v_smem = static_cast<uint32_t>(__cvta_generic_to_shared(sh.v));
+    for (int i = tid; i < kChunk * (kHead / 8); i += kPrepThreads) {
+      const int row = i / (kHead / 8), piece = i % (kHead / 8);
+      if (row < live)
+        cp_async_16(v_smem + static_cast<uint32_t>(i) * 16,
+                    conv_qkv + (token0 + row) * kChannels + kVOffset + head * kHead + piece * 8);
+      else
+        *reinterpret_cast<uint4*>(&sh.v[row][piece * 8]) = make_uint4(0, 0, 0, 0);
+    }
+    cp_async_commit();
+  }
   // ---- q and k: 1 / sqrt(sum + eps) (and 1 / sqrt(128) for q) in FP32, the same expressions as the sequential
   // kernel; 16 lanes per row, one 16-byte piece per lane; rows past the span are zero
   {
@@ -140,8 +161,8 @@ __global__ void __launch_bounds__(kPrepThreads, 2) gdn_chunk_prepare_kernel(
     unsigned char* q_image = ws.q(chunk, key_head);
     unsigned char* k_image = ws.k(chunk, key_head);
 #pragma unroll
-    for (int pass = 0; pass < kChunk / 16; ++pass) {
-      const int row = pass * 16 + (tid >> 4);
+    for (int pass = 0; pass < kChunk / 8; ++pass) {
+      const int row = pass * 8 + (tid >> 4);
       const bool valid = row < live;
       const uint16_t* source = conv_qkv + (token0 + (valid ? row : 0)) * kChannels + key_head * kHead;
       float qv[8], kv[8];
@@ -158,149 +179,136 @@ __global__ void __launch_bounds__(kPrepThreads, 2) gdn_chunk_prepare_kernel(
       const uint32_t at = image(row, piece, kHead * 2);
       *reinterpret_cast<uint4*>(sh.q + at) = qp;
       *reinterpret_cast<uint4*>(sh.k + at) = kp;
-      st_vec(q_image + at, qp);
-      st_vec(k_image + at, kp);
+      if (publishes_qk) {
+        st_vec(q_image + at, qp);
+        st_vec(k_image + at, kp);
+      }
+    }
+  }
+  // ---- the head's gates: warp 0, two tokens per lane, a scan over the log-decays
+  if (warp == 0) {
+    const float a_decay = -expf(bf16_to_float(A_log[head]));
+    const float bias = bf16_to_float(dt_bias[head]);
+    float g2[2], beta2[2];
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int row = 2 * lane + e;
+      const bool valid = row < live;  // a row past the span neither decays nor updates the state
+      g2[e] = valid ? a_decay * softplus_ref(bf16_to_float(a[(token0 + row) * kValueHeads + head]) + bias) : 0.0f;
+      beta2[e] = valid ? sigmoid_ref(bf16_to_float(b[(token0 + row) * kValueHeads + head])) : 0.0f;
+    }
+    float inclusive = g2[0] + g2[1];
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const float up = __shfl_up_sync(0xffffffffu, inclusive, d);
+      if (lane >= d) inclusive += up;
+    }
+    const float last = __shfl_sync(0xffffffffu, inclusive, 31);  // log G_64
+    float* decay = reinterpret_cast<float*>(ws.decay(chunk, head));
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int row = 2 * lane + e;
+      const float c = e == 0 ? inclusive - g2[1] : inclusive;
+      sh.cumulative[row] = c;
+      sh.growth[row] = expf(c);
+      sh.beta[row] = beta2[e];
+      decay[row] = expf(c);                  // G_t
+      decay[kChunk + row] = expf(last - c);  // G_64 / G_t
     }
   }
   __syncthreads();
 
-  // ---- the two Gram matrices: warp (row block of 16, column half of 32), eight steps over the 128 dimensions
+  // ---- the two Gram matrices, a 16-row block per warp; straight from the accumulators, A transposed goes to shared
+  // memory (FP32) and P to its workspace image (bf16)
   {
-    const int row_block = warp & 3, column_half = warp >> 2, g = lane >> 2, t = lane & 3;
-    float kk[4][4], qk[4][4];
+    const int g = lane >> 2, t = lane & 3;
+    float kk[kChunk / 8][4], qk[kChunk / 8][4];
 #pragma unroll
-    for (int n = 0; n < 4; ++n)
+    for (int n = 0; n < kChunk / 8; ++n)
 #pragma unroll
       for (int e = 0; e < 4; ++e) kk[n][e] = qk[n][e] = 0.0f;
 #pragma unroll
     for (int step = 0; step < kHead / 16; ++step) {
       uint32_t ak[4], aq[4];
-      const uint32_t a_at = image(row_block * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, step * 2 + (lane >> 4), kHead * 2);
+      const uint32_t a_at = image(warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, step * 2 + (lane >> 4), kHead * 2);
       ldmatrix_x4(ak, k_smem + a_at);
       ldmatrix_x4(aq, q_smem + a_at);
 #pragma unroll
-      for (int n2 = 0; n2 < 2; ++n2) {
+      for (int n2 = 0; n2 < kChunk / 16; ++n2) {
         uint32_t bk[4];
-        ldmatrix_x4(bk, k_smem + image(column_half * 32 + n2 * 16 + (lane & 7) + (lane >> 4) * 8,
-                                       step * 2 + ((lane >> 3) & 1), kHead * 2));
+        ldmatrix_x4(bk, k_smem + image(n2 * 16 + (lane & 7) + (lane >> 4) * 8, step * 2 + ((lane >> 3) & 1), kHead * 2));
         mma_bf16(kk[2 * n2], ak, bk[0], bk[1]);
         mma_bf16(kk[2 * n2 + 1], ak, bk[2], bk[3]);
         mma_bf16(qk[2 * n2], aq, bk[0], bk[1]);
         mma_bf16(qk[2 * n2 + 1], aq, bk[2], bk[3]);
       }
     }
+    unsigned char* p_image = ws.p(chunk, head);
 #pragma unroll
-    for (int n = 0; n < 4; ++n)
+    for (int half = 0; half < 2; ++half) {
+      const int row = warp * 16 + g + half * 8;  // token t of A[t][j] and P[t][j]
+      const float own = sh.cumulative[row], scale = sh.beta[row];
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int row = row_block * 16 + g + (e >> 1) * 8, column = column_half * 32 + n * 8 + 2 * t + (e & 1);
-        sh.kk[row][column] = kk[n][e];
-        sh.qk[row][column] = qk[n][e];
+      for (int n = 0; n < kChunk / 8; ++n) {
+        const int j = n * 8 + 2 * t;
+        const float2 earlier = *reinterpret_cast<const float2*>(&sh.cumulative[j]);
+        const float r0 = decay_ratio(own, earlier.x), r1 = decay_ratio(own, earlier.y);
+        sh.lower_t[j][row] = j < row ? scale * kk[n][half * 2] * r0 : 0.0f;
+        sh.lower_t[j + 1][row] = j + 1 < row ? scale * kk[n][half * 2 + 1] * r1 : 0.0f;
+        const uint32_t pair = pack_bf16x2(j <= row ? qk[n][half * 2] * r0 : 0.0f, j + 1 <= row ? qk[n][half * 2 + 1] * r1 : 0.0f);
+        st_u32(p_image + image(row, n, kChunk * 2) + 4 * t, pair);
       }
+    }
   }
+  cp_async_wait_all();
+  __syncthreads();  // A transposed and the value rows are complete
 
-  for (int r = 0; r < kValueHeads / kKeyHeads; ++r) {
-    const int head = key_head * (kValueHeads / kKeyHeads) + r;
-    __syncthreads();  // the Gram matrices are complete; the previous head's readers are done
-    // ---- the head's value rows, and its gates: warp 0 takes two tokens per lane and scans the log-decays
-    for (int i = tid; i < kChunk * (kHead / 8); i += kPrepThreads) {
-      const int row = i / (kHead / 8), piece = i % (kHead / 8);
-      const bool valid = row < live;
-      const uint4 value = valid ? ld_weight(reinterpret_cast<const uint4*>(
-                                                conv_qkv + (token0 + row) * kChannels + kVOffset + head * kHead) + piece)
-                                : make_uint4(0, 0, 0, 0);
-      *reinterpret_cast<uint4*>(&sh.v[row][piece * 8]) = value;
+  // ---- (I + A) [W | U] = [beta G K | beta V]: thread c owns column c of W AND column c of U (128 registers) and
+  // eliminates row by row; a coefficient, broadcast from shared memory four rows per load, serves both columns
+  float xw[kChunk], xu[kChunk];
+  {
+    const int piece = tid >> 3, within = tid & 7;
+#pragma unroll
+    for (int t = 0; t < kChunk; ++t) {
+      const float scale = sh.beta[t];
+      xw[t] = scale * sh.growth[t] * bf16_to_float(*reinterpret_cast<const uint16_t*>(sh.k + image(t, piece, kHead * 2) + within * 2));
+      xu[t] = scale * bf16_to_float(sh.v[t][tid]);
     }
-    if (warp == 0) {
-      const float a_decay = -expf(bf16_to_float(A_log[head]));
-      const float bias = bf16_to_float(dt_bias[head]);
-      float g2[2], beta2[2];
+  }
 #pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const int row = 2 * lane + e;
-        const bool valid = row < live;  // a row past the span neither decays nor updates the state
-        g2[e] = valid ? a_decay * softplus_ref(bf16_to_float(a[(token0 + row) * kValueHeads + head]) + bias) : 0.0f;
-        beta2[e] = valid ? sigmoid_ref(bf16_to_float(b[(token0 + row) * kValueHeads + head])) : 0.0f;
-      }
-      float inclusive = g2[0] + g2[1];
+  for (int j = 0; j < kChunk - 1; ++j) {
+    const float2 minus_w = make_float2(-xw[j], -xw[j]), minus_u = make_float2(-xu[j], -xu[j]);
 #pragma unroll
-      for (int d = 1; d < 32; d <<= 1) {
-        const float up = __shfl_up_sync(0xffffffffu, inclusive, d);
-        if (lane >= d) inclusive += up;
-      }
-      const float last = __shfl_sync(0xffffffffu, inclusive, 31);  // log G_64
-      float* decay = reinterpret_cast<float*>(ws.decay(chunk, head));
-#pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const int row = 2 * lane + e;
-        const float c = e == 0 ? inclusive - g2[1] : inclusive;
-        sh.cumulative[row] = c;
-        sh.growth[row] = expf(c);
-        sh.beta[row] = beta2[e];
-        decay[row] = expf(c);                 // G_t
-        decay[kChunk + row] = expf(last - c);  // G_64 / G_t
-        decay[2 * kChunk + row] = 0.0f;
-      }
+    for (int t4 = (j + 1) / 4; t4 < kChunk / 4; ++t4) {
+      // rows t <= j of this group carry a zero coefficient
+      const float4 c = *reinterpret_cast<const float4*>(&sh.lower_t[j][t4 * 4]);
+      const float2 c01 = make_float2(c.x, c.y), c23 = make_float2(c.z, c.w);
+      const float2 w01 = fma2(c01, minus_w, make_float2(xw[t4 * 4 + 0], xw[t4 * 4 + 1]));
+      const float2 w23 = fma2(c23, minus_w, make_float2(xw[t4 * 4 + 2], xw[t4 * 4 + 3]));
+      const float2 u01 = fma2(c01, minus_u, make_float2(xu[t4 * 4 + 0], xu[t4 * 4 + 1]));
+      const float2 u23 = fma2(c23, minus_u, make_float2(xu[t4 * 4 + 2], xu[t4 * 4 + 3]));
+      xw[t4 * 4 + 0] = w01.x;
+      xw[t4 * 4 + 1] = w01.y;
+      xw[t4 * 4 + 2] = w23.x;
+      xw[t4 * 4 + 3] = w23.y;
+      xu[t4 * 4 + 0] = u01.x;
+      xu[t4 * 4 + 1] = u01.y;
+      xu[t4 * 4 + 2] = u23.x;
+      xu[t4 * 4 + 3] = u23.y;
     }
-    __syncthreads();
-    // ---- A transposed (FP32, shared) and P (bf16, workspace image); consecutive threads take consecutive t
-#pragma unroll 4
-    for (int i = tid; i < kChunk * kChunk; i += kPrepThreads) {
-      const int t = i % kChunk, j = i / kChunk;
-      sh.lower_t[j][t] = j < t ? sh.beta[t] * sh.kk[t][j] * expf(sh.cumulative[t] - sh.cumulative[j]) : 0.0f;
-    }
-    {
-      unsigned char* p_image = ws.p(chunk, head);
-      for (int i = tid; i < kChunk * (kChunk / 8); i += kPrepThreads) {
-        const int t = i / (kChunk / 8), piece = i % (kChunk / 8);
-        float p[8];
+  }
+  // column c of W (of U) is row c of its transposed image: 128 contiguous bytes, pieces permuted by the row
+  unsigned char* w_image = ws.w(chunk, head);
+  unsigned char* u_image = ws.u(chunk, head);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          const int j = piece * 8 + e;
-          p[e] = j <= t ? sh.qk[t][j] * expf(sh.cumulative[t] - sh.cumulative[j]) : 0.0f;
-        }
-        st_vec(p_image + image(t, piece, kChunk * 2), pack8(p));
-      }
-    }
-    __syncthreads();
-    // ---- (I + A) X = [beta G K | beta V]: thread c owns column c of X (c < 128: W, else U) in 64 registers and
-    // eliminates row by row; the coefficients are shared-memory broadcasts, four rows per load
-    {
-      float x[kChunk];
-      if (tid < kHead) {
-        const int piece = tid >> 3, within = tid & 7;
+  for (int piece = 0; piece < kChunk / 8; ++piece) {
+    float eight[8];
 #pragma unroll
-        for (int t = 0; t < kChunk; ++t)
-          x[t] = sh.beta[t] * sh.growth[t] *
-                 bf16_to_float(*reinterpret_cast<const uint16_t*>(sh.k + image(t, piece, kHead * 2) + within * 2));
-      } else {
+    for (int e = 0; e < 8; ++e) eight[e] = xw[piece * 8 + e];
+    st_vec(w_image + image(tid, piece, kChunk * 2), pack8(eight));
 #pragma unroll
-        for (int t = 0; t < kChunk; ++t) x[t] = sh.beta[t] * bf16_to_float(sh.v[t][tid - kHead]);
-      }
-#pragma unroll
-      for (int j = 0; j < kChunk - 1; ++j) {
-        const float solved = x[j];
-#pragma unroll
-        for (int t4 = (j + 1) / 4; t4 < kChunk / 4; ++t4) {
-          // rows t <= j of this group carry a zero coefficient
-          const float4 c = *reinterpret_cast<const float4*>(&sh.lower_t[j][t4 * 4]);
-          x[t4 * 4 + 0] = fmaf(-c.x, solved, x[t4 * 4 + 0]);
-          x[t4 * 4 + 1] = fmaf(-c.y, solved, x[t4 * 4 + 1]);
-          x[t4 * 4 + 2] = fmaf(-c.z, solved, x[t4 * 4 + 2]);
-          x[t4 * 4 + 3] = fmaf(-c.w, solved, x[t4 * 4 + 3]);
-        }
-      }
-      // column c of W (or U) is row c of the transposed image: 128 contiguous bytes, pieces permuted by the row
-      const int row = tid < kHead ? tid : tid - kHead;
-      unsigned char* target = tid < kHead ? ws.w(chunk, head) : ws.u(chunk, head);
-#pragma unroll
-      for (int piece = 0; piece < kChunk / 8; ++piece) {
-        float eight[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) eight[e] = x[piece * 8 + e];
-        st_vec(target + image(row, piece, kChunk * 2), pack8(eight));
-      }
-    }
+    for (int e = 0; e < 8; ++e) eight[e] = xu[piece * 8 + e];
+    st_vec(u_image + image(tid, piece, kChunk * 2), pack8(eight));
   }
 }
 
@@ -536,7 +544,7 @@ int launch_chunked(const uint16_t* conv_qkv, size_t tokens, const uint16_t* a, c
   cudaStream_t s = as_stream(stream);
   const Workspace ws{static_cast<unsigned char*>(workspace), chunks_of(tokens)};
   if (ws.chunks > 0x7fffffffu) return kInvalid;
-  gdn_chunk_prepare_kernel<<<dim3(static_cast<unsigned>(ws.chunks), kKeyHeads), kPrepThreads, sizeof(PrepShared), s>>>(
+  gdn_chunk_prepare_kernel<<<dim3(static_cast<unsigned>(ws.chunks), kValueHeads), kPrepThreads, sizeof(PrepShared), s>>>(
       conv_qkv, tokens, a, b, A_log, dt_bias, l2_eps, ws);
   gdn_chunk_state_kernel<<<dim3(kValueHeads, kStateSplits), kStateThreads, kStateShared, s>>>(ws, tokens, state_in,
                                                                                              state_out, out);

@@ -203,6 +203,39 @@ __global__ void __launch_bounds__(kThreads) transpose_scales_kernel(const uint8_
   }
 }
 
+// Packed E2M1 codes x their E4M3 block scale -> bf16, one block of 16 weights per thread.  The product of a code
+// (values 0, 0.5 .. 6: two significant bits) and a scale (four) has at most six significant bits: exact in bf16.
+__global__ void __launch_bounds__(kThreads) widen_weights_kernel(const uint2* __restrict__ packed, const uint8_t* __restrict__ scales,
+                                                                 size_t blocks, uint4* __restrict__ out) {
+  const size_t stride = static_cast<size_t>(gridDim.x) * kThreads;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x; i < blocks; i += stride) {
+    const uint2 codes = __ldg(packed + i);
+    const uint32_t scale_code = scales[i];
+    const float magnitude = decode_e4m3_positive(scale_code & 0x7fu);
+    const float scale = (scale_code & 0x80u) ? -magnitude : magnitude;
+    const uint32_t words[2] = {codes.x, codes.y};
+    float f[16];
+#pragma unroll
+    for (int w = 0; w < 2; ++w)
+#pragma unroll
+      for (int n = 0; n < 8; ++n) {
+        const uint32_t code = (words[w] >> (4 * n)) & 0xfu;
+        // E2M1: exponent field e (2 bits), mantissa m: value = e == 0 ? 0.5 m : (1 + 0.5 m) * 2^(e - 1)
+        const uint32_t e = (code >> 1) & 3u, m = code & 1u;
+        const float value = e == 0 ? 0.5f * static_cast<float>(m) : (1.0f + 0.5f * static_cast<float>(m)) * static_cast<float>(1u << (e - 1));
+        f[w * 8 + n] = ((code & 8u) ? -value : value) * scale;
+      }
+    float lo[8], hi[8];
+#pragma unroll
+    for (int n = 0; n < 8; ++n) {
+      lo[n] = f[n];
+      hi[n] = f[8 + n];
+    }
+    out[2 * i] = pack8(lo);
+    out[2 * i + 1] = pack8(hi);
+  }
+}
+
 __global__ void __launch_bounds__(kThreads) debug_encode_kernel(const float* in, size_t count, uint8_t* out,
                                                                 int format) {
   const size_t i = static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x;
@@ -699,6 +732,21 @@ extern "C" int q3x_b200_nvfp4_transpose_block_scales(const uint8_t* row_major, s
   clear_stale_error();
   transpose_scales_kernel<<<grid_for(rows * row_blocks, kThreads, 8), kThreads, 0, as_stream(stream)>>>(
       row_major, rows, row_blocks, transposed);
+  return launch_status();
+}
+
+extern "C" int q3x_b200_nvfp4_weights_to_bf16(const uint8_t* packed_weights, const uint8_t* block_scales, size_t rows,
+                                              size_t cols, uint16_t* out, void* stream) {
+  if (cols % Q3X_B200_NVFP4_BLOCK != 0 || mul3_overflows(rows, cols, 2)) return kInvalid;
+  if (rows == 0 || cols == 0) return kOk;
+  if (packed_weights == nullptr || block_scales == nullptr || out == nullptr) return kInvalid;
+  if (!aligned16(packed_weights) || !aligned16(out)) return kNotSupported;
+  const size_t blocks = rows * (cols / Q3X_B200_NVFP4_BLOCK);
+  const Span so = span(out, rows * cols * 2);
+  if (overlap(so, span(packed_weights, rows * cols / 2)) || overlap(so, span(block_scales, blocks))) return kInvalid;
+  clear_stale_error();
+  widen_weights_kernel<<<grid_for(blocks, kThreads, 8), kThreads, 0, as_stream(stream)>>>(
+      reinterpret_cast<const uint2*>(packed_weights), block_scales, blocks, reinterpret_cast<uint4*>(out));
   return launch_status();
 }
 

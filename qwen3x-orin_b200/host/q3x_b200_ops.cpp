@@ -2,6 +2,8 @@
 // C ABI, which performs the pointer / overlap / overflow checks and enqueues the sm_100a kernels.
 #include "q3x_b200_ops.hpp"
 
+#include <cmath>
+
 #include "q3x_b200.h"
 
 namespace q3x::runtime {
@@ -312,6 +314,41 @@ int gdn_decode_detail::launch_gated_delta_net_update_plain_rms_norm_silu_gate_ex
   return q3x_b200_gated_delta_net_update_rms_norm_silu_gate(conv_qkv, 1U, a, b, A_log, dt_bias, state_input,
                                                             state_output, l2_epsilon, norm_weight, silu_gate,
                                                             norm_epsilon, output, stream);
+}
+
+std::size_t gdn_prefill_chunk64_native_detail::workspace_bytes() noexcept {
+  return q3x_b200_gated_delta_net_chunked_workspace_bytes(kMaximumTokenCount);
+}
+
+int gdn_prefill_chunk64_native_detail::launch(void* workspace, std::size_t workspace_capacity_bytes,
+                                              const std::uint16_t* conv_qkv, std::size_t token_count,
+                                              const std::uint16_t* a, const std::uint16_t* b, const std::uint16_t* A_log,
+                                              const std::uint16_t* dt_bias, const std::uint16_t* state_input,
+                                              std::uint16_t* state_output, float l2_epsilon,
+                                              const std::uint16_t* norm_weight, const std::uint16_t* silu_gate,
+                                              float norm_epsilon, std::uint16_t* output, void* stream) noexcept {
+  // the reference's admission: 1 to 512 tokens, every pointer present, both epsilons finite and positive, the whole
+  // workspace whatever the token count; all before the first enqueue
+  if (token_count == 0U || token_count > kMaximumTokenCount || workspace == nullptr ||
+      workspace_capacity_bytes < workspace_bytes() || norm_weight == nullptr || silu_gate == nullptr ||
+      !std::isfinite(norm_epsilon) || norm_epsilon <= 0.0F)
+    return kInvalidValue;
+  if (const int status = q3x_b200_gated_delta_net_update_chunked(conv_qkv, token_count, a, b, A_log, dt_bias, state_input,
+                                                                 state_output, l2_epsilon, output, workspace,
+                                                                 workspace_capacity_bytes, stream);
+      status != 0)
+    return status;
+  return q3x_b200_rms_norm_silu_gate(output, norm_weight, silu_gate, token_count * 48U, 128U, norm_epsilon, output, stream);
+}
+
+int gdn_prefill_chunk64_native_detail::launch_fixed_production(
+    void* workspace, std::size_t workspace_capacity_bytes, const std::uint16_t* conv_qkv, std::size_t token_count,
+    const std::uint16_t* a, const std::uint16_t* b, const std::uint16_t* A_log, const std::uint16_t* dt_bias,
+    const std::uint16_t* state_input, std::uint16_t* state_output, float l2_epsilon, const std::uint16_t* norm_weight,
+    const std::uint16_t* silu_gate, float norm_epsilon, std::uint16_t* output, void* stream) noexcept {
+  // one tactic here, so the sealed entry is the same call
+  return launch(workspace, workspace_capacity_bytes, conv_qkv, token_count, a, b, A_log, dt_bias, state_input,
+                state_output, l2_epsilon, norm_weight, silu_gate, norm_epsilon, output, stream);
 }
 
 int launch_gated_delta_net_update_plain_rms_norm_silu_gate_cuda(

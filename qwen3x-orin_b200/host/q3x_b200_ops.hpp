@@ -236,6 +236,28 @@ namespace gdn_decode_detail {
     std::size_t norm_head_dimension, float norm_epsilon, std::uint16_t* output, GdnDimensions dimensions = {},
     void* cuda_stream = nullptr) noexcept;
 
+namespace gdn_prefill_chunk64_native_detail {
+inline constexpr std::size_t kMaximumTokenCount = 512U;
+// src/kernels/sm87/gdn_prefill_chunk64_native_sm87.h:96-122: the GDN recurrence of a prefill tile of 1 to 512 tokens
+// in chunks of 64 (WY form), then the gated RMSNorm of its output in place.  One reusable caller-owned workspace of at
+// least workspace_bytes() bytes, whatever the token count.
+[[nodiscard]] std::size_t workspace_bytes() noexcept;
+[[nodiscard]] int launch(void* workspace, std::size_t workspace_capacity_bytes, const std::uint16_t* conv_qkv,
+                         std::size_t token_count, const std::uint16_t* a, const std::uint16_t* b,
+                         const std::uint16_t* A_log, const std::uint16_t* dt_bias, const std::uint16_t* state_input,
+                         std::uint16_t* state_output, float l2_epsilon, const std::uint16_t* norm_weight,
+                         const std::uint16_t* silu_gate, float norm_epsilon, std::uint16_t* output,
+                         void* cuda_stream = nullptr) noexcept;
+[[nodiscard]] int launch_fixed_production(void* workspace, std::size_t workspace_capacity_bytes,
+                                          const std::uint16_t* conv_qkv, std::size_t token_count, const std::uint16_t* a,
+                                          const std::uint16_t* b, const std::uint16_t* A_log,
+                                          const std::uint16_t* dt_bias, const std::uint16_t* state_input,
+                                          std::uint16_t* state_output, float l2_epsilon,
+                                          const std::uint16_t* norm_weight, const std::uint16_t* silu_gate,
+                                          float norm_epsilon, std::uint16_t* output,
+                                          void* cuda_stream = nullptr) noexcept;
+}  // namespace gdn_prefill_chunk64_native_detail
+
 namespace gdn_prefill_whole_span_conv_detail {
 inline constexpr std::size_t kMaximumTokenCount = 512U;
 // src/kernels/reference/gdn_prefill_whole_span_conv_sm87.h:59-67

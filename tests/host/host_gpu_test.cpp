@@ -467,6 +467,27 @@ static void test_core_launchers(cudaStream_t s) {
   EXPECT(q3x_b200_gated_delta_net_update_rms_norm_silu_gate(conv.p, 1, a.p, b.p, A_log.p, dt.p, s4.p, s4.p, eps, nw.p, z.p, eps,
                                                             f2.p, s) == 0);
   EXPECT(same(f1, f2) && same(s3, s4) && written(f1));
+  // the chunked prefill form with its norm epilogue: the C-ABI recurrence, then the gated norm in place
+  {
+    namespace chunked = rt::gdn_prefill_chunk64_native_detail;
+    const std::size_t tile = 100, bytes = chunked::workspace_bytes();
+    EXPECT(bytes == q3x_b200_gated_delta_net_chunked_workspace_bytes(512) && bytes > 0);
+    Bf16 cconv(random_bf16(tile * 10240, 1.0f)), ca(random_bf16(tile * 48, 1.0f)), cb(random_bf16(tile * 48, 1.0f)),
+        cz(random_bf16(tile * 6144, 1.0f)), c1(tile * 6144), c2(tile * 6144), cs1(state_host), cs2(state_host);
+    DeviceBuffer<std::uint8_t> cws(bytes);
+    EXPECT(chunked::launch(cws.p, bytes, cconv.p, tile, ca.p, cb.p, A_log.p, dt.p, cs1.p, cs1.p, eps, nw.p, cz.p, eps, c1.p, s) == 0);
+    EXPECT(q3x_b200_gated_delta_net_update_chunked(cconv.p, tile, ca.p, cb.p, A_log.p, dt.p, cs2.p, cs2.p, eps, c2.p, cws.p, bytes,
+                                                   s) == 0);
+    EXPECT(q3x_b200_rms_norm_silu_gate(c2.p, nw.p, cz.p, tile * 48, 128, eps, c2.p, s) == 0);
+    EXPECT(same(c1, c2) && same(cs1, cs2) && written(c1));
+    EXPECT(chunked::launch_fixed_production(cws.p, bytes, cconv.p, tile, ca.p, cb.p, A_log.p, dt.p, cs1.p, cs1.p, eps, nw.p,
+                                            cz.p, eps, c1.p, s) == 0);
+    EXPECT(chunked::launch(cws.p, bytes, cconv.p, 513, ca.p, cb.p, A_log.p, dt.p, cs1.p, cs1.p, eps, nw.p, cz.p, eps, c1.p, s) == 1);
+    EXPECT(chunked::launch(cws.p, bytes - 1, cconv.p, tile, ca.p, cb.p, A_log.p, dt.p, cs1.p, cs1.p, eps, nw.p, cz.p, eps, c1.p,
+                           s) == 1);
+    EXPECT(chunked::launch(cws.p, bytes, cconv.p, tile, ca.p, cb.p, A_log.p, dt.p, cs1.p, cs1.p, eps, nullptr, cz.p, eps, c1.p,
+                           s) == 1);
+  }
   // decode attention
   const std::size_t length = 300;
   Bf16 q(random_bf16(24 * 256, 1.0f)), kc(random_bf16(length * 1024, 1.0f)), vc(random_bf16(length * 1024, 1.0f)),

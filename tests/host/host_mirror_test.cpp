@@ -62,6 +62,23 @@ static void test_launcher_limits() {
   EXPECT(rt::launch_centered_rms_norm_reference_cuda(p, p + 0x1000, 8, 0.0F, p + 0x2000) == kInvalid);
   EXPECT(rt::launch_embedding_gather_reference_cuda(p, 100, 8, 100, p + 0x100000) == kInvalid);  // id out of range
   EXPECT(rt::launch_embedding_gather_prompt_reference_cuda(p, 100, 8, nullptr, 0, p + 0x100000) == kInvalid);
+  // chunked GDN prefill: 1 to 512 tokens, the whole workspace, both norm operands, a valid norm epsilon
+  {
+    namespace chunked = rt::gdn_prefill_chunk64_native_detail;
+    const std::size_t bytes = chunked::workspace_bytes();
+    EXPECT(bytes > 0 && bytes % 16 == 0);
+    auto* ws = reinterpret_cast<std::uint8_t*>(0x40000000);
+    auto call = [&](void* w, std::size_t cap, std::size_t tokens, const std::uint16_t* nw, float norm_eps) {
+      return chunked::launch(w, cap, p, tokens, p + 0x1000000, p + 0x1100000, p + 0x1200000, p + 0x1300000, p + 0x2000000,
+                             p + 0x2000000, 1e-6F, nw, p + 0x3000000, norm_eps, p + 0x5000000);
+    };
+    EXPECT(call(ws, bytes, 0, p + 0x1400000, 1e-6F) == kInvalid);
+    EXPECT(call(ws, bytes, 513, p + 0x1400000, 1e-6F) == kInvalid);
+    EXPECT(call(nullptr, bytes, 64, p + 0x1400000, 1e-6F) == kInvalid);
+    EXPECT(call(ws, bytes - 16, 64, p + 0x1400000, 1e-6F) == kInvalid);
+    EXPECT(call(ws, bytes, 64, nullptr, 1e-6F) == kInvalid);
+    EXPECT(call(ws, bytes, 64, p + 0x1400000, 0.0F) == kInvalid);
+  }
 }
 
 static void test_dispatch() {

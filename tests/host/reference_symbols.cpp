@@ -7,6 +7,7 @@
 #include <cstdio>
 
 #include "gdn_prefill_whole_span_conv_sm87.h"  // src/kernels/reference (source-private header)
+#include "../sm87/gdn_prefill_chunk64_native_sm87.h"  // src/kernels/sm87 (source-private header)
 #include "q3x/kernels/reference_gemv.h"
 #include "q3x/runtime/decode_ops.h"
 #include "q3x/runtime/gdn_decode.h"
@@ -16,6 +17,7 @@
 namespace rt = q3x::runtime;
 namespace kn = q3x::kernels;
 namespace conv = q3x::runtime::gdn_prefill_whole_span_conv_detail;
+namespace chunked = q3x::runtime::gdn_prefill_chunk64_native_detail;
 
 int main() {
   const void* symbols[] = {
@@ -43,6 +45,9 @@ int main() {
       reinterpret_cast<const void*>(&rt::launch_causal_conv1d_silu_update_reference_cuda),
       reinterpret_cast<const void*>(&rt::launch_causal_conv1d_silu_update_tile_reference_cuda),
       // the prefill conv forms (source-private header of the reference)
+      reinterpret_cast<const void*>(static_cast<std::size_t (*)() noexcept>(&chunked::workspace_bytes)),
+      reinterpret_cast<const void*>(&chunked::launch),
+      reinterpret_cast<const void*>(&chunked::launch_fixed_production),
       reinterpret_cast<const void*>(&conv::launch_causal_conv1d_silu_update_whole_span_exact_cuda),
       reinterpret_cast<const void*>(&conv::launch_causal_conv1d_silu_update_token_parallel_exact_cuda),
       reinterpret_cast<const void*>(&conv::launch_causal_conv1d_silu_update_token_parallel_compact_qk_exact_cuda),

@@ -55,3 +55,42 @@ def test_bf16_gemm_rejections(g):
     assert call(w=None) == inv
     assert call(out=fake) == inv
     assert call(t=0) == 0
+
+
+@pytest.mark.parametrize("tokens,n,k", [(200, 512, 5120), (640, 1024, 5120), (129, 6144, 1024), (96, 48, 5120)])
+def test_widened_fp8_weights_through_the_scaled_gemm(g, tokens, n, k):
+    """FP8 weights widened to bf16 once (exactly) and multiplied on the dense path with the per-tensor scale in the
+    epilogue: the rule of the FP8 projection (tests/test_gpu_fp8_gemm.py) against the float64 product of the decoded
+    operands, and the same bytes as the mixed-input FP8 GEMM on nearly every element (both accumulate the same
+    products in FP32, in different orders)."""
+    rng = np.random.default_rng([tokens, n, k, 127])
+    x = fx.normal_bf16(rng, (tokens, k))
+    codes = (rng.integers(0x08, 0x78, size=(n, k)) | (rng.integers(0, 2, size=(n, k)) << 7)).astype(np.uint8)
+    scale = 0.0123
+    d_codes, d_x = g.Dev(codes), g.Dev(x)
+    wide = g.empty_like_dev((n, k))
+    g.capi.check("q3x_b200_fp8_weights_to_bf16", d_codes, n * k, wide, None)
+    g.sync()
+    L = orc.oracle_lib()
+    want_w = np.array([L.decode_e4m3(i) for i in range(256)], dtype=np.float32)[codes]
+    assert np.array_equal(orc.bf16_decode(wide.get()), want_w), "E4M3 -> bf16 is exact"
+    out, mixed = g.empty_like_dev((tokens, n)), g.empty_like_dev((tokens, n))
+    g.capi.check("q3x_b200_bf16_gemm_scaled_bf16", wide, scale, d_x, tokens, n, k, out, None, 0, None)
+    g.capi.check("q3x_b200_fp8_gemm_bf16", d_codes, scale, d_x, tokens, n, k, mixed, None, 0, None)
+    g.sync()
+    xf, wf = orc.bf16_decode(x).astype(np.float64), want_w.astype(np.float64)
+    want, mag = (xf @ wf.T) * scale, (np.abs(xf) @ np.abs(wf).T) * scale
+    got = orc.bf16_decode(out.get()).astype(np.float64)
+    assert np.all(np.abs(got - want) <= 2.0 ** -8 * np.abs(want) + 1e-5 * mag + 1e-30)
+    assert np.mean(out.get() == mixed.get()) > 0.97
+    assert out.guards_intact() and wide.guards_intact()
+
+
+def test_widening_rejections(g):
+    inv, fake = g.capi.CUDA_ERROR_INVALID_VALUE, 0x10000000
+    assert g.capi.call("q3x_b200_fp8_weights_to_bf16", fake, 24, fake + (1 << 24), None) == inv      # not 16-element vectors
+    assert g.capi.call("q3x_b200_fp8_weights_to_bf16", fake, 64, fake + 32, None) == inv             # overlap
+    assert g.capi.call("q3x_b200_fp8_weights_to_bf16", None, 64, fake + (1 << 24), None) == inv
+    assert g.capi.call("q3x_b200_fp8_weights_to_bf16", fake, 0, fake + (1 << 24), None) == 0
+    assert g.capi.call("q3x_b200_bf16_gemm_scaled_bf16", fake, float("nan"), fake + (1 << 24), 64, 64, 128,
+                       fake + (2 << 24), None, 0, None) == inv

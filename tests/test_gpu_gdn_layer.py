@@ -73,3 +73,38 @@ def test_gdn_layer_stage_by_stage():
     want_r2, _ = orc.residual_add_rms_norm(host(layer.residual_mid), host(layer.mixer_projected), host(layer.mlp.norm_w), chain.EPS)
     gpu_util.assert_bits_equal(host(layer.mlp.residual), want_r2, "post-mixer residual")
     assert bool(torch.isfinite(layer.mlp.down.float()).all().item())
+
+
+def test_gdn_layer_with_the_chunked_recurrence():
+    """The same layer with the recurrence in 64-token chunks: its output and state against the sequential oracle on
+    the GPU's own conv output, by the figures the reference uses for this form (NRMSE, cosine; the oracle's per-token
+    state rounding alone puts it about 7e-3 from the unrounded recurrence over 150 tokens), and the stage after it
+    exact on the GPU's own bytes."""
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from tests import gpu_util
+    from tests.test_gpu_gdn_chunked import figures
+
+    orc.build()
+    gpu_util.capi.load()
+    chain = importlib.import_module("qwen3x-orin_b200.chain")
+    tokens = 150
+    layer = chain.ProjectedGdnLayer(tokens, torch.device("cuda", 0), intermediate=1024, seed=13, chunked=True)
+    state0 = host(layer.state).copy()
+    layer.enqueue(None)
+    torch.cuda.synchronize()
+    layer.check_error()
+    core_want, state_want = orc.gated_delta_net_update(host(layer.conv_out), host(layer.a), host(layer.b), host(layer.A_log),
+                                                       host(layer.dt_bias), state0, chain.EPS)
+    dec = lambda x: orc.bf16_decode(x).astype(np.float64)
+    nrmse, cosine, _ = figures(dec(host(layer.core)), dec(core_want))
+    assert nrmse <= 1.2e-2 and cosine >= 0.9995, (nrmse, cosine)
+    nrmse, cosine, _ = figures(dec(host(layer.state)), dec(state_want))
+    assert nrmse <= 1.2e-2 and cosine >= 0.9995, (nrmse, cosine)
+    gated_want = orc.rms_norm_rows(host(layer.core).reshape(tokens, 48, 128), host(layer.gdn_norm_w), chain.EPS, centered=False,
+                                   gate=host(layer.z).reshape(tokens, 48, 128)).reshape(tokens, -1)
+    gpu_util.assert_bf16_within(host(layer.gated), gated_want, 1, 0.98, "gated norm")
+    c, s, _ = orc.nvfp4_quantize(host(layer.gated), CHUNK)
+    gpu_util.assert_bits_equal(host(layer.gated_codes), c, "codes")
+    gpu_util.assert_bits_equal(host(layer.gated_scales), s, "block scales")
+    assert bool(torch.isfinite(layer.mlp.down.float()).all().item())

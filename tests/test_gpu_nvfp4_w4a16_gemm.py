@@ -70,3 +70,42 @@ def test_w4a16_gemm_rejections(g):
     assert call(w=None) == inv
     assert call(out=fake) == inv
     assert call(t=0) == 0
+
+
+@pytest.mark.parametrize("tokens,n,k", [(200, 512, 5120), (130, 5120, 1024), (64, 48, 512)])
+def test_widened_nvfp4_weights_through_the_scaled_dense_gemm(g, tokens, n, k):
+    """An NVFP4 weight widened to bf16 once (code x block scale, exact) and multiplied on the dense path with the
+    second-level scale in the epilogue: the widened bytes equal the oracle's dequantisation at scale 1, the product
+    obeys the rule above, and nearly every output byte equals the weight-only kernel's (same products, FP32 sums in
+    another order)."""
+    rng = np.random.default_rng([tokens, n, k, 131])
+    x = fx.normal_bf16(rng, (tokens, k))
+    packed = rng.integers(0, 256, size=(n, k // 2), dtype=np.uint8)
+    scales = rng.integers(0x08, 0x68, size=(n, k // 16), dtype=np.uint8)
+    scales[0, 0] |= 0x80  # a negative block scale
+    scale_2 = 0.004
+    d_p, d_s, d_x = g.Dev(packed), g.Dev(scales), g.Dev(x)
+    wide = g.empty_like_dev((n, k))
+    g.capi.check("q3x_b200_nvfp4_weights_to_bf16", d_p, d_s, n, k, wide, None)
+    g.sync()
+    unit = orc.nvfp4_dequantize(packed, scales, 1.0).astype(np.float32)
+    assert np.array_equal(orc.bf16_decode(wide.get()), unit), "code x block scale is exact in bf16"
+    out = g.empty_like_dev((tokens, n))
+    g.capi.check("q3x_b200_bf16_gemm_scaled_bf16", wide, scale_2, d_x, tokens, n, k, out, None, 0, None)
+    d_st = g.empty_like_dev((k // 16, n))
+    g.capi.check("q3x_b200_nvfp4_transpose_block_scales", d_s, n, k, d_st, None)
+    need = g.capi.lib().q3x_b200_nvfp4_w4a16_gemm_workspace_bytes(tokens, n, k)
+    ws, mixed = g.empty_like_dev((max(need, 256),), dtype=np.uint8), g.empty_like_dev((tokens, n))
+    g.capi.check("q3x_b200_nvfp4_w4a16_gemm_bf16", d_p, d_st, scale_2, d_x, tokens, n, k, mixed, ws, need, None)
+    g.sync()
+    deq, xf = unit.astype(np.float64) * scale_2, orc.bf16_decode(x).astype(np.float64)
+    want, mag = xf @ deq.T, np.abs(xf) @ np.abs(deq).T
+    got = orc.bf16_decode(out.get()).astype(np.float64)
+    assert np.all(np.abs(got - want) <= 2.0 ** -8 * np.abs(want) + 1e-5 * mag + 1e-30)
+    assert np.mean(out.get() == mixed.get()) > 0.97
+    assert out.guards_intact() and wide.guards_intact()
+    inv, fake = g.capi.CUDA_ERROR_INVALID_VALUE, 0x10000000
+    assert g.capi.call("q3x_b200_nvfp4_weights_to_bf16", fake, fake + (1 << 24), 8, 24, fake + (2 << 24), None) == inv
+    assert g.capi.call("q3x_b200_nvfp4_weights_to_bf16", fake, fake + (1 << 24), 8, 32, fake + 64, None) == inv
+    assert g.capi.call("q3x_b200_nvfp4_weights_to_bf16", fake, None, 8, 32, fake + (2 << 24), None) == inv
+    assert g.capi.call("q3x_b200_nvfp4_weights_to_bf16", fake, fake + (1 << 24), 0, 32, fake + (2 << 24), None) == 0

@@ -57,7 +57,7 @@ def test_mirror_defines_the_reference_symbols(host_lib, tmp_path):
     subprocess.run(cmd, check=True, capture_output=True, text=True)
     out = subprocess.run([exe], capture_output=True, text=True)
     assert out.returncode == 0, out.stdout + out.stderr
-    assert "68 reference launcher symbols resolved" in out.stdout
+    assert "71 reference launcher symbols resolved" in out.stdout
 
 
 @pytest.mark.skipif(not HAVE_REFERENCE, reason="no reference checkout")
