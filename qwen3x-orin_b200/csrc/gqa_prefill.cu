@@ -14,6 +14,8 @@
 // an ldmatrix fall into different banks.  The causal mask only touches tiles that reach past the block's first
 // token.  The epilogue normalises, rounds, applies the gate, and leaves through shared memory as 128-bit stores.
 // (The host reference keeps the probabilities in FP32; here each one meets V as a pair of bf16 operands, see below.)
+#include <cstdlib>
+
 #include "device_utils.cuh"
 #include "host_checks.hpp"
 #include "q3x_b200.h"
@@ -24,13 +26,22 @@ namespace {
 constexpr int kQHeads = 24, kKvHeads = 4, kDim = 256, kGroup = kQHeads / kKvHeads;
 constexpr int kBlockTokens = 16;                 // query tokens per CTA (one MMA row block per warp)
 constexpr int kTileKeys = 64;                    // keys per pipeline stage
-constexpr int kWarps = kGroup;                   // one warp per query head of the KV group
-constexpr int kThreads = kWarps * 32;
+// Two shapes of CTA.  Narrow: 6 warps = the 6 query heads of a KV group over one 16-token block (a K / V tile serves
+// 96 query rows).  Wide: 8 warps = 8 consecutive 16-token blocks of ONE query head (128 query rows per tile): two warps
+// on each of the SM's four schedulers instead of two on two and one on two, which is what bounds the narrow shape on
+// long tiles; the 6 heads of a group then read the same K / V tiles from L2 in 6 CTAs.
+template <bool kWide>
+struct Shape {
+  static constexpr int kWarps = kWide ? 8 : kGroup;
+  static constexpr int kThreads = kWarps * 32;
+  static constexpr int kCtaTokens = kWide ? kWarps * kBlockTokens : kBlockTokens;
+  static constexpr size_t kQBytes = static_cast<size_t>(kWarps) * kBlockTokens * kDim * 2;  // 48 / 64 KB
+};
 constexpr int kRowChunks = kDim * 2 / 16;        // 16-byte chunks in one 256-element bf16 row (32)
 constexpr int kStages = 2;
-constexpr size_t kQBytes = static_cast<size_t>(kWarps) * kBlockTokens * kDim * 2;   // 48 KB
 constexpr size_t kTileBytes = static_cast<size_t>(kTileKeys) * kDim * 2;            // 32 KB
-constexpr size_t kSharedBytes = kQBytes + 2 * kStages * kTileBytes;                 // 176 KB
+template <bool kWide>
+constexpr size_t shared_bytes() { return Shape<kWide>::kQBytes + 2 * kStages * kTileBytes; }  // 176 / 192 KB
 
 // byte offset of 16-byte chunk `chunk` of row `row` inside a [rows, 256] bf16 tile
 __device__ __forceinline__ uint32_t swizzled(int row, int chunk) {
@@ -68,8 +79,8 @@ __device__ __forceinline__ float exp2_approx(float x) {
 
 // Requests one K and one V tile (keys [first_key, first_key + 64) of KV head `kv`) into a stage.
 __device__ __forceinline__ void request_tile(const uint16_t* key_cache, const uint16_t* value_cache, int kv,
-                                             size_t first_key, size_t keys, uint32_t k_smem, uint32_t v_smem) {
-  for (int i = threadIdx.x; i < kTileKeys * kRowChunks; i += kThreads) {
+                                             size_t first_key, size_t keys, uint32_t k_smem, uint32_t v_smem, int threads) {
+  for (int i = threadIdx.x; i < kTileKeys * kRowChunks; i += threads) {
     const int row = i / kRowChunks, chunk = i % kRowChunks;
     const size_t key = first_key + row;
     const bool valid = key < keys;
@@ -79,7 +90,8 @@ __device__ __forceinline__ void request_tile(const uint16_t* key_cache, const ui
   }
 }
 
-__global__ void __launch_bounds__(kThreads, 1) gqa_prefill_kernel(const uint16_t* __restrict__ query,
+template <bool kWide>
+__global__ void __launch_bounds__(Shape<kWide>::kThreads, 1) gqa_prefill_kernel(const uint16_t* __restrict__ query,
                                                                   const uint16_t* __restrict__ key_cache,
                                                                   const uint16_t* __restrict__ value_cache,
                                                                   const uint16_t* __restrict__ gate, size_t first_position,
@@ -88,11 +100,19 @@ __global__ void __launch_bounds__(kThreads, 1) gqa_prefill_kernel(const uint16_t
   extern __shared__ __align__(128) unsigned char shared[];
   const uint32_t smem = static_cast<uint32_t>(__cvta_generic_to_shared(shared));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-  const int kv = blockIdx.y, head = kv * kGroup + warp;
+  constexpr int kThreads = Shape<kWide>::kThreads;
+  constexpr size_t kQBytes = Shape<kWide>::kQBytes;
+  const int head = kWide ? static_cast<int>(blockIdx.y) : static_cast<int>(blockIdx.y) * kGroup + warp;
+  const int kv = head / kGroup;
   // the last blocks of a tile see the most keys: they are scheduled first, so that the short ones fill the tail
-  const size_t token0 = static_cast<size_t>(gridDim.x - 1 - blockIdx.x) * kBlockTokens;
-  const size_t keys = first_position + min(token0 + kBlockTokens, tokens);  // keys visible to the block's last token
+  const size_t cta_token0 = static_cast<size_t>(gridDim.x - 1 - blockIdx.x) * Shape<kWide>::kCtaTokens;
+  const size_t token0 = kWide ? cta_token0 + static_cast<size_t>(warp) * kBlockTokens : cta_token0;  // this warp's block
+  // keys visible to the CTA's last token: the tiles every warp helps to fetch
+  const size_t keys = first_position + min(cta_token0 + Shape<kWide>::kCtaTokens, tokens);
   const int tiles = static_cast<int>((keys + kTileKeys - 1) / kTileKeys);
+  // ... and to this warp's last token: the tiles it computes on (none for a block wholly past the tile's end)
+  const size_t own_keys = token0 < tokens ? first_position + min(token0 + kBlockTokens, tokens) : 0;
+  const int own_tiles = static_cast<int>((own_keys + kTileKeys - 1) / kTileKeys);
   const uint32_t q_smem = smem + warp * (kBlockTokens * kDim * 2);
   auto k_stage = [&](int s) { return smem + static_cast<uint32_t>(kQBytes + (2 * s) * kTileBytes); };
   auto v_stage = [&](int s) { return smem + static_cast<uint32_t>(kQBytes + (2 * s + 1) * kTileBytes); };
@@ -104,7 +124,7 @@ __global__ void __launch_bounds__(kThreads, 1) gqa_prefill_kernel(const uint16_t
     const bool valid = token < tokens;
     cp_async_16(q_smem + swizzled(row, chunk), query + ((valid ? token : 0) * kQHeads + head) * kDim + chunk * 8, valid);
   }
-  request_tile(key_cache, value_cache, kv, 0, keys, k_stage(0), v_stage(0));
+  request_tile(key_cache, value_cache, kv, 0, keys, k_stage(0), v_stage(0), kThreads);
   cp_async_commit();
 
   float o[kDim / 8][4];
@@ -118,10 +138,11 @@ __global__ void __launch_bounds__(kThreads, 1) gqa_prefill_kernel(const uint16_t
     const int stage = tile & 1;
     if (tile + 1 < tiles)
       request_tile(key_cache, value_cache, kv, static_cast<size_t>(tile + 1) * kTileKeys, keys, k_stage(stage ^ 1),
-                   v_stage(stage ^ 1));
+                   v_stage(stage ^ 1), kThreads);
     cp_async_commit();
     cp_async_wait<1>();  // everything but the newest group: this tile (and the queries) has landed
     __syncthreads();
+    if (tile < own_tiles) {  // (warp-uniform) a warp whose block ends before this tile only helps to fetch it
 
     // ---- S = Q K^T: 16 rows x 64 keys, 8 column blocks of 8 keys
     float s[kTileKeys / 8][4];
@@ -213,6 +234,7 @@ __global__ void __launch_bounds__(kThreads, 1) gqa_prefill_kernel(const uint16_t
         mma_bf16(o[2 * n2 + 1], lo, b[2], b[3]);
       }
     }
+    }  // tile < own_tiles
     __syncthreads();  // the stage is requested again two iterations from now
   }
   cp_async_wait<0>();
@@ -280,16 +302,35 @@ extern "C" int q3x_b200_gqa_attention_prefill_sigmoid_gate(const uint16_t* query
   if (!aligned16(query) || !aligned16(key_cache) || !aligned16(value_cache) || !aligned16(out) ||
       (gate != nullptr && !aligned16(gate)))
     return kNotSupported;
-  const size_t blocks = (tokens + kBlockTokens - 1) / kBlockTokens;
-  if (blocks > 0x7fffffffu) return kNotSupported;
+  if (tokens / kBlockTokens + 1 > 0x7fffffffu) return kNotSupported;
   clear_stale_error();
-  static const cudaError_t attribute = cudaFuncSetAttribute(gqa_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                            static_cast<int>(kSharedBytes));
+  static const cudaError_t attribute = [] {
+    cudaError_t e = cudaFuncSetAttribute(gqa_prefill_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(shared_bytes<false>()));
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(gqa_prefill_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(shared_bytes<true>()));
+    return e;
+  }();
   if (attribute != cudaSuccess) {
     (void)cudaGetLastError();
     return static_cast<int>(attribute);
   }
-  gqa_prefill_kernel<<<dim3(static_cast<unsigned>(blocks), kKvHeads), kThreads, kSharedBytes, as_stream(stream)>>>(
-      query, key_cache, value_cache, gate, first_position, tokens, scale * 1.4426950408889634f, out);
+  const float scale_log2e = scale * 1.4426950408889634f;
+  // the wide shape from the length at which its 24 x blocks CTAs fill the SMs; short tiles keep the narrow one
+  // (Q3X_B200_GQA_WIDE_FROM moves the boundary, for measurements)
+  static const size_t wide_from = [] {
+    const char* text = std::getenv("Q3X_B200_GQA_WIDE_FROM");
+    return text != nullptr ? static_cast<size_t>(std::strtoull(text, nullptr, 10)) : static_cast<size_t>(1024);
+  }();
+  if (tokens >= wide_from) {
+    const unsigned blocks = static_cast<unsigned>((tokens + Shape<true>::kCtaTokens - 1) / Shape<true>::kCtaTokens);
+    gqa_prefill_kernel<true><<<dim3(blocks, kQHeads), Shape<true>::kThreads, shared_bytes<true>(), as_stream(stream)>>>(
+        query, key_cache, value_cache, gate, first_position, tokens, scale_log2e, out);
+  } else {
+    const unsigned blocks = static_cast<unsigned>((tokens + kBlockTokens - 1) / kBlockTokens);
+    gqa_prefill_kernel<false><<<dim3(blocks, kKvHeads), Shape<false>::kThreads, shared_bytes<false>(), as_stream(stream)>>>(
+        query, key_cache, value_cache, gate, first_position, tokens, scale_log2e, out);
+  }
   return launch_status();
 }

@@ -40,7 +40,9 @@ def expected(q, kc, vc, gate, first):
 
 @pytest.mark.parametrize("tokens,first,gated,sharp", [(2, 0, True, 1.0), (16, 0, False, 1.0), (40, 0, True, 1.0),
                                                        (37, 100, True, 1.0), (130, 63, True, 3.0), (512, 0, True, 1.0),
-                                                       (200, 512, True, 1.0), (64, 1000, False, 3.0)])
+                                                       (200, 512, True, 1.0), (64, 1000, False, 3.0),
+                                                       # 1024 tokens and more take the wide CTA shape (8 token blocks of one head)
+                                                       (1100, 0, True, 1.0), (1030, 77, False, 3.0)])
 def test_prefill_attention_matches_the_per_token_reference(g, tokens, first, gated, sharp):
     rng = np.random.default_rng([tokens, first, int(gated), 111])
     length = first + tokens
