@@ -41,7 +41,7 @@ def expected(q, kc, vc, gate, first):
 @pytest.mark.parametrize("tokens,first,gated,sharp", [(2, 0, True, 1.0), (16, 0, False, 1.0), (40, 0, True, 1.0),
                                                        (37, 100, True, 1.0), (130, 63, True, 3.0), (512, 0, True, 1.0),
                                                        (200, 512, True, 1.0), (64, 1000, False, 3.0),
-                                                       # 1024 tokens and more take the wide CTA shape (8 token blocks of one head)
+                                                       # (tiles longer than the reference's 512)
                                                        (1100, 0, True, 1.0), (1030, 77, False, 3.0)])
 def test_prefill_attention_matches_the_per_token_reference(g, tokens, first, gated, sharp):
     rng = np.random.default_rng([tokens, first, int(gated), 111])
@@ -65,6 +65,30 @@ def test_prefill_attention_matches_the_per_token_reference(g, tokens, first, gat
     # of a value at the bottom of its binade (3.9e-3 at 0.48 against 8e-3 x 0.48 = 3.87e-3; about one element in a
     # million): there the rule is the quota form (at most 2 per 100 000 outside it, two ulps of the row as the bound).
     g.assert_reference_tolerance(got, want, "prefill attention", amplified=gated)
+
+
+def test_prefill_attention_of_a_long_tile_on_sampled_tokens(g):
+    """Tiles of 4096 tokens and more run in the wide CTA shape (eight 16-token blocks of one query head per CTA): a
+    4133-token tile appended at position 50 (the last CTA holds 37 tokens: two full blocks, a partial one and five idle
+    warps), checked against the per-token oracle on sampled tokens, block edges and the tile's two ends."""
+    rng = np.random.default_rng(119)
+    tokens, first = 4133, 50
+    length = first + tokens
+    q = fx.normal_bf16(rng, (tokens, 24, 256))
+    kc, vc = fx.normal_bf16(rng, (length, 4, 256)), fx.normal_bf16(rng, (length, 4, 256))
+    gate = fx.normal_bf16(rng, (tokens, 24, 256), 2.0)
+    out = g.empty_like_dev((tokens, 24, 256))
+    g.capi.check("q3x_b200_gqa_attention_prefill_sigmoid_gate", g.Dev(q), g.Dev(kc), g.Dev(vc), g.Dev(gate), first, tokens,
+                 SCALE, out, None)
+    g.sync()
+    assert out.guards_intact()
+    picks = sorted(set([0, 1, 15, 16, 127, 128, 129, 2047, 2048, 4095, 4096, 4111, 4112, 4127, 4128, 4131, 4132]) |
+                   set(int(t) for t in rng.choice(tokens, size=48, replace=False)))
+    got = out.get()[picks]
+    want = np.stack([orc.gqa_attention(q[t], kc[:first + t + 1], vc[:first + t + 1], SCALE, gate=gate[t])[0] for t in picks])
+    g.assert_sum_within(got, want, 3, 1e-5, 0.98, "prefill attention, long tile")
+    g.assert_reference_tolerance(got, want, "prefill attention, long tile", amplified=True)
+    assert bool(np.isfinite(orc.bf16_decode(out.get())).all())
 
 
 def test_prefill_attention_equals_decode_attention_on_its_last_token(g):
