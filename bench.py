@@ -636,8 +636,7 @@ def probe_projection_ops(cuda_index=0, aim_ms=60.0, tokens=8192):
                      "sm_mhz": clk.get("sm_mhz"), "reasons": clk.get("reasons")}
         del a_codes, w_codes, a_scales, w_scales, ws, y
     # bulk causal attention of a 512-token tile appended at positions 0, 8192 and 65536 (one layer's cache)
-    for first in (0, 8192, 65536):
-        tile = 512
+    for first, tile in ((0, 512), (8192, 512), (65536, 512), (0, 8192)):  # the last one runs in the wide CTA shape
         length = first + tile
         q = torch.randn((tile, 24, 256), generator=gen, device=dev, dtype=torch.float32).to(torch.bfloat16)
         gate_t = torch.randn((tile, 24, 256), generator=gen, device=dev, dtype=torch.float32).to(torch.bfloat16)
@@ -672,7 +671,7 @@ def probe_projection_ops(cuda_index=0, aim_ms=60.0, tokens=8192):
         # visible (query, key) pairs x 24 heads x 256 dims x 2 products x 2 flops
         pairs = tile * first + tile * (tile + 1) // 2
         tflops = 4.0 * pairs * 24 * 256 / (us * 1e-6) / 1e12
-        out[f"gqa_prefill_512_tokens_at_{first}"] = {"us": round(us, 1), "TFLOPs": round(tflops, 1),
+        out[f"gqa_prefill_{tile}_tokens_at_{first}"] = {"us": round(us, 1), "TFLOPs": round(tflops, 1),
                                                      "frac_of_measured_bf16_dense": round(tflops / bf16_peak, 3) if bf16_peak else None,
                                                      "sm_mhz": clk.get("sm_mhz")}
         del q, gate_t, kc, vc, y
