@@ -450,6 +450,14 @@ int q3x_b200_gated_delta_net_update_rms_norm_silu_gate(
  * least q3x_b200_gated_delta_net_chunked_workspace_bytes(tokens) bytes (about 2.4 MB per 64 tokens), 16-byte
  * aligned, disjoint from every operand; stale contents do not matter. */
 size_t q3x_b200_gated_delta_net_chunked_workspace_bytes(size_t tokens);
+/* The sequential half of the chunked form exists twice: path 0 keeps the state in the accumulators of mma.sync
+ * products (two CTAs per head; the default, the faster one today), path 1 keeps it in tensor memory and issues
+ * tcgen05 products from shared-memory descriptors (one CTA per head).  Same operands, same roundings, sums in another
+ * order.  Process-wide switch (initially from the environment variable Q3X_B200_GDN_CHUNK_PATH = "tcgen05");
+ * cudaErrorInvalidValue for any other value.  The last 256 bytes of the workspace hold a word that path 1 raises
+ * when one of its bounded waits on the tensor cores runs out (the results of that call are then invalid); every call
+ * of path 1 clears it first. */
+int q3x_b200_gated_delta_net_chunked_select_path(int path);
 int q3x_b200_gated_delta_net_update_chunked(const uint16_t* conv_qkv, size_t tokens, const uint16_t* a,
                                             const uint16_t* b, const uint16_t* A_log, const uint16_t* dt_bias,
                                             const uint16_t* state_in, uint16_t* state_out, float l2_eps,

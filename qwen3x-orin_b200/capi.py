@@ -78,6 +78,7 @@ SIGNATURES = {
     "q3x_b200_nvfp4_gemv": (_i, [_p, _p, _f, _p, _z, _z, _p, _p, _p]),
     "q3x_b200_gated_delta_net_update": (_i, [_p, _z, _p, _p, _p, _p, _p, _p, _f, _p, _p]),
     "q3x_b200_gated_delta_net_chunked_workspace_bytes": (_z, [_z]),
+    "q3x_b200_gated_delta_net_chunked_select_path": (_i, [_i]),
     "q3x_b200_gated_delta_net_update_chunked": (_i, [_p, _z, _p, _p, _p, _p, _p, _p, _f, _p, _p, _z, _p]),
     "q3x_b200_gated_delta_net_update_rms_norm_silu_gate": (_i, [_p, _z, _p, _p, _p, _p, _p, _p, _f, _p, _p, _f, _p, _p]),
     "q3x_b200_gqa_decode_workspace_floats": (_z, [_z]),

@@ -18,6 +18,10 @@
 // Against the token-sequential form, which rounds the state to bf16 after every token, results agree to the noise of
 // that rounding, not bit for bit (the reference reports the same comparison as a characterisation, tests/
 // reference_gdn_prefill_chunk64_reference_engine_e2e_test.cpp:1990-2080).
+#include <atomic>
+#include <cstdlib>
+#include <string>
+
 #include "device_utils.cuh"
 #include "host_checks.hpp"
 #include "q3x_b200.h"
@@ -35,8 +39,11 @@ constexpr int kChunk = 64;
 
 // ---- workspace: per chunk, images that the second kernel copies into shared memory as they are -------------------
 // (16-byte pieces of a row are permuted by the row's low three bits, so that ldmatrix reads them without conflicts)
-constexpr size_t kQkTile = static_cast<size_t>(kChunk) * kHead * 2;   // [64 tokens][128] bf16, 256-byte rows
-constexpr size_t kWTile = static_cast<size_t>(kHead) * kChunk * 2;    // [128 columns][64 tokens] bf16, 128-byte rows
+// All images have 128-byte rows (64 bf16): a [rows][128] operand is two blocks of [rows][64], the second `rows` x 128
+// bytes after the first -- the layout a tensor-core shared-memory descriptor with 128-byte swizzling names directly.
+constexpr size_t kQkTile = static_cast<size_t>(kChunk) * kHead * 2;   // q, W: [64 tokens][128 key dims] in two blocks;
+                                                                      // k transposed: [128 key dims][64 tokens]
+constexpr size_t kWTile = static_cast<size_t>(kHead) * kChunk * 2;    // U transposed: [128 value rows][64 tokens]
 constexpr size_t kPTile = static_cast<size_t>(kChunk) * kChunk * 2;   // [64][64] bf16, 128-byte rows
 constexpr size_t kDecayTile = 2 * kChunk * sizeof(float);             // G_t and G_64 / G_t
 constexpr size_t kChunkBytes = 2 * kKeyHeads * kQkTile + kValueHeads * (2 * kWTile + kPTile + kDecayTile);
@@ -67,6 +74,10 @@ struct Workspace {
 __device__ __forceinline__ uint32_t image(int row, int piece, int pitch) {
   return static_cast<uint32_t>(row * pitch + ((piece ^ (row & 7)) << 4));
 }
+// ... and of piece `piece` (0 .. 15, eight columns each) of row `row` of a [64][128] operand in two blocks
+__device__ __forceinline__ uint32_t blocked(int row, int piece) {
+  return static_cast<uint32_t>((piece >> 3) * (kChunk * 128)) + image(row, piece & 7, 128);
+}
 
 __device__ __forceinline__ void cp_async_16(uint32_t smem, const void* global) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem), "l"(global) : "memory");
@@ -75,11 +86,6 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-               : "r"(addr));
-}
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
                : "r"(addr));
 }
@@ -159,7 +165,6 @@ __global__ void __launch_bounds__(kPrepThreads, 3) gdn_chunk_prepare_kernel(
     const int piece = tid & 15;
     const float inv_sqrt_dim = __fdiv_rn(1.0f, sqrtf(static_cast<float>(kHead)));
     unsigned char* q_image = ws.q(chunk, key_head);
-    unsigned char* k_image = ws.k(chunk, key_head);
 #pragma unroll
     for (int pass = 0; pass < kChunk / 8; ++pass) {
       const int row = pass * 8 + (tid >> 4);
@@ -179,10 +184,7 @@ __global__ void __launch_bounds__(kPrepThreads, 3) gdn_chunk_prepare_kernel(
       const uint32_t at = image(row, piece, kHead * 2);
       *reinterpret_cast<uint4*>(sh.q + at) = qp;
       *reinterpret_cast<uint4*>(sh.k + at) = kp;
-      if (publishes_qk) {
-        st_vec(q_image + at, qp);
-        st_vec(k_image + at, kp);
-      }
+      if (publishes_qk) st_vec(q_image + blocked(row, piece), qp);  // (k leaves transposed, from the solve's prologue)
     }
   }
   // ---- the head's gates: warp 0, two tokens per lane, a scan over the log-decays
@@ -269,9 +271,22 @@ __global__ void __launch_bounds__(kPrepThreads, 3) gdn_chunk_prepare_kernel(
   {
     const int piece = tid >> 3, within = tid & 7;
 #pragma unroll
+    for (int t = 0; t < kChunk; ++t)
+      xw[t] = bf16_to_float(*reinterpret_cast<const uint16_t*>(sh.k + image(t, piece, kHead * 2) + within * 2));
+    if (publishes_qk) {  // this thread's key dimension over the 64 tokens: one 128-byte row of the transposed k image
+      unsigned char* k_image = ws.k(chunk, key_head);
+#pragma unroll
+      for (int p8 = 0; p8 < kChunk / 8; ++p8) {
+        float eight[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) eight[e] = xw[p8 * 8 + e];
+        st_vec(k_image + image(tid, p8, kChunk * 2), pack8(eight));  // (bf16 values: the packing is exact)
+      }
+    }
+#pragma unroll
     for (int t = 0; t < kChunk; ++t) {
       const float scale = sh.beta[t];
-      xw[t] = scale * sh.growth[t] * bf16_to_float(*reinterpret_cast<const uint16_t*>(sh.k + image(t, piece, kHead * 2) + within * 2));
+      xw[t] *= scale * sh.growth[t];
       xu[t] = scale * bf16_to_float(sh.v[t][tid]);
     }
   }
@@ -297,19 +312,24 @@ __global__ void __launch_bounds__(kPrepThreads, 3) gdn_chunk_prepare_kernel(
       xu[t4 * 4 + 3] = u23.y;
     }
   }
-  // column c of W (of U) is row c of its transposed image: 128 contiguous bytes, pieces permuted by the row
-  unsigned char* w_image = ws.w(chunk, head);
+  // column c of U is row c of its transposed image: 128 contiguous bytes, pieces permuted by the row
   unsigned char* u_image = ws.u(chunk, head);
 #pragma unroll
   for (int piece = 0; piece < kChunk / 8; ++piece) {
     float eight[8];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) eight[e] = xw[piece * 8 + e];
-    st_vec(w_image + image(tid, piece, kChunk * 2), pack8(eight));
-#pragma unroll
     for (int e = 0; e < 8; ++e) eight[e] = xu[piece * 8 + e];
     st_vec(u_image + image(tid, piece, kChunk * 2), pack8(eight));
   }
+  // W leaves token-major ([token][key dim] in two blocks, the B operand of S W^T with the key dimension contiguous):
+  // transposed through the shared memory that held q (every warp is past the Gram products), then 16 bytes a thread
+#pragma unroll
+  for (int t = 0; t < kChunk; ++t)
+    *reinterpret_cast<uint16_t*>(sh.q + blocked(t, tid >> 3) + (tid & 7) * 2) = float_to_bf16(xw[t]);
+  __syncthreads();
+  unsigned char* w_image = ws.w(chunk, head);
+  for (int i = tid; i < static_cast<int>(kQkTile / 16); i += kPrepThreads)
+    st_vec(w_image + i * 16, *reinterpret_cast<const uint4*>(sh.q + i * 16));
 }
 
 // ================================================================================================================
@@ -403,12 +423,13 @@ __global__ void __launch_bounds__(kStateThreads, 1) gdn_chunk_state_kernel(Works
 #pragma unroll
       for (int n2 = 0; n2 < kChunk / 16; ++n2) {
         uint32_t bw[4], bq[4];
-        // W^T image: rows are key dimensions (the product's k), 16-byte pieces are 8 tokens (its n): transposed loads
-        ldmatrix_x4_trans(bw, stage + kStageW + image(step * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, n2 * 2 + (lane >> 4), kChunk * 2));
+        // W and Q images: rows are tokens (the product's n), pieces are 8 key dimensions (its k), 64 per block
+        ldmatrix_x4(bw, stage + kStageW + (step >> 2) * (kChunk * 128) +
+                            image(n2 * 16 + (lane & 7) + (lane >> 4) * 8, (step & 3) * 2 + ((lane >> 3) & 1), 128));
         mma_bf16(pred[2 * n2], sa[step], bw[0], bw[1]);
         mma_bf16(pred[2 * n2 + 1], sa[step], bw[2], bw[3]);
-        // Q image: rows are tokens (n), pieces are 8 key dimensions (k): plain loads
-        ldmatrix_x4(bq, stage + kStageQ + image(n2 * 16 + (lane & 7) + (lane >> 4) * 8, step * 2 + ((lane >> 3) & 1), kHead * 2));
+        ldmatrix_x4(bq, stage + kStageQ + (step >> 2) * (kChunk * 128) +
+                            image(n2 * 16 + (lane & 7) + (lane >> 4) * 8, (step & 3) * 2 + ((lane >> 3) & 1), 128));
         mma_bf16(o[2 * n2], sa[step], bq[0], bq[1]);
         mma_bf16(o[2 * n2 + 1], sa[step], bq[2], bq[3]);
       }
@@ -447,7 +468,7 @@ __global__ void __launch_bounds__(kStateThreads, 1) gdn_chunk_state_kernel(Works
         mma_bf16(o[2 * n2 + 1], da[step], bp[2], bp[3]);
       }
     }
-    // ---- S^T <- G_64 S^T + (D^T diag(G_64 / G)) K  (K image: rows are tokens (k), pieces 8 key dimensions (n))
+    // ---- S^T <- G_64 S^T + (D^T diag(G_64 / G)) K  (transposed K image: rows are key dimensions (n), pieces 8 tokens (k))
     {
       const float whole = growth[kChunk - 1];
 #pragma unroll
@@ -460,7 +481,7 @@ __global__ void __launch_bounds__(kStateThreads, 1) gdn_chunk_state_kernel(Works
 #pragma unroll
       for (int n2 = 0; n2 < kHead / 16; ++n2) {
         uint32_t bk[4];
-        ldmatrix_x4_trans(bk, stage + kStageK + image(step * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, n2 * 2 + (lane >> 4), kHead * 2));
+        ldmatrix_x4(bk, stage + kStageK + image(n2 * 16 + (lane & 7) + (lane >> 4) * 8, step * 2 + ((lane >> 3) & 1), kChunk * 2));
         mma_bf16(S[2 * n2], ds[step], bk[0], bk[1]);
         mma_bf16(S[2 * n2 + 1], ds[step], bk[2], bk[3]);
       }
@@ -500,7 +521,296 @@ __global__ void __launch_bounds__(kStateThreads, 1) gdn_chunk_state_kernel(Works
   }
 }
 
+// ================================================================================================================
+// The sequential path on the fifth-generation tensor cores (tcgen05): one CTA of 128 threads per value head.  The
+// state S^T [128 value rows x 128 key dimensions] lives in tensor memory as FP32 for the whole call, thread r owning
+// value row r (tensor-memory lane r).  Per chunk:
+//   1. every thread reads its row of S, leaves it in shared memory as the bf16 A operand of this chunk's products and
+//      writes G_64 S back (the decayed state the chunk's update accumulates onto);
+//   2. one thread issues  pred^T = S W^T  and  o1^T = S Q^T  (M 128, N 64, K 128 each);
+//   3. every thread reads its row of pred, forms D^T = U^T - pred^T, and leaves D and its decayed copy in shared memory
+//      as bf16 A operands;
+//   4. one thread issues  o2^T = D P^T  (N 64, K 64)  and  S^T += (D diag(G_64 / G)) K  (N 128, K 64);
+//   5. every thread reads its rows of o1 and o2, o = o1 G_t + o2, and the chunk's outputs leave through shared memory.
+// The B operands are the workspace images as they are (rows of 64 bf16, 16-byte pieces permuted by the row = the
+// 128-byte swizzle of a shared-memory matrix descriptor), copied into a two-stage ring by cp.async.  Every wait on
+// the MMA barrier is bounded; if one runs out the CTA raises the workspace's error word, frees its tensor memory and
+// returns.
+// ================================================================================================================
+namespace tc {
+// 128 value rows x kParts: thread (row, part) owns a quarter of its row's columns in every per-row pass, so that a
+// scheduler has four warps to overlap (warps w and w + 4k read the same 32 tensor-memory lanes)
+constexpr int kParts = 4;
+constexpr int kThreads = 128 * kParts;
+// tensor-memory columns (FP32): the state, pred (whose columns o2 takes once every thread has read pred), o1
+constexpr uint32_t kColumnsS = 0, kColumnsPred = 128, kColumnsO1 = 192, kColumnsO2 = kColumnsPred, kColumnsAllocated = 256;
+constexpr size_t kOperandS = 0;                          // [128][128] bf16 in two blocks of [128][64]: 32 KB
+constexpr size_t kOperandD = kOperandS + 32768;          // [128][64] bf16: 16 KB (and the output tile afterwards)
+constexpr size_t kOperandDecayed = kOperandD + 16384;    // 16 KB
+constexpr size_t kStages = kOperandDecayed + 16384;
+constexpr size_t kInW = 0, kInQ = kInW + kQkTile, kInK = kInQ + kQkTile, kInP = kInK + kQkTile, kInU = kInP + kPTile,
+                 kInDecay = kInU + kWTile, kStageBytes = (kInDecay + kDecayTile + 1023) / 1024 * 1024;
+constexpr size_t kBarrier = kStages + 2 * kStageBytes;   // the MMA barrier (8 bytes), the tensor-memory base (4)
+constexpr size_t kShared = kBarrier + 64;
+static_assert(kShared <= 227 * 1024, "one CTA per SM");
+constexpr uint32_t kWaitLimit = 1u << 20;
+
+// K-major operand of 64-element (128-byte) rows, 128-byte swizzle, groups of eight rows 1024 bytes apart
+__device__ __forceinline__ uint64_t operand_descriptor(uint32_t shared_address) {
+  return static_cast<uint64_t>((shared_address & 0x3ffffu) >> 4) | (static_cast<uint64_t>(1) << 16) |
+         (static_cast<uint64_t>(1024 >> 4) << 32) | (static_cast<uint64_t>(1) << 46) | (static_cast<uint64_t>(2) << 61);
+}
+// bf16 x bf16 -> FP32, M = 128, N = n, both operands K-major
+__host__ __device__ constexpr uint32_t instruction_descriptor(int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
+}
+__device__ __forceinline__ void mma(uint32_t accumulator, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(accumulator),
+      "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// D[128, n] (+)= A[128, k] B[n, k]^T: 16 elements of k per instruction; 64 per block of either operand
+__device__ __forceinline__ void product(uint32_t accumulator, uint32_t a_base, uint32_t a_block_bytes, uint32_t b_base,
+                                        uint32_t b_block_bytes, int k, uint32_t idesc, bool accumulate) {
+  for (int step = 0; step < k / 16; ++step) {
+    const uint32_t block = step >> 2, inside = (step & 3) * 32;
+    mma(accumulator, operand_descriptor(a_base + block * a_block_bytes + inside),
+        operand_descriptor(b_base + block * b_block_bytes + inside), idesc, (accumulate || step > 0) ? 1u : 0u);
+  }
+}
+__device__ __forceinline__ void commit(uint32_t barrier) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(barrier) : "memory");
+}
+__device__ __forceinline__ bool wait(uint32_t barrier, uint32_t parity) {
+  for (uint32_t spin = 0; spin < kWaitLimit; ++spin) {
+    uint32_t done;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(done)
+                 : "r"(barrier), "r"(parity)
+                 : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ void fence_async_proxy() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void request_chunk(const Workspace& ws, size_t chunk, int head, uint32_t stage) {
+  auto copy = [&](size_t at, const unsigned char* from, size_t bytes) {
+    for (size_t i = static_cast<size_t>(threadIdx.x) * 16; i < bytes; i += static_cast<size_t>(kThreads) * 16)
+      cp_async_16(stage + static_cast<uint32_t>(at + i), from + i);
+  };
+  copy(kInW, ws.w(chunk, head), kQkTile);
+  copy(kInQ, ws.q(chunk, head / (kValueHeads / kKeyHeads)), kQkTile);
+  copy(kInK, ws.k(chunk, head / (kValueHeads / kKeyHeads)), kQkTile);
+  copy(kInP, ws.p(chunk, head), kPTile);
+  copy(kInU, ws.u(chunk, head), kWTile);
+  copy(kInDecay, ws.decay(chunk, head), kDecayTile);
+}
+
+// n consecutive columns of this thread's lane (the loads are waited for by the caller, so that several can be in flight)
+__device__ __forceinline__ void load16(uint32_t address, uint32_t (&r)[16]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+               : "r"(address)
+               : "memory");
+}
+__device__ __forceinline__ void load32(uint32_t address, uint32_t (&r)[32]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+               : "r"(address)
+               : "memory");
+}
+__device__ __forceinline__ void store32(uint32_t address, const uint32_t (&r)[32]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(address), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]) : "memory");
+}
+__device__ __forceinline__ void wait_loads() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void wait_stores() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+__global__ void __launch_bounds__(kThreads, 1) gdn_chunk_state_tcgen05_kernel(Workspace ws, size_t tokens,
+                                                                              const uint16_t* state_in, uint16_t* state_out,
+                                                                              uint16_t* __restrict__ out, uint32_t* error_word) {
+  extern __shared__ __align__(1024) unsigned char shared[];
+  const uint32_t smem = static_cast<uint32_t>(__cvta_generic_to_shared(shared));
+  const int head = blockIdx.x, row = threadIdx.x & 127, part = threadIdx.x >> 7, warp = threadIdx.x >> 5;
+  const uint32_t barrier = smem + static_cast<uint32_t>(kBarrier);
+  volatile uint32_t* base_slot = reinterpret_cast<volatile uint32_t*>(shared + kBarrier + 16);
+
+  request_chunk(ws, 0, head, smem + static_cast<uint32_t>(kStages));
+  cp_async_commit();
+  if (threadIdx.x == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(barrier) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem + static_cast<uint32_t>(kBarrier + 16)),
+                 "r"(kColumnsAllocated)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tmem = *base_slot;
+  const uint32_t lane_base = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);  // this warp's 32 lanes
+  constexpr int kStateColumns = kHead / kParts;   // 32 key dimensions of the state per thread
+  constexpr int kTokenColumns = kChunk / kParts;  // 16 tokens of pred / o per thread
+
+  // ---- the state enters tensor memory: thread (r, p) brings key dimensions 32p .. 32p + 31 of value row r
+  {
+    const uint16_t* source = state_in + (static_cast<size_t>(head) * kHead + row) * kHead + part * kStateColumns;
+    uint32_t r[32];
+#pragma unroll
+    for (int piece = 0; piece < 4; ++piece) {
+      float f[8];
+      unpack8(ld_vec(source + piece * 8), f);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) r[piece * 8 + e] = __float_as_uint(f[e]);
+    }
+    store32(lane_base + kColumnsS + part * kStateColumns, r);
+    wait_stores();
+  }
+
+  uint32_t parity = 0;
+  bool healthy = true;
+  for (size_t chunk = 0; chunk < ws.chunks; ++chunk) {
+    const size_t stage_at = kStages + (chunk & 1) * kStageBytes;
+    const uint32_t stage = smem + static_cast<uint32_t>(stage_at);
+    const float* growth = reinterpret_cast<const float*>(shared + stage_at + kInDecay);  // G_t
+    const float* to_end = growth + kChunk;                                               // G_64 / G_t
+    cp_async_wait_all();
+    fence_async_proxy();  // the copies were generic-proxy writes; the tensor core reads through the async proxy
+    __syncthreads();      // this chunk's operands are in place; everybody is done with the other stage
+    if (chunk + 1 < ws.chunks) request_chunk(ws, chunk + 1, head, smem + static_cast<uint32_t>(kStages + ((chunk + 1) & 1) * kStageBytes));
+    cp_async_commit();
+
+    // ---- 1. S as the bf16 A operand of this chunk's first products; they are issued before anything else happens
+    uint32_t s_part[32];
+    load32(lane_base + kColumnsS + part * kStateColumns, s_part);
+    wait_loads();
+#pragma unroll
+    for (int piece = 0; piece < 4; ++piece) {
+      float f[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(s_part[piece * 8 + e]);
+      *reinterpret_cast<uint4*>(shared + kOperandS + (part >> 1) * 16384 + image(row, (part & 1) * 4 + piece, 128)) = pack8(f);
+    }
+    fence_async_proxy();
+    fence_before_sync();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      fence_after_sync();
+      product(tmem + kColumnsPred, smem + kOperandS, 16384, stage + kInW, kChunk * 128, kHead, instruction_descriptor(kChunk), false);
+      commit(barrier);  // D needs pred only ...
+      product(tmem + kColumnsO1, smem + kOperandS, 16384, stage + kInQ, kChunk * 128, kHead, instruction_descriptor(kChunk),
+              false);  // ... o1 completes with the second commit of the chunk
+    }
+    // ---- underneath those products: G_64 S back to tensor memory (the update accumulates onto it)
+    {
+      const float whole = growth[kChunk - 1];
+#pragma unroll
+      for (int e = 0; e < 32; ++e) s_part[e] = __float_as_uint(__uint_as_float(s_part[e]) * whole);
+      store32(lane_base + kColumnsS + part * kStateColumns, s_part);
+      wait_stores();
+    }
+    healthy = __syncthreads_and(wait(barrier, parity)) != 0;  // pred
+    parity ^= 1;
+    if (!healthy) break;
+    fence_after_sync();
+    // ---- 2. D^T = U^T - pred^T and its decayed copy as bf16 A operands: tokens 16p .. 16p + 15 of row r
+    {
+      uint32_t r[16];
+      load16(lane_base + kColumnsPred + part * kTokenColumns, r);
+      wait_loads();
+#pragma unroll
+      for (int piece = 0; piece < 2; ++piece) {
+        float u[8], d[8], decayed[8];
+        unpack8(*reinterpret_cast<const uint4*>(shared + stage_at + kInU + image(row, part * 2 + piece, 128)), u);
+        const float4 e0 = *reinterpret_cast<const float4*>(to_end + part * kTokenColumns + piece * 8);
+        const float4 e1 = *reinterpret_cast<const float4*>(to_end + part * kTokenColumns + piece * 8 + 4);
+        const float factor[8] = {e0.x, e0.y, e0.z, e0.w, e1.x, e1.y, e1.z, e1.w};
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          d[e] = u[e] - __uint_as_float(r[piece * 8 + e]);
+          decayed[e] = d[e] * factor[e];
+        }
+        *reinterpret_cast<uint4*>(shared + kOperandD + image(row, part * 2 + piece, 128)) = pack8(d);
+        *reinterpret_cast<uint4*>(shared + kOperandDecayed + image(row, part * 2 + piece, 128)) = pack8(decayed);
+      }
+    }
+    fence_async_proxy();
+    fence_before_sync();
+    __syncthreads();
+    // ---- S^T += (D diag(G_64 / G)) K, o2^T = D P^T
+    if (threadIdx.x == 0) {
+      fence_after_sync();
+      product(tmem + kColumnsS, smem + kOperandDecayed, 0, stage + kInK, 0, kChunk, instruction_descriptor(kHead), true);
+      product(tmem + kColumnsO2, smem + kOperandD, 0, stage + kInP, 0, kChunk, instruction_descriptor(kChunk), false);
+      commit(barrier);
+    }
+    healthy = __syncthreads_and(wait(barrier, parity)) != 0;  // everything issued so far: the state, o1 and o2
+    parity ^= 1;
+    if (!healthy) break;
+    fence_after_sync();
+    // ---- 3. the chunk's outputs, o = o1 G_t + o2: tokens 16p .. 16p + 15 of value row r; the 32 rows of a warp make
+    // one 64-byte segment per token
+    {
+      uint32_t first[16], second[16];
+      load16(lane_base + kColumnsO1 + part * kTokenColumns, first);
+      load16(lane_base + kColumnsO2 + part * kTokenColumns, second);
+      wait_loads();
+      const size_t token0 = chunk * kChunk + part * kTokenColumns;
+      uint16_t* target = out + (token0 * kValueHeads + head) * kHead + row;
+#pragma unroll
+      for (int token = 0; token < kTokenColumns; ++token)
+        if (token0 + token < tokens)
+          target[static_cast<size_t>(token) * kValueHeads * kHead] = float_to_bf16(
+              fmaf(__uint_as_float(first[token]), growth[part * kTokenColumns + token], __uint_as_float(second[token])));
+    }
+    fence_before_sync();
+  }
+  cp_async_wait_all();
+  if (!healthy) {
+    if (threadIdx.x == 0) atomicExch(error_word, 1u);
+  } else {
+    fence_after_sync();
+    // ---- the state leaves as bf16, rounded once
+    uint16_t* target = state_out + (static_cast<size_t>(head) * kHead + row) * kHead + part * kStateColumns;
+    uint32_t r[32];
+    load32(lane_base + kColumnsS + part * kStateColumns, r);
+    wait_loads();
+#pragma unroll
+    for (int piece = 0; piece < 4; ++piece) {
+      float f[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[piece * 8 + e]);
+      st_vec(target + piece * 8, pack8(f));
+    }
+  }
+  fence_before_sync();
+  __syncthreads();
+  if (warp == 0)
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kColumnsAllocated) : "memory");
+}
+}  // namespace tc
+
 size_t chunks_of(size_t tokens) { return (tokens + kChunk - 1) / kChunk; }
+constexpr size_t kErrorSlot = 256;  // after the chunk images: a word a kernel raises when a bounded wait runs out
+
+__global__ void clear_error_kernel(uint32_t* error_word) { *error_word = 0u; }
+
+// Which form of the sequential kernel runs: 0 = mma.sync (two CTAs per head; the faster one today), 1 = tcgen05 (one
+// CTA per head, state in tensor memory).  Process-wide; starts from Q3X_B200_GDN_CHUNK_PATH ("tcgen05" selects 1).
+std::atomic<int>& chunk_path() {
+  static std::atomic<int> path{[] {
+    const char* text = std::getenv("Q3X_B200_GDN_CHUNK_PATH");
+    return text != nullptr && std::string(text) == "tcgen05" ? 1 : 0;
+  }()};
+  return path;
+}
+bool use_tcgen05() { return chunk_path().load(std::memory_order_relaxed) == 1; }
 
 int launch_chunked(const uint16_t* conv_qkv, size_t tokens, const uint16_t* a, const uint16_t* b, const uint16_t* A_log,
                    const uint16_t* dt_bias, const uint16_t* state_in, uint16_t* state_out, float l2_eps, uint16_t* out,
@@ -512,7 +822,7 @@ int launch_chunked(const uint16_t* conv_qkv, size_t tokens, const uint16_t* a, c
   if (conv_qkv == nullptr || a == nullptr || b == nullptr || A_log == nullptr || dt_bias == nullptr ||
       state_in == nullptr || state_out == nullptr || out == nullptr || workspace == nullptr)
     return kInvalid;
-  const size_t need = chunks_of(tokens) * kChunkBytes;
+  const size_t need = chunks_of(tokens) * kChunkBytes + kErrorSlot;
   if (workspace_bytes < need) return kInvalid;
   constexpr size_t kStateBytes = static_cast<size_t>(kValueHeads) * kHead * kHead * 2;
   const size_t out_bytes = tokens * kValueHeads * kHead * 2;
@@ -538,6 +848,9 @@ int launch_chunked(const uint16_t* conv_qkv, size_t tokens, const uint16_t* a, c
     if (e == cudaSuccess)
       e = cudaFuncSetAttribute(gdn_chunk_state_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                static_cast<int>(kStateShared));
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(tc::gdn_chunk_state_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(tc::kShared));
     return static_cast<int>(e);
   }();
   if (configured != kOk) return configured;
@@ -546,17 +859,31 @@ int launch_chunked(const uint16_t* conv_qkv, size_t tokens, const uint16_t* a, c
   if (ws.chunks > 0x7fffffffu) return kInvalid;
   gdn_chunk_prepare_kernel<<<dim3(static_cast<unsigned>(ws.chunks), kValueHeads), kPrepThreads, sizeof(PrepShared), s>>>(
       conv_qkv, tokens, a, b, A_log, dt_bias, l2_eps, ws);
-  gdn_chunk_state_kernel<<<dim3(kValueHeads, kStateSplits), kStateThreads, kStateShared, s>>>(ws, tokens, state_in,
-                                                                                             state_out, out);
+  uint32_t* error_word = reinterpret_cast<uint32_t*>(static_cast<unsigned char*>(workspace) + ws.chunks * kChunkBytes);
+  if (use_tcgen05()) {
+    clear_error_kernel<<<1, 1, 0, s>>>(error_word);
+    tc::gdn_chunk_state_tcgen05_kernel<<<kValueHeads, tc::kThreads, tc::kShared, s>>>(ws, tokens, state_in, state_out, out,
+                                                                                      error_word);
+  } else {
+    gdn_chunk_state_kernel<<<dim3(kValueHeads, kStateSplits), kStateThreads, kStateShared, s>>>(ws, tokens, state_in,
+                                                                                               state_out, out);
+  }
   return launch_status();
 }
 
 }  // namespace
 }  // namespace q3x
 
+extern "C" int q3x_b200_gated_delta_net_chunked_select_path(int path) {
+  if (path != 0 && path != 1) return q3x::host::kInvalid;
+  q3x::chunk_path().store(path, std::memory_order_relaxed);
+  return q3x::host::kOk;
+}
+
 extern "C" size_t q3x_b200_gated_delta_net_chunked_workspace_bytes(size_t tokens) {
   const size_t chunks = q3x::chunks_of(tokens);
-  return q3x::host::mul_overflows(chunks, q3x::kChunkBytes) ? 0 : chunks * q3x::kChunkBytes;
+  if (chunks == 0 || q3x::host::mul_overflows(chunks, q3x::kChunkBytes)) return 0;
+  return chunks * q3x::kChunkBytes + q3x::kErrorSlot;
 }
 
 extern "C" int q3x_b200_gated_delta_net_update_chunked(const uint16_t* conv_qkv, size_t tokens, const uint16_t* a,
