@@ -489,6 +489,13 @@ int q3x_b200_gqa_attention_prefill_sigmoid_gate(const uint16_t* query, const uin
                                                 const uint16_t* value_cache, const uint16_t* gate,
                                                 size_t first_position, size_t tokens, float scale, uint16_t* out,
                                                 void* stream);
+/* The prefill attention exists twice: path 1 on tcgen05 (the default: 128 tokens of one head per CTA, scores and
+ * output in tensor memory, the probabilities as two bf16 operands), path 0 on mma.sync.  Process-wide switch
+ * (the environment variable Q3X_B200_GQA_PREFILL_PATH = "mma" starts on path 0).  Path 1 bounds every wait on the
+ * tensor cores; q3x_b200_gqa_prefill_tcgen05_error synchronises and returns its sticky error word (0 = no wait ever
+ * ran out, -1 = the word could not be read). */
+int q3x_b200_gqa_prefill_select_path(int path);
+int q3x_b200_gqa_prefill_tcgen05_error(void);
 
 /* launch_bf16_gemv_reference_cuda / launch_bf16_gemv_bf16_cuda, launch_fp8_gemv_reference_cuda and
  * launch_nvfp4_gemv_reference_cuda (include/q3x/kernels/reference_gemv.h:64-130): batch-one projections

@@ -84,6 +84,8 @@ SIGNATURES = {
     "q3x_b200_gqa_decode_workspace_floats": (_z, [_z]),
     "q3x_b200_gqa_attention_decode_sigmoid_gate": (_i, [_p, _p, _p, _z, _f, _p, _z, _p, _p, _p]),
     "q3x_b200_gqa_attention_prefill_sigmoid_gate": (_i, [_p, _p, _p, _p, _z, _z, _f, _p, _p]),
+    "q3x_b200_gqa_prefill_select_path": (_i, [_i]),
+    "q3x_b200_gqa_prefill_tcgen05_error": (_i, []),
     "q3x_b200_softmax": (_i, [_p, _z, _z, _p, _p]),
     "q3x_b200_bf16_greedy_argmax": (_i, [_p, _z, _p, _p]),
 }

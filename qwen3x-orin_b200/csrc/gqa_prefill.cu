@@ -14,11 +14,14 @@
 // an ldmatrix fall into different banks.  The causal mask only touches tiles that reach past the block's first
 // token.  The epilogue normalises, rounds, applies the gate, and leaves through shared memory as 128-bit stores.
 // (The host reference keeps the probabilities in FP32; here each one meets V as a pair of bf16 operands, see below.)
+#include <atomic>
 #include <cstdlib>
+#include <string>
 
 #include "device_utils.cuh"
 #include "host_checks.hpp"
 #include "q3x_b200.h"
+#include "tcgen05.cuh"
 
 namespace q3x {
 namespace {
@@ -279,6 +282,244 @@ __global__ void __launch_bounds__(Shape<kWide>::kThreads, 1) gqa_prefill_kernel(
   }
 }
 
+// ================================================================================================================
+// The same attention on the fifth-generation tensor cores (tcgen05).  One CTA = 128 consecutive tokens of one query
+// head; thread r owns query row r, which is tensor-memory lane r, so the softmax of a row needs no exchange between
+// threads.  Per tile of 64 keys: S = Q K^T (M 128, N 64, K 256) into 64 columns of tensor memory; every thread reads
+// its row, masks, exponentiates against the row's reference maximum and leaves the probabilities in shared memory
+// as TWO bf16 A operands (rounding and remainder, as above); O += P V (M 128, N 256, K 64, twice) accumulates in 256
+// columns.  V is used as it lies in the cache ([key][dimension]: an MN-major B operand); K and Q are K-major.  The
+// reference maximum only moves when a tile exceeds it by more than 2^16 in the exponent's scale (then O and the row
+// sum are rescaled through tensor memory), so the accumulator is normally never touched between products.  S of the
+// next tile is issued together with P V of this one.  Every wait on the tensor cores is bounded; a wait that runs out
+// raises a sticky error word (q3x_b200_gqa_prefill_tcgen05_error) and the CTA frees its tensor memory and returns.
+// ================================================================================================================
+namespace tcattn {
+using namespace q3x::tcgen05;
+constexpr int kRows = 128, kThreads = 128, kKeys = 64;
+constexpr size_t kQ = 0;                                   // [128][256] bf16 in four blocks of [128][64]: 64 KB
+constexpr size_t kStages = 65536, kKVBytes = 32768, kStageBytes = 2 * kKVBytes;  // K then V: [64][256] in four blocks
+constexpr size_t kPHi = kStages + 2 * kStageBytes, kPLo = kPHi + 16384;          // [128][64] bf16 each
+constexpr size_t kBarrier = kPLo + 16384, kShared = kBarrier + 64;
+static_assert(kShared <= 227 * 1024, "one CTA per SM");
+constexpr uint32_t kColumnsS = 0, kColumnsO = 64, kColumnsAllocated = 512;
+constexpr float kRescaleThreshold = 16.0f;  // in units of the exponent (log2)
+
+__device__ unsigned int g_error = 0;
+
+__device__ __forceinline__ void request_tile(const uint16_t* key_cache, const uint16_t* value_cache, int kv, size_t first_key,
+                                             size_t keys, uint32_t stage) {
+  for (int i = threadIdx.x; i < kKeys * kRowChunks; i += kThreads) {
+    const int row = i / kRowChunks, piece = i % kRowChunks;
+    const size_t key = first_key + row;
+    const bool valid = key < keys;
+    const size_t element = ((valid ? key : 0) * kKvHeads + kv) * kDim + piece * 8;
+    const uint32_t at = static_cast<uint32_t>((piece >> 3) * (kKeys * 128) + row * 128 + (((piece & 7) ^ (row & 7)) << 4));
+    cp_async_16(stage + at, key_cache + element, valid);
+    cp_async_16(stage + static_cast<uint32_t>(kKVBytes) + at, value_cache + element, valid);
+  }
+}
+
+__global__ void __launch_bounds__(kThreads, 1) gqa_prefill_tcgen05_kernel(const uint16_t* __restrict__ query,
+                                                                          const uint16_t* __restrict__ key_cache,
+                                                                          const uint16_t* __restrict__ value_cache,
+                                                                          const uint16_t* __restrict__ gate, size_t first_position,
+                                                                          size_t tokens, float scale_log2e,
+                                                                          uint16_t* __restrict__ out) {
+  extern __shared__ __align__(1024) unsigned char shared[];
+  const uint32_t smem = static_cast<uint32_t>(__cvta_generic_to_shared(shared));
+  const int row = threadIdx.x, warp = threadIdx.x >> 5;
+  const int head = blockIdx.y, kv = head / kGroup;
+  const size_t token0 = static_cast<size_t>(gridDim.x - 1 - blockIdx.x) * kRows;  // heaviest blocks first
+  const size_t keys = first_position + min(token0 + kRows, tokens);               // visible to the CTA's last token
+  const int tiles = static_cast<int>((keys + kKeys - 1) / kKeys);
+  const size_t position = first_position + token0 + row;                          // a key is visible when key <= position
+  const uint32_t barrier = smem + static_cast<uint32_t>(kBarrier);
+  volatile uint32_t* base_slot = reinterpret_cast<volatile uint32_t*>(shared + kBarrier + 16);
+
+  // the queries (rows past the tile are zero) and the first K / V tile
+  for (int i = threadIdx.x; i < kRows * kRowChunks; i += kThreads) {
+    const int r = i / kRowChunks, piece = i % kRowChunks;
+    const size_t token = token0 + r;
+    const bool valid = token < tokens;
+    cp_async_16(smem + static_cast<uint32_t>(kQ + (piece >> 3) * (kRows * 128) + r * 128 + (((piece & 7) ^ (r & 7)) << 4)),
+                query + ((valid ? token : 0) * kQHeads + head) * kDim + piece * 8, valid);
+  }
+  request_tile(key_cache, value_cache, kv, 0, keys, smem + static_cast<uint32_t>(kStages));
+  cp_async_commit();
+  if (threadIdx.x == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(barrier) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem + static_cast<uint32_t>(kBarrier + 16)),
+                 "r"(kColumnsAllocated)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  cp_async_wait<0>();
+  fence_async_proxy();
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tmem = *base_slot;
+  const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+  if (threadIdx.x == 0) {
+    product(tmem + kColumnsS, smem + kQ, kRows * 128, smem + static_cast<uint32_t>(kStages), kKeys * 128, kDim,
+            instruction_descriptor(kKeys), false);
+    commit(barrier);
+  }
+
+  float reference = -INFINITY, row_sum = 0.0f;
+  uint32_t parity = 0;
+  bool healthy = true;
+  for (int tile = 0; tile < tiles; ++tile) {
+    const uint32_t stage = smem + static_cast<uint32_t>(kStages + (tile & 1) * kStageBytes);
+    healthy = __syncthreads_and(wait(barrier, parity)) != 0;  // S of this tile, P V of the previous one
+    parity ^= 1;
+    if (!healthy) break;
+    fence_after_sync();
+    // the other stage is free now: the next tile's keys and values
+    if (tile + 1 < tiles)
+      request_tile(key_cache, value_cache, kv, static_cast<size_t>(tile + 1) * kKeys, keys,
+                   smem + static_cast<uint32_t>(kStages + ((tile + 1) & 1) * kStageBytes));
+    cp_async_commit();
+
+    // ---- this row's 64 scores
+    float s[kKeys];
+    {
+      uint32_t raw[2][32];
+      load32(lane_base + kColumnsS, raw[0]);
+      load32(lane_base + kColumnsS + 32, raw[1]);
+      wait_loads();
+#pragma unroll
+      for (int e = 0; e < kKeys; ++e) s[e] = __uint_as_float(raw[e >> 5][e & 31]);
+    }
+    const size_t tile_key0 = static_cast<size_t>(tile) * kKeys;
+    if (tile_key0 + kKeys - 1 > first_position + token0) {  // (CTA-uniform) the tile reaches past the block's first token
+#pragma unroll
+      for (int e = 0; e < kKeys; ++e)
+        if (tile_key0 + e > position) s[e] = -INFINITY;
+    }
+    float tile_max = -INFINITY;
+#pragma unroll
+    for (int e = 0; e < kKeys; ++e) tile_max = fmaxf(tile_max, s[e]);
+    // ---- the reference maximum moves only when it has to; then O and the sum follow it
+    float factor = 1.0f;
+    bool moved = false;
+    if (reference == -INFINITY) {
+      reference = tile_max;  // (key 0 is visible to every row, so this is finite from the first tile on)
+    } else if ((tile_max - reference) * scale_log2e > kRescaleThreshold) {
+      factor = exp2_approx((reference - tile_max) * scale_log2e);
+      reference = tile_max;
+      row_sum *= factor;
+      moved = true;
+    }
+    if (tile > 0 && __any_sync(kFullMask, moved)) {
+#pragma unroll 1
+      for (int group = 0; group < kDim / 32; ++group) {
+        uint32_t o[32];
+        load32(lane_base + kColumnsO + group * 32, o);
+        wait_loads();
+#pragma unroll
+        for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * factor);
+        store32(lane_base + kColumnsO + group * 32, o);
+      }
+      wait_stores();
+    }
+    // ---- probabilities against the reference, as two bf16 operands; the sum takes them unrounded
+#pragma unroll
+    for (int piece = 0; piece < kKeys / 8; ++piece) {
+      uint32_t hi[4], lo[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float first = exp2_approx((s[piece * 8 + 2 * j] - reference) * scale_log2e);
+        const float second = exp2_approx((s[piece * 8 + 2 * j + 1] - reference) * scale_log2e);
+        row_sum += first + second;
+        hi[j] = pack_bf16x2(first, second);
+        lo[j] = pack_bf16x2(first - bf16_lo(hi[j]), second - bf16_hi(hi[j]));
+      }
+      const uint32_t at = static_cast<uint32_t>(row * 128 + ((piece ^ (row & 7)) << 4));
+      *reinterpret_cast<uint4*>(shared + kPHi + at) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+      *reinterpret_cast<uint4*>(shared + kPLo + at) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+    }
+    cp_async_wait<0>();  // the next tile's keys have to be there before its scores are issued
+    fence_async_proxy();
+    fence_before_sync();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      fence_after_sync();
+      const uint32_t values = stage + static_cast<uint32_t>(kKVBytes);
+      constexpr uint32_t kIdescPV = instruction_descriptor(kDim) | kBOperandMnMajor;
+#pragma unroll
+      for (int step = 0; step < kKeys / 16; ++step)
+        mma(tmem + kColumnsO, operand_descriptor(smem + static_cast<uint32_t>(kPHi) + step * 32),
+            operand_descriptor_mn(values + step * 2048, kKeys * 128), kIdescPV, (tile > 0 || step > 0) ? 1u : 0u);
+#pragma unroll
+      for (int step = 0; step < kKeys / 16; ++step)
+        mma(tmem + kColumnsO, operand_descriptor(smem + static_cast<uint32_t>(kPLo) + step * 32),
+            operand_descriptor_mn(values + step * 2048, kKeys * 128), kIdescPV, 1u);
+      if (tile + 1 < tiles)
+        product(tmem + kColumnsS, smem + kQ, kRows * 128, smem + static_cast<uint32_t>(kStages + ((tile + 1) & 1) * kStageBytes),
+                kKeys * 128, kDim, instruction_descriptor(kKeys), false);
+      commit(barrier);
+    }
+  }
+  if (healthy) {
+    healthy = __syncthreads_and(wait(barrier, parity)) != 0;  // the last P V
+    fence_after_sync();
+  }
+  cp_async_wait<0>();
+  if (!healthy) {
+    if (threadIdx.x == 0) atomicExch(&g_error, 1u);
+  } else {
+    // ---- epilogue: normalise, round, gate, round; this thread's row, 512 contiguous bytes.  (The tensor-memory loads
+    // are warp-collective: every lane executes them, a lane whose row lies past the tile just stores nothing.)
+    const bool stores = token0 + row < tokens;
+    const float inverse = 1.0f / row_sum;
+    const size_t base = ((stores ? token0 + row : 0) * kQHeads + head) * kDim;
+#pragma unroll 1
+    for (int group = 0; group < kDim / 32; ++group) {
+      uint32_t o[32];
+      load32(lane_base + kColumnsO + group * 32, o);
+      wait_loads();
+      if (stores) {
+#pragma unroll
+        for (int piece = 0; piece < 4; ++piece) {
+          float v[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(o[piece * 8 + e]) * inverse;
+          uint4 value = pack8(v);
+          if (gate != nullptr) {
+            float z[8];
+            unpack8(value, v);
+            unpack8(ld_stream(gate + base + group * 32 + piece * 8), z);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] = v[e] * stable_sigmoid(z[e]);
+            value = pack8(v);
+          }
+          st_vec(out + base + group * 32 + piece * 8, value);
+        }
+      }
+    }
+  }
+  fence_before_sync();
+  __syncthreads();
+  if (warp == 0)
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kColumnsAllocated) : "memory");
+}
+}  // namespace tcattn
+
+// Which kernel serves the entry point: 1 = tcgen05 (the default: 1.5 to 2 times the other from a thousand tokens on,
+// level with it below), 0 = mma.sync (two CTA shapes).  Process-wide; Q3X_B200_GQA_PREFILL_PATH = "mma" starts on 0.
+std::atomic<int>& prefill_path() {
+  static std::atomic<int> path{[] {
+    const char* text = std::getenv("Q3X_B200_GQA_PREFILL_PATH");
+    return text != nullptr && std::string(text) == "mma" ? 0 : 1;
+  }()};
+  return path;
+}
+
 }  // namespace
 }  // namespace q3x
 
@@ -310,6 +551,9 @@ extern "C" int q3x_b200_gqa_attention_prefill_sigmoid_gate(const uint16_t* query
     if (e == cudaSuccess)
       e = cudaFuncSetAttribute(gqa_prefill_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                static_cast<int>(shared_bytes<true>()));
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(tcattn::gqa_prefill_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(tcattn::kShared));
     return e;
   }();
   if (attribute != cudaSuccess) {
@@ -324,7 +568,11 @@ extern "C" int q3x_b200_gqa_attention_prefill_sigmoid_gate(const uint16_t* query
     const char* text = std::getenv("Q3X_B200_GQA_WIDE_FROM");
     return text != nullptr ? static_cast<size_t>(std::strtoull(text, nullptr, 10)) : static_cast<size_t>(4096);
   }();
-  if (tokens >= wide_from) {
+  if (prefill_path().load(std::memory_order_relaxed) == 1) {
+    const unsigned blocks = static_cast<unsigned>((tokens + tcattn::kRows - 1) / tcattn::kRows);
+    tcattn::gqa_prefill_tcgen05_kernel<<<dim3(blocks, kQHeads), tcattn::kThreads, tcattn::kShared, as_stream(stream)>>>(
+        query, key_cache, value_cache, gate, first_position, tokens, scale_log2e, out);
+  } else if (tokens >= wide_from) {
     const unsigned blocks = static_cast<unsigned>((tokens + Shape<true>::kCtaTokens - 1) / Shape<true>::kCtaTokens);
     gqa_prefill_kernel<true><<<dim3(blocks, kQHeads), Shape<true>::kThreads, shared_bytes<true>(), as_stream(stream)>>>(
         query, key_cache, value_cache, gate, first_position, tokens, scale_log2e, out);
@@ -334,4 +582,16 @@ extern "C" int q3x_b200_gqa_attention_prefill_sigmoid_gate(const uint16_t* query
         query, key_cache, value_cache, gate, first_position, tokens, scale_log2e, out);
   }
   return launch_status();
+}
+
+extern "C" int q3x_b200_gqa_prefill_select_path(int path) {
+  if (path != 0 && path != 1) return kInvalid;
+  prefill_path().store(path, std::memory_order_relaxed);
+  return kOk;
+}
+
+extern "C" int q3x_b200_gqa_prefill_tcgen05_error(void) {
+  unsigned int word = 0;
+  if (cudaMemcpyFromSymbol(&word, tcattn::g_error, sizeof(word)) != cudaSuccess) return -1;
+  return static_cast<int>(word);
 }

@@ -127,7 +127,9 @@ def assert_reference_tolerance(got, want, what="", amplified=False):
     assert bad.size <= allowed, (f"{what}: {bad.size} of {err.size} elements beyond max(2e-3, 8e-3|e|) ({allowed} allowed); "
                                  f"worst {err[bad].max():.3e} at expected {e[fin][bad[np.argmax(err[bad])]]:.6g}")
     if bad.size:
-        hard = 2.0 ** -7 * row_scale[fin][bad]
+        # two bf16 ulps AT the row's largest magnitude m: 2 * 2^(floor(log2 m) - 7), which lies between 2^-7 m and 2^-6 m
+        scale = np.maximum(row_scale[fin][bad], 2.0 ** -120)
+        hard = 2.0 * 2.0 ** (np.floor(np.log2(scale)) - 7.0)
         assert np.all(err[bad] <= hard), f"{what}: an element differs by more than two ulps of its row's magnitude"
 
 

@@ -68,27 +68,91 @@ def test_prefill_attention_matches_the_per_token_reference(g, tokens, first, gat
 
 
 def test_prefill_attention_of_a_long_tile_on_sampled_tokens(g):
-    """Tiles of 4096 tokens and more run in the wide CTA shape (eight 16-token blocks of one query head per CTA): a
-    4133-token tile appended at position 50 (the last CTA holds 37 tokens: two full blocks, a partial one and five idle
-    warps), checked against the per-token oracle on sampled tokens, block edges and the tile's two ends."""
+    """A 4133-token tile appended at position 50 (33 CTAs of 128 tokens on the tcgen05 path, the last one holding 37;
+    on the mma.sync path this length takes the wide CTA shape), checked against the per-token oracle on sampled tokens,
+    block edges and the tile's two ends -- on both paths."""
     rng = np.random.default_rng(119)
     tokens, first = 4133, 50
     length = first + tokens
     q = fx.normal_bf16(rng, (tokens, 24, 256))
     kc, vc = fx.normal_bf16(rng, (length, 4, 256)), fx.normal_bf16(rng, (length, 4, 256))
     gate = fx.normal_bf16(rng, (tokens, 24, 256), 2.0)
-    out = g.empty_like_dev((tokens, 24, 256))
-    g.capi.check("q3x_b200_gqa_attention_prefill_sigmoid_gate", g.Dev(q), g.Dev(kc), g.Dev(vc), g.Dev(gate), first, tokens,
-                 SCALE, out, None)
-    g.sync()
-    assert out.guards_intact()
     picks = sorted(set([0, 1, 15, 16, 127, 128, 129, 2047, 2048, 4095, 4096, 4111, 4112, 4127, 4128, 4131, 4132]) |
                    set(int(t) for t in rng.choice(tokens, size=48, replace=False)))
-    got = out.get()[picks]
     want = np.stack([orc.gqa_attention(q[t], kc[:first + t + 1], vc[:first + t + 1], SCALE, gate=gate[t])[0] for t in picks])
-    g.assert_sum_within(got, want, 3, 1e-5, 0.98, "prefill attention, long tile")
-    g.assert_reference_tolerance(got, want, "prefill attention, long tile", amplified=True)
-    assert bool(np.isfinite(orc.bf16_decode(out.get())).all())
+    d_q, d_k, d_v, d_g = g.Dev(q), g.Dev(kc), g.Dev(vc), g.Dev(gate)
+    for path in (1, 0):
+        out = g.empty_like_dev((tokens, 24, 256))
+        g.capi.check("q3x_b200_gqa_prefill_select_path", path)
+        try:
+            g.capi.check("q3x_b200_gqa_attention_prefill_sigmoid_gate", d_q, d_k, d_v, d_g, first, tokens, SCALE, out, None)
+            g.sync()
+        finally:
+            g.capi.check("q3x_b200_gqa_prefill_select_path", 1)
+        assert out.guards_intact()
+        got = out.get()[picks]
+        g.assert_sum_within(got, want, 3, 1e-5, 0.98, f"prefill attention, long tile, path {path}")
+        g.assert_reference_tolerance(got, want, f"prefill attention, long tile, path {path}", amplified=True)
+        assert bool(np.isfinite(orc.bf16_decode(out.get())).all())
+    assert g.capi.lib().q3x_b200_gqa_prefill_tcgen05_error() == 0
+
+
+@pytest.mark.parametrize("path", [1, 0])
+def test_prefill_attention_with_rising_scores(g, path):
+    """Scores that climb by about 30 (in units of the exponent, log2) per 64-key tile: the running maximum of every row
+    keeps moving, which on the tcgen05 path (1) makes the reference maximum jump and the accumulator in tensor memory
+    be rescaled several times per row, and on the mma.sync path (0) exercises the per-tile correction.  Both against the
+    per-token oracle; and the tcgen05 path's error word stays clear."""
+    rng = np.random.default_rng(121)
+    tokens, first = 300, 40
+    length = first + tokens
+    q = orc.bf16_encode(np.ones((tokens, 24, 256), np.float32) + 0.05 * rng.standard_normal((tokens, 24, 256)).astype(np.float32))
+    ramp = (np.arange(length, dtype=np.float32) * 0.02)[:, None, None]           # q . k grows by 5.1 per key
+    kc = orc.bf16_encode(ramp * np.ones((length, 4, 256), np.float32) + 0.05 * rng.standard_normal((length, 4, 256)).astype(np.float32))
+    vc = fx.normal_bf16(rng, (length, 4, 256))
+    gate = fx.normal_bf16(rng, (tokens, 24, 256), 2.0)
+    out = g.empty_like_dev((tokens, 24, 256))
+    g.capi.check("q3x_b200_gqa_prefill_select_path", path)
+    try:
+        g.capi.check("q3x_b200_gqa_attention_prefill_sigmoid_gate", g.Dev(q), g.Dev(kc), g.Dev(vc), g.Dev(gate), first, tokens,
+                     SCALE, out, None)
+        g.sync()
+    finally:
+        g.capi.check("q3x_b200_gqa_prefill_select_path", 1)
+    assert out.guards_intact()
+    assert g.capi.lib().q3x_b200_gqa_prefill_tcgen05_error() == 0
+    want = expected(q, kc, vc, gate, first)
+    g.assert_sum_within(out.get(), want, 3, 1e-5, 0.98, "prefill attention, rising scores")
+    g.assert_reference_tolerance(out.get(), want, "prefill attention, rising scores", amplified=True)
+
+
+def test_both_prefill_attention_paths_agree(g):
+    """The mma.sync path on the inputs of the first test's largest case, against the tcgen05 path (the default, which
+    every other test here runs): same operands, sums in another order."""
+    rng = np.random.default_rng(122)
+    tokens, first = 700, 100
+    length = first + tokens
+    q = fx.normal_bf16(rng, (tokens, 24, 256))
+    kc, vc = fx.normal_bf16(rng, (length, 4, 256)), fx.normal_bf16(rng, (length, 4, 256))
+    gate = fx.normal_bf16(rng, (tokens, 24, 256), 2.0)
+    outs = []
+    for path in (1, 0):
+        out = g.empty_like_dev((tokens, 24, 256))
+        g.capi.check("q3x_b200_gqa_prefill_select_path", path)
+        try:
+            g.capi.check("q3x_b200_gqa_attention_prefill_sigmoid_gate", g.Dev(q), g.Dev(kc), g.Dev(vc), g.Dev(gate), first,
+                         tokens, SCALE, out, None)
+            g.sync()
+        finally:
+            g.capi.check("q3x_b200_gqa_prefill_select_path", 1)
+        outs.append(out.get())
+    assert g.capi.lib().q3x_b200_gqa_prefill_tcgen05_error() == 0
+    assert np.mean(outs[0] == outs[1]) > 0.99
+    # (both round the same FP32 weighted averages summed in another order: one ulp apart where they differ, two behind
+    # the gate at the bottom of a binade -- the rule of the oracle comparison above, one path standing in for the oracle)
+    g.assert_sum_within(outs[0], outs[1], 3, 1e-5, 0.99, "tcgen05 against mma.sync")
+    g.assert_reference_tolerance(outs[0], outs[1], "tcgen05 against mma.sync", amplified=True)
+    assert g.capi.call("q3x_b200_gqa_prefill_select_path", 3) == 1
 
 
 def test_prefill_attention_equals_decode_attention_on_its_last_token(g):
