@@ -121,3 +121,45 @@ def test_host_side_argument_checks(capi):
     assert capi.lib().q3x_b200_nvfp4_group_count(513, 512) == 2
     assert capi.lib().q3x_b200_nvfp4_group_count(513, 0) == 1
     assert capi.lib().q3x_b200_nvfp4_group_count(0, 512) == 0
+
+
+def test_host_side_argument_checks_of_the_tensor_core_entries(capi):
+    """The panel projections, the chunked recurrence and the path switches: everything these refuse they refuse on the
+    host, before any CUDA call (so this runs without a GPU)."""
+    c, L = capi.call, capi.lib()
+    B = A + (1 << 30)
+    # dense scaled projection and the exact widenings that feed it
+    assert c("q3x_b200_bf16_gemm_scaled_bf16", A, float("nan"), B, 64, 64, 128, B + (1 << 24), None, 0, None) == INVALID
+    assert c("q3x_b200_bf16_gemm_scaled_bf16", A, 1.0, B, 64, 60, 128, B + (1 << 24), None, 0, None) == INVALID   # N % 8
+    assert c("q3x_b200_bf16_gemm_scaled_bf16", A, 1.0, B, 64, 64, 100, B + (1 << 24), None, 0, None) == INVALID   # K % 8
+    assert c("q3x_b200_bf16_gemm_scaled_bf16", A, 1.0, B, 64, 64, 128, A + 64, None, 0, None) == INVALID          # out on W
+    assert c("q3x_b200_bf16_gemm_scaled_bf16", None, 1.0, B, 64, 64, 128, B + (1 << 24), None, 0, None) == INVALID
+    assert c("q3x_b200_bf16_gemm_scaled_bf16", A, 1.0, B, 0, 64, 128, B + (1 << 24), None, 0, None) == OK
+    assert c("q3x_b200_fp8_weights_to_bf16", A, 24, B, None) == INVALID            # whole 16-element vectors only
+    assert c("q3x_b200_fp8_weights_to_bf16", A, 64, A + 32, None) == INVALID        # overlap
+    assert c("q3x_b200_fp8_weights_to_bf16", None, 64, B, None) == INVALID
+    assert c("q3x_b200_fp8_weights_to_bf16", A, 0, B, None) == OK
+    assert c("q3x_b200_nvfp4_weights_to_bf16", A, B, 8, 24, B + (1 << 24), None) == INVALID    # cols % 16
+    assert c("q3x_b200_nvfp4_weights_to_bf16", A, B, 8, 32, A + 64, None) == INVALID           # out on the codes
+    assert c("q3x_b200_nvfp4_weights_to_bf16", A, None, 8, 32, B + (1 << 24), None) == INVALID
+    assert c("q3x_b200_nvfp4_weights_to_bf16", A, B, 0, 32, B + (1 << 24), None) == OK
+    # chunked recurrence: workspace arithmetic and refusals
+    one = L.q3x_b200_gated_delta_net_chunked_workspace_bytes(64)
+    assert one > 0 and L.q3x_b200_gated_delta_net_chunked_workspace_bytes(1) == one
+    assert L.q3x_b200_gated_delta_net_chunked_workspace_bytes(65) == 2 * (one - 256) + 256
+    assert L.q3x_b200_gated_delta_net_chunked_workspace_bytes(0) == 0
+    state, ws = A + (1 << 26), B + (1 << 28)
+    chunked = lambda **kw: c("q3x_b200_gated_delta_net_update_chunked", A, kw.get("tokens", 64), A + (1 << 22), A + (1 << 23),
+                             A + (1 << 24), A + (1 << 24) + 4096, state, kw.get("state_out", state), kw.get("eps", 1e-6),
+                             kw.get("out", B), kw.get("ws", ws), kw.get("ws_bytes", one), None)
+    assert chunked(ws_bytes=one - 16) == INVALID
+    assert chunked(ws=None) == INVALID
+    assert chunked(eps=0.0) == INVALID
+    assert chunked(out=state) == INVALID
+    assert chunked(state_out=state + 64) == INVALID   # partial overlap of the two states
+    assert chunked(ws=B) == INVALID                   # workspace on the output
+    assert chunked(tokens=0) == OK
+    # path switches take 0 or 1
+    for name in ("q3x_b200_gated_delta_net_chunked_select_path", "q3x_b200_gqa_prefill_select_path"):
+        assert c(name, 2) == INVALID and c(name, -1) == INVALID
+    assert c("q3x_b200_gated_delta_net_chunked_select_path", 0) == OK and c("q3x_b200_gqa_prefill_select_path", 1) == OK
