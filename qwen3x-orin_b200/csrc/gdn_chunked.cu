@@ -11,9 +11,10 @@
 //     M_64 = G_64 M_0 + (diag(G_64 / G) K)^T D
 // so everything that does not involve M_0 is computed for all chunks in parallel (first kernel: q / k normalisation,
 // the two 64 x 64 Gram matrices on the tensor cores, the triangular solves in FP32 registers, one thread per column
-// of W or U), and only three small products per chunk stay on the sequential path (second kernel: the state of a
-// head, split over two CTAs by value rows, lives in the accumulators of four warps; its operands stream through a
-// two-stage shared-memory pipeline).  Operands of the tensor-core products are bf16 with FP32 accumulation, the
+// of W and of U), and only a few small products per chunk stay on the sequential path, which exists in two forms:
+// with the state of a head, split over two CTAs by value rows, in the accumulators of mma.sync products (the default),
+// and with the state in tensor memory and tcgen05 products issued from shared-memory descriptors; either way the
+// chunk's operands stream through a two-stage shared-memory pipeline from images the first kernel wrote.  Operands of the tensor-core products are bf16 with FP32 accumulation, the
 // reference's own boundaries for this form; the state between chunks stays FP32 and is rounded once, on the way out.
 // Against the token-sequential form, which rounds the state to bf16 after every token, results agree to the noise of
 // that rounding, not bit for bit (the reference reports the same comparison as a characterisation, tests/
